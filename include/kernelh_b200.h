@@ -1,0 +1,184 @@
+/*
+ * kernelh_b200 - C ABI of the B200 (sm_100a) implementation of kernel.h's
+ * seven launched kernel templates.
+ *
+ * This header is the drop-in boundary. kernel.h itself is a C++23 program with
+ * no foreign-function interface; what a replacement of its launch path must
+ * offer is (a) the kernel-name + shape-map operator surface of its template
+ * registry and CLI, (b) its runtime's launch objects, and (c) the pure host
+ * helpers its harness and tests use. Each entry point below names the
+ * reference interface it stands in for (paths relative to the reference
+ * project root). All pointers are plain pointers, all sizes plain integers.
+ *
+ * Conventions
+ *   - Every function returns 0 on success. 77 means "no usable CUDA driver or
+ *     device" (the reference's skip code, include/kernelh/runtime/
+ *     runtime_error.hpp:15-20), 2 means a usage error (unknown kernel, bad
+ *     shape, wrong buffer count), 1001 means a device-side bounded wait ran
+ *     out, any other value is the driver's error code.
+ *   - kh_last_error() returns the message of the calling thread's last failure.
+ *   - Tensors are fp32, row-major, contiguous. Device-pointer calls enqueue on
+ *     `stream` (a CUstream / cudaStream_t, NULL = default stream) and return
+ *     without waiting. There is no CPU path: without a B200 the compute calls
+ *     fail with 77 or the driver's error.
+ *   - A context is bound to one device and is not thread-safe; scratch memory
+ *     (operand splits, scan state) belongs to the context, so launches of one
+ *     context must not overlap on the GPU across streams.
+ */
+#ifndef KERNELH_B200_H
+#define KERNELH_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct kh_context kh_context;
+
+const char *kh_last_error(void);
+const char *kh_version(void);
+
+/* ---- device context -------------------------------------------------------
+ * make_cuda_backend() + DeviceContext::create(backend, ordinal)
+ * (include/kernelh/runtime/backend.hpp:98-104, device_context.hpp:22-23). */
+int kh_context_create(int device_ordinal, kh_context **out);
+void kh_context_destroy(kh_context *ctx);
+int kh_device_count(int *count);
+/* DeviceInfo (include/kernelh/runtime/backend.hpp:32-39) plus the B200 fields. */
+typedef struct {
+  char name[256];
+  int64_t vram_bytes;
+  int64_t static_smem_per_block;
+  int64_t optin_smem_per_block;
+  int64_t smem_per_sm;
+  int64_t l2_bytes;
+  int32_t sm_count;
+  int32_t warp_size;
+  int32_t max_threads_per_block;
+  int32_t regs_per_sm;
+  int32_t max_blocks_per_sm;
+  int32_t cc_major;
+  int32_t cc_minor;
+  int32_t ordinal;
+} kh_device_info;
+int kh_device_info_get(kh_context *ctx, kh_device_info *out);
+
+/* ---- operator surface: kernel name + shape --------------------------------
+ * program().kernel(name).shape(map) (include/kernelh/dsl/program.hpp:85-149)
+ * followed by the runtime launch the reference's callers do by hand
+ * (bench/harness/kernelh_backend.cpp:205-436). `shape` is the CLI text
+ * "k=v,k=v" (tools/kernelh/main.cpp:242-266). Buffers are passed in template
+ * order:
+ *   vecadd     n                       a, b, c
+ *   fused_gelu n | rows,cols [bias=1]  x, tmp (may be NULL), out | x, bias, out
+ *   scan       n                       x, y
+ *   softmax    rows, cols              x, y
+ *   layernorm  rows, cols              x, gamma, beta, y
+ *   gemm       m, n, k                 A, B, C
+ *   attention  batch, heads, seq, head_dim   Q, K, V, O
+ * Launch geometry and scratch are chosen by the library. */
+int kh_launch(kh_context *ctx, const char *kernel, const char *shape, void *const *device_buffers,
+              int n_buffers, void *stream);
+/* Same call on host buffers: inputs are copied to the device, the kernel runs,
+ * outputs are copied back; blocking. This is the path the reference's
+ * end-to-end checks take (Buffer::copy_from_host, launch, copy_to_host:
+ * test/unit/e2e_gemm_test.cpp:130-206). */
+int kh_run_host(kh_context *ctx, const char *kernel, const char *shape, void *const *host_buffers,
+                int n_buffers);
+/* Waits for `stream` and reports a device-side wait that ran out (1001). */
+int kh_synchronize(kh_context *ctx, void *stream);
+
+/* Typed forms of kh_launch, one per template (lib/dsl/kernels/<name>.cpp). */
+int kh_vecadd(kh_context *ctx, const float *a, const float *b, float *c, int64_t n, void *stream);
+int kh_fused_gelu(kh_context *ctx, const float *x, float *out, int64_t n, void *stream);
+int kh_fused_gelu_bias(kh_context *ctx, const float *x, const float *bias, float *out, int64_t n,
+                       void *stream);
+int kh_scan(kh_context *ctx, const float *x, float *y, int64_t n, void *stream);
+int kh_softmax(kh_context *ctx, const float *x, float *y, int64_t rows, int64_t cols, void *stream);
+int kh_layernorm(kh_context *ctx, const float *x, const float *gamma, const float *beta, float *y,
+                 int64_t rows, int64_t cols, void *stream);
+int kh_gemm(kh_context *ctx, const float *a, const float *b, float *c, int64_t m, int64_t n,
+            int64_t k, void *stream);
+int kh_attention(kh_context *ctx, const float *q, const float *k, const float *v, float *o,
+                 int64_t batch, int64_t heads, int64_t seq, int64_t head_dim, void *stream);
+
+/* Device memory of the context's device (Buffer::allocate / copy_from_host /
+ * copy_to_host, include/kernelh/runtime/buffer.hpp). */
+int kh_malloc(kh_context *ctx, size_t bytes, void **out);
+int kh_free(kh_context *ctx, void *ptr);
+int kh_memcpy_h2d(kh_context *ctx, void *dst, const void *src, size_t bytes);
+int kh_memcpy_d2h(kh_context *ctx, void *dst, const void *src, size_t bytes);
+
+/* One timed bench row: warm-up launches, then the median of `iters`
+ * event-timed launches (bench/harness/timer.cpp:29-67), and the rate by the
+ * reference's metric formulas (bench/harness/metrics.cpp:14-52). Buffers are
+ * allocated by the library and filled with a fixed pattern. */
+int kh_bench_row(kh_context *ctx, const char *kernel, const char *shape, int warmup, int iters,
+                 double *ms_median, double *rate, int *rate_is_gflops);
+
+/* ---- registry ----------------------------------------------------------------
+ * registeredKernels() and the unknown-name error of emit()
+ * (lib/dsl/registry.cpp:23-42, lib/dsl/program.cpp:27-37). */
+int kh_registered_kernels(char *buf, int cap); /* comma separated, sorted */
+/* The launch plan for a shape on a device-limits token ("sm_100a"): counts of
+ * caller buffers, scratch bytes, launches, and the main launch's geometry. */
+typedef struct {
+  int32_t n_buffers;
+  int32_t n_launches;
+  int64_t workspace_bytes;
+  char entry[64];          /* entry symbol of the last (main) launch */
+  uint32_t grid[3];
+  uint32_t block[3];
+  int64_t dynamic_smem;
+  int32_t param_count;     /* kernel parameters of the main launch */
+  int32_t tmem_columns;
+  double work;             /* flops or bytes per the reference's conventions */
+  int32_t work_is_flops;
+} kh_plan_info;
+int kh_plan(const char *kernel, const char *shape, const char *target_token, int sm_count,
+            kh_plan_info *out);
+/* The embedded sm_100a code object that holds a kernel's entry symbols (what
+ * `kernelh compile --target nvptx-sm_100a` writes as <name>.cubin). */
+int kh_kernel_image(const char *kernel, const void **image, size_t *size);
+
+/* ---- host helpers ----------------------------------------------------------------
+ * LaunchArgs::add_memref (lib/runtime/descriptor_packing.cpp:19-39): packs
+ * `count` buffers; shapes are concatenated, ranks[i] dims each. Returns the
+ * slot count through *n_slots. */
+int kh_pack_memrefs(const uint64_t *ptrs, const int64_t *shapes, const int *ranks, int count,
+                    uint64_t *slots, int cap, int *n_slots);
+/* device_limits_for(token) (lib/compiler/device_limits.cpp:122-134). fields:
+ * lds, warp, max_threads, grid x/y/z, vram, warps_per_sm, regs_per_sm, sms,
+ * optin_smem, smem_per_sm, max_blocks_per_sm, tmem_columns. */
+int kh_device_limits(const char *token, int64_t *fields14, char *name, int name_cap);
+/* CLI target -> table token (tools/kernelh/main.cpp:375-390); 2 if unknown,
+ * with the list of valid targets in kh_last_error(). */
+int kh_target_token(const char *cli_target, char *buf, int cap);
+/* LaunchVerifier::verify (lib/compiler/launch_verifier.cpp:109-172): 0 when
+ * launchable, 1 with every violation, one per line, in `msg`. */
+int kh_verify_launch(const char *token, int threads, int gx, int gy, int gz, uint64_t static_smem,
+                     uint64_t dynamic_smem, int warps_per_sm_override, char *msg, int cap);
+/* occupancy_report (lib/compiler/occupancy.cpp:124-223). out5: register-limited
+ * warps, smem-limited blocks, thread-limited blocks, achieved, limiter
+ * (0 none, 1 vgpr, 2 lds, 3 threads); sm3: resident blocks per SM, per-SM
+ * occupancy percent x 100, limiter index (0 none, 1 registers, 2 shared
+ * memory, 3 warps, 4 block cap, 5 tensor memory). */
+int kh_occupancy(const char *token, int regs, int64_t static_smem, int threads, int64_t dynamic_smem,
+                 int tmem_columns, int *out5, double *theoretical_pct, int *sm3);
+/* bench/harness/metrics.cpp:14-52 by name ("gemm_flops", "scan_bytes", ...). */
+double kh_metric(const char *what, int64_t a, int64_t b, int64_t c, int64_t d);
+double kh_rate(int gflops, double work, double ms);
+/* bench/harness/csv.cpp:9-57. */
+int kh_csv_header(char *buf, int cap);
+int kh_csv_line(const char *kernel, const char *shape, const char *backend, double ms, double rate,
+                const char *timestamp, const char *device, char *buf, int cap);
+/* parse_shape_text + shape_to_text (bench/harness/shape_text.cpp:10-44). */
+int kh_shape_roundtrip(const char *text, char *buf, int cap);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* KERNELH_B200_H */

@@ -1,0 +1,325 @@
+"""kernelh_b200: kernel.h's seven launched kernel templates, hand-written for
+NVIDIA B200 (sm_100a), behind kernel.h's kernel-name + shape operator surface.
+
+This module is a thin ctypes binding of the C ABI in ``include/kernelh_b200.h``
+(``libkernelh_b200.so``, built in-tree by ``kernelh_b200.build``). It mirrors
+the reference's host interface: a device context, ``launch(kernel, shape,
+buffers)`` with the CLI's ``k=v,k=v`` shape text, the launch verifier, the
+device-limits table, the occupancy model, bench metrics and the results CSV
+line. There is no CPU implementation behind any compute call: without the
+native library this import fails, and without a B200 the compute calls raise.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+_PKG = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_PKG, "libkernelh_b200.so")
+
+DRIVER_UNAVAILABLE = 77
+USAGE_ERROR = 2
+DEVICE_TIMEOUT = 1001
+
+KERNELS = ("attention", "fused_gelu", "gemm", "layernorm", "scan", "softmax", "vecadd")
+
+
+class KernelhError(RuntimeError):
+    def __init__(self, code: int, message: str):
+        super().__init__(f"[{code}] {message}")
+        self.code = code
+        self.message = message
+
+
+class DeviceInfo(C.Structure):
+    _fields_ = [("name", C.c_char * 256), ("vram_bytes", C.c_int64),
+                ("static_smem_per_block", C.c_int64), ("optin_smem_per_block", C.c_int64),
+                ("smem_per_sm", C.c_int64), ("l2_bytes", C.c_int64), ("sm_count", C.c_int32),
+                ("warp_size", C.c_int32), ("max_threads_per_block", C.c_int32),
+                ("regs_per_sm", C.c_int32), ("max_blocks_per_sm", C.c_int32),
+                ("cc_major", C.c_int32), ("cc_minor", C.c_int32), ("ordinal", C.c_int32)]
+
+
+class PlanInfo(C.Structure):
+    _fields_ = [("n_buffers", C.c_int32), ("n_launches", C.c_int32),
+                ("workspace_bytes", C.c_int64), ("entry", C.c_char * 64),
+                ("grid", C.c_uint32 * 3), ("block", C.c_uint32 * 3), ("dynamic_smem", C.c_int64),
+                ("param_count", C.c_int32), ("tmem_columns", C.c_int32), ("work", C.c_double),
+                ("work_is_flops", C.c_int32)]
+
+
+def _load() -> C.CDLL:
+    if not os.path.exists(LIB_PATH):
+        raise ImportError(
+            f"{LIB_PATH} is missing: build it with `python -m kernelh_b200.build` "
+            "(needs nvcc and g++); there is no fallback implementation")
+    L = C.CDLL(LIB_PATH)
+    vp, i64, f32p = C.c_void_p, C.c_int64, C.c_void_p
+    L.kh_last_error.restype = C.c_char_p
+    L.kh_version.restype = C.c_char_p
+    L.kh_context_create.argtypes = [C.c_int, C.POINTER(vp)]
+    L.kh_context_destroy.argtypes = [vp]
+    L.kh_context_destroy.restype = None
+    L.kh_device_count.argtypes = [C.POINTER(C.c_int)]
+    L.kh_device_info_get.argtypes = [vp, C.POINTER(DeviceInfo)]
+    L.kh_launch.argtypes = [vp, C.c_char_p, C.c_char_p, C.POINTER(vp), C.c_int, vp]
+    L.kh_run_host.argtypes = [vp, C.c_char_p, C.c_char_p, C.POINTER(vp), C.c_int]
+    L.kh_synchronize.argtypes = [vp, vp]
+    L.kh_vecadd.argtypes = [vp, f32p, f32p, f32p, i64, vp]
+    L.kh_fused_gelu.argtypes = [vp, f32p, f32p, i64, vp]
+    L.kh_fused_gelu_bias.argtypes = [vp, f32p, f32p, f32p, i64, vp]
+    L.kh_scan.argtypes = [vp, f32p, f32p, i64, vp]
+    L.kh_softmax.argtypes = [vp, f32p, f32p, i64, i64, vp]
+    L.kh_layernorm.argtypes = [vp, f32p, f32p, f32p, f32p, i64, i64, vp]
+    L.kh_gemm.argtypes = [vp, f32p, f32p, f32p, i64, i64, i64, vp]
+    L.kh_attention.argtypes = [vp, f32p, f32p, f32p, f32p, i64, i64, i64, i64, vp]
+    L.kh_malloc.argtypes = [vp, C.c_size_t, C.POINTER(vp)]
+    L.kh_free.argtypes = [vp, vp]
+    L.kh_memcpy_h2d.argtypes = [vp, vp, vp, C.c_size_t]
+    L.kh_memcpy_d2h.argtypes = [vp, vp, vp, C.c_size_t]
+    L.kh_bench_row.argtypes = [vp, C.c_char_p, C.c_char_p, C.c_int, C.c_int,
+                               C.POINTER(C.c_double), C.POINTER(C.c_double), C.POINTER(C.c_int)]
+    L.kh_registered_kernels.argtypes = [C.c_char_p, C.c_int]
+    L.kh_plan.argtypes = [C.c_char_p, C.c_char_p, C.c_char_p, C.c_int, C.POINTER(PlanInfo)]
+    L.kh_kernel_image.argtypes = [C.c_char_p, C.POINTER(vp), C.POINTER(C.c_size_t)]
+    L.kh_pack_memrefs.argtypes = [C.POINTER(C.c_uint64), C.POINTER(C.c_int64), C.POINTER(C.c_int),
+                                  C.c_int, C.POINTER(C.c_uint64), C.c_int, C.POINTER(C.c_int)]
+    L.kh_device_limits.argtypes = [C.c_char_p, C.POINTER(C.c_int64), C.c_char_p, C.c_int]
+    L.kh_target_token.argtypes = [C.c_char_p, C.c_char_p, C.c_int]
+    L.kh_verify_launch.argtypes = [C.c_char_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_uint64,
+                                   C.c_uint64, C.c_int, C.c_char_p, C.c_int]
+    L.kh_occupancy.argtypes = [C.c_char_p, C.c_int, C.c_int64, C.c_int, C.c_int64, C.c_int,
+                               C.POINTER(C.c_int), C.POINTER(C.c_double), C.POINTER(C.c_int)]
+    L.kh_metric.argtypes = [C.c_char_p, i64, i64, i64, i64]
+    L.kh_metric.restype = C.c_double
+    L.kh_rate.argtypes = [C.c_int, C.c_double, C.c_double]
+    L.kh_rate.restype = C.c_double
+    L.kh_csv_header.argtypes = [C.c_char_p, C.c_int]
+    L.kh_csv_line.argtypes = [C.c_char_p, C.c_char_p, C.c_char_p, C.c_double, C.c_double,
+                              C.c_char_p, C.c_char_p, C.c_char_p, C.c_int]
+    L.kh_shape_roundtrip.argtypes = [C.c_char_p, C.c_char_p, C.c_int]
+    return L
+
+
+lib = _load()
+
+
+def _check(rc: int) -> None:
+    if rc != 0:
+        raise KernelhError(rc, (lib.kh_last_error() or b"").decode(errors="replace"))
+
+
+def _ptr(x) -> int | None:
+    """Device or host address of a torch tensor / numpy array / int / None."""
+    if x is None:
+        return None
+    if isinstance(x, int):
+        return x
+    if hasattr(x, "data_ptr"):
+        return x.data_ptr()
+    if hasattr(x, "ctypes"):
+        return x.ctypes.data
+    raise TypeError(f"cannot take the address of {type(x)!r}")
+
+
+def shape_text(**shape: int) -> str:
+    return ",".join(f"{k}={int(v)}" for k, v in shape.items())
+
+
+class Context:
+    """A device context: the reference's ``make_cuda_backend()`` +
+    ``DeviceContext::create(backend, ordinal)``, plus the launch machinery."""
+
+    def __init__(self, device_ordinal: int = 0):
+        h = C.c_void_p()
+        _check(lib.kh_context_create(device_ordinal, C.byref(h)))
+        self._h = h
+
+    def close(self) -> None:
+        if getattr(self, "_h", None):
+            lib.kh_context_destroy(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def device_info(self) -> DeviceInfo:
+        info = DeviceInfo()
+        _check(lib.kh_device_info_get(self._h, C.byref(info)))
+        return info
+
+    # ---- operator surface ----------------------------------------------------
+    def launch(self, kernel: str, shape: str, buffers, stream: int | None = None) -> None:
+        """Enqueue `kernel` for the CLI-style `shape` text on DEVICE buffers."""
+        arr = (C.c_void_p * len(buffers))(*[_ptr(b) for b in buffers])
+        _check(lib.kh_launch(self._h, kernel.encode(), shape.encode(), arr, len(buffers), stream))
+
+    def run_host(self, kernel: str, shape: str, buffers) -> None:
+        """Same on HOST buffers: copy in, launch, copy out, wait."""
+        arr = (C.c_void_p * len(buffers))(*[_ptr(b) for b in buffers])
+        _check(lib.kh_run_host(self._h, kernel.encode(), shape.encode(), arr, len(buffers)))
+
+    def synchronize(self, stream: int | None = None) -> None:
+        _check(lib.kh_synchronize(self._h, stream))
+
+    def bench_row(self, kernel: str, shape: str, warmup: int = 5, iters: int = 20):
+        ms, rate, is_gflops = C.c_double(), C.c_double(), C.c_int()
+        _check(lib.kh_bench_row(self._h, kernel.encode(), shape.encode(), warmup, iters,
+                                C.byref(ms), C.byref(rate), C.byref(is_gflops)))
+        return ms.value, rate.value, bool(is_gflops.value)
+
+    # ---- typed entry points ----------------------------------------------------
+    def vecadd(self, a, b, c, n, stream=None):
+        _check(lib.kh_vecadd(self._h, _ptr(a), _ptr(b), _ptr(c), n, stream))
+
+    def fused_gelu(self, x, out, n, stream=None):
+        _check(lib.kh_fused_gelu(self._h, _ptr(x), _ptr(out), n, stream))
+
+    def fused_gelu_bias(self, x, bias, out, n, stream=None):
+        _check(lib.kh_fused_gelu_bias(self._h, _ptr(x), _ptr(bias), _ptr(out), n, stream))
+
+    def scan(self, x, y, n, stream=None):
+        _check(lib.kh_scan(self._h, _ptr(x), _ptr(y), n, stream))
+
+    def softmax(self, x, y, rows, cols, stream=None):
+        _check(lib.kh_softmax(self._h, _ptr(x), _ptr(y), rows, cols, stream))
+
+    def layernorm(self, x, gamma, beta, y, rows, cols, stream=None):
+        _check(lib.kh_layernorm(self._h, _ptr(x), _ptr(gamma), _ptr(beta), _ptr(y), rows, cols,
+                                stream))
+
+    def gemm(self, a, b, c, m, n, k, stream=None):
+        _check(lib.kh_gemm(self._h, _ptr(a), _ptr(b), _ptr(c), m, n, k, stream))
+
+    def attention(self, q, k, v, o, batch, heads, seq, head_dim, stream=None):
+        _check(lib.kh_attention(self._h, _ptr(q), _ptr(k), _ptr(v), _ptr(o), batch, heads, seq,
+                                head_dim, stream))
+
+    # ---- raw device memory -------------------------------------------------------
+    def malloc(self, nbytes: int) -> int:
+        p = C.c_void_p()
+        _check(lib.kh_malloc(self._h, nbytes, C.byref(p)))
+        return p.value
+
+    def free(self, ptr: int) -> None:
+        _check(lib.kh_free(self._h, ptr))
+
+    def memcpy_h2d(self, dst: int, src, nbytes: int) -> None:
+        _check(lib.kh_memcpy_h2d(self._h, dst, _ptr(src), nbytes))
+
+    def memcpy_d2h(self, dst, src: int, nbytes: int) -> None:
+        _check(lib.kh_memcpy_d2h(self._h, _ptr(dst), src, nbytes))
+
+
+# --------------------------------------------------------------------------- host helpers
+def device_count() -> int:
+    n = C.c_int()
+    _check(lib.kh_device_count(C.byref(n)))
+    return n.value
+
+
+def registered_kernels() -> list[str]:
+    buf = C.create_string_buffer(1024)
+    _check(lib.kh_registered_kernels(buf, 1024))
+    return buf.value.decode().split(",")
+
+
+def plan(kernel: str, shape: str, target: str = "sm_100a", sm_count: int = 148) -> PlanInfo:
+    info = PlanInfo()
+    _check(lib.kh_plan(kernel.encode(), shape.encode(), target.encode(), sm_count, C.byref(info)))
+    return info
+
+
+def kernel_image(kernel: str) -> bytes:
+    p, n = C.c_void_p(), C.c_size_t()
+    _check(lib.kh_kernel_image(kernel.encode(), C.byref(p), C.byref(n)))
+    return C.string_at(p.value, n.value)
+
+
+def pack_memrefs(ptrs, shapes) -> list[int]:
+    flat = [d for s in shapes for d in s]
+    ranks = [len(s) for s in shapes]
+    P = (C.c_uint64 * len(ptrs))(*ptrs)
+    S = (C.c_int64 * max(len(flat), 1))(*flat)
+    R = (C.c_int * len(ranks))(*ranks)
+    slots = (C.c_uint64 * 256)()
+    n = C.c_int()
+    _check(lib.kh_pack_memrefs(P, S, R, len(ptrs), slots, 256, C.byref(n)))
+    return [int(slots[i]) for i in range(n.value)]
+
+
+LIMIT_FIELDS = ("lds_bytes_per_workgroup", "wavefront_size", "max_threads_per_workgroup",
+                "max_grid_x", "max_grid_y", "max_grid_z", "vram_bytes", "waves_per_cu",
+                "reg_file_per_cu", "cu_count", "max_dynamic_smem_optin", "smem_per_sm",
+                "max_blocks_per_sm", "tmem_columns_per_sm")
+
+
+def device_limits(token: str) -> dict:
+    f = (C.c_int64 * 14)()
+    name = C.create_string_buffer(256)
+    _check(lib.kh_device_limits(token.encode() if token is not None else None, f, name, 256))
+    out = dict(zip(LIMIT_FIELDS, [int(v) for v in f]))
+    out["name"] = name.value.decode()
+    return out
+
+
+def target_token(cli_target: str) -> str:
+    buf = C.create_string_buffer(64)
+    _check(lib.kh_target_token(cli_target.encode(), buf, 64))
+    return buf.value.decode()
+
+
+def verify_launch(token: str, threads: int, grid=(1, 1, 1), static_smem: int = 0,
+                  dynamic_smem: int = 0, warps_per_sm_override: int = 0) -> str:
+    """'' when the launch is acceptable, else every violation, one per line."""
+    msg = C.create_string_buffer(8192)
+    rc = lib.kh_verify_launch(token.encode(), threads, grid[0], grid[1], grid[2], static_smem,
+                              dynamic_smem, warps_per_sm_override, msg, 8192)
+    if rc not in (0, 1):
+        _check(rc)
+    return msg.value.decode()
+
+
+def occupancy(token: str, regs: int, static_smem: int, threads: int, dynamic_smem: int = 0,
+              tmem_columns: int = 0) -> dict:
+    out5 = (C.c_int * 5)()
+    pct = C.c_double()
+    sm3 = (C.c_int * 3)()
+    _check(lib.kh_occupancy(token.encode(), regs, static_smem, threads, dynamic_smem, tmem_columns,
+                            out5, C.byref(pct), sm3))
+    return {"vgpr_limited_waves": out5[0], "lds_limited_blocks": out5[1],
+            "thread_limited_blocks": out5[2], "achieved_waves": out5[3],
+            "limiter": ("none", "vgpr", "lds", "threads")[out5[4]], "theoretical_pct": pct.value,
+            "sm_resident_blocks": sm3[0], "sm_occupancy_pct": sm3[1] / 100.0,
+            "sm_limiter": ("none", "registers", "shared memory", "warps", "block cap",
+                           "tensor memory")[sm3[2]]}
+
+
+def metric(what: str, a: int = 0, b: int = 0, c: int = 0, d: int = 0) -> float:
+    return lib.kh_metric(what.encode(), a, b, c, d)
+
+
+def rate(gflops: bool, work: float, ms: float) -> float:
+    return lib.kh_rate(int(gflops), work, ms)
+
+
+def csv_header() -> str:
+    buf = C.create_string_buffer(256)
+    lib.kh_csv_header(buf, 256)
+    return buf.value.decode()
+
+
+def csv_line(kernel, shape, backend, ms, rate_, timestamp, device) -> str:
+    buf = C.create_string_buffer(2048)
+    lib.kh_csv_line(kernel.encode(), shape.encode(), backend.encode(), ms, rate_,
+                    timestamp.encode(), device.encode(), buf, 2048)
+    return buf.value.decode()
+
+
+def shape_roundtrip(text: str) -> str:
+    buf = C.create_string_buffer(1024)
+    lib.kh_shape_roundtrip(text.encode(), buf, 1024)
+    return buf.value.decode()

@@ -1,0 +1,431 @@
+// Implementation of the C ABI declared in include/kernelh_b200.h: a thin shell
+// over the C++ runtime, registry and harness. No exception leaves this file.
+#include "kernelh_b200.h"
+
+#include "../harness/csv.hpp"
+#include "../harness/metrics.hpp"
+#include "../harness/timer.hpp"
+#include "../registry/executor.hpp"
+#include "../registry/registry.hpp"
+#include "../runtime/launch_verifier.hpp"
+#include "../runtime/occupancy.hpp"
+
+#include <cstring>
+#include <string>
+#include <vector>
+
+struct kh_context {
+  std::unique_ptr<kh::Executor> exec;
+};
+
+namespace {
+
+thread_local std::string g_last_error;
+
+int set_error(int code, const std::string &message) {
+  g_last_error = message;
+  return code == 0 ? 1 : code;
+}
+int set_error(const kh::Error &e) { return set_error(e.code, e.message); }
+
+int copy_out(const std::string &s, char *buf, int cap) {
+  if (buf != nullptr && cap > 0) {
+    const size_t n = std::min(s.size(), static_cast<size_t>(cap - 1));
+    std::memcpy(buf, s.data(), n);
+    buf[n] = '\0';
+  }
+  return static_cast<int>(s.size());
+}
+
+template <typename F> int guarded(F &&f) {
+  try {
+    return f();
+  } catch (const std::exception &e) {
+    return set_error(2, e.what());
+  } catch (...) {
+    return set_error(1, "unknown C++ exception");
+  }
+}
+
+int need_ctx(kh_context *ctx) {
+  if (ctx == nullptr || !ctx->exec) return set_error(2, "null kernelh_b200 context");
+  return 0;
+}
+
+int launch_named(kh_context *ctx, const char *kernel, const kh::ShapeMap &shape,
+                 std::vector<void *> buffers, void *stream) {
+  if (int rc = need_ctx(ctx)) return rc;
+  return guarded([&] {
+    auto r = ctx->exec->run(kernel, shape, buffers, stream);
+    return r ? 0 : set_error(r.error());
+  });
+}
+
+} // namespace
+
+extern "C" {
+
+const char *kh_last_error(void) { return g_last_error.c_str(); }
+const char *kh_version(void) { return "kernelh_b200 0.1 (sm_100a)"; }
+
+int kh_context_create(int device_ordinal, kh_context **out) {
+  if (out == nullptr) return set_error(2, "kh_context_create: null out pointer");
+  *out = nullptr;
+  return guarded([&] {
+    auto backend = kh::make_cuda_backend();
+    if (!backend) return set_error(backend.error());
+    auto exec = kh::Executor::create(*backend, device_ordinal);
+    if (!exec) return set_error(exec.error());
+    *out = new kh_context{std::move(*exec)};
+    return 0;
+  });
+}
+
+void kh_context_destroy(kh_context *ctx) { delete ctx; }
+
+int kh_device_count(int *count) {
+  return guarded([&] {
+    auto backend = kh::make_cuda_backend();
+    if (!backend) return set_error(backend.error());
+    auto n = (*backend)->device_count();
+    if (!n) return set_error(n.error());
+    if (count) *count = *n;
+    return 0;
+  });
+}
+
+int kh_device_info_get(kh_context *ctx, kh_device_info *out) {
+  if (int rc = need_ctx(ctx)) return rc;
+  if (out == nullptr) return set_error(2, "kh_device_info_get: null out pointer");
+  const kh::DeviceInfo &i = ctx->exec->info();
+  std::memset(out, 0, sizeof *out);
+  copy_out(i.name, out->name, sizeof out->name);
+  out->vram_bytes = i.vram_bytes;
+  out->static_smem_per_block = i.lds_bytes_per_workgroup;
+  out->optin_smem_per_block = i.smem_optin_per_block;
+  out->smem_per_sm = i.smem_per_sm;
+  out->l2_bytes = i.l2_bytes;
+  out->sm_count = static_cast<int32_t>(i.cu_count);
+  out->warp_size = i.wavefront_size;
+  out->max_threads_per_block = i.max_threads_per_workgroup;
+  out->regs_per_sm = i.regs_per_sm;
+  out->max_blocks_per_sm = i.max_blocks_per_sm;
+  out->cc_major = i.cc_major;
+  out->cc_minor = i.cc_minor;
+  out->ordinal = i.ordinal;
+  return 0;
+}
+
+int kh_launch(kh_context *ctx, const char *kernel, const char *shape, void *const *device_buffers,
+              int n_buffers, void *stream) {
+  if (kernel == nullptr || shape == nullptr) return set_error(2, "kh_launch: null kernel or shape");
+  const kh::ShapeMap map = kh::parse_shape_text(shape);
+  if (map.empty()) return set_error(2, std::string("malformed --shape text '") + shape + "' (expected k=v,k=v with integer values)");
+  std::vector<void *> bufs(device_buffers, device_buffers + (n_buffers > 0 ? n_buffers : 0));
+  return launch_named(ctx, kernel, map, std::move(bufs), stream);
+}
+
+int kh_run_host(kh_context *ctx, const char *kernel, const char *shape, void *const *host_buffers,
+                int n_buffers) {
+  if (int rc = need_ctx(ctx)) return rc;
+  if (kernel == nullptr || shape == nullptr) return set_error(2, "kh_run_host: null kernel or shape");
+  const kh::ShapeMap map = kh::parse_shape_text(shape);
+  if (map.empty()) return set_error(2, std::string("malformed --shape text '") + shape + "' (expected k=v,k=v with integer values)");
+  std::vector<void *> bufs(host_buffers, host_buffers + (n_buffers > 0 ? n_buffers : 0));
+  return guarded([&] {
+    auto r = ctx->exec->run_host(kernel, map, bufs);
+    return r ? 0 : set_error(r.error());
+  });
+}
+
+int kh_synchronize(kh_context *ctx, void *stream) {
+  if (int rc = need_ctx(ctx)) return rc;
+  auto r = ctx->exec->synchronize(stream);
+  return r ? 0 : set_error(r.error());
+}
+
+int kh_vecadd(kh_context *ctx, const float *a, const float *b, float *c, int64_t n, void *stream) {
+  return launch_named(ctx, "vecadd", {{"n", n}},
+                      {const_cast<float *>(a), const_cast<float *>(b), c}, stream);
+}
+int kh_fused_gelu(kh_context *ctx, const float *x, float *out, int64_t n, void *stream) {
+  return launch_named(ctx, "fused_gelu", {{"n", n}}, {const_cast<float *>(x), nullptr, out}, stream);
+}
+int kh_fused_gelu_bias(kh_context *ctx, const float *x, const float *bias, float *out, int64_t n,
+                       void *stream) {
+  return launch_named(ctx, "fused_gelu", {{"n", n}, {"bias", 1}},
+                      {const_cast<float *>(x), const_cast<float *>(bias), out}, stream);
+}
+int kh_scan(kh_context *ctx, const float *x, float *y, int64_t n, void *stream) {
+  return launch_named(ctx, "scan", {{"n", n}}, {const_cast<float *>(x), y}, stream);
+}
+int kh_softmax(kh_context *ctx, const float *x, float *y, int64_t rows, int64_t cols, void *stream) {
+  return launch_named(ctx, "softmax", {{"rows", rows}, {"cols", cols}}, {const_cast<float *>(x), y},
+                      stream);
+}
+int kh_layernorm(kh_context *ctx, const float *x, const float *gamma, const float *beta, float *y,
+                 int64_t rows, int64_t cols, void *stream) {
+  return launch_named(ctx, "layernorm", {{"rows", rows}, {"cols", cols}},
+                      {const_cast<float *>(x), const_cast<float *>(gamma),
+                       const_cast<float *>(beta), y},
+                      stream);
+}
+int kh_gemm(kh_context *ctx, const float *a, const float *b, float *c, int64_t m, int64_t n,
+            int64_t k, void *stream) {
+  return launch_named(ctx, "gemm", {{"m", m}, {"n", n}, {"k", k}},
+                      {const_cast<float *>(a), const_cast<float *>(b), c}, stream);
+}
+int kh_attention(kh_context *ctx, const float *q, const float *k, const float *v, float *o,
+                 int64_t batch, int64_t heads, int64_t seq, int64_t head_dim, void *stream) {
+  return launch_named(ctx, "attention",
+                      {{"batch", batch}, {"heads", heads}, {"seq", seq}, {"head_dim", head_dim}},
+                      {const_cast<float *>(q), const_cast<float *>(k), const_cast<float *>(v), o},
+                      stream);
+}
+
+int kh_malloc(kh_context *ctx, size_t bytes, void **out) {
+  if (int rc = need_ctx(ctx)) return rc;
+  if (out == nullptr) return set_error(2, "kh_malloc: null out pointer");
+  (void)ctx->exec->backend().make_current();
+  auto p = ctx->exec->backend().malloc(bytes);
+  if (!p) return set_error(p.error());
+  *out = *p;
+  return 0;
+}
+int kh_free(kh_context *ctx, void *ptr) {
+  if (int rc = need_ctx(ctx)) return rc;
+  (void)ctx->exec->backend().make_current();
+  auto r = ctx->exec->backend().free(ptr);
+  return r ? 0 : set_error(r.error());
+}
+int kh_memcpy_h2d(kh_context *ctx, void *dst, const void *src, size_t bytes) {
+  if (int rc = need_ctx(ctx)) return rc;
+  (void)ctx->exec->backend().make_current();
+  auto r = ctx->exec->backend().memcpy_h2d(dst, src, bytes);
+  return r ? 0 : set_error(r.error());
+}
+int kh_memcpy_d2h(kh_context *ctx, void *dst, const void *src, size_t bytes) {
+  if (int rc = need_ctx(ctx)) return rc;
+  (void)ctx->exec->backend().make_current();
+  auto r = ctx->exec->backend().memcpy_d2h(dst, src, bytes);
+  return r ? 0 : set_error(r.error());
+}
+
+int kh_bench_row(kh_context *ctx, const char *kernel, const char *shape, int warmup, int iters,
+                 double *ms_median, double *rate, int *rate_is_gflops) {
+  if (int rc = need_ctx(ctx)) return rc;
+  return guarded([&] {
+    const kh::ShapeMap map = kh::parse_shape_text(shape ? shape : "");
+    if (map.empty()) return set_error(2, "kh_bench_row: malformed shape text");
+    kh::Executor &ex = *ctx->exec;
+    const kh::KernelPlan plan = kh::find_kernel(kernel).plan(map, ex.limits());
+    std::vector<kh::Buffer> owned;
+    std::vector<void *> bufs;
+    for (const kh::TensorArg &t : plan.tensors) {
+      auto b = kh::Buffer::allocate(ex.backend_ptr(), static_cast<size_t>(t.elements()) * 4);
+      if (!b) return set_error(b.error());
+      // 0x3c003c00 is the fp32 value 0.0078..., finite and harmless for every kernel
+      if (auto r = ex.backend().memset32_async(b->data(), 0x3c003c00u, static_cast<size_t>(t.elements()), nullptr); !r)
+        return set_error(r.error());
+      bufs.push_back(b->data());
+      owned.push_back(std::move(*b));
+    }
+    auto ms = kh::bench::time_launch_median(
+        ex.backend_ptr(), [&] { return ex.run(kernel, map, bufs, nullptr); }, warmup, iters, nullptr);
+    if (!ms) return set_error(ms.error());
+    if (auto r = ex.synchronize(nullptr); !r) return set_error(r.error());
+    if (ms_median) *ms_median = *ms;
+    if (rate)
+      *rate = plan.work_is_flops ? kh::bench::gflops_from_ms(plan.work, *ms)
+                                 : kh::bench::gbps_from_ms(plan.work, *ms);
+    if (rate_is_gflops) *rate_is_gflops = plan.work_is_flops ? 1 : 0;
+    return 0;
+  });
+}
+
+int kh_registered_kernels(char *buf, int cap) {
+  return guarded([&] {
+    std::string s;
+    for (const std::string &n : kh::registered_kernels()) {
+      if (!s.empty()) s += ',';
+      s += n;
+    }
+    copy_out(s, buf, cap);
+    return 0;
+  });
+}
+
+int kh_plan(const char *kernel, const char *shape, const char *target_token, int sm_count,
+            kh_plan_info *out) {
+  if (out == nullptr) return set_error(2, "kh_plan: null out pointer");
+  return guarded([&] {
+    kh::DeviceLimits limits = kh::device_limits_for(target_token);
+    if (sm_count > 0) limits.cu_count = sm_count;
+    const kh::ShapeMap map = kh::parse_shape_text(shape ? shape : "");
+    const kh::KernelPlan plan = kh::find_kernel(kernel ? kernel : "").plan(map, limits);
+    std::memset(out, 0, sizeof *out);
+    out->n_buffers = static_cast<int32_t>(plan.tensors.size());
+    out->n_launches = static_cast<int32_t>(plan.steps.size());
+    out->workspace_bytes = static_cast<int64_t>(plan.workspace_bytes);
+    const kh::LaunchStep &s = plan.steps.back();
+    copy_out(s.entry, out->entry, sizeof out->entry);
+    out->grid[0] = s.grid.x; out->grid[1] = s.grid.y; out->grid[2] = s.grid.z;
+    out->block[0] = s.block.x; out->block[1] = s.block.y; out->block[2] = s.block.z;
+    out->dynamic_smem = static_cast<int64_t>(s.dynamic_smem);
+    out->param_count = s.param_count;
+    out->tmem_columns = s.tmem_columns;
+    out->work = plan.work;
+    out->work_is_flops = plan.work_is_flops ? 1 : 0;
+    return 0;
+  });
+}
+
+int kh_kernel_image(const char *kernel, const void **image, size_t *size) {
+  return guarded([&] {
+    const std::string name(kernel ? kernel : "");
+    const kh::KernelRecord &rec = kh::find_kernel(name);
+    const kh::CodeObject *co = kh::find_code_object(rec.code_object);
+    if (co == nullptr || co->size == 0)
+      return set_error(1, "no embedded sm_100a code object for kernel '" + rec.name + "'");
+    if (image) *image = co->image;
+    if (size) *size = co->size;
+    return 0;
+  });
+}
+
+int kh_pack_memrefs(const uint64_t *ptrs, const int64_t *shapes, const int *ranks, int count,
+                    uint64_t *slots, int cap, int *n_slots) {
+  kh::LaunchArgs args;
+  const int64_t *sp = shapes;
+  for (int i = 0; i < count; ++i) {
+    args.add_memref(reinterpret_cast<const void *>(ptrs[i]), std::vector<int64_t>(sp, sp + ranks[i]));
+    sp += ranks[i];
+  }
+  const auto &raw = args.raw_slots();
+  for (size_t i = 0; i < raw.size() && static_cast<int>(i) < cap; ++i) slots[i] = raw[i];
+  if (n_slots) *n_slots = static_cast<int>(raw.size());
+  return 0;
+}
+
+int kh_device_limits(const char *token, int64_t *f, char *name, int name_cap) {
+  return guarded([&] {
+    const kh::DeviceLimits &l = kh::device_limits_for(token);
+    f[0] = l.lds_bytes_per_workgroup; f[1] = l.wavefront_size; f[2] = l.max_threads_per_workgroup;
+    f[3] = l.max_grid_dim[0]; f[4] = l.max_grid_dim[1]; f[5] = l.max_grid_dim[2];
+    f[6] = l.vram_bytes; f[7] = l.waves_per_cu; f[8] = l.reg_file_per_cu; f[9] = l.cu_count;
+    f[10] = l.max_dynamic_smem_optin; f[11] = l.smem_per_sm; f[12] = l.max_blocks_per_sm;
+    f[13] = l.tmem_columns_per_sm;
+    copy_out(l.name, name, name_cap);
+    return 0;
+  });
+}
+
+int kh_target_token(const char *cli_target, char *buf, int cap) {
+  const std::string tok = kh::device_token_for_cli_target(cli_target ? cli_target : "");
+  if (tok.empty()) {
+    std::string list;
+    for (const std::string &t : kh::known_cli_targets()) {
+      if (!list.empty()) list += ", ";
+      list += t;
+    }
+    return set_error(2, std::string("unknown --target '") + (cli_target ? cli_target : "") +
+                            "'; valid --target values: " + list);
+  }
+  copy_out(tok, buf, cap);
+  return 0;
+}
+
+int kh_verify_launch(const char *token, int threads, int gx, int gy, int gz, uint64_t static_smem,
+                     uint64_t dynamic_smem, int warps_per_sm_override, char *msg, int cap) {
+  return guarded([&] {
+    kh::DeviceLimits l = kh::device_limits_for(token);
+    if (warps_per_sm_override > 0) l.waves_per_cu = warps_per_sm_override;
+    kh::LaunchConfig c;
+    c.threads_per_workgroup = threads;
+    c.grid_x = gx; c.grid_y = gy; c.grid_z = gz;
+    c.static_shared_bytes = static_smem;
+    c.dynamic_shared_bytes = dynamic_smem;
+    auto r = kh::LaunchVerifier().verify(c, l);
+    if (r) {
+      copy_out("", msg, cap);
+      return 0;
+    }
+    copy_out(r.error(), msg, cap);
+    g_last_error = r.error();
+    return 1;
+  });
+}
+
+int kh_occupancy(const char *token, int regs, int64_t static_smem, int threads, int64_t dynamic_smem,
+                 int tmem_columns, int *out5, double *theoretical_pct, int *sm3) {
+  return guarded([&] {
+    kh::OccupancyInput in;
+    in.kernel = "k";
+    in.target = token ? token : "";
+    in.vgpr_count = regs;
+    in.lds_bytes = static_smem;
+    in.threads_per_workgroup = threads;
+    in.dynamic_smem_bytes = dynamic_smem;
+    in.tmem_columns = tmem_columns;
+    const kh::OccupancyReport r = kh::occupancy_report(in, kh::device_limits_for(token));
+    if (out5) {
+      out5[0] = r.vgpr_limited_waves; out5[1] = r.lds_limited_blocks; out5[2] = r.thread_limited_blocks;
+      out5[3] = r.achieved_waves; out5[4] = static_cast<int>(r.limiter);
+    }
+    if (theoretical_pct) *theoretical_pct = r.theoretical_pct;
+    if (sm3) {
+      static const char *names[] = {"none", "registers", "shared memory", "warps", "block cap", "tensor memory"};
+      int idx = 0;
+      for (int i = 0; i < 6; ++i)
+        if (r.sm_limiter == names[i]) idx = i;
+      sm3[0] = r.sm_resident_blocks;
+      sm3[1] = static_cast<int>(r.sm_occupancy_pct * 100.0 + 0.5);
+      sm3[2] = idx;
+    }
+    return 0;
+  });
+}
+
+double kh_metric(const char *what, int64_t a, int64_t b, int64_t c, int64_t d) {
+  using namespace kh::bench;
+  const std::string w(what ? what : "");
+  if (w == "gemm_flops") return gemm_flops(a, b, c);
+  if (w == "gemm_bytes") return gemm_bytes(a, b, c);
+  if (w == "elementwise_bytes") return elementwise_bytes(a, b);
+  if (w == "layernorm_bytes") return layernorm_bytes(a, b);
+  if (w == "scan_bytes") return scan_bytes(a);
+  if (w == "fused_gelu_bytes") return fused_gelu_bytes(a);
+  if (w == "attention_flops") return attention_flops(a, b, c, d);
+  if (w == "vecadd_bytes") return vecadd_bytes(a);
+  return -1.0;
+}
+
+double kh_rate(int gflops, double work, double ms) {
+  return gflops ? kh::bench::gflops_from_ms(work, ms) : kh::bench::gbps_from_ms(work, ms);
+}
+
+int kh_csv_header(char *buf, int cap) {
+  copy_out(kh::bench::kCsvHeader, buf, cap);
+  return 0;
+}
+
+int kh_csv_line(const char *kernel, const char *shape, const char *backend, double ms, double rate,
+                const char *timestamp, const char *device, char *buf, int cap) {
+  kh::bench::BenchRow r;
+  r.kernel = kernel ? kernel : "";
+  r.shape = shape ? shape : "";
+  r.backend = backend ? backend : "";
+  r.ms_median = ms;
+  r.gflops_or_gbps = rate;
+  r.timestamp = timestamp ? timestamp : "";
+  r.device = device ? device : "";
+  copy_out(kh::bench::csv_line(r), buf, cap);
+  return 0;
+}
+
+int kh_shape_roundtrip(const char *text, char *buf, int cap) {
+  copy_out(kh::shape_to_text(kh::parse_shape_text(text ? text : "")), buf, cap);
+  return 0;
+}
+
+} // extern "C"

@@ -1,0 +1,402 @@
+// attention: O = softmax(Q K^T / sqrt(d)) V, non-causal, fp32, d = 64,
+// tensors [batch, heads, seq, 64] contiguous, seq a multiple of 64.
+//
+// Replaces the kernel the reference generates from
+// lib/dsl/kernels/attention.cpp:86-289 (one 64-thread block per query row,
+// every block re-staging all of K and V in tiles of 64 with a per-key online
+// rescale, 268-276; head_dim pinned to 64 and seq % 64 == 0, 109-120). Entry
+// symbol `attention`; the first 44 parameters are the reference's: (Q, K, V,
+// O) as rank-4 memref descriptors. The TMA-fed kernel then takes six tensor
+// maps and a status pointer.
+//
+// Flash-style: a CTA owns 128 query rows of one (batch, head) and streams K/V
+// in tiles of 64 keys. Both contractions run on tcgen05 tensor cores in 3xTF32
+// (operands split once into hi = tf32(x), lo = x - hi; products lo.hi, hi.lo,
+// hi.hi into one fp32 accumulator):
+//   S = Q K^T   A = Q tile (shared memory, K-major), B = K tile (K-major)
+//   PV = P V    A = P (tensor memory), B = V^T tile (K-major over keys)
+// Scores, probabilities and the per-tile PV product live in tensor memory;
+// the running max, sum and the 64-wide output row live in registers of the
+// thread that owns the row (one thread per tensor-memory lane).
+//
+// Two launches:
+//  attention_split  writes Q/8 (the 1/sqrt(64) scale is exact), K and V^T as
+//      hi/lo pairs into scratch.
+//  attention  warp 0 feeds TMA (Q once; a 2-stage ring of K/V tiles, 64 KiB
+//      per stage); warp 1 issues the MMAs (S of tile j+1 is issued before PV
+//      of tile j so the tensor core works while softmax runs); warps 2-5 (one
+//      thread per query row) do the online softmax and own the output.
+//
+// Tensor-bound: 4 b h s^2 d useful flops; 3xTF32 puts the ceiling at one third
+// of the TF32 tensor rate.
+#include "kh_tcgen05.cuh"
+
+namespace {
+
+constexpr int kHeadDim = 64;
+constexpr int kBQ = 128;  // query rows per CTA
+constexpr int kBKV = 64;  // keys per tile
+constexpr int kStages = 2;
+constexpr int kThreads = 192;
+constexpr int kChunkRowsBytes = 128; // one swizzle row: 32 fp32
+constexpr int kQChunkBytes = kBQ * kChunkRowsBytes;   // 16 KiB: 128 rows x 32 fp32
+constexpr int kKVChunkBytes = kBKV * kChunkRowsBytes; // 8 KiB: 64 rows x 32 fp32
+constexpr int kQBytes = 4 * kQChunkBytes;             // hi c0,c1 + lo c0,c1 = 64 KiB
+constexpr int kStageBytes = 8 * kKVChunkBytes;        // K hi/lo + V^T hi/lo, 2 chunks each = 64 KiB
+// tensor-memory columns
+constexpr uint32_t kColS0 = 0, kColS1 = 64, kColPHi = 128, kColPLo = 192, kColPV = 256;
+constexpr uint32_t kTmemCols = 512;
+
+__device__ __forceinline__ float tf32_hi(float x) {
+  uint32_t u = __float_as_uint(x);
+  u = (u + 0x1000u) & 0xFFFFE000u;
+  return __uint_as_float(u);
+}
+
+// D[tmem] (+)= A[tmem] * B[smem]
+__device__ __forceinline__ void umma_tf32_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t desc_b,
+                                             uint32_t idesc, uint32_t accumulate) {
+  asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+               "tcgen05.mma.cta_group::1.kind::tf32 [%0], [%1], %2, %3, p;\n\t}" ::"r"(tmem_d),
+               "r"(tmem_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+               : "memory");
+}
+
+__device__ __forceinline__ void tmem_st_32x32(uint32_t taddr, const uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+      "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};" ::"r"(taddr),
+      "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+      "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]),
+      "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]),
+      "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]),
+      "r"(r[30]), "r"(r[31])
+      : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() {
+  asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
+
+} // namespace
+
+// Q, K, V [bh, seq, 64] -> q_hi, q_lo (scaled by 1/8), k_hi, k_lo [bh*seq, 64]
+// and vt_hi, vt_lo [bh*64, seq] (V transposed per (batch, head)).
+extern "C" __global__ void __launch_bounds__(256)
+attention_split(KH_MEMREF4(const float, q), KH_MEMREF4(const float, k), KH_MEMREF4(const float, v),
+                float *__restrict__ q_hi, float *__restrict__ q_lo, float *__restrict__ k_hi,
+                float *__restrict__ k_lo, float *__restrict__ vt_hi, float *__restrict__ vt_lo) {
+  __shared__ float tile[32][33];
+  const float *__restrict__ q = KH_DATA(q);
+  const float *__restrict__ k = KH_DATA(k);
+  const float *__restrict__ v = KH_DATA(v);
+  const int64_t bh = q_size0 * q_size1, seq = q_size2;
+  const int64_t total4 = bh * seq * kHeadDim / 4;
+  const int64_t tid = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  const int64_t nthreads = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  // Q and K keep their layout (the tensors are contiguous, so a flat sweep does).
+  for (int64_t i = tid; i < total4; i += nthreads) {
+    const float4 fq = __ldcs(reinterpret_cast<const float4 *>(q) + i);
+    const float4 fk = __ldcs(reinterpret_cast<const float4 *>(k) + i);
+    float4 h, l;
+    const float sq[4] = {fq.x * 0.125f, fq.y * 0.125f, fq.z * 0.125f, fq.w * 0.125f};
+    h = make_float4(tf32_hi(sq[0]), tf32_hi(sq[1]), tf32_hi(sq[2]), tf32_hi(sq[3]));
+    l = make_float4(sq[0] - h.x, sq[1] - h.y, sq[2] - h.z, sq[3] - h.w);
+    reinterpret_cast<float4 *>(q_hi)[i] = h;
+    reinterpret_cast<float4 *>(q_lo)[i] = l;
+    h = make_float4(tf32_hi(fk.x), tf32_hi(fk.y), tf32_hi(fk.z), tf32_hi(fk.w));
+    l = make_float4(fk.x - h.x, fk.y - h.y, fk.z - h.z, fk.w - h.w);
+    reinterpret_cast<float4 *>(k_hi)[i] = h;
+    reinterpret_cast<float4 *>(k_lo)[i] = l;
+  }
+  // V: 32 x 32 tiles through shared memory, [seq, 64] -> [64, seq] per (batch, head).
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+  const int64_t tiles_s = seq >> 5, tiles_per_bh = tiles_s * 2;
+  for (int64_t t = blockIdx.x; t < bh * tiles_per_bh; t += gridDim.x) {
+    const int64_t b = t / tiles_per_bh, r = t - b * tiles_per_bh;
+    const int64_t s0 = (r >> 1) << 5, d0 = (r & 1) << 5;
+    const float *src = v + b * seq * kHeadDim;
+    __syncthreads();
+#pragma unroll
+    for (int j = 0; j < 4; ++j) tile[ty + 8 * j][tx] = src[(s0 + ty + 8 * j) * kHeadDim + d0 + tx];
+    __syncthreads();
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float val = tile[tx][ty + 8 * j];
+      const float h = tf32_hi(val);
+      const int64_t o = (b * kHeadDim + d0 + ty + 8 * j) * seq + s0 + tx;
+      vt_hi[o] = h;
+      vt_lo[o] = val - h;
+    }
+  }
+}
+
+extern "C" __global__ void __launch_bounds__(kThreads, 1)
+attention(KH_MEMREF4(const float, q), KH_MEMREF4(const float, k), KH_MEMREF4(const float, v),
+          KH_MEMREF4(float, o), const __grid_constant__ khd::TensorMap tm_q_hi,
+          const __grid_constant__ khd::TensorMap tm_q_lo, const __grid_constant__ khd::TensorMap tm_k_hi,
+          const __grid_constant__ khd::TensorMap tm_k_lo, const __grid_constant__ khd::TensorMap tm_vt_hi,
+          const __grid_constant__ khd::TensorMap tm_vt_lo, uint32_t *status) {
+  (void)q_alloc; (void)q_ptr; (void)q_off; (void)q_size3; (void)q_stride0; (void)q_stride1;
+  (void)q_stride2; (void)q_stride3;
+  (void)k_alloc; (void)k_ptr; (void)k_off; (void)k_size0; (void)k_size1; (void)k_size2; (void)k_size3;
+  (void)k_stride0; (void)k_stride1; (void)k_stride2; (void)k_stride3;
+  (void)v_alloc; (void)v_ptr; (void)v_off; (void)v_size0; (void)v_size1; (void)v_size2; (void)v_size3;
+  (void)v_stride0; (void)v_stride1; (void)v_stride2; (void)v_stride3;
+  (void)o_size0; (void)o_size1; (void)o_size2; (void)o_size3; (void)o_stride0; (void)o_stride1;
+  (void)o_stride2; (void)o_stride3; (void)o_alloc;
+  extern __shared__ uint8_t smem_raw[];
+  // barriers: q_full, kv_full[2], kv_empty[2], s_full[2], p_ready, pv_full
+  __shared__ __align__(8) uint64_t bars[9];
+  __shared__ uint32_t s_tmem_base;
+  __shared__ int s_abort;
+
+  const int64_t seq = q_size2;
+  const int64_t q_tiles = (seq + kBQ - 1) / kBQ;
+  const int64_t bh = blockIdx.x / q_tiles;
+  const int q0 = static_cast<int>((blockIdx.x - bh * q_tiles) * kBQ);
+  const int num_kv = static_cast<int>(seq / kBKV);
+  float *__restrict__ out = KH_DATA(o);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  const uint32_t smem_q = (khd::smem_u32(smem_raw) + 1023u) & ~1023u;
+  const uint32_t smem_kv = smem_q + kQBytes;
+  const uint32_t bar_q = khd::smem_u32(&bars[0]);
+  const uint32_t bar_kv_full = khd::smem_u32(&bars[1]);
+  const uint32_t bar_kv_empty = khd::smem_u32(&bars[3]);
+  const uint32_t bar_s_full = khd::smem_u32(&bars[5]);
+  const uint32_t bar_p_ready = khd::smem_u32(&bars[7]);
+  const uint32_t bar_pv_full = khd::smem_u32(&bars[8]);
+
+  if (threadIdx.x == 0) {
+    s_abort = 0;
+    khd::mbar_init(bar_q, 1);
+    for (int s = 0; s < kStages; ++s) {
+      khd::mbar_init(bar_kv_full + 8 * s, 1);
+      khd::mbar_init(bar_kv_empty + 8 * s, 1);
+      khd::mbar_init(bar_s_full + 8 * s, 1);
+    }
+    khd::mbar_init(bar_p_ready, kBQ); // one arrival per softmax thread
+    khd::mbar_init(bar_pv_full, 1);
+    khd::mbar_fence_init();
+    khd::tma_prefetch_descriptor(&tm_q_hi);
+    khd::tma_prefetch_descriptor(&tm_q_lo);
+    khd::tma_prefetch_descriptor(&tm_k_hi);
+    khd::tma_prefetch_descriptor(&tm_k_lo);
+    khd::tma_prefetch_descriptor(&tm_vt_hi);
+    khd::tma_prefetch_descriptor(&tm_vt_lo);
+  }
+  if (warp == 1) {
+    khd::tmem_alloc(khd::smem_u32(&s_tmem_base), kTmemCols);
+    khd::tmem_relinquish();
+  }
+  khd::tc_fence_before_sync();
+  __syncthreads();
+  khd::tc_fence_after_sync();
+  const uint32_t tmem_base = s_tmem_base;
+
+  if (warp == 0) {
+    // ---- TMA producer -----------------------------------------------------------
+    if (lane == 0) {
+      const int q_row = static_cast<int>(bh * seq) + q0;
+      khd::mbar_arrive_expect_tx(bar_q, kQBytes);
+      khd::tma_load_2d(smem_q + 0 * kQChunkBytes, &tm_q_hi, 0, q_row, bar_q);
+      khd::tma_load_2d(smem_q + 1 * kQChunkBytes, &tm_q_hi, 32, q_row, bar_q);
+      khd::tma_load_2d(smem_q + 2 * kQChunkBytes, &tm_q_lo, 0, q_row, bar_q);
+      khd::tma_load_2d(smem_q + 3 * kQChunkBytes, &tm_q_lo, 32, q_row, bar_q);
+      for (int j = 0; j < num_kv; ++j) {
+        const int s = j % kStages;
+        const uint32_t phase = static_cast<uint32_t>((j / kStages) & 1);
+        if (!khd::mbar_wait(bar_kv_empty + 8 * s, phase ^ 1u, &s_abort, status,
+                            khd::kStatusEmptyWaitTimeout, static_cast<uint32_t>(j)))
+          break;
+        const uint32_t st = smem_kv + s * kStageBytes;
+        const uint32_t bar = bar_kv_full + 8 * s;
+        khd::mbar_arrive_expect_tx(bar, kStageBytes);
+        const int k_row = static_cast<int>(bh * seq) + j * kBKV;
+        const int v_row = static_cast<int>(bh * kHeadDim);
+        const int v_col = j * kBKV;
+        khd::tma_load_2d(st + 0 * kKVChunkBytes, &tm_k_hi, 0, k_row, bar);
+        khd::tma_load_2d(st + 1 * kKVChunkBytes, &tm_k_hi, 32, k_row, bar);
+        khd::tma_load_2d(st + 2 * kKVChunkBytes, &tm_k_lo, 0, k_row, bar);
+        khd::tma_load_2d(st + 3 * kKVChunkBytes, &tm_k_lo, 32, k_row, bar);
+        khd::tma_load_2d(st + 4 * kKVChunkBytes, &tm_vt_hi, v_col, v_row, bar);
+        khd::tma_load_2d(st + 5 * kKVChunkBytes, &tm_vt_hi, v_col + 32, v_row, bar);
+        khd::tma_load_2d(st + 6 * kKVChunkBytes, &tm_vt_lo, v_col, v_row, bar);
+        khd::tma_load_2d(st + 7 * kKVChunkBytes, &tm_vt_lo, v_col + 32, v_row, bar);
+      }
+    }
+  } else if (warp == 1) {
+    // ---- MMA issuer ---------------------------------------------------------------
+    if (lane == 0) {
+      constexpr uint32_t idesc = khd::umma_idesc_tf32(kBQ, kBKV); // M128 N64 for both products
+      // S_j = Q K_j^T into S buffer j % 2
+      auto issue_s = [&](int j) {
+        const uint32_t st = smem_kv + (j % kStages) * kStageBytes;
+        const uint32_t d = tmem_base + ((j & 1) ? kColS1 : kColS0);
+#pragma unroll
+        for (int kk = 0; kk < kHeadDim / 8; ++kk) {
+          const int chunk = kk >> 2;
+          const uint64_t adv = static_cast<uint64_t>((kk & 3) * 2);
+          const uint64_t q_hi = khd::umma_desc_k128(smem_q + (0 + chunk) * kQChunkBytes) + adv;
+          const uint64_t q_lo = khd::umma_desc_k128(smem_q + (2 + chunk) * kQChunkBytes) + adv;
+          const uint64_t k_hi = khd::umma_desc_k128(st + (0 + chunk) * kKVChunkBytes) + adv;
+          const uint64_t k_lo = khd::umma_desc_k128(st + (2 + chunk) * kKVChunkBytes) + adv;
+          khd::umma_tf32_ss(d, q_lo, k_hi, idesc, kk != 0 ? 1u : 0u);
+          khd::umma_tf32_ss(d, q_hi, k_lo, idesc, 1u);
+          khd::umma_tf32_ss(d, q_hi, k_hi, idesc, 1u);
+        }
+        khd::umma_commit(bar_s_full + 8 * (j & 1));
+      };
+      bool ok = khd::mbar_wait(bar_q, 0u, &s_abort, status, khd::kStatusTmaWaitTimeout, 1000u);
+      ok = ok && khd::mbar_wait(bar_kv_full, 0u, &s_abort, status, khd::kStatusTmaWaitTimeout, 0u);
+      if (ok) {
+        khd::tc_fence_after_sync();
+        issue_s(0);
+      }
+      for (int j = 0; j < num_kv && ok; ++j) {
+        if (j + 1 < num_kv) {
+          const int s1 = (j + 1) % kStages;
+          ok = khd::mbar_wait(bar_kv_full + 8 * s1, static_cast<uint32_t>(((j + 1) / kStages) & 1),
+                              &s_abort, status, khd::kStatusTmaWaitTimeout, static_cast<uint32_t>(j + 1));
+          if (!ok) break;
+          khd::tc_fence_after_sync();
+          issue_s(j + 1);
+        }
+        ok = khd::mbar_wait(bar_p_ready, static_cast<uint32_t>(j & 1), &s_abort, status,
+                            khd::kStatusEpilogueWaitTimeout, static_cast<uint32_t>(j));
+        if (!ok) break;
+        khd::tc_fence_after_sync();
+        // PV_j = P_j V_j: A = P (tensor memory, 64 columns hi / 64 lo), B = V^T tile
+        const uint32_t st = smem_kv + (j % kStages) * kStageBytes;
+        const uint32_t d = tmem_base + kColPV;
+#pragma unroll
+        for (int kk = 0; kk < kBKV / 8; ++kk) {
+          const int chunk = kk >> 2;
+          const uint64_t adv = static_cast<uint64_t>((kk & 3) * 2);
+          const uint64_t v_hi = khd::umma_desc_k128(st + (4 + chunk) * kKVChunkBytes) + adv;
+          const uint64_t v_lo = khd::umma_desc_k128(st + (6 + chunk) * kKVChunkBytes) + adv;
+          const uint32_t p_hi = tmem_base + kColPHi + kk * 8;
+          const uint32_t p_lo = tmem_base + kColPLo + kk * 8;
+          umma_tf32_ts(d, p_lo, v_hi, idesc, kk != 0 ? 1u : 0u);
+          umma_tf32_ts(d, p_hi, v_lo, idesc, 1u);
+          umma_tf32_ts(d, p_hi, v_hi, idesc, 1u);
+        }
+        khd::umma_commit(bar_pv_full);
+        khd::umma_commit(bar_kv_empty + 8 * (j % kStages));
+      }
+    }
+  } else {
+    // ---- softmax + output: one thread per query row ----------------------------------
+    const int quad = warp & 3;
+    const uint32_t lane_base = static_cast<uint32_t>(quad * 32) << 16;
+    const int row_in_tile = quad * 32 + lane;
+    float acc[kHeadDim];
+#pragma unroll
+    for (int i = 0; i < kHeadDim; ++i) acc[i] = 0.f;
+    float m = -INFINITY, l = 0.f;
+    bool ok = true;
+    constexpr float kLog2e = 1.4426950408889634f;
+
+    for (int j = 0; j < num_kv && ok; ++j) {
+      ok = khd::mbar_wait(bar_s_full + 8 * (j & 1), static_cast<uint32_t>((j >> 1) & 1), &s_abort,
+                          status, khd::kStatusMmaWaitTimeout, static_cast<uint32_t>(j));
+      if (!ok) break;
+      khd::tc_fence_after_sync();
+      uint32_t s0[32], s1[32];
+      const uint32_t s_addr = tmem_base + lane_base + ((j & 1) ? kColS1 : kColS0);
+      khd::tmem_ld_32x32(s_addr, s0);
+      khd::tmem_ld_32x32(s_addr + 32, s1);
+      khd::tmem_ld_wait();
+      float mx = -INFINITY;
+#pragma unroll
+      for (int i = 0; i < 32; ++i)
+        mx = fmaxf(mx, fmaxf(__uint_as_float(s0[i]), __uint_as_float(s1[i])));
+      const float m_new = fmaxf(m, mx);
+      const float alpha = exp2f((m - m_new) * kLog2e); // m = -inf on the first tile gives 0
+      const float mb = m_new * kLog2e;
+      float sum = 0.f;
+#pragma unroll
+      for (int i = 0; i < 32; ++i) {
+        const float p0 = exp2f(fmaf(__uint_as_float(s0[i]), kLog2e, -mb));
+        const float p1 = exp2f(fmaf(__uint_as_float(s1[i]), kLog2e, -mb));
+        s0[i] = __float_as_uint(p0);
+        s1[i] = __float_as_uint(p1);
+        sum += p0 + p1;
+      }
+      l = l * alpha + sum;
+      m = m_new;
+
+      // Fold in the previous tile's PV (normalised to the previous max), then
+      // move the running output to the new max. Waiting here also means the
+      // tensor core has finished reading P of the previous tile.
+      if (j > 0) {
+        ok = khd::mbar_wait(bar_pv_full, static_cast<uint32_t>((j - 1) & 1), &s_abort, status,
+                            khd::kStatusMmaWaitTimeout, 2000u + static_cast<uint32_t>(j));
+        if (!ok) break;
+        khd::tc_fence_after_sync();
+        uint32_t t[32];
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          khd::tmem_ld_32x32(tmem_base + lane_base + kColPV + 32 * h, t);
+          khd::tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) acc[32 * h + i] = (acc[32 * h + i] + __uint_as_float(t[i])) * alpha;
+        }
+      }
+      // P -> tensor memory as hi / lo
+      {
+        uint32_t hi[32];
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          uint32_t(&src)[32] = h ? s1 : s0;
+#pragma unroll
+          for (int i = 0; i < 32; ++i) hi[i] = __float_as_uint(tf32_hi(__uint_as_float(src[i])));
+          tmem_st_32x32(tmem_base + lane_base + kColPHi + 32 * h, hi);
+#pragma unroll
+          for (int i = 0; i < 32; ++i)
+            hi[i] = __float_as_uint(__uint_as_float(src[i]) - __uint_as_float(hi[i]));
+          tmem_st_32x32(tmem_base + lane_base + kColPLo + 32 * h, hi);
+        }
+        tmem_st_wait();
+      }
+      khd::tc_fence_before_sync();
+      khd::mbar_arrive(bar_p_ready);
+    }
+    if (ok && num_kv > 0) {
+      ok = khd::mbar_wait(bar_pv_full, static_cast<uint32_t>((num_kv - 1) & 1), &s_abort, status,
+                          khd::kStatusMmaWaitTimeout, 3000u);
+      if (ok) {
+        khd::tc_fence_after_sync();
+        const float inv = 1.0f / l;
+        const int64_t row = static_cast<int64_t>(q0) + row_in_tile;
+        float *orow = out + (bh * seq + row) * kHeadDim;
+        uint32_t t[32];
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          khd::tmem_ld_32x32(tmem_base + lane_base + kColPV + 32 * h, t);
+          khd::tmem_ld_wait();
+          if (row < seq) {
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+              __stcs(reinterpret_cast<float4 *>(orow + 32 * h) + i,
+                     make_float4((acc[32 * h + 4 * i + 0] + __uint_as_float(t[4 * i + 0])) * inv,
+                                 (acc[32 * h + 4 * i + 1] + __uint_as_float(t[4 * i + 1])) * inv,
+                                 (acc[32 * h + 4 * i + 2] + __uint_as_float(t[4 * i + 2])) * inv,
+                                 (acc[32 * h + 4 * i + 3] + __uint_as_float(t[4 * i + 3])) * inv));
+          }
+        }
+      }
+    }
+    khd::tc_fence_before_sync();
+  }
+
+  __syncthreads();
+  if (s_abort) {
+    for (int i = 0; i < 64; ++i) __nanosleep(10000);
+  }
+  if (warp == 1) {
+    khd::tc_fence_after_sync();
+    khd::tmem_dealloc(tmem_base, kTmemCols);
+  }
+}

@@ -1,0 +1,266 @@
+// gemm: C = A . B, row-major fp32, A is m x k, B is k x n, C is m x n, zero
+// seeded accumulator and a plain store (no alpha/beta).
+//
+// Replaces the kernel the reference generates from
+// lib/dsl/kernels/gemm.cpp:116-296 (32x32x32 tiles of scalar fp32 FMAs, one
+// k-tile staged in 8 KiB of static shared memory). Entry symbol `gemm`; the
+// first 21 parameters are the reference's: (A, B, C) as rank-2 memref
+// descriptors. The TMA-fed kernel then takes four tensor maps, the k-block
+// count and a status pointer.
+//
+// Arithmetic: 3xTF32. Each operand is split once into hi = tf32(x) (round to
+// nearest, low 13 mantissa bits cleared) and lo = x - hi (exact in fp32), and
+// every k-step issues three tensor-core products into one fp32 accumulator in
+// tensor memory: lo.hi, hi.lo, hi.hi (lo.lo, ~2^-22 relative, is dropped).
+//
+// Two launches:
+//  gemm_split_a / gemm_split_bt  write A_hi, A_lo (m x kp) and B^T_hi, B^T_lo
+//      (n x kp) into scratch, kp = k rounded up to 32 and zero padded, so both
+//      tensor-core operands are K-major with 128-byte rows whatever k is.
+//  gemm  one CTA per 128 x 256 tile of C. Warp 0 feeds a 2-stage ring of
+//      {A_hi, A_lo, B_hi, B_lo} k-blocks (32 fp32 deep, 96 KiB per stage) with
+//      TMA (128-byte swizzle, out-of-range rows read as zero, which is what
+//      makes ragged m and n work); warp 1 issues tcgen05.mma (M128 N256 K8,
+//      kind::tf32) and releases stages with tcgen05.commit; warps 2-5 read the
+//      256-column fp32 accumulator from tensor memory and store C.
+//
+// Tensor-bound: 2 m n k useful flops; three MMAs per k-step put the ceiling
+// at one third of the TF32 tensor rate.
+#include "kh_tcgen05.cuh"
+
+namespace {
+
+constexpr int kBM = 128;
+constexpr int kBN = 256;
+constexpr int kBK = 32; // fp32 elements: one 128-byte swizzle row
+constexpr int kStages = 2;
+constexpr int kATileBytes = kBM * kBK * 4;                         // 16 KiB
+constexpr int kBTileBytes = kBN * kBK * 4;                         // 32 KiB
+constexpr int kStageBytes = 2 * kATileBytes + 2 * kBTileBytes;     // 96 KiB
+constexpr int kTmemCols = 256;
+constexpr int kThreads = 192;
+constexpr int kGroupM = 16; // m-tiles per rasterisation group (L2 reuse of B)
+
+__device__ __forceinline__ float tf32_hi(float x) {
+  // round to nearest (ties away) on the 13 dropped bits, in integer arithmetic
+  uint32_t u = __float_as_uint(x);
+  u = (u + 0x1000u) & 0xFFFFE000u;
+  return __uint_as_float(u);
+}
+
+} // namespace
+
+// A (m x k, any strides) -> hi, lo (m x kp, contiguous), zero padded in k.
+extern "C" __global__ void __launch_bounds__(256)
+gemm_split_a(KH_MEMREF2(const float, a), float *__restrict__ hi, float *__restrict__ lo, int64_t kp) {
+  const float *__restrict__ a = KH_DATA(a);
+  const int64_t m = a_size0, k = a_size1;
+  const int64_t kp4 = kp >> 2;
+  const int64_t total = m * kp4;
+  const bool vec_ok = khd::is_aligned16(a) && a_stride1 == 1 && (a_stride0 & 3) == 0;
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int64_t r = i / kp4, c = (i - r * kp4) << 2;
+    float v[4];
+    if (vec_ok && c + 4 <= k) {
+      const float4 f = __ldcs(reinterpret_cast<const float4 *>(a + r * a_stride0 + c));
+      v[0] = f.x; v[1] = f.y; v[2] = f.z; v[3] = f.w;
+    } else {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) v[j] = (c + j < k) ? a[r * a_stride0 + (c + j) * a_stride1] : 0.f;
+    }
+    float4 h, l;
+    h.x = tf32_hi(v[0]); h.y = tf32_hi(v[1]); h.z = tf32_hi(v[2]); h.w = tf32_hi(v[3]);
+    l.x = v[0] - h.x; l.y = v[1] - h.y; l.z = v[2] - h.z; l.w = v[3] - h.w;
+    *reinterpret_cast<float4 *>(hi + r * kp + c) = h;
+    *reinterpret_cast<float4 *>(lo + r * kp + c) = l;
+  }
+}
+
+// B (k x n, any strides) -> B^T hi, lo (n x kp, contiguous), zero padded in k.
+// 32 x 32 tiles through shared memory so both sides stay coalesced.
+extern "C" __global__ void __launch_bounds__(256)
+gemm_split_bt(KH_MEMREF2(const float, b), float *__restrict__ hi, float *__restrict__ lo, int64_t kp) {
+  __shared__ float tile[32][33];
+  const float *__restrict__ b = KH_DATA(b);
+  const int64_t k = b_size0, n = b_size1;
+  const int64_t tiles_n = (n + 31) >> 5, tiles_k = kp >> 5;
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5; // 32 x 8
+  for (int64_t t = blockIdx.x; t < tiles_n * tiles_k; t += gridDim.x) {
+    const int64_t tk = t / tiles_n, tn = t - tk * tiles_n;
+    const int64_t k0 = tk << 5, n0 = tn << 5;
+    __syncthreads();
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int64_t kk = k0 + ty + 8 * j, nn = n0 + tx;
+      tile[ty + 8 * j][tx] = (kk < k && nn < n) ? b[kk * b_stride0 + nn * b_stride1] : 0.f;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int64_t nn = n0 + ty + 8 * j, kk = k0 + tx;
+      if (nn < n) {
+        const float v = tile[tx][ty + 8 * j];
+        const float h = tf32_hi(v);
+        hi[nn * kp + kk] = h;
+        lo[nn * kp + kk] = v - h;
+      }
+    }
+  }
+}
+
+extern "C" __global__ void __launch_bounds__(kThreads, 1)
+gemm(KH_MEMREF2(const float, a), KH_MEMREF2(const float, b), KH_MEMREF2(float, c),
+     const __grid_constant__ khd::TensorMap tm_a_hi, const __grid_constant__ khd::TensorMap tm_a_lo,
+     const __grid_constant__ khd::TensorMap tm_b_hi, const __grid_constant__ khd::TensorMap tm_b_lo,
+     int64_t k_blocks, uint32_t *status) {
+  (void)a_alloc; (void)a_ptr; (void)a_off; (void)a_size1; (void)a_stride0; (void)a_stride1;
+  (void)b_alloc; (void)b_ptr; (void)b_off; (void)b_size0; (void)b_stride0; (void)b_stride1;
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ __align__(8) uint64_t bars[2 * kStages + 1];
+  __shared__ uint32_t s_tmem_base;
+  __shared__ int s_abort;
+
+  const int64_t m = a_size0, n = b_size1;
+  float *__restrict__ c = KH_DATA(c);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  // 1024-byte aligned operand ring (the swizzle pattern is anchored there)
+  const uint32_t ring = (khd::smem_u32(smem_raw) + 1023u) & ~1023u;
+  const uint32_t full0 = khd::smem_u32(&bars[0]);
+  const uint32_t empty0 = khd::smem_u32(&bars[kStages]);
+  const uint32_t accum_bar = khd::smem_u32(&bars[2 * kStages]);
+
+  // ---- tile coordinates: groups of kGroupM m-tiles sweep n together ---------
+  const int64_t tiles_m = (m + kBM - 1) / kBM, tiles_n = (n + kBN - 1) / kBN;
+  const int64_t tile = blockIdx.x;
+  const int64_t per_group = kGroupM * tiles_n;
+  const int64_t group = tile / per_group;
+  const int64_t first_m = group * kGroupM;
+  const int64_t rows_in_group = (tiles_m - first_m < kGroupM) ? (tiles_m - first_m) : kGroupM;
+  const int64_t in_group = tile - group * per_group;
+  const int64_t tile_m = first_m + in_group % rows_in_group;
+  const int64_t tile_n = in_group / rows_in_group;
+  const int m0 = static_cast<int>(tile_m * kBM), n0 = static_cast<int>(tile_n * kBN);
+
+  if (threadIdx.x == 0) {
+    s_abort = 0;
+    for (int s = 0; s < kStages; ++s) {
+      khd::mbar_init(full0 + 8 * s, 1);
+      khd::mbar_init(empty0 + 8 * s, 1);
+    }
+    khd::mbar_init(accum_bar, 1);
+    khd::mbar_fence_init();
+    khd::tma_prefetch_descriptor(&tm_a_hi);
+    khd::tma_prefetch_descriptor(&tm_a_lo);
+    khd::tma_prefetch_descriptor(&tm_b_hi);
+    khd::tma_prefetch_descriptor(&tm_b_lo);
+  }
+  if (warp == 1) {
+    khd::tmem_alloc(khd::smem_u32(&s_tmem_base), kTmemCols);
+    khd::tmem_relinquish();
+  }
+  khd::tc_fence_before_sync();
+  __syncthreads();
+  khd::tc_fence_after_sync();
+  const uint32_t tmem_base = s_tmem_base;
+
+  if (warp == 0) {
+    // ---- TMA producer ---------------------------------------------------------
+    if (lane == 0) {
+      for (int64_t kb = 0; kb < k_blocks; ++kb) {
+        const int s = static_cast<int>(kb % kStages);
+        const uint32_t phase = static_cast<uint32_t>((kb / kStages) & 1);
+        if (!khd::mbar_wait(empty0 + 8 * s, phase ^ 1u, &s_abort, status,
+                            khd::kStatusEmptyWaitTimeout, static_cast<uint32_t>(kb)))
+          break;
+        const uint32_t stage = ring + s * kStageBytes;
+        const uint32_t bar = full0 + 8 * s;
+        khd::mbar_arrive_expect_tx(bar, kStageBytes);
+        const int kx = static_cast<int>(kb * kBK);
+        khd::tma_load_2d(stage, &tm_a_hi, kx, m0, bar);
+        khd::tma_load_2d(stage + kATileBytes, &tm_a_lo, kx, m0, bar);
+        khd::tma_load_2d(stage + 2 * kATileBytes, &tm_b_hi, kx, n0, bar);
+        khd::tma_load_2d(stage + 2 * kATileBytes + kBTileBytes, &tm_b_lo, kx, n0, bar);
+      }
+    }
+  } else if (warp == 1) {
+    // ---- MMA issuer -------------------------------------------------------------
+    if (lane == 0) {
+      constexpr uint32_t idesc = khd::umma_idesc_tf32(kBM, kBN);
+      bool ok = true;
+      for (int64_t kb = 0; kb < k_blocks && ok; ++kb) {
+        const int s = static_cast<int>(kb % kStages);
+        const uint32_t phase = static_cast<uint32_t>((kb / kStages) & 1);
+        ok = khd::mbar_wait(full0 + 8 * s, phase, &s_abort, status, khd::kStatusTmaWaitTimeout,
+                            static_cast<uint32_t>(kb));
+        if (!ok) break;
+        khd::tc_fence_after_sync();
+        const uint32_t stage = ring + s * kStageBytes;
+        const uint64_t a_hi = khd::umma_desc_k128(stage);
+        const uint64_t a_lo = khd::umma_desc_k128(stage + kATileBytes);
+        const uint64_t b_hi = khd::umma_desc_k128(stage + 2 * kATileBytes);
+        const uint64_t b_lo = khd::umma_desc_k128(stage + 2 * kATileBytes + kBTileBytes);
+#pragma unroll
+        for (int kk = 0; kk < kBK / 8; ++kk) {
+          const uint64_t adv = static_cast<uint64_t>(kk * 2); // 32 bytes >> 4
+          khd::umma_tf32_ss(tmem_base, a_lo + adv, b_hi + adv, idesc, (kb | kk) != 0 ? 1u : 0u);
+          khd::umma_tf32_ss(tmem_base, a_hi + adv, b_lo + adv, idesc, 1u);
+          khd::umma_tf32_ss(tmem_base, a_hi + adv, b_hi + adv, idesc, 1u);
+        }
+        khd::umma_commit(empty0 + 8 * s); // stage reusable once these MMAs retire
+      }
+      if (ok) khd::umma_commit(accum_bar);
+    }
+  } else {
+    // ---- epilogue: tensor memory -> registers -> C -------------------------------
+    const int quad = warp & 3; // this warp's 32 tensor-memory lanes
+    const bool ok = k_blocks == 0 ||
+                    khd::mbar_wait(accum_bar, 0u, &s_abort, status, khd::kStatusMmaWaitTimeout,
+                                   static_cast<uint32_t>(blockIdx.x));
+    if (ok && k_blocks > 0) {
+      khd::tc_fence_after_sync();
+      const int64_t row = static_cast<int64_t>(m0) + quad * 32 + lane;
+      float *crow = c + row * c_stride0;
+      const bool vec_ok = c_stride1 == 1 && (c_stride0 & 3) == 0 && khd::is_aligned16(c);
+#pragma unroll 1
+      for (int chunk = 0; chunk < kBN / 32; ++chunk) {
+        uint32_t r[32];
+        khd::tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + chunk * 32, r);
+        khd::tmem_ld_wait();
+        const int64_t col0 = static_cast<int64_t>(n0) + chunk * 32;
+        if (row < m) {
+          if (vec_ok && col0 + 32 <= n) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+              __stcs(reinterpret_cast<float4 *>(crow + col0) + j,
+                     make_float4(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]),
+                                 __uint_as_float(r[4 * j + 2]), __uint_as_float(r[4 * j + 3])));
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (col0 + j < n) crow[(col0 + j) * c_stride1] = __uint_as_float(r[j]);
+          }
+        }
+      }
+    } else if (ok) {
+      // k == 0: the product is all zeros
+      const int64_t row = static_cast<int64_t>(m0) + quad * 32 + lane;
+      if (row < m)
+        for (int j = 0; j < kBN; ++j)
+          if (n0 + j < n) c[row * c_stride0 + (n0 + j) * c_stride1] = 0.f;
+    }
+    khd::tc_fence_before_sync();
+  }
+
+  __syncthreads();
+  if (s_abort) {
+    // A wait gave up: leave time for copies still in flight to land before the
+    // shared memory and tensor memory are released.
+    for (int i = 0; i < 64; ++i) __nanosleep(10000);
+  }
+  if (warp == 1) {
+    khd::tc_fence_after_sync();
+    khd::tmem_dealloc(tmem_base, kTmemCols);
+  }
+}

@@ -1,0 +1,60 @@
+// Shared device-side definitions for the sm_100a kernels.
+//
+// Device ABI. Every tensor argument arrives as the expanded memref descriptor
+// the reference's code generator emits for a kernel parameter
+// (lib/compiler/emitter.cpp:712-725): allocated pointer, aligned pointer,
+// offset, sizes[N], strides[N] - 2N+3 eight-byte parameters, packed on the
+// host by LaunchArgs::add_memref. The entry symbol equals the kernel name.
+// The macros below declare those parameters; data is read at aligned+offset,
+// and shapes are taken from the descriptor, not from compile-time constants.
+#pragma once
+
+#include <cstdint>
+
+#define KH_MEMREF1(T, name)                                                                        \
+  T *name##_alloc, T *name##_ptr, int64_t name##_off, int64_t name##_size0, int64_t name##_stride0
+#define KH_MEMREF2(T, name)                                                                        \
+  T *name##_alloc, T *name##_ptr, int64_t name##_off, int64_t name##_size0, int64_t name##_size1,  \
+      int64_t name##_stride0, int64_t name##_stride1
+#define KH_MEMREF4(T, name)                                                                        \
+  T *name##_alloc, T *name##_ptr, int64_t name##_off, int64_t name##_size0, int64_t name##_size1,  \
+      int64_t name##_size2, int64_t name##_size3, int64_t name##_stride0, int64_t name##_stride1,  \
+      int64_t name##_stride2, int64_t name##_stride3
+#define KH_DATA(name) ((name##_ptr) + (name##_off))
+
+namespace khd {
+
+// Status word protocol for kernels with waits (scan look-back, mbarrier
+// pipelines): status[0] == 0 means clean; a wait that runs out of its
+// iteration budget stores a non-zero code (first writer wins) and the kernel
+// stops issuing work and returns. The host reads the word after the stream
+// sync and maps it to an error. No trap, no device assert.
+enum : uint32_t {
+  kStatusOk = 0,
+  kStatusScanLookbackTimeout = 1,
+  kStatusTmaWaitTimeout = 2,
+  kStatusMmaWaitTimeout = 3,
+  kStatusEpilogueWaitTimeout = 4,
+  kStatusEmptyWaitTimeout = 5,
+};
+
+__device__ __forceinline__ void report_status(uint32_t *status, uint32_t code, uint32_t detail) {
+  if (status != nullptr && atomicCAS(status, 0u, code) == 0u) status[1] = detail;
+}
+
+__device__ __forceinline__ bool is_aligned16(const void *p) {
+  return (reinterpret_cast<uintptr_t>(p) & 15u) == 0;
+}
+
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+} // namespace khd

@@ -1,0 +1,120 @@
+// Registry record of the attention template: shape rules of the reference's
+// lib/dsl/kernels/attention.cpp:94-120 (all four keys required and positive,
+// head_dim pinned to 64, seq a multiple of the 64-key tile), the scratch
+// layout of the hi/lo split, the six tensor maps and the two launches.
+#include "executor.hpp"
+#include "registry.hpp"
+
+#include <stdexcept>
+
+namespace kh {
+namespace {
+
+constexpr int64_t kHeadDim = 64, kBQ = 128, kBKV = 64;
+constexpr size_t kAttnSmem = 64 * 1024 + 2 * 64 * 1024 + 1024;
+
+KernelPlan plan_attention(const ShapeMap &shape, const DeviceLimits &l) {
+  for (const char *key : {"batch", "heads", "seq", "head_dim"})
+    if (!shape.count(key))
+      throw std::runtime_error("attention template: shape attributes 'batch', 'heads', 'seq' and "
+                               "'head_dim' are required (missing '" + std::string(key) + "')");
+  const int64_t b = shape.at("batch"), h = shape.at("heads"), s = shape.at("seq"),
+                d = shape.at("head_dim");
+  if (b <= 0 || h <= 0 || s <= 0 || d <= 0)
+    throw std::runtime_error("attention template: shape attributes 'batch', 'heads', 'seq' and "
+                             "'head_dim' must be positive");
+  if (s % kBKV != 0)
+    throw std::runtime_error("attention template: shape attribute 'seq' must be divisible by the "
+                             "K/V tile extent 64 (got seq = " + std::to_string(s) + ")");
+  if (d != kHeadDim)
+    throw std::runtime_error("attention template: the kernel is pinned to head_dim = 64 (got "
+                             "head_dim = " + std::to_string(d) + ")");
+  KernelPlan p;
+  p.kernel = "attention";
+  p.shape = shape;
+  for (const char *name : {"Q", "K", "V"}) p.tensors.push_back({name, {b, h, s, d}, false});
+  p.tensors.push_back({"O", {b, h, s, d}, true});
+  const int64_t elems = b * h * s * d;
+  p.workspace_bytes = static_cast<size_t>(elems) * 4 * 6;
+  long sms = query_cu_count(l);
+  if (sms <= 0) sms = 148;
+  LaunchStep split;
+  split.entry = "attention_split";
+  split.block = {256, 1, 1};
+  const int64_t want = (elems / 4 + 255) / 256;
+  split.grid = {static_cast<unsigned>(std::min<int64_t>(want, sms * 8)), 1, 1};
+  split.param_count = 33 + 6;
+  LaunchStep main;
+  main.entry = "attention";
+  main.block = {192, 1, 1};
+  main.grid = {static_cast<unsigned>(b * h * ((s + kBQ - 1) / kBQ)), 1, 1};
+  main.dynamic_smem = kAttnSmem;
+  main.param_count = 44 + 6 + 1;
+  main.tmem_columns = 512;
+  p.steps = {split, main};
+  p.work = 4.0 * static_cast<double>(b) * static_cast<double>(h) * static_cast<double>(s) *
+           static_cast<double>(s) * static_cast<double>(d);
+  p.work_is_flops = true;
+  return p;
+}
+
+Result<void> run_attention(Executor &ex, const KernelPlan &p, const std::vector<void *> &buf,
+                           StreamHandle stream) {
+  const std::vector<int64_t> &shape = p.tensors[0].shape;
+  const int64_t bh = shape[0] * shape[1], s = shape[2];
+  const int64_t elems = bh * s * kHeadDim;
+  auto ws = ex.workspace(p.workspace_bytes);
+  if (!ws) return std::unexpected(ws.error());
+  float *base = static_cast<float *>(*ws);
+  float *q_hi = base, *q_lo = base + elems, *k_hi = base + 2 * elems, *k_lo = base + 3 * elems,
+        *vt_hi = base + 4 * elems, *vt_lo = base + 5 * elems;
+
+  auto f_split = ex.function("attention", "attention_split");
+  if (!f_split) return std::unexpected(f_split.error());
+  auto f_main = ex.function("attention", "attention");
+  if (!f_main) return std::unexpected(f_main.error());
+  {
+    LaunchArgs args;
+    for (int i = 0; i < 3; ++i) args.add_memref(buf[i], shape);
+    for (float *ptr : {q_hi, q_lo, k_hi, k_lo, vt_hi, vt_lo})
+      args.add_scalar<uint64_t>(reinterpret_cast<uint64_t>(ptr));
+    if (auto r = ex.launch(*f_split, p.steps[0], args, stream); !r) return r;
+  }
+  // Q, K: [bh*seq rows, 64]; V^T: [bh*64 rows, seq]. 32-column boxes = one swizzle row.
+  auto make_map = [&](const float *ptr, int64_t cols, int64_t rows, uint32_t box_rows) {
+    TensorMapSpec t;
+    t.global_address = ptr;
+    t.rank = 2;
+    t.dims[0] = static_cast<uint64_t>(cols);
+    t.dims[1] = static_cast<uint64_t>(rows);
+    t.strides_bytes[0] = static_cast<uint64_t>(cols) * 4;
+    t.box[0] = 32;
+    t.box[1] = box_rows;
+    t.swizzle_bytes = 128;
+    return ex.backend().encode_tensor_map(t);
+  };
+  LaunchArgs args;
+  for (int i = 0; i < 4; ++i) args.add_memref(buf[i], shape);
+  struct M { const float *p; int64_t cols, rows; uint32_t box; };
+  const M maps[6] = {{q_hi, kHeadDim, bh * s, static_cast<uint32_t>(kBQ)},
+                     {q_lo, kHeadDim, bh * s, static_cast<uint32_t>(kBQ)},
+                     {k_hi, kHeadDim, bh * s, static_cast<uint32_t>(kBKV)},
+                     {k_lo, kHeadDim, bh * s, static_cast<uint32_t>(kBKV)},
+                     {vt_hi, s, bh * kHeadDim, static_cast<uint32_t>(kHeadDim)},
+                     {vt_lo, s, bh * kHeadDim, static_cast<uint32_t>(kHeadDim)}};
+  for (const M &mm : maps) {
+    auto t = make_map(mm.p, mm.cols, mm.rows, mm.box);
+    if (!t) return std::unexpected(t.error());
+    args.add_tensor_map(*t);
+  }
+  args.add_scalar<uint64_t>(reinterpret_cast<uint64_t>(ex.status_word()));
+  return ex.launch(*f_main, p.steps[1], args, stream);
+}
+
+} // namespace
+
+void register_attention_kernel() {
+  register_kernel({"attention", "attention", plan_attention, run_attention});
+}
+
+} // namespace kh

@@ -1,0 +1,217 @@
+#include "executor.hpp"
+
+#include "../runtime/launch_verifier.hpp"
+
+#include <algorithm>
+#include <climits>
+#include <cstring>
+
+namespace kh {
+
+Result<std::unique_ptr<Executor>> Executor::create(std::shared_ptr<Backend> backend, int ordinal) {
+  if (!backend) return fail(1, "Executor::create: null backend");
+  auto ctx = DeviceContext::create(backend, ordinal);
+  if (!ctx) return std::unexpected(ctx.error());
+  std::unique_ptr<Executor> ex(new Executor());
+  ex->backend_ = backend;
+  ex->info_ = ctx->info();
+  if (ex->info_.cc_major != 10)
+    return fail(1, "Executor::create: device '" + ex->info_.name + "' is compute capability " +
+                       std::to_string(ex->info_.cc_major) + "." + std::to_string(ex->info_.cc_minor) +
+                       "; the kernels are built for sm_100a only");
+  ex->limits_ = resolve_limits(*backend);
+  auto st = Buffer::allocate(backend, 256);
+  if (!st) return std::unexpected(st.error());
+  ex->status_ = std::move(*st);
+  if (auto r = backend->memset32_async(ex->status_.data(), 0, 64, nullptr); !r)
+    return std::unexpected(r.error());
+  if (auto r = backend->device_synchronize(); !r) return std::unexpected(r.error());
+  return ex;
+}
+
+Executor::~Executor() {
+  if (backend_ && host_stream_) (void)backend_->stream_destroy(host_stream_);
+}
+
+Result<KernelFunction> Executor::function(const std::string &code_object, const std::string &entry) {
+  const std::string key = code_object + ":" + entry;
+  if (auto it = functions_.find(key); it != functions_.end()) return it->second.fn;
+  auto mod = modules_.find(code_object);
+  if (mod == modules_.end()) {
+    const CodeObject *co = find_code_object(code_object);
+    if (co == nullptr || co->size == 0)
+      return fail(1, "no embedded sm_100a code object named '" + code_object +
+                         "' (the library was built without its CUDA kernels)");
+    auto loaded = GpuModule::load(backend_, co->image, co->size);
+    if (!loaded) return fail(loaded.error().code, "loading code object '" + code_object + "': " +
+                                                      loaded.error().message);
+    mod = modules_.emplace(code_object, std::move(*loaded)).first;
+  }
+  auto fn = mod->second.get_function(entry.c_str());
+  if (!fn) return std::unexpected(fn.error());
+  FunctionInfo fi;
+  fi.fn = *fn;
+  if (auto attrs = backend_->function_attributes(fn->handle))
+    fi.static_smem = static_cast<size_t>(attrs->static_smem_bytes);
+  functions_[key] = fi;
+  return *fn;
+}
+
+Result<void *> Executor::workspace(size_t bytes) {
+  if (bytes == 0) bytes = 256;
+  if (workspace_.size() < bytes) {
+    // Work queued on any stream may still read the old allocation.
+    if (auto r = backend_->device_synchronize(); !r) return std::unexpected(r.error());
+    workspace_ = Buffer();
+    auto b = Buffer::allocate(backend_, bytes);
+    if (!b) return fail(b.error().code, "scratch allocation of " + std::to_string(bytes) +
+                                            " bytes failed: " + b.error().message);
+    workspace_ = std::move(*b);
+  }
+  return workspace_.data();
+}
+
+Result<void> Executor::launch(KernelFunction fn, const LaunchStep &step, LaunchArgs &args,
+                              StreamHandle s) {
+  FunctionInfo *fi = nullptr;
+  for (auto &kv : functions_)
+    if (kv.second.fn.handle == fn.handle) fi = &kv.second;
+  LaunchConfig cfg;
+  cfg.grid_x = static_cast<int>(std::min<unsigned>(step.grid.x, INT_MAX));
+  cfg.grid_y = static_cast<int>(step.grid.y);
+  cfg.grid_z = static_cast<int>(step.grid.z);
+  cfg.threads_per_workgroup = static_cast<int>(step.block.x * step.block.y * step.block.z);
+  cfg.static_shared_bytes = fi ? fi->static_smem : 0;
+  cfg.dynamic_shared_bytes = step.dynamic_smem;
+  cfg.cluster_size = static_cast<int>(step.cluster);
+  if (step.dynamic_smem > 0 && fi != nullptr && fi->optin_smem < step.dynamic_smem &&
+      cfg.static_shared_bytes + step.dynamic_smem <= static_cast<size_t>(limits_.max_dynamic_smem_optin)) {
+    if (auto r = backend_->function_set_max_dynamic_smem(fn.handle, step.dynamic_smem); !r)
+      return fail(r.error().code, "launch of '" + step.entry + "': dynamic shared memory opt-in failed: " +
+                                      r.error().message);
+    fi->optin_smem = step.dynamic_smem;
+  }
+  // Limits are checked analytically on every launch; the driver's occupancy
+  // answer is asked for by KernelLaunch::launch and the occupancy report.
+  LaunchVerifier verifier;
+  if (auto ok = verifier.verify(cfg, limits_, nullptr); !ok)
+    return fail(1, "launch of '" + step.entry + "' refused: " + ok.error());
+  return backend_->launch_kernel(fn.handle, step.grid, step.block, step.dynamic_smem, s, args.params(),
+                                 step.cluster);
+}
+
+Result<Executor::ScanTicket> Executor::scan_ticket(int64_t tiles, unsigned grid) {
+  if (tiles > scan_capacity_tiles_ || scan_epoch_ >= (1u << 30) - 1) {
+    const int64_t cap = std::max<int64_t>(tiles, 4096);
+    if (auto r = backend_->device_synchronize(); !r) return std::unexpected(r.error());
+    scan_state_ = Buffer();
+    const size_t words = 2 + 3 * static_cast<size_t>(cap);
+    auto b = Buffer::allocate(backend_, words * 8);
+    if (!b) return std::unexpected(b.error());
+    scan_state_ = std::move(*b);
+    if (auto r = backend_->memset32_async(scan_state_.data(), 0, words * 2, nullptr); !r)
+      return std::unexpected(r.error());
+    if (auto r = backend_->device_synchronize(); !r) return std::unexpected(r.error());
+    scan_capacity_tiles_ = cap;
+    scan_epoch_ = 0;
+    scan_ticket_base_ = 0;
+  }
+  ScanTicket t;
+  t.state = scan_state_.data();
+  t.epoch = ++scan_epoch_;
+  t.ticket_base = scan_ticket_base_;
+  scan_ticket_base_ += static_cast<uint64_t>(tiles) + grid; // each block ends on one surplus ticket
+  return t;
+}
+
+Result<void> Executor::run(const std::string &kernel, const ShapeMap &shape,
+                           const std::vector<void *> &buffers, StreamHandle stream) {
+  if (auto r = backend_->make_current(); !r) return r;
+  const KernelRecord *rec = nullptr;
+  KernelPlan plan;
+  try {
+    rec = &find_kernel(kernel);
+    plan = rec->plan(shape, limits_);
+  } catch (const std::exception &e) {
+    return fail(2, e.what());
+  }
+  if (buffers.size() != plan.tensors.size())
+    return fail(2, "kernel '" + kernel + "' takes " + std::to_string(plan.tensors.size()) +
+                       " buffers, got " + std::to_string(buffers.size()));
+  for (size_t i = 0; i < buffers.size(); ++i)
+    if (buffers[i] == nullptr && plan.tensors[i].name != "tmp")
+      return fail(2, "kernel '" + kernel + "': buffer '" + plan.tensors[i].name + "' is null");
+  return rec->run(*this, plan, buffers, stream);
+}
+
+Result<void> Executor::synchronize(StreamHandle stream) {
+  if (auto r = backend_->make_current(); !r) return r;
+  if (auto r = backend_->stream_synchronize(stream); !r) return r;
+  uint32_t host[2] = {0, 0};
+  if (auto r = backend_->memcpy_d2h(host, status_.data(), sizeof host); !r) return r;
+  uint32_t scan_host[2] = {0, 0};
+  if (scan_state_.data() != nullptr) {
+    if (auto r = backend_->memcpy_d2h(scan_host, static_cast<char *>(scan_state_.data()) + 8,
+                                      sizeof scan_host);
+        !r)
+      return r;
+  }
+  if (host[0] == 0 && scan_host[0] == 0) return {};
+  // Clear so that the next launch starts clean; scan state is rebuilt from scratch.
+  (void)backend_->memset32_async(status_.data(), 0, 2, nullptr);
+  if (scan_host[0] != 0) scan_capacity_tiles_ = 0;
+  (void)backend_->device_synchronize();
+  const uint32_t code = host[0] ? host[0] : scan_host[0];
+  const uint32_t detail = host[0] ? host[1] : scan_host[1];
+  static const char *names[] = {"ok", "scan look-back wait", "TMA (full-stage) wait",
+                                "MMA (accumulator) wait", "epilogue wait", "empty-stage wait"};
+  return fail(kDeviceTimeout, std::string("a device-side bounded wait ran out: ") +
+                                  (code < 6 ? names[code] : "unknown wait") + " (code " +
+                                  std::to_string(code) + ", detail " + std::to_string(detail) +
+                                  "); the kernel stopped and its output is incomplete");
+}
+
+Result<void> Executor::run_host(const std::string &kernel, const ShapeMap &shape,
+                                const std::vector<void *> &host) {
+  if (auto r = backend_->make_current(); !r) return r;
+  KernelPlan plan;
+  try {
+    plan = find_kernel(kernel).plan(shape, limits_);
+  } catch (const std::exception &e) {
+    return fail(2, e.what());
+  }
+  if (host.size() != plan.tensors.size())
+    return fail(2, "kernel '" + kernel + "' takes " + std::to_string(plan.tensors.size()) +
+                       " buffers, got " + std::to_string(host.size()));
+  if (host_stream_ == nullptr) {
+    auto s = backend_->stream_create();
+    if (!s) return std::unexpected(s.error());
+    host_stream_ = *s;
+  }
+  if (host_pool_.size() < plan.tensors.size()) host_pool_.resize(plan.tensors.size());
+  std::vector<void *> dev(plan.tensors.size());
+  for (size_t i = 0; i < plan.tensors.size(); ++i) {
+    const size_t bytes = static_cast<size_t>(plan.tensors[i].elements()) * 4;
+    if (host_pool_[i].size() < bytes) {
+      if (auto r = backend_->device_synchronize(); !r) return r;
+      host_pool_[i] = Buffer();
+      auto b = Buffer::allocate(backend_, bytes);
+      if (!b) return std::unexpected(b.error());
+      host_pool_[i] = std::move(*b);
+    }
+    dev[i] = host_pool_[i].data();
+    if (!plan.tensors[i].is_output && host[i] != nullptr)
+      if (auto r = backend_->memcpy_h2d_async(dev[i], host[i], bytes, host_stream_); !r) return r;
+  }
+  if (auto r = run(kernel, shape, dev, host_stream_); !r) return r;
+  for (size_t i = 0; i < plan.tensors.size(); ++i)
+    if (plan.tensors[i].is_output && host[i] != nullptr)
+      if (auto r = backend_->memcpy_d2h_async(host[i], dev[i],
+                                              static_cast<size_t>(plan.tensors[i].elements()) * 4,
+                                              host_stream_);
+          !r)
+        return r;
+  return synchronize(host_stream_);
+}
+
+} // namespace kh

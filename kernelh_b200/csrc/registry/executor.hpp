@@ -1,0 +1,75 @@
+// Executor: one device's launch machinery behind the kernel-name + shape
+// operator surface. Owns the loaded code objects, a grow-only scratch
+// allocation, the scan look-back state, the device status word that bounded
+// waits report into, and a pool of device buffers for host-pointer calls.
+// The path fails loudly when the driver, a code object or an entry symbol is
+// missing; there is no CPU path.
+#pragma once
+
+#include "../runtime/objects.hpp"
+#include "registry.hpp"
+
+#include <map>
+#include <memory>
+#include <string>
+#include <vector>
+
+namespace kh {
+
+class Executor {
+public:
+  static Result<std::unique_ptr<Executor>> create(std::shared_ptr<Backend> backend, int ordinal);
+  ~Executor();
+
+  Backend &backend() { return *backend_; }
+  const std::shared_ptr<Backend> &backend_ptr() const { return backend_; }
+  const DeviceInfo &info() const { return info_; }
+  const DeviceLimits &limits() const { return limits_; }
+
+  // Plans and enqueues `kernel` for `shape` on device buffers (plan.tensors order).
+  Result<void> run(const std::string &kernel, const ShapeMap &shape,
+                   const std::vector<void *> &buffers, StreamHandle stream);
+  // Same through host buffers: inputs are copied in, outputs copied back, the
+  // device status is checked. Blocking.
+  Result<void> run_host(const std::string &kernel, const ShapeMap &shape,
+                        const std::vector<void *> &host_buffers);
+  // Waits for `stream` and turns a recorded device-side wait timeout into an Error.
+  Result<void> synchronize(StreamHandle stream);
+
+  // ---- used by the kernel records ------------------------------------------------
+  Result<KernelFunction> function(const std::string &code_object, const std::string &entry);
+  Result<void *> workspace(size_t bytes);
+  Result<void> launch(KernelFunction fn, const LaunchStep &step, LaunchArgs &args, StreamHandle s);
+  uint32_t *status_word() const { return static_cast<uint32_t *>(status_.data()); }
+
+  struct ScanTicket {
+    void *state;
+    uint32_t epoch;
+    uint64_t ticket_base;
+  };
+  // Look-back state for a scan of `tiles` tiles launched with `grid` blocks.
+  Result<ScanTicket> scan_ticket(int64_t tiles, unsigned grid);
+
+private:
+  Executor() = default;
+  struct FunctionInfo {
+    KernelFunction fn;
+    size_t static_smem = 0;
+    size_t optin_smem = 0; // largest dynamic size already opted in
+  };
+  std::shared_ptr<Backend> backend_;
+  DeviceInfo info_;
+  DeviceLimits limits_{};
+  std::map<std::string, GpuModule> modules_;
+  std::map<std::string, FunctionInfo> functions_;
+  Buffer workspace_;
+  Buffer status_;
+  Buffer scan_state_;
+  int64_t scan_capacity_tiles_ = 0;
+  uint32_t scan_epoch_ = 0;
+  uint64_t scan_ticket_base_ = 0;
+  std::vector<Buffer> host_pool_;
+  StreamHandle host_stream_ = nullptr;
+};
+
+} // namespace kh

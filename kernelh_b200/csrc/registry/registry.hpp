@@ -1,0 +1,80 @@
+// Kernel registry: process-wide map from a kernel-template name to the record
+// that knows how to plan and launch it. Same behaviour as the reference's
+// registry (include/kernelh/dsl/program.hpp:64-67, lib/dsl/registry.cpp:23-42,
+// lib/dsl/program.cpp:27-37): built-ins appear on first use, registering an
+// existing name replaces it, names list sorted, and an unknown name throws
+// std::runtime_error "unknown kernel template '<name>'; registered kernels: ...".
+// The registered value here is a hand-written kernel (code object, entry
+// symbols, launch plan) rather than an IR-emitting function; launch geometry
+// belongs to the record, not to the caller.
+#pragma once
+
+#include "../runtime/backend.hpp"
+#include "../runtime/device_limits.hpp"
+#include "shape_text.hpp"
+
+#include <functional>
+#include <string>
+#include <vector>
+
+namespace kh {
+
+class Executor;
+
+struct TensorArg {
+  std::string name;
+  std::vector<int64_t> shape; // fp32 elements, row-major contiguous
+  bool is_output = false;
+  int64_t elements() const {
+    int64_t n = 1;
+    for (int64_t d : shape) n *= d;
+    return n;
+  }
+};
+
+struct LaunchStep {
+  std::string entry;
+  LaunchDims grid, block;
+  size_t dynamic_smem = 0;
+  unsigned cluster = 1;
+  int param_count = 0;   // kernel parameters (descriptor slots + extras)
+  int tmem_columns = 0;
+};
+
+struct KernelPlan {
+  std::string kernel;
+  ShapeMap shape;
+  std::vector<TensorArg> tensors; // caller-visible buffers, template order
+  size_t workspace_bytes = 0;     // scratch the executor provides
+  std::vector<LaunchStep> steps;
+  double work = 0.0;              // flops or bytes, the reference's metric conventions
+  bool work_is_flops = false;
+};
+
+struct KernelRecord {
+  std::string name;
+  std::string code_object; // which embedded cubin holds the entry symbols
+  // Validates the shape (throws std::runtime_error naming the offending key,
+  // as the reference's templates do) and lays out the launch for `limits`.
+  std::function<KernelPlan(const ShapeMap &, const DeviceLimits &)> plan;
+  // Enqueues the launches of `plan` on `stream`; `buffers` are device pointers
+  // in plan.tensors order.
+  std::function<Result<void>(Executor &, const KernelPlan &, const std::vector<void *> &,
+                             StreamHandle)>
+      run;
+};
+
+void register_kernel(KernelRecord record);
+std::vector<std::string> registered_kernels();
+const KernelRecord &find_kernel(const std::string &name);
+
+// Embedded code objects (one cubin per kernel source), generated at build time.
+struct CodeObject {
+  const char *name;
+  const unsigned char *image;
+  size_t size;
+};
+const CodeObject *find_code_object(const std::string &name);
+std::vector<std::string> code_object_names();
+
+} // namespace kh

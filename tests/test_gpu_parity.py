@@ -1,0 +1,320 @@
+"""Parity of the sm_100a kernels with the fp64 CPU oracle, called through the C
+ABI on a real B200. Inputs, references, tolerances and negative controls are
+those of the reference's end-to-end tests (test/unit/e2e_*_test.cpp), followed
+by the benchmark configurations' synthetic inputs with the stricter bounds
+stated for them: vecadd bit-exact; max relative error (floored at 1e-3 * rms of
+the reference) <= 1e-5 for the elementwise and row kernels and <= 1e-5 * sqrt(K)
+for scan (K = n), gemm (K = k) and attention (K = seq)."""
+import math
+
+import numpy as np
+import pytest
+
+torch = pytest.importorskip("torch")
+import kernelh_b200 as kh
+
+pytestmark = pytest.mark.gpu
+
+REL = 1e-5
+
+
+@pytest.fixture(scope="module")
+def ctx():
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    torch.cuda.set_device(0)
+    torch.zeros(1, device="cuda")
+    c = kh.Context(0)
+    assert c.device_info().cc_major == 10
+    yield c
+    c.close()
+
+
+def dev(a):
+    return torch.from_numpy(np.ascontiguousarray(a)).cuda()
+
+
+def run(ctx, kernel, shape, inputs, out_shape):
+    """Launch through kh_launch on device tensors; returns the output as numpy."""
+    out = torch.full(out_shape, float("nan"), dtype=torch.float32, device="cuda")
+    bufs = [dev(x) if isinstance(x, np.ndarray) else x for x in inputs] + [out]
+    ctx.launch(kernel, shape, bufs, torch.cuda.current_stream().cuda_stream)
+    ctx.synchronize(torch.cuda.current_stream().cuda_stream)
+    return out.cpu().numpy()
+
+
+# --------------------------------------------------------------------------- vecadd
+@pytest.mark.parametrize("n", [1024, 65536, 1 << 20, 1, 3, 1025, 4097, 1000003])
+def test_vecadd_reference_pattern_bit_exact(ctx, oracle, n):
+    a, b = oracle.vecadd_pattern(n)
+    c = run(ctx, "vecadd", f"n={n}", [a, b], (n,))
+    ref = oracle.vecadd_ref(a, b)
+    assert oracle.compare(c, ref).max_abs <= 1e-6  # the reference's bound
+    assert oracle.bit_mismatches(c, ref) == 0      # the bound asked of this build
+    # negative control: a - b must disagree everywhere
+    assert oracle.bit_mismatches(c, oracle.vecadd_ref(a, b, subtract=True)) == n
+
+
+def test_vecadd_benchmark_config_bit_exact(ctx, oracle):
+    n = 1 << 24
+    a = oracle.uniform(n, oracle.BASE_SEED, -1, 1)
+    b = oracle.uniform(n, oracle.BASE_SEED + 1, -1, 1)
+    c = run(ctx, "vecadd", f"n={n}", [a, b], (n,))
+    assert oracle.bit_mismatches(c, oracle.vecadd_ref(a, b)) == 0
+
+
+def test_vecadd_misaligned_pointers_and_typed_entry(ctx, oracle):
+    n = 10007
+    a, b = oracle.vecadd_pattern(n + 1)
+    da, db = dev(a), dev(b)
+    out = torch.zeros(n + 1, device="cuda")
+    ctx.vecadd(da[1:], db[1:], out[1:], n, torch.cuda.current_stream().cuda_stream)
+    ctx.synchronize()
+    assert oracle.bit_mismatches(out[1:].cpu().numpy(), oracle.vecadd_ref(a[1:].copy(), b[1:].copy())) == 0
+    assert out[0].item() == 0.0
+
+
+def test_run_host_path(ctx, oracle):
+    n = 100000
+    a, b = oracle.vecadd_pattern(n)
+    c = np.zeros(n, np.float32)
+    ctx.run_host("vecadd", f"n={n}", [a, b, c])
+    assert oracle.bit_mismatches(c, oracle.vecadd_ref(a, b)) == 0
+
+
+# --------------------------------------------------------------------------- fused_gelu
+@pytest.mark.parametrize("n", [4194304, 1048576, 1000, 7])
+def test_fused_gelu_reference_inputs(ctx, oracle, n):
+    x = oracle.lcg(n, 0x3A5F91)
+    y = run(ctx, "fused_gelu", f"n={n}", [x, None], (n,))
+    cmp_ = oracle.compare(y, oracle.fused_gelu_ref(x))
+    assert cmp_.non_finite == 0 and cmp_.max_abs <= 1e-4  # the reference's bound
+    assert cmp_.max_rel_floored <= REL
+    xs = oracle.lcg(n, 0x9C21A7)
+    ys = run(ctx, "fused_gelu", f"n={n}", [xs, None], (n,))
+    if n >= 1000:  # negative control: GELU without tanh must fail the same check
+        assert oracle.compare(ys, oracle.fused_gelu_ref(xs, no_tanh_control=True)).max_abs > 1e-4
+
+
+def test_fused_gelu_rows_cols_shape_and_bias_form(ctx, oracle):
+    x = oracle.lcg(64 * 96, 0x3A5F91)
+    y = run(ctx, "fused_gelu", "rows=64,cols=96", [x, None], (64 * 96,))
+    assert oracle.compare(y, oracle.fused_gelu_ref(x)).max_rel_floored <= REL
+    n = 1 << 22
+    x = oracle.normal(n, oracle.BASE_SEED, 0, 1)
+    bias = oracle.normal(n, oracle.BASE_SEED + 1, 0, 1)
+    y = run(ctx, "fused_gelu", f"n={n},bias=1", [x, bias], (n,))
+    cmp_ = oracle.compare(y, oracle.bias_gelu_ref(x, bias))
+    assert cmp_.non_finite == 0 and cmp_.max_rel_floored <= REL and cmp_.max_abs <= 1e-4
+    wide = oracle.normal(4096, 5, 0, 30)  # saturating arguments stay finite
+    y = run(ctx, "fused_gelu", "n=4096,bias=1", [wide, np.zeros(4096, np.float32)], (4096,))
+    assert oracle.compare(y, oracle.bias_gelu_ref(wide, np.zeros(4096, np.float32))).max_rel_floored <= REL
+
+
+# --------------------------------------------------------------------------- softmax
+@pytest.mark.parametrize("rows,cols", [(4096, 1024), (16384, 4096), (1, 8192), (37, 1000), (5, 333),
+                                       (3, 10000), (2, 4), (9, 12288)])
+def test_softmax_reference_inputs(ctx, oracle, rows, cols):
+    x = oracle.lcg((rows, cols), 0x27AB13)
+    y = run(ctx, "softmax", f"rows={rows},cols={cols}", [x], (rows, cols))
+    ref = oracle.softmax_ref(x)
+    cmp_ = oracle.compare(y, ref)
+    assert cmp_.non_finite == 0 and cmp_.max_abs <= 1e-4
+    assert cmp_.max_rel_floored <= REL
+    np.testing.assert_allclose(y.sum(axis=1), 1.0, atol=1e-5)
+    assert oracle.compare(y, oracle.softmax_ref(x, uniform_control=True)).max_abs > (1e-4 if cols <= 4096 else 0)
+
+
+def test_softmax_stability_rows(ctx, oracle):
+    pat = np.array([1000, -1000, 0, 0.5, -0.5], np.float32)
+    x = np.ascontiguousarray(np.tile(pat, 1024 * 1024 // 5 + 1)[:1024 * 1024].reshape(1024, 1024))
+    y = run(ctx, "softmax", "rows=1024,cols=1024", [x], (1024, 1024))
+    cmp_ = oracle.compare(y, oracle.softmax_ref(x))
+    assert cmp_.non_finite == 0 and cmp_.max_abs <= 1e-4
+
+
+def test_softmax_benchmark_config(ctx, oracle):
+    x = oracle.normal((4096, 1024), oracle.BASE_SEED, 0, 2.0)  # N(0, 4) read as variance 4
+    y = run(ctx, "softmax", "rows=4096,cols=1024", [x], (4096, 1024))
+    cmp_ = oracle.compare(y, oracle.softmax_ref(x))
+    assert cmp_.non_finite == 0 and cmp_.max_rel_floored <= REL
+
+
+# --------------------------------------------------------------------------- layernorm
+@pytest.mark.parametrize("rows,cols", [(4096, 1024), (16384, 4096), (37, 1000), (5, 333), (3, 10000),
+                                       (2, 4)])
+def test_layernorm_reference_inputs(ctx, oracle, rows, cols):
+    s = oracle.LcgStream(0x2E2E8A)
+    x, g, b = s.fill((rows, cols)), s.fill(cols), s.fill(cols)
+    y = run(ctx, "layernorm", f"rows={rows},cols={cols}", [x, g, b], (rows, cols))
+    cmp_ = oracle.compare(y, oracle.layernorm_ref(x, g, b))
+    assert cmp_.non_finite == 0 and cmp_.max_abs <= 1e-4
+    assert cmp_.max_rel_floored <= REL
+
+
+def test_layernorm_constant_rows_give_beta(ctx, oracle):
+    s = oracle.LcgStream(0xC0578A)
+    g, b = s.fill(1024), s.fill(1024)
+    x = np.full((64, 1024), 3.0, np.float32)
+    y = run(ctx, "layernorm", "rows=64,cols=1024", [x, g, b], (64, 1024))
+    assert np.isfinite(y).all()
+    assert oracle.compare(y, oracle.layernorm_ref(x, g, b)).max_abs <= 1e-4
+    assert np.array_equal(y[0], b)
+    with np.errstate(all="ignore"):  # negative control: eps = 0 turns these rows into NaN
+        assert not (oracle.compare(y, oracle.layernorm_ref(x, g, b, eps=0.0)).max_abs <= 1e-4)
+
+
+def test_layernorm_benchmark_config(ctx, oracle):
+    x = oracle.normal((4096, 1024), oracle.BASE_SEED, 0, 1)
+    g = oracle.uniform(1024, oracle.BASE_SEED + 1, 0.5, 1.5)
+    b = oracle.normal(1024, oracle.BASE_SEED + 2, 0, 0.1)  # N(0, 0.1) read as sigma 0.1
+    y = run(ctx, "layernorm", "rows=4096,cols=1024", [x, g, b], (4096, 1024))
+    cmp_ = oracle.compare(y, oracle.layernorm_ref(x, g, b))
+    assert cmp_.non_finite == 0 and cmp_.max_rel_floored <= REL
+
+
+# --------------------------------------------------------------------------- scan
+@pytest.mark.parametrize("n,atol", [(1024, 1e-4), (65536, 1e-3), (1 << 20, 5e-3), (1000, 1e-4),
+                                    (1, 1e-4), (4096, 1e-4), (4097, 1e-4)])
+def test_scan_reference_inputs(ctx, oracle, n, atol):
+    x = oracle.mt19937_unit(n, 0x29C0FFEE)
+    y = run(ctx, "scan", f"n={n}", [x], (n,))
+    ref = oracle.scan_ref(x)
+    assert oracle.compare(y, ref).max_abs <= atol  # the reference's per-size bound
+    assert oracle.bit_mismatches(y, ref) == 0      # exact sums: every association order agrees
+    if n >= 1024:
+        xc = oracle.mt19937_unit(1024, 0x51AC0D3E)
+        yc = run(ctx, "scan", "n=1024", [xc], (1024,))
+        assert oracle.compare(yc, oracle.scan_ref(xc, exclusive=True)).max_abs > 1e-4
+
+
+def test_scan_benchmark_config_and_repeated_launches(ctx, oracle):
+    n = 1000000
+    x = oracle.uniform(n, oracle.BASE_SEED, 0, 1)
+    ref = oracle.scan_ref(x)
+    for _ in range(4):  # the look-back state is reused across launches (epochs)
+        y = run(ctx, "scan", f"n={n}", [x], (n,))
+        cmp_ = oracle.compare(y, ref)
+        assert cmp_.max_rel_floored <= REL * math.sqrt(n)
+        assert oracle.bit_mismatches(y, ref) == 0
+    assert np.all(np.diff(y.astype(np.float64)) >= 0)  # non-negative input: non-decreasing
+
+
+def test_scan_large_and_signed(ctx, oracle):
+    n = (1 << 24) + 5
+    x = oracle.uniform(n, 99, -1, 1)
+    y = run(ctx, "scan", f"n={n}", [x], (n,))
+    ref = oracle.scan_ref(x)
+    assert oracle.compare(y, ref).max_abs <= 1e-3
+    assert oracle.bit_mismatches(y, ref) <= n // 1000  # fp64 sums of general data: last-bit ties only
+
+
+# --------------------------------------------------------------------------- gemm
+@pytest.mark.parametrize("size", [128, 512, 1024, 1000, 2048])
+def test_gemm_reference_pattern(ctx, oracle, size):
+    a, b = oracle.gemm_pattern(size, size, size)
+    c = run(ctx, "gemm", f"m={size},n={size},k={size}", [a, b], (size, size))
+    ref = oracle.gemm_ref(a, b)
+    assert oracle.compare(c, ref).rel_frobenius <= 1e-5  # the reference's bound
+    assert oracle.bit_mismatches(c, ref) == 0            # exact integers survive the 3xTF32 split
+
+
+def test_gemm_negative_control(ctx, oracle):
+    a, b = oracle.gemm_pattern(256, 256, 256)
+    c = run(ctx, "gemm", "m=256,n=256,k=256", [a, b], (256, 256))
+    assert oracle.compare(c, oracle.gemm_ref(a, b)).rel_frobenius <= 1e-5
+    assert oracle.compare(c, oracle.gemm_ref(a, b, b_transposed=True)).rel_frobenius > 1e-5
+
+
+@pytest.mark.parametrize("m,n,k", [(512, 512, 512), (100, 200, 72), (129, 257, 33), (1, 1, 1),
+                                   (300, 40, 1000), (1024, 768, 4096)])
+def test_gemm_uniform_inputs_keep_fp32_accuracy(ctx, oracle, m, n, k):
+    a = oracle.uniform((m, k), oracle.BASE_SEED, -1, 1)
+    b = oracle.uniform((k, n), oracle.BASE_SEED + 1, -1, 1)
+    c = run(ctx, "gemm", f"m={m},n={n},k={k}", [a, b], (m, n))
+    cmp_ = oracle.compare(c, oracle.gemm_ref(a, b))
+    assert cmp_.non_finite == 0
+    assert cmp_.rel_frobenius <= 1e-5
+    assert cmp_.max_rel_floored <= REL * math.sqrt(k)
+
+
+def test_gemm_8192_sampled_rows_and_scaling_property(ctx, oracle):
+    size = 8192
+    a = oracle.uniform((size, size), oracle.BASE_SEED, -1, 1)
+    b = oracle.uniform((size, size), oracle.BASE_SEED + 1, -1, 1)
+    da, db = dev(a), dev(b)
+    c = run(ctx, "gemm", f"m={size},n={size},k={size}", [da, db], (size, size))
+    rows = np.sort(np.random.default_rng(1).choice(size, 48, replace=False))
+    ref = oracle.gemm_ref_pick_rows(a, b, rows)
+    cmp_ = oracle.compare(c[rows], ref)
+    assert cmp_.rel_frobenius <= 1e-5
+    assert cmp_.max_rel_floored <= REL * math.sqrt(size)
+    # scaling A by a power of two scales every hi/lo part exactly: C doubles bit for bit
+    c2 = run(ctx, "gemm", f"m={size},n={size},k={size}", [da * 2, db], (size, size))
+    assert np.array_equal(c2, c * 2)
+
+
+# --------------------------------------------------------------------------- attention
+def attention_inputs(oracle, b, h, s):
+    return (oracle.lcg((b, h, s, 64), 0x313A171B), oracle.lcg((b, h, s, 64), 0x51AC0D3E),
+            oracle.lcg((b, h, s, 64), 0x29C0FFEE))
+
+
+@pytest.mark.parametrize("b,h,s", [(2, 8, 512), (2, 8, 1024), (1, 1, 64), (1, 3, 192)])
+def test_attention_reference_inputs(ctx, oracle, b, h, s):
+    q, k, v = attention_inputs(oracle, b, h, s)
+    o = run(ctx, "attention", f"batch={b},heads={h},seq={s},head_dim=64", [q, k, v], (b, h, s, 64))
+    cmp_ = oracle.compare(o, oracle.attention_ref(q, k, v), rtol=2e-3)
+    assert cmp_.non_finite == 0
+    assert cmp_.max_violation <= 2e-3  # |gpu-ref| <= 2e-3 + 2e-3 |ref| on every element
+    assert cmp_.max_rel_floored <= REL * math.sqrt(s)
+
+
+def test_attention_negative_control(ctx, oracle):
+    q, k, v = attention_inputs(oracle, 2, 8, 256)
+    o = run(ctx, "attention", "batch=2,heads=8,seq=256,head_dim=64", [q, k, v], (2, 8, 256, 64))
+    assert oracle.compare(o, oracle.attention_ref(q, k, v)).max_abs <= 2e-3
+    assert oracle.compare(o, oracle.attention_ref(q, k, v, scaled=False)).max_abs > 2e-3
+
+
+def test_attention_benchmark_parity_config(ctx, oracle):
+    shape = (1, 1, 1024, 64)
+    q, k, v = (oracle.normal(shape, oracle.BASE_SEED + i, 0, 1) for i in range(3))
+    o = run(ctx, "attention", "batch=1,heads=1,seq=1024,head_dim=64", [q, k, v], shape)
+    cmp_ = oracle.compare(o, oracle.attention_ref(q, k, v), rtol=2e-3)
+    assert cmp_.non_finite == 0 and cmp_.max_violation <= 2e-3
+    assert cmp_.max_rel_floored <= REL * math.sqrt(1024)
+    assert o.min() >= v.min() - 1e-4 and o.max() <= v.max() + 1e-4  # rows are convex combinations of V
+
+
+def test_attention_batched_config_sampled(ctx, oracle):
+    shape = (8, 16, 1024, 64)
+    q, k, v = (oracle.normal(shape, oracle.BASE_SEED + i, 0, 1) for i in range(3))
+    o = run(ctx, "attention", "batch=8,heads=16,seq=1024,head_dim=64", [q, k, v], shape)
+    for lo in (0, 63, 127):  # three of the 128 (batch, head) problems in fp64
+        ref = oracle.attention_ref(q, k, v, bh_begin=lo, bh_end=lo + 1).reshape(128, 1024, 64)[lo]
+        cmp_ = oracle.compare(o.reshape(128, 1024, 64)[lo], ref, rtol=2e-3)
+        assert cmp_.non_finite == 0 and cmp_.max_violation <= 2e-3
+        assert cmp_.max_rel_floored <= REL * math.sqrt(1024)
+
+
+# --------------------------------------------------------------------------- surface
+def test_launch_errors_are_reported(ctx):
+    x = torch.zeros(16, device="cuda")
+    with pytest.raises(kh.KernelhError) as e:
+        ctx.launch("vecadd", "n=16", [x, x])
+    assert e.value.code == kh.USAGE_ERROR and "takes 3 buffers, got 2" in e.value.message
+    with pytest.raises(kh.KernelhError) as e:
+        ctx.launch("nope", "n=16", [x])
+    assert "unknown kernel template 'nope'" in e.value.message
+    with pytest.raises(kh.KernelhError) as e:
+        ctx.launch("vecadd", "n=abc", [x, x, x])
+    assert "malformed --shape" in e.value.message
+
+
+def test_bench_row_reports_reference_metrics(ctx):
+    ms, rate, is_gflops = ctx.bench_row("vecadd", "n=16777216", 2, 5)
+    assert ms > 0 and not is_gflops
+    assert rate == pytest.approx(kh.rate(False, kh.metric("vecadd_bytes", 1 << 24), ms))
+    ms, rate, is_gflops = ctx.bench_row("gemm", "m=512,n=512,k=512", 2, 5)
+    assert is_gflops and rate == pytest.approx(kh.rate(True, 268435456.0, ms))

@@ -1,0 +1,222 @@
+"""Host logic of the runtime through the C ABI, against the fixtures generated
+from the reference's own host code (tests/golden/make_golden.py), plus the
+B200 additions. Runs without a GPU."""
+import ctypes as C
+import os
+import re
+import subprocess
+
+import pytest
+
+import kernelh_b200 as kh
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def test_library_exports_every_declared_symbol():
+    header = open(os.path.join(ROOT, "include", "kernelh_b200.h")).read()
+    header = re.sub(r"/\*.*?\*/", "", header, flags=re.S)
+    declared = set(re.findall(r"\b(kh_[a-z0-9_]+)\s*\(", header))
+    assert len(declared) >= 30
+    out = subprocess.run(["nm", "-D", "--defined-only", kh.LIB_PATH], capture_output=True, text=True,
+                         check=True).stdout
+    exported = set(re.findall(r" T (kh_[a-z0-9_]+)", out))
+    assert declared <= exported, sorted(declared - exported)
+    for name in declared:
+        assert hasattr(kh.lib, name)
+    assert b"sm_100a" in kh.lib.kh_version()
+
+
+def test_descriptor_packing_matches_reference(golden):
+    for case in golden["host"]["descriptor_slots"]:
+        assert kh.pack_memrefs(case["ptrs"], case["shapes"]) == case["slots"]
+    # rank-1 / rank-2 / rank-4 descriptors take 5 / 7 / 11 eight-byte slots
+    assert len(kh.pack_memrefs([8], [[16]])) == 5
+    assert len(kh.pack_memrefs([8], [[4, 4]])) == 7
+    assert len(kh.pack_memrefs([8], [[2, 2, 2, 2]])) == 11
+    slots = kh.pack_memrefs([0x1000], [[3, 5, 7]])
+    assert slots == [0x1000, 0x1000, 0, 3, 5, 7, 35, 7, 1]
+
+
+def test_device_limits_table(golden):
+    ref = golden["host"]["device_limits"]
+    for tok in ("gfx1101", "sm_80"):
+        got = kh.device_limits(tok)
+        assert [got[f] for f in kh.LIMIT_FIELDS[:10]] == ref[tok]["fields"]
+        assert got["name"] == ref[tok]["name"]
+        assert got["max_dynamic_smem_optin"] == 0  # the reference's targets have no opt-in carve-out
+    b200 = kh.device_limits("sm_100a")
+    assert b200["lds_bytes_per_workgroup"] == 49152
+    assert b200["max_dynamic_smem_optin"] == 232448
+    assert b200["smem_per_sm"] == 233472
+    assert (b200["wavefront_size"], b200["max_threads_per_workgroup"]) == (32, 1024)
+    assert (b200["waves_per_cu"], b200["reg_file_per_cu"], b200["max_blocks_per_sm"]) == (64, 65536, 32)
+    assert b200["tmem_columns_per_sm"] == 512
+    assert b200["cu_count"] == 0  # runtime query
+    assert "sm_100a" in b200["name"]
+    with pytest.raises(kh.KernelhError) as e:
+        kh.device_limits("sm_999")
+    # same text as the reference apart from the longer list of known targets
+    assert e.value.message == ref["unknown_message_sm_999"] + ", sm_100a"
+    with pytest.raises(kh.KernelhError):
+        kh.device_limits("")
+
+
+def test_cli_target_tokens():
+    assert kh.target_token("nvptx-sm_100a") == "sm_100a"
+    assert kh.target_token("nvptx-sm_80") == "sm_80"
+    assert kh.target_token("amdgcn-gfx1101") == "gfx1101"
+    with pytest.raises(kh.KernelhError) as e:
+        kh.target_token("nvptx-sm_90")
+    assert e.value.code == kh.USAGE_ERROR and "valid --target values" in e.value.message
+    assert "nvptx-sm_100a" in e.value.message
+
+
+def test_launch_verifier_matches_reference_messages(golden):
+    for c in golden["host"]["launch_verifier"]:
+        msg = kh.verify_launch(c["target"], c["threads"], c["grid"], c["shared"], 0,
+                               c["waves_per_cu_override"])
+        assert msg == c["message"], c
+        assert (msg != "") == (c["rc"] != 0)
+
+
+def test_launch_verifier_dynamic_shared_memory_rule():
+    assert kh.verify_launch("sm_100a", 192, (2048, 1, 1), 48, 197632) == ""
+    assert kh.verify_launch("sm_100a", 192, (1, 1, 1), 0, 232448) == ""
+    msg = kh.verify_launch("sm_100a", 192, (1, 1, 1), 1024, 232448)
+    assert "static + dynamic 233472 bytes exceeds the 232448-byte opt-in limit" in msg
+    # a target without opt-in keeps the static limit for the sum
+    msg = kh.verify_launch("sm_80", 256, (1, 1, 1), 0, 65536)
+    assert "no opt-in carve-out" in msg
+    # every rule still reports at once
+    msg = kh.verify_launch("sm_100a", 4100, (1, 1, 70000), 50000, 300000)
+    assert len(msg.splitlines()) == 6
+
+
+def test_occupancy_matches_reference(golden):
+    for c in golden["host"]["occupancy"]:
+        got = kh.occupancy(c["target"], c["vgpr"], c["lds"], c["threads"])
+        assert [got["vgpr_limited_waves"], got["lds_limited_blocks"], got["thread_limited_blocks"],
+                got["achieved_waves"]] == c["out"][:4]
+        assert ("none", "vgpr", "lds", "threads").index(got["limiter"]) == c["out"][4]
+        assert got["theoretical_pct"] == pytest.approx(c["pct"])
+
+
+def test_occupancy_b200_per_sm_view():
+    # gemm: 192 threads, 120 registers, 48 B static + 197632 B dynamic, 256 TMEM columns
+    o = kh.occupancy("sm_100a", 120, 48, 192, 197632, 256)
+    assert o["sm_resident_blocks"] == 1 and o["sm_limiter"] == "shared memory"
+    assert o["sm_occupancy_pct"] == pytest.approx(100.0 * 6 / 64, abs=0.01)
+    # a streaming kernel: 256 threads, 40 registers -> 6 blocks by registers, 8 by warps
+    o = kh.occupancy("sm_100a", 40, 0, 256)
+    assert o["sm_resident_blocks"] == 6 and o["sm_limiter"] == "registers"
+    # tensor memory as the limiter
+    o = kh.occupancy("sm_100a", 32, 0, 128, 1024, 512)
+    assert o["sm_resident_blocks"] == 1 and o["sm_limiter"] == "tensor memory"
+
+
+def test_metrics_and_rates_match_reference(golden):
+    for m in golden["host"]["metrics"]:
+        assert kh.metric(m["what"], *m["args"]) == m["value"]
+    for r in golden["host"]["rates"]:
+        assert kh.rate(bool(r["gflops"]), r["work"], r["ms"]) == r["value"]
+    assert kh.metric("vecadd_bytes", 1 << 24) == 201326592.0
+    assert kh.metric("nonsense") == -1.0
+
+
+def test_csv_matches_reference(golden):
+    assert kh.csv_header() == golden["host"]["csv"]["header"]
+    for c in golden["host"]["csv"]["lines"]:
+        assert kh.csv_line(*c["row"]) == c["line"]
+
+
+def test_shape_text_matches_reference(golden):
+    for c in golden["host"]["shape_text"]:
+        assert kh.shape_roundtrip(c["text"]) == c["roundtrip"], c
+
+
+def test_registry_lists_sorted_names_and_rejects_unknown():
+    names = kh.registered_kernels()
+    assert names == sorted(names)
+    assert set(names) == set(kh.KERNELS)
+    with pytest.raises(kh.KernelhError) as e:
+        kh.plan("nope", "n=4")
+    assert e.value.message.startswith("unknown kernel template 'nope'; registered kernels: ")
+    assert "attention, fused_gelu, gemm" in e.value.message
+
+
+@pytest.mark.parametrize("kernel,shape,missing", [
+    ("vecadd", "m=4", "'n'"), ("scan", "m=4", "'n'"), ("gemm", "m=4,n=4", "'k'"),
+    ("softmax", "rows=4", "'rows' and 'cols'"), ("layernorm", "cols=4", "'rows' and 'cols'"),
+    ("fused_gelu", "rows=4", "'n', or 'rows' AND 'cols'"),
+    ("attention", "batch=1,heads=1,seq=64", "'head_dim'"),
+])
+def test_shape_errors_name_the_key(kernel, shape, missing):
+    with pytest.raises(kh.KernelhError) as e:
+        kh.plan(kernel, shape)
+    assert e.value.code == kh.USAGE_ERROR
+    assert kernel + " template" in e.value.message and missing in e.value.message
+
+
+def test_shape_value_rules():
+    for kernel, shape in (("vecadd", "n=0"), ("gemm", "m=4,n=-1,k=4"), ("softmax", "rows=0,cols=4"),
+                          ("attention", "batch=1,heads=1,seq=0,head_dim=64")):
+        with pytest.raises(kh.KernelhError) as e:
+            kh.plan(kernel, shape)
+        assert "must be positive" in e.value.message
+    with pytest.raises(kh.KernelhError) as e:
+        kh.plan("attention", "batch=1,heads=1,seq=100,head_dim=64")
+    assert "divisible by the K/V tile extent 64 (got seq = 100)" in e.value.message
+    with pytest.raises(kh.KernelhError) as e:
+        kh.plan("attention", "batch=1,heads=1,seq=128,head_dim=32")
+    assert "pinned to head_dim = 64" in e.value.message
+
+
+def test_plans_for_the_benchmark_configurations():
+    p = kh.plan("vecadd", "n=16777216")
+    assert (p.n_buffers, p.n_launches, p.param_count) == (3, 1, 15)
+    assert p.block[0] == 256 and p.grid[0] % 148 == 0 or p.grid[0] <= 148 * 6
+    assert p.work == 201326592.0 and not p.work_is_flops
+    p = kh.plan("fused_gelu", "n=4194304,bias=1")
+    assert p.entry == b"fused_gelu_bias" and p.work == 50331648.0
+    assert kh.plan("fused_gelu", "rows=2048,cols=2048").entry == b"fused_gelu"
+    p = kh.plan("softmax", "rows=4096,cols=1024")
+    assert p.param_count == 14 and p.work == 33554432.0
+    assert p.grid[0] * (p.block[0] // 32) >= 4096  # one pass, a warp per row
+    assert p.grid[0] <= 148 * 4 and p.block[0] == 7 * 32  # 28 rows per SM as 4 blocks of 7 warps
+    p = kh.plan("layernorm", "rows=4096,cols=1024")
+    assert p.param_count == 24 and p.work == 33562624.0
+    p = kh.plan("softmax", "rows=16384,cols=4096")
+    assert p.block[0] == 256 and p.grid[0] == 148 * 8
+    p = kh.plan("scan", "n=1000000")
+    assert p.work == 8000000.0 and p.workspace_bytes == (2 + 3 * 245) * 8
+    p = kh.plan("gemm", "m=8192,n=8192,k=8192")
+    assert p.entry == b"gemm" and p.n_launches == 3 and p.grid[0] == 64 * 32 and p.block[0] == 192
+    assert p.dynamic_smem == 2 * 98304 + 1024 and p.tmem_columns == 256
+    assert p.workspace_bytes == 2 * 8192 * 8192 * 4 * 2
+    assert p.work == 1099511627776.0 and p.work_is_flops
+    assert kh.verify_launch("sm_100a", p.block[0], tuple(p.grid), 48, p.dynamic_smem) == ""
+    p = kh.plan("gemm", "m=1000,n=1000,k=1000")
+    assert p.grid[0] == 8 * 4 and p.workspace_bytes == 2000 * 1024 * 8
+    p = kh.plan("attention", "batch=8,heads=16,seq=1024,head_dim=64")
+    assert p.grid[0] == 128 * 8 and p.param_count == 51 and p.work == 34359738368.0
+    assert kh.verify_launch("sm_100a", p.block[0], tuple(p.grid), 80, p.dynamic_smem) == ""
+
+
+def test_embedded_code_objects_are_sm100_elf():
+    for k in kh.KERNELS:
+        image = kh.kernel_image(k)
+        assert image[:4] == b"\x7fELF" and len(image) > 1000
+        assert k.encode() in image  # the entry symbol equals the kernel name
+    assert b"tcgen05" not in kh.kernel_image("vecadd")
+
+
+def test_compute_calls_fail_loudly_without_a_device():
+    import torch
+
+    if torch.cuda.is_available():
+        pytest.skip("a GPU is present")
+    with pytest.raises(kh.KernelhError) as e:
+        kh.Context(0)
+    assert e.value.code == kh.DRIVER_UNAVAILABLE
+    assert "cuInit" in e.value.message or "dlopen" in e.value.message
