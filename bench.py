@@ -1,0 +1,415 @@
+#!/usr/bin/env python
+"""Benchmark of the hot path: fp32 GEMM 8192^3 (C = A.B, 3xTF32 on tcgen05) on
+1/2/4/8 B200, with the memory-bound kernels' GB/s reported beside it at N = 1.
+
+    python bench.py --gpus N --steps K --warmup W            # this repository's kernels
+    python bench.py --impl reference --gpus N --steps K ...  # the reference's fp64 CPU routine
+
+One "step" is one pass of the path over one batch of synthetic input: the
+operand split, the tensor-core GEMM and (N > 1) the all-gather of the C row
+shards. Rank 0 prints ONE JSON line. Under torchrun every rank owns one GPU;
+A and C are sharded by M-row blocks, B is replicated before timing (input
+placement), and the NCCL all-gather of C is inside the timed region.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+SIZE = 8192
+FLOPS = 2.0 * SIZE ** 3
+METRIC = "fp32 GEMM 8192^3 TFLOP/s"
+SEED = 0x4B310001
+
+
+def parse_args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="kernelh_b200", choices=["kernelh_b200", "reference"])
+    ap.add_argument("--size", type=int, default=SIZE, help=argparse.SUPPRESS)
+    ap.add_argument("--no-extras", action="store_true",
+                    help="skip the memory-bound rows, the e2e leg and the CPU baseline")
+    return ap.parse_args()
+
+
+def measured_peaks() -> dict:
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            p = json.load(f)
+        p["source"] = "measured"
+        return p
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0,
+            "source": "fallback"}
+
+
+# --------------------------------------------------------------------------- clocks
+class ClockSampler:
+    """Samples SM clock and throttle reasons with nvidia-smi during the timed region."""
+
+    QUERY = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+             "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+             "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index = index
+        self.proc = None
+        self.lines: list[str] = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
+                 "-i", str(self.index), "-lms", "100"], stdout=subprocess.PIPE,
+                stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._pump, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _pump(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        sm, smax, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in self.lines:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 7:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                smax.append(float(parts[1]))
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[3:7]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        sm.sort()
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(smax) if smax else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+# --------------------------------------------------------------------------- CPU arm
+def cpu_gemm_sample(size: int, steps: int, warmup: int):
+    """Times the reference's fp64 CPU routine (test/unit/e2e_gemm_test.cpp:92-108)
+    on the host cores for a bounded sample of the workload's C rows. Uses the
+    reference's own code when it was compiled here (oracle/_ref), else the oracle's
+    restatement of it. Returns (tflops, cores, kind, sample text, ms per step)."""
+    import numpy as np
+
+    from oracle import oracle_py as O
+
+    cores = os.cpu_count() or 1
+    try:
+        cores = len(os.sched_getaffinity(0))
+    except AttributeError:
+        pass
+    a_full_rows = None
+    b = O.uniform((size, size), SEED + 1, -1, 1)
+    if O.ref_available():
+        kind = "reference"
+        threads = min(cores, 32)
+        rows_per_thread = 4
+        rows = threads * rows_per_thread
+        a_full_rows = O.uniform((rows, size), SEED, -1, 1)
+        R = O.ref()
+        handle = R.khref_gemm_prepare(b.reshape(-1), size, size)
+        out = np.empty((rows, size), np.float32)
+
+        def one_step():
+            ts = []
+            for t in range(threads):
+                lo = t * rows_per_thread
+                th = threading.Thread(target=R.khref_gemm_rows, args=(
+                    handle, a_full_rows[lo:lo + rows_per_thread].reshape(-1),
+                    out[lo:lo + rows_per_thread].reshape(-1), rows_per_thread))
+                th.start()
+                ts.append(th)
+            for th in ts:
+                th.join()
+    else:
+        kind = "port"
+        threads = O.num_threads()
+        rows = max(threads * 4, 8)
+        a_full_rows = O.uniform((rows, size), SEED, -1, 1)
+
+        def one_step():
+            O.gemm_ref(a_full_rows, b)
+
+    for _ in range(min(warmup, 1)):
+        one_step()
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        one_step()
+    dt = (time.perf_counter() - t0) / steps
+    tflops = 2.0 * rows * size * size / dt / 1e12
+    sample = (f"{rows} of {size} rows of C per step (full K and N), fp64 accumulation, "
+              f"{threads} host threads")
+    return tflops, threads, kind, sample, dt * 1e3
+
+
+def reference_arm(args) -> None:
+    """`--impl reference`: the reference's CPU implementation of the path, rank 0 only."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    tflops, threads, kind, sample, ms = cpu_gemm_sample(args.size, max(args.steps, 1), args.warmup)
+    line = {
+        "impl": "reference", "metric": METRIC, "value": tflops, "unit": "TFLOP/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms,
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f64",
+        "data": "synthetic",
+        "config": {"workload": f"gemm m=n=k={args.size} fp32 row-major, A,B ~ U[-1,1) seeded",
+                   "sample": sample},
+        "cpu_baseline": {"value": tflops, "unit": "TFLOP/s", "cores": threads, "kind": kind,
+                         "sample": sample},
+        "e2e": {"value": tflops, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def time_rotating(torch, launch, sets, iters):
+    """Average ms per launch over `iters` launches that rotate through `sets`
+    argument sets whose total size exceeds L2, after 3 warm-up rounds."""
+    for _ in range(3):
+        for s in sets:
+            launch(s)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(iters):
+        launch(sets[i % len(sets)])
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / iters
+
+
+def memory_bound_rows(torch, ctx, stream, hbm_peak: float) -> dict:
+    """GB/s of the five HBM-bound kernels at the benchmark configurations' sizes
+    (rotating through buffer sets larger than L2) and at a large size."""
+    out = {}
+
+    def row(name, kernel, shape, make, bytes_per_launch, nsets, iters=200):
+        sets = [make() for _ in range(nsets)]
+        ms = time_rotating(torch, lambda s: ctx.launch(kernel, shape, s, stream), sets, iters)
+        gbs = bytes_per_launch / ms / 1e6
+        out[name] = {"shape": shape, "ms": ms, "gbs": gbs, "frac_of_measured_hbm": gbs / hbm_peak,
+                     "buffer_sets": nsets}
+
+    f = lambda *shape: torch.randn(*shape, device="cuda")
+    n = 1 << 24
+    row("vecadd", "vecadd", f"n={n}", lambda: [f(n), f(n), f(n)], 3 * n * 4, 3)
+    n = 1 << 22
+    row("fused_gelu_bias", "fused_gelu", f"n={n},bias=1", lambda: [f(n), f(n), f(n)], 3 * n * 4, 8)
+    row("fused_gelu", "fused_gelu", f"n={n}", lambda: [f(n), None, f(n)], 2 * n * 4, 8)
+    r, c = 4096, 1024
+    row("softmax", "softmax", f"rows={r},cols={c}", lambda: [f(r, c), f(r, c)], 2 * r * c * 4, 8)
+    g, b = f(c), f(c)
+    row("layernorm", "layernorm", f"rows={r},cols={c}", lambda: [f(r, c), g, b, f(r, c)],
+        2 * r * c * 4 + 2 * c * 4, 8)
+    n = 1000000
+    row("scan", "scan", f"n={n}", lambda: [torch.rand(n, device="cuda"), f(n)], 2 * n * 4, 24)
+    # large sizes: one buffer set is already far larger than L2
+    n = 1 << 28
+    row("vecadd_large", "vecadd", f"n={n}", lambda: [f(n), f(n), f(n)], 3 * n * 4, 1, 20)
+    row("fused_gelu_bias_large", "fused_gelu", f"n={n},bias=1", lambda: [f(n), f(n), f(n)], 3 * n * 4, 1, 20)
+    r = 262144
+    row("softmax_large", "softmax", f"rows={r},cols={c}", lambda: [f(r, c), f(r, c)], 2 * r * c * 4, 1, 20)
+    row("layernorm_large", "layernorm", f"rows={r},cols={c}", lambda: [f(r, c), g, b, f(r, c)],
+        2 * r * c * 4, 1, 20)
+    n = 1 << 26
+    row("scan_large", "scan", f"n={n}", lambda: [torch.rand(n, device="cuda"), f(n)], 2 * n * 4, 1, 20)
+    return out
+
+
+def gpu_arm(args) -> None:
+    import torch
+    import torch.distributed as dist
+
+    import kernelh_b200 as kh
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        if rank == 0:
+            sys.stderr.write(f"bench.py: --gpus {args.gpus} needs {args.gpus} ranks (torchrun), "
+                             f"found WORLD_SIZE={world}\n")
+        sys.exit(2)
+    if not torch.cuda.is_available():
+        sys.stderr.write("bench.py: no CUDA device; the kernels have no CPU path\n")
+        sys.exit(77)
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    ctx = kh.Context(local_rank)
+    stream = torch.cuda.current_stream().cuda_stream
+    peaks = measured_peaks()
+    size = args.size
+    flops = 2.0 * size ** 3
+    if size % world != 0:
+        raise SystemExit(f"size {size} is not divisible by {world} ranks")
+    rows = size // world
+
+    # Synthetic inputs, identical on every rank: A, B ~ U[-1, 1), seeded.
+    gen = torch.Generator(device="cuda")
+    gen.manual_seed(SEED)
+    a = torch.rand(size, size, device="cuda", generator=gen) * 2 - 1
+    b = torch.rand(size, size, device="cuda", generator=gen) * 2 - 1
+    c = torch.zeros(size, size, device="cuda")
+    a_shard = a[rank * rows:(rank + 1) * rows]
+    c_shard = c[rank * rows:(rank + 1) * rows]
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+
+    def step():
+        ctx.gemm(a_shard, b, c_shard, rows, size, size, stream)
+        if world > 1:
+            dist.all_gather_into_tensor(c, c_shard)
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    ctx.synchronize(stream)
+
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    launches_before = ctx.launch_count()
+    barrier()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        step()
+    e1.record()
+    torch.cuda.synchronize()
+    barrier()
+    ms_total = e0.elapsed_time(e1)
+    launches = ctx.launch_count() - launches_before
+    clocks = sampler.stop() if rank == 0 else None
+    ctx.synchronize(stream)
+    t = torch.tensor([ms_total], device="cuda", dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms_step = t.item() / args.steps
+    value = flops / (ms_step * 1e-3) / 1e12
+
+    # ---- the dominant kernel alone, per-launch, on this rank's stream -------------------
+    ctx.profile(True)
+    for _ in range(args.steps):
+        ctx.gemm(a_shard, b, c_shard, rows, size, size, stream)
+    prof = ctx.profile_report()
+    ctx.profile(False)
+    gemm_launches, gemm_ms = prof["gemm"]
+    kernel_ms = gemm_ms / gemm_launches
+    achieved = (flops / world) / (kernel_ms * 1e-3) / 1e12
+    # 3xTF32 ceiling: the measured bf16 tensor rate, halved for TF32 (the spec
+    # ratio), divided by the three products per k-step. Sustained figure: the
+    # kernel is timed inside a back-to-back loop.
+    peak = peaks["bf16_tflops_sustained"] / 2.0 / 3.0
+    traffic = None
+    tpath = os.path.join(ROOT, "profiles", "gemm_traffic.json")
+    if os.path.exists(tpath):
+        with open(tpath) as f:
+            tj = json.load(f)
+        traffic = tj.get("dram_bytes_per_launch_8192")
+        if traffic is not None and world > 1:
+            traffic = traffic / world
+    roofline = {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
+                "frac": achieved / peak, "traffic": traffic, "kernel": "gemm (tcgen05 3xTF32)",
+                "kernel_ms": kernel_ms, "split_ms": (prof["gemm_split_a"][1] + prof["gemm_split_bt"][1]) / gemm_launches,
+                "peak_note": f"bf16_tflops_sustained of {peaks['source']} / 2 (TF32) / 3 (three products)"}
+
+    # ---- sampled correctness of what was timed (checker, not measured) -------------------
+    pick = torch.tensor([0, size // 3, size - 1], device="cuda")
+    ref = a[pick].double() @ b.double()
+    err = ((c[pick].double() - ref).abs().max() / ref.pow(2).mean().sqrt()).item()
+
+    line = {
+        "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
+        "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "f32 (3xTF32 tensor-core products, fp32 accumulate)",
+        "data": "synthetic",
+        "config": {"workload": f"gemm m=n=k={size} fp32 row-major, A,B ~ U[-1,1) seeded",
+                   "sharding": f"A and C by {world} M-row blocks, B replicated before timing; "
+                               "NCCL all-gather of C inside the timed step" if world > 1 else "single GPU",
+                   "l2": "inputs (2 x 256 MiB) and the 1 GiB operand-split scratch are larger than the 126 MB L2",
+                   "step": "gemm_split_a + gemm_split_bt + gemm" + (" + all_gather" if world > 1 else "")},
+        "roofline": roofline, "gpu_launches": int(launches),
+        "sampled_max_err_over_rms": err,
+    }
+    if clocks is not None:
+        line["clocks"] = clocks
+
+    # ---- end to end through the host-buffer entry point -------------------------------------
+    if not args.no_extras:
+        a_h = a_shard.cpu().pin_memory()
+        b_h = b.cpu().pin_memory()
+        c_h = torch.empty(rows, size).pin_memory()
+        shape = f"m={rows},n={size},k={size}"
+        e2e_steps = max(3, min(args.steps, 5))
+        ctx.run_host("gemm", shape, [a_h, b_h, c_h])
+        barrier()
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        for _ in range(e2e_steps):
+            ctx.run_host("gemm", shape, [a_h, b_h, c_h])
+        torch.cuda.synchronize()
+        dt = torch.tensor([(time.perf_counter() - t0) / e2e_steps], device="cuda", dtype=torch.float64)
+        if world > 1:
+            dist.all_reduce(dt, op=dist.ReduceOp.MAX)
+        line["e2e"] = {"value": flops / dt.item() / 1e12, "unit": "TFLOP/s",
+                       "h2d_bytes_per_step": int(a_h.numel() * 4 + b_h.numel() * 4),
+                       "d2h_bytes_per_step": int(c_h.numel() * 4), "steps": e2e_steps,
+                       "ms_per_step": dt.item() * 1e3,
+                       "note": "kh_run_host on pinned host buffers: H2D of the A shard and B, split, gemm, "
+                               "D2H of the C shard, per rank"}
+        e2e_ok = torch.equal(c_h, c_shard.cpu())
+        line["e2e"]["matches_device_path"] = bool(e2e_ok)
+        del a_h, b_h, c_h
+
+    if rank == 0 and world == 1 and not args.no_extras:
+        del a, b, c
+        torch.cuda.empty_cache()
+        line["memory_bound"] = memory_bound_rows(torch, ctx, stream, peaks["hbm_gbs"])
+        line["memory_bound_peak"] = {"hbm_gbs": peaks["hbm_gbs"], "source": peaks["source"]}
+        tflops, threads, kind, sample, _ = cpu_gemm_sample(size, 2, 1)
+        line["cpu_baseline"] = {"value": tflops, "unit": "TFLOP/s", "cores": threads, "kind": kind,
+                                "sample": sample}
+    ctx.close()
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+
+
+def main() -> None:
+    args = parse_args()
+    if args.impl == "reference":
+        reference_arm(args)
+    else:
+        gpu_arm(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -90,6 +90,15 @@ int kh_run_host(kh_context *ctx, const char *kernel, const char *shape, void *co
 /* Waits for `stream` and reports a device-side wait that ran out (1001). */
 int kh_synchronize(kh_context *ctx, void *stream);
 
+/* Per-launch device timing (the reference times launches with GPU events,
+ * include/kernelh/runtime/event_timer.hpp): while enabled, every kernel launch
+ * of this context is bracketed by events on its stream. kh_profile_report
+ * waits for them and writes "entry:launches:total_ms;..." into buf.
+ * kh_launch_count returns how many kernels the context has launched so far. */
+int kh_profile_enable(kh_context *ctx, int on);
+int kh_profile_report(kh_context *ctx, char *buf, int cap);
+int kh_launch_count(kh_context *ctx, uint64_t *count);
+
 /* Typed forms of kh_launch, one per template (lib/dsl/kernels/<name>.cpp). */
 int kh_vecadd(kh_context *ctx, const float *a, const float *b, float *c, int64_t n, void *stream);
 int kh_fused_gelu(kh_context *ctx, const float *x, float *out, int64_t n, void *stream);

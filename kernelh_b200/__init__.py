@@ -2,7 +2,7 @@
 NVIDIA B200 (sm_100a), behind kernel.h's kernel-name + shape operator surface.
 
 This module is a thin ctypes binding of the C ABI in ``include/kernelh_b200.h``
-(``libkernelh_b200.so``, built in-tree by ``kernelh_b200.build``). It mirrors
+(``libkernelh_b200.so``, built in-tree by ``kernelh_b200/csrc/build.py``). It mirrors
 the reference's host interface: a device context, ``launch(kernel, shape,
 buffers)`` with the CLI's ``k=v,k=v`` shape text, the launch verifier, the
 device-limits table, the occupancy model, bench metrics and the results CSV
@@ -51,7 +51,7 @@ class PlanInfo(C.Structure):
 def _load() -> C.CDLL:
     if not os.path.exists(LIB_PATH):
         raise ImportError(
-            f"{LIB_PATH} is missing: build it with `python -m kernelh_b200.build` "
+            f"{LIB_PATH} is missing: build it with `python kernelh_b200/csrc/build.py` "
             "(needs nvcc and g++); there is no fallback implementation")
     L = C.CDLL(LIB_PATH)
     vp, i64, f32p = C.c_void_p, C.c_int64, C.c_void_p
@@ -65,6 +65,9 @@ def _load() -> C.CDLL:
     L.kh_launch.argtypes = [vp, C.c_char_p, C.c_char_p, C.POINTER(vp), C.c_int, vp]
     L.kh_run_host.argtypes = [vp, C.c_char_p, C.c_char_p, C.POINTER(vp), C.c_int]
     L.kh_synchronize.argtypes = [vp, vp]
+    L.kh_profile_enable.argtypes = [vp, C.c_int]
+    L.kh_profile_report.argtypes = [vp, C.c_char_p, C.c_int]
+    L.kh_launch_count.argtypes = [vp, C.POINTER(C.c_uint64)]
     L.kh_vecadd.argtypes = [vp, f32p, f32p, f32p, i64, vp]
     L.kh_fused_gelu.argtypes = [vp, f32p, f32p, i64, vp]
     L.kh_fused_gelu_bias.argtypes = [vp, f32p, f32p, f32p, i64, vp]
@@ -164,6 +167,24 @@ class Context:
 
     def synchronize(self, stream: int | None = None) -> None:
         _check(lib.kh_synchronize(self._h, stream))
+
+    def profile(self, on: bool) -> None:
+        _check(lib.kh_profile_enable(self._h, int(on)))
+
+    def profile_report(self) -> dict:
+        """{entry: (launches, total_ms)} of the launches made while profiling."""
+        buf = C.create_string_buffer(4096)
+        _check(lib.kh_profile_report(self._h, buf, 4096))
+        out = {}
+        for item in filter(None, buf.value.decode().split(";")):
+            name, count, ms = item.split(":")
+            out[name] = (int(count), float(ms))
+        return out
+
+    def launch_count(self) -> int:
+        n = C.c_uint64()
+        _check(lib.kh_launch_count(self._h, C.byref(n)))
+        return n.value
 
     def bench_row(self, kernel: str, shape: str, warmup: int = 5, iters: int = 20):
         ms, rate, is_gflops = C.c_double(), C.c_double(), C.c_int()

@@ -144,6 +144,24 @@ int kh_synchronize(kh_context *ctx, void *stream) {
   return r ? 0 : set_error(r.error());
 }
 
+int kh_profile_enable(kh_context *ctx, int on) {
+  if (int rc = need_ctx(ctx)) return rc;
+  ctx->exec->profile_enable(on != 0);
+  return 0;
+}
+int kh_profile_report(kh_context *ctx, char *buf, int cap) {
+  if (int rc = need_ctx(ctx)) return rc;
+  auto r = ctx->exec->profile_report();
+  if (!r) return set_error(r.error());
+  copy_out(*r, buf, cap);
+  return 0;
+}
+int kh_launch_count(kh_context *ctx, uint64_t *count) {
+  if (int rc = need_ctx(ctx)) return rc;
+  if (count) *count = ctx->exec->launches_issued();
+  return 0;
+}
+
 int kh_vecadd(kh_context *ctx, const float *a, const float *b, float *c, int64_t n, void *stream) {
   return launch_named(ctx, "vecadd", {{"n", n}},
                       {const_cast<float *>(a), const_cast<float *>(b), c}, stream);

@@ -96,8 +96,44 @@ Result<void> Executor::launch(KernelFunction fn, const LaunchStep &step, LaunchA
   LaunchVerifier verifier;
   if (auto ok = verifier.verify(cfg, limits_, nullptr); !ok)
     return fail(1, "launch of '" + step.entry + "' refused: " + ok.error());
-  return backend_->launch_kernel(fn.handle, step.grid, step.block, step.dynamic_smem, s, args.params(),
-                                 step.cluster);
+  ++launches_issued_;
+  if (!profiling_)
+    return backend_->launch_kernel(fn.handle, step.grid, step.block, step.dynamic_smem, s,
+                                   args.params(), step.cluster);
+  auto e0 = backend_->event_create();
+  if (!e0) return std::unexpected(e0.error());
+  auto e1 = backend_->event_create();
+  if (!e1) return std::unexpected(e1.error());
+  if (auto r = backend_->event_record(*e0, s); !r) return r;
+  auto launched = backend_->launch_kernel(fn.handle, step.grid, step.block, step.dynamic_smem, s,
+                                          args.params(), step.cluster);
+  if (auto r = backend_->event_record(*e1, s); !r) return r;
+  profiled_.push_back({step.entry, *e0, *e1});
+  return launched;
+}
+
+Result<std::string> Executor::profile_report() {
+  std::map<std::string, std::pair<int, double>> acc;
+  Error first_error;
+  for (const ProfiledLaunch &p : profiled_) {
+    if (auto r = backend_->event_synchronize(p.end); !r && first_error.code == 0) first_error = r.error();
+    if (auto ms = backend_->event_elapsed_time(p.start, p.end)) {
+      acc[p.entry].first += 1;
+      acc[p.entry].second += *ms;
+    } else if (first_error.code == 0) {
+      first_error = ms.error();
+    }
+    (void)backend_->event_destroy(p.start);
+    (void)backend_->event_destroy(p.end);
+  }
+  profiled_.clear();
+  if (first_error.code != 0) return std::unexpected(first_error);
+  std::string out;
+  for (const auto &kv : acc) {
+    if (!out.empty()) out += ';';
+    out += kv.first + ":" + std::to_string(kv.second.first) + ":" + std::to_string(kv.second.second);
+  }
+  return out;
 }
 
 Result<Executor::ScanTicket> Executor::scan_ticket(int64_t tiles, unsigned grid) {

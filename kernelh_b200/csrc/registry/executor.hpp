@@ -42,6 +42,13 @@ public:
   Result<void> launch(KernelFunction fn, const LaunchStep &step, LaunchArgs &args, StreamHandle s);
   uint32_t *status_word() const { return static_cast<uint32_t *>(status_.data()); }
 
+  // Per-launch timing: while enabled, every launch is bracketed by two events
+  // on its stream. profile_report() waits for them and returns
+  // "entry:launches:total_ms" items joined by ';', then forgets them.
+  void profile_enable(bool on) { profiling_ = on; }
+  Result<std::string> profile_report();
+  uint64_t launches_issued() const { return launches_issued_; }
+
   struct ScanTicket {
     void *state;
     uint32_t epoch;
@@ -68,6 +75,13 @@ private:
   int64_t scan_capacity_tiles_ = 0;
   uint32_t scan_epoch_ = 0;
   uint64_t scan_ticket_base_ = 0;
+  struct ProfiledLaunch {
+    std::string entry;
+    EventHandle start, end;
+  };
+  bool profiling_ = false;
+  std::vector<ProfiledLaunch> profiled_;
+  uint64_t launches_issued_ = 0;
   std::vector<Buffer> host_pool_;
   StreamHandle host_stream_ = nullptr;
 };

@@ -14,6 +14,7 @@ extern "C" {
 typedef struct {
   double max_abs;
   double max_rel_floored;
+  double max_rel;
   double rel_frobenius;
   double max_violation;
   double ref_rms;

@@ -32,7 +32,7 @@ def build(force: bool = False) -> None:
 
 
 class _CompareResult(C.Structure):
-    _fields_ = [("max_abs", C.c_double), ("max_rel_floored", C.c_double),
+    _fields_ = [("max_abs", C.c_double), ("max_rel_floored", C.c_double), ("max_rel", C.c_double),
                 ("rel_frobenius", C.c_double), ("max_violation", C.c_double),
                 ("ref_rms", C.c_double), ("non_finite", C.c_int64)]
 
@@ -41,6 +41,7 @@ class _CompareResult(C.Structure):
 class Compare:
     max_abs: float
     max_rel_floored: float
+    max_rel: float
     rel_frobenius: float
     max_violation: float
     ref_rms: float
@@ -219,7 +220,7 @@ def compare(got: np.ndarray, ref: np.ndarray, rtol: float = 0.0) -> Compare:
     else:
         lib().kho_compare_f32_f32(got, np.ascontiguousarray(ref, np.float32).reshape(-1),
                                   got.size, rtol, C.byref(r))
-    return Compare(r.max_abs, r.max_rel_floored, r.rel_frobenius, r.max_violation, r.ref_rms,
+    return Compare(r.max_abs, r.max_rel_floored, r.max_rel, r.rel_frobenius, r.max_violation, r.ref_rms,
                    int(r.non_finite))
 
 
@@ -261,6 +262,10 @@ def ref():
         R.khref_gemm_ref.argtypes = [_f32p, _f32p, _f32p, C.c_long, C.c_long, C.c_long]
         R.khref_gemm_rel_frobenius.argtypes = [_f32p, _f32p, C.c_long]
         R.khref_gemm_rel_frobenius.restype = C.c_double
+        R.khref_gemm_prepare.argtypes = [_f32p, C.c_long, C.c_long]
+        R.khref_gemm_prepare.restype = C.c_void_p
+        R.khref_gemm_rows.argtypes = [C.c_void_p, _f32p, _f32p, C.c_long]
+        R.khref_gemm_release.argtypes = [C.c_void_p]
         R.khref_vecadd_fill.argtypes = [_f32p, _f32p, C.c_long]
         R.khref_scan_fill.argtypes = [_f32p, C.c_long, C.c_uint]
         R.khref_pack_memrefs.argtypes = [C.POINTER(C.c_ulonglong), C.POINTER(C.c_longlong),

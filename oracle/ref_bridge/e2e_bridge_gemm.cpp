@@ -18,3 +18,29 @@ extern "C" double khref_gemm_rel_frobenius(const float *c, const float *ref, lon
   std::vector<float> vc(c, c + count), vr(ref, ref + count);
   return relative_frobenius(vc, vr, static_cast<size_t>(count));
 }
+
+// Row-sliced use of the reference's fill_reference for timing it on several
+// host threads: B is held once, each call forms C rows for the A rows given.
+namespace {
+struct GemmPrepared {
+  std::vector<float> b;
+  long n = 0, k = 0;
+};
+} // namespace
+
+extern "C" void *khref_gemm_prepare(const float *b, long n, long k) {
+  auto *h = new GemmPrepared;
+  h->b.assign(b, b + k * n);
+  h->n = n;
+  h->k = k;
+  return h;
+}
+
+extern "C" void khref_gemm_rows(void *handle, const float *a_rows, float *out, long rows) {
+  auto *h = static_cast<GemmPrepared *>(handle);
+  std::vector<float> va(a_rows, a_rows + rows * h->k), vr(static_cast<size_t>(rows * h->n));
+  fill_reference(va, h->b, vr, rows, h->n, h->k);
+  std::copy(vr.begin(), vr.end(), out);
+}
+
+extern "C" void khref_gemm_release(void *handle) { delete static_cast<GemmPrepared *>(handle); }

@@ -139,6 +139,7 @@ def test_compare_metrics(oracle):
     assert c.rel_frobenius == pytest.approx(0.5 / np.sqrt(21.0))
     assert c.max_violation == pytest.approx(0.5 - 0.4)
     assert c.max_rel_floored == pytest.approx(0.125)
+    assert c.max_rel == pytest.approx(0.125)  # |ref| = 4 > rms
     assert c.non_finite == 0
     bad = got.copy()
     bad[1] = np.nan
