@@ -12,6 +12,11 @@
 // nearest, low 13 mantissa bits cleared) and lo = x - hi (exact in fp32), and
 // every k-step issues three tensor-core products into one fp32 accumulator in
 // tensor memory: lo.hi, hi.lo, hi.hi (lo.lo, ~2^-22 relative, is dropped).
+// The tensor core's fp32 accumulation truncates, which biases long sums (the
+// error grew linearly with k when a whole k = 8192 product stayed in tensor
+// memory), so only K = 256 is accumulated there at a time: two accumulators
+// alternate, and each finished chunk is added into fp32 registers with
+// round-to-nearest by the epilogue warps while the next chunk is running.
 //
 // Two launches:
 //  gemm_split_a / gemm_split_bt  write A_hi, A_lo (m x kp) and B^T_hi, B^T_lo
@@ -21,8 +26,8 @@
 //      {A_hi, A_lo, B_hi, B_lo} k-blocks (32 fp32 deep, 96 KiB per stage) with
 //      TMA (128-byte swizzle, out-of-range rows read as zero, which is what
 //      makes ragged m and n work); warp 1 issues tcgen05.mma (M128 N256 K8,
-//      kind::tf32) and releases stages with tcgen05.commit; warps 2-5 read the
-//      256-column fp32 accumulator from tensor memory and store C.
+//      kind::tf32) and releases stages with tcgen05.commit; warps 2-9 drain the
+//      256-column fp32 accumulators from tensor memory chunk by chunk and store C.
 //
 // Tensor-bound: 2 m n k useful flops; three MMAs per k-step put the ceiling
 // at one third of the TF32 tensor rate.
@@ -37,8 +42,10 @@ constexpr int kStages = 2;
 constexpr int kATileBytes = kBM * kBK * 4;                         // 16 KiB
 constexpr int kBTileBytes = kBN * kBK * 4;                         // 32 KiB
 constexpr int kStageBytes = 2 * kATileBytes + 2 * kBTileBytes;     // 96 KiB
-constexpr int kTmemCols = 256;
-constexpr int kThreads = 192;
+constexpr int kTmemCols = 512;      // two 256-column accumulators, used alternately
+constexpr int kChunkBlocks = 8;     // k-blocks accumulated in tensor memory before a drain (K = 256)
+constexpr int kEpilogueWarps = 8;
+constexpr int kThreads = 64 + 32 * kEpilogueWarps; // TMA warp + MMA warp + epilogue warps
 constexpr int kGroupM = 16; // m-tiles per rasterisation group (L2 reuse of B)
 
 __device__ __forceinline__ float tf32_hi(float x) {
@@ -117,7 +124,8 @@ gemm(KH_MEMREF2(const float, a), KH_MEMREF2(const float, b), KH_MEMREF2(float, c
   (void)a_alloc; (void)a_ptr; (void)a_off; (void)a_size1; (void)a_stride0; (void)a_stride1;
   (void)b_alloc; (void)b_ptr; (void)b_off; (void)b_size0; (void)b_stride0; (void)b_stride1;
   extern __shared__ uint8_t smem_raw[];
-  __shared__ __align__(8) uint64_t bars[2 * kStages + 1];
+  // full[kStages], empty[kStages], acc_full[2], acc_empty[2]
+  __shared__ __align__(8) uint64_t bars[2 * kStages + 4];
   __shared__ uint32_t s_tmem_base;
   __shared__ int s_abort;
 
@@ -129,7 +137,8 @@ gemm(KH_MEMREF2(const float, a), KH_MEMREF2(const float, b), KH_MEMREF2(float, c
   const uint32_t ring = (khd::smem_u32(smem_raw) + 1023u) & ~1023u;
   const uint32_t full0 = khd::smem_u32(&bars[0]);
   const uint32_t empty0 = khd::smem_u32(&bars[kStages]);
-  const uint32_t accum_bar = khd::smem_u32(&bars[2 * kStages]);
+  const uint32_t acc_full0 = khd::smem_u32(&bars[2 * kStages]);
+  const uint32_t acc_empty0 = khd::smem_u32(&bars[2 * kStages + 2]);
 
   // ---- tile coordinates: groups of kGroupM m-tiles sweep n together ---------
   const int64_t tiles_m = (m + kBM - 1) / kBM, tiles_n = (n + kBN - 1) / kBN;
@@ -142,6 +151,7 @@ gemm(KH_MEMREF2(const float, a), KH_MEMREF2(const float, b), KH_MEMREF2(float, c
   const int64_t tile_m = first_m + in_group % rows_in_group;
   const int64_t tile_n = in_group / rows_in_group;
   const int m0 = static_cast<int>(tile_m * kBM), n0 = static_cast<int>(tile_n * kBN);
+  const int64_t num_chunks = (k_blocks + kChunkBlocks - 1) / kChunkBlocks;
 
   if (threadIdx.x == 0) {
     s_abort = 0;
@@ -149,7 +159,10 @@ gemm(KH_MEMREF2(const float, a), KH_MEMREF2(const float, b), KH_MEMREF2(float, c
       khd::mbar_init(full0 + 8 * s, 1);
       khd::mbar_init(empty0 + 8 * s, 1);
     }
-    khd::mbar_init(accum_bar, 1);
+    for (int i = 0; i < 2; ++i) {
+      khd::mbar_init(acc_full0 + 8 * i, 1);
+      khd::mbar_init(acc_empty0 + 8 * i, kEpilogueWarps); // one arrival per epilogue warp
+    }
     khd::mbar_fence_init();
     khd::tma_prefetch_descriptor(&tm_a_hi);
     khd::tma_prefetch_descriptor(&tm_a_lo);
@@ -190,12 +203,23 @@ gemm(KH_MEMREF2(const float, a), KH_MEMREF2(const float, b), KH_MEMREF2(float, c
       constexpr uint32_t idesc = khd::umma_idesc_tf32(kBM, kBN);
       bool ok = true;
       for (int64_t kb = 0; kb < k_blocks && ok; ++kb) {
+        const int64_t chunk = kb / kChunkBlocks;
+        const int in_chunk = static_cast<int>(kb - chunk * kChunkBlocks);
+        const int buf = static_cast<int>(chunk & 1);
+        if (in_chunk == 0) {
+          // the accumulator buffer must have been drained (two chunks ago)
+          ok = khd::mbar_wait(acc_empty0 + 8 * buf, static_cast<uint32_t>((chunk >> 1) & 1) ^ 1u,
+                              &s_abort, status, khd::kStatusEpilogueWaitTimeout,
+                              static_cast<uint32_t>(chunk));
+          if (!ok) break;
+        }
         const int s = static_cast<int>(kb % kStages);
         const uint32_t phase = static_cast<uint32_t>((kb / kStages) & 1);
         ok = khd::mbar_wait(full0 + 8 * s, phase, &s_abort, status, khd::kStatusTmaWaitTimeout,
                             static_cast<uint32_t>(kb));
         if (!ok) break;
         khd::tc_fence_after_sync();
+        const uint32_t d = tmem_base + static_cast<uint32_t>(buf * kBN);
         const uint32_t stage = ring + s * kStageBytes;
         const uint64_t a_hi = khd::umma_desc_k128(stage);
         const uint64_t a_lo = khd::umma_desc_k128(stage + kATileBytes);
@@ -204,53 +228,64 @@ gemm(KH_MEMREF2(const float, a), KH_MEMREF2(const float, b), KH_MEMREF2(float, c
 #pragma unroll
         for (int kk = 0; kk < kBK / 8; ++kk) {
           const uint64_t adv = static_cast<uint64_t>(kk * 2); // 32 bytes >> 4
-          khd::umma_tf32_ss(tmem_base, a_lo + adv, b_hi + adv, idesc, (kb | kk) != 0 ? 1u : 0u);
-          khd::umma_tf32_ss(tmem_base, a_hi + adv, b_lo + adv, idesc, 1u);
-          khd::umma_tf32_ss(tmem_base, a_hi + adv, b_hi + adv, idesc, 1u);
+          khd::umma_tf32_ss(d, a_lo + adv, b_hi + adv, idesc, (in_chunk | kk) != 0 ? 1u : 0u);
+          khd::umma_tf32_ss(d, a_hi + adv, b_lo + adv, idesc, 1u);
+          khd::umma_tf32_ss(d, a_hi + adv, b_hi + adv, idesc, 1u);
         }
         khd::umma_commit(empty0 + 8 * s); // stage reusable once these MMAs retire
+        if (in_chunk == kChunkBlocks - 1 || kb == k_blocks - 1)
+          khd::umma_commit(acc_full0 + 8 * buf); // chunk complete: hand it to the epilogue
       }
-      if (ok) khd::umma_commit(accum_bar);
     }
   } else {
-    // ---- epilogue: tensor memory -> registers -> C -------------------------------
-    const int quad = warp & 3; // this warp's 32 tensor-memory lanes
-    const bool ok = k_blocks == 0 ||
-                    khd::mbar_wait(accum_bar, 0u, &s_abort, status, khd::kStatusMmaWaitTimeout,
-                                   static_cast<uint32_t>(blockIdx.x));
-    if (ok && k_blocks > 0) {
+    // ---- epilogue: drain every K chunk from tensor memory into fp32 registers
+    //      (round-to-nearest adds), then store C. Two warps share each 32-lane
+    //      quarter of tensor memory and take 128 columns each. -------------------------
+    const int ew = warp - 2;
+    const int quad = warp & 3;
+    const int half = ew >> 2;
+    const uint32_t lane_base = static_cast<uint32_t>(quad * 32) << 16;
+    float acc[kBN / 2];
+#pragma unroll
+    for (int i = 0; i < kBN / 2; ++i) acc[i] = 0.f;
+    bool ok = true;
+    for (int64_t chunk = 0; chunk < num_chunks && ok; ++chunk) {
+      const int buf = static_cast<int>(chunk & 1);
+      ok = khd::mbar_wait(acc_full0 + 8 * buf, static_cast<uint32_t>((chunk >> 1) & 1), &s_abort,
+                          status, khd::kStatusMmaWaitTimeout, static_cast<uint32_t>(chunk));
+      if (!ok) break;
       khd::tc_fence_after_sync();
-      const int64_t row = static_cast<int64_t>(m0) + quad * 32 + lane;
-      float *crow = c + row * c_stride0;
-      const bool vec_ok = c_stride1 == 1 && (c_stride0 & 3) == 0 && khd::is_aligned16(c);
-#pragma unroll 1
-      for (int chunk = 0; chunk < kBN / 32; ++chunk) {
+      const uint32_t src = tmem_base + lane_base + static_cast<uint32_t>(buf * kBN + half * (kBN / 2));
+#pragma unroll
+      for (int piece = 0; piece < kBN / 2 / 32; ++piece) {
         uint32_t r[32];
-        khd::tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + chunk * 32, r);
+        khd::tmem_ld_32x32(src + piece * 32, r);
         khd::tmem_ld_wait();
-        const int64_t col0 = static_cast<int64_t>(n0) + chunk * 32;
-        if (row < m) {
-          if (vec_ok && col0 + 32 <= n) {
 #pragma unroll
-            for (int j = 0; j < 8; ++j)
-              __stcs(reinterpret_cast<float4 *>(crow + col0) + j,
-                     make_float4(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]),
-                                 __uint_as_float(r[4 * j + 2]), __uint_as_float(r[4 * j + 3])));
-          } else {
+        for (int j = 0; j < 32; ++j) acc[piece * 32 + j] += __uint_as_float(r[j]);
+      }
+      khd::tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) khd::mbar_arrive(acc_empty0 + 8 * buf);
+    }
+    if (ok) {
+      const int64_t row = static_cast<int64_t>(m0) + quad * 32 + lane;
+      const int64_t col0 = static_cast<int64_t>(n0) + half * (kBN / 2);
+      if (row < m) {
+        float *crow = c + row * c_stride0;
+        const bool vec_ok = c_stride1 == 1 && (c_stride0 & 3) == 0 && khd::is_aligned16(c);
+        if (vec_ok && col0 + kBN / 2 <= n) {
 #pragma unroll
-            for (int j = 0; j < 32; ++j)
-              if (col0 + j < n) crow[(col0 + j) * c_stride1] = __uint_as_float(r[j]);
-          }
+          for (int j = 0; j < kBN / 2 / 4; ++j)
+            __stcs(reinterpret_cast<float4 *>(crow + col0) + j,
+                   make_float4(acc[4 * j], acc[4 * j + 1], acc[4 * j + 2], acc[4 * j + 3]));
+        } else {
+#pragma unroll
+          for (int j = 0; j < kBN / 2; ++j)
+            if (col0 + j < n) crow[(col0 + j) * c_stride1] = acc[j];
         }
       }
-    } else if (ok) {
-      // k == 0: the product is all zeros
-      const int64_t row = static_cast<int64_t>(m0) + quad * 32 + lane;
-      if (row < m)
-        for (int j = 0; j < kBN; ++j)
-          if (n0 + j < n) c[row * c_stride0 + (n0 + j) * c_stride1] = 0.f;
     }
-    khd::tc_fence_before_sync();
   }
 
   __syncthreads();

@@ -219,12 +219,12 @@ KernelPlan plan_gemm(const ShapeMap &shape, const DeviceLimits &l) {
   sb.param_count = 10;
   LaunchStep g;
   g.entry = "gemm";
-  g.block = {192, 1, 1};
+  g.block = {320, 1, 1};
   const int64_t tiles = ((m + kGemmBM - 1) / kGemmBM) * ((n + kGemmBN - 1) / kGemmBN);
   g.grid = {static_cast<unsigned>(tiles), 1, 1};
   g.dynamic_smem = kGemmStages * kGemmStageBytes + 1024;
   g.param_count = 21 + 4 + 2;
-  g.tmem_columns = 256;
+  g.tmem_columns = 512;
   p.steps = {sa, sb, g};
   p.work = 2.0 * static_cast<double>(m) * static_cast<double>(n) * static_cast<double>(k);
   p.work_is_flops = true;
