@@ -113,6 +113,18 @@ int kh_gemm(kh_context *ctx, const float *a, const float *b, float *c, int64_t m
 int kh_attention(kh_context *ctx, const float *q, const float *k, const float *v, float *o,
                  int64_t batch, int64_t heads, int64_t seq, int64_t head_dim, void *stream);
 
+/* No counterpart in the reference. The scan for callers that must not allocate
+ * device memory (memory-pool owners, allocator-free plugin callbacks, fixed
+ * audited budgets): same result as kh_scan, but the look-back scratch is a
+ * fixed array inside the library image instead of a cuMemAlloc'ed buffer, so
+ * the call allocates and frees nothing. n may not exceed
+ * kh_scan_noalloc_max_elements() (16,777,216; larger n is refused with code 2).
+ * The owning device must be current; the first call on a device resolves the
+ * array's address and should be made outside stream capture; calls on one
+ * device share the array and must not overlap on the GPU. */
+int kh_scan_noalloc(const float *x, float *y, int64_t n, void *stream);
+int64_t kh_scan_noalloc_max_elements(void);
+
 /* Device memory of the context's device (Buffer::allocate / copy_from_host /
  * copy_to_host, include/kernelh/runtime/buffer.hpp). */
 int kh_malloc(kh_context *ctx, size_t bytes, void **out);

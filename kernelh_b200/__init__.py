@@ -72,6 +72,8 @@ def _load() -> C.CDLL:
     L.kh_fused_gelu.argtypes = [vp, f32p, f32p, i64, vp]
     L.kh_fused_gelu_bias.argtypes = [vp, f32p, f32p, f32p, i64, vp]
     L.kh_scan.argtypes = [vp, f32p, f32p, i64, vp]
+    L.kh_scan_noalloc.argtypes = [f32p, f32p, i64, vp]
+    L.kh_scan_noalloc_max_elements.restype = C.c_int64
     L.kh_softmax.argtypes = [vp, f32p, f32p, i64, i64, vp]
     L.kh_layernorm.argtypes = [vp, f32p, f32p, f32p, f32p, i64, i64, vp]
     L.kh_gemm.argtypes = [vp, f32p, f32p, f32p, i64, i64, i64, vp]
@@ -233,6 +235,18 @@ class Context:
 
     def memcpy_d2h(self, dst, src: int, nbytes: int) -> None:
         _check(lib.kh_memcpy_d2h(self._h, _ptr(dst), src, nbytes))
+
+
+def scan_noalloc(x, y, n: int, stream: int | None = None) -> None:
+    """Inclusive prefix sum without any device allocation: for callers that own
+    all device memory themselves or may not call an allocator. Uses a fixed
+    scratch array inside the library (n <= scan_noalloc_max_elements()); the
+    tensors' device must be current; calls on one device must not overlap."""
+    _check(lib.kh_scan_noalloc(_ptr(x), _ptr(y), n, stream))
+
+
+def scan_noalloc_max_elements() -> int:
+    return int(lib.kh_scan_noalloc_max_elements())
 
 
 # --------------------------------------------------------------------------- host helpers

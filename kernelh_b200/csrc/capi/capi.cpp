@@ -66,6 +66,9 @@ int launch_named(kh_context *ctx, const char *kernel, const kh::ShapeMap &shape,
 extern "C" {
 
 const char *kh_last_error(void) { return g_last_error.c_str(); }
+// For entry points implemented outside this file: records the calling thread's
+// error message and returns the code to hand back.
+int kh_detail_set_error(int code, const char *message) { return set_error(code, message ? message : ""); }
 const char *kh_version(void) { return "kernelh_b200 0.1 (sm_100a)"; }
 
 int kh_context_create(int device_ordinal, kh_context **out) {
