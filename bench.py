@@ -185,20 +185,45 @@ def reference_arm(args) -> None:
     print(json.dumps(line), flush=True)
 
 
-def time_rotating(torch, launch, sets, iters):
-    """Average ms per launch over `iters` launches that rotate through `sets`
-    argument sets whose total size exceeds L2, after 3 warm-up rounds."""
+def time_rotating(torch, launch, sets, iters, use_graph=True):
+    """Average ms per launch while rotating through `sets` argument sets whose
+    total size exceeds L2. The launches are captured once into a CUDA graph and
+    the graph is replayed, so the figure is the GPU's back-to-back rate and not
+    the host's launch rate (these kernels run for 5-35 us). Falls back to a plain
+    launch loop when capture is not possible. Returns (ms, method)."""
+    stream = torch.cuda.current_stream().cuda_stream
     for _ in range(3):
         for s in sets:
-            launch(s)
+            launch(s, stream)
     torch.cuda.synchronize()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    if use_graph:
+        try:
+            per_graph = max(len(sets), (32 // len(sets)) * len(sets))
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                cs = torch.cuda.current_stream().cuda_stream
+                for i in range(per_graph):
+                    launch(sets[i % len(sets)], cs)
+            replays = max(3, iters // per_graph)
+            for _ in range(2):
+                g.replay()
+            torch.cuda.synchronize()
+            e0.record()
+            for _ in range(replays):
+                g.replay()
+            e1.record()
+            torch.cuda.synchronize()
+            return e0.elapsed_time(e1) / (replays * per_graph), "cuda graph replay"
+        except Exception as exc:  # capture refused: time the plain loop instead
+            sys.stderr.write(f"bench.py: graph capture failed ({exc}); timing a launch loop\n")
+            torch.cuda.synchronize()
     e0.record()
     for i in range(iters):
-        launch(sets[i % len(sets)])
+        launch(sets[i % len(sets)], stream)
     e1.record()
     torch.cuda.synchronize()
-    return e0.elapsed_time(e1) / iters
+    return e0.elapsed_time(e1) / iters, "launch loop"
 
 
 def memory_bound_rows(torch, ctx, stream, hbm_peak: float) -> dict:
@@ -208,10 +233,13 @@ def memory_bound_rows(torch, ctx, stream, hbm_peak: float) -> dict:
 
     def row(name, kernel, shape, make, bytes_per_launch, nsets, iters=200):
         sets = [make() for _ in range(nsets)]
-        ms = time_rotating(torch, lambda s: ctx.launch(kernel, shape, s, stream), sets, iters)
+        # scan's look-back state carries a per-launch epoch chosen on the host, so a
+        # captured scan launch cannot be replayed: it is timed as a launch loop.
+        ms, method = time_rotating(torch, lambda s, st: ctx.launch(kernel, shape, s, st), sets, iters,
+                                   use_graph=(kernel != "scan"))
         gbs = bytes_per_launch / ms / 1e6
         out[name] = {"shape": shape, "ms": ms, "gbs": gbs, "frac_of_measured_hbm": gbs / hbm_peak,
-                     "buffer_sets": nsets}
+                     "buffer_sets": nsets, "timing": method}
 
     f = lambda *shape: torch.randn(*shape, device="cuda")
     n = 1 << 24
@@ -244,6 +272,7 @@ def gpu_arm(args) -> None:
     import torch.distributed as dist
 
     import kernelh_b200 as kh
+    from kernelh_b200 import sharding
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -264,9 +293,8 @@ def gpu_arm(args) -> None:
     peaks = measured_peaks()
     size = args.size
     flops = 2.0 * size ** 3
-    if size % world != 0:
-        raise SystemExit(f"size {size} is not divisible by {world} ranks")
-    rows = size // world
+    row_lo, row_hi = sharding.gemm_shard_shape(size, size, size, world, rank)["rows"]
+    rows = row_hi - row_lo
 
     # Synthetic inputs, identical on every rank: A, B ~ U[-1, 1), seeded.
     gen = torch.Generator(device="cuda")
@@ -274,8 +302,8 @@ def gpu_arm(args) -> None:
     a = torch.rand(size, size, device="cuda", generator=gen) * 2 - 1
     b = torch.rand(size, size, device="cuda", generator=gen) * 2 - 1
     c = torch.zeros(size, size, device="cuda")
-    a_shard = a[rank * rows:(rank + 1) * rows]
-    c_shard = c[rank * rows:(rank + 1) * rows]
+    a_shard = a[row_lo:row_hi]
+    c_shard = c[row_lo:row_hi]
 
     def barrier():
         if world > 1:
@@ -284,7 +312,7 @@ def gpu_arm(args) -> None:
     def step():
         ctx.gemm(a_shard, b, c_shard, rows, size, size, stream)
         if world > 1:
-            dist.all_gather_into_tensor(c, c_shard)
+            sharding.gather_output(c, c_shard, dist)
 
     for _ in range(max(args.warmup, 3)):
         step()

@@ -16,10 +16,11 @@
 // `state` is scratch of 64-bit words owned by the caller:
 //   word 0            ticket counter (monotonic across launches)
 //   word 1            status word (low u32) + detail (high u32), 0 = clean
-//   words 2+3t..4+3t  tile t: flag, block aggregate (f64), inclusive prefix (f64)
-// A flag holds (epoch << 2) | s with s = 1 "aggregate published", s = 2
-// "inclusive prefix published"; a flag of another epoch reads as "nothing
-// yet", so the scratch never has to be cleared between launches: the host
+//   words 2+2t, 3+2t  tile t: two self-validating halves of {fp64 value, tag}
+// A tag holds (epoch << 2) | s with s = 1 "the value is this tile's aggregate",
+// s = 2 "the value is the inclusive prefix up to this tile"; a tag of another
+// epoch reads as "nothing yet", so the scratch never has to be cleared between
+// launches: the host
 // passes a fresh epoch and the counter value at which this launch's tickets
 // start. Launches that share a state buffer must not overlap on the GPU.
 //
@@ -28,7 +29,7 @@
 // look-back spin runs out, the kernel records kStatusScanLookbackTimeout in the
 // status word, stops and returns; other blocks see the word and stop too.
 //
-// HBM-bound: 8 bytes per element; the scratch traffic is 24 bytes per
+// HBM-bound: 8 bytes per element; the scratch traffic is 16 bytes per
 // 4096-element tile.
 #include "kh_device.cuh"
 
@@ -36,34 +37,45 @@ namespace {
 
 constexpr int kThreads = 256;
 constexpr int kPerThread = 16;
+constexpr int kRows = kPerThread / 4;        // float4 per thread per tile
 constexpr int kTile = kThreads * kPerThread; // 4096 elements
 constexpr uint32_t kSpinLimit = 1u << 22;
+constexpr int kLook = 4; // tile descriptors each lane reads per look-back step
 
-__device__ __forceinline__ uint32_t ld_acquire_u32(const uint32_t *p) {
+__device__ __forceinline__ uint32_t ld_relaxed_u32(const uint32_t *p) {
   uint32_t v;
-  asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
   return v;
 }
-__device__ __forceinline__ void st_release_u32(uint32_t *p, uint32_t v) {
-  asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+
+// A tile descriptor is two 64-bit words, each {32 bits of the fp64 value, tag},
+// tag = (epoch << 2) | status. Each word is written whole, so a reader that
+// finds the same valid tag in both words has a consistent value without any
+// fence or second dependent load: one 128-bit load per look-back step.
+__device__ __forceinline__ void publish(unsigned long long *slot, double value, uint32_t tag) {
+  const unsigned long long bits = static_cast<unsigned long long>(__double_as_longlong(value));
+  const unsigned long long w0 = (bits & 0xFFFFFFFF00000000ull) | tag;
+  const unsigned long long w1 = (bits << 32) | tag;
+  asm volatile("st.relaxed.gpu.global.v2.u64 [%0], {%1, %2};" ::"l"(slot), "l"(w0), "l"(w1) : "memory");
 }
-__device__ __forceinline__ double ld_relaxed_f64(const double *p) {
-  double v;
-  asm volatile("ld.relaxed.gpu.global.f64 %0, [%1];" : "=d"(v) : "l"(p) : "memory");
-  return v;
-}
-__device__ __forceinline__ void st_relaxed_f64(double *p, double v) {
-  asm volatile("st.relaxed.gpu.global.f64 [%0], %1;" ::"l"(p), "d"(v) : "memory");
+// Returns the status (0 = nothing usable yet) and the value.
+__device__ __forceinline__ uint32_t peek(const unsigned long long *slot, uint32_t epoch, double *value) {
+  unsigned long long w0, w1;
+  asm volatile("ld.relaxed.gpu.global.v2.u64 {%0, %1}, [%2];" : "=l"(w0), "=l"(w1) : "l"(slot) : "memory");
+  const uint32_t t0 = static_cast<uint32_t>(w0), t1 = static_cast<uint32_t>(w1);
+  if (t0 != t1 || (t0 >> 2) != epoch) return 0u;
+  *value = __longlong_as_double(static_cast<long long>((w0 & 0xFFFFFFFF00000000ull) | (w1 >> 32)));
+  return t0 & 3u;
 }
 
 } // namespace
 
-extern "C" __global__ void __launch_bounds__(kThreads)
+extern "C" __global__ void __launch_bounds__(kThreads, 4)
 scan(KH_MEMREF1(const float, x), KH_MEMREF1(float, y), KH_MEMREF1(unsigned long long, state),
      uint32_t epoch, unsigned long long ticket_base) {
-  __shared__ double warp_totals[kThreads / 32];
+  __shared__ double warp_totals[kRows * (kThreads / 32)];
   __shared__ double s_exclusive;
-  __shared__ unsigned long long s_tile;
+  __shared__ unsigned long long s_tile[2];
   __shared__ int s_abort;
 
   const float *__restrict__ x = KH_DATA(x);
@@ -76,117 +88,148 @@ scan(KH_MEMREF1(const float, x), KH_MEMREF1(float, y), KH_MEMREF1(unsigned long 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const bool vec_ok = khd::is_aligned16(x) && khd::is_aligned16(y) && x_stride0 == 1 && y_stride0 == 1;
 
+  if (tid == 0) {
+    s_tile[0] = atomicAdd(state, 1ull) - ticket_base;
+    s_abort = 0;
+  }
+  __syncthreads();
+
   // Persistent over tickets: any grid size works, and a grid larger than the
-  // tile count just finds no ticket.
-  while (true) {
-    if (tid == 0) {
-      s_tile = atomicAdd(state, 1ull) - ticket_base;
-      s_abort = 0;
-    }
-    __syncthreads();
-    const int64_t tile = static_cast<int64_t>(s_tile);
+  // tile count just finds no ticket. The next ticket is requested at the top of
+  // an iteration and only read at its end, so the atomic's round trip overlaps
+  // the tile's loads.
+  for (int it = 0;; ++it) {
+    const int64_t tile = static_cast<int64_t>(s_tile[it & 1]);
     if (tile >= num_tiles) {
       // Every block ends on exactly one surplus ticket, so a clean launch moves
       // the counter by num_tiles + gridDim.x: the host advances ticket_base by that.
       return;
     }
-    const int64_t base = tile * kTile + static_cast<int64_t>(tid) * kPerThread;
+    unsigned long long next_ticket = 0;
+    if (tid == 0) next_ticket = atomicAdd(state, 1ull) - ticket_base;
 
-    // ---- load (widen to fp64) and thread-serial scan ---------------------
-    double v[kPerThread];
-    if (vec_ok && base + kPerThread <= n) {
-      const float4 *p = reinterpret_cast<const float4 *>(x + base);
+    // Element order inside a tile: kRows rows of 1024 elements; thread t owns the
+    // four consecutive elements 4t..4t+3 of every row, so each load and store
+    // instruction of a warp covers one contiguous 512-byte run. The inputs stay
+    // in registers as fp32; fp64 prefixes are formed twice (totals now, outputs
+    // later) instead of being held, which keeps four blocks resident per SM.
+    const int64_t tile_base = tile * kTile;
+    const bool full_tile = tile_base + kTile <= n;
+    float4 f[kRows];
+    if (vec_ok && full_tile) {
+      const float4 *p = reinterpret_cast<const float4 *>(x + tile_base) + tid;
 #pragma unroll
-      for (int i = 0; i < kPerThread / 4; ++i) {
-        const float4 f = p[i];
-        v[4 * i + 0] = f.x; v[4 * i + 1] = f.y; v[4 * i + 2] = f.z; v[4 * i + 3] = f.w;
-      }
+      for (int i = 0; i < kRows; ++i) f[i] = __ldcs(p + i * kThreads);
     } else {
 #pragma unroll
-      for (int i = 0; i < kPerThread; ++i)
-        v[i] = (base + i < n) ? static_cast<double>(x[(base + i) * x_stride0]) : 0.0;
-    }
+      for (int i = 0; i < kRows; ++i) {
+        float t[4];
 #pragma unroll
-    for (int i = 1; i < kPerThread; ++i) v[i] += v[i - 1];
-
-    // ---- block scan of the per-thread totals ------------------------------
-    double incl = v[kPerThread - 1];
+        for (int j = 0; j < 4; ++j) {
+          const int64_t e = tile_base + i * (kThreads * 4) + tid * 4 + j;
+          t[j] = e < n ? x[e * x_stride0] : 0.f;
+        }
+        f[i] = make_float4(t[0], t[1], t[2], t[3]);
+      }
+    }
+    double run_total[kRows], incl[kRows];
+#pragma unroll
+    for (int i = 0; i < kRows; ++i) {
+      run_total[i] = ((static_cast<double>(f[i].x) + static_cast<double>(f[i].y)) +
+                      static_cast<double>(f[i].z)) + static_cast<double>(f[i].w);
+      incl[i] = run_total[i];
+    }
 #pragma unroll
     for (int o = 1; o < 32; o <<= 1) {
-      const double up = __shfl_up_sync(0xffffffffu, incl, o);
-      if (lane >= o) incl += up;
-    }
-    if (lane == 31) warp_totals[warp] = incl;
-    __syncthreads();
-    double warp_offset = 0.0, block_total = 0.0;
 #pragma unroll
-    for (int w = 0; w < kThreads / 32; ++w) {
-      const double t = warp_totals[w];
-      if (w < warp) warp_offset += t;
-      block_total += t;
+      for (int i = 0; i < kRows; ++i) {
+        const double up = __shfl_up_sync(0xffffffffu, incl[i], o);
+        if (lane >= o) incl[i] += up;
+      }
     }
-    const double thread_exclusive = warp_offset + (incl - v[kPerThread - 1]);
+    if (lane == 31) {
+#pragma unroll
+      for (int i = 0; i < kRows; ++i) warp_totals[i * (kThreads / 32) + warp] = incl[i];
+    }
+    __syncthreads();
+    // (row, warp) totals in element order; everything before mine is my offset
+    double thread_exclusive[kRows];
+    double block_total = 0.0;
+    {
+      double running = 0.0;
+#pragma unroll
+      for (int i = 0; i < kRows; ++i) {
+#pragma unroll
+        for (int w = 0; w < kThreads / 32; ++w) {
+          if (w == warp) thread_exclusive[i] = running + (incl[i] - run_total[i]);
+          running += warp_totals[i * (kThreads / 32) + w];
+        }
+      }
+      block_total = running;
+    }
 
-    // ---- decoupled look-back (warp 0) -------------------------------------
+    // ---- decoupled look-back (warp 0): kLook descriptors per lane, so one
+    //      round trip to L2 covers a window of 32 * kLook preceding tiles --------
     if (warp == 0) {
-      uint32_t *flag_of = nullptr;
-      unsigned long long *slot = state + 2 + 3 * tile;
-      flag_of = reinterpret_cast<uint32_t *>(slot);
+      unsigned long long *slot = state + 2 + 2 * tile;
       double exclusive = 0.0;
       bool aborted = false;
       if (tile == 0) {
-        if (lane == 0) {
-          st_relaxed_f64(reinterpret_cast<double *>(slot + 2), block_total);
-          st_release_u32(flag_of, (epoch << 2) | 2u);
-        }
+        if (lane == 0) publish(slot, block_total, (epoch << 2) | 2u);
       } else {
-        if (lane == 0) {
-          st_relaxed_f64(reinterpret_cast<double *>(slot + 1), block_total);
-          st_release_u32(flag_of, (epoch << 2) | 1u);
-        }
-        int64_t window_end = tile; // look at tiles [window_end-32, window_end)
+        if (lane == 0) publish(slot, block_total, (epoch << 2) | 1u);
+        int64_t window_end = tile; // look at tiles [window_end - 32*kLook, window_end)
         while (true) {
-          const int64_t t = window_end - 1 - lane;
-          uint32_t st = 2u; // lanes before tile 0 act as "inclusive prefix 0"
-          double val = 0.0;
-          if (t >= 0) {
-            const unsigned long long *ps = state + 2 + 3 * t;
-            const uint32_t *pf = reinterpret_cast<const uint32_t *>(ps);
-            uint32_t f = ld_acquire_u32(pf);
+          uint32_t st[kLook];
+          double val[kLook];
+#pragma unroll
+          for (int k = 0; k < kLook; ++k) {
+            const int64_t t = window_end - 1 - (32 * k + lane);
+            st[k] = 2u; // positions before tile 0 act as "inclusive prefix 0"
+            val[k] = 0.0;
+            if (t >= 0) st[k] = peek(state + 2 + 2 * t, epoch, &val[k]);
+          }
+#pragma unroll
+          for (int k = 0; k < kLook; ++k) {
+            const int64_t t = window_end - 1 - (32 * k + lane);
             uint32_t spins = 0;
-            while ((f >> 2) != epoch || (f & 3u) == 0u) {
-              if (++spins > kSpinLimit || ((spins & 1023u) == 0u && ld_acquire_u32(status) != 0u)) {
+            while (st[k] == 0u && !aborted) {
+              if (++spins > kSpinLimit || ((spins & 1023u) == 0u && ld_relaxed_u32(status) != 0u)) {
                 aborted = true;
                 break;
               }
-              __nanosleep(32);
-              f = ld_acquire_u32(pf);
-            }
-            if (!aborted) {
-              st = f & 3u;
-              val = ld_relaxed_f64(reinterpret_cast<const double *>(ps + st));
+              __nanosleep(20);
+              st[k] = peek(state + 2 + 2 * t, epoch, &val[k]);
             }
           }
           if (__any_sync(0xffffffffu, aborted)) {
             aborted = true;
             break;
           }
-          // lanes are ordered nearest-first; stop at the first inclusive prefix
-          const uint32_t incl_mask = __ballot_sync(0xffffffffu, st == 2u);
-          const int first = incl_mask ? (__ffs(incl_mask) - 1) : 32;
-          double contrib = (lane <= first) ? val : 0.0;
+          // positions are ordered nearest-first (k major, lane minor): take every
+          // aggregate before the first inclusive prefix, and that prefix itself
+          double contrib = 0.0;
+          bool found = false;
+#pragma unroll
+          for (int k = 0; k < kLook; ++k) {
+            const uint32_t incl_mask = __ballot_sync(0xffffffffu, st[k] == 2u);
+            if (!found) {
+              const int first = incl_mask ? (__ffs(incl_mask) - 1) : 32;
+              if (lane <= first) contrib += val[k];
+              found = incl_mask != 0u;
+            }
+          }
 #pragma unroll
           for (int o = 16; o > 0; o >>= 1) contrib += __shfl_xor_sync(0xffffffffu, contrib, o);
           exclusive += contrib;
-          if (first < 32) break;
-          window_end -= 32;
+          if (found) break;
+          window_end -= 32 * kLook;
         }
         if (aborted) {
           if (lane == 0) khd::report_status(status, khd::kStatusScanLookbackTimeout,
                                             static_cast<uint32_t>(tile));
         } else if (lane == 0) {
-          st_relaxed_f64(reinterpret_cast<double *>(slot + 2), exclusive + block_total);
-          st_release_u32(flag_of, (epoch << 2) | 2u);
+          publish(slot, exclusive + block_total, (epoch << 2) | 2u);
         }
       }
       if (lane == 0) {
@@ -196,22 +239,35 @@ scan(KH_MEMREF1(const float, x), KH_MEMREF1(float, y), KH_MEMREF1(unsigned long 
     }
     __syncthreads();
     if (s_abort) return;
-    const double offset = s_exclusive + thread_exclusive;
+    const double tile_offset = s_exclusive;
 
-    // ---- store (one rounding) ---------------------------------------------
-    if (vec_ok && base + kPerThread <= n) {
-      float4 *p = reinterpret_cast<float4 *>(y + base);
+    // ---- store (one rounding per element) -----------------------------------
+    if (vec_ok && full_tile) {
+      float4 *p = reinterpret_cast<float4 *>(y + tile_base) + tid;
 #pragma unroll
-      for (int i = 0; i < kPerThread / 4; ++i)
-        __stcs(p + i, make_float4(static_cast<float>(offset + v[4 * i + 0]),
-                                  static_cast<float>(offset + v[4 * i + 1]),
-                                  static_cast<float>(offset + v[4 * i + 2]),
-                                  static_cast<float>(offset + v[4 * i + 3])));
+      for (int i = 0; i < kRows; ++i) {
+        double o = tile_offset + thread_exclusive[i];
+        float4 r;
+        o += static_cast<double>(f[i].x); r.x = static_cast<float>(o);
+        o += static_cast<double>(f[i].y); r.y = static_cast<float>(o);
+        o += static_cast<double>(f[i].z); r.z = static_cast<float>(o);
+        o += static_cast<double>(f[i].w); r.w = static_cast<float>(o);
+        __stcs(p + i * kThreads, r);
+      }
     } else {
 #pragma unroll
-      for (int i = 0; i < kPerThread; ++i)
-        if (base + i < n) y[(base + i) * y_stride0] = static_cast<float>(offset + v[i]);
+      for (int i = 0; i < kRows; ++i) {
+        double o = tile_offset + thread_exclusive[i];
+        const float t[4] = {f[i].x, f[i].y, f[i].z, f[i].w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const int64_t e = tile_base + i * (kThreads * 4) + tid * 4 + j;
+          o += static_cast<double>(t[j]);
+          if (e < n) y[e * y_stride0] = static_cast<float>(o);
+        }
+      }
     }
+    if (tid == 0) s_tile[(it + 1) & 1] = next_ticket;
     __syncthreads(); // shared words are rewritten by the next ticket
   }
 }

@@ -2,14 +2,14 @@
 // allocate device memory.
 //
 // Who needs this. The ordinary scan entry points keep their look-back scratch
-// (a ticket counter plus three 64-bit words per 4096-element tile) in a buffer
+// (a ticket counter plus two 64-bit words per 4096-element tile) in a buffer
 // the context allocates with cuMemAlloc on first use and grows on demand. Some
 // hosts cannot do that: code running inside a memory pool or arena that owns
 // every byte of the device and forbids side allocations, plugin callbacks that
 // must not call an allocator because an allocation may synchronise the device,
 // and code whose device memory budget is fixed and audited up front. For them
 // the scratch here is a file-scope __device__ array that is part of the
-// library's image: every GPU that loads the library carries it (98,320 bytes)
+// library's image: every GPU that loads the library carries it (65,552 bytes)
 // until the process exits, and nothing is allocated or freed by the call.
 //
 // Limits and rules
@@ -42,7 +42,7 @@ namespace {
 
 constexpr int64_t kMaxElements = int64_t(1) << 24;
 constexpr int64_t kMaxTiles = kMaxElements / kTile; // 4096
-constexpr int64_t kStateWords = 2 + 3 * kMaxTiles;
+constexpr int64_t kStateWords = 2 + 2 * kMaxTiles;
 
 // The scratch itself. In host code this name is only a handle for
 // cudaGetSymbolAddress, never a pointer a kernel could use.
@@ -95,7 +95,7 @@ extern "C" int kh_scan_noalloc(const float *x, float *y, int64_t n, void *stream
   }
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const int64_t tiles = (n + kTile - 1) / kTile;
-  const int64_t words = 2 + 3 * tiles;
+  const int64_t words = 2 + 2 * tiles;
   // The array keeps what the last call left: clear the part this call reads.
   if (cudaError_t e = cudaMemsetAsync(d.scratch, 0, static_cast<size_t>(words) * 8, s); e != cudaSuccess)
     return fail_cuda("cudaMemsetAsync", e);

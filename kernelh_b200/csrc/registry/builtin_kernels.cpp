@@ -170,7 +170,7 @@ KernelPlan plan_scan(const ShapeMap &shape, const DeviceLimits &l) {
   s.grid = {static_cast<unsigned>(std::min<int64_t>(tiles, sm_count(l) * 4)), 1, 1};
   s.param_count = 17;
   p.steps = {s};
-  p.workspace_bytes = static_cast<size_t>(2 + 3 * tiles) * 8;
+  p.workspace_bytes = static_cast<size_t>(2 + 2 * tiles) * 8;
   p.work = 2.0 * static_cast<double>(n) * 4.0;
   return p;
 }
@@ -186,7 +186,7 @@ Result<void> run_scan(Executor &ex, const KernelPlan &p, const std::vector<void 
   LaunchArgs args;
   args.add_memref(b[0], {n});
   args.add_memref(b[1], {n});
-  args.add_memref(ticket->state, {static_cast<int64_t>(2 + 3 * tiles)});
+  args.add_memref(ticket->state, {static_cast<int64_t>(2 + 2 * tiles)});
   args.add_scalar<uint32_t>(ticket->epoch);
   args.add_scalar<uint64_t>(ticket->ticket_base);
   return ex.launch(*fn, p.steps[0], args, stream);

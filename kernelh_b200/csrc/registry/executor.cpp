@@ -141,7 +141,7 @@ Result<Executor::ScanTicket> Executor::scan_ticket(int64_t tiles, unsigned grid)
     const int64_t cap = std::max<int64_t>(tiles, 4096);
     if (auto r = backend_->device_synchronize(); !r) return std::unexpected(r.error());
     scan_state_ = Buffer();
-    const size_t words = 2 + 3 * static_cast<size_t>(cap);
+    const size_t words = 2 + 2 * static_cast<size_t>(cap);
     auto b = Buffer::allocate(backend_, words * 8);
     if (!b) return std::unexpected(b.error());
     scan_state_ = std::move(*b);

@@ -1,0 +1,89 @@
+"""The `kernelh` command-line tool: the reference CLI's grammar, messages and
+exit codes (tools/kernelh/main.cpp:125-158, 375-390) for the verbs that touch
+this path, plus the new `run` verb."""
+import os
+import re
+import subprocess
+
+import numpy as np
+import pytest
+
+import kernelh_b200 as kh
+
+CLI = os.path.join(os.path.dirname(kh.LIB_PATH), "bin", "kernelh")
+
+
+def cli(*args):
+    return subprocess.run([CLI, *args], capture_output=True, text=True)
+
+
+def test_compile_writes_the_sm100a_code_object(tmp_path):
+    r = cli("compile", "--kernel", "softmax", "--shape", "rows=4096,cols=1024", "--target",
+            "nvptx-sm_100a", "--out", str(tmp_path))
+    assert r.returncode == 0, r.stderr
+    assert r.stdout.splitlines() == [f"wrote {tmp_path}/softmax.cubin", "compile ok"]
+    blob = (tmp_path / "softmax.cubin").read_bytes()
+    assert blob[:4] == b"\x7fELF" and b"softmax" in blob
+    assert blob == kh.kernel_image("softmax")
+    # --flag=value form
+    r = cli("compile", "--kernel=vecadd", "--target=nvptx-sm_100a", f"--out={tmp_path}")
+    assert r.returncode == 0 and (tmp_path / "vecadd.cubin").exists()
+
+
+def test_compile_errors_and_exit_codes(tmp_path):
+    r = cli("compile", "--kernel", "gemm", "--target", "nvptx-sm_90", "--out", str(tmp_path))
+    assert r.returncode == 1 and "valid --target values" in r.stderr
+    r = cli("compile", "--kernel", "gemm", "--target", "nvptx-sm_80", "--out", str(tmp_path))
+    assert r.returncode == 1 and "only carries sm_100a code objects" in r.stderr
+    r = cli("compile", "--kernel", "nope", "--target", "nvptx-sm_100a", "--out", str(tmp_path))
+    assert r.returncode == 1 and "unknown kernel template 'nope'; registered kernels:" in r.stderr
+    r = cli("compile", "--kernel", "gemm", "--shape", "m=4,n=4", "--target", "nvptx-sm_100a", "--out",
+            str(tmp_path))
+    assert r.returncode == 1 and "shape attribute 'k' is required" in r.stderr
+    assert cli("compile", "--kernel", "gemm").returncode == 2
+    assert cli().returncode == 2
+    assert cli("explore").returncode == 2
+    assert cli("run", "--kernel").returncode == 2
+
+
+def test_occupancy_report_for_the_planned_launch():
+    r = cli("bench", "--occupancy", "--kernel", "attention", "--shape",
+            "batch=8,heads=16,seq=1024,head_dim=64", "--target", "nvptx-sm_100a")
+    assert r.returncode == 0
+    assert '"threads_per_workgroup": 192' in r.stdout and '"tmem_columns": 512' in r.stdout
+    assert '"sm_resident_blocks": 1' in r.stdout
+
+
+def test_run_and_bench_skip_with_77_without_a_device():
+    import torch
+
+    if torch.cuda.is_available():
+        pytest.skip("a GPU is present")
+    assert cli("run", "--kernel", "vecadd", "--shape", "n=1024").returncode == 77
+    assert cli("bench", "--kernel", "vecadd", "--shape", "n=1024").returncode == 77
+
+
+@pytest.mark.gpu
+def test_run_matches_the_oracle_on_bit_exact_kernels(oracle, tmp_path):
+    n = 100000
+    r = cli("run", "--kernel", "vecadd", "--shape", f"n={n}", "--seed", "0x27ab13", "--dump",
+            str(tmp_path / "c.bin"))
+    assert r.returncode == 0, r.stderr
+    s = oracle.LcgStream(0x27AB13)
+    a, b = s.fill(n), s.fill(n)
+    ref = oracle.vecadd_ref(a, b)
+    got = np.fromfile(tmp_path / "c.bin", np.float32)
+    assert oracle.bit_mismatches(got, ref) == 0
+    assert f"fnv1a={oracle.fnv1a(ref):016x}" in r.stdout and "run ok" in r.stdout
+
+
+@pytest.mark.gpu
+def test_bench_row_and_results_csv(tmp_path):
+    r = cli("bench", "--kernel", "softmax", "--shape", "rows=4096,cols=1024", "--warmup", "2",
+            "--iters", "5", "--out", str(tmp_path))
+    assert r.returncode == 0, r.stderr
+    assert re.search(r"bench: kernelh softmax \[rows=4096,cols=1024\] ms_median=\d+\.\d+ rate=\d+\.\d+ GB/s",
+                     r.stdout)
+    lines = (tmp_path / "results.csv").read_text().splitlines()
+    assert lines[0] == "kernel,shape,backend,ms_median,gflops_or_gbps,timestamp,device"
+    assert lines[1].startswith('softmax,"rows=4096,cols=1024",kernelh,') and "B200" in lines[1]
