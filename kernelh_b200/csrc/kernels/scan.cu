@@ -40,7 +40,7 @@ constexpr int kPerThread = 16;
 constexpr int kRows = kPerThread / 4;        // float4 per thread per tile
 constexpr int kTile = kThreads * kPerThread; // 4096 elements
 constexpr uint32_t kSpinLimit = 1u << 22;
-constexpr int kLook = 4; // tile descriptors each lane reads per look-back step
+constexpr int kLook = 8; // tile descriptors each lane reads per look-back step
 
 __device__ __forceinline__ uint32_t ld_relaxed_u32(const uint32_t *p) {
   uint32_t v;
@@ -58,10 +58,13 @@ __device__ __forceinline__ void publish(unsigned long long *slot, double value, 
   const unsigned long long w1 = (bits << 32) | tag;
   asm volatile("st.relaxed.gpu.global.v2.u64 [%0], {%1, %2};" ::"l"(slot), "l"(w0), "l"(w1) : "memory");
 }
-// Returns the status (0 = nothing usable yet) and the value.
-__device__ __forceinline__ uint32_t peek(const unsigned long long *slot, uint32_t epoch, double *value) {
-  unsigned long long w0, w1;
+__device__ __forceinline__ void load_descriptor(const unsigned long long *slot, unsigned long long &w0,
+                                                unsigned long long &w1) {
   asm volatile("ld.relaxed.gpu.global.v2.u64 {%0, %1}, [%2];" : "=l"(w0), "=l"(w1) : "l"(slot) : "memory");
+}
+// Returns the status (0 = nothing usable yet) and the value.
+__device__ __forceinline__ uint32_t decode_descriptor(unsigned long long w0, unsigned long long w1,
+                                                      uint32_t epoch, double *value) {
   const uint32_t t0 = static_cast<uint32_t>(w0), t1 = static_cast<uint32_t>(w1);
   if (t0 != t1 || (t0 >> 2) != epoch) return 0u;
   *value = __longlong_as_double(static_cast<long long>((w0 & 0xFFFFFFFF00000000ull) | (w1 >> 32)));
@@ -95,9 +98,9 @@ scan(KH_MEMREF1(const float, x), KH_MEMREF1(float, y), KH_MEMREF1(unsigned long 
   __syncthreads();
 
   // Persistent over tickets: any grid size works, and a grid larger than the
-  // tile count just finds no ticket. The next ticket is requested at the top of
-  // an iteration and only read at its end, so the atomic's round trip overlaps
-  // the tile's loads.
+  // tile count just finds no ticket. A ticket is only taken when the block is
+  // ready to load that tile: a tile that is claimed early publishes its
+  // aggregate late, and every later tile's look-back would wait for it.
   for (int it = 0;; ++it) {
     const int64_t tile = static_cast<int64_t>(s_tile[it & 1]);
     if (tile >= num_tiles) {
@@ -105,9 +108,6 @@ scan(KH_MEMREF1(const float, x), KH_MEMREF1(float, y), KH_MEMREF1(unsigned long 
       // the counter by num_tiles + gridDim.x: the host advances ticket_base by that.
       return;
     }
-    unsigned long long next_ticket = 0;
-    if (tid == 0) next_ticket = atomicAdd(state, 1ull) - ticket_base;
-
     // Element order inside a tile: kRows rows of 1024 elements; thread t owns the
     // four consecutive elements 4t..4t+3 of every row, so each load and store
     // instruction of a warp covers one contiguous 512-byte run. The inputs stay
@@ -182,12 +182,21 @@ scan(KH_MEMREF1(const float, x), KH_MEMREF1(float, y), KH_MEMREF1(unsigned long 
         while (true) {
           uint32_t st[kLook];
           double val[kLook];
+          unsigned long long w0[kLook], w1[kLook];
+          // all loads of the window are issued before any result is looked at,
+          // so one step costs one round trip to L2 whatever kLook is
+#pragma unroll
+          for (int k = 0; k < kLook; ++k) {
+            const int64_t t = window_end - 1 - (32 * k + lane);
+            w0[k] = w1[k] = 0ull;
+            if (t >= 0) load_descriptor(state + 2 + 2 * t, w0[k], w1[k]);
+          }
 #pragma unroll
           for (int k = 0; k < kLook; ++k) {
             const int64_t t = window_end - 1 - (32 * k + lane);
             st[k] = 2u; // positions before tile 0 act as "inclusive prefix 0"
             val[k] = 0.0;
-            if (t >= 0) st[k] = peek(state + 2 + 2 * t, epoch, &val[k]);
+            if (t >= 0) st[k] = decode_descriptor(w0[k], w1[k], epoch, &val[k]);
           }
 #pragma unroll
           for (int k = 0; k < kLook; ++k) {
@@ -199,7 +208,8 @@ scan(KH_MEMREF1(const float, x), KH_MEMREF1(float, y), KH_MEMREF1(unsigned long 
                 break;
               }
               __nanosleep(20);
-              st[k] = peek(state + 2 + 2 * t, epoch, &val[k]);
+              load_descriptor(state + 2 + 2 * t, w0[k], w1[k]);
+              st[k] = decode_descriptor(w0[k], w1[k], epoch, &val[k]);
             }
           }
           if (__any_sync(0xffffffffu, aborted)) {
@@ -267,7 +277,7 @@ scan(KH_MEMREF1(const float, x), KH_MEMREF1(float, y), KH_MEMREF1(unsigned long 
         }
       }
     }
-    if (tid == 0) s_tile[(it + 1) & 1] = next_ticket;
+    if (tid == 0) s_tile[(it + 1) & 1] = atomicAdd(state, 1ull) - ticket_base;
     __syncthreads(); // shared words are rewritten by the next ticket
   }
 }
