@@ -38,6 +38,9 @@ def parse_args():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="kernelh_b200", choices=["kernelh_b200", "reference"])
     ap.add_argument("--size", type=int, default=SIZE, help=argparse.SUPPRESS)
+    ap.add_argument("--gather", default="p2p", choices=["p2p", "nccl"],
+                    help="N > 1: 'p2p' = the gemm epilogue stores C tiles into every rank's C over NVLink "
+                         "(symmetric memory) and a barrier follows; 'nccl' = plain gemm + NCCL all-gather")
     ap.add_argument("--no-extras", action="store_true",
                     help="skip the memory-bound rows, the e2e leg and the CPU baseline")
     return ap.parse_args()
@@ -301,7 +304,27 @@ def gpu_arm(args) -> None:
     gen.manual_seed(SEED)
     a = torch.rand(size, size, device="cuda", generator=gen) * 2 - 1
     b = torch.rand(size, size, device="cuda", generator=gen) * 2 - 1
-    c = torch.zeros(size, size, device="cuda")
+    gather = "none"
+    symm = None
+    c = None
+    if world > 1 and args.gather == "p2p":
+        # Every rank's C lives in symmetric memory, so each rank holds an address for
+        # every other rank's C and the gemm epilogue can store its tiles into all of them.
+        try:
+            import torch.distributed._symmetric_memory as symm_mem
+
+            c = symm_mem.empty((size, size), dtype=torch.float32, device=torch.device("cuda", local_rank))
+            symm = symm_mem.rendezvous(c, dist.group.WORLD.group_name)
+            replicas = [int(p) for p in symm.buffer_ptrs]
+            c.zero_()
+            gather = "p2p"
+        except Exception as exc:  # no peer mapping on this box: use the collective instead
+            if rank == 0:
+                sys.stderr.write(f"bench.py: symmetric memory unavailable ({exc!r}); using NCCL all-gather\n")
+            c = None
+    if c is None:
+        c = torch.zeros(size, size, device="cuda")
+        gather = "nccl" if world > 1 else "none"
     a_shard = a[row_lo:row_hi]
     c_shard = c[row_lo:row_hi]
 
@@ -310,9 +333,13 @@ def gpu_arm(args) -> None:
             dist.barrier()
 
     def step():
-        ctx.gemm(a_shard, b, c_shard, rows, size, size, stream)
-        if world > 1:
-            sharding.gather_output(c, c_shard, dist)
+        if gather == "p2p":
+            ctx.gemm_allgather(a_shard, b, replicas, rank, rows, size, size, stream)
+            symm.barrier()  # all ranks' stores have landed before anyone reads C
+        else:
+            ctx.gemm(a_shard, b, c_shard, rows, size, size, stream)
+            if world > 1:
+                sharding.gather_output(c, c_shard, dist)
 
     for _ in range(max(args.warmup, 3)):
         step()
@@ -344,10 +371,15 @@ def gpu_arm(args) -> None:
     # ---- the dominant kernel alone, per-launch, on this rank's stream -------------------
     ctx.profile(True)
     for _ in range(args.steps):
-        ctx.gemm(a_shard, b, c_shard, rows, size, size, stream)
+        if gather == "p2p":
+            ctx.gemm_allgather(a_shard, b, replicas, rank, rows, size, size, stream)
+        else:
+            ctx.gemm(a_shard, b, c_shard, rows, size, size, stream)
     prof = ctx.profile_report()
     ctx.profile(False)
-    gemm_launches, gemm_ms = prof["gemm"]
+    if symm is not None:
+        symm.barrier()
+    gemm_launches, gemm_ms = prof["gemm_allgather" if gather == "p2p" else "gemm"]
     kernel_ms = gemm_ms / gemm_launches
     achieved = (flops / world) / (kernel_ms * 1e-3) / 1e12
     # 3xTF32 ceiling: the measured bf16 tensor rate, halved for TF32 (the spec
@@ -363,7 +395,7 @@ def gpu_arm(args) -> None:
         if traffic is not None and world > 1:
             traffic = traffic / world
     roofline = {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
-                "frac": achieved / peak, "traffic": traffic, "kernel": "gemm (tcgen05 3xTF32)",
+                "frac": achieved / peak, "traffic": traffic, "kernel": ("gemm_allgather" if gather == "p2p" else "gemm") + " (tcgen05 3xTF32)",
                 "kernel_ms": kernel_ms, "split_ms": (prof["gemm_split_a"][1] + prof["gemm_split_bt"][1]) / gemm_launches,
                 "peak_note": f"bf16_tflops_sustained of {peaks['source']} / 2 (TF32) / 3 (three products)"}
 
@@ -378,10 +410,13 @@ def gpu_arm(args) -> None:
         "scaling": "strong", "vs_baseline": None, "dtype": "f32 (3xTF32 tensor-core products, fp32 accumulate)",
         "data": "synthetic",
         "config": {"workload": f"gemm m=n=k={size} fp32 row-major, A,B ~ U[-1,1) seeded",
-                   "sharding": f"A and C by {world} M-row blocks, B replicated before timing; "
-                               "NCCL all-gather of C inside the timed step" if world > 1 else "single GPU",
+                   "sharding": (f"A and C by {world} M-row blocks, B replicated before timing; " + (
+                       "all-gather fused into the gemm epilogue (peer stores over NVLink into every rank's C) "
+                       "+ barrier, inside the timed step" if gather == "p2p" else
+                       "NCCL all-gather of C inside the timed step")) if world > 1 else "single GPU",
                    "l2": "inputs (2 x 256 MiB) and the 1 GiB operand-split scratch are larger than the 126 MB L2",
-                   "step": "gemm_split_a + gemm_split_bt + gemm" + (" + all_gather" if world > 1 else "")},
+                   "step": "gemm_split_a + gemm_split_bt + " + {"none": "gemm", "nccl": "gemm + nccl all_gather",
+                                                                 "p2p": "gemm_allgather + barrier"}[gather]},
         "roofline": roofline, "gpu_launches": int(launches),
         "sampled_max_err_over_rms": err,
     }

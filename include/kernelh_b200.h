@@ -113,6 +113,17 @@ int kh_gemm(kh_context *ctx, const float *a, const float *b, float *c, int64_t m
 int kh_attention(kh_context *ctx, const float *q, const float *k, const float *v, float *o,
                  int64_t batch, int64_t heads, int64_t seq, int64_t head_dim, void *stream);
 
+/* No counterpart in the reference (which is single-GPU). The M-row-sharded gemm
+ * for several GPUs of one box with the all-gather of the C shards fused into
+ * the kernel's epilogue: `a_shard` is this rank's m_shard x k rows of A, `b`
+ * the whole k x n B, and `c_replicas[i]` (i < world <= 8) the address, mapped
+ * on this device, of rank i's full (world*m_shard) x n C, this rank's own
+ * included. Every finished tile is stored to all replicas at row
+ * rank*m_shard (plain peer stores over NVLink; nothing is loaded from a peer).
+ * The caller runs a barrier across ranks after the kernel before reading C. */
+int kh_gemm_allgather(kh_context *ctx, const float *a_shard, const float *b, void *const *c_replicas,
+                      int world, int rank, int64_t m_shard, int64_t n, int64_t k, void *stream);
+
 /* No counterpart in the reference. The scan for callers that must not allocate
  * device memory (memory-pool owners, allocator-free plugin callbacks, fixed
  * audited budgets): same result as kh_scan, but the look-back scratch is a

@@ -77,6 +77,7 @@ def _load() -> C.CDLL:
     L.kh_softmax.argtypes = [vp, f32p, f32p, i64, i64, vp]
     L.kh_layernorm.argtypes = [vp, f32p, f32p, f32p, f32p, i64, i64, vp]
     L.kh_gemm.argtypes = [vp, f32p, f32p, f32p, i64, i64, i64, vp]
+    L.kh_gemm_allgather.argtypes = [vp, f32p, f32p, C.POINTER(vp), C.c_int, C.c_int, i64, i64, i64, vp]
     L.kh_attention.argtypes = [vp, f32p, f32p, f32p, f32p, i64, i64, i64, i64, vp]
     L.kh_malloc.argtypes = [vp, C.c_size_t, C.POINTER(vp)]
     L.kh_free.argtypes = [vp, vp]
@@ -216,6 +217,13 @@ class Context:
 
     def gemm(self, a, b, c, m, n, k, stream=None):
         _check(lib.kh_gemm(self._h, _ptr(a), _ptr(b), _ptr(c), m, n, k, stream))
+
+    def gemm_allgather(self, a_shard, b, c_replicas, rank, m_shard, n, k, stream=None):
+        """Sharded gemm whose epilogue stores every C tile into all ranks' full C
+        (`c_replicas`: addresses mapped on this device, this rank's own included)."""
+        arr = (C.c_void_p * len(c_replicas))(*[_ptr(p) for p in c_replicas])
+        _check(lib.kh_gemm_allgather(self._h, _ptr(a_shard), _ptr(b), arr, len(c_replicas), rank,
+                                     m_shard, n, k, stream))
 
     def attention(self, q, k, v, o, batch, heads, seq, head_dim, stream=None):
         _check(lib.kh_attention(self._h, _ptr(q), _ptr(k), _ptr(v), _ptr(o), batch, heads, seq,

@@ -196,6 +196,17 @@ int kh_gemm(kh_context *ctx, const float *a, const float *b, float *c, int64_t m
   return launch_named(ctx, "gemm", {{"m", m}, {"n", n}, {"k", k}},
                       {const_cast<float *>(a), const_cast<float *>(b), c}, stream);
 }
+int kh_gemm_allgather(kh_context *ctx, const float *a_shard, const float *b, void *const *c_replicas,
+                      int world, int rank, int64_t m_shard, int64_t n, int64_t k, void *stream) {
+  if (int rc = need_ctx(ctx)) return rc;
+  if (c_replicas == nullptr || world <= 0) return set_error(2, "kh_gemm_allgather: no C replicas given");
+  return guarded([&] {
+    if (auto r = ctx->exec->backend().make_current(); !r) return set_error(r.error());
+    std::vector<void *> reps(c_replicas, c_replicas + world);
+    auto r = kh::run_gemm_allgather(*ctx->exec, a_shard, b, reps, rank, m_shard, n, k, stream);
+    return r ? 0 : set_error(r.error());
+  });
+}
 int kh_attention(kh_context *ctx, const float *q, const float *k, const float *v, float *o,
                  int64_t batch, int64_t heads, int64_t seq, int64_t head_dim, void *stream) {
   return launch_named(ctx, "attention",

@@ -221,7 +221,7 @@ KernelPlan plan_gemm(const ShapeMap &shape, const DeviceLimits &l) {
   g.entry = "gemm";
   g.block = {320, 1, 1};
   const int64_t tiles = ((m + kGemmBM - 1) / kGemmBM) * ((n + kGemmBN - 1) / kGemmBN);
-  g.grid = {static_cast<unsigned>(tiles), 1, 1};
+  g.grid = {static_cast<unsigned>(std::min<int64_t>(tiles, sms)), 1, 1}; // persistent: one CTA per SM
   g.dynamic_smem = kGemmStages * kGemmStageBytes + 1024;
   g.param_count = 21 + 4 + 2;
   g.tmem_columns = 512;
@@ -231,8 +231,16 @@ KernelPlan plan_gemm(const ShapeMap &shape, const DeviceLimits &l) {
   return p;
 }
 
-Result<void> run_gemm(Executor &ex, const KernelPlan &p, const std::vector<void *> &b,
-                      StreamHandle stream) {
+// Destinations of gemm_allgather's fused all-gather; layout shared with the kernel.
+struct GatherTargets {
+  float *base[8];
+  int count;
+  int self;
+  int64_t row_offset;
+};
+
+Result<void> launch_gemm(Executor &ex, const KernelPlan &p, const std::vector<void *> &b,
+                         StreamHandle stream, const GatherTargets *gather) {
   const int64_t m = p.tensors[0].shape[0], k = p.tensors[0].shape[1], n = p.tensors[1].shape[1];
   const int64_t kp = (k + kGemmBK - 1) / kGemmBK * kGemmBK;
   auto ws = ex.workspace(p.workspace_bytes);
@@ -246,7 +254,7 @@ Result<void> run_gemm(Executor &ex, const KernelPlan &p, const std::vector<void 
   if (!f_sa) return std::unexpected(f_sa.error());
   auto f_sb = ex.function("gemm", "gemm_split_bt");
   if (!f_sb) return std::unexpected(f_sb.error());
-  auto f_g = ex.function("gemm", "gemm");
+  auto f_g = ex.function("gemm", gather ? "gemm_allgather" : "gemm");
   if (!f_g) return std::unexpected(f_g.error());
 
   {
@@ -289,17 +297,53 @@ Result<void> run_gemm(Executor &ex, const KernelPlan &p, const std::vector<void 
   LaunchArgs args;
   args.add_memref(b[0], {m, k});
   args.add_memref(b[1], {k, n});
-  args.add_memref(b[2], {m, n});
+  if (!gather) args.add_memref(b[2], {m, n});
   args.add_tensor_map(*t_ah);
   args.add_tensor_map(*t_al);
   args.add_tensor_map(*t_bh);
   args.add_tensor_map(*t_bl);
   args.add_scalar<int64_t>(kp / kGemmBK);
   args.add_scalar<uint64_t>(reinterpret_cast<uint64_t>(ex.status_word()));
-  return ex.launch(*f_g, p.steps[2], args, stream);
+  if (gather) args.add_struct_bytes(gather, sizeof *gather);
+  LaunchStep step = p.steps[2];
+  if (gather) step.entry = "gemm_allgather";
+  return ex.launch(*f_g, step, args, stream);
+}
+
+Result<void> run_gemm(Executor &ex, const KernelPlan &p, const std::vector<void *> &b,
+                      StreamHandle stream) {
+  return launch_gemm(ex, p, b, stream, nullptr);
 }
 
 } // namespace
+
+// The M-row-sharded product with the all-gather fused into the epilogue:
+// `a_shard` is this rank's (m_shard x k) rows of A, `b` the whole B, and
+// `replicas[i]` the address, valid on this device, of rank i's full C.
+Result<void> run_gemm_allgather(Executor &ex, const void *a_shard, const void *b,
+                                const std::vector<void *> &replicas, int rank, int64_t m_shard,
+                                int64_t n, int64_t k, StreamHandle stream) {
+  if (replicas.empty() || replicas.size() > 8)
+    return fail(2, "gemm_allgather: between 1 and 8 C replicas are supported, got " +
+                       std::to_string(replicas.size()));
+  if (rank < 0 || rank >= static_cast<int>(replicas.size()))
+    return fail(2, "gemm_allgather: rank " + std::to_string(rank) + " is outside the replica list");
+  KernelPlan plan;
+  try {
+    plan = plan_gemm({{"m", m_shard}, {"n", n}, {"k", k}}, ex.limits());
+  } catch (const std::exception &e) {
+    return fail(2, e.what());
+  }
+  GatherTargets t{};
+  t.count = static_cast<int>(replicas.size());
+  for (int i = 0; i < t.count; ++i) {
+    if (replicas[i] == nullptr) return fail(2, "gemm_allgather: null C replica pointer");
+    t.base[i] = static_cast<float *>(replicas[i]);
+  }
+  t.self = rank;
+  t.row_offset = static_cast<int64_t>(rank) * m_shard;
+  return launch_gemm(ex, plan, {const_cast<void *>(a_shard), const_cast<void *>(b), nullptr}, stream, &t);
+}
 
 void register_attention_kernel(); // attention_kernel.cpp
 

@@ -86,4 +86,9 @@ private:
   StreamHandle host_stream_ = nullptr;
 };
 
+// builtin_kernels.cpp
+Result<void> run_gemm_allgather(Executor &ex, const void *a_shard, const void *b,
+                                const std::vector<void *> &replicas, int rank, int64_t m_shard,
+                                int64_t n, int64_t k, StreamHandle stream);
+
 } // namespace kh

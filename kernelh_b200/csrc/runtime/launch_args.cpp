@@ -31,6 +31,12 @@ void LaunchArgs::add_tensor_map(const TensorMapBytes &map) {
   maps_.push_back(map);
 }
 
+void LaunchArgs::add_struct_bytes(const void *value, size_t byte_size) {
+  TensorMapBytes blob{};
+  std::memcpy(&blob, value, byte_size > sizeof blob ? sizeof blob : byte_size);
+  add_tensor_map(blob);
+}
+
 void **LaunchArgs::params() {
   params_.resize(order_.size());
   for (size_t i = 0; i < order_.size(); ++i)

@@ -24,6 +24,8 @@ public:
   void add_scalar_bytes(const void *value, size_t byte_size);
   template <typename T> void add_scalar(T value) { add_scalar_bytes(&value, sizeof(T)); }
   void add_tensor_map(const TensorMapBytes &map);
+  // A by-value struct parameter of up to 128 bytes (stored 64-byte aligned).
+  void add_struct_bytes(const void *value, size_t byte_size);
 
   // Number of kernel parameters: 8-byte slots plus tensor maps.
   size_t param_count() const { return order_.size(); }

@@ -254,6 +254,26 @@ def test_gemm_8192_sampled_rows_and_scaling_property(ctx, oracle):
     assert np.array_equal(c2, c * 2)
 
 
+def test_gemm_allgather_two_shards_fill_every_replica(ctx, oracle):
+    """The fused gemm + all-gather on one GPU: the two ranks' launches run one
+    after the other and each stores its row shard into both replicas of C."""
+    m, n, k = 512, 768, 320
+    a = oracle.uniform((m, k), oracle.BASE_SEED, -1, 1)
+    b = oracle.uniform((k, n), oracle.BASE_SEED + 1, -1, 1)
+    da, db = dev(a), dev(b)
+    replicas = [torch.full((m, n), float("nan"), device="cuda") for _ in range(2)]
+    stream = torch.cuda.current_stream().cuda_stream
+    for rank in range(2):
+        ctx.gemm_allgather(da[rank * 256:(rank + 1) * 256], db, replicas, rank, 256, n, k, stream)
+    ctx.synchronize(stream)
+    plain = run(ctx, "gemm", f"m={m},n={n},k={k}", [da, db], (m, n))
+    for r in replicas:
+        assert np.array_equal(r.cpu().numpy(), plain)  # same tiles, same arithmetic
+    assert oracle.compare(plain, oracle.gemm_ref(a, b)).rel_frobenius <= 1e-5
+    with pytest.raises(kh.KernelhError):
+        ctx.gemm_allgather(da, db, replicas, 2, 256, n, k, stream)
+
+
 # --------------------------------------------------------------------------- attention
 def attention_inputs(oracle, b, h, s):
     return (oracle.lcg((b, h, s, 64), 0x313A171B), oracle.lcg((b, h, s, 64), 0x51AC0D3E),
