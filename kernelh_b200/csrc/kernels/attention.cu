@@ -24,8 +24,9 @@
 //      hi/lo pairs into scratch.
 //  attention  warp 0 feeds TMA (Q once; a 2-stage ring of K/V tiles, 64 KiB
 //      per stage); warp 1 issues the MMAs (S of tile j+1 is issued before PV
-//      of tile j so the tensor core works while softmax runs); warps 2-5 (one
-//      thread per query row) do the online softmax and own the output.
+//      of tile j so the tensor core works while softmax runs); warps 2-9 (two
+//      threads per query row, 32 key columns each) do the online softmax and
+//      own the output.
 //
 // Tensor-bound: 4 b h s^2 d useful flops; 3xTF32 puts the ceiling at one third
 // of the TF32 tensor rate.
@@ -37,7 +38,8 @@ constexpr int kHeadDim = 64;
 constexpr int kBQ = 128;  // query rows per CTA
 constexpr int kBKV = 64;  // keys per tile
 constexpr int kStages = 2;
-constexpr int kThreads = 192;
+constexpr int kSoftmaxThreads = 256; // two per query row
+constexpr int kThreads = 64 + kSoftmaxThreads;
 constexpr int kChunkRowsBytes = 128; // one swizzle row: 32 fp32
 constexpr int kQChunkBytes = kBQ * kChunkRowsBytes;   // 16 KiB: 128 rows x 32 fp32
 constexpr int kKVChunkBytes = kBKV * kChunkRowsBytes; // 8 KiB: 64 rows x 32 fp32
@@ -146,10 +148,11 @@ attention(KH_MEMREF4(const float, q), KH_MEMREF4(const float, k), KH_MEMREF4(con
   (void)o_size0; (void)o_size1; (void)o_size2; (void)o_size3; (void)o_stride0; (void)o_stride1;
   (void)o_stride2; (void)o_stride3; (void)o_alloc;
   extern __shared__ uint8_t smem_raw[];
-  // barriers: q_full, kv_full[2], kv_empty[2], s_full[2], p_ready, pv_full
-  __shared__ __align__(8) uint64_t bars[9];
+  // barriers: q_full, kv_full[2], kv_empty[2], s_full[2], p_ready, pv_full, row_exchange
+  __shared__ __align__(8) uint64_t bars[10];
   __shared__ uint32_t s_tmem_base;
   __shared__ int s_abort;
+  __shared__ float s_rowmax[2][2][kBQ]; // [tile parity][column half][row]
 
   const int64_t seq = q_size2;
   const int64_t q_tiles = (seq + kBQ - 1) / kBQ;
@@ -167,6 +170,7 @@ attention(KH_MEMREF4(const float, q), KH_MEMREF4(const float, k), KH_MEMREF4(con
   const uint32_t bar_s_full = khd::smem_u32(&bars[5]);
   const uint32_t bar_p_ready = khd::smem_u32(&bars[7]);
   const uint32_t bar_pv_full = khd::smem_u32(&bars[8]);
+  const uint32_t bar_exchange = khd::smem_u32(&bars[9]);
 
   if (threadIdx.x == 0) {
     s_abort = 0;
@@ -176,8 +180,9 @@ attention(KH_MEMREF4(const float, q), KH_MEMREF4(const float, k), KH_MEMREF4(con
       khd::mbar_init(bar_kv_empty + 8 * s, 1);
       khd::mbar_init(bar_s_full + 8 * s, 1);
     }
-    khd::mbar_init(bar_p_ready, kBQ); // one arrival per softmax thread
+    khd::mbar_init(bar_p_ready, kSoftmaxThreads); // one arrival per softmax thread
     khd::mbar_init(bar_pv_full, 1);
+    khd::mbar_init(bar_exchange, kSoftmaxThreads);
     khd::mbar_fence_init();
     khd::tma_prefetch_descriptor(&tm_q_hi);
     khd::tma_prefetch_descriptor(&tm_q_lo);
@@ -287,14 +292,18 @@ attention(KH_MEMREF4(const float, q), KH_MEMREF4(const float, k), KH_MEMREF4(con
       }
     }
   } else {
-    // ---- softmax + output: one thread per query row ----------------------------------
+    // ---- softmax + output: two threads per query row. Warps 2-5 take key
+    //      columns 0-31 of every tile (and output columns 0-31), warps 6-9 the
+    //      other half; a warp may only touch tensor-memory lanes 32*(warp%4).. ----------
+    const int ew = warp - 2;
     const int quad = warp & 3;
+    const int half = ew >> 2;
     const uint32_t lane_base = static_cast<uint32_t>(quad * 32) << 16;
     const int row_in_tile = quad * 32 + lane;
-    float acc[kHeadDim];
+    float acc[32];
 #pragma unroll
-    for (int i = 0; i < kHeadDim; ++i) acc[i] = 0.f;
-    float m = -INFINITY, l = 0.f;
+    for (int i = 0; i < 32; ++i) acc[i] = 0.f;
+    float m = -INFINITY, l = 0.f; // l is this thread's half of the row sum
     bool ok = true;
     constexpr float kLog2e = 1.4426950408889634f;
 
@@ -303,26 +312,30 @@ attention(KH_MEMREF4(const float, q), KH_MEMREF4(const float, k), KH_MEMREF4(con
                           status, khd::kStatusMmaWaitTimeout, static_cast<uint32_t>(j));
       if (!ok) break;
       khd::tc_fence_after_sync();
-      uint32_t s0[32], s1[32];
-      const uint32_t s_addr = tmem_base + lane_base + ((j & 1) ? kColS1 : kColS0);
-      khd::tmem_ld_32x32(s_addr, s0);
-      khd::tmem_ld_32x32(s_addr + 32, s1);
+      uint32_t sv[32];
+      khd::tmem_ld_32x32(tmem_base + lane_base + ((j & 1) ? kColS1 : kColS0) + 32 * half, sv);
       khd::tmem_ld_wait();
       float mx = -INFINITY;
 #pragma unroll
-      for (int i = 0; i < 32; ++i)
-        mx = fmaxf(mx, fmaxf(__uint_as_float(s0[i]), __uint_as_float(s1[i])));
+      for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(sv[i]));
+      // the row maximum needs the partner thread's half: exchange through shared
+      // memory (double buffered by tile parity). The meeting point is an
+      // mbarrier, not bar.sync, so that it is a bounded wait like all others.
+      s_rowmax[j & 1][half][row_in_tile] = mx;
+      khd::mbar_arrive(bar_exchange);
+      ok = khd::mbar_wait(bar_exchange, static_cast<uint32_t>(j & 1), &s_abort, status,
+                          khd::kStatusEpilogueWaitTimeout, 4000u + static_cast<uint32_t>(j));
+      if (!ok) break;
+      mx = fmaxf(mx, s_rowmax[j & 1][half ^ 1][row_in_tile]);
       const float m_new = fmaxf(m, mx);
       const float alpha = exp2f((m - m_new) * kLog2e); // m = -inf on the first tile gives 0
       const float mb = m_new * kLog2e;
       float sum = 0.f;
 #pragma unroll
       for (int i = 0; i < 32; ++i) {
-        const float p0 = exp2f(fmaf(__uint_as_float(s0[i]), kLog2e, -mb));
-        const float p1 = exp2f(fmaf(__uint_as_float(s1[i]), kLog2e, -mb));
-        s0[i] = __float_as_uint(p0);
-        s1[i] = __float_as_uint(p1);
-        sum += p0 + p1;
+        const float p = exp2f(fmaf(__uint_as_float(sv[i]), kLog2e, -mb));
+        sv[i] = __float_as_uint(p);
+        sum += p;
       }
       l = l * alpha + sum;
       m = m_new;
@@ -336,28 +349,21 @@ attention(KH_MEMREF4(const float, q), KH_MEMREF4(const float, k), KH_MEMREF4(con
         if (!ok) break;
         khd::tc_fence_after_sync();
         uint32_t t[32];
+        khd::tmem_ld_32x32(tmem_base + lane_base + kColPV + 32 * half, t);
+        khd::tmem_ld_wait();
 #pragma unroll
-        for (int h = 0; h < 2; ++h) {
-          khd::tmem_ld_32x32(tmem_base + lane_base + kColPV + 32 * h, t);
-          khd::tmem_ld_wait();
-#pragma unroll
-          for (int i = 0; i < 32; ++i) acc[32 * h + i] = (acc[32 * h + i] + __uint_as_float(t[i])) * alpha;
-        }
+        for (int i = 0; i < 32; ++i) acc[i] = (acc[i] + __uint_as_float(t[i])) * alpha;
       }
       // P -> tensor memory as hi / lo
       {
         uint32_t hi[32];
 #pragma unroll
-        for (int h = 0; h < 2; ++h) {
-          uint32_t(&src)[32] = h ? s1 : s0;
+        for (int i = 0; i < 32; ++i) hi[i] = __float_as_uint(tf32_hi(__uint_as_float(sv[i])));
+        tmem_st_32x32(tmem_base + lane_base + kColPHi + 32 * half, hi);
 #pragma unroll
-          for (int i = 0; i < 32; ++i) hi[i] = __float_as_uint(tf32_hi(__uint_as_float(src[i])));
-          tmem_st_32x32(tmem_base + lane_base + kColPHi + 32 * h, hi);
-#pragma unroll
-          for (int i = 0; i < 32; ++i)
-            hi[i] = __float_as_uint(__uint_as_float(src[i]) - __uint_as_float(hi[i]));
-          tmem_st_32x32(tmem_base + lane_base + kColPLo + 32 * h, hi);
-        }
+        for (int i = 0; i < 32; ++i)
+          hi[i] = __float_as_uint(__uint_as_float(sv[i]) - __uint_as_float(hi[i]));
+        tmem_st_32x32(tmem_base + lane_base + kColPLo + 32 * half, hi);
         tmem_st_wait();
       }
       khd::tc_fence_before_sync();
@@ -366,25 +372,27 @@ attention(KH_MEMREF4(const float, q), KH_MEMREF4(const float, k), KH_MEMREF4(con
     if (ok && num_kv > 0) {
       ok = khd::mbar_wait(bar_pv_full, static_cast<uint32_t>((num_kv - 1) & 1), &s_abort, status,
                           khd::kStatusMmaWaitTimeout, 3000u);
+      // the two halves of a row sum meet here
+      s_rowmax[num_kv & 1][half][row_in_tile] = l;
+      khd::mbar_arrive(bar_exchange);
+      ok = ok && khd::mbar_wait(bar_exchange, static_cast<uint32_t>(num_kv & 1), &s_abort, status,
+                                khd::kStatusEpilogueWaitTimeout, 5000u);
       if (ok) {
         khd::tc_fence_after_sync();
-        const float inv = 1.0f / l;
+        const float inv = 1.0f / (l + s_rowmax[num_kv & 1][half ^ 1][row_in_tile]);
         const int64_t row = static_cast<int64_t>(q0) + row_in_tile;
-        float *orow = out + (bh * seq + row) * kHeadDim;
+        float *orow = out + (bh * seq + row) * kHeadDim + 32 * half;
         uint32_t t[32];
+        khd::tmem_ld_32x32(tmem_base + lane_base + kColPV + 32 * half, t);
+        khd::tmem_ld_wait();
+        if (row < seq) {
 #pragma unroll
-        for (int h = 0; h < 2; ++h) {
-          khd::tmem_ld_32x32(tmem_base + lane_base + kColPV + 32 * h, t);
-          khd::tmem_ld_wait();
-          if (row < seq) {
-#pragma unroll
-            for (int i = 0; i < 8; ++i)
-              __stcs(reinterpret_cast<float4 *>(orow + 32 * h) + i,
-                     make_float4((acc[32 * h + 4 * i + 0] + __uint_as_float(t[4 * i + 0])) * inv,
-                                 (acc[32 * h + 4 * i + 1] + __uint_as_float(t[4 * i + 1])) * inv,
-                                 (acc[32 * h + 4 * i + 2] + __uint_as_float(t[4 * i + 2])) * inv,
-                                 (acc[32 * h + 4 * i + 3] + __uint_as_float(t[4 * i + 3])) * inv));
-          }
+          for (int i = 0; i < 8; ++i)
+            __stcs(reinterpret_cast<float4 *>(orow) + i,
+                   make_float4((acc[4 * i + 0] + __uint_as_float(t[4 * i + 0])) * inv,
+                               (acc[4 * i + 1] + __uint_as_float(t[4 * i + 1])) * inv,
+                               (acc[4 * i + 2] + __uint_as_float(t[4 * i + 2])) * inv,
+                               (acc[4 * i + 3] + __uint_as_float(t[4 * i + 3])) * inv));
         }
       }
     }

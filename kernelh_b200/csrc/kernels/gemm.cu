@@ -191,8 +191,8 @@ __device__ __forceinline__ void gemm_body(int64_t m, int64_t n, float *__restric
                                           const khd::TensorMap &tm_b_lo, int64_t k_blocks, uint32_t *status,
                                           const GatherTargets *targets) {
   extern __shared__ uint8_t smem_raw[];
-  // full[kStages], empty[kStages], acc_full[2], acc_empty[2]
-  __shared__ __align__(8) uint64_t bars[2 * kStages + 4];
+  // full[kStages], empty[kStages], acc_full[2], acc_empty[2], tile_stored
+  __shared__ __align__(8) uint64_t bars[2 * kStages + 5];
   __shared__ uint32_t s_tmem_base;
   __shared__ int s_abort;
 
@@ -204,6 +204,7 @@ __device__ __forceinline__ void gemm_body(int64_t m, int64_t n, float *__restric
   const uint32_t empty0 = khd::smem_u32(&bars[kStages]);
   const uint32_t acc_full0 = khd::smem_u32(&bars[2 * kStages]);
   const uint32_t acc_empty0 = khd::smem_u32(&bars[2 * kStages + 2]);
+  const uint32_t tile_stored = khd::smem_u32(&bars[2 * kStages + 4]);
 
   const int64_t tiles_m = (m + kBM - 1) / kBM, tiles_n = (n + kBN - 1) / kBN;
   const int64_t num_tiles = tiles_m * tiles_n;
@@ -219,6 +220,7 @@ __device__ __forceinline__ void gemm_body(int64_t m, int64_t n, float *__restric
       khd::mbar_init(acc_full0 + 8 * i, 1);
       khd::mbar_init(acc_empty0 + 8 * i, kEpilogueWarps); // one arrival per epilogue warp
     }
+    khd::mbar_init(tile_stored, kEpilogueWarps * 32);
     khd::mbar_fence_init();
     khd::tma_prefetch_descriptor(&tm_a_hi);
     khd::tma_prefetch_descriptor(&tm_a_lo);
@@ -308,7 +310,7 @@ __device__ __forceinline__ void gemm_body(int64_t m, int64_t n, float *__restric
     const int quad = warp & 3;
     const int half = ew >> 2;
     const uint32_t lane_base = static_cast<uint32_t>(quad * 32) << 16;
-    uint32_t g_chunk = 0;
+    uint32_t g_chunk = 0, stored_phase = 0;
     PendingPush pending{0, 0, 32};
     bool ok = true;
     for (int64_t tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
@@ -367,9 +369,13 @@ __device__ __forceinline__ void gemm_body(int64_t m, int64_t n, float *__restric
         }
       }
       if (kGather) {
-        // the tile is read back by other warps of this CTA when it is pushed
+        // The tile is read back by other warps of this CTA when it is pushed: all
+        // epilogue threads meet on an mbarrier (a bounded wait, unlike bar.sync).
         __threadfence_block();
-        asm volatile("bar.sync 1, %0;" ::"r"(kEpilogueWarps * 32) : "memory");
+        khd::mbar_arrive(tile_stored);
+        ok = khd::mbar_wait(tile_stored, stored_phase, &s_abort, status, khd::kStatusEpilogueWaitTimeout,
+                            9000u);
+        stored_phase ^= 1u;
         pending = PendingPush{tc.m0, tc.n0, 0};
       }
     }

@@ -46,7 +46,7 @@ KernelPlan plan_attention(const ShapeMap &shape, const DeviceLimits &l) {
   split.param_count = 33 + 6;
   LaunchStep main;
   main.entry = "attention";
-  main.block = {192, 1, 1};
+  main.block = {320, 1, 1};
   main.grid = {static_cast<unsigned>(b * h * ((s + kBQ - 1) / kBQ)), 1, 1};
   main.dynamic_smem = kAttnSmem;
   main.param_count = 44 + 6 + 1;
