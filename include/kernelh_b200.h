@@ -90,6 +90,20 @@ int kh_run_host(kh_context *ctx, const char *kernel, const char *shape, void *co
 /* Waits for `stream` and reports a device-side wait that ran out (1001). */
 int kh_synchronize(kh_context *ctx, void *stream);
 
+/* The reference runtime's own launch sequence, for callers that keep choosing
+ * launch geometry themselves: GpuModule::load(image) + get_function(entry) +
+ * KernelLaunch(...).grid().block().shared_mem_bytes().memref_arg()...launch()
+ * (include/kernelh/runtime/gpu_module.hpp, kernel_launch.hpp; lib/runtime/
+ * kernel_launch.cpp:100-132). `image` is a code object (e.g. from
+ * kh_kernel_image); buffers are packed as memref descriptors (ptrs[i] with
+ * ranks[i] dims taken from `shapes`). The launch is verified against the device
+ * limits first and refused (code 1, "KernelLaunch::launch refused: ..." with
+ * every violation) when it cannot run; a bad image gives the driver's error. */
+int kh_module_launch(kh_context *ctx, const void *image, size_t image_size, const char *entry,
+                     const uint32_t grid[3], const uint32_t block[3], size_t dynamic_smem,
+                     const uint64_t *ptrs, const int64_t *shapes, const int *ranks, int n_memrefs,
+                     void *stream);
+
 /* Per-launch device timing (the reference times launches with GPU events,
  * include/kernelh/runtime/event_timer.hpp): while enabled, every kernel launch
  * of this context is bracketed by events on its stream. kh_profile_report

@@ -65,6 +65,9 @@ def _load() -> C.CDLL:
     L.kh_launch.argtypes = [vp, C.c_char_p, C.c_char_p, C.POINTER(vp), C.c_int, vp]
     L.kh_run_host.argtypes = [vp, C.c_char_p, C.c_char_p, C.POINTER(vp), C.c_int]
     L.kh_synchronize.argtypes = [vp, vp]
+    L.kh_module_launch.argtypes = [vp, C.c_char_p, C.c_size_t, C.c_char_p, C.POINTER(C.c_uint32),
+                                   C.POINTER(C.c_uint32), C.c_size_t, C.POINTER(C.c_uint64),
+                                   C.POINTER(C.c_int64), C.POINTER(C.c_int), C.c_int, vp]
     L.kh_profile_enable.argtypes = [vp, C.c_int]
     L.kh_profile_report.argtypes = [vp, C.c_char_p, C.c_int]
     L.kh_launch_count.argtypes = [vp, C.POINTER(C.c_uint64)]
@@ -170,6 +173,18 @@ class Context:
 
     def synchronize(self, stream: int | None = None) -> None:
         _check(lib.kh_synchronize(self._h, stream))
+
+    def module_launch(self, image: bytes, entry: str, grid, block, buffers, shapes,
+                      dynamic_smem: int = 0, stream: int | None = None) -> None:
+        """The reference runtime's sequence with caller-chosen geometry: load the
+        code object, look up `entry`, pack `buffers` as memref descriptors of
+        `shapes`, verify the launch against the device limits, launch, wait."""
+        flat = [d for s_ in shapes for d in s_]
+        _check(lib.kh_module_launch(
+            self._h, image, len(image), entry.encode(), (C.c_uint32 * 3)(*grid), (C.c_uint32 * 3)(*block),
+            dynamic_smem, (C.c_uint64 * len(buffers))(*[_ptr(b) for b in buffers]),
+            (C.c_int64 * max(len(flat), 1))(*flat), (C.c_int * len(shapes))(*[len(s_) for s_ in shapes]),
+            len(buffers), stream))
 
     def profile(self, on: bool) -> None:
         _check(lib.kh_profile_enable(self._h, int(on)))

@@ -147,6 +147,35 @@ int kh_synchronize(kh_context *ctx, void *stream) {
   return r ? 0 : set_error(r.error());
 }
 
+int kh_module_launch(kh_context *ctx, const void *image, size_t image_size, const char *entry,
+                     const uint32_t grid[3], const uint32_t block[3], size_t dynamic_smem,
+                     const uint64_t *ptrs, const int64_t *shapes, const int *ranks, int n_memrefs,
+                     void *stream) {
+  if (int rc = need_ctx(ctx)) return rc;
+  if (entry == nullptr || grid == nullptr || block == nullptr)
+    return set_error(2, "kh_module_launch: null entry, grid or block");
+  return guarded([&] {
+    auto backend = ctx->exec->backend_ptr();
+    if (auto r = backend->make_current(); !r) return set_error(r.error());
+    auto module = kh::GpuModule::load(backend, image, image_size);
+    if (!module) return set_error(module.error());
+    auto fn = module->get_function(entry);
+    if (!fn) return set_error(fn.error());
+    kh::KernelLaunch launch(backend);
+    launch.grid(grid[0], grid[1], grid[2]).block(block[0], block[1], block[2]).shared_mem_bytes(dynamic_smem).stream(stream);
+    const int64_t *sp = shapes;
+    for (int i = 0; i < n_memrefs; ++i) {
+      launch.memref_arg(reinterpret_cast<const void *>(ptrs[i]), std::vector<int64_t>(sp, sp + ranks[i]));
+      sp += ranks[i];
+    }
+    auto r = launch.launch(*fn);
+    if (!r) return set_error(r.error());
+    // the module is unloaded when this scope ends: wait for the kernel first
+    if (auto s = backend->stream_synchronize(stream); !s) return set_error(s.error());
+    return 0;
+  });
+}
+
 int kh_profile_enable(kh_context *ctx, int on) {
   if (int rc = need_ctx(ctx)) return rc;
   ctx->exec->profile_enable(on != 0);

@@ -22,11 +22,14 @@
 // Two launches:
 //  attention_split  writes Q/8 (the 1/sqrt(64) scale is exact), K and V^T as
 //      hi/lo pairs into scratch.
-//  attention  warp 0 feeds TMA (Q once; a 2-stage ring of K/V tiles, 64 KiB
-//      per stage); warp 1 issues the MMAs (S of tile j+1 is issued before PV
-//      of tile j so the tensor core works while softmax runs); warps 2-9 (two
-//      threads per query row, 32 key columns each) do the online softmax and
-//      own the output.
+//  attention  warp 0 feeds TMA (Q once; separate 2-deep rings of K and V^T
+//      tiles, 32 KiB each, so that K of tile j+2 can load as soon as S_j has
+//      run); warp 1 issues the MMAs (S of tile j+1 is issued before PV of tile
+//      j so the tensor core works while softmax runs); warps 2-5 and 6-9 are
+//      two softmax groups (one thread per query row each) that take the even
+//      and the odd tiles with their own running max, sum and output row and
+//      are merged at the end, so two tiles are in the softmax stage at once.
+//      Scores, P and PV are double buffered in tensor memory, one set per group.
 //
 // Tensor-bound: 4 b h s^2 d useful flops; 3xTF32 puts the ceiling at one third
 // of the TF32 tensor rate.
@@ -38,21 +41,30 @@ constexpr int kHeadDim = 64;
 constexpr int kBQ = 128;  // query rows per CTA
 constexpr int kBKV = 64;  // keys per tile
 constexpr int kStages = 2;
-constexpr int kSoftmaxThreads = 256; // two per query row
+constexpr int kSoftmaxThreads = 256; // two groups of one thread per query row
 constexpr int kThreads = 64 + kSoftmaxThreads;
 constexpr int kChunkRowsBytes = 128; // one swizzle row: 32 fp32
 constexpr int kQChunkBytes = kBQ * kChunkRowsBytes;   // 16 KiB: 128 rows x 32 fp32
 constexpr int kKVChunkBytes = kBKV * kChunkRowsBytes; // 8 KiB: 64 rows x 32 fp32
 constexpr int kQBytes = 4 * kQChunkBytes;             // hi c0,c1 + lo c0,c1 = 64 KiB
-constexpr int kStageBytes = 8 * kKVChunkBytes;        // K hi/lo + V^T hi/lo, 2 chunks each = 64 KiB
-// tensor-memory columns
-constexpr uint32_t kColS0 = 0, kColS1 = 64, kColPHi = 128, kColPLo = 192, kColPV = 256;
+constexpr int kHalfStageBytes = 4 * kKVChunkBytes;    // one K (or V^T) tile: hi c0,c1 + lo c0,c1 = 32 KiB
+// tensor-memory columns: two score buffers, two P buffers (64 hi + 64 lo columns
+// each), two PV buffers
+constexpr uint32_t kColS0 = 0, kColS1 = 64, kColP0 = 128, kColP1 = 256, kColPV0 = 384, kColPV1 = 448;
 constexpr uint32_t kTmemCols = 512;
 
 __device__ __forceinline__ float tf32_hi(float x) {
   uint32_t u = __float_as_uint(x);
   u = (u + 0x1000u) & 0xFFFFE000u;
   return __uint_as_float(u);
+}
+
+// 2^x by the special-function unit (2 ulp, flushes denormals): the arguments
+// here are <= 0 and the results feed a sum of at least 1.
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
 }
 
 // D[tmem] (+)= A[tmem] * B[smem]
@@ -64,17 +76,22 @@ __device__ __forceinline__ void umma_tf32_ts(uint32_t tmem_d, uint32_t tmem_a, u
                : "memory");
 }
 
-__device__ __forceinline__ void tmem_st_32x32(uint32_t taddr, const uint32_t (&r)[32]) {
-  asm volatile(
-      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
-      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
-      "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};" ::"r"(taddr),
-      "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
-      "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]),
-      "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]),
-      "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]),
-      "r"(r[30]), "r"(r[31])
-      : "memory");
+// 16-column variants (smaller register footprint for temporaries)
+__device__ __forceinline__ void tmem_ld_32x16(uint32_t taddr, uint32_t (&r)[16]) {
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+               "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+                 "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
+                 "=r"(r[14]), "=r"(r[15])
+               : "r"(taddr)
+               : "memory");
+}
+__device__ __forceinline__ void tmem_st_32x16(uint32_t taddr, const uint32_t (&r)[16]) {
+  asm volatile("tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+               "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};" ::"r"(taddr),
+               "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+               "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+               : "memory");
 }
 __device__ __forceinline__ void tmem_st_wait() {
   asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
@@ -148,11 +165,10 @@ attention(KH_MEMREF4(const float, q), KH_MEMREF4(const float, k), KH_MEMREF4(con
   (void)o_size0; (void)o_size1; (void)o_size2; (void)o_size3; (void)o_stride0; (void)o_stride1;
   (void)o_stride2; (void)o_stride3; (void)o_alloc;
   extern __shared__ uint8_t smem_raw[];
-  // barriers: q_full, kv_full[2], kv_empty[2], s_full[2], p_ready, pv_full, row_exchange
-  __shared__ __align__(8) uint64_t bars[10];
+  // q_full, k_full[2], k_empty[2], v_full[2], v_empty[2], s_full[2], p_ready[2], pv_full[2], exchange
+  __shared__ __align__(8) uint64_t bars[16];
   __shared__ uint32_t s_tmem_base;
   __shared__ int s_abort;
-  __shared__ float s_rowmax[2][2][kBQ]; // [tile parity][column half][row]
 
   const int64_t seq = q_size2;
   const int64_t q_tiles = (seq + kBQ - 1) / kBQ;
@@ -163,25 +179,30 @@ attention(KH_MEMREF4(const float, q), KH_MEMREF4(const float, k), KH_MEMREF4(con
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
   const uint32_t smem_q = (khd::smem_u32(smem_raw) + 1023u) & ~1023u;
-  const uint32_t smem_kv = smem_q + kQBytes;
+  const uint32_t smem_k = smem_q + kQBytes;                 // 2 stages of K hi c0,c1 / lo c0,c1
+  const uint32_t smem_v = smem_k + kStages * kHalfStageBytes; // 2 stages of V^T hi c0,c1 / lo c0,c1
   const uint32_t bar_q = khd::smem_u32(&bars[0]);
-  const uint32_t bar_kv_full = khd::smem_u32(&bars[1]);
-  const uint32_t bar_kv_empty = khd::smem_u32(&bars[3]);
-  const uint32_t bar_s_full = khd::smem_u32(&bars[5]);
-  const uint32_t bar_p_ready = khd::smem_u32(&bars[7]);
-  const uint32_t bar_pv_full = khd::smem_u32(&bars[8]);
-  const uint32_t bar_exchange = khd::smem_u32(&bars[9]);
+  const uint32_t bar_k_full = khd::smem_u32(&bars[1]);
+  const uint32_t bar_k_empty = khd::smem_u32(&bars[3]);
+  const uint32_t bar_v_full = khd::smem_u32(&bars[5]);
+  const uint32_t bar_v_empty = khd::smem_u32(&bars[7]);
+  const uint32_t bar_s_full = khd::smem_u32(&bars[9]);
+  const uint32_t bar_p_ready = khd::smem_u32(&bars[11]);
+  const uint32_t bar_pv_full = khd::smem_u32(&bars[13]);
+  const uint32_t bar_exchange = khd::smem_u32(&bars[15]);
 
   if (threadIdx.x == 0) {
     s_abort = 0;
     khd::mbar_init(bar_q, 1);
-    for (int s = 0; s < kStages; ++s) {
-      khd::mbar_init(bar_kv_full + 8 * s, 1);
-      khd::mbar_init(bar_kv_empty + 8 * s, 1);
+    for (int s = 0; s < 2; ++s) {
+      khd::mbar_init(bar_k_full + 8 * s, 1);
+      khd::mbar_init(bar_k_empty + 8 * s, 1);
+      khd::mbar_init(bar_v_full + 8 * s, 1);
+      khd::mbar_init(bar_v_empty + 8 * s, 1);
       khd::mbar_init(bar_s_full + 8 * s, 1);
+      khd::mbar_init(bar_p_ready + 8 * s, kBQ); // one arrival per thread of the group that owns the buffer
+      khd::mbar_init(bar_pv_full + 8 * s, 1);
     }
-    khd::mbar_init(bar_p_ready, kSoftmaxThreads); // one arrival per softmax thread
-    khd::mbar_init(bar_pv_full, 1);
     khd::mbar_init(bar_exchange, kSoftmaxThreads);
     khd::mbar_fence_init();
     khd::tma_prefetch_descriptor(&tm_q_hi);
@@ -201,7 +222,8 @@ attention(KH_MEMREF4(const float, q), KH_MEMREF4(const float, k), KH_MEMREF4(con
   const uint32_t tmem_base = s_tmem_base;
 
   if (warp == 0) {
-    // ---- TMA producer -----------------------------------------------------------
+    // ---- TMA producer: K and V have their own 2-deep rings. A K slot is free as
+    //      soon as S of its tile has run, long before the V slot of the same tile. ------
     if (lane == 0) {
       const int q_row = static_cast<int>(bh * seq) + q0;
       khd::mbar_arrive_expect_tx(bar_q, kQBytes);
@@ -210,190 +232,238 @@ attention(KH_MEMREF4(const float, q), KH_MEMREF4(const float, k), KH_MEMREF4(con
       khd::tma_load_2d(smem_q + 2 * kQChunkBytes, &tm_q_lo, 0, q_row, bar_q);
       khd::tma_load_2d(smem_q + 3 * kQChunkBytes, &tm_q_lo, 32, q_row, bar_q);
       for (int j = 0; j < num_kv; ++j) {
-        const int s = j % kStages;
-        const uint32_t phase = static_cast<uint32_t>((j / kStages) & 1);
-        if (!khd::mbar_wait(bar_kv_empty + 8 * s, phase ^ 1u, &s_abort, status,
+        const int s = j & 1;
+        const uint32_t phase = static_cast<uint32_t>((j >> 1) & 1);
+        if (!khd::mbar_wait(bar_k_empty + 8 * s, phase ^ 1u, &s_abort, status,
                             khd::kStatusEmptyWaitTimeout, static_cast<uint32_t>(j)))
           break;
-        const uint32_t st = smem_kv + s * kStageBytes;
-        const uint32_t bar = bar_kv_full + 8 * s;
-        khd::mbar_arrive_expect_tx(bar, kStageBytes);
-        const int k_row = static_cast<int>(bh * seq) + j * kBKV;
-        const int v_row = static_cast<int>(bh * kHeadDim);
-        const int v_col = j * kBKV;
-        khd::tma_load_2d(st + 0 * kKVChunkBytes, &tm_k_hi, 0, k_row, bar);
-        khd::tma_load_2d(st + 1 * kKVChunkBytes, &tm_k_hi, 32, k_row, bar);
-        khd::tma_load_2d(st + 2 * kKVChunkBytes, &tm_k_lo, 0, k_row, bar);
-        khd::tma_load_2d(st + 3 * kKVChunkBytes, &tm_k_lo, 32, k_row, bar);
-        khd::tma_load_2d(st + 4 * kKVChunkBytes, &tm_vt_hi, v_col, v_row, bar);
-        khd::tma_load_2d(st + 5 * kKVChunkBytes, &tm_vt_hi, v_col + 32, v_row, bar);
-        khd::tma_load_2d(st + 6 * kKVChunkBytes, &tm_vt_lo, v_col, v_row, bar);
-        khd::tma_load_2d(st + 7 * kKVChunkBytes, &tm_vt_lo, v_col + 32, v_row, bar);
+        {
+          const uint32_t st = smem_k + s * kHalfStageBytes;
+          const uint32_t bar = bar_k_full + 8 * s;
+          khd::mbar_arrive_expect_tx(bar, kHalfStageBytes);
+          const int k_row = static_cast<int>(bh * seq) + j * kBKV;
+          khd::tma_load_2d(st + 0 * kKVChunkBytes, &tm_k_hi, 0, k_row, bar);
+          khd::tma_load_2d(st + 1 * kKVChunkBytes, &tm_k_hi, 32, k_row, bar);
+          khd::tma_load_2d(st + 2 * kKVChunkBytes, &tm_k_lo, 0, k_row, bar);
+          khd::tma_load_2d(st + 3 * kKVChunkBytes, &tm_k_lo, 32, k_row, bar);
+        }
+        if (!khd::mbar_wait(bar_v_empty + 8 * s, phase ^ 1u, &s_abort, status,
+                            khd::kStatusEmptyWaitTimeout, 1000u + static_cast<uint32_t>(j)))
+          break;
+        {
+          const uint32_t st = smem_v + s * kHalfStageBytes;
+          const uint32_t bar = bar_v_full + 8 * s;
+          khd::mbar_arrive_expect_tx(bar, kHalfStageBytes);
+          const int v_row = static_cast<int>(bh * kHeadDim);
+          const int v_col = j * kBKV;
+          khd::tma_load_2d(st + 0 * kKVChunkBytes, &tm_vt_hi, v_col, v_row, bar);
+          khd::tma_load_2d(st + 1 * kKVChunkBytes, &tm_vt_hi, v_col + 32, v_row, bar);
+          khd::tma_load_2d(st + 2 * kKVChunkBytes, &tm_vt_lo, v_col, v_row, bar);
+          khd::tma_load_2d(st + 3 * kKVChunkBytes, &tm_vt_lo, v_col + 32, v_row, bar);
+        }
       }
     }
   } else if (warp == 1) {
-    // ---- MMA issuer ---------------------------------------------------------------
-    if (lane == 0) {
+    // ---- MMA issuer: S_0, then per tile j: S_{j+1} (other S buffer), PV_j. The
+    //      whole warp walks the loop (waits, descriptor arithmetic: warp-uniform,
+    //      so it stays in uniform registers); only the tcgen05 instructions
+    //      themselves sit under the elected lane. ---------------------------------------
+    {
+      const bool leader = khd::elect_one();
       constexpr uint32_t idesc = khd::umma_idesc_tf32(kBQ, kBKV); // M128 N64 for both products
-      // S_j = Q K_j^T into S buffer j % 2
-      auto issue_s = [&](int j) {
-        const uint32_t st = smem_kv + (j % kStages) * kStageBytes;
-        const uint32_t d = tmem_base + ((j & 1) ? kColS1 : kColS0);
+      // descriptor of chunk c (32 of the 64 k-columns) of a tile, stepped by kk inside it
+      const uint64_t dq_hi = khd::umma_desc_k128(smem_q), dq_lo = khd::umma_desc_k128(smem_q + 2 * kQChunkBytes);
+      constexpr uint64_t kQChunkStep = kQChunkBytes >> 4, kKVChunkStep = kKVChunkBytes >> 4;
+      auto issue_s = [&](int b) {
+        const uint64_t dk_hi = khd::umma_desc_k128(smem_k + b * kHalfStageBytes);
+        const uint64_t dk_lo = dk_hi + 2 * kKVChunkStep;
+        const uint32_t d = tmem_base + (b ? kColS1 : kColS0);
+        if (leader) {
 #pragma unroll
-        for (int kk = 0; kk < kHeadDim / 8; ++kk) {
-          const int chunk = kk >> 2;
-          const uint64_t adv = static_cast<uint64_t>((kk & 3) * 2);
-          const uint64_t q_hi = khd::umma_desc_k128(smem_q + (0 + chunk) * kQChunkBytes) + adv;
-          const uint64_t q_lo = khd::umma_desc_k128(smem_q + (2 + chunk) * kQChunkBytes) + adv;
-          const uint64_t k_hi = khd::umma_desc_k128(st + (0 + chunk) * kKVChunkBytes) + adv;
-          const uint64_t k_lo = khd::umma_desc_k128(st + (2 + chunk) * kKVChunkBytes) + adv;
-          khd::umma_tf32_ss(d, q_lo, k_hi, idesc, kk != 0 ? 1u : 0u);
-          khd::umma_tf32_ss(d, q_hi, k_lo, idesc, 1u);
-          khd::umma_tf32_ss(d, q_hi, k_hi, idesc, 1u);
+          for (int kk = 0; kk < kHeadDim / 8; ++kk) {
+            const uint64_t qoff = (kk >> 2) * kQChunkStep + (kk & 3) * 2;
+            const uint64_t koff = (kk >> 2) * kKVChunkStep + (kk & 3) * 2;
+            khd::umma_tf32_ss(d, dq_lo + qoff, dk_hi + koff, idesc, kk != 0 ? 1u : 0u);
+            khd::umma_tf32_ss(d, dq_hi + qoff, dk_lo + koff, idesc, 1u);
+            khd::umma_tf32_ss(d, dq_hi + qoff, dk_hi + koff, idesc, 1u);
+          }
+          khd::umma_commit(bar_s_full + 8 * b);  // scores ready for the softmax threads
+          khd::umma_commit(bar_k_empty + 8 * b); // and this K slot may be refilled
         }
-        khd::umma_commit(bar_s_full + 8 * (j & 1));
+        __syncwarp();
       };
       bool ok = khd::mbar_wait(bar_q, 0u, &s_abort, status, khd::kStatusTmaWaitTimeout, 1000u);
-      ok = ok && khd::mbar_wait(bar_kv_full, 0u, &s_abort, status, khd::kStatusTmaWaitTimeout, 0u);
+      ok = ok && khd::mbar_wait(bar_k_full, 0u, &s_abort, status, khd::kStatusTmaWaitTimeout, 0u);
+      ok = __all_sync(0xffffffffu, ok);
       if (ok) {
         khd::tc_fence_after_sync();
         issue_s(0);
       }
       for (int j = 0; j < num_kv && ok; ++j) {
+        const int b = j & 1;
+        const uint32_t phase = static_cast<uint32_t>((j >> 1) & 1);
         if (j + 1 < num_kv) {
-          const int s1 = (j + 1) % kStages;
-          ok = khd::mbar_wait(bar_kv_full + 8 * s1, static_cast<uint32_t>(((j + 1) / kStages) & 1),
+          ok = khd::mbar_wait(bar_k_full + 8 * ((j + 1) & 1), static_cast<uint32_t>(((j + 1) >> 1) & 1),
                               &s_abort, status, khd::kStatusTmaWaitTimeout, static_cast<uint32_t>(j + 1));
+          ok = __all_sync(0xffffffffu, ok);
           if (!ok) break;
           khd::tc_fence_after_sync();
-          issue_s(j + 1);
+          issue_s((j + 1) & 1);
         }
-        ok = khd::mbar_wait(bar_p_ready, static_cast<uint32_t>(j & 1), &s_abort, status,
+        ok = khd::mbar_wait(bar_p_ready + 8 * b, phase, &s_abort, status,
                             khd::kStatusEpilogueWaitTimeout, static_cast<uint32_t>(j));
+        ok = ok && khd::mbar_wait(bar_v_full + 8 * b, phase, &s_abort, status,
+                                  khd::kStatusTmaWaitTimeout, 2000u + static_cast<uint32_t>(j));
+        ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
         khd::tc_fence_after_sync();
-        // PV_j = P_j V_j: A = P (tensor memory, 64 columns hi / 64 lo), B = V^T tile
-        const uint32_t st = smem_kv + (j % kStages) * kStageBytes;
-        const uint32_t d = tmem_base + kColPV;
+        // PV_j = P_j V_j: A = P buffer b (tensor memory), B = V^T tile, D = PV buffer b
+        const uint64_t dv_hi = khd::umma_desc_k128(smem_v + b * kHalfStageBytes);
+        const uint64_t dv_lo = dv_hi + 2 * kKVChunkStep;
+        const uint32_t d = tmem_base + (b ? kColPV1 : kColPV0);
+        const uint32_t p_base = tmem_base + (b ? kColP1 : kColP0);
+        if (leader) {
 #pragma unroll
-        for (int kk = 0; kk < kBKV / 8; ++kk) {
-          const int chunk = kk >> 2;
-          const uint64_t adv = static_cast<uint64_t>((kk & 3) * 2);
-          const uint64_t v_hi = khd::umma_desc_k128(st + (4 + chunk) * kKVChunkBytes) + adv;
-          const uint64_t v_lo = khd::umma_desc_k128(st + (6 + chunk) * kKVChunkBytes) + adv;
-          const uint32_t p_hi = tmem_base + kColPHi + kk * 8;
-          const uint32_t p_lo = tmem_base + kColPLo + kk * 8;
-          umma_tf32_ts(d, p_lo, v_hi, idesc, kk != 0 ? 1u : 0u);
-          umma_tf32_ts(d, p_hi, v_lo, idesc, 1u);
-          umma_tf32_ts(d, p_hi, v_hi, idesc, 1u);
+          for (int kk = 0; kk < kBKV / 8; ++kk) {
+            const uint64_t voff = (kk >> 2) * kKVChunkStep + (kk & 3) * 2;
+            umma_tf32_ts(d, p_base + 64 + kk * 8, dv_hi + voff, idesc, kk != 0 ? 1u : 0u);
+            umma_tf32_ts(d, p_base + kk * 8, dv_lo + voff, idesc, 1u);
+            umma_tf32_ts(d, p_base + kk * 8, dv_hi + voff, idesc, 1u);
+          }
+          khd::umma_commit(bar_pv_full + 8 * b);
+          khd::umma_commit(bar_v_empty + 8 * b);
         }
-        khd::umma_commit(bar_pv_full);
-        khd::umma_commit(bar_kv_empty + 8 * (j % kStages));
+        __syncwarp();
       }
     }
   } else {
-    // ---- softmax + output: two threads per query row. Warps 2-5 take key
-    //      columns 0-31 of every tile (and output columns 0-31), warps 6-9 the
-    //      other half; a warp may only touch tensor-memory lanes 32*(warp%4).. ----------
+    // ---- softmax + output: two groups of 128 threads, one thread per query row
+    //      in each. Group g (warps 2-5 / 6-9) takes the tiles of parity g with its
+    //      own running max, sum and output row; the groups work on neighbouring
+    //      tiles at the same time and are merged once at the end. A warp may only
+    //      touch tensor-memory lanes 32*(warp%4).., which both groups cover. -----------
     const int ew = warp - 2;
     const int quad = warp & 3;
-    const int half = ew >> 2;
+    const int g = ew >> 2;
     const uint32_t lane_base = static_cast<uint32_t>(quad * 32) << 16;
     const int row_in_tile = quad * 32 + lane;
-    float acc[32];
+    const uint32_t col_s = g ? kColS1 : kColS0, col_p = g ? kColP1 : kColP0, col_pv = g ? kColPV1 : kColPV0;
+    float acc[kHeadDim]; // running output of this group's tiles, normalised to its max
 #pragma unroll
-    for (int i = 0; i < 32; ++i) acc[i] = 0.f;
-    float m = -INFINITY, l = 0.f; // l is this thread's half of the row sum
+    for (int i = 0; i < kHeadDim; ++i) acc[i] = 0.f;
+    float m = -INFINITY, l = 0.f;
     bool ok = true;
     constexpr float kLog2e = 1.4426950408889634f;
 
-    for (int j = 0; j < num_kv && ok; ++j) {
-      ok = khd::mbar_wait(bar_s_full + 8 * (j & 1), static_cast<uint32_t>((j >> 1) & 1), &s_abort,
-                          status, khd::kStatusMmaWaitTimeout, static_cast<uint32_t>(j));
+    for (int j = g; j < num_kv && ok; j += 2) {
+      const uint32_t phase = static_cast<uint32_t>((j >> 1) & 1);
+      ok = khd::mbar_wait(bar_s_full + 8 * g, phase, &s_abort, status, khd::kStatusMmaWaitTimeout,
+                          static_cast<uint32_t>(j));
       if (!ok) break;
       khd::tc_fence_after_sync();
-      uint32_t sv[32];
-      khd::tmem_ld_32x32(tmem_base + lane_base + ((j & 1) ? kColS1 : kColS0) + 32 * half, sv);
+      uint32_t sv[kBKV];
+      khd::tmem_ld_32x32(tmem_base + lane_base + col_s, *reinterpret_cast<uint32_t(*)[32]>(&sv[0]));
+      khd::tmem_ld_32x32(tmem_base + lane_base + col_s + 32, *reinterpret_cast<uint32_t(*)[32]>(&sv[32]));
       khd::tmem_ld_wait();
       float mx = -INFINITY;
 #pragma unroll
-      for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(sv[i]));
-      // the row maximum needs the partner thread's half: exchange through shared
-      // memory (double buffered by tile parity). The meeting point is an
-      // mbarrier, not bar.sync, so that it is a bounded wait like all others.
-      s_rowmax[j & 1][half][row_in_tile] = mx;
-      khd::mbar_arrive(bar_exchange);
-      ok = khd::mbar_wait(bar_exchange, static_cast<uint32_t>(j & 1), &s_abort, status,
-                          khd::kStatusEpilogueWaitTimeout, 4000u + static_cast<uint32_t>(j));
-      if (!ok) break;
-      mx = fmaxf(mx, s_rowmax[j & 1][half ^ 1][row_in_tile]);
+      for (int i = 0; i < kBKV; ++i) mx = fmaxf(mx, __uint_as_float(sv[i]));
       const float m_new = fmaxf(m, mx);
-      const float alpha = exp2f((m - m_new) * kLog2e); // m = -inf on the first tile gives 0
+      const float alpha = fast_exp2((m - m_new) * kLog2e); // m = -inf on the first tile gives 0
       const float mb = m_new * kLog2e;
       float sum = 0.f;
 #pragma unroll
-      for (int i = 0; i < 32; ++i) {
-        const float p = exp2f(fmaf(__uint_as_float(sv[i]), kLog2e, -mb));
+      for (int i = 0; i < kBKV; ++i) {
+        const float p = fast_exp2(fmaf(__uint_as_float(sv[i]), kLog2e, -mb));
         sv[i] = __float_as_uint(p);
         sum += p;
       }
       l = l * alpha + sum;
       m = m_new;
 
-      // Fold in the previous tile's PV (normalised to the previous max), then
-      // move the running output to the new max. Waiting here also means the
-      // tensor core has finished reading P of the previous tile.
-      if (j > 0) {
-        ok = khd::mbar_wait(bar_pv_full, static_cast<uint32_t>((j - 1) & 1), &s_abort, status,
+      // The group's previous product PV_{j-2} read P buffer g and wrote PV buffer
+      // g: fold it in (it is normalised to the previous max), which also frees
+      // both buffers, then move the running output to the new max.
+      if (j >= 2) {
+        ok = khd::mbar_wait(bar_pv_full + 8 * g, phase ^ 1u, &s_abort, status,
                             khd::kStatusMmaWaitTimeout, 2000u + static_cast<uint32_t>(j));
         if (!ok) break;
         khd::tc_fence_after_sync();
-        uint32_t t[32];
-        khd::tmem_ld_32x32(tmem_base + lane_base + kColPV + 32 * half, t);
-        khd::tmem_ld_wait();
 #pragma unroll
-        for (int i = 0; i < 32; ++i) acc[i] = (acc[i] + __uint_as_float(t[i])) * alpha;
+        for (int h = 0; h < 4; ++h) {
+          uint32_t t[16];
+          tmem_ld_32x16(tmem_base + lane_base + col_pv + 16 * h, t);
+          khd::tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 16; ++i) acc[16 * h + i] = (acc[16 * h + i] + __uint_as_float(t[i])) * alpha;
+        }
       }
       // P -> tensor memory as hi / lo
-      {
-        uint32_t hi[32];
 #pragma unroll
-        for (int i = 0; i < 32; ++i) hi[i] = __float_as_uint(tf32_hi(__uint_as_float(sv[i])));
-        tmem_st_32x32(tmem_base + lane_base + kColPHi + 32 * half, hi);
+      for (int h = 0; h < 4; ++h) {
+        uint32_t hi[16];
 #pragma unroll
-        for (int i = 0; i < 32; ++i)
-          hi[i] = __float_as_uint(__uint_as_float(sv[i]) - __uint_as_float(hi[i]));
-        tmem_st_32x32(tmem_base + lane_base + kColPLo + 32 * half, hi);
-        tmem_st_wait();
+        for (int i = 0; i < 16; ++i) hi[i] = __float_as_uint(tf32_hi(__uint_as_float(sv[16 * h + i])));
+        tmem_st_32x16(tmem_base + lane_base + col_p + 16 * h, hi);
+#pragma unroll
+        for (int i = 0; i < 16; ++i)
+          hi[i] = __float_as_uint(__uint_as_float(sv[16 * h + i]) - __uint_as_float(hi[i]));
+        tmem_st_32x16(tmem_base + lane_base + col_p + 64 + 16 * h, hi);
       }
+      tmem_st_wait();
       khd::tc_fence_before_sync();
-      khd::mbar_arrive(bar_p_ready);
+      khd::mbar_arrive(bar_p_ready + 8 * g);
     }
-    if (ok && num_kv > 0) {
-      ok = khd::mbar_wait(bar_pv_full, static_cast<uint32_t>((num_kv - 1) & 1), &s_abort, status,
+    // this group's last product
+    const int my_tiles = (num_kv - g + 1) / 2;
+    if (ok && my_tiles > 0) {
+      const int jl = g + 2 * (my_tiles - 1);
+      ok = khd::mbar_wait(bar_pv_full + 8 * g, static_cast<uint32_t>((jl >> 1) & 1), &s_abort, status,
                           khd::kStatusMmaWaitTimeout, 3000u);
-      // the two halves of a row sum meet here
-      s_rowmax[num_kv & 1][half][row_in_tile] = l;
-      khd::mbar_arrive(bar_exchange);
-      ok = ok && khd::mbar_wait(bar_exchange, static_cast<uint32_t>(num_kv & 1), &s_abort, status,
-                                khd::kStatusEpilogueWaitTimeout, 5000u);
       if (ok) {
         khd::tc_fence_after_sync();
-        const float inv = 1.0f / (l + s_rowmax[num_kv & 1][half ^ 1][row_in_tile]);
-        const int64_t row = static_cast<int64_t>(q0) + row_in_tile;
-        float *orow = out + (bh * seq + row) * kHeadDim + 32 * half;
-        uint32_t t[32];
-        khd::tmem_ld_32x32(tmem_base + lane_base + kColPV + 32 * half, t);
-        khd::tmem_ld_wait();
-        if (row < seq) {
 #pragma unroll
-          for (int i = 0; i < 8; ++i)
-            __stcs(reinterpret_cast<float4 *>(orow) + i,
-                   make_float4((acc[4 * i + 0] + __uint_as_float(t[4 * i + 0])) * inv,
-                               (acc[4 * i + 1] + __uint_as_float(t[4 * i + 1])) * inv,
-                               (acc[4 * i + 2] + __uint_as_float(t[4 * i + 2])) * inv,
-                               (acc[4 * i + 3] + __uint_as_float(t[4 * i + 3])) * inv));
+        for (int h = 0; h < 4; ++h) {
+          uint32_t t[16];
+          tmem_ld_32x16(tmem_base + lane_base + col_pv + 16 * h, t);
+          khd::tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 16; ++i) acc[16 * h + i] += __uint_as_float(t[i]);
         }
+      }
+    }
+    // Merge: group 1 hands (max, sum, output row) to group 0 through the Q
+    // buffer, which is free once the very last product of the CTA has run.
+    if (ok && num_kv > 0) {
+      const int jt = num_kv - 1;
+      ok = khd::mbar_wait(bar_pv_full + 8 * (jt & 1), static_cast<uint32_t>((jt >> 1) & 1), &s_abort,
+                          status, khd::kStatusMmaWaitTimeout, 3001u);
+    }
+    float *merge = reinterpret_cast<float *>(smem_raw + (smem_q - khd::smem_u32(smem_raw))) +
+                   row_in_tile * (kHeadDim + 3);
+    if (ok && g == 1) {
+      merge[0] = m;
+      merge[1] = l;
+#pragma unroll
+      for (int i = 0; i < kHeadDim; ++i) merge[2 + i] = acc[i];
+    }
+    khd::mbar_arrive(bar_exchange);
+    ok = ok && khd::mbar_wait(bar_exchange, 0u, &s_abort, status, khd::kStatusEpilogueWaitTimeout, 5000u);
+    if (ok && g == 0 && num_kv > 0) {
+      const float m1 = merge[0], l1 = merge[1];
+      const float mt = fmaxf(m, m1);
+      const float w0 = fast_exp2((m - mt) * kLog2e), w1 = fast_exp2((m1 - mt) * kLog2e);
+      const float inv = 1.0f / (l * w0 + l1 * w1);
+      const int64_t row = static_cast<int64_t>(q0) + row_in_tile;
+      float *orow = out + (bh * seq + row) * kHeadDim;
+      if (row < seq) {
+#pragma unroll
+        for (int i = 0; i < kHeadDim / 4; ++i)
+          __stcs(reinterpret_cast<float4 *>(orow) + i,
+                 make_float4((acc[4 * i + 0] * w0 + merge[2 + 4 * i + 0] * w1) * inv,
+                             (acc[4 * i + 1] * w0 + merge[2 + 4 * i + 1] * w1) * inv,
+                             (acc[4 * i + 2] * w0 + merge[2 + 4 * i + 2] * w1) * inv,
+                             (acc[4 * i + 3] * w0 + merge[2 + 4 * i + 3] * w1) * inv));
       }
     }
     khd::tc_fence_before_sync();

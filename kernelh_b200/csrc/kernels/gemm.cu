@@ -261,8 +261,12 @@ __device__ __forceinline__ void gemm_body(int64_t m, int64_t n, float *__restric
       }
     }
   } else if (warp == 1) {
-    // ---- MMA issuer: chunk buffers alternate across tiles too ---------------------
-    if (lane == 0) {
+    // ---- MMA issuer: chunk buffers alternate across tiles too. The whole warp
+    //      walks the loop (waits and descriptor arithmetic are warp-uniform and
+    //      stay in uniform registers); only the tcgen05 instructions themselves
+    //      sit under the elected lane. ---------------------------------------------------
+    {
+      const bool leader = khd::elect_one();
       constexpr uint32_t idesc = khd::umma_idesc_tf32(kBM, kBN);
       uint32_t g_kb = 0, g_chunk = 0;
       bool ok = true;
@@ -274,31 +278,35 @@ __device__ __forceinline__ void gemm_body(int64_t m, int64_t n, float *__restric
             // the accumulator buffer must have been drained (two chunks ago)
             ok = khd::mbar_wait(acc_empty0 + 8 * buf, ((g_chunk >> 1) & 1u) ^ 1u, &s_abort, status,
                                 khd::kStatusEpilogueWaitTimeout, g_chunk);
+            ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
           }
           const int s = static_cast<int>(g_kb % kStages);
           const uint32_t phase = (g_kb / kStages) & 1u;
           ok = khd::mbar_wait(full0 + 8 * s, phase, &s_abort, status, khd::kStatusTmaWaitTimeout, g_kb);
+          ok = __all_sync(0xffffffffu, ok);
           if (!ok) break;
           khd::tc_fence_after_sync();
           const uint32_t d = tmem_base + static_cast<uint32_t>(buf * kBN);
           const uint32_t stage = ring + s * kStageBytes;
           const uint64_t a_hi = khd::umma_desc_k128(stage);
-          const uint64_t a_lo = khd::umma_desc_k128(stage + kATileBytes);
-          const uint64_t b_hi = khd::umma_desc_k128(stage + 2 * kATileBytes);
-          const uint64_t b_lo = khd::umma_desc_k128(stage + 2 * kATileBytes + kBTileBytes);
+          const uint64_t a_lo = a_hi + (kATileBytes >> 4);
+          const uint64_t b_hi = a_hi + (2 * kATileBytes >> 4);
+          const uint64_t b_lo = b_hi + (kBTileBytes >> 4);
+          const bool chunk_end = in_chunk == kChunkBlocks - 1 || kb == k_blocks - 1;
+          if (leader) {
 #pragma unroll
-          for (int kk = 0; kk < kBK / 8; ++kk) {
-            const uint64_t adv = static_cast<uint64_t>(kk * 2); // 32 bytes >> 4
-            khd::umma_tf32_ss(d, a_lo + adv, b_hi + adv, idesc, (in_chunk | kk) != 0 ? 1u : 0u);
-            khd::umma_tf32_ss(d, a_hi + adv, b_lo + adv, idesc, 1u);
-            khd::umma_tf32_ss(d, a_hi + adv, b_hi + adv, idesc, 1u);
+            for (int kk = 0; kk < kBK / 8; ++kk) {
+              const uint64_t adv = static_cast<uint64_t>(kk * 2); // 32 bytes >> 4
+              khd::umma_tf32_ss(d, a_lo + adv, b_hi + adv, idesc, (in_chunk | kk) != 0 ? 1u : 0u);
+              khd::umma_tf32_ss(d, a_hi + adv, b_lo + adv, idesc, 1u);
+              khd::umma_tf32_ss(d, a_hi + adv, b_hi + adv, idesc, 1u);
+            }
+            khd::umma_commit(empty0 + 8 * s); // stage reusable once these MMAs retire
+            if (chunk_end) khd::umma_commit(acc_full0 + 8 * buf); // chunk complete: hand it to the epilogue
           }
-          khd::umma_commit(empty0 + 8 * s); // stage reusable once these MMAs retire
-          if (in_chunk == kChunkBlocks - 1 || kb == k_blocks - 1) {
-            khd::umma_commit(acc_full0 + 8 * buf); // chunk complete: hand it to the epilogue
-            ++g_chunk;
-          }
+          __syncwarp();
+          if (chunk_end) ++g_chunk;
         }
       }
     }

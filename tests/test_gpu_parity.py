@@ -318,6 +318,53 @@ def test_attention_batched_config_sampled(ctx, oracle):
         assert cmp_.max_rel <= REL * math.sqrt(1024)
 
 
+# --------------------------------------------------------------------------- the reference's launch sequence
+def test_reference_launch_geometry_through_kernel_launch(ctx, oracle):
+    """GpuModule::load + KernelLaunch with the geometry the reference's callers
+    choose (bench/harness/kernelh_backend.cpp:223-427): the streaming and row
+    kernels stride over whatever grid they are given."""
+    n = 100003
+    a, b = oracle.vecadd_pattern(n)
+    da, db, dc = dev(a), dev(b), torch.zeros(n, device="cuda")
+    ctx.module_launch(kh.kernel_image("vecadd"), "vecadd", ((n + 255) // 256, 1, 1), (256, 1, 1),
+                      [da, db, dc], [[n], [n], [n]])
+    assert oracle.bit_mismatches(dc.cpu().numpy(), oracle.vecadd_ref(a, b)) == 0
+    rows, cols = 300, 1024
+    x = oracle.lcg((rows, cols), 0x27AB13)
+    dx, dy = dev(x), torch.zeros(rows, cols, device="cuda")
+    ctx.module_launch(kh.kernel_image("softmax"), "softmax", (rows, 1, 1), (min(cols, 256), 1, 1),
+                      [dx, dy], [[rows, cols], [rows, cols]])
+    assert oracle.compare(dy.cpu().numpy(), oracle.softmax_ref(x)).max_abs <= 1e-4
+    s = oracle.LcgStream(0x2E2E8A)
+    x, g, be = s.fill((rows, cols)), s.fill(cols), s.fill(cols)
+    dy.zero_()
+    ctx.module_launch(kh.kernel_image("layernorm"), "layernorm", (rows, 1, 1), (256, 1, 1),
+                      [dev(x), dev(g), dev(be), dy], [[rows, cols], [cols], [cols], [rows, cols]])
+    assert oracle.compare(dy.cpu().numpy(), oracle.layernorm_ref(x, g, be)).max_abs <= 1e-4
+
+
+def test_kernel_launch_refuses_what_the_device_cannot_run(ctx):
+    x = torch.zeros(1024, device="cuda")
+    image = kh.kernel_image("vecadd")
+    with pytest.raises(kh.KernelhError) as e:  # 2048 threads: over the block limit, and occupancy 0
+        ctx.module_launch(image, "vecadd", (1, 1, 1), (2048, 1, 1), [x, x, x], [[1024]] * 3)
+    assert e.value.code == 1 and e.value.message.startswith("KernelLaunch::launch refused: ")
+    assert "threads per workgroup 2048 exceeds the max 1024" in e.value.message
+    with pytest.raises(kh.KernelhError) as e:  # more dynamic shared memory than the opt-in limit
+        ctx.module_launch(image, "vecadd", (1, 1, 1), (256, 1, 1), [x, x, x], [[1024]] * 3,
+                          dynamic_smem=300000)
+    assert "opt-in limit" in e.value.message
+    with pytest.raises(kh.KernelhError) as e:
+        ctx.module_launch(image, "no_such_entry", (1, 1, 1), (256, 1, 1), [x, x, x], [[1024]] * 3)
+    assert e.value.code != 0 and "cuModuleGetFunction(no_such_entry)" in e.value.message
+    with pytest.raises(kh.KernelhError) as e:  # a corrupted code object is a typed error, not a crash
+        ctx.module_launch(b"\x7fELF" + b"garbage" * 64, "vecadd", (1, 1, 1), (256, 1, 1), [x, x, x],
+                          [[1024]] * 3)
+    assert e.value.code != 0 and "cuModuleLoadData" in e.value.message
+    ctx.vecadd(x, x, x, 1024)  # the context is still usable
+    ctx.synchronize()
+
+
 # --------------------------------------------------------------------------- surface
 def test_launch_errors_are_reported(ctx):
     x = torch.zeros(16, device="cuda")
