@@ -22,9 +22,10 @@
 //  gemm_split_a / gemm_split_bt  write A_hi, A_lo (m x kp) and B^T_hi, B^T_lo
 //      (n x kp) into scratch, kp = k rounded up to 32 and zero padded, so both
 //      tensor-core operands are K-major with 128-byte rows whatever k is.
-//  gemm  persistent CTAs (one per SM) walk the 128 x 256 tiles of C. Warp 0 feeds a 2-stage ring of
-//      {A_hi, A_lo, B_hi, B_lo} k-blocks (32 fp32 deep, 96 KiB per stage) with
-//      TMA (128-byte swizzle, out-of-range rows read as zero, which is what
+//  gemm  persistent CTAs (one per SM) walk the 128 x 256 tiles of C. Warp 0 feeds a 4-stage ring of
+//      {A_hi, A_lo, B_hi, B_lo} k-blocks (16 fp32 deep, 48 KiB per stage: three
+//      loads in flight hide the L2 latency that a 2 x 96 KiB ring left exposed) with
+//      TMA (64-byte swizzle, out-of-range rows read as zero, which is what
 //      makes ragged m and n work); warp 1 issues tcgen05.mma (M128 N256 K8,
 //      kind::tf32) and releases stages with tcgen05.commit; warps 2-9 drain the
 //      256-column fp32 accumulators from tensor memory chunk by chunk and store C.
@@ -37,13 +38,13 @@ namespace {
 
 constexpr int kBM = 128;
 constexpr int kBN = 256;
-constexpr int kBK = 32; // fp32 elements: one 128-byte swizzle row
-constexpr int kStages = 2;
-constexpr int kATileBytes = kBM * kBK * 4;                         // 16 KiB
-constexpr int kBTileBytes = kBN * kBK * 4;                         // 32 KiB
-constexpr int kStageBytes = 2 * kATileBytes + 2 * kBTileBytes;     // 96 KiB
+constexpr int kBK = 16; // fp32 elements per k-block: one 64-byte swizzle row
+constexpr int kStages = 4;
+constexpr int kATileBytes = kBM * kBK * 4;                         // 8 KiB
+constexpr int kBTileBytes = kBN * kBK * 4;                         // 16 KiB
+constexpr int kStageBytes = 2 * kATileBytes + 2 * kBTileBytes;     // 48 KiB
 constexpr int kTmemCols = 512;      // two 256-column accumulators, used alternately
-constexpr int kChunkBlocks = 8;     // k-blocks accumulated in tensor memory before a drain (K = 256)
+constexpr int kChunkBlocks = 16;    // k-blocks accumulated in tensor memory before a drain (K = 256)
 constexpr int kEpilogueWarps = 8;
 constexpr int kThreads = 64 + 32 * kEpilogueWarps; // TMA warp + MMA warp + epilogue warps
 constexpr int kGroupM = 16; // m-tiles per rasterisation group (L2 reuse of B)
@@ -289,7 +290,7 @@ __device__ __forceinline__ void gemm_body(int64_t m, int64_t n, float *__restric
           khd::tc_fence_after_sync();
           const uint32_t d = tmem_base + static_cast<uint32_t>(buf * kBN);
           const uint32_t stage = ring + s * kStageBytes;
-          const uint64_t a_hi = khd::umma_desc_k128(stage);
+          const uint64_t a_hi = khd::umma_desc_k64(stage);
           const uint64_t a_lo = a_hi + (kATileBytes >> 4);
           const uint64_t b_hi = a_hi + (2 * kATileBytes >> 4);
           const uint64_t b_lo = b_hi + (kBTileBytes >> 4);

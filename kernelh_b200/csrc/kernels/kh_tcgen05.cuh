@@ -140,6 +140,18 @@ __device__ __forceinline__ uint64_t umma_desc_k128(uint32_t smem_addr) {
   return d;
 }
 
+// Same for rows of 64 bytes (16 fp32) in the 64-byte swizzle: 8-row groups are
+// 512 bytes apart, layout 4 = 64B swizzle; stepping K by 8 fp32 adds 32 bytes.
+__device__ __forceinline__ uint64_t umma_desc_k64(uint32_t smem_addr) {
+  uint64_t d = 0;
+  d |= static_cast<uint64_t>((smem_addr & 0x3FFFFu) >> 4);
+  d |= static_cast<uint64_t>(1) << 16;
+  d |= static_cast<uint64_t>(512 >> 4) << 32;
+  d |= static_cast<uint64_t>(1) << 46;
+  d |= static_cast<uint64_t>(4) << 61;
+  return d;
+}
+
 // Instruction descriptor for kind::tf32, fp32 accumulate, both operands
 // K-major: [4,6) D format 1 = f32; [7,10) A format 2 = tf32; [10,13) B format
 // 2 = tf32; bit 15 / 16 A / B major (0 = K); [17,23) N >> 3; [24,29) M >> 4.

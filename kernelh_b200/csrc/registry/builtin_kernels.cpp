@@ -193,8 +193,9 @@ Result<void> run_scan(Executor &ex, const KernelPlan &p, const std::vector<void 
 }
 
 // ---------------------------------------------------------------- gemm
-constexpr int kGemmBM = 128, kGemmBN = 256, kGemmBK = 32, kGemmStages = 2;
-constexpr size_t kGemmStageBytes = 2 * (kGemmBM * kGemmBK * 4) + 2 * (kGemmBN * kGemmBK * 4);
+// kGemmBK: k padding of the split operands; kGemmTileK: k-block depth of one pipeline stage
+constexpr int kGemmBM = 128, kGemmBN = 256, kGemmBK = 32, kGemmTileK = 16, kGemmStages = 4;
+constexpr size_t kGemmStageBytes = 2 * (kGemmBM * kGemmTileK * 4) + 2 * (kGemmBN * kGemmTileK * 4);
 
 KernelPlan plan_gemm(const ShapeMap &shape, const DeviceLimits &l) {
   const int64_t m = require_positive(shape, "gemm", "m");
@@ -280,9 +281,9 @@ Result<void> launch_gemm(Executor &ex, const KernelPlan &p, const std::vector<vo
     s.dims[0] = static_cast<uint64_t>(kp);
     s.dims[1] = static_cast<uint64_t>(rows);
     s.strides_bytes[0] = static_cast<uint64_t>(kp) * 4;
-    s.box[0] = kGemmBK;
+    s.box[0] = kGemmTileK;
     s.box[1] = box_rows;
-    s.swizzle_bytes = 128;
+    s.swizzle_bytes = 64;
     return ex.backend().encode_tensor_map(s);
   };
   auto t_ah = make_map(a_hi, m, kGemmBM);
@@ -302,7 +303,7 @@ Result<void> launch_gemm(Executor &ex, const KernelPlan &p, const std::vector<vo
   args.add_tensor_map(*t_al);
   args.add_tensor_map(*t_bh);
   args.add_tensor_map(*t_bl);
-  args.add_scalar<int64_t>(kp / kGemmBK);
+  args.add_scalar<int64_t>(kp / kGemmTileK);
   args.add_scalar<uint64_t>(reinterpret_cast<uint64_t>(ex.status_word()));
   if (gather) args.add_struct_bytes(gather, sizeof *gather);
   LaunchStep step = p.steps[2];

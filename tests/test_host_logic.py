@@ -192,7 +192,7 @@ def test_plans_for_the_benchmark_configurations():
     assert p.work == 8000000.0 and p.workspace_bytes == (2 + 2 * 245) * 8
     p = kh.plan("gemm", "m=8192,n=8192,k=8192")
     assert p.entry == b"gemm" and p.n_launches == 3 and p.grid[0] == 148 and p.block[0] == 320
-    assert p.dynamic_smem == 2 * 98304 + 1024 and p.tmem_columns == 512
+    assert p.dynamic_smem == 4 * 49152 + 1024 and p.tmem_columns == 512
     assert p.workspace_bytes == 2 * 8192 * 8192 * 4 * 2
     assert p.work == 1099511627776.0 and p.work_is_flops
     assert kh.verify_launch("sm_100a", p.block[0], tuple(p.grid), 48, p.dynamic_smem) == ""
