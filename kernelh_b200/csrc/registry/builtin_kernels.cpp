@@ -7,6 +7,7 @@
 #include "registry.hpp"
 
 #include <algorithm>
+#include <cstdlib>
 #include <stdexcept>
 
 namespace kh {
@@ -196,6 +197,17 @@ Result<void> run_scan(Executor &ex, const KernelPlan &p, const std::vector<void 
 // kGemmBK: k padding of the split operands; kGemmTileK: k-block depth of one pipeline stage
 constexpr int kGemmBM = 128, kGemmBN = 256, kGemmBK = 32, kGemmTileK = 16, kGemmStages = 4;
 constexpr size_t kGemmStageBytes = 2 * (kGemmBM * kGemmTileK * 4) + 2 * (kGemmBN * kGemmTileK * 4);
+constexpr int kGemmPairStages = 6;
+constexpr size_t kGemmPairStageBytes = 4 * (kGemmBM * kGemmTileK * 4);
+
+// Process-wide choice when the shape has no cta_pair key: KERNELH_GEMM_PAIR=0|1.
+bool gemm_pair_by_default() {
+  static const bool value = [] {
+    const char *e = std::getenv("KERNELH_GEMM_PAIR");
+    return e != nullptr && e[0] == '1';
+  }();
+  return value;
+}
 
 KernelPlan plan_gemm(const ShapeMap &shape, const DeviceLimits &l) {
   const int64_t m = require_positive(shape, "gemm", "m");
@@ -226,6 +238,16 @@ KernelPlan plan_gemm(const ShapeMap &shape, const DeviceLimits &l) {
   g.dynamic_smem = kGemmStages * kGemmStageBytes + 1024;
   g.param_count = 21 + 4 + 2;
   g.tmem_columns = 512;
+  // Optional shape key cta_pair=1: the same product on two-CTA clusters (gemm_pair.cu), each
+  // cluster owning a 256 x 256 tile; a CTA stages half of the B tile, its partner the other half.
+  const auto pair_key = shape.find("cta_pair");
+  if (pair_key != shape.end() ? pair_key->second != 0 : gemm_pair_by_default()) {
+    const int64_t pair_tiles = ((m + 2 * kGemmBM - 1) / (2 * kGemmBM)) * ((n + kGemmBN - 1) / kGemmBN);
+    g.entry = "gemm_pair";
+    g.cluster = 2;
+    g.grid = {static_cast<unsigned>(2 * std::min<int64_t>(pair_tiles, std::max<long>(sms / 2, 1))), 1, 1};
+    g.dynamic_smem = kGemmPairStages * kGemmPairStageBytes + 1024;
+  }
   p.steps = {sa, sb, g};
   p.work = 2.0 * static_cast<double>(m) * static_cast<double>(n) * static_cast<double>(k);
   p.work_is_flops = true;
@@ -255,7 +277,9 @@ Result<void> launch_gemm(Executor &ex, const KernelPlan &p, const std::vector<vo
   if (!f_sa) return std::unexpected(f_sa.error());
   auto f_sb = ex.function("gemm", "gemm_split_bt");
   if (!f_sb) return std::unexpected(f_sb.error());
-  auto f_g = ex.function("gemm", gather ? "gemm_allgather" : "gemm");
+  const bool pair = p.steps[2].entry == "gemm_pair";
+  auto f_g = pair ? ex.function("gemm_pair", gather ? "gemm_pair_allgather" : "gemm_pair")
+                  : ex.function("gemm", gather ? "gemm_allgather" : "gemm");
   if (!f_g) return std::unexpected(f_g.error());
 
   {
@@ -290,9 +314,10 @@ Result<void> launch_gemm(Executor &ex, const KernelPlan &p, const std::vector<vo
   if (!t_ah) return std::unexpected(t_ah.error());
   auto t_al = make_map(a_lo, m, kGemmBM);
   if (!t_al) return std::unexpected(t_al.error());
-  auto t_bh = make_map(b_hi, n, kGemmBN);
+  const uint32_t b_box_rows = pair ? kGemmBN / 2 : kGemmBN;
+  auto t_bh = make_map(b_hi, n, b_box_rows);
   if (!t_bh) return std::unexpected(t_bh.error());
-  auto t_bl = make_map(b_lo, n, kGemmBN);
+  auto t_bl = make_map(b_lo, n, b_box_rows);
   if (!t_bl) return std::unexpected(t_bl.error());
 
   LaunchArgs args;
@@ -307,7 +332,7 @@ Result<void> launch_gemm(Executor &ex, const KernelPlan &p, const std::vector<vo
   args.add_scalar<uint64_t>(reinterpret_cast<uint64_t>(ex.status_word()));
   if (gather) args.add_struct_bytes(gather, sizeof *gather);
   LaunchStep step = p.steps[2];
-  if (gather) step.entry = "gemm_allgather";
+  if (gather) step.entry = pair ? "gemm_pair_allgather" : "gemm_allgather";
   return ex.launch(*f_g, step, args, stream);
 }
 
