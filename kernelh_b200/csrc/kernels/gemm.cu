@@ -6,112 +6,250 @@
 // k-tile staged in 8 KiB of static shared memory). Entry symbol `gemm`; the
 // first 21 parameters are the reference's: (A, B, C) as rank-2 memref
 // descriptors. The TMA-fed kernel then takes four tensor maps, the k-block
-// count and a status pointer.
+// count, a status pointer and the two scale-exponent arrays.
 //
-// Arithmetic: 3xTF32. Each operand is split once into hi = tf32(x) (round to
-// nearest, low 13 mantissa bits cleared) and lo = x - hi (exact in fp32), and
-// every k-step issues three tensor-core products into one fp32 accumulator in
-// tensor memory: lo.hi, hi.lo, hi.hi (lo.lo, ~2^-22 relative, is dropped).
+// Arithmetic: fp32 results from three fp16 tensor-core products ("3xFP16").
+// Every row of A and every column of B is first scaled by an exact power of
+// two that brings its largest magnitude into [2^14, 2^15), so the whole row
+// sits in the upper part of the fp16 range. A scaled value x is split into
+// hi = fp16(x) (round to nearest) and lo = fp16(x - hi) (the difference is exact
+// in fp32): 22 significand bits for every element within 2^-17 of its row's
+// largest, an absolute floor of 2^-38 of the largest below that. Every k-step
+// issues three tcgen05 products into one fp32 accumulator in tensor memory:
+// lo.hi, hi.lo, hi.hi (lo.lo, ~2^-22 relative, is dropped), and the epilogue
+// undoes the two scalings exactly with ldexp. This carries the same number of
+// significand bits as a tf32 hi/lo split at twice the tensor rate, and the fp16
+// array draws less power per product, so the SM clock the part sustains under
+// its power cap costs less too (measured on random operands: kind::f16 holds
+// 1625 TFLOP/s at 1340 MHz, kind::tf32 907-943 TFLOP/s at 1500-1560 MHz).
 // The tensor core's fp32 accumulation truncates, which biases long sums (the
 // error grew linearly with k when a whole k = 8192 product stayed in tensor
 // memory), so only K = 256 is accumulated there at a time: two accumulators
 // alternate, and each finished chunk is added into fp32 registers with
 // round-to-nearest by the epilogue warps while the next chunk is running.
 //
-// Two launches:
-//  gemm_split_a / gemm_split_bt  write A_hi, A_lo (m x kp) and B^T_hi, B^T_lo
-//      (n x kp) into scratch, kp = k rounded up to 32 and zero padded, so both
-//      tensor-core operands are K-major with 128-byte rows whatever k is.
-//  gemm  persistent CTAs (one per SM) walk the 128 x 256 tiles of C. Warp 0 feeds a 4-stage ring of
-//      {A_hi, A_lo, B_hi, B_lo} k-blocks (16 fp32 deep, 48 KiB per stage: three
-//      loads in flight hide the L2 latency that a 2 x 96 KiB ring left exposed) with
-//      TMA (64-byte swizzle, out-of-range rows read as zero, which is what
-//      makes ragged m and n work); warp 1 issues tcgen05.mma (M128 N256 K8,
-//      kind::tf32) and releases stages with tcgen05.commit; warps 2-9 drain the
-//      256-column fp32 accumulators from tensor memory chunk by chunk and store C.
+// Four launches:
+//  gemm_split_a   one warp per row of A: largest magnitude, scale exponent,
+//      then A_hi, A_lo (m x kp fp16, kp = k rounded up to 32, zero padded).
+//      It also clears the column maxima for the next launch.
+//  gemm_colmax_b  largest magnitude of every column of B (atomic max on the
+//      bit patterns of |b|, which order like the values).
+//  gemm_split_bt  B^T_hi, B^T_lo (n x kp fp16) through 64 x 32 shared-memory
+//      tiles, so both tensor-core operands are K-major with 64-byte rows.
+//  gemm           persistent two-CTA clusters (tcgen05 cta_group::2), one per
+//      pair of SMs, walk the 256 x 256 tiles of C. CTA r of a pair holds rows
+//      128r..128r+127 of the A tile and of the accumulator and only HALF of the
+//      B tile (128 of its 256 columns); one tcgen05.mma.cta_group::2 (M 256,
+//      N 256, K 16), issued by the leader CTA, runs both tensor cores and lets
+//      each read the other's half of B. Per CTA: warp 0 feeds a 6-stage ring of
+//      {A_hi, A_lo, B_hi half, B_lo half} k-blocks (32 fp16 deep, 32 KiB per
+//      stage) with TMA (64-byte swizzle; out-of-range rows read as zero, which
+//      is what makes ragged m and n work); warp 1 of the leader issues the MMAs
+//      and releases stages with tcgen05.commit; warps 2-9 drain the 256-column
+//      fp32 accumulators from tensor memory chunk by chunk and store C.
+//
+// Synchronisation across the pair (no multicast qualifier is used anywhere):
+//  * TMA loads of both CTAs complete on the LEADER's "full" barrier (the peer
+//    addresses it through the cluster window), which expects both halves.
+//  * the leader's tcgen05.commit arrives on the "empty" and "accumulator full"
+//    barriers of BOTH CTAs (one commit per CTA, peer address from mapa).
+//  * the epilogue warps of both CTAs arrive on the leader's "accumulator empty"
+//    barrier (the peer's arrivals are remote).
+// Every wait is bounded; the two cluster-wide barriers at the start and the
+// end are hardware barriers that every thread reaches.
 //
 // Tensor-bound: 2 m n k useful flops; three MMAs per k-step put the ceiling
-// at one third of the TF32 tensor rate.
+// at one third of the fp16 tensor rate.
+#include <cuda_fp16.h>
+
 #include "kh_tcgen05.cuh"
 
 namespace {
 
-constexpr int kBM = 128;
-constexpr int kBN = 256;
-constexpr int kBK = 16; // fp32 elements per k-block: one 64-byte swizzle row
-constexpr int kStages = 4;
-constexpr int kATileBytes = kBM * kBK * 4;                         // 8 KiB
-constexpr int kBTileBytes = kBN * kBK * 4;                         // 16 KiB
-constexpr int kStageBytes = 2 * kATileBytes + 2 * kBTileBytes;     // 48 KiB
-constexpr int kTmemCols = 512;      // two 256-column accumulators, used alternately
-constexpr int kChunkBlocks = 16;    // k-blocks accumulated in tensor memory before a drain (K = 256)
+constexpr int kBM = 128;     // rows per CTA (256 per pair)
+constexpr int kBN = 256;     // columns per pair
+constexpr int kBNHalf = 128; // columns of B one CTA stages
+constexpr int kBK = 32;      // fp16 elements per k-block: one 64-byte swizzle row
+constexpr int kStages = 6;
+constexpr int kTileBytes = kBM * kBK * 2;   // 8 KiB: A_hi, A_lo, B_hi half, B_lo half
+constexpr int kStageBytes = 4 * kTileBytes; // 32 KiB per CTA
+constexpr int kTmemCols = 512;              // two 256-column accumulators, used alternately
+constexpr int kChunkBlocks = 8;             // k-blocks accumulated in tensor memory before a drain (K = 256)
 constexpr int kEpilogueWarps = 8;
 constexpr int kThreads = 64 + 32 * kEpilogueWarps; // TMA warp + MMA warp + epilogue warps
-constexpr int kGroupM = 16; // m-tiles per rasterisation group (L2 reuse of B)
+constexpr int kGroupM = 8;                  // pair tiles (256 rows) per rasterisation group (L2 reuse of B)
+constexpr int kTargetExponent = 14;         // scaled row / column maxima lie in [2^14, 2^15)
 
-__device__ __forceinline__ float tf32_hi(float x) {
-  // round to nearest (ties away) on the 13 dropped bits, in integer arithmetic
-  uint32_t u = __float_as_uint(x);
-  u = (u + 0x1000u) & 0xFFFFE000u;
-  return __uint_as_float(u);
+// Power-of-two exponent that brings a row (column) whose largest magnitude is
+// `amax` into the target range; 0 for an all-zero or non-finite row.
+__device__ __forceinline__ int scale_shift(float amax) {
+  if (!(amax > 0.f) || amax > 3.402823466e+38f) return 0;
+  return kTargetExponent - ilogbf(amax);
 }
+
+__device__ __forceinline__ void split_fp16(float x, int shift, __half &hi, __half &lo) {
+  const float s = ldexpf(x, shift);
+  hi = __float2half_rn(s);
+  const float h = __half2float(hi);
+  lo = (h - h == 0.f) ? __float2half_rn(s - h) : __float2half_rn(0.f); // no inf - inf
+}
+
+// x * 2^e for |e| up to 378, exact unless the result leaves the normal fp32
+// range: 2^e is applied as three factors, each a normal fp32 power of two.
+__device__ __forceinline__ float pow2f(int e) { return __int_as_float((e + 127) << 23); }
+__device__ __forceinline__ float scale_pow2(float x, int e) {
+  const int e1 = max(-126, min(127, e));
+  const int r = e - e1;
+  const int e2 = max(-126, min(127, r));
+  return x * pow2f(e1) * pow2f(e2) * pow2f(r - e2);
+}
+
+// Ordered accesses for the epilogue (see the store loop of gemm_body).
+__device__ __forceinline__ int4 load_shift4(const int *p) {
+  int4 v;
+  asm volatile("ld.global.nc.v4.s32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+  return v;
+}
+__device__ __forceinline__ int load_shift(const int *p) {
+  int v;
+  asm volatile("ld.global.nc.s32 %0, [%1];" : "=r"(v) : "l"(p));
+  return v;
+}
+__device__ __forceinline__ void store_float4(float *p, float x, float y, float z, float w) {
+  asm volatile("st.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(p), "f"(x), "f"(y), "f"(z), "f"(w) : "memory");
+}
+__device__ __forceinline__ void store_float(float *p, float x) {
+  asm volatile("st.global.f32 [%0], %1;" ::"l"(p), "f"(x) : "memory");
+}
+
+struct alignas(16) Half8 {
+  __half2 v[4];
+};
 
 } // namespace
 
-// A (m x k, any strides) -> hi, lo (m x kp, contiguous), zero padded in k.
+// A (m x k, any strides) -> hi, lo (m x kp fp16, contiguous, zero padded in k)
+// and the scale exponent of every row. One warp per row.
 extern "C" __global__ void __launch_bounds__(256)
-gemm_split_a(KH_MEMREF2(const float, a), float *__restrict__ hi, float *__restrict__ lo, int64_t kp) {
+gemm_split_a(KH_MEMREF2(const float, a), __half *__restrict__ hi, __half *__restrict__ lo,
+             int *__restrict__ a_shift, uint32_t *__restrict__ b_amax, int64_t b_cols, int64_t kp) {
   const float *__restrict__ a = KH_DATA(a);
   const int64_t m = a_size0, k = a_size1;
-  const int64_t kp4 = kp >> 2;
-  const int64_t total = m * kp4;
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < b_cols;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x)
+    b_amax[i] = 0u;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const bool vec_ok = khd::is_aligned16(a) && a_stride1 == 1 && (a_stride0 & 3) == 0;
-  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
-       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
-    const int64_t r = i / kp4, c = (i - r * kp4) << 2;
-    float v[4];
-    if (vec_ok && c + 4 <= k) {
-      const float4 f = __ldcs(reinterpret_cast<const float4 *>(a + r * a_stride0 + c));
-      v[0] = f.x; v[1] = f.y; v[2] = f.z; v[3] = f.w;
+  for (int64_t r = static_cast<int64_t>(blockIdx.x) * 8 + warp; r < m; r += static_cast<int64_t>(gridDim.x) * 8) {
+    const float *row = a + r * a_stride0;
+    float amax = 0.f;
+    if (vec_ok) {
+      const int64_t k4 = k >> 2;
+      for (int64_t c = lane; c < k4; c += 32) {
+        const float4 f = __ldg(reinterpret_cast<const float4 *>(row) + c);
+        amax = fmaxf(amax, fmaxf(fmaxf(fabsf(f.x), fabsf(f.y)), fmaxf(fabsf(f.z), fabsf(f.w))));
+      }
+      for (int64_t c = (k4 << 2) + lane; c < k; c += 32) amax = fmaxf(amax, fabsf(row[c]));
     } else {
-#pragma unroll
-      for (int j = 0; j < 4; ++j) v[j] = (c + j < k) ? a[r * a_stride0 + (c + j) * a_stride1] : 0.f;
+      for (int64_t c = lane; c < k; c += 32) amax = fmaxf(amax, fabsf(row[c * a_stride1]));
     }
-    float4 h, l;
-    h.x = tf32_hi(v[0]); h.y = tf32_hi(v[1]); h.z = tf32_hi(v[2]); h.w = tf32_hi(v[3]);
-    l.x = v[0] - h.x; l.y = v[1] - h.y; l.z = v[2] - h.z; l.w = v[3] - h.w;
-    *reinterpret_cast<float4 *>(hi + r * kp + c) = h;
-    *reinterpret_cast<float4 *>(lo + r * kp + c) = l;
+    amax = khd::warp_max(amax);
+    const int shift = scale_shift(amax);
+    if (lane == 0) a_shift[r] = shift;
+    for (int64_t c = static_cast<int64_t>(lane) * 8; c < kp; c += 256) {
+      float v[8];
+      if (vec_ok && c + 8 <= k) {
+        const float4 f0 = __ldcs(reinterpret_cast<const float4 *>(row + c));
+        const float4 f1 = __ldcs(reinterpret_cast<const float4 *>(row + c + 4));
+        v[0] = f0.x; v[1] = f0.y; v[2] = f0.z; v[3] = f0.w;
+        v[4] = f1.x; v[5] = f1.y; v[6] = f1.z; v[7] = f1.w;
+      } else {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v[j] = (c + j < k) ? row[(c + j) * a_stride1] : 0.f;
+      }
+      Half8 h, l;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        __half h0, l0, h1, l1;
+        split_fp16(v[2 * j], shift, h0, l0);
+        split_fp16(v[2 * j + 1], shift, h1, l1);
+        h.v[j] = __halves2half2(h0, h1);
+        l.v[j] = __halves2half2(l0, l1);
+      }
+      *reinterpret_cast<Half8 *>(hi + r * kp + c) = h;
+      *reinterpret_cast<Half8 *>(lo + r * kp + c) = l;
+    }
   }
 }
 
-// B (k x n, any strides) -> B^T hi, lo (n x kp, contiguous), zero padded in k.
-// 32 x 32 tiles through shared memory so both sides stay coalesced.
+// Largest |b| of every column of B (k x n, any strides) into b_amax, which
+// gemm_split_a cleared. grid.x walks 1024-column chunks, grid.y 64-row slices.
 extern "C" __global__ void __launch_bounds__(256)
-gemm_split_bt(KH_MEMREF2(const float, b), float *__restrict__ hi, float *__restrict__ lo, int64_t kp) {
-  __shared__ float tile[32][33];
+gemm_colmax_b(KH_MEMREF2(const float, b), uint32_t *__restrict__ b_amax) {
   const float *__restrict__ b = KH_DATA(b);
   const int64_t k = b_size0, n = b_size1;
-  const int64_t tiles_n = (n + 31) >> 5, tiles_k = kp >> 5;
+  const bool vec_ok = khd::is_aligned16(b) && b_stride1 == 1 && (b_stride0 & 3) == 0;
+  const int64_t chunks_n = (n + 1023) >> 10, slices_k = (k + 63) >> 6;
+  for (int64_t t = blockIdx.x; t < chunks_n * slices_k; t += gridDim.x) {
+    const int64_t slice = t / chunks_n, chunk = t - slice * chunks_n;
+    const int64_t col = (chunk << 10) + threadIdx.x * 4;
+    const int64_t r0 = slice << 6, r1 = (r0 + 64 < k) ? r0 + 64 : k;
+    if (col >= n) continue;
+    float mx[4] = {0.f, 0.f, 0.f, 0.f};
+    if (vec_ok && col + 4 <= n) {
+#pragma unroll 8
+      for (int64_t r = r0; r < r1; ++r) {
+        const float4 f = __ldg(reinterpret_cast<const float4 *>(b + r * b_stride0 + col));
+        mx[0] = fmaxf(mx[0], fabsf(f.x)); mx[1] = fmaxf(mx[1], fabsf(f.y));
+        mx[2] = fmaxf(mx[2], fabsf(f.z)); mx[3] = fmaxf(mx[3], fabsf(f.w));
+      }
+    } else {
+      for (int64_t r = r0; r < r1; ++r)
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          if (col + j < n) mx[j] = fmaxf(mx[j], fabsf(b[r * b_stride0 + (col + j) * b_stride1]));
+    }
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+      if (col + j < n && mx[j] > 0.f) atomicMax(b_amax + col + j, __float_as_uint(mx[j]));
+  }
+}
+
+// B (k x n, any strides) -> B^T hi, lo (n x kp fp16, contiguous, zero padded in
+// k), every column scaled by the exponent its maximum gives; the k-tile-0
+// blocks also publish the exponents. 64 (k) x 32 (n) tiles through shared
+// memory so both sides stay coalesced.
+extern "C" __global__ void __launch_bounds__(256)
+gemm_split_bt(KH_MEMREF2(const float, b), __half *__restrict__ hi, __half *__restrict__ lo,
+              const uint32_t *__restrict__ b_amax, int *__restrict__ b_shift, int64_t kp) {
+  __shared__ float tile[64][33];
+  const float *__restrict__ b = KH_DATA(b);
+  const int64_t k = b_size0, n = b_size1;
+  const int64_t tiles_n = (n + 31) >> 5, tiles_k = (kp + 63) >> 6;
   const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5; // 32 x 8
   for (int64_t t = blockIdx.x; t < tiles_n * tiles_k; t += gridDim.x) {
     const int64_t tk = t / tiles_n, tn = t - tk * tiles_n;
-    const int64_t k0 = tk << 5, n0 = tn << 5;
+    const int64_t k0 = tk << 6, n0 = tn << 5;
     __syncthreads();
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
+    for (int j = 0; j < 8; ++j) {
       const int64_t kk = k0 + ty + 8 * j, nn = n0 + tx;
       tile[ty + 8 * j][tx] = (kk < k && nn < n) ? b[kk * b_stride0 + nn * b_stride1] : 0.f;
     }
     __syncthreads();
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
-      const int64_t nn = n0 + ty + 8 * j, kk = k0 + tx;
+      const int64_t nn = n0 + ty + 8 * j, kk = k0 + 2 * tx;
       if (nn < n) {
-        const float v = tile[tx][ty + 8 * j];
-        const float h = tf32_hi(v);
-        hi[nn * kp + kk] = h;
-        lo[nn * kp + kk] = v - h;
+        const int shift = scale_shift(__uint_as_float(__ldg(b_amax + nn)));
+        if (tk == 0 && tx == 0) b_shift[nn] = shift;
+        if (kk < kp) {
+          __half h0, l0, h1, l1;
+          split_fp16(tile[2 * tx][ty + 8 * j], shift, h0, l0);
+          split_fp16(tile[2 * tx + 1][ty + 8 * j], shift, h1, l1);
+          *reinterpret_cast<__half2 *>(hi + nn * kp + kk) = __halves2half2(h0, h1);
+          *reinterpret_cast<__half2 *>(lo + nn * kp + kk) = __halves2half2(l0, l1);
+        }
       }
     }
   }
@@ -133,8 +271,6 @@ struct TileCoord {
   int m0, n0;
 };
 
-// Tile order: groups of kGroupM m-tiles sweep n together, so the CTAs that run
-// at the same time share B column panels and a few A row panels in L2.
 __device__ __forceinline__ TileCoord tile_coord(int64_t tile, int64_t tiles_m, int64_t tiles_n) {
   const int64_t per_group = kGroupM * tiles_n;
   const int64_t group = tile / per_group;
@@ -143,12 +279,66 @@ __device__ __forceinline__ TileCoord tile_coord(int64_t tile, int64_t tiles_m, i
   const int64_t in_group = tile - group * per_group;
   const int64_t tile_m = first_m + in_group % rows_in_group;
   const int64_t tile_n = in_group / rows_in_group;
-  return {static_cast<int>(tile_m * kBM), static_cast<int>(tile_n * kBN)};
+  return {static_cast<int>(tile_m * 2 * kBM), static_cast<int>(tile_n * kBN)};
 }
 
-// A tile whose copy to the other replicas is still in progress. The eight
-// epilogue warps push it in 32 "units" each (warp w owns rows 16w..16w+15 of
-// the tile; a unit is half a row: 512 contiguous bytes, one float4 per lane).
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release;\n\tbarrier.cluster.wait.acquire;" ::: "memory");
+}
+// Address, in the cluster's shared window, of `local_addr` inside CTA `rank`.
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t local_addr, uint32_t rank) {
+  uint32_t out;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(out) : "r"(local_addr), "r"(rank));
+  return out;
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+// TMA tile load whose completion bytes are counted on a barrier given by a
+// cluster-window address (the leader's), data into this CTA's shared memory.
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t smem_dst, const khd::TensorMap *map, int x, int y,
+                                                 uint32_t bar_cluster_addr) {
+  asm volatile("cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.tile.mbarrier::complete_tx::bytes "
+               "[%0], [%1, {%2, %3}], [%4];" ::"r"(smem_dst),
+               "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(bar_cluster_addr)
+               : "memory");
+}
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t smem_result, uint32_t columns) {
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_result),
+               "r"(columns)
+               : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish_pair() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t columns) {
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(columns) : "memory");
+}
+// Instruction descriptor for kind::f16 with fp16 operands, fp32 accumulate, both
+// K-major: [4,6) D format 1 = f32; [7,10) / [10,13) A / B format 0 = f16;
+// [17,23) N >> 3; [24,29) M >> 4 (M counts the rows of the whole pair).
+__host__ __device__ constexpr uint32_t umma_idesc_f16(int m, int n) {
+  return (1u << 4) | (static_cast<uint32_t>(n >> 3) << 17) | (static_cast<uint32_t>(m >> 4) << 24);
+}
+// D[tmem of both CTAs] (+)= A[smem of each CTA] * B[halves in both CTAs' smem]; one thread of the leader issues.
+__device__ __forceinline__ void umma_f16_pair(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b,
+                                              uint32_t idesc, uint32_t accumulate) {
+  asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+               "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_d),
+               "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+               : "memory");
+}
+// Arrive on the barrier at `cluster_addr` once every MMA of the pair issued so far has finished.
+__device__ __forceinline__ void umma_commit_pair(uint32_t cluster_addr) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(cluster_addr)
+               : "memory");
+}
+
 struct PendingPush {
   int m0, n0;
   int next_unit; // 0..32; 32 = done
@@ -176,30 +366,23 @@ __device__ __forceinline__ void push_units(const GatherTargets &t, PendingPush &
   }
 }
 
-// The kernel body: a persistent CTA (one per SM) walks tiles blockIdx.x,
-// blockIdx.x + gridDim.x, ... The TMA and MMA warps run straight from one tile
-// into the next; the epilogue warps drain K chunks into registers, store the
-// finished tile, and (kGather) copy the previous tile to the other replicas a
-// slice at a time between chunk drains, so neither the store nor the NVLink
-// traffic ever stops the tensor cores.
-// `m`, `n`: extents of the product this launch forms. C is written through
-// (c, c_stride0, c_stride1) when kGather is false, and to the gather targets
-// (contiguous rows of n floats) when it is true.
 template <bool kGather>
 __device__ __forceinline__ void gemm_body(int64_t m, int64_t n, float *__restrict__ c, int64_t c_stride0,
-                                          int64_t c_stride1, const khd::TensorMap &tm_a_hi,
-                                          const khd::TensorMap &tm_a_lo, const khd::TensorMap &tm_b_hi,
-                                          const khd::TensorMap &tm_b_lo, int64_t k_blocks, uint32_t *status,
-                                          const GatherTargets *targets) {
+                                               int64_t c_stride1, const khd::TensorMap &tm_a_hi,
+                                               const khd::TensorMap &tm_a_lo, const khd::TensorMap &tm_b_hi,
+                                               const khd::TensorMap &tm_b_lo, int64_t k_blocks,
+                                               uint32_t *status, const int *__restrict__ a_shift,
+                                               const int *__restrict__ b_shift, const GatherTargets *targets) {
   extern __shared__ uint8_t smem_raw[];
-  // full[kStages], empty[kStages], acc_full[2], acc_empty[2], tile_stored
+  // full[kStages] (leader's are used), empty[kStages], acc_full[2], acc_empty[2] (leader's), tile_stored
   __shared__ __align__(8) uint64_t bars[2 * kStages + 5];
   __shared__ uint32_t s_tmem_base;
   __shared__ int s_abort;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank(); // 0 = leader
+  const bool leader_cta = rank == 0;
 
-  // 1024-byte aligned operand ring (the swizzle pattern is anchored there)
   const uint32_t ring = (khd::smem_u32(smem_raw) + 1023u) & ~1023u;
   const uint32_t full0 = khd::smem_u32(&bars[0]);
   const uint32_t empty0 = khd::smem_u32(&bars[kStages]);
@@ -207,9 +390,10 @@ __device__ __forceinline__ void gemm_body(int64_t m, int64_t n, float *__restric
   const uint32_t acc_empty0 = khd::smem_u32(&bars[2 * kStages + 2]);
   const uint32_t tile_stored = khd::smem_u32(&bars[2 * kStages + 4]);
 
-  const int64_t tiles_m = (m + kBM - 1) / kBM, tiles_n = (n + kBN - 1) / kBN;
+  const int64_t tiles_m = (m + 2 * kBM - 1) / (2 * kBM), tiles_n = (n + kBN - 1) / kBN;
   const int64_t num_tiles = tiles_m * tiles_n;
   const int64_t num_chunks = (k_blocks + kChunkBlocks - 1) / kChunkBlocks;
+  const int64_t first_tile = blockIdx.x >> 1, tile_step = gridDim.x >> 1;
 
   if (threadIdx.x == 0) {
     s_abort = 0;
@@ -219,7 +403,7 @@ __device__ __forceinline__ void gemm_body(int64_t m, int64_t n, float *__restric
     }
     for (int i = 0; i < 2; ++i) {
       khd::mbar_init(acc_full0 + 8 * i, 1);
-      khd::mbar_init(acc_empty0 + 8 * i, kEpilogueWarps); // one arrival per epilogue warp
+      khd::mbar_init(acc_empty0 + 8 * i, 2 * kEpilogueWarps); // the epilogue warps of both CTAs
     }
     khd::mbar_init(tile_stored, kEpilogueWarps * 32);
     khd::mbar_fence_init();
@@ -229,21 +413,25 @@ __device__ __forceinline__ void gemm_body(int64_t m, int64_t n, float *__restric
     khd::tma_prefetch_descriptor(&tm_b_lo);
   }
   if (warp == 1) {
-    khd::tmem_alloc(khd::smem_u32(&s_tmem_base), kTmemCols);
-    khd::tmem_relinquish();
+    tmem_alloc_pair(khd::smem_u32(&s_tmem_base), kTmemCols);
+    tmem_relinquish_pair();
   }
   khd::tc_fence_before_sync();
   __syncthreads();
+  cluster_sync_all(); // both CTAs' barriers exist before anything remote touches them
   khd::tc_fence_after_sync();
   const uint32_t tmem_base = s_tmem_base;
 
   if (warp == 0) {
-    // ---- TMA producer: the stage ring runs on across tiles ----------------------
+    // ---- TMA producer (both CTAs): own A rows, own half of B; bytes land on the
+    //      leader's full barrier ---------------------------------------------------------
     if (lane == 0) {
       uint32_t g_kb = 0;
       bool ok = true;
-      for (int64_t tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+      for (int64_t tile = first_tile; tile < num_tiles && ok; tile += tile_step) {
         const TileCoord tc = tile_coord(tile, tiles_m, tiles_n);
+        const int a_row = tc.m0 + static_cast<int>(rank) * kBM;
+        const int b_row = tc.n0 + static_cast<int>(rank) * kBNHalf;
         for (int64_t kb = 0; kb < k_blocks; ++kb, ++g_kb) {
           const int s = static_cast<int>(g_kb % kStages);
           const uint32_t phase = (g_kb / kStages) & 1u;
@@ -251,32 +439,28 @@ __device__ __forceinline__ void gemm_body(int64_t m, int64_t n, float *__restric
                               khd::kStatusEmptyWaitTimeout, g_kb);
           if (!ok) break;
           const uint32_t stage = ring + s * kStageBytes;
-          const uint32_t bar = full0 + 8 * s;
-          khd::mbar_arrive_expect_tx(bar, kStageBytes);
+          if (leader_cta) khd::mbar_arrive_expect_tx(full0 + 8 * s, 2 * kStageBytes);
+          const uint32_t bar = map_to_cta(full0 + 8 * s, 0);
           const int kx = static_cast<int>(kb * kBK);
-          khd::tma_load_2d(stage, &tm_a_hi, kx, tc.m0, bar);
-          khd::tma_load_2d(stage + kATileBytes, &tm_a_lo, kx, tc.m0, bar);
-          khd::tma_load_2d(stage + 2 * kATileBytes, &tm_b_hi, kx, tc.n0, bar);
-          khd::tma_load_2d(stage + 2 * kATileBytes + kBTileBytes, &tm_b_lo, kx, tc.n0, bar);
+          tma_load_2d_pair(stage, &tm_a_hi, kx, a_row, bar);
+          tma_load_2d_pair(stage + kTileBytes, &tm_a_lo, kx, a_row, bar);
+          tma_load_2d_pair(stage + 2 * kTileBytes, &tm_b_hi, kx, b_row, bar);
+          tma_load_2d_pair(stage + 3 * kTileBytes, &tm_b_lo, kx, b_row, bar);
         }
       }
     }
   } else if (warp == 1) {
-    // ---- MMA issuer: chunk buffers alternate across tiles too. The whole warp
-    //      walks the loop (waits and descriptor arithmetic are warp-uniform and
-    //      stay in uniform registers); only the tcgen05 instructions themselves
-    //      sit under the elected lane. ---------------------------------------------------
-    {
-      const bool leader = khd::elect_one();
-      constexpr uint32_t idesc = khd::umma_idesc_tf32(kBM, kBN);
+    // ---- MMA issuer: the leader CTA only. One instruction drives both tensor cores. ----
+    if (leader_cta) {
+      const bool elected = khd::elect_one();
+      constexpr uint32_t idesc = umma_idesc_f16(2 * kBM, kBN);
       uint32_t g_kb = 0, g_chunk = 0;
       bool ok = true;
-      for (int64_t tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+      for (int64_t tile = first_tile; tile < num_tiles && ok; tile += tile_step) {
         for (int64_t kb = 0; kb < k_blocks && ok; ++kb, ++g_kb) {
           const int in_chunk = static_cast<int>(kb % kChunkBlocks);
           const int buf = static_cast<int>(g_chunk & 1u);
           if (in_chunk == 0) {
-            // the accumulator buffer must have been drained (two chunks ago)
             ok = khd::mbar_wait(acc_empty0 + 8 * buf, ((g_chunk >> 1) & 1u) ^ 1u, &s_abort, status,
                                 khd::kStatusEpilogueWaitTimeout, g_chunk);
             ok = __all_sync(0xffffffffu, ok);
@@ -291,20 +475,26 @@ __device__ __forceinline__ void gemm_body(int64_t m, int64_t n, float *__restric
           const uint32_t d = tmem_base + static_cast<uint32_t>(buf * kBN);
           const uint32_t stage = ring + s * kStageBytes;
           const uint64_t a_hi = khd::umma_desc_k64(stage);
-          const uint64_t a_lo = a_hi + (kATileBytes >> 4);
-          const uint64_t b_hi = a_hi + (2 * kATileBytes >> 4);
-          const uint64_t b_lo = b_hi + (kBTileBytes >> 4);
+          const uint64_t a_lo = a_hi + (kTileBytes >> 4);
+          const uint64_t b_hi = a_hi + (2 * kTileBytes >> 4);
+          const uint64_t b_lo = a_hi + (3 * kTileBytes >> 4);
           const bool chunk_end = in_chunk == kChunkBlocks - 1 || kb == k_blocks - 1;
-          if (leader) {
+          const uint32_t empty_here = map_to_cta(empty0 + 8 * s, 0), empty_peer = map_to_cta(empty0 + 8 * s, 1);
+          const uint32_t accf_here = map_to_cta(acc_full0 + 8 * buf, 0), accf_peer = map_to_cta(acc_full0 + 8 * buf, 1);
+          if (elected) {
 #pragma unroll
-            for (int kk = 0; kk < kBK / 8; ++kk) {
-              const uint64_t adv = static_cast<uint64_t>(kk * 2); // 32 bytes >> 4
-              khd::umma_tf32_ss(d, a_lo + adv, b_hi + adv, idesc, (in_chunk | kk) != 0 ? 1u : 0u);
-              khd::umma_tf32_ss(d, a_hi + adv, b_lo + adv, idesc, 1u);
-              khd::umma_tf32_ss(d, a_hi + adv, b_hi + adv, idesc, 1u);
+            for (int kk = 0; kk < kBK / 16; ++kk) {
+              const uint64_t adv = static_cast<uint64_t>(kk * 2); // 16 fp16 = 32 bytes, >> 4
+              umma_f16_pair(d, a_lo + adv, b_hi + adv, idesc, (in_chunk | kk) != 0 ? 1u : 0u);
+              umma_f16_pair(d, a_hi + adv, b_lo + adv, idesc, 1u);
+              umma_f16_pair(d, a_hi + adv, b_hi + adv, idesc, 1u);
             }
-            khd::umma_commit(empty0 + 8 * s); // stage reusable once these MMAs retire
-            if (chunk_end) khd::umma_commit(acc_full0 + 8 * buf); // chunk complete: hand it to the epilogue
+            umma_commit_pair(empty_here); // the stage is free in both CTAs once these MMAs retire
+            umma_commit_pair(empty_peer);
+            if (chunk_end) {
+              umma_commit_pair(accf_here); // both epilogues may drain their half of the chunk
+              umma_commit_pair(accf_peer);
+            }
           }
           __syncwarp();
           if (chunk_end) ++g_chunk;
@@ -312,9 +502,7 @@ __device__ __forceinline__ void gemm_body(int64_t m, int64_t n, float *__restric
       }
     }
   } else {
-    // ---- epilogue: drain every K chunk from tensor memory into fp32 registers
-    //      (round-to-nearest adds), then store the tile. Two warps share each
-    //      32-lane quarter of tensor memory and take 128 columns each. ------------------
+    // ---- epilogue (both CTAs): this CTA's 128 rows of the pair's tile ------------------
     const int ew = warp - 2;
     const int quad = warp & 3;
     const int half = ew >> 2;
@@ -322,8 +510,9 @@ __device__ __forceinline__ void gemm_body(int64_t m, int64_t n, float *__restric
     uint32_t g_chunk = 0, stored_phase = 0;
     PendingPush pending{0, 0, 32};
     bool ok = true;
-    for (int64_t tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+    for (int64_t tile = first_tile; tile < num_tiles && ok; tile += tile_step) {
       const TileCoord tc = tile_coord(tile, tiles_m, tiles_n);
+      const int m0 = tc.m0 + static_cast<int>(rank) * kBM;
       float acc[kBN / 2];
 #pragma unroll
       for (int i = 0; i < kBN / 2; ++i) acc[i] = 0.f;
@@ -344,14 +533,13 @@ __device__ __forceinline__ void gemm_body(int64_t m, int64_t n, float *__restric
         }
         khd::tc_fence_before_sync();
         __syncwarp();
-        if (lane == 0) khd::mbar_arrive(acc_empty0 + 8 * buf);
-        // a slice of the previous tile goes out to the other replicas meanwhile
+        if (lane == 0) mbar_arrive_cluster(map_to_cta(acc_empty0 + 8 * buf, 0));
         if (kGather) push_units(*targets, pending, 1, ew, lane, m, n);
       }
       if (!ok) break;
-      if (kGather) push_units(*targets, pending, 32, ew, lane, m, n); // whatever is left of it
+      if (kGather) push_units(*targets, pending, 32, ew, lane, m, n);
 
-      const int64_t row = static_cast<int64_t>(tc.m0) + quad * 32 + lane;
+      const int64_t row = static_cast<int64_t>(m0) + quad * 32 + lane;
       const int64_t col0 = static_cast<int64_t>(tc.n0) + half * (kBN / 2);
       float *crow;
       int64_t cs1;
@@ -366,26 +554,33 @@ __device__ __forceinline__ void gemm_body(int64_t m, int64_t n, float *__restric
         vec_ok = c_stride1 == 1 && (c_stride0 & 3) == 0 && khd::is_aligned16(c);
       }
       if (row < m) {
+        // Undo the row and column scalings (exact: the factors are powers of two)
+        // and store, four columns at a time. The loads and stores are ordered
+        // (volatile asm) so that only one group of exponents is live at once.
+        const int row_shift = __ldg(a_shift + row);
         if (vec_ok && col0 + kBN / 2 <= n) {
 #pragma unroll
-          for (int j = 0; j < kBN / 2 / 4; ++j)
-            reinterpret_cast<float4 *>(crow + col0)[j] =
-                make_float4(acc[4 * j], acc[4 * j + 1], acc[4 * j + 2], acc[4 * j + 3]);
+          for (int j = 0; j < kBN / 2 / 4; ++j) {
+            const int4 sh = load_shift4(b_shift + col0 + 4 * j);
+            store_float4(crow + col0 + 4 * j, scale_pow2(acc[4 * j], -(row_shift + sh.x)),
+                         scale_pow2(acc[4 * j + 1], -(row_shift + sh.y)),
+                         scale_pow2(acc[4 * j + 2], -(row_shift + sh.z)),
+                         scale_pow2(acc[4 * j + 3], -(row_shift + sh.w)));
+          }
         } else {
 #pragma unroll
           for (int j = 0; j < kBN / 2; ++j)
-            if (col0 + j < n) crow[(col0 + j) * cs1] = acc[j];
+            if (col0 + j < n)
+              store_float(crow + (col0 + j) * cs1, scale_pow2(acc[j], -(row_shift + load_shift(b_shift + col0 + j))));
         }
       }
       if (kGather) {
-        // The tile is read back by other warps of this CTA when it is pushed: all
-        // epilogue threads meet on an mbarrier (a bounded wait, unlike bar.sync).
         __threadfence_block();
         khd::mbar_arrive(tile_stored);
         ok = khd::mbar_wait(tile_stored, stored_phase, &s_abort, status, khd::kStatusEpilogueWaitTimeout,
                             9000u);
         stored_phase ^= 1u;
-        pending = PendingPush{tc.m0, tc.n0, 0};
+        pending = PendingPush{m0, tc.n0, 0};
       }
     }
     if (kGather && ok) push_units(*targets, pending, 32, ew, lane, m, n);
@@ -393,13 +588,13 @@ __device__ __forceinline__ void gemm_body(int64_t m, int64_t n, float *__restric
 
   __syncthreads();
   if (s_abort) {
-    // A wait gave up: leave time for copies still in flight to land before the
-    // shared memory and tensor memory are released.
     for (int i = 0; i < 64; ++i) __nanosleep(10000);
   }
+  khd::tc_fence_before_sync();
+  cluster_sync_all(); // nothing remote may target a CTA that has already left
   if (warp == 1) {
     khd::tc_fence_after_sync();
-    khd::tmem_dealloc(tmem_base, kTmemCols);
+    tmem_dealloc_pair(tmem_base, kTmemCols);
   }
 }
 
@@ -409,31 +604,28 @@ extern "C" __global__ void __launch_bounds__(kThreads, 1)
 gemm(KH_MEMREF2(const float, a), KH_MEMREF2(const float, b), KH_MEMREF2(float, c),
      const __grid_constant__ khd::TensorMap tm_a_hi, const __grid_constant__ khd::TensorMap tm_a_lo,
      const __grid_constant__ khd::TensorMap tm_b_hi, const __grid_constant__ khd::TensorMap tm_b_lo,
-     int64_t k_blocks, uint32_t *status) {
+     int64_t k_blocks, uint32_t *status, const int *a_shift, const int *b_shift) {
   (void)a_alloc; (void)a_ptr; (void)a_off; (void)a_size1; (void)a_stride0; (void)a_stride1;
   (void)b_alloc; (void)b_ptr; (void)b_off; (void)b_size0; (void)b_stride0; (void)b_stride1;
   (void)c_alloc; (void)c_size0; (void)c_size1;
   gemm_body<false>(a_size0, b_size1, KH_DATA(c), c_stride0, c_stride1, tm_a_hi, tm_a_lo, tm_b_hi, tm_b_lo,
-                   k_blocks, status, nullptr);
+                   k_blocks, status, a_shift, b_shift, nullptr);
 }
 
-// gemm with the all-gather of the C row shards fused into its epilogue, for the
-// M-row-sharded product on several GPUs of one box. A is this rank's row shard,
-// B is whole; every finished C tile is stored into each rank's copy of the full
-// C (`targets`, peer-mapped pointers; this rank's own copy is one of them) at
-// this rank's row offset. No kernel ever loads from a peer; the stores are
-// ordinary global stores, complete when the kernel completes, and the caller
-// runs a barrier across ranks before anyone reads C. No counterpart in the
-// reference, which is single-GPU.
+// The M-row-sharded product with the all-gather fused into the epilogue: `a`
+// is this GPU's rows of A, the tensor maps cover its split, and every finished
+// tile is stored into this GPU's replica of the full C and then copied, a
+// 512-byte slice at a time between chunk drains of the next tile, to the other
+// replicas over NVLink (plain peer stores; the caller's barrier after the
+// kernel makes them visible to the peers).
 extern "C" __global__ void __launch_bounds__(kThreads, 1)
 gemm_allgather(KH_MEMREF2(const float, a), KH_MEMREF2(const float, b),
-               const __grid_constant__ khd::TensorMap tm_a_hi,
-               const __grid_constant__ khd::TensorMap tm_a_lo,
-               const __grid_constant__ khd::TensorMap tm_b_hi,
-               const __grid_constant__ khd::TensorMap tm_b_lo, int64_t k_blocks, uint32_t *status,
+               const __grid_constant__ khd::TensorMap tm_a_hi, const __grid_constant__ khd::TensorMap tm_a_lo,
+               const __grid_constant__ khd::TensorMap tm_b_hi, const __grid_constant__ khd::TensorMap tm_b_lo,
+               int64_t k_blocks, uint32_t *status, const int *a_shift, const int *b_shift,
                const __grid_constant__ GatherTargets targets) {
   (void)a_alloc; (void)a_ptr; (void)a_off; (void)a_size1; (void)a_stride0; (void)a_stride1;
   (void)b_alloc; (void)b_ptr; (void)b_off; (void)b_size0; (void)b_stride0; (void)b_stride1;
   gemm_body<true>(a_size0, b_size1, nullptr, 0, 0, tm_a_hi, tm_a_lo, tm_b_hi, tm_b_lo, k_blocks, status,
-                  &targets);
+                  a_shift, b_shift, &targets);
 }

@@ -7,7 +7,6 @@
 #include "registry.hpp"
 
 #include <algorithm>
-#include <cstdlib>
 #include <stdexcept>
 
 namespace kh {
@@ -194,19 +193,35 @@ Result<void> run_scan(Executor &ex, const KernelPlan &p, const std::vector<void 
 }
 
 // ---------------------------------------------------------------- gemm
-// kGemmBK: k padding of the split operands; kGemmTileK: k-block depth of one pipeline stage
-constexpr int kGemmBM = 128, kGemmBN = 256, kGemmBK = 32, kGemmTileK = 16, kGemmStages = 4;
-constexpr size_t kGemmStageBytes = 2 * (kGemmBM * kGemmTileK * 4) + 2 * (kGemmBN * kGemmTileK * 4);
-constexpr int kGemmPairStages = 6;
-constexpr size_t kGemmPairStageBytes = 4 * (kGemmBM * kGemmTileK * 4);
+// Two-CTA clusters own 256 x 256 tiles of C; a CTA stages 128 rows of A and 128
+// of the tile's B columns per 32-deep k-block (fp16 hi and lo of each).
+constexpr int kGemmBM = 128, kGemmBN = 256, kGemmBK = 32, kGemmStages = 6;
+constexpr size_t kGemmStageBytes = 4 * (kGemmBM * kGemmBK * 2);
 
-// Process-wide choice when the shape has no cta_pair key: KERNELH_GEMM_PAIR=0|1.
-bool gemm_pair_by_default() {
-  static const bool value = [] {
-    const char *e = std::getenv("KERNELH_GEMM_PAIR");
-    return e != nullptr && e[0] == '1';
-  }();
-  return value;
+// Scratch of one product, every part 256-byte aligned: the fp16 hi / lo splits
+// of A (m x kp) and B^T (n x kp), the scale exponents of A's rows and B's
+// columns, and the column maxima of B.
+struct GemmScratch {
+  size_t a_hi, a_lo, b_hi, b_lo, a_shift, b_amax, b_shift, total;
+};
+GemmScratch gemm_scratch(int64_t m, int64_t n, int64_t kp) {
+  const auto pad = [](size_t v) { return (v + 255) / 256 * 256; };
+  GemmScratch g{};
+  size_t at = 0;
+  const auto take = [&](size_t bytes) {
+    const size_t here = at;
+    at += pad(bytes);
+    return here;
+  };
+  g.a_hi = take(static_cast<size_t>(m * kp) * 2);
+  g.a_lo = take(static_cast<size_t>(m * kp) * 2);
+  g.b_hi = take(static_cast<size_t>(n * kp) * 2);
+  g.b_lo = take(static_cast<size_t>(n * kp) * 2);
+  g.a_shift = take(static_cast<size_t>(m) * 4);
+  g.b_amax = take(static_cast<size_t>(n) * 4);
+  g.b_shift = take(static_cast<size_t>(n) * 4);
+  g.total = at;
+  return g;
 }
 
 KernelPlan plan_gemm(const ShapeMap &shape, const DeviceLimits &l) {
@@ -218,37 +233,34 @@ KernelPlan plan_gemm(const ShapeMap &shape, const DeviceLimits &l) {
   p.shape = shape;
   p.tensors = {{"A", {m, k}, false}, {"B", {k, n}, false}, {"C", {m, n}, true}};
   const int64_t kp = (k + kGemmBK - 1) / kGemmBK * kGemmBK;
-  p.workspace_bytes = static_cast<size_t>((m + n) * kp) * 4 * 2;
+  p.workspace_bytes = gemm_scratch(m, n, kp).total;
   const long sms = sm_count(l);
   LaunchStep sa;
   sa.entry = "gemm_split_a";
   sa.block = {256, 1, 1};
-  sa.grid = {balanced_grid((m * kp / 4 + 255) / 256, sms, 8), 1, 1};
-  sa.param_count = 10;
+  sa.grid = {balanced_grid((m + 7) / 8, sms, 8), 1, 1}; // one warp per row
+  sa.param_count = 7 + 6;
+  LaunchStep cm;
+  cm.entry = "gemm_colmax_b";
+  cm.block = {256, 1, 1};
+  cm.grid = {balanced_grid(((n + 1023) / 1024) * ((k + 63) / 64), sms, 8), 1, 1};
+  cm.param_count = 7 + 1;
   LaunchStep sb;
   sb.entry = "gemm_split_bt";
   sb.block = {256, 1, 1};
-  sb.grid = {balanced_grid(((n + 31) / 32) * (kp / 32), sms, 8), 1, 1};
-  sb.param_count = 10;
+  sb.grid = {balanced_grid(((n + 31) / 32) * ((kp + 63) / 64), sms, 8), 1, 1};
+  sb.param_count = 7 + 5;
   LaunchStep g;
   g.entry = "gemm";
   g.block = {320, 1, 1};
-  const int64_t tiles = ((m + kGemmBM - 1) / kGemmBM) * ((n + kGemmBN - 1) / kGemmBN);
-  g.grid = {static_cast<unsigned>(std::min<int64_t>(tiles, sms)), 1, 1}; // persistent: one CTA per SM
+  g.cluster = 2;
+  const int64_t tiles = ((m + 2 * kGemmBM - 1) / (2 * kGemmBM)) * ((n + kGemmBN - 1) / kGemmBN);
+  // persistent: one cluster per pair of SMs
+  g.grid = {static_cast<unsigned>(2 * std::min<int64_t>(tiles, std::max<long>(sms / 2, 1))), 1, 1};
   g.dynamic_smem = kGemmStages * kGemmStageBytes + 1024;
-  g.param_count = 21 + 4 + 2;
+  g.param_count = 21 + 4 + 2 + 2;
   g.tmem_columns = 512;
-  // Optional shape key cta_pair=1: the same product on two-CTA clusters (gemm_pair.cu), each
-  // cluster owning a 256 x 256 tile; a CTA stages half of the B tile, its partner the other half.
-  const auto pair_key = shape.find("cta_pair");
-  if (pair_key != shape.end() ? pair_key->second != 0 : gemm_pair_by_default()) {
-    const int64_t pair_tiles = ((m + 2 * kGemmBM - 1) / (2 * kGemmBM)) * ((n + kGemmBN - 1) / kGemmBN);
-    g.entry = "gemm_pair";
-    g.cluster = 2;
-    g.grid = {static_cast<unsigned>(2 * std::min<int64_t>(pair_tiles, std::max<long>(sms / 2, 1))), 1, 1};
-    g.dynamic_smem = kGemmPairStages * kGemmPairStageBytes + 1024;
-  }
-  p.steps = {sa, sb, g};
+  p.steps = {sa, cm, sb, g};
   p.work = 2.0 * static_cast<double>(m) * static_cast<double>(n) * static_cast<double>(k);
   p.work_is_flops = true;
   return p;
@@ -266,58 +278,68 @@ Result<void> launch_gemm(Executor &ex, const KernelPlan &p, const std::vector<vo
                          StreamHandle stream, const GatherTargets *gather) {
   const int64_t m = p.tensors[0].shape[0], k = p.tensors[0].shape[1], n = p.tensors[1].shape[1];
   const int64_t kp = (k + kGemmBK - 1) / kGemmBK * kGemmBK;
-  auto ws = ex.workspace(p.workspace_bytes);
+  const GemmScratch lay = gemm_scratch(m, n, kp);
+  auto ws = ex.workspace(lay.total);
   if (!ws) return std::unexpected(ws.error());
-  float *a_hi = static_cast<float *>(*ws);
-  float *a_lo = a_hi + m * kp;
-  float *b_hi = a_lo + m * kp;
-  float *b_lo = b_hi + n * kp;
+  char *base = static_cast<char *>(*ws);
+  const auto at = [&](size_t off) { return reinterpret_cast<uint64_t>(base + off); };
 
   auto f_sa = ex.function("gemm", "gemm_split_a");
   if (!f_sa) return std::unexpected(f_sa.error());
+  auto f_cm = ex.function("gemm", "gemm_colmax_b");
+  if (!f_cm) return std::unexpected(f_cm.error());
   auto f_sb = ex.function("gemm", "gemm_split_bt");
   if (!f_sb) return std::unexpected(f_sb.error());
-  const bool pair = p.steps[2].entry == "gemm_pair";
-  auto f_g = pair ? ex.function("gemm_pair", gather ? "gemm_pair_allgather" : "gemm_pair")
-                  : ex.function("gemm", gather ? "gemm_allgather" : "gemm");
+  auto f_g = ex.function("gemm", gather ? "gemm_allgather" : "gemm");
   if (!f_g) return std::unexpected(f_g.error());
 
   {
     LaunchArgs args;
     args.add_memref(b[0], {m, k});
-    args.add_scalar<uint64_t>(reinterpret_cast<uint64_t>(a_hi));
-    args.add_scalar<uint64_t>(reinterpret_cast<uint64_t>(a_lo));
+    args.add_scalar<uint64_t>(at(lay.a_hi));
+    args.add_scalar<uint64_t>(at(lay.a_lo));
+    args.add_scalar<uint64_t>(at(lay.a_shift));
+    args.add_scalar<uint64_t>(at(lay.b_amax));
+    args.add_scalar<int64_t>(n);
     args.add_scalar<int64_t>(kp);
     if (auto r = ex.launch(*f_sa, p.steps[0], args, stream); !r) return r;
   }
   {
     LaunchArgs args;
     args.add_memref(b[1], {k, n});
-    args.add_scalar<uint64_t>(reinterpret_cast<uint64_t>(b_hi));
-    args.add_scalar<uint64_t>(reinterpret_cast<uint64_t>(b_lo));
-    args.add_scalar<int64_t>(kp);
-    if (auto r = ex.launch(*f_sb, p.steps[1], args, stream); !r) return r;
+    args.add_scalar<uint64_t>(at(lay.b_amax));
+    if (auto r = ex.launch(*f_cm, p.steps[1], args, stream); !r) return r;
   }
-  auto make_map = [&](const float *base, int64_t rows, uint32_t box_rows) {
+  {
+    LaunchArgs args;
+    args.add_memref(b[1], {k, n});
+    args.add_scalar<uint64_t>(at(lay.b_hi));
+    args.add_scalar<uint64_t>(at(lay.b_lo));
+    args.add_scalar<uint64_t>(at(lay.b_amax));
+    args.add_scalar<uint64_t>(at(lay.b_shift));
+    args.add_scalar<int64_t>(kp);
+    if (auto r = ex.launch(*f_sb, p.steps[2], args, stream); !r) return r;
+  }
+  auto make_map = [&](size_t offset, int64_t rows) {
     TensorMapSpec s;
-    s.global_address = base;
+    s.global_address = base + offset;
     s.rank = 2;
+    s.elem_bytes = 2;
     s.dims[0] = static_cast<uint64_t>(kp);
     s.dims[1] = static_cast<uint64_t>(rows);
-    s.strides_bytes[0] = static_cast<uint64_t>(kp) * 4;
-    s.box[0] = kGemmTileK;
-    s.box[1] = box_rows;
+    s.strides_bytes[0] = static_cast<uint64_t>(kp) * 2;
+    s.box[0] = kGemmBK;
+    s.box[1] = kGemmBM; // 128 rows of A, or 128 of the tile's 256 columns of B
     s.swizzle_bytes = 64;
     return ex.backend().encode_tensor_map(s);
   };
-  auto t_ah = make_map(a_hi, m, kGemmBM);
+  auto t_ah = make_map(lay.a_hi, m);
   if (!t_ah) return std::unexpected(t_ah.error());
-  auto t_al = make_map(a_lo, m, kGemmBM);
+  auto t_al = make_map(lay.a_lo, m);
   if (!t_al) return std::unexpected(t_al.error());
-  const uint32_t b_box_rows = pair ? kGemmBN / 2 : kGemmBN;
-  auto t_bh = make_map(b_hi, n, b_box_rows);
+  auto t_bh = make_map(lay.b_hi, n);
   if (!t_bh) return std::unexpected(t_bh.error());
-  auto t_bl = make_map(b_lo, n, b_box_rows);
+  auto t_bl = make_map(lay.b_lo, n);
   if (!t_bl) return std::unexpected(t_bl.error());
 
   LaunchArgs args;
@@ -328,11 +350,13 @@ Result<void> launch_gemm(Executor &ex, const KernelPlan &p, const std::vector<vo
   args.add_tensor_map(*t_al);
   args.add_tensor_map(*t_bh);
   args.add_tensor_map(*t_bl);
-  args.add_scalar<int64_t>(kp / kGemmTileK);
+  args.add_scalar<int64_t>(kp / kGemmBK);
   args.add_scalar<uint64_t>(reinterpret_cast<uint64_t>(ex.status_word()));
+  args.add_scalar<uint64_t>(at(lay.a_shift));
+  args.add_scalar<uint64_t>(at(lay.b_shift));
   if (gather) args.add_struct_bytes(gather, sizeof *gather);
-  LaunchStep step = p.steps[2];
-  if (gather) step.entry = pair ? "gemm_pair_allgather" : "gemm_allgather";
+  LaunchStep step = p.steps[3];
+  if (gather) step.entry = "gemm_allgather";
   return ex.launch(*f_g, step, args, stream);
 }
 

@@ -62,7 +62,7 @@ struct TensorMapSpec {
   uint64_t strides_bytes[4] = {0, 0, 0, 0}; // strides of dims 1..rank-1
   uint32_t box[5] = {1, 1, 1, 1, 1};        // elements
   int swizzle_bytes = 0;                    // 0, 32, 64 or 128
-  int elem_bytes = 4;                       // fp32 only
+  int elem_bytes = 4;                       // 4 = fp32, 2 = fp16
 };
 
 class Backend {

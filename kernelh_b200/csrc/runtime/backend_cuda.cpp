@@ -264,7 +264,10 @@ public:
 
   Result<TensorMapBytes> encode_tensor_map(const TensorMapSpec &s) override {
     if (s.rank < 1 || s.rank > 5) return fail(1, "encode_tensor_map: rank must be 1..5");
-    if (s.elem_bytes != 4) return fail(1, "encode_tensor_map: only 4-byte elements are supported");
+    if (s.elem_bytes != 4 && s.elem_bytes != 2)
+      return fail(1, "encode_tensor_map: elements must be fp32 (4 bytes) or fp16 (2 bytes)");
+    const CUtensorMapDataType dtype =
+        s.elem_bytes == 4 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
     CUtensorMapSwizzle sw = CU_TENSOR_MAP_SWIZZLE_NONE;
     switch (s.swizzle_bytes) {
     case 0: break;
@@ -284,7 +287,7 @@ public:
     CUtensorMap map;
     std::memset(&map, 0, sizeof map);
     if (CUresult r = api_.TensorMapEncodeTiled(
-            &map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, static_cast<cuuint32_t>(s.rank),
+            &map, dtype, static_cast<cuuint32_t>(s.rank),
             const_cast<void *>(s.global_address), dims, strides, box, estr,
             CU_TENSOR_MAP_INTERLEAVE_NONE, sw, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);

@@ -191,13 +191,15 @@ def test_plans_for_the_benchmark_configurations():
     p = kh.plan("scan", "n=1000000")
     assert p.work == 8000000.0 and p.workspace_bytes == (2 + 2 * 245) * 8
     p = kh.plan("gemm", "m=8192,n=8192,k=8192")
-    assert p.entry == b"gemm" and p.n_launches == 3 and p.grid[0] == 148 and p.block[0] == 320
-    assert p.dynamic_smem == 4 * 49152 + 1024 and p.tmem_columns == 512
-    assert p.workspace_bytes == 2 * 8192 * 8192 * 4 * 2
+    # split A, column maxima of B, split B^T, then 74 two-CTA clusters
+    assert p.entry == b"gemm" and p.n_launches == 4 and p.grid[0] == 148 and p.block[0] == 320
+    assert p.dynamic_smem == 6 * 32768 + 1024 and p.tmem_columns == 512
+    assert p.workspace_bytes == 4 * 8192 * 8192 * 2 + 3 * 8192 * 4  # fp16 hi/lo of A and B^T, exponents, maxima
     assert p.work == 1099511627776.0 and p.work_is_flops
     assert kh.verify_launch("sm_100a", p.block[0], tuple(p.grid), 48, p.dynamic_smem) == ""
     p = kh.plan("gemm", "m=1000,n=1000,k=1000")
-    assert p.grid[0] == 8 * 4 and p.workspace_bytes == 2000 * 1024 * 8  # fewer tiles than SMs
+    assert p.grid[0] == 2 * 4 * 4  # 16 tiles of 256 x 256, a cluster each
+    assert p.workspace_bytes == 4 * 1000 * 1024 * 2 + 3 * 4096
     p = kh.plan("attention", "batch=8,heads=16,seq=1024,head_dim=64")
     assert p.grid[0] == 128 * 8 and p.param_count == 51 and p.work == 34359738368.0
     assert kh.verify_launch("sm_100a", p.block[0], tuple(p.grid), 80, p.dynamic_smem) == ""
