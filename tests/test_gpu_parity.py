@@ -216,7 +216,7 @@ def test_gemm_reference_pattern(ctx, oracle, size):
     c = run(ctx, "gemm", f"m={size},n={size},k={size}", [a, b], (size, size))
     ref = oracle.gemm_ref(a, b)
     assert oracle.compare(c, ref).rel_frobenius <= 1e-5  # the reference's bound
-    assert oracle.bit_mismatches(c, ref) == 0            # exact integers survive the 3xTF32 split
+    assert oracle.bit_mismatches(c, ref) == 0            # exact integers survive the scaled fp16 hi/lo split
 
 
 def test_gemm_negative_control(ctx, oracle):
@@ -236,6 +236,35 @@ def test_gemm_uniform_inputs_keep_fp32_accuracy(ctx, oracle, m, n, k):
     assert cmp_.non_finite == 0
     assert cmp_.rel_frobenius <= 1e-5
     assert cmp_.max_rel <= REL * math.sqrt(k)
+
+
+@pytest.mark.parametrize("kind", ["rows_and_columns", "inside_rows", "tiny_times_huge"])
+def test_gemm_is_insensitive_to_operand_scaling(ctx, oracle, kind):
+    """The fp16 splits see every row of A and column of B scaled into one fixed
+    range, so magnitudes from 1e-38 to 1e+15 must not cost accuracy: the error
+    stays a small multiple of fp32 epsilon of (|A| |B|) element by element."""
+    m, n, k = 512, 768, 1000
+    a = oracle.normal((m, k), oracle.BASE_SEED + 7, 0, 1)
+    b = oracle.normal((k, n), oracle.BASE_SEED + 8, 0, 1)
+    rng = np.random.default_rng(5)
+    if kind == "rows_and_columns":
+        a *= (10.0 ** rng.integers(-15, 16, (m, 1))).astype(np.float32)
+        b *= (10.0 ** rng.integers(-15, 16, (1, n))).astype(np.float32)
+        a[3] = 0
+        b[:, 5] = 0
+    elif kind == "inside_rows":
+        a *= (2.0 ** rng.integers(-30, 1, (m, k))).astype(np.float32)
+        b *= (2.0 ** rng.integers(-30, 1, (k, n))).astype(np.float32)
+    else:
+        a *= np.float32(1e-38)
+        b *= np.float32(1e30)
+    c = run(ctx, "gemm", f"m={m},n={n},k={k}", [a, b], (m, n)).astype(np.float64)
+    ref = a.astype(np.float64) @ b.astype(np.float64)
+    bound = np.abs(a).astype(np.float64) @ np.abs(b).astype(np.float64)
+    assert np.all(np.isfinite(c))
+    assert np.max(np.abs(c - ref) / np.maximum(bound, 1e-300)) <= 4e-6
+    if kind == "rows_and_columns":
+        assert not c[3].any() and not c[:, 5].any()
 
 
 def test_gemm_8192_sampled_rows_and_scaling_property(ctx, oracle):
