@@ -16,6 +16,7 @@ from __future__ import annotations
 import argparse
 import json
 import os
+import re
 import subprocess
 import sys
 import threading
@@ -387,13 +388,13 @@ def gpu_arm(args) -> None:
     # the kernel is timed inside a back-to-back loop.
     peak = peaks["bf16_tflops_sustained"] / 3.0
     traffic = None
-    tpath = os.path.join(ROOT, "profiles", "gemm_traffic.json")
-    if os.path.exists(tpath):
+    # DRAM bytes of one 8192^3 launch, from the committed ncu capture (text summary)
+    tpath = os.path.join(ROOT, "profiles", "gemm_8192_dram_traffic.md")
+    if size == 8192 and os.path.exists(tpath):
         with open(tpath) as f:
-            tj = json.load(f)
-        traffic = tj.get("dram_bytes_per_launch_8192")
-        if traffic is not None and world > 1:
-            traffic = traffic / world
+            found = re.search(r"^dram_bytes_per_launch:\s*(\d+)", f.read(), re.M)
+        if found:
+            traffic = int(found.group(1)) / world
     roofline = {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
                 "frac": achieved / peak, "traffic": traffic, "kernel": ("gemm_allgather" if gather == "p2p" else "gemm") + " (tcgen05 3xFP16)",
                 "kernel_ms": kernel_ms, "split_ms": (prof["gemm_split_a"][1] + prof["gemm_colmax_b"][1] + prof["gemm_split_bt"][1]) / gemm_launches,
@@ -444,8 +445,9 @@ def gpu_arm(args) -> None:
                        "h2d_bytes_per_step": int(a_h.numel() * 4 + b_h.numel() * 4),
                        "d2h_bytes_per_step": int(c_h.numel() * 4), "steps": e2e_steps,
                        "ms_per_step": dt.item() * 1e3,
-                       "note": "kh_run_host on pinned host buffers: H2D of the A shard and B, split, gemm, "
-                               "D2H of the C shard, per rank"}
+                       "note": "kh_run_host on pinned host buffers, per rank: H2D of B, then the A shard in "
+                               "about eight row blocks; each block is split and multiplied while the next is "
+                               "on the wire and the finished rows of C go back over the other direction of the link"}
         e2e_ok = torch.equal(c_h, c_shard.cpu())
         line["e2e"]["matches_device_path"] = bool(e2e_ok)
         del a_h, b_h, c_h

@@ -224,16 +224,10 @@ GemmScratch gemm_scratch(int64_t m, int64_t n, int64_t kp) {
   return g;
 }
 
-KernelPlan plan_gemm(const ShapeMap &shape, const DeviceLimits &l) {
-  const int64_t m = require_positive(shape, "gemm", "m");
-  const int64_t n = require_positive(shape, "gemm", "n");
-  const int64_t k = require_positive(shape, "gemm", "k");
-  KernelPlan p;
-  p.kernel = "gemm";
-  p.shape = shape;
-  p.tensors = {{"A", {m, k}, false}, {"B", {k, n}, false}, {"C", {m, n}, true}};
+// The four launches of one m x n x k product: split A, column maxima of B,
+// split B^T, multiply.
+std::vector<LaunchStep> gemm_steps(int64_t m, int64_t n, int64_t k, const DeviceLimits &l) {
   const int64_t kp = (k + kGemmBK - 1) / kGemmBK * kGemmBK;
-  p.workspace_bytes = gemm_scratch(m, n, kp).total;
   const long sms = sm_count(l);
   LaunchStep sa;
   sa.entry = "gemm_split_a";
@@ -260,7 +254,20 @@ KernelPlan plan_gemm(const ShapeMap &shape, const DeviceLimits &l) {
   g.dynamic_smem = kGemmStages * kGemmStageBytes + 1024;
   g.param_count = 21 + 4 + 2 + 2;
   g.tmem_columns = 512;
-  p.steps = {sa, cm, sb, g};
+  return {sa, cm, sb, g};
+}
+
+KernelPlan plan_gemm(const ShapeMap &shape, const DeviceLimits &l) {
+  const int64_t m = require_positive(shape, "gemm", "m");
+  const int64_t n = require_positive(shape, "gemm", "n");
+  const int64_t k = require_positive(shape, "gemm", "k");
+  KernelPlan p;
+  p.kernel = "gemm";
+  p.shape = shape;
+  p.tensors = {{"A", {m, k}, false}, {"B", {k, n}, false}, {"C", {m, n}, true}};
+  const int64_t kp = (k + kGemmBK - 1) / kGemmBK * kGemmBK;
+  p.workspace_bytes = gemm_scratch(m, n, kp).total;
+  p.steps = gemm_steps(m, n, k, l);
   p.work = 2.0 * static_cast<double>(m) * static_cast<double>(n) * static_cast<double>(k);
   p.work_is_flops = true;
   return p;
@@ -274,95 +281,202 @@ struct GatherTargets {
   int64_t row_offset;
 };
 
-Result<void> launch_gemm(Executor &ex, const KernelPlan &p, const std::vector<void *> &b,
-                         StreamHandle stream, const GatherTargets *gather) {
-  const int64_t m = p.tensors[0].shape[0], k = p.tensors[0].shape[1], n = p.tensors[1].shape[1];
-  const int64_t kp = (k + kGemmBK - 1) / kGemmBK * kGemmBK;
-  const GemmScratch lay = gemm_scratch(m, n, kp);
-  auto ws = ex.workspace(lay.total);
+// One product being enqueued: sizes, scratch and the entry points.
+struct GemmJob {
+  Executor &ex;
+  int64_t m, n, k, kp;
+  GemmScratch lay;
+  char *base = nullptr; // scratch
+  KernelFunction split_a, colmax_b, split_bt, multiply, multiply_gather;
+  uint64_t at(size_t off) const { return reinterpret_cast<uint64_t>(base + off); }
+};
+
+Result<GemmJob> gemm_job(Executor &ex, int64_t m, int64_t n, int64_t k) {
+  GemmJob j{ex, m, n, k, (k + kGemmBK - 1) / kGemmBK * kGemmBK, {}, nullptr, {}, {}, {}, {}, {}};
+  j.lay = gemm_scratch(m, n, j.kp);
+  auto ws = ex.workspace(j.lay.total);
   if (!ws) return std::unexpected(ws.error());
-  char *base = static_cast<char *>(*ws);
-  const auto at = [&](size_t off) { return reinterpret_cast<uint64_t>(base + off); };
+  j.base = static_cast<char *>(*ws);
+  const std::pair<const char *, KernelFunction *> entries[] = {{"gemm_split_a", &j.split_a},
+                                                               {"gemm_colmax_b", &j.colmax_b},
+                                                               {"gemm_split_bt", &j.split_bt},
+                                                               {"gemm", &j.multiply},
+                                                               {"gemm_allgather", &j.multiply_gather}};
+  for (const auto &[name, slot] : entries) {
+    auto f = ex.function("gemm", name);
+    if (!f) return std::unexpected(f.error());
+    *slot = *f;
+  }
+  return j;
+}
 
-  auto f_sa = ex.function("gemm", "gemm_split_a");
-  if (!f_sa) return std::unexpected(f_sa.error());
-  auto f_cm = ex.function("gemm", "gemm_colmax_b");
-  if (!f_cm) return std::unexpected(f_cm.error());
-  auto f_sb = ex.function("gemm", "gemm_split_bt");
-  if (!f_sb) return std::unexpected(f_sb.error());
-  auto f_g = ex.function("gemm", gather ? "gemm_allgather" : "gemm");
-  if (!f_g) return std::unexpected(f_g.error());
+// Column maxima, exponents and the fp16 splits of B^T. `clear_maxima`: zero the
+// maxima here (otherwise the gemm_split_a launched before this did).
+Result<void> gemm_enqueue_b(const GemmJob &j, const void *b_dev, const std::vector<LaunchStep> &steps,
+                            StreamHandle stream, bool clear_maxima) {
+  if (clear_maxima)
+    if (auto r = j.ex.backend().memset32_async(j.base + j.lay.b_amax, 0, static_cast<size_t>(j.n), stream); !r)
+      return r;
+  {
+    LaunchArgs args;
+    args.add_memref(const_cast<void *>(b_dev), {j.k, j.n});
+    args.add_scalar<uint64_t>(j.at(j.lay.b_amax));
+    if (auto r = j.ex.launch(j.colmax_b, steps[1], args, stream); !r) return r;
+  }
+  LaunchArgs args;
+  args.add_memref(const_cast<void *>(b_dev), {j.k, j.n});
+  args.add_scalar<uint64_t>(j.at(j.lay.b_hi));
+  args.add_scalar<uint64_t>(j.at(j.lay.b_lo));
+  args.add_scalar<uint64_t>(j.at(j.lay.b_amax));
+  args.add_scalar<uint64_t>(j.at(j.lay.b_shift));
+  args.add_scalar<int64_t>(j.kp);
+  return j.ex.launch(j.split_bt, steps[2], args, stream);
+}
 
-  {
-    LaunchArgs args;
-    args.add_memref(b[0], {m, k});
-    args.add_scalar<uint64_t>(at(lay.a_hi));
-    args.add_scalar<uint64_t>(at(lay.a_lo));
-    args.add_scalar<uint64_t>(at(lay.a_shift));
-    args.add_scalar<uint64_t>(at(lay.b_amax));
-    args.add_scalar<int64_t>(n);
-    args.add_scalar<int64_t>(kp);
-    if (auto r = ex.launch(*f_sa, p.steps[0], args, stream); !r) return r;
-  }
-  {
-    LaunchArgs args;
-    args.add_memref(b[1], {k, n});
-    args.add_scalar<uint64_t>(at(lay.b_amax));
-    if (auto r = ex.launch(*f_cm, p.steps[1], args, stream); !r) return r;
-  }
-  {
-    LaunchArgs args;
-    args.add_memref(b[1], {k, n});
-    args.add_scalar<uint64_t>(at(lay.b_hi));
-    args.add_scalar<uint64_t>(at(lay.b_lo));
-    args.add_scalar<uint64_t>(at(lay.b_amax));
-    args.add_scalar<uint64_t>(at(lay.b_shift));
-    args.add_scalar<int64_t>(kp);
-    if (auto r = ex.launch(*f_sb, p.steps[2], args, stream); !r) return r;
-  }
-  auto make_map = [&](size_t offset, int64_t rows) {
+// Exponents and fp16 splits of rows [row0, row0 + rows) of A, read from `a_rows`.
+// `clear_cols` > 0 also zeroes that many column maxima of B for a later gemm_enqueue_b.
+Result<void> gemm_enqueue_a(const GemmJob &j, const void *a_rows, int64_t row0, int64_t rows,
+                            const LaunchStep &step, StreamHandle stream, int64_t clear_cols) {
+  LaunchArgs args;
+  args.add_memref(const_cast<void *>(a_rows), {rows, j.k});
+  args.add_scalar<uint64_t>(j.at(j.lay.a_hi + static_cast<size_t>(row0 * j.kp) * 2));
+  args.add_scalar<uint64_t>(j.at(j.lay.a_lo + static_cast<size_t>(row0 * j.kp) * 2));
+  args.add_scalar<uint64_t>(j.at(j.lay.a_shift + static_cast<size_t>(row0) * 4));
+  args.add_scalar<uint64_t>(j.at(j.lay.b_amax));
+  args.add_scalar<int64_t>(clear_cols);
+  args.add_scalar<int64_t>(j.kp);
+  return j.ex.launch(j.split_a, step, args, stream);
+}
+
+// C rows [row0, row0 + rows) = (split rows of A) . (split B): `c_rows` is where
+// row `row0` of C goes (ignored when gathering).
+Result<void> gemm_enqueue_multiply(const GemmJob &j, const void *a_rows, const void *b_dev, void *c_rows,
+                                   int64_t row0, int64_t rows, LaunchStep step, StreamHandle stream,
+                                   const GatherTargets *gather) {
+  auto make_map = [&](size_t offset, int64_t map_rows) {
     TensorMapSpec s;
-    s.global_address = base + offset;
+    s.global_address = j.base + offset;
     s.rank = 2;
     s.elem_bytes = 2;
-    s.dims[0] = static_cast<uint64_t>(kp);
-    s.dims[1] = static_cast<uint64_t>(rows);
-    s.strides_bytes[0] = static_cast<uint64_t>(kp) * 2;
+    s.dims[0] = static_cast<uint64_t>(j.kp);
+    s.dims[1] = static_cast<uint64_t>(map_rows);
+    s.strides_bytes[0] = static_cast<uint64_t>(j.kp) * 2;
     s.box[0] = kGemmBK;
     s.box[1] = kGemmBM; // 128 rows of A, or 128 of the tile's 256 columns of B
     s.swizzle_bytes = 64;
-    return ex.backend().encode_tensor_map(s);
+    return j.ex.backend().encode_tensor_map(s);
   };
-  auto t_ah = make_map(lay.a_hi, m);
+  const size_t a_off = static_cast<size_t>(row0 * j.kp) * 2;
+  auto t_ah = make_map(j.lay.a_hi + a_off, rows);
   if (!t_ah) return std::unexpected(t_ah.error());
-  auto t_al = make_map(lay.a_lo, m);
+  auto t_al = make_map(j.lay.a_lo + a_off, rows);
   if (!t_al) return std::unexpected(t_al.error());
-  auto t_bh = make_map(lay.b_hi, n);
+  auto t_bh = make_map(j.lay.b_hi, j.n);
   if (!t_bh) return std::unexpected(t_bh.error());
-  auto t_bl = make_map(lay.b_lo, n);
+  auto t_bl = make_map(j.lay.b_lo, j.n);
   if (!t_bl) return std::unexpected(t_bl.error());
 
   LaunchArgs args;
-  args.add_memref(b[0], {m, k});
-  args.add_memref(b[1], {k, n});
-  if (!gather) args.add_memref(b[2], {m, n});
+  args.add_memref(const_cast<void *>(a_rows), {rows, j.k});
+  args.add_memref(const_cast<void *>(b_dev), {j.k, j.n});
+  if (!gather) args.add_memref(c_rows, {rows, j.n});
   args.add_tensor_map(*t_ah);
   args.add_tensor_map(*t_al);
   args.add_tensor_map(*t_bh);
   args.add_tensor_map(*t_bl);
-  args.add_scalar<int64_t>(kp / kGemmBK);
-  args.add_scalar<uint64_t>(reinterpret_cast<uint64_t>(ex.status_word()));
-  args.add_scalar<uint64_t>(at(lay.a_shift));
-  args.add_scalar<uint64_t>(at(lay.b_shift));
-  if (gather) args.add_struct_bytes(gather, sizeof *gather);
-  LaunchStep step = p.steps[3];
-  if (gather) step.entry = "gemm_allgather";
-  return ex.launch(*f_g, step, args, stream);
+  args.add_scalar<int64_t>(j.kp / kGemmBK);
+  args.add_scalar<uint64_t>(reinterpret_cast<uint64_t>(j.ex.status_word()));
+  args.add_scalar<uint64_t>(j.at(j.lay.a_shift + static_cast<size_t>(row0) * 4));
+  args.add_scalar<uint64_t>(j.at(j.lay.b_shift));
+  if (gather) {
+    args.add_struct_bytes(gather, sizeof *gather);
+    step.entry = "gemm_allgather";
+  }
+  return j.ex.launch(gather ? j.multiply_gather : j.multiply, step, args, stream);
+}
+
+Result<void> launch_gemm(Executor &ex, const KernelPlan &p, const std::vector<void *> &b,
+                         StreamHandle stream, const GatherTargets *gather) {
+  const int64_t m = p.tensors[0].shape[0], k = p.tensors[0].shape[1], n = p.tensors[1].shape[1];
+  auto job = gemm_job(ex, m, n, k);
+  if (!job) return std::unexpected(job.error());
+  if (auto r = gemm_enqueue_a(*job, b[0], 0, m, p.steps[0], stream, n); !r) return r;
+  if (auto r = gemm_enqueue_b(*job, b[1], p.steps, stream, false); !r) return r;
+  return gemm_enqueue_multiply(*job, b[0], b[1], gather ? nullptr : b[2], 0, m, p.steps[3], stream, gather);
 }
 
 Result<void> run_gemm(Executor &ex, const KernelPlan &p, const std::vector<void *> &b,
                       StreamHandle stream) {
   return launch_gemm(ex, p, b, stream, nullptr);
+}
+
+// Host-buffer form of the product, pipelined over PCIe: B goes up first and is
+// split; A then goes up in row blocks, and while block i+1 is on the wire,
+// block i is split and multiplied and the finished rows of C of block i-1 go
+// back down (the two directions of the link run at once). `dev` are device
+// staging buffers for A, B and C.
+Result<void> run_gemm_host(Executor &ex, const KernelPlan &p, const std::vector<void *> &host,
+                           const std::vector<void *> &dev, const HostStreams &hs) {
+  const int64_t m = p.tensors[0].shape[0], k = p.tensors[0].shape[1], n = p.tensors[1].shape[1];
+  Backend &be = ex.backend();
+  auto job = gemm_job(ex, m, n, k);
+  if (!job) return std::unexpected(job.error());
+  // row blocks: about eight, whole 256-row cluster tiles
+  const int64_t block_rows = std::max<int64_t>(256, ((m + 7) / 8 + 255) / 256 * 256);
+  const int64_t blocks = (m + block_rows - 1) / block_rows;
+  std::vector<EventHandle> events;
+  const auto fresh_event = [&]() -> Result<EventHandle> {
+    auto e = be.event_create();
+    if (e) events.push_back(*e);
+    return e;
+  };
+  const auto body = [&]() -> Result<void> {
+    if (host[1] != nullptr)
+      if (auto r = be.memcpy_h2d_async(dev[1], host[1], static_cast<size_t>(k * n) * 4, hs.in); !r) return r;
+    auto b_up = fresh_event();
+    if (!b_up) return std::unexpected(b_up.error());
+    if (auto r = be.event_record(*b_up, hs.in); !r) return r;
+    if (auto r = be.stream_wait_event(hs.compute, *b_up); !r) return r;
+    if (auto r = gemm_enqueue_b(*job, dev[1], p.steps, hs.compute, true); !r) return r;
+    for (int64_t i = 0; i < blocks; ++i) {
+      const int64_t row0 = i * block_rows, rows = std::min(block_rows, m - row0);
+      char *a_rows = static_cast<char *>(dev[0]) + static_cast<size_t>(row0 * k) * 4;
+      char *c_rows = static_cast<char *>(dev[2]) + static_cast<size_t>(row0 * n) * 4;
+      if (host[0] != nullptr)
+        if (auto r = be.memcpy_h2d_async(a_rows, static_cast<const char *>(host[0]) + static_cast<size_t>(row0 * k) * 4,
+                                         static_cast<size_t>(rows * k) * 4, hs.in);
+            !r)
+          return r;
+      auto a_up = fresh_event();
+      if (!a_up) return std::unexpected(a_up.error());
+      if (auto r = be.event_record(*a_up, hs.in); !r) return r;
+      if (auto r = be.stream_wait_event(hs.compute, *a_up); !r) return r;
+      const std::vector<LaunchStep> steps = gemm_steps(rows, n, k, ex.limits());
+      if (auto r = gemm_enqueue_a(*job, a_rows, row0, rows, steps[0], hs.compute, 0); !r) return r;
+      if (auto r = gemm_enqueue_multiply(*job, a_rows, dev[1], c_rows, row0, rows, steps[3], hs.compute, nullptr); !r)
+        return r;
+      auto c_done = fresh_event();
+      if (!c_done) return std::unexpected(c_done.error());
+      if (auto r = be.event_record(*c_done, hs.compute); !r) return r;
+      if (auto r = be.stream_wait_event(hs.out, *c_done); !r) return r;
+      if (host[2] != nullptr)
+        if (auto r = be.memcpy_d2h_async(static_cast<char *>(host[2]) + static_cast<size_t>(row0 * n) * 4, c_rows,
+                                         static_cast<size_t>(rows * n) * 4, hs.out);
+            !r)
+          return r;
+    }
+    return {};
+  };
+  Result<void> enqueued = body();
+  // drain all three streams whatever happened, then report the first failure
+  Result<void> s_in = be.stream_synchronize(hs.in);
+  Result<void> s_compute = ex.synchronize(hs.compute);
+  Result<void> s_out = be.stream_synchronize(hs.out);
+  for (EventHandle e : events) (void)be.event_destroy(e);
+  if (!enqueued) return enqueued;
+  if (!s_compute) return s_compute;
+  if (!s_in) return s_in;
+  return s_out;
 }
 
 } // namespace
@@ -413,7 +527,7 @@ void register_builtin_kernels() {
                    [](const ShapeMap &s, const DeviceLimits &l) { return plan_rows("layernorm", s, l, true); },
                    run_rows});
   register_kernel({"scan", "scan", plan_scan, run_scan});
-  register_kernel({"gemm", "gemm", plan_gemm, run_gemm});
+  register_kernel({"gemm", "gemm", plan_gemm, run_gemm, run_gemm_host});
   register_attention_kernel();
 }
 

@@ -30,7 +30,8 @@ Result<std::unique_ptr<Executor>> Executor::create(std::shared_ptr<Backend> back
 }
 
 Executor::~Executor() {
-  if (backend_ && host_stream_) (void)backend_->stream_destroy(host_stream_);
+  for (StreamHandle s : {host_stream_, host_in_stream_, host_out_stream_})
+    if (backend_ && s) (void)backend_->stream_destroy(s);
 }
 
 Result<KernelFunction> Executor::function(const std::string &code_object, const std::string &entry) {
@@ -236,6 +237,18 @@ Result<void> Executor::run_host(const std::string &kernel, const ShapeMap &shape
       host_pool_[i] = std::move(*b);
     }
     dev[i] = host_pool_[i].data();
+  }
+  if (const KernelRecord &record = find_kernel(kernel); record.run_host) {
+    for (StreamHandle *s : {&host_in_stream_, &host_out_stream_}) {
+      if (*s != nullptr) continue;
+      auto created = backend_->stream_create();
+      if (!created) return std::unexpected(created.error());
+      *s = *created;
+    }
+    return record.run_host(*this, plan, host, dev, HostStreams{host_in_stream_, host_stream_, host_out_stream_});
+  }
+  for (size_t i = 0; i < plan.tensors.size(); ++i) {
+    const size_t bytes = static_cast<size_t>(plan.tensors[i].elements()) * 4;
     if (!plan.tensors[i].is_output && host[i] != nullptr)
       if (auto r = backend_->memcpy_h2d_async(dev[i], host[i], bytes, host_stream_); !r) return r;
   }

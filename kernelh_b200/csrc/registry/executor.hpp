@@ -84,6 +84,7 @@ private:
   uint64_t launches_issued_ = 0;
   std::vector<Buffer> host_pool_;
   StreamHandle host_stream_ = nullptr;
+  StreamHandle host_in_stream_ = nullptr, host_out_stream_ = nullptr;
 };
 
 // builtin_kernels.cpp

@@ -51,6 +51,11 @@ struct KernelPlan {
   bool work_is_flops = false;
 };
 
+// The streams a host-buffer run may spread its work over.
+struct HostStreams {
+  StreamHandle in = nullptr, compute = nullptr, out = nullptr;
+};
+
 struct KernelRecord {
   std::string name;
   std::string code_object; // which embedded cubin holds the entry symbols
@@ -62,6 +67,13 @@ struct KernelRecord {
   std::function<Result<void>(Executor &, const KernelPlan &, const std::vector<void *> &,
                              StreamHandle)>
       run;
+  // Optional host-buffer form that overlaps transfers with compute: `host` are
+  // the caller's buffers, `dev` device staging buffers of the same sizes. It
+  // returns with everything finished. Kernels without one use upload, run,
+  // download on a single stream.
+  std::function<Result<void>(Executor &, const KernelPlan &, const std::vector<void *> &host,
+                             const std::vector<void *> &dev, const HostStreams &)>
+      run_host = nullptr;
 };
 
 void register_kernel(KernelRecord record);

@@ -106,6 +106,7 @@ public:
   virtual Result<EventHandle> event_create() = 0;
   virtual Result<void> event_record(EventHandle e, StreamHandle s) = 0;
   virtual Result<void> event_synchronize(EventHandle e) = 0;
+  virtual Result<void> stream_wait_event(StreamHandle s, EventHandle e) = 0; // later work of s waits for e
   virtual Result<bool> event_query(EventHandle e) = 0; // true = complete
   virtual Result<float> event_elapsed_time(EventHandle start, EventHandle end) = 0;
   virtual Result<void> event_destroy(EventHandle e) = 0;

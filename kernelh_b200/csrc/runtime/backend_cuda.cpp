@@ -57,6 +57,7 @@ namespace {
   X(StreamCreate, "cuStreamCreate", CUresult (*)(CUstream *, unsigned))                            \
   X(StreamDestroy, "cuStreamDestroy_v2", CUresult (*)(CUstream))                                   \
   X(StreamSynchronize, "cuStreamSynchronize", CUresult (*)(CUstream))                              \
+  X(StreamWaitEvent, "cuStreamWaitEvent", CUresult (*)(CUstream, CUevent, unsigned))               \
   X(EventCreate, "cuEventCreate", CUresult (*)(CUevent *, unsigned))                               \
   X(EventRecord, "cuEventRecord", CUresult (*)(CUevent, CUstream))                                 \
   X(EventSynchronize, "cuEventSynchronize", CUresult (*)(CUevent))                                 \
@@ -377,6 +378,12 @@ public:
         r != CUDA_SUCCESS)
       return err(r, "cuEventElapsedTime");
     return ms;
+  }
+  Result<void> stream_wait_event(StreamHandle s, EventHandle e) override {
+    if (CUresult r = api_.StreamWaitEvent(static_cast<CUstream>(s), static_cast<CUevent>(e), 0);
+        r != CUDA_SUCCESS)
+      return err(r, "cuStreamWaitEvent");
+    return {};
   }
   Result<void> event_destroy(EventHandle e) override {
     if (CUresult r = api_.EventDestroy(static_cast<CUevent>(e)); r != CUDA_SUCCESS)

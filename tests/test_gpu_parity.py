@@ -267,6 +267,19 @@ def test_gemm_is_insensitive_to_operand_scaling(ctx, oracle, kind):
         assert not c[3].any() and not c[:, 5].any()
 
 
+@pytest.mark.parametrize("m,n,k", [(2500, 384, 200), (256, 256, 64), (100, 40, 33)])
+def test_gemm_host_path_is_pipelined_and_identical(ctx, oracle, m, n, k):
+    """kh_run_host for gemm uploads A in row blocks and multiplies them while the
+    next block is on the wire; the result equals the device path bit for bit."""
+    a = oracle.uniform((m, k), oracle.BASE_SEED + 11, -1, 1)
+    b = oracle.uniform((k, n), oracle.BASE_SEED + 12, -1, 1)
+    c_dev = run(ctx, "gemm", f"m={m},n={n},k={k}", [a, b], (m, n))
+    c_host = np.full((m, n), np.nan, np.float32)
+    ctx.run_host("gemm", f"m={m},n={n},k={k}", [a, b, c_host])
+    assert np.array_equal(c_host, c_dev)
+    assert oracle.compare(c_host, oracle.gemm_ref(a, b)).rel_frobenius <= 1e-5
+
+
 def test_gemm_8192_sampled_rows_and_scaling_property(ctx, oracle):
     size = 8192
     a = oracle.uniform((size, size), oracle.BASE_SEED, -1, 1)
