@@ -29,12 +29,13 @@
 // round-to-nearest by the epilogue warps while the next chunk is running.
 //
 // Four launches:
-//  gemm_split_a   one warp per row of A: largest magnitude, scale exponent,
-//      then A_hi, A_lo (m x kp fp16, kp = k rounded up to 32, zero padded).
+//  gemm_split_a   per row of A: largest magnitude, scale exponent, then A_hi,
+//      A_lo (m x kp fp16, kp = k rounded up to 32, zero padded); long rows are
+//      staged whole in shared memory by bulk copies (TMA), double buffered.
 //      It also clears the column maxima for the next launch.
 //  gemm_colmax_b  largest magnitude of every column of B (atomic max on the
 //      bit patterns of |b|, which order like the values).
-//  gemm_split_bt  B^T_hi, B^T_lo (n x kp fp16) through 64 x 32 shared-memory
+//  gemm_split_bt  B^T_hi, B^T_lo (n x kp fp16) through 64 x 128 shared-memory
 //      tiles, so both tensor-core operands are K-major with 64-byte rows.
 //  gemm           persistent two-CTA clusters (tcgen05 cta_group::2), one per
 //      pair of SMs, walk the 256 x 256 tiles of C. CTA r of a pair holds rows
@@ -87,13 +88,6 @@ __device__ __forceinline__ int scale_shift(float amax) {
   return kTargetExponent - ilogbf(amax);
 }
 
-__device__ __forceinline__ void split_fp16(float x, int shift, __half &hi, __half &lo) {
-  const float s = ldexpf(x, shift);
-  hi = __float2half_rn(s);
-  const float h = __half2float(hi);
-  lo = (h - h == 0.f) ? __float2half_rn(s - h) : __float2half_rn(0.f); // no inf - inf
-}
-
 // x * 2^e for |e| up to 378, exact unless the result leaves the normal fp32
 // range: 2^e is applied as three factors, each a normal fp32 power of two.
 __device__ __forceinline__ float pow2f(int e) { return __int_as_float((e + 127) << 23); }
@@ -102,6 +96,13 @@ __device__ __forceinline__ float scale_pow2(float x, int e) {
   const int r = e - e1;
   const int e2 = max(-126, min(127, r));
   return x * pow2f(e1) * pow2f(e2) * pow2f(r - e2);
+}
+
+__device__ __forceinline__ void split_fp16(float x, int shift, __half &hi, __half &lo) {
+  const float s = scale_pow2(x, shift);
+  hi = __float2half_rn(s);
+  const float h = __half2float(hi);
+  lo = (h - h == 0.f) ? __float2half_rn(s - h) : __float2half_rn(0.f); // no inf - inf
 }
 
 // Ordered accesses for the epilogue (see the store loop of gemm_body).
@@ -129,57 +130,203 @@ struct alignas(16) Half8 {
 } // namespace
 
 // A (m x k, any strides) -> hi, lo (m x kp fp16, contiguous, zero padded in k)
-// and the scale exponent of every row. One warp per row.
-extern "C" __global__ void __launch_bounds__(256)
-gemm_split_a(KH_MEMREF2(const float, a), __half *__restrict__ hi, __half *__restrict__ lo,
-             int *__restrict__ a_shift, uint32_t *__restrict__ b_amax, int64_t b_cols, int64_t kp) {
-  const float *__restrict__ a = KH_DATA(a);
-  const int64_t m = a_size0, k = a_size1;
-  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < b_cols;
-       i += static_cast<int64_t>(gridDim.x) * blockDim.x)
-    b_amax[i] = 0u;
+// and the scale exponent of every row. A team of kTeam threads (a warp for
+// short rows, the whole block for long ones) owns a row: it reads the row once
+// into registers (kHeld groups of 8 values per thread; longer rows are read
+// again for the second step), reduces the largest magnitude, and writes the two splits.
+template <int kTeam, int kHeld>
+__device__ __forceinline__ void split_a_rows(const float *__restrict__ a, int64_t m, int64_t k, int64_t a_stride0,
+                                             int64_t a_stride1, __half *__restrict__ hi, __half *__restrict__ lo,
+                                             int *__restrict__ a_shift, int64_t kp, float *team_max) {
+  constexpr int kTeamsPerBlock = 256 / kTeam;
+  const int team = threadIdx.x / kTeam, member = threadIdx.x % kTeam;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const bool vec_ok = khd::is_aligned16(a) && a_stride1 == 1 && (a_stride0 & 3) == 0;
-  for (int64_t r = static_cast<int64_t>(blockIdx.x) * 8 + warp; r < m; r += static_cast<int64_t>(gridDim.x) * 8) {
-    const float *row = a + r * a_stride0;
+  const bool fits = kHeld > 0 && kp <= static_cast<int64_t>(kTeam) * 8 * kHeld;
+  const int64_t first = static_cast<int64_t>(blockIdx.x) * kTeamsPerBlock;
+  const int64_t step = static_cast<int64_t>(gridDim.x) * kTeamsPerBlock;
+  // every team of a block makes the same number of trips (block-wide barriers below)
+  for (int64_t r0 = first; r0 < m; r0 += step) {
+    const int64_t r = r0 + team;
+    const bool live = r < m;
+    const float *row = a + (live ? r : 0) * a_stride0;
+    float v[kHeld > 0 ? kHeld : 1][8];
     float amax = 0.f;
-    if (vec_ok) {
-      const int64_t k4 = k >> 2;
-      for (int64_t c = lane; c < k4; c += 32) {
-        const float4 f = __ldg(reinterpret_cast<const float4 *>(row) + c);
-        amax = fmaxf(amax, fmaxf(fmaxf(fabsf(f.x), fabsf(f.y)), fmaxf(fabsf(f.z), fabsf(f.w))));
-      }
-      for (int64_t c = (k4 << 2) + lane; c < k; c += 32) amax = fmaxf(amax, fabsf(row[c]));
-    } else {
-      for (int64_t c = lane; c < k; c += 32) amax = fmaxf(amax, fabsf(row[c * a_stride1]));
-    }
-    amax = khd::warp_max(amax);
-    const int shift = scale_shift(amax);
-    if (lane == 0) a_shift[r] = shift;
-    for (int64_t c = static_cast<int64_t>(lane) * 8; c < kp; c += 256) {
-      float v[8];
+    const auto load8 = [&](int64_t c, float (&out)[8]) {
       if (vec_ok && c + 8 <= k) {
         const float4 f0 = __ldcs(reinterpret_cast<const float4 *>(row + c));
         const float4 f1 = __ldcs(reinterpret_cast<const float4 *>(row + c + 4));
-        v[0] = f0.x; v[1] = f0.y; v[2] = f0.z; v[3] = f0.w;
-        v[4] = f1.x; v[5] = f1.y; v[6] = f1.z; v[7] = f1.w;
+        out[0] = f0.x; out[1] = f0.y; out[2] = f0.z; out[3] = f0.w;
+        out[4] = f1.x; out[5] = f1.y; out[6] = f1.z; out[7] = f1.w;
       } else {
 #pragma unroll
-        for (int j = 0; j < 8; ++j) v[j] = (c + j < k) ? row[(c + j) * a_stride1] : 0.f;
+        for (int j = 0; j < 8; ++j) out[j] = (c + j < k) ? row[(c + j) * a_stride1] : 0.f;
       }
+    };
+    if (live) {
+      if (fits) {
+#pragma unroll
+        for (int g = 0; g < kHeld; ++g) {
+          const int64_t c = (static_cast<int64_t>(g) * kTeam + member) * 8;
+          if (c < kp) {
+            load8(c, v[g]);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(v[g][j]));
+          }
+        }
+      } else {
+        for (int64_t c = static_cast<int64_t>(member) * 8; c < kp; c += kTeam * 8) {
+          float t[8];
+          load8(c, t);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(t[j]));
+        }
+      }
+    }
+    amax = khd::warp_max(amax);
+    if (kTeam > 32) {
+      __syncthreads();
+      if (lane == 0) team_max[warp] = amax;
+      __syncthreads();
+      amax = team_max[0];
+#pragma unroll
+      for (int w = 1; w < 8; ++w) amax = fmaxf(amax, team_max[w]);
+    }
+    if (!live) continue;
+    const int shift = scale_shift(amax);
+    if (member == 0) a_shift[r] = shift;
+    const auto store8 = [&](int64_t c, const float (&in)[8]) {
       Half8 h, l;
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
         __half h0, l0, h1, l1;
-        split_fp16(v[2 * j], shift, h0, l0);
-        split_fp16(v[2 * j + 1], shift, h1, l1);
+        split_fp16(in[2 * j], shift, h0, l0);
+        split_fp16(in[2 * j + 1], shift, h1, l1);
         h.v[j] = __halves2half2(h0, h1);
         l.v[j] = __halves2half2(l0, l1);
       }
       *reinterpret_cast<Half8 *>(hi + r * kp + c) = h;
       *reinterpret_cast<Half8 *>(lo + r * kp + c) = l;
+    };
+    if (fits) {
+#pragma unroll
+      for (int g = 0; g < kHeld; ++g) {
+        const int64_t c = (static_cast<int64_t>(g) * kTeam + member) * 8;
+        if (c < kp) store8(c, v[g]);
+      }
+    } else {
+      for (int64_t c = static_cast<int64_t>(member) * 8; c < kp; c += kTeam * 8) {
+        float t[8];
+        load8(c, t);
+        store8(c, t);
+      }
     }
   }
+}
+
+// Rows of 1025..8192 values, contiguous and 16-byte aligned: the whole row is
+// brought into shared memory by one bulk copy (TMA) while the block works on
+// the previous row, so a row is read from HBM exactly once and the copies never
+// stop. Two row buffers in dynamic shared memory.
+__device__ __forceinline__ void split_a_staged(const float *__restrict__ a, int64_t m, int64_t k, int64_t a_stride0,
+                                               __half *__restrict__ hi, __half *__restrict__ lo,
+                                               int *__restrict__ a_shift, int64_t kp, uint32_t *status,
+                                               float *team_max) {
+  extern __shared__ __align__(16) uint8_t staged_rows[];
+  __shared__ __align__(8) uint64_t bars[2];
+  __shared__ int s_abort;
+  const uint32_t row_bytes = static_cast<uint32_t>(k) * 4u;
+  const uint32_t buf0 = khd::smem_u32(staged_rows), bar0 = khd::smem_u32(&bars[0]);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) {
+    s_abort = 0;
+    khd::mbar_init(bar0, 1);
+    khd::mbar_init(bar0 + 8, 1);
+    khd::mbar_fence_init();
+  }
+  __syncthreads();
+  const auto fetch = [&](int64_t r, int buf) {
+    khd::mbar_arrive_expect_tx(bar0 + 8 * buf, row_bytes);
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                     buf0 + buf * row_bytes),
+                 "l"(a + r * a_stride0), "r"(row_bytes), "r"(bar0 + 8 * buf)
+                 : "memory");
+  };
+  if (threadIdx.x == 0 && blockIdx.x < m) fetch(blockIdx.x, 0);
+  int64_t trip = 0;
+  for (int64_t r = blockIdx.x; r < m; r += gridDim.x, ++trip) {
+    const int buf = static_cast<int>(trip & 1);
+    if (threadIdx.x == 0 && r + gridDim.x < m) fetch(r + gridDim.x, buf ^ 1);
+    bool ok = khd::mbar_wait(bar0 + 8 * buf, static_cast<uint32_t>(trip >> 1) & 1u, &s_abort, status,
+                             khd::kStatusTmaWaitTimeout, static_cast<uint32_t>(r));
+    if (!__syncthreads_and(ok)) break;
+    const float *row = reinterpret_cast<const float *>(staged_rows + buf * row_bytes);
+    float amax = 0.f;
+    for (int64_t c = static_cast<int64_t>(threadIdx.x) * 4; c < k; c += 1024) { // k is a multiple of 4
+      const float4 f = *reinterpret_cast<const float4 *>(row + c);
+      amax = fmaxf(amax, fmaxf(fmaxf(fabsf(f.x), fabsf(f.y)), fmaxf(fabsf(f.z), fabsf(f.w))));
+    }
+    amax = khd::warp_max(amax);
+    if (lane == 0) team_max[warp] = amax;
+    __syncthreads();
+    amax = team_max[0];
+#pragma unroll
+    for (int w = 1; w < 8; ++w) amax = fmaxf(amax, team_max[w]);
+    const int shift = scale_shift(amax);
+    if (threadIdx.x == 0) a_shift[r] = shift;
+    for (int64_t c = static_cast<int64_t>(threadIdx.x) * 8; c < kp; c += 2048) {
+      float v[8];
+      if (c + 8 <= k) {
+        const float4 f0 = *reinterpret_cast<const float4 *>(row + c);
+        const float4 f1 = *reinterpret_cast<const float4 *>(row + c + 4);
+        v[0] = f0.x; v[1] = f0.y; v[2] = f0.z; v[3] = f0.w;
+        v[4] = f1.x; v[5] = f1.y; v[6] = f1.z; v[7] = f1.w;
+      } else {
+#pragma unroll
+        for (int q = 0; q < 8; ++q) v[q] = (c + q < k) ? row[c + q] : 0.f;
+      }
+      Half8 h, l;
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        __half h0, l0, h1, l1;
+        split_fp16(v[2 * q], shift, h0, l0);
+        split_fp16(v[2 * q + 1], shift, h1, l1);
+        h.v[q] = __halves2half2(h0, h1);
+        l.v[q] = __halves2half2(l0, l1);
+      }
+      *reinterpret_cast<Half8 *>(hi + r * kp + c) = h;
+      *reinterpret_cast<Half8 *>(lo + r * kp + c) = l;
+    }
+    __syncthreads(); // the row buffer and team_max are free again
+  }
+  if (s_abort) // a wait ran out: give the copy still in flight time to land before the block leaves
+    for (int i = 0; i < 64; ++i) __nanosleep(10000);
+}
+
+__device__ __forceinline__ uint32_t dynamic_smem_bytes() {
+  uint32_t v;
+  asm volatile("mov.u32 %0, %%dynamic_smem_size;" : "=r"(v));
+  return v;
+}
+
+extern "C" __global__ void __launch_bounds__(256, 3)
+gemm_split_a(KH_MEMREF2(const float, a), __half *__restrict__ hi, __half *__restrict__ lo,
+             int *__restrict__ a_shift, uint32_t *__restrict__ b_amax, int64_t b_cols, int64_t kp,
+             uint32_t *status) {
+  __shared__ float team_max[8];
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < b_cols;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x)
+    b_amax[i] = 0u;
+  const float *a = KH_DATA(a);
+  const int64_t k = a_size1;
+  const bool stageable = kp > 1024 && (k & 3) == 0 && a_stride1 == 1 && (a_stride0 & 3) == 0 &&
+                         khd::is_aligned16(a) && static_cast<uint64_t>(k) * 8 <= dynamic_smem_bytes();
+  if (stageable)
+    split_a_staged(a, a_size0, k, a_stride0, hi, lo, a_shift, kp, status, team_max);
+  else if (kp <= 1024)
+    split_a_rows<32, 4>(a, a_size0, k, a_stride0, a_stride1, hi, lo, a_shift, kp, team_max);
+  else
+    split_a_rows<256, 0>(a, a_size0, k, a_stride0, a_stride1, hi, lo, a_shift, kp, team_max);
 }
 
 // Largest |b| of every column of B (k x n, any strides) into b_amax, which
@@ -217,39 +364,63 @@ gemm_colmax_b(KH_MEMREF2(const float, b), uint32_t *__restrict__ b_amax) {
 
 // B (k x n, any strides) -> B^T hi, lo (n x kp fp16, contiguous, zero padded in
 // k), every column scaled by the exponent its maximum gives; the k-tile-0
-// blocks also publish the exponents. 64 (k) x 32 (n) tiles through shared
-// memory so both sides stay coalesced.
+// blocks also publish the exponents. 64 (k) x 128 (n) tiles through shared
+// memory: a warp reads 512 contiguous bytes of a row of B, and writes 128-byte
+// runs (64 k-values) of four rows of B^T at a time, 16 bytes per lane.
 extern "C" __global__ void __launch_bounds__(256)
 gemm_split_bt(KH_MEMREF2(const float, b), __half *__restrict__ hi, __half *__restrict__ lo,
               const uint32_t *__restrict__ b_amax, int *__restrict__ b_shift, int64_t kp) {
-  __shared__ float tile[64][33];
+  constexpr int kTK = 64, kTN = 128;
+  // float4 groups of a row are stored at group ^ (row / 8 mod 8): conflict-free both ways
+  __shared__ __align__(16) float tile[kTK][kTN];
   const float *__restrict__ b = KH_DATA(b);
   const int64_t k = b_size0, n = b_size1;
-  const int64_t tiles_n = (n + 31) >> 5, tiles_k = (kp + 63) >> 6;
-  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5; // 32 x 8
+  const int64_t tiles_n = (n + kTN - 1) / kTN, tiles_k = (kp + kTK - 1) / kTK;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const bool vec_ok = khd::is_aligned16(b) && b_stride1 == 1 && (b_stride0 & 3) == 0;
   for (int64_t t = blockIdx.x; t < tiles_n * tiles_k; t += gridDim.x) {
-    const int64_t tk = t / tiles_n, tn = t - tk * tiles_n;
-    const int64_t k0 = tk << 6, n0 = tn << 5;
+    // k-tiles of one column strip are neighbours in time: their 128-byte writes fill whole rows of B^T
+    const int64_t tn = t / tiles_k, tk = t - tn * tiles_k;
+    const int64_t k0 = tk * kTK, n0 = tn * kTN;
     __syncthreads();
 #pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      const int64_t kk = k0 + ty + 8 * j, nn = n0 + tx;
-      tile[ty + 8 * j][tx] = (kk < k && nn < n) ? b[kk * b_stride0 + nn * b_stride1] : 0.f;
+    for (int j = 0; j < kTK / 8; ++j) {
+      const int kl = warp + 8 * j;
+      const int64_t kk = k0 + kl, nn = n0 + lane * 4;
+      float4 f = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (kk < k) {
+        if (vec_ok && nn + 4 <= n) {
+          f = __ldcs(reinterpret_cast<const float4 *>(b + kk * b_stride0 + nn));
+        } else {
+          if (nn < n) f.x = b[kk * b_stride0 + nn * b_stride1];
+          if (nn + 1 < n) f.y = b[kk * b_stride0 + (nn + 1) * b_stride1];
+          if (nn + 2 < n) f.z = b[kk * b_stride0 + (nn + 2) * b_stride1];
+          if (nn + 3 < n) f.w = b[kk * b_stride0 + (nn + 3) * b_stride1];
+        }
+      }
+      *reinterpret_cast<float4 *>(&tile[kl][(lane ^ ((kl >> 3) & 7)) * 4]) = f;
     }
     __syncthreads();
+    const int sub = lane >> 3, kgroup = lane & 7; // 4 rows of B^T per warp store, 8 k-values per lane
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      const int64_t nn = n0 + ty + 8 * j, kk = k0 + 2 * tx;
-      if (nn < n) {
+    for (int j = 0; j < kTN / 32; ++j) {
+      const int nl = warp * 16 + j * 4 + sub;
+      const int64_t nn = n0 + nl, kk = k0 + kgroup * 8;
+      if (nn < n && kk < kp) {
         const int shift = scale_shift(__uint_as_float(__ldg(b_amax + nn)));
-        if (tk == 0 && tx == 0) b_shift[nn] = shift;
-        if (kk < kp) {
+        if (tk == 0 && kgroup == 0) b_shift[nn] = shift;
+        const int col = (((nl >> 2) ^ kgroup) << 2) | (nl & 3); // rows kgroup*8.. share one swizzle
+        Half8 h, l;
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
           __half h0, l0, h1, l1;
-          split_fp16(tile[2 * tx][ty + 8 * j], shift, h0, l0);
-          split_fp16(tile[2 * tx + 1][ty + 8 * j], shift, h1, l1);
-          *reinterpret_cast<__half2 *>(hi + nn * kp + kk) = __halves2half2(h0, h1);
-          *reinterpret_cast<__half2 *>(lo + nn * kp + kk) = __halves2half2(l0, l1);
+          split_fp16(tile[kgroup * 8 + 2 * q][col], shift, h0, l0);
+          split_fp16(tile[kgroup * 8 + 2 * q + 1][col], shift, h1, l1);
+          h.v[q] = __halves2half2(h0, h1);
+          l.v[q] = __halves2half2(l0, l1);
         }
+        *reinterpret_cast<Half8 *>(hi + nn * kp + kk) = h;
+        *reinterpret_cast<Half8 *>(lo + nn * kp + kk) = l;
       }
     }
   }

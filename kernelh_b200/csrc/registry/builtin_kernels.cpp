@@ -232,8 +232,12 @@ std::vector<LaunchStep> gemm_steps(int64_t m, int64_t n, int64_t k, const Device
   LaunchStep sa;
   sa.entry = "gemm_split_a";
   sa.block = {256, 1, 1};
-  sa.grid = {balanced_grid((m + 7) / 8, sms, 8), 1, 1}; // one warp per row
-  sa.param_count = 7 + 6;
+  // a warp per row for short rows (8 rows per block); the whole block for long ones, which
+  // are staged in two shared-memory row buffers when a row is at most 32 KiB
+  const bool staged = kp > 1024 && k % 4 == 0 && k * 4 <= 32768;
+  sa.grid = {balanced_grid(kp <= 1024 ? (m + 7) / 8 : m, sms, 3), 1, 1};
+  sa.dynamic_smem = staged ? static_cast<size_t>(k) * 8 : 0;
+  sa.param_count = 7 + 7;
   LaunchStep cm;
   cm.entry = "gemm_colmax_b";
   cm.block = {256, 1, 1};
@@ -242,7 +246,7 @@ std::vector<LaunchStep> gemm_steps(int64_t m, int64_t n, int64_t k, const Device
   LaunchStep sb;
   sb.entry = "gemm_split_bt";
   sb.block = {256, 1, 1};
-  sb.grid = {balanced_grid(((n + 31) / 32) * ((kp + 63) / 64), sms, 8), 1, 1};
+  sb.grid = {balanced_grid(((n + 127) / 128) * ((kp + 63) / 64), sms, 6), 1, 1}; // 64 x 128 tiles
   sb.param_count = 7 + 5;
   LaunchStep g;
   g.entry = "gemm";
@@ -345,6 +349,7 @@ Result<void> gemm_enqueue_a(const GemmJob &j, const void *a_rows, int64_t row0, 
   args.add_scalar<uint64_t>(j.at(j.lay.b_amax));
   args.add_scalar<int64_t>(clear_cols);
   args.add_scalar<int64_t>(j.kp);
+  args.add_scalar<uint64_t>(reinterpret_cast<uint64_t>(j.ex.status_word()));
   return j.ex.launch(j.split_a, step, args, stream);
 }
 
