@@ -98,11 +98,30 @@ __device__ __forceinline__ float scale_pow2(float x, int e) {
   return x * pow2f(e1) * pow2f(e2) * pow2f(r - e2);
 }
 
-__device__ __forceinline__ void split_fp16(float x, int shift, __half &hi, __half &lo) {
-  const float s = scale_pow2(x, shift);
-  hi = __float2half_rn(s);
-  const float h = __half2float(hi);
-  lo = (h - h == 0.f) ? __float2half_rn(s - h) : __float2half_rn(0.f); // no inf - inf
+// The power of two a row (column) is scaled by, prepared once per row: one
+// factor when 2^shift is a normal fp32 number, three otherwise.
+struct RowScale {
+  float f1, f2, f3;
+  bool single;
+};
+__device__ __forceinline__ RowScale row_scale(int shift) {
+  const int e1 = max(-126, min(127, shift));
+  const int r = shift - e1;
+  const int e2 = max(-126, min(127, r));
+  return {pow2f(e1), pow2f(e2), pow2f(r - e2), r == 0};
+}
+// Two scaled values -> their fp16 hi parts and the fp16 of what hi left over.
+// (x - hi is exact in fp32. An infinite input gives hi = inf and lo = NaN: the
+// products are non-finite either way.)
+__device__ __forceinline__ void split_fp16x2(float x0, float x1, const RowScale &sc, __half2 &hi, __half2 &lo) {
+  float s0 = x0 * sc.f1, s1 = x1 * sc.f1;
+  if (!sc.single) {
+    s0 = s0 * sc.f2 * sc.f3;
+    s1 = s1 * sc.f2 * sc.f3;
+  }
+  hi = __floats2half2_rn(s0, s1);
+  const float2 h = __half22float2(hi);
+  lo = __floats2half2_rn(s0 - h.x, s1 - h.y);
 }
 
 // Ordered accesses for the epilogue (see the store loop of gemm_body).
@@ -194,16 +213,13 @@ __device__ __forceinline__ void split_a_rows(const float *__restrict__ a, int64_
     }
     if (!live) continue;
     const int shift = scale_shift(amax);
+    const RowScale scale = row_scale(shift);
     if (member == 0) a_shift[r] = shift;
     const auto store8 = [&](int64_t c, const float (&in)[8]) {
       Half8 h, l;
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
-        __half h0, l0, h1, l1;
-        split_fp16(in[2 * j], shift, h0, l0);
-        split_fp16(in[2 * j + 1], shift, h1, l1);
-        h.v[j] = __halves2half2(h0, h1);
-        l.v[j] = __halves2half2(l0, l1);
+        split_fp16x2(in[2 * j], in[2 * j + 1], scale, h.v[j], l.v[j]);
       }
       *reinterpret_cast<Half8 *>(hi + r * kp + c) = h;
       *reinterpret_cast<Half8 *>(lo + r * kp + c) = l;
@@ -273,6 +289,7 @@ __device__ __forceinline__ void split_a_staged(const float *__restrict__ a, int6
 #pragma unroll
     for (int w = 1; w < 8; ++w) amax = fmaxf(amax, team_max[w]);
     const int shift = scale_shift(amax);
+    const RowScale scale = row_scale(shift);
     if (threadIdx.x == 0) a_shift[r] = shift;
     for (int64_t c = static_cast<int64_t>(threadIdx.x) * 8; c < kp; c += 2048) {
       float v[8];
@@ -288,11 +305,7 @@ __device__ __forceinline__ void split_a_staged(const float *__restrict__ a, int6
       Half8 h, l;
 #pragma unroll
       for (int q = 0; q < 4; ++q) {
-        __half h0, l0, h1, l1;
-        split_fp16(v[2 * q], shift, h0, l0);
-        split_fp16(v[2 * q + 1], shift, h1, l1);
-        h.v[q] = __halves2half2(h0, h1);
-        l.v[q] = __halves2half2(l0, l1);
+        split_fp16x2(v[2 * q], v[2 * q + 1], scale, h.v[q], l.v[q]);
       }
       *reinterpret_cast<Half8 *>(hi + r * kp + c) = h;
       *reinterpret_cast<Half8 *>(lo + r * kp + c) = l;
@@ -408,16 +421,13 @@ gemm_split_bt(KH_MEMREF2(const float, b), __half *__restrict__ hi, __half *__res
       const int64_t nn = n0 + nl, kk = k0 + kgroup * 8;
       if (nn < n && kk < kp) {
         const int shift = scale_shift(__uint_as_float(__ldg(b_amax + nn)));
+        const RowScale scale = row_scale(shift);
         if (tk == 0 && kgroup == 0) b_shift[nn] = shift;
         const int col = (((nl >> 2) ^ kgroup) << 2) | (nl & 3); // rows kgroup*8.. share one swizzle
         Half8 h, l;
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
-          __half h0, l0, h1, l1;
-          split_fp16(tile[kgroup * 8 + 2 * q][col], shift, h0, l0);
-          split_fp16(tile[kgroup * 8 + 2 * q + 1][col], shift, h1, l1);
-          h.v[q] = __halves2half2(h0, h1);
-          l.v[q] = __halves2half2(l0, l1);
+          split_fp16x2(tile[kgroup * 8 + 2 * q][col], tile[kgroup * 8 + 2 * q + 1][col], scale, h.v[q], l.v[q]);
         }
         *reinterpret_cast<Half8 *>(hi + nn * kp + kk) = h;
         *reinterpret_cast<Half8 *>(lo + nn * kp + kk) = l;
