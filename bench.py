@@ -39,9 +39,11 @@ def parse_args():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="kernelh_b200", choices=["kernelh_b200", "reference"])
     ap.add_argument("--size", type=int, default=SIZE, help=argparse.SUPPRESS)
-    ap.add_argument("--gather", default="p2p", choices=["p2p", "nccl"],
+    ap.add_argument("--gather", default="p2p", choices=["p2p", "p2p-st", "nccl"],
                     help="N > 1: 'p2p' = the gemm epilogue stores C tiles into every rank's C over NVLink "
-                         "(symmetric memory) and a barrier follows; 'nccl' = plain gemm + NCCL all-gather")
+                         "(symmetric memory; one multimem.st per tile piece through the NVSwitch multicast "
+                         "address when there is one, else plain peer stores) and a barrier follows; "
+                         "'p2p-st' = the same, forcing plain peer stores; 'nccl' = plain gemm + NCCL all-gather")
     ap.add_argument("--no-extras", action="store_true",
                     help="skip the memory-bound rows, the e2e leg and the CPU baseline")
     return ap.parse_args()
@@ -308,7 +310,8 @@ def gpu_arm(args) -> None:
     gather = "none"
     symm = None
     c = None
-    if world > 1 and args.gather == "p2p":
+    multicast = 0
+    if world > 1 and args.gather in ("p2p", "p2p-st"):
         # Every rank's C lives in symmetric memory, so each rank holds an address for
         # every other rank's C and the gemm epilogue can store its tiles into all of them.
         try:
@@ -317,6 +320,7 @@ def gpu_arm(args) -> None:
             c = symm_mem.empty((size, size), dtype=torch.float32, device=torch.device("cuda", local_rank))
             symm = symm_mem.rendezvous(c, dist.group.WORLD.group_name)
             replicas = [int(p) for p in symm.buffer_ptrs]
+            multicast = int(getattr(symm, "multicast_ptr", 0) or 0) if args.gather == "p2p" else 0
             c.zero_()
             gather = "p2p"
         except Exception as exc:  # no peer mapping on this box: use the collective instead
@@ -335,7 +339,10 @@ def gpu_arm(args) -> None:
 
     def step():
         if gather == "p2p":
-            ctx.gemm_allgather(a_shard, b, replicas, rank, rows, size, size, stream)
+            if multicast:
+                ctx.gemm_allgather_multicast(a_shard, b, c, multicast, world, rank, rows, size, size, stream)
+            else:
+                ctx.gemm_allgather(a_shard, b, replicas, rank, rows, size, size, stream)
             symm.barrier()  # all ranks' stores have landed before anyone reads C
         else:
             ctx.gemm(a_shard, b, c_shard, rows, size, size, stream)
@@ -372,7 +379,9 @@ def gpu_arm(args) -> None:
     # ---- the dominant kernel alone, per-launch, on this rank's stream -------------------
     ctx.profile(True)
     for _ in range(args.steps):
-        if gather == "p2p":
+        if gather == "p2p" and multicast:
+            ctx.gemm_allgather_multicast(a_shard, b, c, multicast, world, rank, rows, size, size, stream)
+        elif gather == "p2p":
             ctx.gemm_allgather(a_shard, b, replicas, rank, rows, size, size, stream)
         else:
             ctx.gemm(a_shard, b, c_shard, rows, size, size, stream)
@@ -412,8 +421,10 @@ def gpu_arm(args) -> None:
         "data": "synthetic",
         "config": {"workload": f"gemm m=n=k={size} fp32 row-major, A,B ~ U[-1,1) seeded",
                    "sharding": (f"A and C by {world} M-row blocks, B replicated before timing; " + (
-                       "all-gather fused into the gemm epilogue (peer stores over NVLink into every rank's C) "
-                       "+ barrier, inside the timed step" if gather == "p2p" else
+                       "all-gather fused into the gemm epilogue (" + (
+                           "multimem.st through the NVSwitch multicast address of every rank's C" if multicast else
+                           "peer stores over NVLink into every rank's C") +
+                       ") + barrier, inside the timed step" if gather == "p2p" else
                        "NCCL all-gather of C inside the timed step")) if world > 1 else "single GPU",
                    "l2": "inputs (2 x 256 MiB) and the 512 MiB operand-split scratch are larger than the 126 MB L2",
                    "step": "gemm_split_a + gemm_colmax_b + gemm_split_bt + " + {"none": "gemm", "nccl": "gemm + nccl all_gather",

@@ -138,6 +138,17 @@ int kh_attention(kh_context *ctx, const float *q, const float *k, const float *v
 int kh_gemm_allgather(kh_context *ctx, const float *a_shard, const float *b, void *const *c_replicas,
                       int world, int rank, int64_t m_shard, int64_t n, int64_t k, void *stream);
 
+/* No counterpart in the reference. The same with the C replicas bound to one
+ * NVLink multicast object (NVSwitch systems): `c_local` is this rank's own
+ * (world*m_shard) x n C and `c_multicast` the multicast address of that buffer
+ * across all ranks (e.g. torch symmetric memory's multicast_ptr). Every tile
+ * is stored to c_local and then sent once with multimem.st; the switch
+ * delivers it to every rank, so a rank's links carry its shard once instead
+ * of world-1 times. Same barrier rule as kh_gemm_allgather. */
+int kh_gemm_allgather_multicast(kh_context *ctx, const float *a_shard, const float *b, float *c_local,
+                                void *c_multicast, int world, int rank, int64_t m_shard, int64_t n,
+                                int64_t k, void *stream);
+
 /* No counterpart in the reference. The scan for callers that must not allocate
  * device memory (memory-pool owners, allocator-free plugin callbacks, fixed
  * audited budgets): same result as kh_scan, but the look-back scratch is a

@@ -81,6 +81,7 @@ def _load() -> C.CDLL:
     L.kh_layernorm.argtypes = [vp, f32p, f32p, f32p, f32p, i64, i64, vp]
     L.kh_gemm.argtypes = [vp, f32p, f32p, f32p, i64, i64, i64, vp]
     L.kh_gemm_allgather.argtypes = [vp, f32p, f32p, C.POINTER(vp), C.c_int, C.c_int, i64, i64, i64, vp]
+    L.kh_gemm_allgather_multicast.argtypes = [vp, f32p, f32p, f32p, vp, C.c_int, C.c_int, i64, i64, i64, vp]
     L.kh_attention.argtypes = [vp, f32p, f32p, f32p, f32p, i64, i64, i64, i64, vp]
     L.kh_malloc.argtypes = [vp, C.c_size_t, C.POINTER(vp)]
     L.kh_free.argtypes = [vp, vp]
@@ -239,6 +240,13 @@ class Context:
         arr = (C.c_void_p * len(c_replicas))(*[_ptr(p) for p in c_replicas])
         _check(lib.kh_gemm_allgather(self._h, _ptr(a_shard), _ptr(b), arr, len(c_replicas), rank,
                                      m_shard, n, k, stream))
+
+    def gemm_allgather_multicast(self, a_shard, b, c_local, c_multicast, world, rank, m_shard, n, k, stream=None):
+        """Sharded gemm whose epilogue stores every C tile to `c_local` (this rank's
+        full C) and sends it once through the replicas' NVLink multicast address
+        (`c_multicast`), reaching all ranks' full C."""
+        _check(lib.kh_gemm_allgather_multicast(self._h, _ptr(a_shard), _ptr(b), _ptr(c_local),
+                                               C.c_void_p(int(c_multicast)), world, rank, m_shard, n, k, stream))
 
     def attention(self, q, k, v, o, batch, heads, seq, head_dim, stream=None):
         _check(lib.kh_attention(self._h, _ptr(q), _ptr(k), _ptr(v), _ptr(o), batch, heads, seq,

@@ -232,7 +232,23 @@ int kh_gemm_allgather(kh_context *ctx, const float *a_shard, const float *b, voi
   return guarded([&] {
     if (auto r = ctx->exec->backend().make_current(); !r) return set_error(r.error());
     std::vector<void *> reps(c_replicas, c_replicas + world);
-    auto r = kh::run_gemm_allgather(*ctx->exec, a_shard, b, reps, rank, m_shard, n, k, stream);
+    auto r = kh::run_gemm_allgather(*ctx->exec, a_shard, b, reps, nullptr, rank, world, m_shard, n, k, stream);
+    return r ? 0 : set_error(r.error());
+  });
+}
+int kh_gemm_allgather_multicast(kh_context *ctx, const float *a_shard, const float *b, float *c_local,
+                                void *c_multicast, int world, int rank, int64_t m_shard, int64_t n,
+                                int64_t k, void *stream) {
+  if (int rc = need_ctx(ctx)) return rc;
+  if (c_multicast == nullptr || c_local == nullptr)
+    return set_error(2, "kh_gemm_allgather_multicast: null C address");
+  if (world < 1 || world > 8 || rank < 0 || rank >= world)
+    return set_error(2, "kh_gemm_allgather_multicast: rank / world out of range");
+  return guarded([&] {
+    if (auto r = ctx->exec->backend().make_current(); !r) return set_error(r.error());
+    std::vector<void *> reps(static_cast<size_t>(world), nullptr);
+    reps[static_cast<size_t>(rank)] = c_local;
+    auto r = kh::run_gemm_allgather(*ctx->exec, a_shard, b, reps, c_multicast, rank, world, m_shard, n, k, stream);
     return r ? 0 : set_error(r.error());
   });
 }

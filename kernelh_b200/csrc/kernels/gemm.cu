@@ -141,6 +141,14 @@ __device__ __forceinline__ void store_float4(float *p, float x, float y, float z
 __device__ __forceinline__ void store_float(float *p, float x) {
   asm volatile("st.global.f32 [%0], %1;" ::"l"(p), "f"(x) : "memory");
 }
+// The same through an NVLink multicast address: the switch delivers the store to every bound GPU.
+__device__ __forceinline__ void multicast_store_float4(float *p, float x, float y, float z, float w) {
+  asm volatile("multimem.st.weak.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(p), "f"(x), "f"(y), "f"(z), "f"(w)
+               : "memory");
+}
+__device__ __forceinline__ void multicast_store_float(float *p, float x) {
+  asm volatile("multimem.st.weak.global.f32 [%0], %1;" ::"l"(p), "f"(x) : "memory");
+}
 
 struct alignas(16) Half8 {
   __half2 v[4];
@@ -439,13 +447,18 @@ gemm_split_bt(KH_MEMREF2(const float, b), __half *__restrict__ hi, __half *__res
 namespace {
 
 // Destinations of the fused all-gather: every finished C tile goes to each
-// listed replica of the full matrix, `row_offset` rows down. base[self] is this
-// GPU's own replica.
+// replica of the full matrix, `row_offset` rows down. The tile is stored to
+// base[self], this GPU's own replica, and then copied out in 512-byte warp-wide
+// slices: with multimem.st through `multicast`, the replicas' NVLink multicast
+// address, when there is one (the switch delivers each store to every GPU, so
+// the tile crosses this GPU's links once), else with plain peer stores to the
+// other listed replicas.
 struct GatherTargets {
   float *base[8];
   int count;
   int self;
   int64_t row_offset;
+  float *multicast; // NVLink multicast address of the replicas (one store reaches all), or null
 };
 
 struct TileCoord {
@@ -535,13 +548,21 @@ __device__ __forceinline__ void push_units(const GatherTargets &t, PendingPush &
     const int64_t off = (t.row_offset + row) * n + col;
     if ((n & 3) == 0) {
       const float4 v = __ldcg(reinterpret_cast<const float4 *>(local + off));
-      for (int d = 0; d < t.count; ++d)
-        if (d != t.self) *reinterpret_cast<float4 *>(t.base[d] + off) = v;
+      if (t.multicast != nullptr) {
+        multicast_store_float4(t.multicast + off, v.x, v.y, v.z, v.w);
+      } else {
+        for (int d = 0; d < t.count; ++d)
+          if (d != t.self) *reinterpret_cast<float4 *>(t.base[d] + off) = v;
+      }
     } else {
       for (int j = 0; j < 4 && col + j < n; ++j) {
         const float v = __ldcg(local + off + j);
-        for (int d = 0; d < t.count; ++d)
-          if (d != t.self) t.base[d][off + j] = v;
+        if (t.multicast != nullptr) {
+          multicast_store_float(t.multicast + off + j, v);
+        } else {
+          for (int d = 0; d < t.count; ++d)
+            if (d != t.self) t.base[d][off + j] = v;
+        }
       }
     }
   }
@@ -743,16 +764,19 @@ __device__ __forceinline__ void gemm_body(int64_t m, int64_t n, float *__restric
 #pragma unroll
           for (int j = 0; j < kBN / 2 / 4; ++j) {
             const int4 sh = load_shift4(b_shift + col0 + 4 * j);
-            store_float4(crow + col0 + 4 * j, scale_pow2(acc[4 * j], -(row_shift + sh.x)),
-                         scale_pow2(acc[4 * j + 1], -(row_shift + sh.y)),
-                         scale_pow2(acc[4 * j + 2], -(row_shift + sh.z)),
-                         scale_pow2(acc[4 * j + 3], -(row_shift + sh.w)));
+            const float x = scale_pow2(acc[4 * j], -(row_shift + sh.x));
+            const float y = scale_pow2(acc[4 * j + 1], -(row_shift + sh.y));
+            const float z = scale_pow2(acc[4 * j + 2], -(row_shift + sh.z));
+            const float w = scale_pow2(acc[4 * j + 3], -(row_shift + sh.w));
+            store_float4(crow + col0 + 4 * j, x, y, z, w);
           }
         } else {
 #pragma unroll
           for (int j = 0; j < kBN / 2; ++j)
-            if (col0 + j < n)
-              store_float(crow + (col0 + j) * cs1, scale_pow2(acc[j], -(row_shift + load_shift(b_shift + col0 + j))));
+            if (col0 + j < n) {
+              const float x = scale_pow2(acc[j], -(row_shift + load_shift(b_shift + col0 + j)));
+              store_float(crow + (col0 + j) * cs1, x);
+            }
         }
       }
       if (kGather) {

@@ -283,6 +283,7 @@ struct GatherTargets {
   int count;
   int self;
   int64_t row_offset;
+  float *multicast;
 };
 
 // One product being enqueued: sizes, scratch and the entry points.
@@ -490,12 +491,14 @@ Result<void> run_gemm_host(Executor &ex, const KernelPlan &p, const std::vector<
 // `a_shard` is this rank's (m_shard x k) rows of A, `b` the whole B, and
 // `replicas[i]` the address, valid on this device, of rank i's full C.
 Result<void> run_gemm_allgather(Executor &ex, const void *a_shard, const void *b,
-                                const std::vector<void *> &replicas, int rank, int64_t m_shard,
-                                int64_t n, int64_t k, StreamHandle stream) {
-  if (replicas.empty() || replicas.size() > 8)
-    return fail(2, "gemm_allgather: between 1 and 8 C replicas are supported, got " +
+                                const std::vector<void *> &replicas, void *multicast, int rank,
+                                int world, int64_t m_shard, int64_t n, int64_t k, StreamHandle stream) {
+  if (world < 1 || world > 8)
+    return fail(2, "gemm_allgather: between 1 and 8 ranks are supported, got " + std::to_string(world));
+  if (static_cast<int>(replicas.size()) != world)
+    return fail(2, "gemm_allgather: " + std::to_string(world) + " C replicas expected, got " +
                        std::to_string(replicas.size()));
-  if (rank < 0 || rank >= static_cast<int>(replicas.size()))
+  if (rank < 0 || rank >= world)
     return fail(2, "gemm_allgather: rank " + std::to_string(rank) + " is outside the replica list");
   KernelPlan plan;
   try {
@@ -504,9 +507,12 @@ Result<void> run_gemm_allgather(Executor &ex, const void *a_shard, const void *b
     return fail(2, e.what());
   }
   GatherTargets t{};
-  t.count = static_cast<int>(replicas.size());
-  for (int i = 0; i < t.count; ++i) {
-    if (replicas[i] == nullptr) return fail(2, "gemm_allgather: null C replica pointer");
+  t.count = world;
+  t.multicast = static_cast<float *>(multicast);
+  for (int i = 0; i < world; ++i) {
+    // with a multicast address only this rank's own replica is stored to directly
+    if (replicas[i] == nullptr && (multicast == nullptr || i == rank))
+      return fail(2, "gemm_allgather: null C replica pointer");
     t.base[i] = static_cast<float *>(replicas[i]);
   }
   t.self = rank;

@@ -88,8 +88,9 @@ private:
 };
 
 // builtin_kernels.cpp
+// `multicast` non-null: the replicas' NVLink multicast address (then only replicas[rank] is read).
 Result<void> run_gemm_allgather(Executor &ex, const void *a_shard, const void *b,
-                                const std::vector<void *> &replicas, int rank, int64_t m_shard,
-                                int64_t n, int64_t k, StreamHandle stream);
+                                const std::vector<void *> &replicas, void *multicast, int rank,
+                                int world, int64_t m_shard, int64_t n, int64_t k, StreamHandle stream);
 
 } // namespace kh
