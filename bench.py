@@ -273,6 +273,19 @@ def memory_bound_rows(torch, ctx, stream, hbm_peak: float) -> dict:
     return out
 
 
+def attention_rows(torch, ctx) -> dict:
+    """TFLOP/s (4 b h s^2 d useful flops) of the fused attention at the reference's
+    benchmark shape and at a batched one; split pass included."""
+    out = {}
+    for name, (bsz, heads, seq, dim) in (("reference_shape", (1, 1, 1024, 64)), ("batched", (8, 16, 1024, 64))):
+        shape = f"batch={bsz},heads={heads},seq={seq},head_dim={dim}"
+        sets = [[torch.randn(bsz, heads, seq, dim, device="cuda") for _ in range(4)] for _ in range(4)]
+        ms, method = time_rotating(torch, lambda s, st: ctx.launch("attention", shape, s, st), sets, 50)
+        out[name] = {"shape": shape, "ms": ms, "tflops": 4.0 * bsz * heads * seq * seq * dim / ms / 1e9,
+                     "buffer_sets": 4, "timing": method}
+    return out
+
+
 def gpu_arm(args) -> None:
     import torch
     import torch.distributed as dist
@@ -467,6 +480,7 @@ def gpu_arm(args) -> None:
         del a, b, c
         torch.cuda.empty_cache()
         line["memory_bound"] = memory_bound_rows(torch, ctx, stream, peaks["hbm_gbs"])
+        line["attention"] = attention_rows(torch, ctx)
         line["memory_bound_peak"] = {"hbm_gbs": peaks["hbm_gbs"], "source": peaks["source"]}
         tflops, threads, kind, sample, _ = cpu_gemm_sample(size, 2, 1)
         line["cpu_baseline"] = {"value": tflops, "unit": "TFLOP/s", "cores": threads, "kind": kind,

@@ -29,9 +29,19 @@
 // look-back spin runs out, the kernel records kStatusScanLookbackTimeout in the
 // status word, stops and returns; other blocks see the word and stop too.
 //
+// Data path: a block keeps a ring of three 16 KiB tile buffers in shared memory,
+// filled by bulk copies (TMA) that one thread starts two tiles ahead, so loads
+// never stop while a block waits in its look-back. The work on a tile is split
+// in two stages that are software-pipelined across tiles: stage A (as soon as
+// the tile's bytes have landed) forms the tile's total and publishes it as the
+// tile's aggregate; stage B (one tile later) does the look-back, the final
+// prefixes and the store, re-reading the tile from shared memory. Aggregates are
+// therefore visible about one tile-time before their own look-back starts, and a
+// look-back rarely has to wait for a predecessor.
+//
 // HBM-bound: 8 bytes per element; the scratch traffic is 16 bytes per
 // 4096-element tile.
-#include "kh_device.cuh"
+#include "kh_tcgen05.cuh"
 
 namespace {
 
@@ -41,6 +51,7 @@ constexpr int kRows = kPerThread / 4;        // float4 per thread per tile
 constexpr int kTile = kThreads * kPerThread; // 4096 elements
 constexpr uint32_t kSpinLimit = 1u << 22;
 constexpr int kLook = 8; // tile descriptors each lane reads per look-back step
+constexpr int kSlots = 3; // tile buffers per block: one being stored, one reduced, one loading
 
 __device__ __forceinline__ uint32_t ld_relaxed_u32(const uint32_t *p) {
   uint32_t v;
@@ -76,9 +87,11 @@ __device__ __forceinline__ uint32_t decode_descriptor(unsigned long long w0, uns
 extern "C" __global__ void __launch_bounds__(kThreads, 4)
 scan(KH_MEMREF1(const float, x), KH_MEMREF1(float, y), KH_MEMREF1(unsigned long long, state),
      uint32_t epoch, unsigned long long ticket_base) {
+  extern __shared__ __align__(16) uint8_t ring_raw[]; // kSlots tile buffers
+  __shared__ __align__(8) uint64_t full_bar[kSlots];
+  __shared__ long long s_tile[kSlots]; // tile held by each buffer; >= num_tiles: none
   __shared__ double warp_totals[kRows * (kThreads / 32)];
   __shared__ double s_exclusive;
-  __shared__ unsigned long long s_tile[2];
   __shared__ int s_abort;
 
   const float *__restrict__ x = KH_DATA(x);
@@ -87,56 +100,85 @@ scan(KH_MEMREF1(const float, x), KH_MEMREF1(float, y), KH_MEMREF1(unsigned long 
   const int64_t n = x_size0;
   const int64_t num_tiles = (n + kTile - 1) / kTile;
   uint32_t *status = reinterpret_cast<uint32_t *>(state + 1);
+  float *ring = reinterpret_cast<float *>(ring_raw);
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const bool vec_ok = khd::is_aligned16(x) && khd::is_aligned16(y) && x_stride0 == 1 && y_stride0 == 1;
+  const bool bulk_ok = khd::is_aligned16(x) && x_stride0 == 1; // tiles start 16 KiB apart
+  const bool vec_out = khd::is_aligned16(y) && y_stride0 == 1;
+  const uint32_t bar0 = khd::smem_u32(&full_bar[0]);
 
   if (tid == 0) {
-    s_tile[0] = atomicAdd(state, 1ull) - ticket_base;
     s_abort = 0;
+    for (int s = 0; s < kSlots; ++s) khd::mbar_init(bar0 + 8 * s, 1);
+    khd::mbar_fence_init();
   }
   __syncthreads();
 
-  // Persistent over tickets: any grid size works, and a grid larger than the
-  // tile count just finds no ticket. A ticket is only taken when the block is
-  // ready to load that tile: a tile that is claimed early publishes its
-  // aggregate late, and every later tile's look-back would wait for it.
-  for (int it = 0;; ++it) {
-    const int64_t tile = static_cast<int64_t>(s_tile[it & 1]);
-    if (tile >= num_tiles) {
-      // Every block ends on exactly one surplus ticket, so a clean launch moves
-      // the counter by num_tiles + gridDim.x: the host advances ticket_base by that.
-      return;
+  // Thread 0 only. Takes the next ticket (tiles are claimed in ticket order, and a
+  // block works through its tiles in the order it claimed them, so a tile only ever
+  // waits for tiles that are being worked on) and starts the copy of that tile into
+  // `slot`. Once a ticket is past the end no more are taken: every block ends on
+  // exactly one surplus ticket, so a clean launch moves the counter by
+  // num_tiles + gridDim.x, which is what the host advances ticket_base by.
+  bool exhausted = false;
+  const auto fill = [&](int slot) {
+    long long tile = num_tiles;
+    if (!exhausted) {
+      tile = static_cast<long long>(atomicAdd(state, 1ull) - ticket_base);
+      exhausted = tile >= num_tiles;
     }
-    // Element order inside a tile: kRows rows of 1024 elements; thread t owns the
-    // four consecutive elements 4t..4t+3 of every row, so each load and store
-    // instruction of a warp covers one contiguous 512-byte run. The inputs stay
-    // in registers as fp32; fp64 prefixes are formed twice (totals now, outputs
-    // later) instead of being held, which keeps four blocks resident per SM.
-    const int64_t tile_base = tile * kTile;
-    const bool full_tile = tile_base + kTile <= n;
-    float4 f[kRows];
-    if (vec_ok && full_tile) {
-      const float4 *p = reinterpret_cast<const float4 *>(x + tile_base) + tid;
-#pragma unroll
-      for (int i = 0; i < kRows; ++i) f[i] = __ldcs(p + i * kThreads);
+    s_tile[slot] = tile < num_tiles ? tile : num_tiles;
+    if (tile >= num_tiles || !bulk_ok) return;
+    const int64_t base = tile * kTile;
+    const int64_t count = (n - base < kTile) ? (n - base) : kTile;
+    const uint32_t bytes = static_cast<uint32_t>(count * 4) & ~15u;
+    float *dst = ring + slot * kTile;
+    for (int64_t e = bytes / 4; e < count; ++e) dst[e] = x[base + e]; // at most 3 tail elements
+    if (bytes != 0) {
+      khd::mbar_arrive_expect_tx(bar0 + 8 * slot, bytes);
+      asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                       khd::smem_u32(dst)),
+                   "l"(x + base), "r"(bytes), "r"(bar0 + 8 * slot)
+                   : "memory");
     } else {
-#pragma unroll
-      for (int i = 0; i < kRows; ++i) {
-        float t[4];
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          const int64_t e = tile_base + i * (kThreads * 4) + tid * 4 + j;
-          t[j] = e < n ? x[e * x_stride0] : 0.f;
-        }
-        f[i] = make_float4(t[0], t[1], t[2], t[3]);
-      }
+      khd::mbar_arrive(bar0 + 8 * slot);
     }
+  };
+
+  // Stage A of the block's seq-th tile: wait for its bytes, form the per-thread
+  // exclusive offsets inside the tile and the tile total, publish the total.
+  // Element order inside a tile: kRows rows of 1024 elements; thread t owns the
+  // four consecutive elements 4t..4t+3 of every row, so each shared-memory read
+  // and each global store of a warp covers one contiguous 512-byte run.
+  // Returns false when a wait ran out (block-uniform).
+  const auto stage_a = [&](int seq, int64_t tile, double (&thread_exclusive)[kRows], double &block_total) -> bool {
+    const int slot = seq % kSlots;
+    float *buf = ring + slot * kTile;
+    const int64_t tile_base = tile * kTile;
+    if (bulk_ok) {
+      const bool ok = khd::mbar_wait(bar0 + 8 * slot, static_cast<uint32_t>(seq / kSlots) & 1u, &s_abort, status,
+                                     khd::kStatusTmaWaitTimeout, static_cast<uint32_t>(tile));
+      if (__syncthreads_or(!ok)) return false;
+    } else {
+      // strided or misaligned input: the threads fetch the tile themselves
+      for (int e = tid; e < kTile; e += kThreads)
+        buf[e] = tile_base + e < n ? x[(tile_base + e) * x_stride0] : 0.f;
+      __syncthreads();
+    }
+    const bool full_tile = tile_base + kTile <= n;
     double run_total[kRows], incl[kRows];
 #pragma unroll
     for (int i = 0; i < kRows; ++i) {
-      run_total[i] = ((static_cast<double>(f[i].x) + static_cast<double>(f[i].y)) +
-                      static_cast<double>(f[i].z)) + static_cast<double>(f[i].w);
+      float4 f = *reinterpret_cast<const float4 *>(buf + i * (kThreads * 4) + tid * 4);
+      if (!full_tile) {
+        const int64_t e = tile_base + i * (kThreads * 4) + tid * 4;
+        if (e >= n) f.x = 0.f;
+        if (e + 1 >= n) f.y = 0.f;
+        if (e + 2 >= n) f.z = 0.f;
+        if (e + 3 >= n) f.w = 0.f;
+      }
+      run_total[i] = ((static_cast<double>(f.x) + static_cast<double>(f.y)) + static_cast<double>(f.z)) +
+                     static_cast<double>(f.w);
       incl[i] = run_total[i];
     }
 #pragma unroll
@@ -153,20 +195,43 @@ scan(KH_MEMREF1(const float, x), KH_MEMREF1(float, y), KH_MEMREF1(unsigned long 
     }
     __syncthreads();
     // (row, warp) totals in element order; everything before mine is my offset
-    double thread_exclusive[kRows];
-    double block_total = 0.0;
-    {
-      double running = 0.0;
+    double running = 0.0;
 #pragma unroll
-      for (int i = 0; i < kRows; ++i) {
+    for (int i = 0; i < kRows; ++i) {
 #pragma unroll
-        for (int w = 0; w < kThreads / 32; ++w) {
-          if (w == warp) thread_exclusive[i] = running + (incl[i] - run_total[i]);
-          running += warp_totals[i * (kThreads / 32) + w];
-        }
+      for (int w = 0; w < kThreads / 32; ++w) {
+        if (w == warp) thread_exclusive[i] = running + (incl[i] - run_total[i]);
+        running += warp_totals[i * (kThreads / 32) + w];
       }
-      block_total = running;
     }
+    block_total = running;
+    // tile 0 has nothing before it: its total already is its inclusive prefix
+    if (tid == 0) publish(state + 2 + 2 * tile, block_total, (epoch << 2) | (tile == 0 ? 2u : 1u));
+    return true;
+  };
+
+  if (tid == 0) {
+    fill(0);
+    fill(1);
+  }
+  __syncthreads();
+  double next_exclusive[kRows] = {};
+  double next_total = 0.0;
+  if (s_tile[0] < num_tiles && !stage_a(0, s_tile[0], next_exclusive, next_total)) return;
+
+  for (int seq = 0;; ++seq) {
+    const int64_t tile = s_tile[seq % kSlots];
+    if (tile >= num_tiles) break;
+    double thread_exclusive[kRows];
+#pragma unroll
+    for (int i = 0; i < kRows; ++i) thread_exclusive[i] = next_exclusive[i];
+    const double block_total = next_total;
+    // the buffer of the tile before this one is free: start the tile after next
+    if (tid == 0) fill((seq + 2) % kSlots);
+    // stage A of the next tile first, so that its aggregate is out before this
+    // tile's look-back begins (stage_a's barriers also publish s_tile to the block)
+    const int64_t next_tile = s_tile[(seq + 1) % kSlots];
+    if (next_tile < num_tiles && !stage_a(seq + 1, next_tile, next_exclusive, next_total)) break;
 
     // ---- decoupled look-back (warp 0): kLook descriptors per lane, so one
     //      round trip to L2 covers a window of 32 * kLook preceding tiles --------
@@ -174,10 +239,7 @@ scan(KH_MEMREF1(const float, x), KH_MEMREF1(float, y), KH_MEMREF1(unsigned long 
       unsigned long long *slot = state + 2 + 2 * tile;
       double exclusive = 0.0;
       bool aborted = false;
-      if (tile == 0) {
-        if (lane == 0) publish(slot, block_total, (epoch << 2) | 2u);
-      } else {
-        if (lane == 0) publish(slot, block_total, (epoch << 2) | 1u);
+      if (tile != 0) { // tile 0 published its inclusive prefix in stage A
         int64_t window_end = tile; // look at tiles [window_end - 32*kLook, window_end)
         while (true) {
           uint32_t st[kLook];
@@ -244,40 +306,39 @@ scan(KH_MEMREF1(const float, x), KH_MEMREF1(float, y), KH_MEMREF1(unsigned long 
       }
       if (lane == 0) {
         s_exclusive = exclusive;
-        s_abort = aborted ? 1 : 0;
+        if (aborted) s_abort = 1;
       }
     }
     __syncthreads();
-    if (s_abort) return;
+    if (s_abort) break;
     const double tile_offset = s_exclusive;
 
-    // ---- store (one rounding per element) -----------------------------------
-    if (vec_ok && full_tile) {
-      float4 *p = reinterpret_cast<float4 *>(y + tile_base) + tid;
+
+    // ---- store (one rounding per element), values re-read from the tile buffer --------
+    const float *buf = ring + (seq % kSlots) * kTile;
+    const int64_t tile_base = tile * kTile;
+    const bool full_tile = tile_base + kTile <= n;
 #pragma unroll
-      for (int i = 0; i < kRows; ++i) {
-        double o = tile_offset + thread_exclusive[i];
-        float4 r;
-        o += static_cast<double>(f[i].x); r.x = static_cast<float>(o);
-        o += static_cast<double>(f[i].y); r.y = static_cast<float>(o);
-        o += static_cast<double>(f[i].z); r.z = static_cast<float>(o);
-        o += static_cast<double>(f[i].w); r.w = static_cast<float>(o);
-        __stcs(p + i * kThreads, r);
-      }
-    } else {
-#pragma unroll
-      for (int i = 0; i < kRows; ++i) {
-        double o = tile_offset + thread_exclusive[i];
-        const float t[4] = {f[i].x, f[i].y, f[i].z, f[i].w};
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          const int64_t e = tile_base + i * (kThreads * 4) + tid * 4 + j;
-          o += static_cast<double>(t[j]);
-          if (e < n) y[e * y_stride0] = static_cast<float>(o);
-        }
+    for (int i = 0; i < kRows; ++i) {
+      const float4 f = *reinterpret_cast<const float4 *>(buf + i * (kThreads * 4) + tid * 4);
+      double o = tile_offset + thread_exclusive[i];
+      float4 r;
+      o += static_cast<double>(f.x); r.x = static_cast<float>(o);
+      o += static_cast<double>(f.y); r.y = static_cast<float>(o);
+      o += static_cast<double>(f.z); r.z = static_cast<float>(o);
+      o += static_cast<double>(f.w); r.w = static_cast<float>(o);
+      const int64_t e = tile_base + i * (kThreads * 4) + tid * 4;
+      if (vec_out && full_tile) {
+        __stcs(reinterpret_cast<float4 *>(y + e), r);
+      } else {
+        if (e < n) y[e * y_stride0] = r.x;
+        if (e + 1 < n) y[(e + 1) * y_stride0] = r.y;
+        if (e + 2 < n) y[(e + 2) * y_stride0] = r.z;
+        if (e + 3 < n) y[(e + 3) * y_stride0] = r.w;
       }
     }
-    if (tid == 0) s_tile[(it + 1) & 1] = atomicAdd(state, 1ull) - ticket_base;
-    __syncthreads(); // shared words are rewritten by the next ticket
+    __syncthreads(); // the tile buffer and the shared words are free again
   }
+  if (s_abort) // a wait ran out: give the copies still in flight time to land before the block leaves
+    for (int i = 0; i < 64; ++i) __nanosleep(10000);
 }

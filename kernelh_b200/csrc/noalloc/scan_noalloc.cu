@@ -16,7 +16,8 @@
 //   * n <= kh_scan_noalloc_max_elements() (16,777,216); larger sizes are
 //     refused with a usage error, never truncated.
 //   * The first call on a device looks up the array's device address and the
-//     SM count (once per device, with that device current). Make that first
+//     SM count and raises the kernel's shared-memory limit (once per device,
+//     with that device current). Make that first
 //     call outside any stream capture.
 //   * All calls on a device share the one array. The part a call uses is
 //     cleared on the stream before its kernel, so a call never sees an earlier
@@ -90,6 +91,11 @@ extern "C" int kh_scan_noalloc(const float *x, float *y, int64_t n, void *stream
     if (cudaError_t e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
         e != cudaSuccess)
       return fail_cuda("cudaDeviceGetAttribute", e);
+    // the kernel's ring of tile buffers is dynamic shared memory beyond the default limit
+    if (cudaError_t e = cudaFuncSetAttribute(kh_scan_noalloc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             kSlots * kTile * 4);
+        e != cudaSuccess)
+      return fail_cuda("cudaFuncSetAttribute", e);
     d.sm_count = sms > 0 ? sms : 1;
     d.scratch = static_cast<unsigned long long *>(p);
   }
@@ -101,7 +107,7 @@ extern "C" int kh_scan_noalloc(const float *x, float *y, int64_t n, void *stream
     return fail_cuda("cudaMemsetAsync", e);
   const int64_t want = static_cast<int64_t>(d.sm_count) * 4;
   const unsigned grid = static_cast<unsigned>(tiles < want ? tiles : want);
-  kh_scan_noalloc_kernel<<<grid, kThreads, 0, s>>>(
+  kh_scan_noalloc_kernel<<<grid, kThreads, kSlots * kTile * 4, s>>>(
       x, x, 0, n, 1,                      // x as a rank-1 memref descriptor
       y, y, 0, n, 1,                      // y
       d.scratch, d.scratch, 0, words, 1,  // state

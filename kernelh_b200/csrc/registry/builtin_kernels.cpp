@@ -168,6 +168,7 @@ KernelPlan plan_scan(const ShapeMap &shape, const DeviceLimits &l) {
   s.entry = "scan";
   s.block = {256, 1, 1};
   s.grid = {static_cast<unsigned>(std::min<int64_t>(tiles, sm_count(l) * 4)), 1, 1};
+  s.dynamic_smem = 3 * kScanTile * 4; // ring of three tile buffers
   s.param_count = 17;
   p.steps = {s};
   p.workspace_bytes = static_cast<size_t>(2 + 2 * tiles) * 8;
