@@ -7,35 +7,50 @@
 // rescale, 268-276; head_dim pinned to 64 and seq % 64 == 0, 109-120). Entry
 // symbol `attention`; the first 44 parameters are the reference's: (Q, K, V,
 // O) as rank-4 memref descriptors. The TMA-fed kernel then takes six tensor
-// maps and a status pointer.
+// maps, the scale exponents and a status pointer.
 //
 // Flash-style: a CTA owns 128 query rows of one (batch, head) and streams K/V
-// in tiles of 64 keys. Both contractions run on tcgen05 tensor cores in 3xTF32
-// (operands split once into hi = tf32(x), lo = x - hi; products lo.hi, hi.lo,
-// hi.hi into one fp32 accumulator):
+// in tiles of 64 keys. Both contractions run on tcgen05 tensor cores as three
+// fp16 products of scaled hi/lo splits (see kh_fp16_split.cuh; products lo.hi,
+// hi.lo, hi.hi into one fp32 accumulator):
 //   S = Q K^T   A = Q tile (shared memory, K-major), B = K tile (K-major)
-//   PV = P V    A = P (tensor memory), B = V^T tile (K-major over keys)
+//   PV = P V    A = P (tensor memory, two fp16 per column), B = V^T tile
+//               (K-major over keys)
+// Q, K and V are scaled by one power of two per tile of 64 rows (the tile's
+// largest magnitude goes to [2^14, 2^15)). A score tile therefore carries one
+// factor per (query tile, key tile), which the softmax folds, with 1/sqrt(64),
+// into the constant it multiplies that tile's scores by; a PV tile carries the
+// factor of its V tile, applied when the tile is added to the running output
+// row. P lies in [0, 1] and is multiplied by 2^14 before its split so that its
+// lo part stays a normal fp16.
 // Scores, probabilities and the per-tile PV product live in tensor memory;
 // the running max, sum and the 64-wide output row live in registers of the
 // thread that owns the row (one thread per tensor-memory lane).
 //
 // Two launches:
-//  attention_split  writes Q/8 (the 1/sqrt(64) scale is exact), K and V^T as
-//      hi/lo pairs into scratch.
+//  attention_split  writes Q, K and V^T as scaled fp16 hi/lo pairs into scratch
+//      and the exponent of every 64-row tile.
 //  attention  warp 0 feeds TMA (Q once; separate 2-deep rings of K and V^T
-//      tiles, 32 KiB each, so that K of tile j+2 can load as soon as S_j has
-//      run); warp 1 issues the MMAs (S of tile j+1 is issued before PV of tile
-//      j so the tensor core works while softmax runs); warps 2-5 and 6-9 are
-//      two softmax groups (one thread per query row each) that take the even
-//      and the odd tiles with their own running max, sum and output row and
-//      are merged at the end, so two tiles are in the softmax stage at once.
+//      tiles, so that K of tile j+2 can load as soon as S_j has run); warp 1
+//      issues the MMAs (S of tile j+1 is issued before PV of tile j so the
+//      tensor core works while softmax runs); warps 2-5 and 6-9 are two
+//      softmax groups (one thread per query row each) that take the even and
+//      the odd tiles with their own running max, sum and output row and are
+//      merged at the end, so two tiles are in the softmax stage at once.
 //      Scores, P and PV are double buffered in tensor memory, one set per group.
 //
-// Tensor-bound: 4 b h s^2 d useful flops; 3xTF32 puts the ceiling at one third
-// of the TF32 tensor rate.
+// Tensor-bound: 4 b h s^2 d useful flops; three products put the ceiling at one
+// third of the fp16 tensor rate.
+#include "kh_fp16_split.cuh"
 #include "kh_tcgen05.cuh"
 
 namespace {
+
+using khd::Half8;
+using khd::RowScale;
+using khd::row_scale;
+using khd::scale_shift;
+using khd::split_fp16x2;
 
 constexpr int kHeadDim = 64;
 constexpr int kBQ = 128;  // query rows per CTA
@@ -43,21 +58,16 @@ constexpr int kBKV = 64;  // keys per tile
 constexpr int kStages = 2;
 constexpr int kSoftmaxThreads = 256; // two groups of one thread per query row
 constexpr int kThreads = 64 + kSoftmaxThreads;
-constexpr int kChunkRowsBytes = 128; // one swizzle row: 32 fp32
-constexpr int kQChunkBytes = kBQ * kChunkRowsBytes;   // 16 KiB: 128 rows x 32 fp32
-constexpr int kKVChunkBytes = kBKV * kChunkRowsBytes; // 8 KiB: 64 rows x 32 fp32
-constexpr int kQBytes = 4 * kQChunkBytes;             // hi c0,c1 + lo c0,c1 = 64 KiB
-constexpr int kHalfStageBytes = 4 * kKVChunkBytes;    // one K (or V^T) tile: hi c0,c1 + lo c0,c1 = 32 KiB
-// tensor-memory columns: two score buffers, two P buffers (64 hi + 64 lo columns
-// each), two PV buffers
-constexpr uint32_t kColS0 = 0, kColS1 = 64, kColP0 = 128, kColP1 = 256, kColPV0 = 384, kColPV1 = 448;
+constexpr int kRowBytes = 128;                       // 64 fp16: one 128-byte swizzle row
+constexpr int kQTileBytes = kBQ * kRowBytes;         // 16 KiB: 128 rows, hi or lo
+constexpr int kKVTileBytes = kBKV * kRowBytes;       // 8 KiB: 64 rows (keys, or rows of V^T), hi or lo
+constexpr int kQBytes = 2 * kQTileBytes;             // hi + lo = 32 KiB
+constexpr int kHalfStageBytes = 2 * kKVTileBytes;    // one K (or V^T) tile: hi + lo = 16 KiB
+constexpr int kPShift = 14;                          // P is split as P * 2^14
+// tensor-memory columns: two score buffers, two P buffers (32 columns of packed
+// fp16 pairs for hi, 32 for lo), two PV buffers
+constexpr uint32_t kColS0 = 0, kColS1 = 64, kColP0 = 128, kColP1 = 192, kColPV0 = 256, kColPV1 = 320;
 constexpr uint32_t kTmemCols = 512;
-
-__device__ __forceinline__ float tf32_hi(float x) {
-  uint32_t u = __float_as_uint(x);
-  u = (u + 0x1000u) & 0xFFFFE000u;
-  return __uint_as_float(u);
-}
 
 // 2^x by the special-function unit (2 ulp, flushes denormals): the arguments
 // here are <= 0 and the results feed a sum of at least 1.
@@ -67,11 +77,25 @@ __device__ __forceinline__ float fast_exp2(float x) {
   return y;
 }
 
-// D[tmem] (+)= A[tmem] * B[smem]
-__device__ __forceinline__ void umma_tf32_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t desc_b,
-                                             uint32_t idesc, uint32_t accumulate) {
+// Instruction descriptor for kind::f16 with fp16 operands, fp32 accumulate, both
+// K-major: [4,6) D format 1 = f32; [7,10) / [10,13) A / B format 0 = f16;
+// [17,23) N >> 3; [24,29) M >> 4.
+__host__ __device__ constexpr uint32_t umma_idesc_f16(int m, int n) {
+  return (1u << 4) | (static_cast<uint32_t>(n >> 3) << 17) | (static_cast<uint32_t>(m >> 4) << 24);
+}
+// D[tmem] (+)= A[smem] * B[smem]
+__device__ __forceinline__ void umma_f16_ss(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
+                                            uint32_t accumulate) {
   asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-               "tcgen05.mma.cta_group::1.kind::tf32 [%0], [%1], %2, %3, p;\n\t}" ::"r"(tmem_d),
+               "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_d),
+               "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+               : "memory");
+}
+// D[tmem] (+)= A[tmem] * B[smem]; A holds two fp16 per 32-bit column (k even in the low half)
+__device__ __forceinline__ void umma_f16_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t desc_b, uint32_t idesc,
+                                            uint32_t accumulate) {
+  asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+               "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}" ::"r"(tmem_d),
                "r"(tmem_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
                : "memory");
 }
@@ -97,55 +121,99 @@ __device__ __forceinline__ void tmem_st_wait() {
   asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
 }
 
+__device__ __forceinline__ uint32_t half2_bits(__half2 h) { return *reinterpret_cast<uint32_t *>(&h); }
+
 } // namespace
 
-// Q, K, V [bh, seq, 64] -> q_hi, q_lo (scaled by 1/8), k_hi, k_lo [bh*seq, 64]
-// and vt_hi, vt_lo [bh*64, seq] (V transposed per (batch, head)).
+// Q, K, V [bh, seq, 64] -> q_hi, q_lo, k_hi, k_lo [bh*seq, 64] and vt_hi, vt_lo
+// [bh*64, seq] (V transposed per (batch, head)) as fp16. The unit of scaling is
+// a tile of 64 rows (queries or keys) of one slice: a block takes one tile of one
+// tensor at a time, finds its largest magnitude, and writes the two splits scaled
+// by the exponent that gives; shifts[(t * bh + slice) * tiles + tile] receives
+// the exponent (t = 0, 1, 2 for Q, K, V).
 extern "C" __global__ void __launch_bounds__(256)
 attention_split(KH_MEMREF4(const float, q), KH_MEMREF4(const float, k), KH_MEMREF4(const float, v),
-                float *__restrict__ q_hi, float *__restrict__ q_lo, float *__restrict__ k_hi,
-                float *__restrict__ k_lo, float *__restrict__ vt_hi, float *__restrict__ vt_lo) {
-  __shared__ float tile[32][33];
-  const float *__restrict__ q = KH_DATA(q);
-  const float *__restrict__ k = KH_DATA(k);
-  const float *__restrict__ v = KH_DATA(v);
+                __half *__restrict__ q_hi, __half *__restrict__ q_lo, __half *__restrict__ k_hi,
+                __half *__restrict__ k_lo, __half *__restrict__ vt_hi, __half *__restrict__ vt_lo,
+                int *__restrict__ shifts) {
+  // float4 groups of a row are stored at group ^ (row / 8 mod 8): conflict-free both ways
+  __shared__ __align__(16) float tile[64][64];
+  __shared__ float warp_max[8];
   const int64_t bh = q_size0 * q_size1, seq = q_size2;
-  const int64_t total4 = bh * seq * kHeadDim / 4;
-  const int64_t tid = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
-  const int64_t nthreads = static_cast<int64_t>(gridDim.x) * blockDim.x;
-  // Q and K keep their layout (the tensors are contiguous, so a flat sweep does).
-  for (int64_t i = tid; i < total4; i += nthreads) {
-    const float4 fq = __ldcs(reinterpret_cast<const float4 *>(q) + i);
-    const float4 fk = __ldcs(reinterpret_cast<const float4 *>(k) + i);
-    float4 h, l;
-    const float sq[4] = {fq.x * 0.125f, fq.y * 0.125f, fq.z * 0.125f, fq.w * 0.125f};
-    h = make_float4(tf32_hi(sq[0]), tf32_hi(sq[1]), tf32_hi(sq[2]), tf32_hi(sq[3]));
-    l = make_float4(sq[0] - h.x, sq[1] - h.y, sq[2] - h.z, sq[3] - h.w);
-    reinterpret_cast<float4 *>(q_hi)[i] = h;
-    reinterpret_cast<float4 *>(q_lo)[i] = l;
-    h = make_float4(tf32_hi(fk.x), tf32_hi(fk.y), tf32_hi(fk.z), tf32_hi(fk.w));
-    l = make_float4(fk.x - h.x, fk.y - h.y, fk.z - h.z, fk.w - h.w);
-    reinterpret_cast<float4 *>(k_hi)[i] = h;
-    reinterpret_cast<float4 *>(k_lo)[i] = l;
+  const int64_t tiles = seq >> 6;
+  const float *const src[3] = {KH_DATA(q), KH_DATA(k), KH_DATA(v)};
+  __half *const dst_hi[2] = {q_hi, k_hi};
+  __half *const dst_lo[2] = {q_lo, k_lo};
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  // the tile of a job is 64 x 64 contiguous values = 1024 float4; a thread takes float4 tid, tid + 256, ...
+  const int64_t jobs = 3 * bh * tiles;
+  const auto tile_of = [&](int64_t job) {
+    const int64_t t = job / (bh * tiles), rest = job - t * bh * tiles; // rest = slice * tiles + tile
+    return reinterpret_cast<const float4 *>(src[t] + rest * (64 * kHeadDim)) + threadIdx.x;
+  };
+  float4 n0 = make_float4(0.f, 0.f, 0.f, 0.f), n1 = n0, n2 = n0, n3 = n0;
+  if (blockIdx.x < jobs) {
+    const float4 *p = tile_of(blockIdx.x);
+    n0 = __ldcs(p); n1 = __ldcs(p + 256); n2 = __ldcs(p + 512); n3 = __ldcs(p + 768);
   }
-  // V: 32 x 32 tiles through shared memory, [seq, 64] -> [64, seq] per (batch, head).
-  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
-  const int64_t tiles_s = seq >> 5, tiles_per_bh = tiles_s * 2;
-  for (int64_t t = blockIdx.x; t < bh * tiles_per_bh; t += gridDim.x) {
-    const int64_t b = t / tiles_per_bh, r = t - b * tiles_per_bh;
-    const int64_t s0 = (r >> 1) << 5, d0 = (r & 1) << 5;
-    const float *src = v + b * seq * kHeadDim;
+  for (int64_t job = blockIdx.x; job < jobs; job += gridDim.x) {
+    const int64_t t = job / (bh * tiles), rest = job - t * bh * tiles;
+    const int64_t slice = rest / tiles, s0 = (rest - slice * tiles) << 6;
+    const float4 f0 = n0, f1 = n1, f2 = n2, f3 = n3;
+    if (job + gridDim.x < jobs) { // the next tile's loads fly while this one is worked on
+      const float4 *p = tile_of(job + gridDim.x);
+      n0 = __ldcs(p); n1 = __ldcs(p + 256); n2 = __ldcs(p + 512); n3 = __ldcs(p + 768);
+    }
+    float m = fmaxf(fmaxf(fmaxf(fabsf(f0.x), fabsf(f0.y)), fmaxf(fabsf(f0.z), fabsf(f0.w))),
+                    fmaxf(fmaxf(fabsf(f1.x), fabsf(f1.y)), fmaxf(fabsf(f1.z), fabsf(f1.w))));
+    m = fmaxf(m, fmaxf(fmaxf(fmaxf(fabsf(f2.x), fabsf(f2.y)), fmaxf(fabsf(f2.z), fabsf(f2.w))),
+                       fmaxf(fmaxf(fabsf(f3.x), fabsf(f3.y)), fmaxf(fabsf(f3.z), fabsf(f3.w)))));
+    m = khd::warp_max(m);
+    __syncthreads(); // the previous job is done with warp_max and the tile
+    if (lane == 0) warp_max[warp] = m;
+    if (t == 2) {
+      // V goes through shared memory: row = key, 16 float4 groups per row; float4 tid + 256 j
+      // is group tid % 16 of row tid / 16 + 16 j
+      const int sl = threadIdx.x >> 4, g = threadIdx.x & 15;
+      *reinterpret_cast<float4 *>(&tile[sl][(g ^ ((sl >> 3) & 7)) * 4]) = f0;
+      *reinterpret_cast<float4 *>(&tile[sl + 16][(g ^ (((sl + 16) >> 3) & 7)) * 4]) = f1;
+      *reinterpret_cast<float4 *>(&tile[sl + 32][(g ^ (((sl + 32) >> 3) & 7)) * 4]) = f2;
+      *reinterpret_cast<float4 *>(&tile[sl + 48][(g ^ (((sl + 48) >> 3) & 7)) * 4]) = f3;
+    }
     __syncthreads();
+    m = warp_max[0];
 #pragma unroll
-    for (int j = 0; j < 4; ++j) tile[ty + 8 * j][tx] = src[(s0 + ty + 8 * j) * kHeadDim + d0 + tx];
-    __syncthreads();
+    for (int w = 1; w < 8; ++w) m = fmaxf(m, warp_max[w]);
+    const int shift = scale_shift(m);
+    const RowScale sc = row_scale(shift);
+    if (threadIdx.x == 0) shifts[job] = shift;
+    if (t < 2) {
+      // four values -> 8 bytes of hi and of lo; a warp store covers 256 contiguous bytes
+      const float4 f[4] = {f0, f1, f2, f3};
+      uint2 *out_hi = reinterpret_cast<uint2 *>(dst_hi[t] + (slice * seq + s0) * kHeadDim) + threadIdx.x;
+      uint2 *out_lo = reinterpret_cast<uint2 *>(dst_lo[t] + (slice * seq + s0) * kHeadDim) + threadIdx.x;
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      const float val = tile[tx][ty + 8 * j];
-      const float h = tf32_hi(val);
-      const int64_t o = (b * kHeadDim + d0 + ty + 8 * j) * seq + s0 + tx;
-      vt_hi[o] = h;
-      vt_lo[o] = val - h;
+      for (int j = 0; j < 4; ++j) {
+        __half2 h01, l01, h23, l23;
+        split_fp16x2(f[j].x, f[j].y, sc, h01, l01);
+        split_fp16x2(f[j].z, f[j].w, sc, h23, l23);
+        out_hi[256 * j] = make_uint2(half2_bits(h01), half2_bits(h23));
+        out_lo[256 * j] = make_uint2(half2_bits(l01), half2_bits(l23));
+      }
+    } else {
+      const int sub = lane >> 3, sgroup = lane & 7; // 4 rows of V^T per warp store, 8 keys per lane
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {
+        const int dl = warp * 8 + j * 4 + sub;
+        const int col = (((dl >> 2) ^ sgroup) << 2) | (dl & 3); // rows sgroup*8.. share one swizzle
+        Half8 h, l;
+#pragma unroll
+        for (int qd = 0; qd < 4; ++qd)
+          split_fp16x2(tile[sgroup * 8 + 2 * qd][col], tile[sgroup * 8 + 2 * qd + 1][col], sc, h.v[qd], l.v[qd]);
+        const int64_t o = (slice * kHeadDim + dl) * seq + s0 + sgroup * 8;
+        *reinterpret_cast<Half8 *>(vt_hi + o) = h;
+        *reinterpret_cast<Half8 *>(vt_lo + o) = l;
+      }
     }
   }
 }
@@ -155,7 +223,7 @@ attention(KH_MEMREF4(const float, q), KH_MEMREF4(const float, k), KH_MEMREF4(con
           KH_MEMREF4(float, o), const __grid_constant__ khd::TensorMap tm_q_hi,
           const __grid_constant__ khd::TensorMap tm_q_lo, const __grid_constant__ khd::TensorMap tm_k_hi,
           const __grid_constant__ khd::TensorMap tm_k_lo, const __grid_constant__ khd::TensorMap tm_vt_hi,
-          const __grid_constant__ khd::TensorMap tm_vt_lo, uint32_t *status) {
+          const __grid_constant__ khd::TensorMap tm_vt_lo, const int *__restrict__ shifts, uint32_t *status) {
   (void)q_alloc; (void)q_ptr; (void)q_off; (void)q_size3; (void)q_stride0; (void)q_stride1;
   (void)q_stride2; (void)q_stride3;
   (void)k_alloc; (void)k_ptr; (void)k_off; (void)k_size0; (void)k_size1; (void)k_size2; (void)k_size3;
@@ -179,8 +247,8 @@ attention(KH_MEMREF4(const float, q), KH_MEMREF4(const float, k), KH_MEMREF4(con
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
   const uint32_t smem_q = (khd::smem_u32(smem_raw) + 1023u) & ~1023u;
-  const uint32_t smem_k = smem_q + kQBytes;                 // 2 stages of K hi c0,c1 / lo c0,c1
-  const uint32_t smem_v = smem_k + kStages * kHalfStageBytes; // 2 stages of V^T hi c0,c1 / lo c0,c1
+  const uint32_t smem_k = smem_q + kQBytes;                   // 2 stages of K hi, lo
+  const uint32_t smem_v = smem_k + kStages * kHalfStageBytes; // 2 stages of V^T hi, lo
   const uint32_t bar_q = khd::smem_u32(&bars[0]);
   const uint32_t bar_k_full = khd::smem_u32(&bars[1]);
   const uint32_t bar_k_empty = khd::smem_u32(&bars[3]);
@@ -227,10 +295,8 @@ attention(KH_MEMREF4(const float, q), KH_MEMREF4(const float, k), KH_MEMREF4(con
     if (lane == 0) {
       const int q_row = static_cast<int>(bh * seq) + q0;
       khd::mbar_arrive_expect_tx(bar_q, kQBytes);
-      khd::tma_load_2d(smem_q + 0 * kQChunkBytes, &tm_q_hi, 0, q_row, bar_q);
-      khd::tma_load_2d(smem_q + 1 * kQChunkBytes, &tm_q_hi, 32, q_row, bar_q);
-      khd::tma_load_2d(smem_q + 2 * kQChunkBytes, &tm_q_lo, 0, q_row, bar_q);
-      khd::tma_load_2d(smem_q + 3 * kQChunkBytes, &tm_q_lo, 32, q_row, bar_q);
+      khd::tma_load_2d(smem_q, &tm_q_hi, 0, q_row, bar_q);
+      khd::tma_load_2d(smem_q + kQTileBytes, &tm_q_lo, 0, q_row, bar_q);
       for (int j = 0; j < num_kv; ++j) {
         const int s = j & 1;
         const uint32_t phase = static_cast<uint32_t>((j >> 1) & 1);
@@ -242,10 +308,8 @@ attention(KH_MEMREF4(const float, q), KH_MEMREF4(const float, k), KH_MEMREF4(con
           const uint32_t bar = bar_k_full + 8 * s;
           khd::mbar_arrive_expect_tx(bar, kHalfStageBytes);
           const int k_row = static_cast<int>(bh * seq) + j * kBKV;
-          khd::tma_load_2d(st + 0 * kKVChunkBytes, &tm_k_hi, 0, k_row, bar);
-          khd::tma_load_2d(st + 1 * kKVChunkBytes, &tm_k_hi, 32, k_row, bar);
-          khd::tma_load_2d(st + 2 * kKVChunkBytes, &tm_k_lo, 0, k_row, bar);
-          khd::tma_load_2d(st + 3 * kKVChunkBytes, &tm_k_lo, 32, k_row, bar);
+          khd::tma_load_2d(st, &tm_k_hi, 0, k_row, bar);
+          khd::tma_load_2d(st + kKVTileBytes, &tm_k_lo, 0, k_row, bar);
         }
         if (!khd::mbar_wait(bar_v_empty + 8 * s, phase ^ 1u, &s_abort, status,
                             khd::kStatusEmptyWaitTimeout, 1000u + static_cast<uint32_t>(j)))
@@ -256,10 +320,8 @@ attention(KH_MEMREF4(const float, q), KH_MEMREF4(const float, k), KH_MEMREF4(con
           khd::mbar_arrive_expect_tx(bar, kHalfStageBytes);
           const int v_row = static_cast<int>(bh * kHeadDim);
           const int v_col = j * kBKV;
-          khd::tma_load_2d(st + 0 * kKVChunkBytes, &tm_vt_hi, v_col, v_row, bar);
-          khd::tma_load_2d(st + 1 * kKVChunkBytes, &tm_vt_hi, v_col + 32, v_row, bar);
-          khd::tma_load_2d(st + 2 * kKVChunkBytes, &tm_vt_lo, v_col, v_row, bar);
-          khd::tma_load_2d(st + 3 * kKVChunkBytes, &tm_vt_lo, v_col + 32, v_row, bar);
+          khd::tma_load_2d(st, &tm_vt_hi, v_col, v_row, bar);
+          khd::tma_load_2d(st + kKVTileBytes, &tm_vt_lo, v_col, v_row, bar);
         }
       }
     }
@@ -270,22 +332,21 @@ attention(KH_MEMREF4(const float, q), KH_MEMREF4(const float, k), KH_MEMREF4(con
     //      themselves sit under the elected lane. ---------------------------------------
     {
       const bool leader = khd::elect_one();
-      constexpr uint32_t idesc = khd::umma_idesc_tf32(kBQ, kBKV); // M128 N64 for both products
-      // descriptor of chunk c (32 of the 64 k-columns) of a tile, stepped by kk inside it
-      const uint64_t dq_hi = khd::umma_desc_k128(smem_q), dq_lo = khd::umma_desc_k128(smem_q + 2 * kQChunkBytes);
-      constexpr uint64_t kQChunkStep = kQChunkBytes >> 4, kKVChunkStep = kKVChunkBytes >> 4;
+      constexpr uint32_t idesc = umma_idesc_f16(kBQ, kBKV); // M128 N64 K16 for both products
+      // a tile row is one 128-byte swizzle row (64 fp16); a k-step of 16 fp16 moves 32 bytes (2 encoded)
+      const uint64_t dq_hi = khd::umma_desc_k128(smem_q), dq_lo = khd::umma_desc_k128(smem_q + kQTileBytes);
+      constexpr uint64_t kKVTileStep = kKVTileBytes >> 4;
       auto issue_s = [&](int b) {
         const uint64_t dk_hi = khd::umma_desc_k128(smem_k + b * kHalfStageBytes);
-        const uint64_t dk_lo = dk_hi + 2 * kKVChunkStep;
+        const uint64_t dk_lo = dk_hi + kKVTileStep;
         const uint32_t d = tmem_base + (b ? kColS1 : kColS0);
         if (leader) {
 #pragma unroll
-          for (int kk = 0; kk < kHeadDim / 8; ++kk) {
-            const uint64_t qoff = (kk >> 2) * kQChunkStep + (kk & 3) * 2;
-            const uint64_t koff = (kk >> 2) * kKVChunkStep + (kk & 3) * 2;
-            khd::umma_tf32_ss(d, dq_lo + qoff, dk_hi + koff, idesc, kk != 0 ? 1u : 0u);
-            khd::umma_tf32_ss(d, dq_hi + qoff, dk_lo + koff, idesc, 1u);
-            khd::umma_tf32_ss(d, dq_hi + qoff, dk_hi + koff, idesc, 1u);
+          for (int kk = 0; kk < kHeadDim / 16; ++kk) {
+            const uint64_t off = static_cast<uint64_t>(kk * 2);
+            umma_f16_ss(d, dq_lo + off, dk_hi + off, idesc, kk != 0 ? 1u : 0u);
+            umma_f16_ss(d, dq_hi + off, dk_lo + off, idesc, 1u);
+            umma_f16_ss(d, dq_hi + off, dk_hi + off, idesc, 1u);
           }
           khd::umma_commit(bar_s_full + 8 * b);  // scores ready for the softmax threads
           khd::umma_commit(bar_k_empty + 8 * b); // and this K slot may be refilled
@@ -319,16 +380,16 @@ attention(KH_MEMREF4(const float, q), KH_MEMREF4(const float, k), KH_MEMREF4(con
         khd::tc_fence_after_sync();
         // PV_j = P_j V_j: A = P buffer b (tensor memory), B = V^T tile, D = PV buffer b
         const uint64_t dv_hi = khd::umma_desc_k128(smem_v + b * kHalfStageBytes);
-        const uint64_t dv_lo = dv_hi + 2 * kKVChunkStep;
+        const uint64_t dv_lo = dv_hi + kKVTileStep;
         const uint32_t d = tmem_base + (b ? kColPV1 : kColPV0);
         const uint32_t p_base = tmem_base + (b ? kColP1 : kColP0);
         if (leader) {
 #pragma unroll
-          for (int kk = 0; kk < kBKV / 8; ++kk) {
-            const uint64_t voff = (kk >> 2) * kKVChunkStep + (kk & 3) * 2;
-            umma_tf32_ts(d, p_base + 64 + kk * 8, dv_hi + voff, idesc, kk != 0 ? 1u : 0u);
-            umma_tf32_ts(d, p_base + kk * 8, dv_lo + voff, idesc, 1u);
-            umma_tf32_ts(d, p_base + kk * 8, dv_hi + voff, idesc, 1u);
+          for (int kk = 0; kk < kBKV / 16; ++kk) { // 16 keys = 8 packed columns of P
+            const uint64_t voff = static_cast<uint64_t>(kk * 2);
+            umma_f16_ts(d, p_base + 32 + kk * 8, dv_hi + voff, idesc, kk != 0 ? 1u : 0u);
+            umma_f16_ts(d, p_base + kk * 8, dv_lo + voff, idesc, 1u);
+            umma_f16_ts(d, p_base + kk * 8, dv_hi + voff, idesc, 1u);
           }
           khd::umma_commit(bar_pv_full + 8 * b);
           khd::umma_commit(bar_v_empty + 8 * b);
@@ -353,7 +414,14 @@ attention(KH_MEMREF4(const float, q), KH_MEMREF4(const float, k), KH_MEMREF4(con
     for (int i = 0; i < kHeadDim; ++i) acc[i] = 0.f;
     float m = -INFINITY, l = 0.f;
     bool ok = true;
-    constexpr float kLog2e = 1.4426950408889634f;
+    // Exponents of the 64-row tiles: shifts[(t * slices + slice) * tiles + tile], t = 0, 1, 2 for Q, K, V.
+    // The running max `m` is kept in exp2 units, i.e. true score * log2(e) / sqrt(64).
+    const int64_t slices = gridDim.x / q_tiles;
+    const int *k_shifts = shifts + (slices + bh) * num_kv, *v_shifts = shifts + (2 * slices + bh) * num_kv;
+    const int row_q = q0 + row_in_tile;
+    const int shift_q = __ldg(shifts + bh * num_kv + (row_q < seq ? row_q >> 6 : 0));
+    constexpr float kLog2eOverSqrtD = 1.4426950408889634f * 0.125f;
+    float v_factor_prev = 0.f; // 2^-(14 + exponent of the V tile) of this group's previous product
 
     for (int j = g; j < num_kv && ok; j += 2) {
       const uint32_t phase = static_cast<uint32_t>((j >> 1) & 1);
@@ -365,16 +433,17 @@ attention(KH_MEMREF4(const float, q), KH_MEMREF4(const float, k), KH_MEMREF4(con
       khd::tmem_ld_32x32(tmem_base + lane_base + col_s, *reinterpret_cast<uint32_t(*)[32]>(&sv[0]));
       khd::tmem_ld_32x32(tmem_base + lane_base + col_s + 32, *reinterpret_cast<uint32_t(*)[32]>(&sv[32]));
       khd::tmem_ld_wait();
+      // this tile's scores carry 2^(shift_q + shift_k): one positive factor brings them to exp2 units
+      const float f = khd::scale_pow2(kLog2eOverSqrtD, -(shift_q + __ldg(k_shifts + j)));
       float mx = -INFINITY;
 #pragma unroll
       for (int i = 0; i < kBKV; ++i) mx = fmaxf(mx, __uint_as_float(sv[i]));
-      const float m_new = fmaxf(m, mx);
-      const float alpha = fast_exp2((m - m_new) * kLog2e); // m = -inf on the first tile gives 0
-      const float mb = m_new * kLog2e;
+      const float m_new = fmaxf(m, mx * f);
+      const float alpha = fast_exp2(m - m_new); // m = -inf on the first tile gives 0
       float sum = 0.f;
 #pragma unroll
       for (int i = 0; i < kBKV; ++i) {
-        const float p = fast_exp2(fmaf(__uint_as_float(sv[i]), kLog2e, -mb));
+        const float p = fast_exp2(fmaf(__uint_as_float(sv[i]), f, -m_new));
         sv[i] = __float_as_uint(p);
         sum += p;
       }
@@ -395,20 +464,26 @@ attention(KH_MEMREF4(const float, q), KH_MEMREF4(const float, k), KH_MEMREF4(con
           tmem_ld_32x16(tmem_base + lane_base + col_pv + 16 * h, t);
           khd::tmem_ld_wait();
 #pragma unroll
-          for (int i = 0; i < 16; ++i) acc[16 * h + i] = (acc[16 * h + i] + __uint_as_float(t[i])) * alpha;
+          for (int i = 0; i < 16; ++i)
+            acc[16 * h + i] = fmaf(__uint_as_float(t[i]), v_factor_prev, acc[16 * h + i]) * alpha;
         }
       }
-      // P -> tensor memory as hi / lo
+      v_factor_prev = khd::scale_pow2(1.0f, -(kPShift + __ldg(v_shifts + j))); // P was split as P * 2^14
+      // P * 2^14 -> tensor memory as fp16 hi / lo, two keys per 32-bit column
 #pragma unroll
-      for (int h = 0; h < 4; ++h) {
-        uint32_t hi[16];
+      for (int h = 0; h < 2; ++h) {
+        uint32_t hi[16], lo[16];
 #pragma unroll
-        for (int i = 0; i < 16; ++i) hi[i] = __float_as_uint(tf32_hi(__uint_as_float(sv[16 * h + i])));
+        for (int i = 0; i < 16; ++i) {
+          const float p0 = __uint_as_float(sv[32 * h + 2 * i]) * 16384.f;
+          const float p1 = __uint_as_float(sv[32 * h + 2 * i + 1]) * 16384.f;
+          const __half2 h2 = __floats2half2_rn(p0, p1);
+          const float2 back = __half22float2(h2);
+          hi[i] = half2_bits(h2);
+          lo[i] = half2_bits(__floats2half2_rn(p0 - back.x, p1 - back.y));
+        }
         tmem_st_32x16(tmem_base + lane_base + col_p + 16 * h, hi);
-#pragma unroll
-        for (int i = 0; i < 16; ++i)
-          hi[i] = __float_as_uint(__uint_as_float(sv[16 * h + i]) - __uint_as_float(hi[i]));
-        tmem_st_32x16(tmem_base + lane_base + col_p + 64 + 16 * h, hi);
+        tmem_st_32x16(tmem_base + lane_base + col_p + 32 + 16 * h, lo);
       }
       tmem_st_wait();
       khd::tc_fence_before_sync();
@@ -428,7 +503,7 @@ attention(KH_MEMREF4(const float, q), KH_MEMREF4(const float, k), KH_MEMREF4(con
           tmem_ld_32x16(tmem_base + lane_base + col_pv + 16 * h, t);
           khd::tmem_ld_wait();
 #pragma unroll
-          for (int i = 0; i < 16; ++i) acc[16 * h + i] += __uint_as_float(t[i]);
+          for (int i = 0; i < 16; ++i) acc[16 * h + i] = fmaf(__uint_as_float(t[i]), v_factor_prev, acc[16 * h + i]);
         }
       }
     }
@@ -452,7 +527,7 @@ attention(KH_MEMREF4(const float, q), KH_MEMREF4(const float, k), KH_MEMREF4(con
     if (ok && g == 0 && num_kv > 0) {
       const float m1 = merge[0], l1 = merge[1];
       const float mt = fmaxf(m, m1);
-      const float w0 = fast_exp2((m - mt) * kLog2e), w1 = fast_exp2((m1 - mt) * kLog2e);
+      const float w0 = fast_exp2(m - mt), w1 = fast_exp2(m1 - mt);
       const float inv = 1.0f / (l * w0 + l1 * w1);
       const int64_t row = static_cast<int64_t>(q0) + row_in_tile;
       float *orow = out + (bh * seq + row) * kHeadDim;

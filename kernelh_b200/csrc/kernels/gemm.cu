@@ -61,11 +61,17 @@
 //
 // Tensor-bound: 2 m n k useful flops; three MMAs per k-step put the ceiling
 // at one third of the fp16 tensor rate.
-#include <cuda_fp16.h>
-
+#include "kh_fp16_split.cuh"
 #include "kh_tcgen05.cuh"
 
 namespace {
+
+using khd::Half8;
+using khd::RowScale;
+using khd::row_scale;
+using khd::scale_pow2;
+using khd::scale_shift;
+using khd::split_fp16x2;
 
 constexpr int kBM = 128;     // rows per CTA (256 per pair)
 constexpr int kBN = 256;     // columns per pair
@@ -79,50 +85,6 @@ constexpr int kChunkBlocks = 8;             // k-blocks accumulated in tensor me
 constexpr int kEpilogueWarps = 8;
 constexpr int kThreads = 64 + 32 * kEpilogueWarps; // TMA warp + MMA warp + epilogue warps
 constexpr int kGroupM = 8;                  // pair tiles (256 rows) per rasterisation group (L2 reuse of B)
-constexpr int kTargetExponent = 14;         // scaled row / column maxima lie in [2^14, 2^15)
-
-// Power-of-two exponent that brings a row (column) whose largest magnitude is
-// `amax` into the target range; 0 for an all-zero or non-finite row.
-__device__ __forceinline__ int scale_shift(float amax) {
-  if (!(amax > 0.f) || amax > 3.402823466e+38f) return 0;
-  return kTargetExponent - ilogbf(amax);
-}
-
-// x * 2^e for |e| up to 378, exact unless the result leaves the normal fp32
-// range: 2^e is applied as three factors, each a normal fp32 power of two.
-__device__ __forceinline__ float pow2f(int e) { return __int_as_float((e + 127) << 23); }
-__device__ __forceinline__ float scale_pow2(float x, int e) {
-  const int e1 = max(-126, min(127, e));
-  const int r = e - e1;
-  const int e2 = max(-126, min(127, r));
-  return x * pow2f(e1) * pow2f(e2) * pow2f(r - e2);
-}
-
-// The power of two a row (column) is scaled by, prepared once per row: one
-// factor when 2^shift is a normal fp32 number, three otherwise.
-struct RowScale {
-  float f1, f2, f3;
-  bool single;
-};
-__device__ __forceinline__ RowScale row_scale(int shift) {
-  const int e1 = max(-126, min(127, shift));
-  const int r = shift - e1;
-  const int e2 = max(-126, min(127, r));
-  return {pow2f(e1), pow2f(e2), pow2f(r - e2), r == 0};
-}
-// Two scaled values -> their fp16 hi parts and the fp16 of what hi left over.
-// (x - hi is exact in fp32. An infinite input gives hi = inf and lo = NaN: the
-// products are non-finite either way.)
-__device__ __forceinline__ void split_fp16x2(float x0, float x1, const RowScale &sc, __half2 &hi, __half2 &lo) {
-  float s0 = x0 * sc.f1, s1 = x1 * sc.f1;
-  if (!sc.single) {
-    s0 = s0 * sc.f2 * sc.f3;
-    s1 = s1 * sc.f2 * sc.f3;
-  }
-  hi = __floats2half2_rn(s0, s1);
-  const float2 h = __half22float2(hi);
-  lo = __floats2half2_rn(s0 - h.x, s1 - h.y);
-}
 
 // Ordered accesses for the epilogue (see the store loop of gemm_body).
 __device__ __forceinline__ int4 load_shift4(const int *p) {
@@ -150,9 +112,6 @@ __device__ __forceinline__ void multicast_store_float(float *p, float x) {
   asm volatile("multimem.st.weak.global.f32 [%0], %1;" ::"l"(p), "f"(x) : "memory");
 }
 
-struct alignas(16) Half8 {
-  __half2 v[4];
-};
 
 } // namespace
 

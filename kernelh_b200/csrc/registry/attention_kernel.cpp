@@ -1,7 +1,7 @@
 // Registry record of the attention template: shape rules of the reference's
 // lib/dsl/kernels/attention.cpp:94-120 (all four keys required and positive,
 // head_dim pinned to 64, seq a multiple of the 64-key tile), the scratch
-// layout of the hi/lo split, the six tensor maps and the two launches.
+// layout of the scaled fp16 hi/lo split, the six tensor maps and the two launches.
 #include "executor.hpp"
 #include "registry.hpp"
 
@@ -11,7 +11,8 @@ namespace kh {
 namespace {
 
 constexpr int64_t kHeadDim = 64, kBQ = 128, kBKV = 64;
-constexpr size_t kAttnSmem = 64 * 1024 + 2 * 64 * 1024 + 1024;
+// Q hi/lo (32 KiB) + two stages each of K and V^T hi/lo (16 KiB per stage) + alignment slack
+constexpr size_t kAttnSmem = 32 * 1024 + 2 * 2 * 16 * 1024 + 1024;
 
 KernelPlan plan_attention(const ShapeMap &shape, const DeviceLimits &l) {
   for (const char *key : {"batch", "heads", "seq", "head_dim"})
@@ -35,21 +36,21 @@ KernelPlan plan_attention(const ShapeMap &shape, const DeviceLimits &l) {
   for (const char *name : {"Q", "K", "V"}) p.tensors.push_back({name, {b, h, s, d}, false});
   p.tensors.push_back({"O", {b, h, s, d}, true});
   const int64_t elems = b * h * s * d;
-  p.workspace_bytes = static_cast<size_t>(elems) * 4 * 6;
+  // six fp16 arrays, then one exponent per 64-row tile of Q, K and V
+  p.workspace_bytes = static_cast<size_t>(elems) * 2 * 6 + static_cast<size_t>(b * h * (s / kBKV)) * 3 * 4;
   long sms = query_cu_count(l);
   if (sms <= 0) sms = 148;
   LaunchStep split;
   split.entry = "attention_split";
   split.block = {256, 1, 1};
-  const int64_t want = (elems / 4 + 255) / 256;
-  split.grid = {static_cast<unsigned>(std::min<int64_t>(want, sms * 8)), 1, 1};
-  split.param_count = 33 + 6;
+  split.grid = {static_cast<unsigned>(std::min<int64_t>(3 * b * h * (s / kBKV), sms * 8)), 1, 1}; // a block per 64-row tile
+  split.param_count = 33 + 7;
   LaunchStep main;
   main.entry = "attention";
   main.block = {320, 1, 1};
   main.grid = {static_cast<unsigned>(b * h * ((s + kBQ - 1) / kBQ)), 1, 1};
   main.dynamic_smem = kAttnSmem;
-  main.param_count = 44 + 6 + 1;
+  main.param_count = 44 + 6 + 2;
   main.tmem_columns = 512;
   p.steps = {split, main};
   p.work = 4.0 * static_cast<double>(b) * static_cast<double>(h) * static_cast<double>(s) *
@@ -65,9 +66,11 @@ Result<void> run_attention(Executor &ex, const KernelPlan &p, const std::vector<
   const int64_t elems = bh * s * kHeadDim;
   auto ws = ex.workspace(p.workspace_bytes);
   if (!ws) return std::unexpected(ws.error());
-  float *base = static_cast<float *>(*ws);
-  float *q_hi = base, *q_lo = base + elems, *k_hi = base + 2 * elems, *k_lo = base + 3 * elems,
-        *vt_hi = base + 4 * elems, *vt_lo = base + 5 * elems;
+  char *base = static_cast<char *>(*ws);
+  const size_t part = static_cast<size_t>(elems) * 2; // one fp16 array; elems is a multiple of 4096
+  char *q_hi = base, *q_lo = base + part, *k_hi = base + 2 * part, *k_lo = base + 3 * part,
+       *vt_hi = base + 4 * part, *vt_lo = base + 5 * part;
+  char *shifts = base + 6 * part;
 
   auto f_split = ex.function("attention", "attention_split");
   if (!f_split) return std::unexpected(f_split.error());
@@ -76,26 +79,27 @@ Result<void> run_attention(Executor &ex, const KernelPlan &p, const std::vector<
   {
     LaunchArgs args;
     for (int i = 0; i < 3; ++i) args.add_memref(buf[i], shape);
-    for (float *ptr : {q_hi, q_lo, k_hi, k_lo, vt_hi, vt_lo})
+    for (char *ptr : {q_hi, q_lo, k_hi, k_lo, vt_hi, vt_lo, shifts})
       args.add_scalar<uint64_t>(reinterpret_cast<uint64_t>(ptr));
     if (auto r = ex.launch(*f_split, p.steps[0], args, stream); !r) return r;
   }
-  // Q, K: [bh*seq rows, 64]; V^T: [bh*64 rows, seq]. 32-column boxes = one swizzle row.
-  auto make_map = [&](const float *ptr, int64_t cols, int64_t rows, uint32_t box_rows) {
+  // Q, K: [bh*seq rows, 64 fp16]; V^T: [bh*64 rows, seq fp16]. 64-column boxes = one 128-byte swizzle row.
+  auto make_map = [&](const char *ptr, int64_t cols, int64_t rows, uint32_t box_rows) {
     TensorMapSpec t;
     t.global_address = ptr;
     t.rank = 2;
+    t.elem_bytes = 2;
     t.dims[0] = static_cast<uint64_t>(cols);
     t.dims[1] = static_cast<uint64_t>(rows);
-    t.strides_bytes[0] = static_cast<uint64_t>(cols) * 4;
-    t.box[0] = 32;
+    t.strides_bytes[0] = static_cast<uint64_t>(cols) * 2;
+    t.box[0] = 64;
     t.box[1] = box_rows;
     t.swizzle_bytes = 128;
     return ex.backend().encode_tensor_map(t);
   };
   LaunchArgs args;
   for (int i = 0; i < 4; ++i) args.add_memref(buf[i], shape);
-  struct M { const float *p; int64_t cols, rows; uint32_t box; };
+  struct M { const char *p; int64_t cols, rows; uint32_t box; };
   const M maps[6] = {{q_hi, kHeadDim, bh * s, static_cast<uint32_t>(kBQ)},
                      {q_lo, kHeadDim, bh * s, static_cast<uint32_t>(kBQ)},
                      {k_hi, kHeadDim, bh * s, static_cast<uint32_t>(kBKV)},
@@ -107,6 +111,7 @@ Result<void> run_attention(Executor &ex, const KernelPlan &p, const std::vector<
     if (!t) return std::unexpected(t.error());
     args.add_tensor_map(*t);
   }
+  args.add_scalar<uint64_t>(reinterpret_cast<uint64_t>(shifts));
   args.add_scalar<uint64_t>(reinterpret_cast<uint64_t>(ex.status_word()));
   return ex.launch(*f_main, p.steps[1], args, stream);
 }
