@@ -421,7 +421,7 @@ attention(KH_MEMREF4(const float, q), KH_MEMREF4(const float, k), KH_MEMREF4(con
     const int row_q = q0 + row_in_tile;
     const int shift_q = __ldg(shifts + bh * num_kv + (row_q < seq ? row_q >> 6 : 0));
     constexpr float kLog2eOverSqrtD = 1.4426950408889634f * 0.125f;
-    float v_factor_prev = 0.f; // 2^-(14 + exponent of the V tile) of this group's previous product
+    float v_factor_prev = 0.f; // 2^-(exponent of the V tile) of this group's previous product
 
     for (int j = g; j < num_kv && ok; j += 2) {
       const uint32_t phase = static_cast<uint32_t>((j >> 1) & 1);
@@ -440,10 +440,13 @@ attention(KH_MEMREF4(const float, q), KH_MEMREF4(const float, k), KH_MEMREF4(con
       for (int i = 0; i < kBKV; ++i) mx = fmaxf(mx, __uint_as_float(sv[i]));
       const float m_new = fmaxf(m, mx * f);
       const float alpha = fast_exp2(m - m_new); // m = -inf on the first tile gives 0
+      // P is produced as P * 2^14 straight from the exponent (its split wants that
+      // range); the row sum `l` and the output row are kept in the same units.
+      const float offset = static_cast<float>(kPShift) - m_new;
       float sum = 0.f;
 #pragma unroll
       for (int i = 0; i < kBKV; ++i) {
-        const float p = fast_exp2(fmaf(__uint_as_float(sv[i]), f, -m_new));
+        const float p = fast_exp2(fmaf(__uint_as_float(sv[i]), f, offset));
         sv[i] = __float_as_uint(p);
         sum += p;
       }
@@ -468,15 +471,15 @@ attention(KH_MEMREF4(const float, q), KH_MEMREF4(const float, k), KH_MEMREF4(con
             acc[16 * h + i] = fmaf(__uint_as_float(t[i]), v_factor_prev, acc[16 * h + i]) * alpha;
         }
       }
-      v_factor_prev = khd::scale_pow2(1.0f, -(kPShift + __ldg(v_shifts + j))); // P was split as P * 2^14
-      // P * 2^14 -> tensor memory as fp16 hi / lo, two keys per 32-bit column
+      v_factor_prev = khd::scale_pow2(1.0f, -__ldg(v_shifts + j)); // V was split as V * 2^shift
+      // P (times 2^14) -> tensor memory as fp16 hi / lo, two keys per 32-bit column
 #pragma unroll
       for (int h = 0; h < 2; ++h) {
         uint32_t hi[16], lo[16];
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
-          const float p0 = __uint_as_float(sv[32 * h + 2 * i]) * 16384.f;
-          const float p1 = __uint_as_float(sv[32 * h + 2 * i + 1]) * 16384.f;
+          const float p0 = __uint_as_float(sv[32 * h + 2 * i]);
+          const float p1 = __uint_as_float(sv[32 * h + 2 * i + 1]);
           const __half2 h2 = __floats2half2_rn(p0, p1);
           const float2 back = __half22float2(h2);
           hi[i] = half2_bits(h2);
