@@ -422,9 +422,16 @@ attention(KH_MEMREF4(const float, q), KH_MEMREF4(const float, k), KH_MEMREF4(con
     const int shift_q = __ldg(shifts + bh * num_kv + (row_q < seq ? row_q >> 6 : 0));
     constexpr float kLog2eOverSqrtD = 1.4426950408889634f * 0.125f;
     float v_factor_prev = 0.f; // 2^-(exponent of the V tile) of this group's previous product
+    // the exponents of this group's next tile are fetched one tile ahead
+    int shift_k_next = g < num_kv ? __ldg(k_shifts + g) : 0, shift_v_next = g < num_kv ? __ldg(v_shifts + g) : 0;
 
     for (int j = g; j < num_kv && ok; j += 2) {
       const uint32_t phase = static_cast<uint32_t>((j >> 1) & 1);
+      const int shift_k = shift_k_next, shift_v = shift_v_next;
+      if (j + 2 < num_kv) {
+        shift_k_next = __ldg(k_shifts + j + 2);
+        shift_v_next = __ldg(v_shifts + j + 2);
+      }
       ok = khd::mbar_wait(bar_s_full + 8 * g, phase, &s_abort, status, khd::kStatusMmaWaitTimeout,
                           static_cast<uint32_t>(j));
       if (!ok) break;
@@ -434,7 +441,7 @@ attention(KH_MEMREF4(const float, q), KH_MEMREF4(const float, k), KH_MEMREF4(con
       khd::tmem_ld_32x32(tmem_base + lane_base + col_s + 32, *reinterpret_cast<uint32_t(*)[32]>(&sv[32]));
       khd::tmem_ld_wait();
       // this tile's scores carry 2^(shift_q + shift_k): one positive factor brings them to exp2 units
-      const float f = khd::scale_pow2(kLog2eOverSqrtD, -(shift_q + __ldg(k_shifts + j)));
+      const float f = khd::scale_pow2(kLog2eOverSqrtD, -(shift_q + shift_k));
       float mx = -INFINITY;
 #pragma unroll
       for (int i = 0; i < kBKV; ++i) mx = fmaxf(mx, __uint_as_float(sv[i]));
@@ -471,19 +478,20 @@ attention(KH_MEMREF4(const float, q), KH_MEMREF4(const float, k), KH_MEMREF4(con
             acc[16 * h + i] = fmaf(__uint_as_float(t[i]), v_factor_prev, acc[16 * h + i]) * alpha;
         }
       }
-      v_factor_prev = khd::scale_pow2(1.0f, -__ldg(v_shifts + j)); // V was split as V * 2^shift
+      v_factor_prev = khd::scale_pow2(1.0f, -shift_v); // V was split as V * 2^shift
       // P (times 2^14) -> tensor memory as fp16 hi / lo, two keys per 32-bit column
 #pragma unroll
       for (int h = 0; h < 2; ++h) {
         uint32_t hi[16], lo[16];
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
+          // hi = the top 11 significant bits (exact in fp16), lo = fp16 of the rest
           const float p0 = __uint_as_float(sv[32 * h + 2 * i]);
           const float p1 = __uint_as_float(sv[32 * h + 2 * i + 1]);
-          const __half2 h2 = __floats2half2_rn(p0, p1);
-          const float2 back = __half22float2(h2);
-          hi[i] = half2_bits(h2);
-          lo[i] = half2_bits(__floats2half2_rn(p0 - back.x, p1 - back.y));
+          const float h0 = __uint_as_float(sv[32 * h + 2 * i] & 0xFFFFE000u);
+          const float h1 = __uint_as_float(sv[32 * h + 2 * i + 1] & 0xFFFFE000u);
+          hi[i] = half2_bits(__floats2half2_rn(h0, h1));
+          lo[i] = half2_bits(__floats2half2_rn(p0 - h0, p1 - h1));
         }
         tmem_st_32x16(tmem_base + lane_base + col_p + 16 * h, hi);
         tmem_st_32x16(tmem_base + lane_base + col_p + 32 + 16 * h, lo);
