@@ -268,6 +268,11 @@ def memory_bound_rows(torch, ctx, stream, hbm_peak: float) -> dict:
     row("softmax_large", "softmax", f"rows={r},cols={c}", lambda: [f(r, c), f(r, c)], 2 * r * c * 4, 1, 20)
     row("layernorm_large", "layernorm", f"rows={r},cols={c}", lambda: [f(r, c), g, b, f(r, c)],
         2 * r * c * 4, 1, 20)
+    r, c = 16384, 4096  # the second row-kernel configuration of the reference's suite: a block per row
+    g4, b4 = f(c), f(c)
+    row("softmax_16384x4096", "softmax", f"rows={r},cols={c}", lambda: [f(r, c), f(r, c)], 2 * r * c * 4, 1, 20)
+    row("layernorm_16384x4096", "layernorm", f"rows={r},cols={c}", lambda: [f(r, c), g4, b4, f(r, c)],
+        2 * r * c * 4, 1, 20)
     n = 1 << 26
     row("scan_large", "scan", f"n={n}", lambda: [torch.rand(n, device="cuda"), f(n)], 2 * n * 4, 1, 20)
     return out

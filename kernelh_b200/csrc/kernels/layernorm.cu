@@ -75,6 +75,58 @@ __device__ __forceinline__ void layernorm_row_regs(const float *__restrict__ xro
   }
 }
 
+// Block-per-row rows of at most kVec float4 per thread, with the next row's
+// loads issued before the current row is reduced, so a block always has a row
+// in flight (the two reductions need four block barriers per row).
+template <int kVec>
+__device__ __forceinline__ void layernorm_rows_block_prefetch(const float *__restrict__ x,
+                                                              const float *__restrict__ gamma,
+                                                              const float *__restrict__ beta, float *__restrict__ y,
+                                                              int64_t rows, int64_t x_stride0, int64_t y_stride0,
+                                                              int nvec, int cols, float *smem) {
+  const int tid = threadIdx.x, tpr = blockDim.x;
+  const float4 *g4 = reinterpret_cast<const float4 *>(gamma);
+  const float4 *b4 = reinterpret_cast<const float4 *>(beta);
+  float4 nxt[kVec];
+  const auto load_row = [&](int64_t r) {
+    const float4 *x4 = reinterpret_cast<const float4 *>(x + r * x_stride0);
+#pragma unroll
+    for (int i = 0; i < kVec; ++i)
+      if (tid + i * tpr < nvec) nxt[i] = __ldcs(x4 + tid + i * tpr);
+  };
+  if (blockIdx.x < rows) load_row(blockIdx.x);
+  for (int64_t r = blockIdx.x; r < rows; r += gridDim.x) {
+    float4 v[kVec];
+#pragma unroll
+    for (int i = 0; i < kVec; ++i) v[i] = nxt[i];
+    if (r + gridDim.x < rows) load_row(r + gridDim.x);
+    float s = 0.f;
+#pragma unroll
+    for (int i = 0; i < kVec; ++i)
+      if (tid + i * tpr < nvec) s += (v[i].x + v[i].y) + (v[i].z + v[i].w);
+    const float mean = row_sum<true>(s, smem) / static_cast<float>(cols);
+    float q = 0.f;
+#pragma unroll
+    for (int i = 0; i < kVec; ++i)
+      if (tid + i * tpr < nvec) {
+        v[i].x -= mean; v[i].y -= mean; v[i].z -= mean; v[i].w -= mean;
+        q += (v[i].x * v[i].x + v[i].y * v[i].y) + (v[i].z * v[i].z + v[i].w * v[i].w);
+      }
+    const float var = row_sum<true>(q, smem) / static_cast<float>(cols);
+    const float rstd = 1.0f / sqrtf(var + kEps);
+    float4 *y4 = reinterpret_cast<float4 *>(y + r * y_stride0);
+#pragma unroll
+    for (int i = 0; i < kVec; ++i) {
+      const int idx = tid + i * tpr;
+      if (idx < nvec) {
+        const float4 g = __ldg(g4 + idx), b = __ldg(b4 + idx);
+        __stcs(y4 + idx, make_float4(fmaf(v[i].x * rstd, g.x, b.x), fmaf(v[i].y * rstd, g.y, b.y),
+                                     fmaf(v[i].z * rstd, g.z, b.z), fmaf(v[i].w * rstd, g.w, b.w)));
+      }
+    }
+  }
+}
+
 } // namespace
 
 extern "C" __global__ void __launch_bounds__(256)
@@ -99,6 +151,11 @@ layernorm(KH_MEMREF2(const float, x), KH_MEMREF1(const float, gamma), KH_MEMREF1
       layernorm_row_regs<false>(x + r * x_stride0, gamma, beta, y + r * y_stride0,
                                 static_cast<int>(cols >> 2), static_cast<int>(cols),
                                 threadIdx.x & 31, 32, smem);
+    return;
+  }
+  if (fast && cols <= static_cast<int64_t>(blockDim.x) * 4 * 4) {
+    layernorm_rows_block_prefetch<4>(x, gamma, beta, y, rows, x_stride0, y_stride0, static_cast<int>(cols >> 2),
+                                     static_cast<int>(cols), smem);
     return;
   }
   if (fast && cols <= static_cast<int64_t>(blockDim.x) * 4 * kMaxVec) {

@@ -86,6 +86,56 @@ __device__ __forceinline__ void softmax_row_regs(const float *__restrict__ xrow,
   }
 }
 
+// Block-per-row rows of at most kVec float4 per thread, with the next row's
+// loads issued before the current row is reduced, so a block always has a row
+// in flight (the reduce needs two block barriers per row).
+template <int kVec>
+__device__ __forceinline__ void softmax_rows_block_prefetch(const float *__restrict__ x, float *__restrict__ y,
+                                                            int64_t rows, int64_t x_stride0, int64_t y_stride0,
+                                                            int nvec, MaxSum *smem) {
+  const int tid = threadIdx.x, tpr = blockDim.x, warp = tid >> 5, nwarps = tpr >> 5;
+  float4 nxt[kVec];
+  const auto load_row = [&](int64_t r) {
+    const float4 *x4 = reinterpret_cast<const float4 *>(x + r * x_stride0);
+#pragma unroll
+    for (int i = 0; i < kVec; ++i)
+      if (tid + i * tpr < nvec) nxt[i] = __ldcs(x4 + tid + i * tpr);
+  };
+  if (blockIdx.x < rows) load_row(blockIdx.x);
+  for (int64_t r = blockIdx.x; r < rows; r += gridDim.x) {
+    float4 v[kVec];
+#pragma unroll
+    for (int i = 0; i < kVec; ++i) v[i] = nxt[i];
+    if (r + gridDim.x < rows) load_row(r + gridDim.x);
+    float m = -INFINITY;
+#pragma unroll
+    for (int i = 0; i < kVec; ++i)
+      if (tid + i * tpr < nvec) m = fmaxf(m, fmaxf(fmaxf(v[i].x, v[i].y), fmaxf(v[i].z, v[i].w)));
+    float s = 0.f;
+#pragma unroll
+    for (int i = 0; i < kVec; ++i)
+      if (tid + i * tpr < nvec) {
+        v[i].x = expf(v[i].x - m);
+        v[i].y = expf(v[i].y - m);
+        v[i].z = expf(v[i].z - m);
+        v[i].w = expf(v[i].w - m);
+        s += (v[i].x + v[i].y) + (v[i].z + v[i].w);
+      }
+    MaxSum t = warp_merge({m, s});
+    __syncthreads(); // smem reuse across rows
+    if ((tid & 31) == 0) smem[warp] = t;
+    __syncthreads();
+    MaxSum acc = smem[0];
+    for (int w = 1; w < nwarps; ++w) acc = merge(acc, smem[w]);
+    const float scale = (m == -INFINITY) ? 0.f : expf(m - acc.m) / acc.s;
+    float4 *y4 = reinterpret_cast<float4 *>(y + r * y_stride0);
+#pragma unroll
+    for (int i = 0; i < kVec; ++i)
+      if (tid + i * tpr < nvec)
+        __stcs(y4 + tid + i * tpr, make_float4(v[i].x * scale, v[i].y * scale, v[i].z * scale, v[i].w * scale));
+  }
+}
+
 } // namespace
 
 extern "C" __global__ void __launch_bounds__(256)
@@ -106,6 +156,11 @@ softmax(KH_MEMREF2(const float, x), KH_MEMREF2(float, y)) {
     for (int64_t r = warp0; r < rows; r += nwarps)
       softmax_row_regs<false>(x + r * x_stride0, y + r * y_stride0, static_cast<int>(cols >> 2),
                               threadIdx.x & 31, 32, smem);
+    return;
+  }
+  if (fast && cols <= static_cast<int64_t>(blockDim.x) * 4 * 4) {
+    // the block per row, next row prefetched
+    softmax_rows_block_prefetch<4>(x, y, rows, x_stride0, y_stride0, static_cast<int>(cols >> 2), smem);
     return;
   }
   if (fast && cols <= static_cast<int64_t>(blockDim.x) * 4 * kMaxVec) {
