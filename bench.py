@@ -481,6 +481,32 @@ def gpu_arm(args) -> None:
         line["e2e"]["matches_device_path"] = bool(e2e_ok)
         del a_h, b_h, c_h
 
+    if world > 1:
+        # Batched attention sharded by (batch, head): every rank runs its share of the 8 x 16
+        # independent problems, no exchange (each slice's output stays with its rank).
+        bsz, heads, seq, dim = 8, 16, 1024, 64
+        shard = sharding.attention_shard_shape(bsz, heads, seq, dim, world, rank)
+        lo, hi = shard["units"]
+        if hi > lo:
+            qkv = [torch.randn(hi - lo, 1, seq, dim, device="cuda") for _ in range(4)]
+            for _ in range(3):
+                ctx.launch("attention", shard["shape"], qkv, stream)
+        barrier()
+        torch.cuda.synchronize()
+        a0, a1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a0.record()
+        for _ in range(10):
+            if hi > lo:
+                ctx.launch("attention", shard["shape"], qkv, stream)
+        a1.record()
+        torch.cuda.synchronize()
+        att = torch.tensor([a0.elapsed_time(a1) / 10], device="cuda")
+        dist.all_reduce(att, op=dist.ReduceOp.MAX)
+        line["attention_sharded"] = {"shape": f"batch={bsz},heads={heads},seq={seq},head_dim={dim}",
+                                     "sharding": f"(batch, head) slices over {world} ranks, no exchange",
+                                     "ms": att.item(),
+                                     "tflops": 4.0 * bsz * heads * seq * seq * dim / att.item() / 1e9}
+
     if rank == 0 and world == 1 and not args.no_extras:
         del a, b, c
         torch.cuda.empty_cache()
