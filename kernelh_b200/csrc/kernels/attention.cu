@@ -77,20 +77,6 @@ __device__ __forceinline__ float fast_exp2(float x) {
   return y;
 }
 
-// Instruction descriptor for kind::f16 with fp16 operands, fp32 accumulate, both
-// K-major: [4,6) D format 1 = f32; [7,10) / [10,13) A / B format 0 = f16;
-// [17,23) N >> 3; [24,29) M >> 4.
-__host__ __device__ constexpr uint32_t umma_idesc_f16(int m, int n) {
-  return (1u << 4) | (static_cast<uint32_t>(n >> 3) << 17) | (static_cast<uint32_t>(m >> 4) << 24);
-}
-// D[tmem] (+)= A[smem] * B[smem]
-__device__ __forceinline__ void umma_f16_ss(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
-                                            uint32_t accumulate) {
-  asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-               "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_d),
-               "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
-               : "memory");
-}
 // D[tmem] (+)= A[tmem] * B[smem]; A holds two fp16 per 32-bit column (k even in the low half)
 __device__ __forceinline__ void umma_f16_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t desc_b, uint32_t idesc,
                                             uint32_t accumulate) {
@@ -332,7 +318,7 @@ attention(KH_MEMREF4(const float, q), KH_MEMREF4(const float, k), KH_MEMREF4(con
     //      themselves sit under the elected lane. ---------------------------------------
     {
       const bool leader = khd::elect_one();
-      constexpr uint32_t idesc = umma_idesc_f16(kBQ, kBKV); // M128 N64 K16 for both products
+      constexpr uint32_t idesc = khd::umma_idesc_f16(kBQ, kBKV); // M128 N64 K16 for both products
       // a tile row is one 128-byte swizzle row (64 fp16); a k-step of 16 fp16 moves 32 bytes (2 encoded)
       const uint64_t dq_hi = khd::umma_desc_k128(smem_q), dq_lo = khd::umma_desc_k128(smem_q + kQTileBytes);
       constexpr uint64_t kKVTileStep = kKVTileBytes >> 4;
@@ -344,9 +330,9 @@ attention(KH_MEMREF4(const float, q), KH_MEMREF4(const float, k), KH_MEMREF4(con
 #pragma unroll
           for (int kk = 0; kk < kHeadDim / 16; ++kk) {
             const uint64_t off = static_cast<uint64_t>(kk * 2);
-            umma_f16_ss(d, dq_lo + off, dk_hi + off, idesc, kk != 0 ? 1u : 0u);
-            umma_f16_ss(d, dq_hi + off, dk_lo + off, idesc, 1u);
-            umma_f16_ss(d, dq_hi + off, dk_hi + off, idesc, 1u);
+            khd::umma_f16_ss(d, dq_lo + off, dk_hi + off, idesc, kk != 0 ? 1u : 0u);
+            khd::umma_f16_ss(d, dq_hi + off, dk_lo + off, idesc, 1u);
+            khd::umma_f16_ss(d, dq_hi + off, dk_hi + off, idesc, 1u);
           }
           khd::umma_commit(bar_s_full + 8 * b);  // scores ready for the softmax threads
           khd::umma_commit(bar_k_empty + 8 * b); // and this K slot may be refilled

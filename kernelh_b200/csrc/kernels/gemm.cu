@@ -472,12 +472,6 @@ __device__ __forceinline__ void tmem_relinquish_pair() {
 __device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t columns) {
   asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(columns) : "memory");
 }
-// Instruction descriptor for kind::f16 with fp16 operands, fp32 accumulate, both
-// K-major: [4,6) D format 1 = f32; [7,10) / [10,13) A / B format 0 = f16;
-// [17,23) N >> 3; [24,29) M >> 4 (M counts the rows of the whole pair).
-__host__ __device__ constexpr uint32_t umma_idesc_f16(int m, int n) {
-  return (1u << 4) | (static_cast<uint32_t>(n >> 3) << 17) | (static_cast<uint32_t>(m >> 4) << 24);
-}
 // D[tmem of both CTAs] (+)= A[smem of each CTA] * B[halves in both CTAs' smem]; one thread of the leader issues.
 __device__ __forceinline__ void umma_f16_pair(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b,
                                               uint32_t idesc, uint32_t accumulate) {
@@ -614,7 +608,7 @@ __device__ __forceinline__ void gemm_body(int64_t m, int64_t n, float *__restric
     // ---- MMA issuer: the leader CTA only. One instruction drives both tensor cores. ----
     if (leader_cta) {
       const bool elected = khd::elect_one();
-      constexpr uint32_t idesc = umma_idesc_f16(2 * kBM, kBN);
+      constexpr uint32_t idesc = khd::umma_idesc_f16(2 * kBM, kBN);
       uint32_t g_kb = 0, g_chunk = 0;
       bool ok = true;
       for (int64_t tile = first_tile; tile < num_tiles && ok; tile += tile_step) {

@@ -81,7 +81,7 @@ __device__ __forceinline__ void tma_prefetch_descriptor(const TensorMap *map) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(map)) : "memory");
 }
 // 2-D tile load global -> this CTA's shared memory; x is the innermost
-// coordinate (elements) and must be a multiple of 4 for fp32 (16 bytes).
+// coordinate (elements) and must be a multiple of 8 for fp16 (16 bytes).
 __device__ __forceinline__ void tma_load_2d(uint32_t smem_dst, const TensorMap *map, int x, int y,
                                             uint32_t bar) {
   asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes "
@@ -89,18 +89,6 @@ __device__ __forceinline__ void tma_load_2d(uint32_t smem_dst, const TensorMap *
                "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(bar)
                : "memory");
 }
-__device__ __forceinline__ void tma_load_3d(uint32_t smem_dst, const TensorMap *map, int x, int y,
-                                            int z, uint32_t bar) {
-  asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes "
-               "[%0], [%1, {%2, %3, %4}], [%5];" ::"r"(smem_dst),
-               "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(z), "r"(bar)
-               : "memory");
-}
-// Generic-proxy writes to shared memory -> visible to the async proxy (TMA / MMA).
-__device__ __forceinline__ void fence_proxy_async_smem() {
-  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-}
-
 // ---- tensor memory ------------------------------------------------------------
 // Whole-warp calls. `columns` is a power of two >= 32.
 __device__ __forceinline__ void tmem_alloc(uint32_t smem_result, uint32_t columns) {
@@ -124,11 +112,11 @@ __device__ __forceinline__ void tc_fence_after_sync() {
 
 // ---- UMMA descriptors ---------------------------------------------------------
 // Shared-memory operand descriptor for a K-major tile whose rows are 128 bytes
-// (32 fp32) in the 128-byte swizzle TMA writes: 8-row groups are 1024 bytes
+// (64 fp16) in the 128-byte swizzle TMA writes: 8-row groups are 1024 bytes
 // apart (stride byte offset), the leading offset is unused for this layout.
 // Bits: [0,14) address >> 4; [16,30) leading offset >> 4; [32,46) stride
 // offset >> 4; [46,48) version = 1 on sm_100; [61,64) layout 2 = 128B swizzle.
-// The tile base must be 1024-byte aligned; stepping K by 8 fp32 inside the
+// The tile base must be 1024-byte aligned; stepping K by 16 fp16 inside the
 // swizzle row adds 32 bytes (2 in encoded units) to the address field.
 __device__ __forceinline__ uint64_t umma_desc_k128(uint32_t smem_addr) {
   uint64_t d = 0;
@@ -140,8 +128,8 @@ __device__ __forceinline__ uint64_t umma_desc_k128(uint32_t smem_addr) {
   return d;
 }
 
-// Same for rows of 64 bytes (16 fp32) in the 64-byte swizzle: 8-row groups are
-// 512 bytes apart, layout 4 = 64B swizzle; stepping K by 8 fp32 adds 32 bytes.
+// Same for rows of 64 bytes (32 fp16) in the 64-byte swizzle: 8-row groups are
+// 512 bytes apart, layout 4 = 64B swizzle; stepping K by 16 fp16 adds 32 bytes.
 __device__ __forceinline__ uint64_t umma_desc_k64(uint32_t smem_addr) {
   uint64_t d = 0;
   d |= static_cast<uint64_t>((smem_addr & 0x3FFFFu) >> 4);
@@ -152,19 +140,19 @@ __device__ __forceinline__ uint64_t umma_desc_k64(uint32_t smem_addr) {
   return d;
 }
 
-// Instruction descriptor for kind::tf32, fp32 accumulate, both operands
-// K-major: [4,6) D format 1 = f32; [7,10) A format 2 = tf32; [10,13) B format
-// 2 = tf32; bit 15 / 16 A / B major (0 = K); [17,23) N >> 3; [24,29) M >> 4.
-__host__ __device__ constexpr uint32_t umma_idesc_tf32(int m, int n) {
-  return (1u << 4) | (2u << 7) | (2u << 10) | (static_cast<uint32_t>(n >> 3) << 17) |
-         (static_cast<uint32_t>(m >> 4) << 24);
+// Instruction descriptor for kind::f16 with fp16 operands, fp32 accumulate, both
+// operands K-major: [4,6) D format 1 = f32; [7,10) / [10,13) A / B format 0 =
+// f16; bit 15 / 16 A / B major (0 = K); [17,23) N >> 3; [24,29) M >> 4 (for
+// cta_group::2, M counts the rows of the whole CTA pair).
+__host__ __device__ constexpr uint32_t umma_idesc_f16(int m, int n) {
+  return (1u << 4) | (static_cast<uint32_t>(n >> 3) << 17) | (static_cast<uint32_t>(m >> 4) << 24);
 }
 
-// D[tmem] (+)= A[smem] * B[smem]; one thread issues.
-__device__ __forceinline__ void umma_tf32_ss(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b,
-                                             uint32_t idesc, uint32_t accumulate) {
+// D[tmem] (+)= A[smem] * B[smem], K = 16 fp16 per instruction; one thread issues.
+__device__ __forceinline__ void umma_f16_ss(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b,
+                                            uint32_t idesc, uint32_t accumulate) {
   asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-               "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_d),
+               "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_d),
                "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
                : "memory");
 }
