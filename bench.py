@@ -489,14 +489,38 @@ def gpu_arm(args) -> None:
         shard = sharding.attention_shard_shape(bsz, heads, seq, dim, world, rank)
         lo, hi = shard["units"]
         even = (bsz * heads) % world == 0
-        o_full = torch.empty(bsz * heads, 1, seq, dim, device="cuda")
-        qkv = [torch.randn(max(hi - lo, 1), 1, seq, dim, device="cuda") for _ in range(3)]
-        o_shard = o_full[lo:hi] if even else torch.empty(max(hi - lo, 1), 1, seq, dim, device="cuda")
+        qkv = [torch.randn(max(hi - lo, 1), seq, dim, device="cuda") for _ in range(3)]
+        o_symm = None
+        att_mode = "none"
+        if even and gather == "p2p":
+            # the whole output lives in symmetric memory on every rank; the kernel sends its tiles there
+            try:
+                o_full = symm_mem.empty((bsz * heads, seq, dim), dtype=torch.float32,
+                                        device=torch.device("cuda", local_rank))
+                o_symm = symm_mem.rendezvous(o_full, dist.group.WORLD.group_name)
+                o_reps = [int(p) for p in o_symm.buffer_ptrs]
+                o_mc = int(getattr(o_symm, "multicast_ptr", 0) or 0) if args.gather == "p2p" else 0
+                att_mode = "fused"
+            except Exception as exc:
+                if rank == 0:
+                    sys.stderr.write(f"bench.py: symmetric memory for the attention output unavailable ({exc!r})\n")
+                o_symm = None
+        if o_symm is None:
+            o_full = torch.empty(bsz * heads, seq, dim, device="cuda")
+            att_mode = "nccl" if even else "none"
+        o_shard = o_full[lo:hi] if even else torch.empty(max(hi - lo, 1), seq, dim, device="cuda")
+        shard_shape = f"batch={hi - lo},heads=1,seq={seq},head_dim={dim}"
 
         def attention_step():
+            if att_mode == "fused":
+                ctx.attention_allgather(qkv[0], qkv[1], qkv[2], o_reps if not o_mc else
+                                        [o_full if i == rank else None for i in range(world)],
+                                        o_mc, rank, hi - lo, seq, dim, stream)
+                o_symm.barrier()
+                return
             if hi > lo:
-                ctx.launch("attention", shard["shape"], qkv + [o_shard], stream)
-            if even:
+                ctx.launch("attention", shard_shape, qkv + [o_shard], stream)
+            if att_mode == "nccl":
                 sharding.gather_output(o_full, o_shard, dist)
 
         for _ in range(3):
@@ -512,9 +536,12 @@ def gpu_arm(args) -> None:
         att = torch.tensor([a0.elapsed_time(a1) / 10], device="cuda")
         dist.all_reduce(att, op=dist.ReduceOp.MAX)
         line["attention_sharded"] = {"shape": f"batch={bsz},heads={heads},seq={seq},head_dim={dim}",
-                                     "sharding": f"(batch, head) slices over {world} ranks" + (
-                                         "; output slices all-gathered (NCCL) inside the timed step" if even
-                                         else "; uneven split, no gather"),
+                                     "sharding": f"(batch, head) slices over {world} ranks" + {
+                                         "fused": "; all-gather of the output fused into the kernel (" + (
+                                             "multimem.st" if att_mode == "fused" and o_mc else "peer stores") +
+                                             " over NVLink) + barrier, inside the timed step",
+                                         "nccl": "; output slices all-gathered (NCCL) inside the timed step",
+                                         "none": "; uneven split, no gather"}[att_mode],
                                      "ms": att.item(),
                                      "tflops": 4.0 * bsz * heads * seq * seq * dim / att.item() / 1e9}
 

@@ -149,6 +149,19 @@ int kh_gemm_allgather_multicast(kh_context *ctx, const float *a_shard, const flo
                                 void *c_multicast, int world, int rank, int64_t m_shard, int64_t n,
                                 int64_t k, void *stream);
 
+/* No counterpart in the reference. Attention over (batch, head) slices sharded
+ * across the GPUs of one box with the all-gather of the output fused into the
+ * kernel: q, k, v are this rank's `slices` x seq x head_dim problems; every
+ * rank keeps the whole (world*slices) x seq x head_dim output, `o_replicas[i]`
+ * being rank i's copy as mapped on this device. Every finished 128-row tile is
+ * stored to this rank's copy at slice rank*slices and sent to the others:
+ * with multimem.st through `o_multicast` (the copies' NVLink multicast
+ * address; then only o_replicas[rank] is read) or, when it is null, with plain
+ * peer stores. Same barrier rule as kh_gemm_allgather. */
+int kh_attention_allgather(kh_context *ctx, const float *q, const float *k, const float *v,
+                           void *const *o_replicas, void *o_multicast, int world, int rank, int64_t slices,
+                           int64_t seq, int64_t head_dim, void *stream);
+
 /* No counterpart in the reference. The scan for callers that must not allocate
  * device memory (memory-pool owners, allocator-free plugin callbacks, fixed
  * audited budgets): same result as kh_scan, but the look-back scratch is a

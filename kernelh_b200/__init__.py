@@ -83,6 +83,7 @@ def _load() -> C.CDLL:
     L.kh_gemm_allgather.argtypes = [vp, f32p, f32p, C.POINTER(vp), C.c_int, C.c_int, i64, i64, i64, vp]
     L.kh_gemm_allgather_multicast.argtypes = [vp, f32p, f32p, f32p, vp, C.c_int, C.c_int, i64, i64, i64, vp]
     L.kh_attention.argtypes = [vp, f32p, f32p, f32p, f32p, i64, i64, i64, i64, vp]
+    L.kh_attention_allgather.argtypes = [vp, f32p, f32p, f32p, C.POINTER(vp), vp, C.c_int, C.c_int, i64, i64, i64, vp]
     L.kh_malloc.argtypes = [vp, C.c_size_t, C.POINTER(vp)]
     L.kh_free.argtypes = [vp, vp]
     L.kh_memcpy_h2d.argtypes = [vp, vp, vp, C.c_size_t]
@@ -251,6 +252,15 @@ class Context:
     def attention(self, q, k, v, o, batch, heads, seq, head_dim, stream=None):
         _check(lib.kh_attention(self._h, _ptr(q), _ptr(k), _ptr(v), _ptr(o), batch, heads, seq,
                                 head_dim, stream))
+
+    def attention_allgather(self, q, k, v, o_replicas, o_multicast, rank, slices, seq, head_dim=64, stream=None):
+        """Attention over this rank's `slices` (batch, head) problems whose output tiles also go to
+        every other rank's copy of the whole output (`o_replicas`: addresses mapped on this device;
+        `o_multicast`: the copies' NVLink multicast address, or 0 for plain peer stores)."""
+        arr = (C.c_void_p * len(o_replicas))(*[(None if p is None else _ptr(p)) for p in o_replicas])
+        _check(lib.kh_attention_allgather(self._h, _ptr(q), _ptr(k), _ptr(v), arr,
+                                          C.c_void_p(int(o_multicast)) if o_multicast else None,
+                                          len(o_replicas), rank, slices, seq, head_dim, stream))
 
     # ---- raw device memory -------------------------------------------------------
     def malloc(self, nbytes: int) -> int:

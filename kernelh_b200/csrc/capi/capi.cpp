@@ -260,6 +260,20 @@ int kh_attention(kh_context *ctx, const float *q, const float *k, const float *v
                       stream);
 }
 
+int kh_attention_allgather(kh_context *ctx, const float *q, const float *k, const float *v,
+                           void *const *o_replicas, void *o_multicast, int world, int rank, int64_t slices,
+                           int64_t seq, int64_t head_dim, void *stream) {
+  if (int rc = need_ctx(ctx)) return rc;
+  if (o_replicas == nullptr || world <= 0) return set_error(2, "kh_attention_allgather: no output replicas given");
+  if (head_dim != 64) return set_error(2, "kh_attention_allgather: the kernel is pinned to head_dim = 64");
+  return guarded([&] {
+    if (auto r = ctx->exec->backend().make_current(); !r) return set_error(r.error());
+    std::vector<void *> reps(o_replicas, o_replicas + world);
+    auto r = kh::run_attention_allgather(*ctx->exec, q, k, v, reps, o_multicast, rank, world, slices, seq, stream);
+    return r ? 0 : set_error(r.error());
+  });
+}
+
 int kh_malloc(kh_context *ctx, size_t bytes, void **out) {
   if (int rc = need_ctx(ctx)) return rc;
   if (out == nullptr) return set_error(2, "kh_malloc: null out pointer");

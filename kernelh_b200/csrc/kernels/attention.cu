@@ -204,32 +204,46 @@ attention_split(KH_MEMREF4(const float, q), KH_MEMREF4(const float, k), KH_MEMRE
   }
 }
 
-extern "C" __global__ void __launch_bounds__(kThreads, 1)
-attention(KH_MEMREF4(const float, q), KH_MEMREF4(const float, k), KH_MEMREF4(const float, v),
-          KH_MEMREF4(float, o), const __grid_constant__ khd::TensorMap tm_q_hi,
-          const __grid_constant__ khd::TensorMap tm_q_lo, const __grid_constant__ khd::TensorMap tm_k_hi,
-          const __grid_constant__ khd::TensorMap tm_k_lo, const __grid_constant__ khd::TensorMap tm_vt_hi,
-          const __grid_constant__ khd::TensorMap tm_vt_lo, const int *__restrict__ shifts, uint32_t *status) {
-  (void)q_alloc; (void)q_ptr; (void)q_off; (void)q_size3; (void)q_stride0; (void)q_stride1;
-  (void)q_stride2; (void)q_stride3;
-  (void)k_alloc; (void)k_ptr; (void)k_off; (void)k_size0; (void)k_size1; (void)k_size2; (void)k_size3;
-  (void)k_stride0; (void)k_stride1; (void)k_stride2; (void)k_stride3;
-  (void)v_alloc; (void)v_ptr; (void)v_off; (void)v_size0; (void)v_size1; (void)v_size2; (void)v_size3;
-  (void)v_stride0; (void)v_stride1; (void)v_stride2; (void)v_stride3;
-  (void)o_size0; (void)o_size1; (void)o_size2; (void)o_size3; (void)o_stride0; (void)o_stride1;
-  (void)o_stride2; (void)o_stride3; (void)o_alloc;
+namespace {
+
+// Where a finished output tile also goes when the (batch, head) slices are
+// sharded over several GPUs and every GPU keeps the whole output: either the
+// NVLink multicast address of the replicas (one multimem.st reaches all of
+// them), or the other GPUs' replicas one by one (plain peer stores). All
+// pointers address this rank's first slice inside the respective replica.
+struct GatherOut {
+  float *peer[8];
+  int count;
+  int self;
+  float *multicast;
+};
+
+__device__ __forceinline__ void multicast_store_float4(float *p, float4 v) {
+  asm volatile("multimem.st.weak.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(p), "f"(v.x), "f"(v.y), "f"(v.z),
+               "f"(v.w)
+               : "memory");
+}
+
+// The kernel body. `seq`: keys (= queries) per slice; `out`: this launch's
+// [slices, seq, 64] output. kGather: after a CTA has stored its 128 x 64 output
+// tile (32 KiB, contiguous), the softmax threads read it back from L2 and send
+// it to the other replicas in 512-byte warp-wide pieces.
+template <bool kGather>
+__device__ __forceinline__ void attention_body(int64_t seq, float *__restrict__ out, const khd::TensorMap &tm_q_hi,
+                                               const khd::TensorMap &tm_q_lo, const khd::TensorMap &tm_k_hi,
+                                               const khd::TensorMap &tm_k_lo, const khd::TensorMap &tm_vt_hi,
+                                               const khd::TensorMap &tm_vt_lo, const int *__restrict__ shifts,
+                                               uint32_t *status, const GatherOut *targets) {
   extern __shared__ uint8_t smem_raw[];
   // q_full, k_full[2], k_empty[2], v_full[2], v_empty[2], s_full[2], p_ready[2], pv_full[2], exchange
   __shared__ __align__(8) uint64_t bars[16];
   __shared__ uint32_t s_tmem_base;
   __shared__ int s_abort;
 
-  const int64_t seq = q_size2;
   const int64_t q_tiles = (seq + kBQ - 1) / kBQ;
   const int64_t bh = blockIdx.x / q_tiles;
   const int q0 = static_cast<int>((blockIdx.x - bh * q_tiles) * kBQ);
   const int num_kv = static_cast<int>(seq / kBKV);
-  float *__restrict__ out = KH_DATA(o);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
   const uint32_t smem_q = (khd::smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -538,6 +552,29 @@ attention(KH_MEMREF4(const float, q), KH_MEMREF4(const float, k), KH_MEMREF4(con
                              (acc[4 * i + 3] * w0 + merge[2 + 4 * i + 3] * w1) * inv));
       }
     }
+    if (kGather) {
+      // the tile is complete in this GPU's replica: make the rows visible to the whole
+      // group of softmax threads, then copy it out
+      __threadfence_block();
+      khd::mbar_arrive(bar_exchange);
+      ok = ok && khd::mbar_wait(bar_exchange, 1u, &s_abort, status, khd::kStatusEpilogueWaitTimeout, 5001u);
+      const int64_t first_row = bh * seq + q0;
+      const int64_t rows_here = (seq - q0 < kBQ) ? (seq - q0) : kBQ;
+      const float4 *src = reinterpret_cast<const float4 *>(out + first_row * kHeadDim);
+      const int t = threadIdx.x - 64; // 0..255
+      if (ok) {
+        for (int64_t i = t; i < rows_here * (kHeadDim / 4); i += kSoftmaxThreads) {
+          const float4 v = __ldcg(src + i);
+          const int64_t off = first_row * kHeadDim + i * 4;
+          if (targets->multicast != nullptr) {
+            multicast_store_float4(targets->multicast + off, v);
+          } else {
+            for (int d = 0; d < targets->count; ++d)
+              if (d != targets->self) *reinterpret_cast<float4 *>(targets->peer[d] + off) = v;
+          }
+        }
+      }
+    }
     khd::tc_fence_before_sync();
   }
 
@@ -549,4 +586,48 @@ attention(KH_MEMREF4(const float, q), KH_MEMREF4(const float, k), KH_MEMREF4(con
     khd::tc_fence_after_sync();
     khd::tmem_dealloc(tmem_base, kTmemCols);
   }
+}
+
+} // namespace
+
+extern "C" __global__ void __launch_bounds__(kThreads, 1)
+attention(KH_MEMREF4(const float, q), KH_MEMREF4(const float, k), KH_MEMREF4(const float, v),
+          KH_MEMREF4(float, o), const __grid_constant__ khd::TensorMap tm_q_hi,
+          const __grid_constant__ khd::TensorMap tm_q_lo, const __grid_constant__ khd::TensorMap tm_k_hi,
+          const __grid_constant__ khd::TensorMap tm_k_lo, const __grid_constant__ khd::TensorMap tm_vt_hi,
+          const __grid_constant__ khd::TensorMap tm_vt_lo, const int *__restrict__ shifts, uint32_t *status) {
+  (void)q_alloc; (void)q_ptr; (void)q_off; (void)q_size0; (void)q_size1; (void)q_size3; (void)q_stride0;
+  (void)q_stride1; (void)q_stride2; (void)q_stride3;
+  (void)k_alloc; (void)k_ptr; (void)k_off; (void)k_size0; (void)k_size1; (void)k_size2; (void)k_size3;
+  (void)k_stride0; (void)k_stride1; (void)k_stride2; (void)k_stride3;
+  (void)v_alloc; (void)v_ptr; (void)v_off; (void)v_size0; (void)v_size1; (void)v_size2; (void)v_size3;
+  (void)v_stride0; (void)v_stride1; (void)v_stride2; (void)v_stride3;
+  (void)o_size0; (void)o_size1; (void)o_size2; (void)o_size3; (void)o_stride0; (void)o_stride1;
+  (void)o_stride2; (void)o_stride3; (void)o_alloc;
+  attention_body<false>(q_size2, KH_DATA(o), tm_q_hi, tm_q_lo, tm_k_hi, tm_k_lo, tm_vt_hi, tm_vt_lo, shifts, status,
+                        nullptr);
+}
+
+// The same for (batch, head) slices sharded over several GPUs, with the
+// all-gather of the output fused in: `o` is this rank's slices inside its own
+// replica of the whole output, and every finished tile is also sent to the
+// other replicas (see GatherOut). The caller's barrier across ranks after the
+// kernel makes the peers' stores visible.
+extern "C" __global__ void __launch_bounds__(kThreads, 1)
+attention_allgather(KH_MEMREF4(const float, q), KH_MEMREF4(const float, k), KH_MEMREF4(const float, v),
+                    KH_MEMREF4(float, o), const __grid_constant__ khd::TensorMap tm_q_hi,
+                    const __grid_constant__ khd::TensorMap tm_q_lo, const __grid_constant__ khd::TensorMap tm_k_hi,
+                    const __grid_constant__ khd::TensorMap tm_k_lo, const __grid_constant__ khd::TensorMap tm_vt_hi,
+                    const __grid_constant__ khd::TensorMap tm_vt_lo, const int *__restrict__ shifts,
+                    uint32_t *status, const __grid_constant__ GatherOut targets) {
+  (void)q_alloc; (void)q_ptr; (void)q_off; (void)q_size0; (void)q_size1; (void)q_size3; (void)q_stride0;
+  (void)q_stride1; (void)q_stride2; (void)q_stride3;
+  (void)k_alloc; (void)k_ptr; (void)k_off; (void)k_size0; (void)k_size1; (void)k_size2; (void)k_size3;
+  (void)k_stride0; (void)k_stride1; (void)k_stride2; (void)k_stride3;
+  (void)v_alloc; (void)v_ptr; (void)v_off; (void)v_size0; (void)v_size1; (void)v_size2; (void)v_size3;
+  (void)v_stride0; (void)v_stride1; (void)v_stride2; (void)v_stride3;
+  (void)o_size0; (void)o_size1; (void)o_size2; (void)o_size3; (void)o_stride0; (void)o_stride1;
+  (void)o_stride2; (void)o_stride3; (void)o_alloc;
+  attention_body<true>(q_size2, KH_DATA(o), tm_q_hi, tm_q_lo, tm_k_hi, tm_k_lo, tm_vt_hi, tm_vt_lo, shifts, status,
+                       &targets);
 }

@@ -59,8 +59,16 @@ KernelPlan plan_attention(const ShapeMap &shape, const DeviceLimits &l) {
   return p;
 }
 
-Result<void> run_attention(Executor &ex, const KernelPlan &p, const std::vector<void *> &buf,
-                           StreamHandle stream) {
+// Destinations of attention_allgather's fused all-gather; layout shared with the kernel.
+struct GatherOut {
+  float *peer[8];
+  int count;
+  int self;
+  float *multicast;
+};
+
+Result<void> launch_attention(Executor &ex, const KernelPlan &p, const std::vector<void *> &buf,
+                              StreamHandle stream, const GatherOut *gather) {
   const std::vector<int64_t> &shape = p.tensors[0].shape;
   const int64_t bh = shape[0] * shape[1], s = shape[2];
   const int64_t elems = bh * s * kHeadDim;
@@ -74,7 +82,7 @@ Result<void> run_attention(Executor &ex, const KernelPlan &p, const std::vector<
 
   auto f_split = ex.function("attention", "attention_split");
   if (!f_split) return std::unexpected(f_split.error());
-  auto f_main = ex.function("attention", "attention");
+  auto f_main = ex.function("attention", gather ? "attention_allgather" : "attention");
   if (!f_main) return std::unexpected(f_main.error());
   {
     LaunchArgs args;
@@ -113,10 +121,52 @@ Result<void> run_attention(Executor &ex, const KernelPlan &p, const std::vector<
   }
   args.add_scalar<uint64_t>(reinterpret_cast<uint64_t>(shifts));
   args.add_scalar<uint64_t>(reinterpret_cast<uint64_t>(ex.status_word()));
-  return ex.launch(*f_main, p.steps[1], args, stream);
+  LaunchStep step = p.steps[1];
+  if (gather) {
+    args.add_struct_bytes(gather, sizeof *gather);
+    step.entry = "attention_allgather";
+  }
+  return ex.launch(*f_main, step, args, stream);
+}
+
+Result<void> run_attention(Executor &ex, const KernelPlan &p, const std::vector<void *> &buf,
+                           StreamHandle stream) {
+  return launch_attention(ex, p, buf, stream, nullptr);
 }
 
 } // namespace
+
+// Attention over `slices` (batch, head) problems of this rank with the all-gather
+// of the output fused into the kernel: `replicas[i]` is rank i's whole
+// [world * slices, seq, 64] output as mapped on this device (only replicas[rank]
+// is needed when `multicast`, the replicas' NVLink multicast address, is given).
+Result<void> run_attention_allgather(Executor &ex, const void *q, const void *k, const void *v,
+                                     const std::vector<void *> &replicas, void *multicast, int rank,
+                                     int world, int64_t slices, int64_t seq, StreamHandle stream) {
+  if (world < 1 || world > 8)
+    return fail(2, "attention_allgather: between 1 and 8 ranks are supported, got " + std::to_string(world));
+  if (rank < 0 || rank >= world || static_cast<int>(replicas.size()) != world)
+    return fail(2, "attention_allgather: rank / replica list do not match the world size");
+  KernelPlan plan;
+  try {
+    plan = plan_attention({{"batch", slices}, {"heads", 1}, {"seq", seq}, {"head_dim", kHeadDim}}, ex.limits());
+  } catch (const std::exception &e) {
+    return fail(2, e.what());
+  }
+  const int64_t shard_elems = slices * seq * kHeadDim; // this rank's slices start this far into a replica
+  GatherOut t{};
+  t.count = world;
+  t.self = rank;
+  t.multicast = multicast ? static_cast<float *>(multicast) + rank * shard_elems : nullptr;
+  for (int i = 0; i < world; ++i) {
+    if (replicas[i] == nullptr && (multicast == nullptr || i == rank))
+      return fail(2, "attention_allgather: null output replica pointer");
+    t.peer[i] = replicas[i] ? static_cast<float *>(replicas[i]) + rank * shard_elems : nullptr;
+  }
+  return launch_attention(ex, plan,
+                          {const_cast<void *>(q), const_cast<void *>(k), const_cast<void *>(v), t.peer[rank]},
+                          stream, &t);
+}
 
 void register_attention_kernel() {
   register_kernel({"attention", "attention", plan_attention, run_attention});

@@ -93,4 +93,9 @@ Result<void> run_gemm_allgather(Executor &ex, const void *a_shard, const void *b
                                 const std::vector<void *> &replicas, void *multicast, int rank,
                                 int world, int64_t m_shard, int64_t n, int64_t k, StreamHandle stream);
 
+// attention_kernel.cpp
+Result<void> run_attention_allgather(Executor &ex, const void *q, const void *k, const void *v,
+                                     const std::vector<void *> &replicas, void *multicast, int rank,
+                                     int world, int64_t slices, int64_t seq, StreamHandle stream);
+
 } // namespace kh

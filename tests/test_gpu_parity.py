@@ -322,6 +322,27 @@ def attention_inputs(oracle, b, h, s):
             oracle.lcg((b, h, s, 64), 0x29C0FFEE))
 
 
+@pytest.mark.parametrize("s", [192, 512])
+def test_attention_allgather_two_shards_fill_every_replica(ctx, oracle, s):
+    """The fused attention + all-gather on one GPU: the two ranks' launches run one
+    after the other and each stores its (batch, head) slices into both replicas of O."""
+    b, h = 2, 3
+    q, k, v = attention_inputs(oracle, b, h, s)
+    plain = run(ctx, "attention", f"batch={b},heads={h},seq={s},head_dim=64", [q, k, v], (b, h, s, 64))
+    dq, dk, dv = (dev(t).reshape(b * h, s, 64) for t in (q, k, v))
+    replicas = [torch.full((b * h, s, 64), float("nan"), device="cuda") for _ in range(2)]
+    stream = torch.cuda.current_stream().cuda_stream
+    slices = b * h // 2
+    for rank in range(2):
+        lo, hi = rank * slices, (rank + 1) * slices
+        ctx.attention_allgather(dq[lo:hi], dk[lo:hi], dv[lo:hi], replicas, 0, rank, slices, s, 64, stream)
+    ctx.synchronize(stream)
+    for r in replicas:
+        assert np.array_equal(r.cpu().numpy().reshape(b, h, s, 64), plain)  # same tiles, same arithmetic
+    with pytest.raises(kh.KernelhError):
+        ctx.attention_allgather(dq, dk, dv, replicas, 0, 2, slices, s, 64, stream)
+
+
 @pytest.mark.parametrize("b,h,s", [(2, 8, 512), (2, 8, 1024), (1, 1, 64), (1, 3, 192)])
 def test_attention_reference_inputs(ctx, oracle, b, h, s):
     q, k, v = attention_inputs(oracle, b, h, s)
