@@ -222,3 +222,14 @@ def test_compute_calls_fail_loudly_without_a_device():
         kh.Context(0)
     assert e.value.code == kh.DRIVER_UNAVAILABLE
     assert "cuInit" in e.value.message or "dlopen" in e.value.message
+
+
+def test_multi_gpu_entry_points_reject_bad_arguments_before_touching_a_device():
+    """The sharded entry points validate their arguments on the host: a null
+    context is a usage error (2) with a message, not a crash."""
+    lib = kh.lib
+    assert lib.kh_gemm_allgather(None, None, None, None, 2, 0, 256, 256, 64, None) == 2
+    assert b"context" in lib.kh_last_error()
+    assert lib.kh_gemm_allgather_multicast(None, None, None, None, None, 2, 0, 256, 256, 64, None) == 2
+    assert lib.kh_attention_allgather(None, None, None, None, None, None, 2, 0, 4, 64, 64, None) == 2
+    assert b"context" in lib.kh_last_error()
