@@ -62,18 +62,41 @@ def measured_peaks() -> dict:
 
 # --------------------------------------------------------------------------- clocks
 class ClockSampler:
-    """Samples SM clock and throttle reasons with nvidia-smi during the timed region."""
+    """Samples the SM clock and the clock-event reasons during the timed region:
+    NVML every 5 ms (reads only), or nvidia-smi every 100 ms when NVML cannot be
+    loaded."""
 
     QUERY = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
              "clocks_event_reasons.sw_power_cap")
+    REASON_BITS = {0x4: "sw_power_cap", 0x8: "hw_slowdown", 0x20: "sw_thermal_slowdown",
+                   0x40: "hw_thermal_slowdown"}
 
     def __init__(self, index: int):
         self.index = index
         self.proc = None
         self.lines: list[str] = []
+        self.nvml = None
+        self.samples: list[tuple[float, int]] = []
+        self.max_mhz = None
+        self.running = False
 
     def start(self):
+        try:
+            import pynvml
+
+            pynvml.nvmlInit()
+            handle = pynvml.nvmlDeviceGetHandleByIndex(self.index)
+            self.max_mhz = float(pynvml.nvmlDeviceGetMaxClockInfo(handle, pynvml.NVML_CLOCK_SM))
+            reasons = getattr(pynvml, "nvmlDeviceGetCurrentClocksEventReasons", None) or \
+                pynvml.nvmlDeviceGetCurrentClocksThrottleReasons
+            self.nvml = (pynvml, handle, reasons)
+            self.running = True
+            self.thread = threading.Thread(target=self._poll, daemon=True)
+            self.thread.start()
+            return
+        except Exception:
+            self.nvml = None
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
@@ -83,11 +106,31 @@ class ClockSampler:
         except OSError:
             self.proc = None
 
+    def _poll(self):
+        pynvml, handle, reasons = self.nvml
+        while self.running:
+            try:
+                self.samples.append((float(pynvml.nvmlDeviceGetClockInfo(handle, pynvml.NVML_CLOCK_SM)),
+                                     int(reasons(handle))))
+            except Exception:
+                pass
+            time.sleep(0.005)
+
     def _pump(self):
         for line in self.proc.stdout:
             self.lines.append(line.strip())
 
     def stop(self) -> dict:
+        if self.nvml is not None:
+            self.running = False
+            self.thread.join(timeout=1.0)
+            sm = sorted(mhz for mhz, _ in self.samples)
+            mask = 0
+            for _, bits in self.samples:
+                mask |= bits
+            found = sorted(name for bit, name in self.REASON_BITS.items() if mask & bit)
+            return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": self.max_mhz,
+                    "sm_min_mhz": sm[0] if sm else None, "samples": len(sm), "reasons": found, "source": "nvml, 5 ms"}
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
         time.sleep(0.15)
@@ -108,7 +151,7 @@ class ClockSampler:
                     reasons.add(name)
         sm.sort()
         return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(smax) if smax else None,
-                "samples": len(sm), "reasons": sorted(reasons)}
+                "samples": len(sm), "reasons": sorted(reasons), "source": "nvidia-smi, 100 ms"}
 
 
 # --------------------------------------------------------------------------- CPU arm
