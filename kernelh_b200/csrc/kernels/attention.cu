@@ -30,10 +30,11 @@
 // Two launches:
 //  attention_split  writes Q, K and V^T as scaled fp16 hi/lo pairs into scratch
 //      and the exponent of every 64-row tile.
-//  attention  warp 0 feeds TMA (Q once; separate 2-deep rings of K and V^T
-//      tiles, so that K of tile j+2 can load as soon as S_j has run); warp 1
-//      issues the MMAs (S of tile j+1 is issued before PV of tile j so the
-//      tensor core works while softmax runs); warps 2-5 and 6-9 are two
+//  attention  warp 0 feeds TMA (Q once; separate 4-deep rings of K and V^T
+//      tiles); warp 1 issues the MMAs (S of tile j+2 goes into the score
+//      buffer of tile j as soon as the softmax group has read S_j out, ahead
+//      of PV of tile j, so a group never waits for scores and the tensor core
+//      works while softmax runs); warps 2-5 and 6-9 are two
 //      softmax groups (one thread per query row each) that take the even and
 //      the odd tiles with their own running max, sum and output row and are
 //      merged at the end, so two tiles are in the softmax stage at once.
@@ -55,9 +56,12 @@ using khd::split_fp16x2;
 constexpr int kHeadDim = 64;
 constexpr int kBQ = 128;  // query rows per CTA
 constexpr int kBKV = 64;  // keys per tile
-constexpr int kStages = 2;
+constexpr int kStages = 4; // K and V^T tiles in flight (rings of their own)
 constexpr int kSoftmaxThreads = 256; // two groups of one thread per query row
-constexpr int kThreads = 64 + kSoftmaxThreads;
+constexpr int kThreads = 64 + kSoftmaxThreads + 32; // producer, issuer of the even tiles, softmax, issuer of the odd tiles
+constexpr int kOddIssuerWarp = (64 + kSoftmaxThreads) / 32;
+// registers are handed out to warps four at a time: bound the kernel as if it had twelve warps
+constexpr int kRegisterBoundThreads = 384;
 constexpr int kRowBytes = 128;                       // 64 fp16: one 128-byte swizzle row
 constexpr int kQTileBytes = kBQ * kRowBytes;         // 16 KiB: 128 rows, hi or lo
 constexpr int kKVTileBytes = kBKV * kRowBytes;       // 8 KiB: 64 rows (keys, or rows of V^T), hi or lo
@@ -235,8 +239,8 @@ __device__ __forceinline__ void attention_body(int64_t seq, float *__restrict__ 
                                                const khd::TensorMap &tm_vt_lo, const int *__restrict__ shifts,
                                                uint32_t *status, const GatherOut *targets) {
   extern __shared__ uint8_t smem_raw[];
-  // q_full, k_full[2], k_empty[2], v_full[2], v_empty[2], s_full[2], p_ready[2], pv_full[2], exchange
-  __shared__ __align__(8) uint64_t bars[16];
+  // q_full, k_full[4], k_empty[4], v_full[4], v_empty[4], s_full[2], s_free[2], p_ready[2], pv_full[2], exchange
+  __shared__ __align__(8) uint64_t bars[2 + 4 * kStages + 8];
   __shared__ uint32_t s_tmem_base;
   __shared__ int s_abort;
 
@@ -247,27 +251,31 @@ __device__ __forceinline__ void attention_body(int64_t seq, float *__restrict__ 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
   const uint32_t smem_q = (khd::smem_u32(smem_raw) + 1023u) & ~1023u;
-  const uint32_t smem_k = smem_q + kQBytes;                   // 2 stages of K hi, lo
-  const uint32_t smem_v = smem_k + kStages * kHalfStageBytes; // 2 stages of V^T hi, lo
+  const uint32_t smem_k = smem_q + kQBytes;                   // kStages stages of K hi, lo
+  const uint32_t smem_v = smem_k + kStages * kHalfStageBytes; // kStages stages of V^T hi, lo
   const uint32_t bar_q = khd::smem_u32(&bars[0]);
   const uint32_t bar_k_full = khd::smem_u32(&bars[1]);
-  const uint32_t bar_k_empty = khd::smem_u32(&bars[3]);
-  const uint32_t bar_v_full = khd::smem_u32(&bars[5]);
-  const uint32_t bar_v_empty = khd::smem_u32(&bars[7]);
-  const uint32_t bar_s_full = khd::smem_u32(&bars[9]);
-  const uint32_t bar_p_ready = khd::smem_u32(&bars[11]);
-  const uint32_t bar_pv_full = khd::smem_u32(&bars[13]);
-  const uint32_t bar_exchange = khd::smem_u32(&bars[15]);
+  const uint32_t bar_k_empty = khd::smem_u32(&bars[1 + kStages]);
+  const uint32_t bar_v_full = khd::smem_u32(&bars[1 + 2 * kStages]);
+  const uint32_t bar_v_empty = khd::smem_u32(&bars[1 + 3 * kStages]);
+  const uint32_t bar_s_full = khd::smem_u32(&bars[1 + 4 * kStages]);
+  const uint32_t bar_s_free = khd::smem_u32(&bars[3 + 4 * kStages]);
+  const uint32_t bar_p_ready = khd::smem_u32(&bars[5 + 4 * kStages]);
+  const uint32_t bar_pv_full = khd::smem_u32(&bars[7 + 4 * kStages]);
+  const uint32_t bar_exchange = khd::smem_u32(&bars[9 + 4 * kStages]);
 
   if (threadIdx.x == 0) {
     s_abort = 0;
     khd::mbar_init(bar_q, 1);
-    for (int s = 0; s < 2; ++s) {
+    for (int s = 0; s < kStages; ++s) {
       khd::mbar_init(bar_k_full + 8 * s, 1);
       khd::mbar_init(bar_k_empty + 8 * s, 1);
       khd::mbar_init(bar_v_full + 8 * s, 1);
       khd::mbar_init(bar_v_empty + 8 * s, 1);
+    }
+    for (int s = 0; s < 2; ++s) {
       khd::mbar_init(bar_s_full + 8 * s, 1);
+      khd::mbar_init(bar_s_free + 8 * s, kBQ); // one arrival per thread of the group once it holds the scores
       khd::mbar_init(bar_p_ready + 8 * s, kBQ); // one arrival per thread of the group that owns the buffer
       khd::mbar_init(bar_pv_full + 8 * s, 1);
     }
@@ -290,16 +298,16 @@ __device__ __forceinline__ void attention_body(int64_t seq, float *__restrict__ 
   const uint32_t tmem_base = s_tmem_base;
 
   if (warp == 0) {
-    // ---- TMA producer: K and V have their own 2-deep rings. A K slot is free as
-    //      soon as S of its tile has run, long before the V slot of the same tile. ------
+    // ---- TMA producer: K and V have their own rings of kStages tiles. A K slot is
+    //      free as soon as S of its tile has run, long before the V slot of that tile. --
     if (lane == 0) {
       const int q_row = static_cast<int>(bh * seq) + q0;
       khd::mbar_arrive_expect_tx(bar_q, kQBytes);
       khd::tma_load_2d(smem_q, &tm_q_hi, 0, q_row, bar_q);
       khd::tma_load_2d(smem_q + kQTileBytes, &tm_q_lo, 0, q_row, bar_q);
       for (int j = 0; j < num_kv; ++j) {
-        const int s = j & 1;
-        const uint32_t phase = static_cast<uint32_t>((j >> 1) & 1);
+        const int s = j % kStages;
+        const uint32_t phase = static_cast<uint32_t>((j / kStages) & 1);
         if (!khd::mbar_wait(bar_k_empty + 8 * s, phase ^ 1u, &s_abort, status,
                             khd::kStatusEmptyWaitTimeout, static_cast<uint32_t>(j)))
           break;
@@ -325,74 +333,79 @@ __device__ __forceinline__ void attention_body(int64_t seq, float *__restrict__ 
         }
       }
     }
-  } else if (warp == 1) {
-    // ---- MMA issuer: S_0, then per tile j: S_{j+1} (other S buffer), PV_j. The
-    //      whole warp walks the loop (waits, descriptor arithmetic: warp-uniform,
-    //      so it stays in uniform registers); only the tcgen05 instructions
-    //      themselves sit under the elected lane. ---------------------------------------
+  } else if (warp == 1 || warp == kOddIssuerWarp) {
+    // ---- MMA issuers, one warp per softmax group: warp 1 takes the even tiles,
+    //      the last warp the odd ones (a single thread cannot issue tcgen05.mma
+    //      fast enough for both). Per tile j of its parity: S_{j+2} into the score
+    //      buffer of tile j as soon as the group has read S_j out (s_free), then
+    //      PV_j once P_j is written; the scores of a group's next tile are
+    //      computed while it still works on the current one. The whole warp walks
+    //      the loop (waits, descriptor arithmetic: warp-uniform, so it stays in
+    //      uniform registers); only the tcgen05 instructions themselves sit
+    //      under the elected lane. ------------------------------------------------------
     {
+      const int g = warp == 1 ? 0 : 1;
       const bool leader = khd::elect_one();
       constexpr uint32_t idesc = khd::umma_idesc_f16(kBQ, kBKV); // M128 N64 K16 for both products
       // a tile row is one 128-byte swizzle row (64 fp16); a k-step of 16 fp16 moves 32 bytes (2 encoded)
       const uint64_t dq_hi = khd::umma_desc_k128(smem_q), dq_lo = khd::umma_desc_k128(smem_q + kQTileBytes);
       constexpr uint64_t kKVTileStep = kKVTileBytes >> 4;
-      auto issue_s = [&](int b) {
-        const uint64_t dk_hi = khd::umma_desc_k128(smem_k + b * kHalfStageBytes);
+      const uint32_t col_s = tmem_base + (g ? kColS1 : kColS0), col_p = tmem_base + (g ? kColP1 : kColP0),
+                     col_pv = tmem_base + (g ? kColPV1 : kColPV0);
+      // S_t = Q K_t^T into this group's score buffer, from ring slot t % kStages
+      auto issue_s = [&](int t) -> bool {
+        const int slot = t % kStages;
+        bool ready = khd::mbar_wait(bar_k_full + 8 * slot, static_cast<uint32_t>((t / kStages) & 1), &s_abort,
+                                    status, khd::kStatusTmaWaitTimeout, static_cast<uint32_t>(t));
+        if (t >= 2) // the group holds S_{t-2} in registers
+          ready = ready && khd::mbar_wait(bar_s_free + 8 * g, static_cast<uint32_t>(((t - 2) >> 1) & 1), &s_abort,
+                                          status, khd::kStatusEpilogueWaitTimeout, 3000u + static_cast<uint32_t>(t));
+        ready = __all_sync(0xffffffffu, ready);
+        if (!ready) return false;
+        khd::tc_fence_after_sync();
+        const uint64_t dk_hi = khd::umma_desc_k128(smem_k + slot * kHalfStageBytes);
         const uint64_t dk_lo = dk_hi + kKVTileStep;
-        const uint32_t d = tmem_base + (b ? kColS1 : kColS0);
         if (leader) {
 #pragma unroll
           for (int kk = 0; kk < kHeadDim / 16; ++kk) {
             const uint64_t off = static_cast<uint64_t>(kk * 2);
-            khd::umma_f16_ss(d, dq_lo + off, dk_hi + off, idesc, kk != 0 ? 1u : 0u);
-            khd::umma_f16_ss(d, dq_hi + off, dk_lo + off, idesc, 1u);
-            khd::umma_f16_ss(d, dq_hi + off, dk_hi + off, idesc, 1u);
+            khd::umma_f16_ss(col_s, dq_lo + off, dk_hi + off, idesc, kk != 0 ? 1u : 0u);
+            khd::umma_f16_ss(col_s, dq_hi + off, dk_lo + off, idesc, 1u);
+            khd::umma_f16_ss(col_s, dq_hi + off, dk_hi + off, idesc, 1u);
           }
-          khd::umma_commit(bar_s_full + 8 * b);  // scores ready for the softmax threads
-          khd::umma_commit(bar_k_empty + 8 * b); // and this K slot may be refilled
+          khd::umma_commit(bar_s_full + 8 * g);     // scores ready for the softmax threads
+          khd::umma_commit(bar_k_empty + 8 * slot); // and this K slot may be refilled
         }
         __syncwarp();
+        return true;
       };
       bool ok = khd::mbar_wait(bar_q, 0u, &s_abort, status, khd::kStatusTmaWaitTimeout, 1000u);
-      ok = ok && khd::mbar_wait(bar_k_full, 0u, &s_abort, status, khd::kStatusTmaWaitTimeout, 0u);
       ok = __all_sync(0xffffffffu, ok);
-      if (ok) {
-        khd::tc_fence_after_sync();
-        issue_s(0);
-      }
-      for (int j = 0; j < num_kv && ok; ++j) {
-        const int b = j & 1;
-        const uint32_t phase = static_cast<uint32_t>((j >> 1) & 1);
-        if (j + 1 < num_kv) {
-          ok = khd::mbar_wait(bar_k_full + 8 * ((j + 1) & 1), static_cast<uint32_t>(((j + 1) >> 1) & 1),
-                              &s_abort, status, khd::kStatusTmaWaitTimeout, static_cast<uint32_t>(j + 1));
-          ok = __all_sync(0xffffffffu, ok);
-          if (!ok) break;
-          khd::tc_fence_after_sync();
-          issue_s((j + 1) & 1);
-        }
-        ok = khd::mbar_wait(bar_p_ready + 8 * b, phase, &s_abort, status,
+      if (ok) khd::tc_fence_after_sync();
+      if (g < num_kv) ok = ok && issue_s(g);
+      for (int j = g; j < num_kv && ok; j += 2) {
+        const int slot = j % kStages;
+        if (j + 2 < num_kv && !issue_s(j + 2)) break;
+        ok = khd::mbar_wait(bar_p_ready + 8 * g, static_cast<uint32_t>((j >> 1) & 1), &s_abort, status,
                             khd::kStatusEpilogueWaitTimeout, static_cast<uint32_t>(j));
-        ok = ok && khd::mbar_wait(bar_v_full + 8 * b, phase, &s_abort, status,
+        ok = ok && khd::mbar_wait(bar_v_full + 8 * slot, static_cast<uint32_t>((j / kStages) & 1), &s_abort, status,
                                   khd::kStatusTmaWaitTimeout, 2000u + static_cast<uint32_t>(j));
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
         khd::tc_fence_after_sync();
-        // PV_j = P_j V_j: A = P buffer b (tensor memory), B = V^T tile, D = PV buffer b
-        const uint64_t dv_hi = khd::umma_desc_k128(smem_v + b * kHalfStageBytes);
+        // PV_j = P_j V_j: A = the group's P buffer (tensor memory), B = V^T tile, D = its PV buffer
+        const uint64_t dv_hi = khd::umma_desc_k128(smem_v + slot * kHalfStageBytes);
         const uint64_t dv_lo = dv_hi + kKVTileStep;
-        const uint32_t d = tmem_base + (b ? kColPV1 : kColPV0);
-        const uint32_t p_base = tmem_base + (b ? kColP1 : kColP0);
         if (leader) {
 #pragma unroll
           for (int kk = 0; kk < kBKV / 16; ++kk) { // 16 keys = 8 packed columns of P
             const uint64_t voff = static_cast<uint64_t>(kk * 2);
-            umma_f16_ts(d, p_base + 32 + kk * 8, dv_hi + voff, idesc, kk != 0 ? 1u : 0u);
-            umma_f16_ts(d, p_base + kk * 8, dv_lo + voff, idesc, 1u);
-            umma_f16_ts(d, p_base + kk * 8, dv_hi + voff, idesc, 1u);
+            umma_f16_ts(col_pv, col_p + 32 + kk * 8, dv_hi + voff, idesc, kk != 0 ? 1u : 0u);
+            umma_f16_ts(col_pv, col_p + kk * 8, dv_lo + voff, idesc, 1u);
+            umma_f16_ts(col_pv, col_p + kk * 8, dv_hi + voff, idesc, 1u);
           }
-          khd::umma_commit(bar_pv_full + 8 * b);
-          khd::umma_commit(bar_v_empty + 8 * b);
+          khd::umma_commit(bar_pv_full + 8 * g);
+          khd::umma_commit(bar_v_empty + 8 * slot);
         }
         __syncwarp();
       }
@@ -440,6 +453,8 @@ __device__ __forceinline__ void attention_body(int64_t seq, float *__restrict__ 
       khd::tmem_ld_32x32(tmem_base + lane_base + col_s, *reinterpret_cast<uint32_t(*)[32]>(&sv[0]));
       khd::tmem_ld_32x32(tmem_base + lane_base + col_s + 32, *reinterpret_cast<uint32_t(*)[32]>(&sv[32]));
       khd::tmem_ld_wait();
+      khd::tc_fence_before_sync();
+      khd::mbar_arrive(bar_s_free + 8 * g); // the score buffer may take S_{j+2}
       // this tile's scores carry 2^(shift_q + shift_k): one positive factor brings them to exp2 units
       const float f = khd::scale_pow2(kLog2eOverSqrtD, -(shift_q + shift_k));
       float mx = -INFINITY;
@@ -590,7 +605,7 @@ __device__ __forceinline__ void attention_body(int64_t seq, float *__restrict__ 
 
 } // namespace
 
-extern "C" __global__ void __launch_bounds__(kThreads, 1)
+extern "C" __global__ void __launch_bounds__(kRegisterBoundThreads, 1)
 attention(KH_MEMREF4(const float, q), KH_MEMREF4(const float, k), KH_MEMREF4(const float, v),
           KH_MEMREF4(float, o), const __grid_constant__ khd::TensorMap tm_q_hi,
           const __grid_constant__ khd::TensorMap tm_q_lo, const __grid_constant__ khd::TensorMap tm_k_hi,
@@ -613,7 +628,7 @@ attention(KH_MEMREF4(const float, q), KH_MEMREF4(const float, k), KH_MEMREF4(con
 // replica of the whole output, and every finished tile is also sent to the
 // other replicas (see GatherOut). The caller's barrier across ranks after the
 // kernel makes the peers' stores visible.
-extern "C" __global__ void __launch_bounds__(kThreads, 1)
+extern "C" __global__ void __launch_bounds__(kRegisterBoundThreads, 1)
 attention_allgather(KH_MEMREF4(const float, q), KH_MEMREF4(const float, k), KH_MEMREF4(const float, v),
                     KH_MEMREF4(float, o), const __grid_constant__ khd::TensorMap tm_q_hi,
                     const __grid_constant__ khd::TensorMap tm_q_lo, const __grid_constant__ khd::TensorMap tm_k_hi,

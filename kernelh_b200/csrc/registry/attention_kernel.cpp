@@ -11,8 +11,8 @@ namespace kh {
 namespace {
 
 constexpr int64_t kHeadDim = 64, kBQ = 128, kBKV = 64;
-// Q hi/lo (32 KiB) + two stages each of K and V^T hi/lo (16 KiB per stage) + alignment slack
-constexpr size_t kAttnSmem = 32 * 1024 + 2 * 2 * 16 * 1024 + 1024;
+// Q hi/lo (32 KiB) + four stages each of K and V^T hi/lo (16 KiB per stage) + alignment slack
+constexpr size_t kAttnSmem = 32 * 1024 + 2 * 4 * 16 * 1024 + 1024;
 
 KernelPlan plan_attention(const ShapeMap &shape, const DeviceLimits &l) {
   for (const char *key : {"batch", "heads", "seq", "head_dim"})
@@ -47,7 +47,7 @@ KernelPlan plan_attention(const ShapeMap &shape, const DeviceLimits &l) {
   split.param_count = 33 + 7;
   LaunchStep main;
   main.entry = "attention";
-  main.block = {320, 1, 1};
+  main.block = {352, 1, 1}; // producer, two MMA issuers, eight softmax warps
   main.grid = {static_cast<unsigned>(b * h * ((s + kBQ - 1) / kBQ)), 1, 1};
   main.dynamic_smem = kAttnSmem;
   main.param_count = 44 + 6 + 2;
