@@ -70,7 +70,8 @@ constexpr int kHalfStageBytes = 2 * kKVTileBytes;    // one K (or V^T) tile: hi 
 constexpr int kPShift = 14;                          // P is split as P * 2^14
 // tensor-memory columns: two score buffers, two P buffers (32 columns of packed
 // fp16 pairs for hi, 32 for lo), two PV buffers
-constexpr uint32_t kColS0 = 0, kColS1 = 64, kColP0 = 128, kColP1 = 192, kColPV0 = 256, kColPV1 = 320;
+constexpr uint32_t kColS0 = 0, kColS1 = 64, kColP0 = 128, kColP1 = 192, kColPV0 = 256, kColPV1 = 320,
+                   kColQHi = 384, kColQLo = 416; // the Q tile as the A operand: 64 fp16 = 32 columns, hi and lo
 constexpr uint32_t kTmemCols = 512;
 
 // 2^x by the special-function unit (2 ulp, flushes denormals): the arguments
@@ -240,7 +241,7 @@ __device__ __forceinline__ void attention_body(int64_t seq, float *__restrict__ 
                                                uint32_t *status, const GatherOut *targets) {
   extern __shared__ uint8_t smem_raw[];
   // q_full, k_full[4], k_empty[4], v_full[4], v_empty[4], s_full[2], s_free[2], p_ready[2], pv_full[2], exchange
-  __shared__ __align__(8) uint64_t bars[2 + 4 * kStages + 8];
+  __shared__ __align__(8) uint64_t bars[2 + 4 * kStages + 8 + 1];
   __shared__ uint32_t s_tmem_base;
   __shared__ int s_abort;
 
@@ -263,6 +264,7 @@ __device__ __forceinline__ void attention_body(int64_t seq, float *__restrict__ 
   const uint32_t bar_p_ready = khd::smem_u32(&bars[5 + 4 * kStages]);
   const uint32_t bar_pv_full = khd::smem_u32(&bars[7 + 4 * kStages]);
   const uint32_t bar_exchange = khd::smem_u32(&bars[9 + 4 * kStages]);
+  const uint32_t bar_q_ready = khd::smem_u32(&bars[10 + 4 * kStages]); // Q sits in tensor memory
 
   if (threadIdx.x == 0) {
     s_abort = 0;
@@ -280,6 +282,7 @@ __device__ __forceinline__ void attention_body(int64_t seq, float *__restrict__ 
       khd::mbar_init(bar_pv_full + 8 * s, 1);
     }
     khd::mbar_init(bar_exchange, kSoftmaxThreads);
+    khd::mbar_init(bar_q_ready, kBQ);
     khd::mbar_fence_init();
     khd::tma_prefetch_descriptor(&tm_q_hi);
     khd::tma_prefetch_descriptor(&tm_q_lo);
@@ -348,7 +351,10 @@ __device__ __forceinline__ void attention_body(int64_t seq, float *__restrict__ 
       const bool leader = khd::elect_one();
       constexpr uint32_t idesc = khd::umma_idesc_f16(kBQ, kBKV); // M128 N64 K16 for both products
       // a tile row is one 128-byte swizzle row (64 fp16); a k-step of 16 fp16 moves 32 bytes (2 encoded)
-      const uint64_t dq_hi = khd::umma_desc_k128(smem_q), dq_lo = khd::umma_desc_k128(smem_q + kQTileBytes);
+      // Q is read from tensor memory (the even group copies it there once): a
+      // k-step of 16 fp16 is 8 columns. Only K and V^T are fetched from shared
+      // memory, whose bandwidth is what the three products of a tile compete for.
+      const uint32_t q_hi = tmem_base + kColQHi, q_lo = tmem_base + kColQLo;
       constexpr uint64_t kKVTileStep = kKVTileBytes >> 4;
       const uint32_t col_s = tmem_base + (g ? kColS1 : kColS0), col_p = tmem_base + (g ? kColP1 : kColP0),
                      col_pv = tmem_base + (g ? kColPV1 : kColPV0);
@@ -369,9 +375,9 @@ __device__ __forceinline__ void attention_body(int64_t seq, float *__restrict__ 
 #pragma unroll
           for (int kk = 0; kk < kHeadDim / 16; ++kk) {
             const uint64_t off = static_cast<uint64_t>(kk * 2);
-            khd::umma_f16_ss(col_s, dq_lo + off, dk_hi + off, idesc, kk != 0 ? 1u : 0u);
-            khd::umma_f16_ss(col_s, dq_hi + off, dk_lo + off, idesc, 1u);
-            khd::umma_f16_ss(col_s, dq_hi + off, dk_hi + off, idesc, 1u);
+            umma_f16_ts(col_s, q_lo + kk * 8, dk_hi + off, idesc, kk != 0 ? 1u : 0u);
+            umma_f16_ts(col_s, q_hi + kk * 8, dk_lo + off, idesc, 1u);
+            umma_f16_ts(col_s, q_hi + kk * 8, dk_hi + off, idesc, 1u);
           }
           khd::umma_commit(bar_s_full + 8 * g);     // scores ready for the softmax threads
           khd::umma_commit(bar_k_empty + 8 * slot); // and this K slot may be refilled
@@ -379,7 +385,7 @@ __device__ __forceinline__ void attention_body(int64_t seq, float *__restrict__ 
         __syncwarp();
         return true;
       };
-      bool ok = khd::mbar_wait(bar_q, 0u, &s_abort, status, khd::kStatusTmaWaitTimeout, 1000u);
+      bool ok = khd::mbar_wait(bar_q_ready, 0u, &s_abort, status, khd::kStatusEpilogueWaitTimeout, 1000u);
       ok = __all_sync(0xffffffffu, ok);
       if (ok) khd::tc_fence_after_sync();
       if (g < num_kv) ok = ok && issue_s(g);
@@ -438,6 +444,32 @@ __device__ __forceinline__ void attention_body(int64_t seq, float *__restrict__ 
     // the exponents of this group's next tile are fetched one tile ahead
     int shift_k_next = g < num_kv ? __ldg(k_shifts + g) : 0, shift_v_next = g < num_kv ? __ldg(v_shifts + g) : 0;
 
+    if (g == 0) {
+      // Q tile -> tensor memory, one row per thread: undo the 128-byte swizzle of
+      // the TMA tile (16-byte chunk c of row r sits at chunk c ^ (r % 8)); a
+      // 32-bit column holds two neighbouring fp16, the even one in the low half.
+      ok = khd::mbar_wait(bar_q, 0u, &s_abort, status, khd::kStatusTmaWaitTimeout, 1001u);
+      if (ok) {
+        const uint8_t *q_tiles_smem = smem_raw + (smem_q - khd::smem_u32(smem_raw));
+#pragma unroll
+        for (int part = 0; part < 2; ++part) { // hi, lo
+          const uint8_t *row = q_tiles_smem + part * kQTileBytes + row_in_tile * kRowBytes;
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            uint32_t w[16];
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+              const uint4 v = *reinterpret_cast<const uint4 *>(row + (((4 * h + c) ^ (row_in_tile & 7)) << 4));
+              w[4 * c + 0] = v.x; w[4 * c + 1] = v.y; w[4 * c + 2] = v.z; w[4 * c + 3] = v.w;
+            }
+            tmem_st_32x16(tmem_base + lane_base + (part ? kColQLo : kColQHi) + 16 * h, w);
+          }
+        }
+        tmem_st_wait();
+        khd::tc_fence_before_sync();
+      }
+      khd::mbar_arrive(bar_q_ready);
+    }
     for (int j = g; j < num_kv && ok; j += 2) {
       const uint32_t phase = static_cast<uint32_t>((j >> 1) & 1);
       const int shift_k = shift_k_next, shift_v = shift_v_next;
