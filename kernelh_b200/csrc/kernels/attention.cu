@@ -70,8 +70,7 @@ constexpr int kHalfStageBytes = 2 * kKVTileBytes;    // one K (or V^T) tile: hi 
 constexpr int kPShift = 14;                          // P is split as P * 2^14
 // tensor-memory columns: two score buffers, two P buffers (32 columns of packed
 // fp16 pairs for hi, 32 for lo), two PV buffers
-constexpr uint32_t kColS0 = 0, kColS1 = 64, kColP0 = 128, kColP1 = 192, kColPV0 = 256, kColPV1 = 320,
-                   kColQHi = 384, kColQLo = 416; // the Q tile as the A operand: 64 fp16 = 32 columns, hi and lo
+constexpr uint32_t kColS0 = 0, kColS1 = 64, kColP0 = 128, kColP1 = 192, kColPV0 = 256, kColPV1 = 320;
 constexpr uint32_t kTmemCols = 512;
 
 // 2^x by the special-function unit (2 ulp, flushes denormals): the arguments
@@ -229,60 +228,71 @@ __device__ __forceinline__ void multicast_store_float4(float *p, float4 v) {
                : "memory");
 }
 
-// The kernel body. `seq`: keys (= queries) per slice; `out`: this launch's
-// [slices, seq, 64] output. kGather: after a CTA has stored its 128 x 64 output
-// tile (32 KiB, contiguous), the softmax threads read it back from L2 and send
-// it to the other replicas in 512-byte warp-wide pieces.
+// The kernel body. `slices`: (batch, head) problems of this launch; `seq`: keys
+// (= queries) per slice; `out`: this launch's [slices, seq, 64] output. The
+// grid is persistent: CTA b takes the work items (one tile of 128 query rows of
+// one slice each) b, b + gridDim.x, ... and every role walks the same list, so
+// that the loads and the first score products of the next item run while the
+// softmax groups finish the current one. kGather: after the 128 x 64 output tile
+// of an item (32 KiB, contiguous) is stored, the group that stored it reads it
+// back from L2 and sends it to the other replicas in 512-byte warp-wide pieces.
 template <bool kGather>
-__device__ __forceinline__ void attention_body(int64_t seq, float *__restrict__ out, const khd::TensorMap &tm_q_hi,
-                                               const khd::TensorMap &tm_q_lo, const khd::TensorMap &tm_k_hi,
-                                               const khd::TensorMap &tm_k_lo, const khd::TensorMap &tm_vt_hi,
-                                               const khd::TensorMap &tm_vt_lo, const int *__restrict__ shifts,
-                                               uint32_t *status, const GatherOut *targets) {
+__device__ __forceinline__ void attention_body(int64_t slices, int64_t seq, float *__restrict__ out,
+                                               const khd::TensorMap &tm_q_hi, const khd::TensorMap &tm_q_lo,
+                                               const khd::TensorMap &tm_k_hi, const khd::TensorMap &tm_k_lo,
+                                               const khd::TensorMap &tm_vt_hi, const khd::TensorMap &tm_vt_lo,
+                                               const int *__restrict__ shifts, uint32_t *status,
+                                               const GatherOut *targets) {
   extern __shared__ uint8_t smem_raw[];
-  // q_full, k_full[4], k_empty[4], v_full[4], v_empty[4], s_full[2], s_free[2], p_ready[2], pv_full[2], exchange
-  __shared__ __align__(8) uint64_t bars[2 + 4 * kStages + 8 + 1];
+  // q_full[2], q_empty[2], k_full, k_empty, v_full, v_empty [kStages each], s_full[2], s_free[2],
+  // p_ready[2], pv_full[2], merge_ready, scratch_free, gather
+  __shared__ __align__(8) uint64_t bars[4 + 4 * kStages + 8 + 3];
   __shared__ uint32_t s_tmem_base;
   __shared__ int s_abort;
+  __shared__ float s_merge_m[kBQ], s_merge_l[kBQ]; // max and sum of the group that hands its row over
 
   const int64_t q_tiles = (seq + kBQ - 1) / kBQ;
-  const int64_t bh = blockIdx.x / q_tiles;
-  const int q0 = static_cast<int>((blockIdx.x - bh * q_tiles) * kBQ);
+  const int64_t items = slices * q_tiles;
   const int num_kv = static_cast<int>(seq / kBKV);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
-  const uint32_t smem_q = (khd::smem_u32(smem_raw) + 1023u) & ~1023u;
-  const uint32_t smem_k = smem_q + kQBytes;                   // kStages stages of K hi, lo
-  const uint32_t smem_v = smem_k + kStages * kHalfStageBytes; // kStages stages of V^T hi, lo
-  const uint32_t bar_q = khd::smem_u32(&bars[0]);
-  const uint32_t bar_k_full = khd::smem_u32(&bars[1]);
-  const uint32_t bar_k_empty = khd::smem_u32(&bars[1 + kStages]);
-  const uint32_t bar_v_full = khd::smem_u32(&bars[1 + 2 * kStages]);
-  const uint32_t bar_v_empty = khd::smem_u32(&bars[1 + 3 * kStages]);
-  const uint32_t bar_s_full = khd::smem_u32(&bars[1 + 4 * kStages]);
-  const uint32_t bar_s_free = khd::smem_u32(&bars[3 + 4 * kStages]);
-  const uint32_t bar_p_ready = khd::smem_u32(&bars[5 + 4 * kStages]);
-  const uint32_t bar_pv_full = khd::smem_u32(&bars[7 + 4 * kStages]);
-  const uint32_t bar_exchange = khd::smem_u32(&bars[9 + 4 * kStages]);
-  const uint32_t bar_q_ready = khd::smem_u32(&bars[10 + 4 * kStages]); // Q sits in tensor memory
+  const uint32_t smem_q = (khd::smem_u32(smem_raw) + 1023u) & ~1023u; // two Q tiles (hi, lo each)
+  const uint32_t smem_k = smem_q + 2 * kQBytes;                       // kStages stages of K hi, lo
+  const uint32_t smem_v = smem_k + kStages * kHalfStageBytes;         // kStages stages of V^T hi, lo
+  const uint32_t smem_scratch = smem_v + kStages * kHalfStageBytes;   // one output row per query row (merge)
+  const uint32_t bar_q_full = khd::smem_u32(&bars[0]);
+  const uint32_t bar_q_empty = khd::smem_u32(&bars[2]);
+  const uint32_t bar_k_full = khd::smem_u32(&bars[4]);
+  const uint32_t bar_k_empty = khd::smem_u32(&bars[4 + kStages]);
+  const uint32_t bar_v_full = khd::smem_u32(&bars[4 + 2 * kStages]);
+  const uint32_t bar_v_empty = khd::smem_u32(&bars[4 + 3 * kStages]);
+  const uint32_t bar_s_full = khd::smem_u32(&bars[4 + 4 * kStages]);
+  const uint32_t bar_s_free = khd::smem_u32(&bars[6 + 4 * kStages]);
+  const uint32_t bar_p_ready = khd::smem_u32(&bars[8 + 4 * kStages]);
+  const uint32_t bar_pv_full = khd::smem_u32(&bars[10 + 4 * kStages]);
+  const uint32_t bar_merge_ready = khd::smem_u32(&bars[12 + 4 * kStages]);
+  const uint32_t bar_scratch_free = khd::smem_u32(&bars[13 + 4 * kStages]);
+  const uint32_t bar_gather = khd::smem_u32(&bars[14 + 4 * kStages]);
 
   if (threadIdx.x == 0) {
     s_abort = 0;
-    khd::mbar_init(bar_q, 1);
+    for (int s = 0; s < 2; ++s) {
+      khd::mbar_init(bar_q_full + 8 * s, 1);
+      khd::mbar_init(bar_q_empty + 8 * s, 2); // both issuers are done with the Q tile
+      khd::mbar_init(bar_s_full + 8 * s, 1);
+      khd::mbar_init(bar_s_free + 8 * s, kBQ);  // one arrival per thread of the group once it holds the scores
+      khd::mbar_init(bar_p_ready + 8 * s, kBQ); // one arrival per thread of the group that owns the buffer
+      khd::mbar_init(bar_pv_full + 8 * s, 1);
+    }
     for (int s = 0; s < kStages; ++s) {
       khd::mbar_init(bar_k_full + 8 * s, 1);
       khd::mbar_init(bar_k_empty + 8 * s, 1);
       khd::mbar_init(bar_v_full + 8 * s, 1);
       khd::mbar_init(bar_v_empty + 8 * s, 1);
     }
-    for (int s = 0; s < 2; ++s) {
-      khd::mbar_init(bar_s_full + 8 * s, 1);
-      khd::mbar_init(bar_s_free + 8 * s, kBQ); // one arrival per thread of the group once it holds the scores
-      khd::mbar_init(bar_p_ready + 8 * s, kBQ); // one arrival per thread of the group that owns the buffer
-      khd::mbar_init(bar_pv_full + 8 * s, 1);
-    }
-    khd::mbar_init(bar_exchange, kSoftmaxThreads);
-    khd::mbar_init(bar_q_ready, kBQ);
+    khd::mbar_init(bar_merge_ready, kBQ);
+    khd::mbar_init(bar_scratch_free, kBQ);
+    khd::mbar_init(bar_gather, kBQ);
     khd::mbar_fence_init();
     khd::tma_prefetch_descriptor(&tm_q_hi);
     khd::tma_prefetch_descriptor(&tm_q_lo);
@@ -301,47 +311,65 @@ __device__ __forceinline__ void attention_body(int64_t seq, float *__restrict__ 
   const uint32_t tmem_base = s_tmem_base;
 
   if (warp == 0) {
-    // ---- TMA producer: K and V have their own rings of kStages tiles. A K slot is
-    //      free as soon as S of its tile has run, long before the V slot of that tile. --
+    // ---- TMA producer: per item the Q tile (two buffers, so the next item's
+    //      tile loads while this one is in use), then the item's K and V^T
+    //      tiles through rings of kStages tiles that run on across items. A K
+    //      slot is free as soon as S of its tile has run, long before the V
+    //      slot of that tile. -----------------------------------------------------------
     if (lane == 0) {
-      const int q_row = static_cast<int>(bh * seq) + q0;
-      khd::mbar_arrive_expect_tx(bar_q, kQBytes);
-      khd::tma_load_2d(smem_q, &tm_q_hi, 0, q_row, bar_q);
-      khd::tma_load_2d(smem_q + kQTileBytes, &tm_q_lo, 0, q_row, bar_q);
-      for (int j = 0; j < num_kv; ++j) {
-        const int s = j % kStages;
-        const uint32_t phase = static_cast<uint32_t>((j / kStages) & 1);
-        if (!khd::mbar_wait(bar_k_empty + 8 * s, phase ^ 1u, &s_abort, status,
-                            khd::kStatusEmptyWaitTimeout, static_cast<uint32_t>(j)))
-          break;
+      uint32_t tile = 0; // tiles loaded so far
+      bool ok = true;
+      int n = 0;
+      for (int64_t w = blockIdx.x; w < items && ok; w += gridDim.x, ++n) {
+        const int64_t bh = w / q_tiles;
+        const int q0 = static_cast<int>((w - bh * q_tiles) * kBQ);
+        const int qb = n & 1;
+        ok = khd::mbar_wait(bar_q_empty + 8 * qb, static_cast<uint32_t>((n >> 1) & 1) ^ 1u, &s_abort, status,
+                            khd::kStatusEmptyWaitTimeout, 4000u);
+        if (!ok) break;
         {
-          const uint32_t st = smem_k + s * kHalfStageBytes;
-          const uint32_t bar = bar_k_full + 8 * s;
-          khd::mbar_arrive_expect_tx(bar, kHalfStageBytes);
-          const int k_row = static_cast<int>(bh * seq) + j * kBKV;
-          khd::tma_load_2d(st, &tm_k_hi, 0, k_row, bar);
-          khd::tma_load_2d(st + kKVTileBytes, &tm_k_lo, 0, k_row, bar);
+          const uint32_t bar = bar_q_full + 8 * qb;
+          const int q_row = static_cast<int>(bh * seq) + q0;
+          khd::mbar_arrive_expect_tx(bar, kQBytes);
+          khd::tma_load_2d(smem_q + qb * kQBytes, &tm_q_hi, 0, q_row, bar);
+          khd::tma_load_2d(smem_q + qb * kQBytes + kQTileBytes, &tm_q_lo, 0, q_row, bar);
         }
-        if (!khd::mbar_wait(bar_v_empty + 8 * s, phase ^ 1u, &s_abort, status,
-                            khd::kStatusEmptyWaitTimeout, 1000u + static_cast<uint32_t>(j)))
-          break;
-        {
-          const uint32_t st = smem_v + s * kHalfStageBytes;
-          const uint32_t bar = bar_v_full + 8 * s;
-          khd::mbar_arrive_expect_tx(bar, kHalfStageBytes);
-          const int v_row = static_cast<int>(bh * kHeadDim);
-          const int v_col = j * kBKV;
-          khd::tma_load_2d(st, &tm_vt_hi, v_col, v_row, bar);
-          khd::tma_load_2d(st + kKVTileBytes, &tm_vt_lo, v_col, v_row, bar);
+        for (int j = 0; j < num_kv; ++j, ++tile) {
+          const int s = static_cast<int>(tile % kStages);
+          const uint32_t phase = (tile / kStages) & 1u;
+          ok = khd::mbar_wait(bar_k_empty + 8 * s, phase ^ 1u, &s_abort, status, khd::kStatusEmptyWaitTimeout,
+                              static_cast<uint32_t>(j));
+          if (!ok) break;
+          {
+            const uint32_t st = smem_k + s * kHalfStageBytes;
+            const uint32_t bar = bar_k_full + 8 * s;
+            khd::mbar_arrive_expect_tx(bar, kHalfStageBytes);
+            const int k_row = static_cast<int>(bh * seq) + j * kBKV;
+            khd::tma_load_2d(st, &tm_k_hi, 0, k_row, bar);
+            khd::tma_load_2d(st + kKVTileBytes, &tm_k_lo, 0, k_row, bar);
+          }
+          ok = khd::mbar_wait(bar_v_empty + 8 * s, phase ^ 1u, &s_abort, status, khd::kStatusEmptyWaitTimeout,
+                              1000u + static_cast<uint32_t>(j));
+          if (!ok) break;
+          {
+            const uint32_t st = smem_v + s * kHalfStageBytes;
+            const uint32_t bar = bar_v_full + 8 * s;
+            khd::mbar_arrive_expect_tx(bar, kHalfStageBytes);
+            const int v_row = static_cast<int>(bh * kHeadDim);
+            const int v_col = j * kBKV;
+            khd::tma_load_2d(st, &tm_vt_hi, v_col, v_row, bar);
+            khd::tma_load_2d(st + kKVTileBytes, &tm_vt_lo, v_col, v_row, bar);
+          }
         }
       }
     }
   } else if (warp == 1 || warp == kOddIssuerWarp) {
-    // ---- MMA issuers, one warp per softmax group: warp 1 takes the even tiles,
-    //      the last warp the odd ones (a single thread cannot issue tcgen05.mma
-    //      fast enough for both). Per tile j of its parity: S_{j+2} into the score
-    //      buffer of tile j as soon as the group has read S_j out (s_free), then
-    //      PV_j once P_j is written; the scores of a group's next tile are
+    // ---- MMA issuers, one warp per softmax group: warp 1 takes the even tiles
+    //      of every item, the last warp the odd ones (a single thread cannot
+    //      issue tcgen05.mma fast enough for both). Per tile j of its parity:
+    //      S_{j+2} into the group's score buffer as soon as the group has read
+    //      S_j out (s_free), then PV_j once P_j is written; the scores of a
+    //      group's next tile, the first tile of the next item included, are
     //      computed while it still works on the current one. The whole warp walks
     //      the loop (waits, descriptor arithmetic: warp-uniform, so it stays in
     //      uniform registers); only the tcgen05 instructions themselves sit
@@ -350,274 +378,280 @@ __device__ __forceinline__ void attention_body(int64_t seq, float *__restrict__ 
       const int g = warp == 1 ? 0 : 1;
       const bool leader = khd::elect_one();
       constexpr uint32_t idesc = khd::umma_idesc_f16(kBQ, kBKV); // M128 N64 K16 for both products
-      // a tile row is one 128-byte swizzle row (64 fp16); a k-step of 16 fp16 moves 32 bytes (2 encoded)
-      // Q is read from tensor memory (the even group copies it there once): a
-      // k-step of 16 fp16 is 8 columns. Only K and V^T are fetched from shared
-      // memory, whose bandwidth is what the three products of a tile compete for.
-      const uint32_t q_hi = tmem_base + kColQHi, q_lo = tmem_base + kColQLo;
       constexpr uint64_t kKVTileStep = kKVTileBytes >> 4;
       const uint32_t col_s = tmem_base + (g ? kColS1 : kColS0), col_p = tmem_base + (g ? kColP1 : kColP0),
                      col_pv = tmem_base + (g ? kColPV1 : kColPV0);
-      // S_t = Q K_t^T into this group's score buffer, from ring slot t % kStages
-      auto issue_s = [&](int t) -> bool {
-        const int slot = t % kStages;
-        bool ready = khd::mbar_wait(bar_k_full + 8 * slot, static_cast<uint32_t>((t / kStages) & 1), &s_abort,
-                                    status, khd::kStatusTmaWaitTimeout, static_cast<uint32_t>(t));
-        if (t >= 2) // the group holds S_{t-2} in registers
-          ready = ready && khd::mbar_wait(bar_s_free + 8 * g, static_cast<uint32_t>(((t - 2) >> 1) & 1), &s_abort,
-                                          status, khd::kStatusEpilogueWaitTimeout, 3000u + static_cast<uint32_t>(t));
-        ready = __all_sync(0xffffffffu, ready);
-        if (!ready) return false;
-        khd::tc_fence_after_sync();
-        const uint64_t dk_hi = khd::umma_desc_k128(smem_k + slot * kHalfStageBytes);
-        const uint64_t dk_lo = dk_hi + kKVTileStep;
-        if (leader) {
-#pragma unroll
-          for (int kk = 0; kk < kHeadDim / 16; ++kk) {
-            const uint64_t off = static_cast<uint64_t>(kk * 2);
-            umma_f16_ts(col_s, q_lo + kk * 8, dk_hi + off, idesc, kk != 0 ? 1u : 0u);
-            umma_f16_ts(col_s, q_hi + kk * 8, dk_lo + off, idesc, 1u);
-            umma_f16_ts(col_s, q_hi + kk * 8, dk_hi + off, idesc, 1u);
-          }
-          khd::umma_commit(bar_s_full + 8 * g);     // scores ready for the softmax threads
-          khd::umma_commit(bar_k_empty + 8 * slot); // and this K slot may be refilled
-        }
-        __syncwarp();
-        return true;
-      };
-      bool ok = khd::mbar_wait(bar_q_ready, 0u, &s_abort, status, khd::kStatusEpilogueWaitTimeout, 1000u);
-      ok = __all_sync(0xffffffffu, ok);
-      if (ok) khd::tc_fence_after_sync();
-      if (g < num_kv) ok = ok && issue_s(g);
-      for (int j = g; j < num_kv && ok; j += 2) {
-        const int slot = j % kStages;
-        if (j + 2 < num_kv && !issue_s(j + 2)) break;
-        ok = khd::mbar_wait(bar_p_ready + 8 * g, static_cast<uint32_t>((j >> 1) & 1), &s_abort, status,
-                            khd::kStatusEpilogueWaitTimeout, static_cast<uint32_t>(j));
-        ok = ok && khd::mbar_wait(bar_v_full + 8 * slot, static_cast<uint32_t>((j / kStages) & 1), &s_abort, status,
-                                  khd::kStatusTmaWaitTimeout, 2000u + static_cast<uint32_t>(j));
+      uint32_t tile_base = 0;  // tiles of the items before this one
+      uint32_t s_count = 0;    // score products this warp has issued
+      uint32_t pv_count = 0;   // PV products this warp has issued
+      bool ok = true;
+      int n = 0;
+      for (int64_t w = blockIdx.x; w < items && ok; w += gridDim.x, ++n, tile_base += static_cast<uint32_t>(num_kv)) {
+        const int qb = n & 1;
+        ok = khd::mbar_wait(bar_q_full + 8 * qb, static_cast<uint32_t>((n >> 1) & 1), &s_abort, status,
+                            khd::kStatusTmaWaitTimeout, 1000u);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
         khd::tc_fence_after_sync();
-        // PV_j = P_j V_j: A = the group's P buffer (tensor memory), B = V^T tile, D = its PV buffer
-        const uint64_t dv_hi = khd::umma_desc_k128(smem_v + slot * kHalfStageBytes);
-        const uint64_t dv_lo = dv_hi + kKVTileStep;
-        if (leader) {
+        // a tile row is one 128-byte swizzle row (64 fp16); a k-step of 16 fp16 moves 32 bytes (2 encoded)
+        const uint64_t dq_hi = khd::umma_desc_k128(smem_q + qb * kQBytes);
+        const uint64_t dq_lo = khd::umma_desc_k128(smem_q + qb * kQBytes + kQTileBytes);
+        // S_t = Q K_t^T into this group's score buffer; tile t of the item sits in ring slot (tile_base + t) % kStages
+        auto issue_s = [&](int t) -> bool {
+          const uint32_t tile = tile_base + static_cast<uint32_t>(t);
+          const int slot = static_cast<int>(tile % kStages);
+          bool ready = khd::mbar_wait(bar_k_full + 8 * slot, (tile / kStages) & 1u, &s_abort, status,
+                                      khd::kStatusTmaWaitTimeout, static_cast<uint32_t>(t));
+          if (s_count >= 1) // the group holds the scores of its previous tile in registers
+            ready = ready && khd::mbar_wait(bar_s_free + 8 * g, (s_count - 1) & 1u, &s_abort, status,
+                                            khd::kStatusEpilogueWaitTimeout, 3000u + static_cast<uint32_t>(t));
+          ready = __all_sync(0xffffffffu, ready);
+          if (!ready) return false;
+          khd::tc_fence_after_sync();
+          const uint64_t dk_hi = khd::umma_desc_k128(smem_k + slot * kHalfStageBytes);
+          const uint64_t dk_lo = dk_hi + kKVTileStep;
+          if (leader) {
 #pragma unroll
-          for (int kk = 0; kk < kBKV / 16; ++kk) { // 16 keys = 8 packed columns of P
-            const uint64_t voff = static_cast<uint64_t>(kk * 2);
-            umma_f16_ts(col_pv, col_p + 32 + kk * 8, dv_hi + voff, idesc, kk != 0 ? 1u : 0u);
-            umma_f16_ts(col_pv, col_p + kk * 8, dv_lo + voff, idesc, 1u);
-            umma_f16_ts(col_pv, col_p + kk * 8, dv_hi + voff, idesc, 1u);
+            for (int kk = 0; kk < kHeadDim / 16; ++kk) {
+              const uint64_t off = static_cast<uint64_t>(kk * 2);
+              khd::umma_f16_ss(col_s, dq_lo + off, dk_hi + off, idesc, kk != 0 ? 1u : 0u);
+              khd::umma_f16_ss(col_s, dq_hi + off, dk_lo + off, idesc, 1u);
+              khd::umma_f16_ss(col_s, dq_hi + off, dk_hi + off, idesc, 1u);
+            }
+            khd::umma_commit(bar_s_full + 8 * g);     // scores ready for the softmax threads
+            khd::umma_commit(bar_k_empty + 8 * slot); // and this K slot may be refilled
+            if (t + 2 >= num_kv) khd::umma_commit(bar_q_empty + 8 * qb); // this warp's last use of the Q tile
           }
-          khd::umma_commit(bar_pv_full + 8 * g);
-          khd::umma_commit(bar_v_empty + 8 * slot);
+          __syncwarp();
+          ++s_count;
+          return true;
+        };
+        if (g < num_kv) {
+          ok = issue_s(g);
+        } else if (leader) {
+          khd::mbar_arrive(bar_q_empty + 8 * qb); // no tile of this parity: nothing of Q is used here
         }
-        __syncwarp();
+        for (int j = g; j < num_kv && ok; j += 2) {
+          const uint32_t tile = tile_base + static_cast<uint32_t>(j);
+          const int slot = static_cast<int>(tile % kStages);
+          if (j + 2 < num_kv && !issue_s(j + 2)) {
+            ok = false;
+            break;
+          }
+          ok = khd::mbar_wait(bar_p_ready + 8 * g, pv_count & 1u, &s_abort, status,
+                              khd::kStatusEpilogueWaitTimeout, static_cast<uint32_t>(j));
+          ok = ok && khd::mbar_wait(bar_v_full + 8 * slot, (tile / kStages) & 1u, &s_abort, status,
+                                    khd::kStatusTmaWaitTimeout, 2000u + static_cast<uint32_t>(j));
+          ok = __all_sync(0xffffffffu, ok);
+          if (!ok) break;
+          khd::tc_fence_after_sync();
+          // PV_j = P_j V_j: A = the group's P buffer (tensor memory), B = V^T tile, D = its PV buffer
+          const uint64_t dv_hi = khd::umma_desc_k128(smem_v + slot * kHalfStageBytes);
+          const uint64_t dv_lo = dv_hi + kKVTileStep;
+          if (leader) {
+#pragma unroll
+            for (int kk = 0; kk < kBKV / 16; ++kk) { // 16 keys = 8 packed columns of P
+              const uint64_t voff = static_cast<uint64_t>(kk * 2);
+              umma_f16_ts(col_pv, col_p + 32 + kk * 8, dv_hi + voff, idesc, kk != 0 ? 1u : 0u);
+              umma_f16_ts(col_pv, col_p + kk * 8, dv_lo + voff, idesc, 1u);
+              umma_f16_ts(col_pv, col_p + kk * 8, dv_hi + voff, idesc, 1u);
+            }
+            khd::umma_commit(bar_pv_full + 8 * g);
+            khd::umma_commit(bar_v_empty + 8 * slot);
+          }
+          __syncwarp();
+          ++pv_count;
+        }
       }
     }
   } else {
     // ---- softmax + output: two groups of 128 threads, one thread per query row
-    //      in each. Group g (warps 2-5 / 6-9) takes the tiles of parity g with its
-    //      own running max, sum and output row; the groups work on neighbouring
-    //      tiles at the same time and are merged once at the end. A warp may only
-    //      touch tensor-memory lanes 32*(warp%4).., which both groups cover. -----------
+    //      in each. Group g (warps 2-5 / 6-9) takes the tiles of parity g of every
+    //      item with its own running max, sum and output row; the groups work on
+    //      neighbouring tiles at the same time. At the end of an item the group
+    //      that did not have the last tile hands its (max, sum, row) over through
+    //      shared memory and goes on to the next item; the group with the last
+    //      tile combines the two and writes the rows out. A warp may only touch
+    //      tensor-memory lanes 32*(warp%4).., which both groups cover. -----------------
     const int ew = warp - 2;
     const int quad = warp & 3;
     const int g = ew >> 2;
     const uint32_t lane_base = static_cast<uint32_t>(quad * 32) << 16;
     const int row_in_tile = quad * 32 + lane;
     const uint32_t col_s = g ? kColS1 : kColS0, col_p = g ? kColP1 : kColP0, col_pv = g ? kColPV1 : kColPV0;
-    float acc[kHeadDim]; // running output of this group's tiles, normalised to its max
-#pragma unroll
-    for (int i = 0; i < kHeadDim; ++i) acc[i] = 0.f;
-    float m = -INFINITY, l = 0.f;
-    bool ok = true;
-    // Exponents of the 64-row tiles: shifts[(t * slices + slice) * tiles + tile], t = 0, 1, 2 for Q, K, V.
-    // The running max `m` is kept in exp2 units, i.e. true score * log2(e) / sqrt(64).
-    const int64_t slices = gridDim.x / q_tiles;
-    const int *k_shifts = shifts + (slices + bh) * num_kv, *v_shifts = shifts + (2 * slices + bh) * num_kv;
-    const int row_q = q0 + row_in_tile;
-    const int shift_q = __ldg(shifts + bh * num_kv + (row_q < seq ? row_q >> 6 : 0));
+    const int merger = (num_kv - 1) & 1; // the group that owns the last tile of an item
+    // the handed-over row: element i of row r at r * 64 + (i ^ (r % 32)), conflict-free for a warp
+    float *scratch_row = reinterpret_cast<float *>(smem_raw + (smem_scratch - khd::smem_u32(smem_raw))) +
+                         row_in_tile * kHeadDim;
     constexpr float kLog2eOverSqrtD = 1.4426950408889634f * 0.125f;
-    float v_factor_prev = 0.f; // 2^-(exponent of the V tile) of this group's previous product
-    // the exponents of this group's next tile are fetched one tile ahead
-    int shift_k_next = g < num_kv ? __ldg(k_shifts + g) : 0, shift_v_next = g < num_kv ? __ldg(v_shifts + g) : 0;
+    uint32_t tiles_done = 0; // tiles this group has been through, over all items
+    bool ok = true;
+    int n = 0;
+    for (int64_t w = blockIdx.x; w < items && ok; w += gridDim.x, ++n) {
+      const int64_t bh = w / q_tiles;
+      const int q0 = static_cast<int>((w - bh * q_tiles) * kBQ);
+      float acc[kHeadDim]; // running output of this group's tiles, normalised to its max
+#pragma unroll
+      for (int i = 0; i < kHeadDim; ++i) acc[i] = 0.f;
+      float m = -INFINITY, l = 0.f;
+      // Exponents of the 64-row tiles: shifts[(t * slices + slice) * tiles + tile], t = 0, 1, 2 for Q, K, V.
+      // The running max `m` is kept in exp2 units, i.e. true score * log2(e) / sqrt(64).
+      const int *k_shifts = shifts + (slices + bh) * num_kv, *v_shifts = shifts + (2 * slices + bh) * num_kv;
+      const int row_q = q0 + row_in_tile;
+      const int shift_q = __ldg(shifts + bh * num_kv + (row_q < seq ? row_q >> 6 : 0));
+      float v_factor_prev = 0.f; // 2^-(exponent of the V tile) of this group's previous product
+      // the exponents of this group's next tile are fetched one tile ahead
+      int shift_k_next = g < num_kv ? __ldg(k_shifts + g) : 0, shift_v_next = g < num_kv ? __ldg(v_shifts + g) : 0;
+      bool first = true; // no product of this item to fold in yet
 
-    if (g == 0) {
-      // Q tile -> tensor memory, one row per thread: undo the 128-byte swizzle of
-      // the TMA tile (16-byte chunk c of row r sits at chunk c ^ (r % 8)); a
-      // 32-bit column holds two neighbouring fp16, the even one in the low half.
-      ok = khd::mbar_wait(bar_q, 0u, &s_abort, status, khd::kStatusTmaWaitTimeout, 1001u);
-      if (ok) {
-        const uint8_t *q_tiles_smem = smem_raw + (smem_q - khd::smem_u32(smem_raw));
+      for (int j = g; j < num_kv && ok; j += 2) {
+        const uint32_t phase = tiles_done & 1u;
+        const int shift_k = shift_k_next, shift_v = shift_v_next;
+        if (j + 2 < num_kv) {
+          shift_k_next = __ldg(k_shifts + j + 2);
+          shift_v_next = __ldg(v_shifts + j + 2);
+        }
+        ok = khd::mbar_wait(bar_s_full + 8 * g, phase, &s_abort, status, khd::kStatusMmaWaitTimeout,
+                            static_cast<uint32_t>(j));
+        if (!ok) break;
+        khd::tc_fence_after_sync();
+        uint32_t sv[kBKV];
+        khd::tmem_ld_32x32(tmem_base + lane_base + col_s, *reinterpret_cast<uint32_t(*)[32]>(&sv[0]));
+        khd::tmem_ld_32x32(tmem_base + lane_base + col_s + 32, *reinterpret_cast<uint32_t(*)[32]>(&sv[32]));
+        khd::tmem_ld_wait();
+        khd::tc_fence_before_sync();
+        khd::mbar_arrive(bar_s_free + 8 * g); // the score buffer may take S_{j+2}
+        // this tile's scores carry 2^(shift_q + shift_k): one positive factor brings them to exp2 units
+        const float f = khd::scale_pow2(kLog2eOverSqrtD, -(shift_q + shift_k));
+        float mx = -INFINITY;
 #pragma unroll
-        for (int part = 0; part < 2; ++part) { // hi, lo
-          const uint8_t *row = q_tiles_smem + part * kQTileBytes + row_in_tile * kRowBytes;
+        for (int i = 0; i < kBKV; ++i) mx = fmaxf(mx, __uint_as_float(sv[i]));
+        const float m_new = fmaxf(m, mx * f);
+        const float alpha = fast_exp2(m - m_new); // m = -inf on the first tile gives 0
+        // P is produced as P * 2^14 straight from the exponent (its split wants that
+        // range); the row sum `l` and the output row are kept in the same units.
+        const float offset = static_cast<float>(kPShift) - m_new;
+        float sum = 0.f;
 #pragma unroll
-          for (int h = 0; h < 2; ++h) {
-            uint32_t w[16];
+        for (int i = 0; i < kBKV; ++i) {
+          const float p = fast_exp2(fmaf(__uint_as_float(sv[i]), f, offset));
+          sv[i] = __float_as_uint(p);
+          sum += p;
+        }
+        l = l * alpha + sum;
+        m = m_new;
+
+        // The group's previous product PV_{j-2} read P buffer g and wrote PV buffer
+        // g: fold it in (it is normalised to the previous max), which also frees
+        // both buffers, then move the running output to the new max.
+        if (!first) {
+          ok = khd::mbar_wait(bar_pv_full + 8 * g, phase ^ 1u, &s_abort, status,
+                              khd::kStatusMmaWaitTimeout, 2000u + static_cast<uint32_t>(j));
+          if (!ok) break;
+          khd::tc_fence_after_sync();
 #pragma unroll
-            for (int c = 0; c < 4; ++c) {
-              const uint4 v = *reinterpret_cast<const uint4 *>(row + (((4 * h + c) ^ (row_in_tile & 7)) << 4));
-              w[4 * c + 0] = v.x; w[4 * c + 1] = v.y; w[4 * c + 2] = v.z; w[4 * c + 3] = v.w;
-            }
-            tmem_st_32x16(tmem_base + lane_base + (part ? kColQLo : kColQHi) + 16 * h, w);
+          for (int h = 0; h < 4; ++h) {
+            uint32_t t[16];
+            tmem_ld_32x16(tmem_base + lane_base + col_pv + 16 * h, t);
+            khd::tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 16; ++i)
+              acc[16 * h + i] = fmaf(__uint_as_float(t[i]), v_factor_prev, acc[16 * h + i]) * alpha;
           }
+        }
+        v_factor_prev = khd::scale_pow2(1.0f, -shift_v); // V was split as V * 2^shift
+        // P (times 2^14) -> tensor memory as fp16 hi / lo, two keys per 32-bit column
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          uint32_t hi[16], lo[16];
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            // hi = the top 11 significant bits (exact in fp16), lo = fp16 of the rest
+            const float p0 = __uint_as_float(sv[32 * h + 2 * i]);
+            const float p1 = __uint_as_float(sv[32 * h + 2 * i + 1]);
+            const float h0 = __uint_as_float(sv[32 * h + 2 * i] & 0xFFFFE000u);
+            const float h1 = __uint_as_float(sv[32 * h + 2 * i + 1] & 0xFFFFE000u);
+            hi[i] = half2_bits(__floats2half2_rn(h0, h1));
+            lo[i] = half2_bits(__floats2half2_rn(p0 - h0, p1 - h1));
+          }
+          tmem_st_32x16(tmem_base + lane_base + col_p + 16 * h, hi);
+          tmem_st_32x16(tmem_base + lane_base + col_p + 32 + 16 * h, lo);
         }
         tmem_st_wait();
         khd::tc_fence_before_sync();
+        khd::mbar_arrive(bar_p_ready + 8 * g);
+        ++tiles_done;
+        first = false;
       }
-      khd::mbar_arrive(bar_q_ready);
-    }
-    for (int j = g; j < num_kv && ok; j += 2) {
-      const uint32_t phase = static_cast<uint32_t>((j >> 1) & 1);
-      const int shift_k = shift_k_next, shift_v = shift_v_next;
-      if (j + 2 < num_kv) {
-        shift_k_next = __ldg(k_shifts + j + 2);
-        shift_v_next = __ldg(v_shifts + j + 2);
+      // this group's last product of the item
+      if (ok && !first) {
+        ok = khd::mbar_wait(bar_pv_full + 8 * g, (tiles_done - 1) & 1u, &s_abort, status,
+                            khd::kStatusMmaWaitTimeout, 3000u);
+        if (ok) {
+          khd::tc_fence_after_sync();
+#pragma unroll
+          for (int h = 0; h < 4; ++h) {
+            uint32_t t[16];
+            tmem_ld_32x16(tmem_base + lane_base + col_pv + 16 * h, t);
+            khd::tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 16; ++i) acc[16 * h + i] = fmaf(__uint_as_float(t[i]), v_factor_prev, acc[16 * h + i]);
+          }
+        }
       }
-      ok = khd::mbar_wait(bar_s_full + 8 * g, phase, &s_abort, status, khd::kStatusMmaWaitTimeout,
-                          static_cast<uint32_t>(j));
       if (!ok) break;
-      khd::tc_fence_after_sync();
-      uint32_t sv[kBKV];
-      khd::tmem_ld_32x32(tmem_base + lane_base + col_s, *reinterpret_cast<uint32_t(*)[32]>(&sv[0]));
-      khd::tmem_ld_32x32(tmem_base + lane_base + col_s + 32, *reinterpret_cast<uint32_t(*)[32]>(&sv[32]));
-      khd::tmem_ld_wait();
-      khd::tc_fence_before_sync();
-      khd::mbar_arrive(bar_s_free + 8 * g); // the score buffer may take S_{j+2}
-      // this tile's scores carry 2^(shift_q + shift_k): one positive factor brings them to exp2 units
-      const float f = khd::scale_pow2(kLog2eOverSqrtD, -(shift_q + shift_k));
-      float mx = -INFINITY;
-#pragma unroll
-      for (int i = 0; i < kBKV; ++i) mx = fmaxf(mx, __uint_as_float(sv[i]));
-      const float m_new = fmaxf(m, mx * f);
-      const float alpha = fast_exp2(m - m_new); // m = -inf on the first tile gives 0
-      // P is produced as P * 2^14 straight from the exponent (its split wants that
-      // range); the row sum `l` and the output row are kept in the same units.
-      const float offset = static_cast<float>(kPShift) - m_new;
-      float sum = 0.f;
-#pragma unroll
-      for (int i = 0; i < kBKV; ++i) {
-        const float p = fast_exp2(fmaf(__uint_as_float(sv[i]), f, offset));
-        sv[i] = __float_as_uint(p);
-        sum += p;
-      }
-      l = l * alpha + sum;
-      m = m_new;
-
-      // The group's previous product PV_{j-2} read P buffer g and wrote PV buffer
-      // g: fold it in (it is normalised to the previous max), which also frees
-      // both buffers, then move the running output to the new max.
-      if (j >= 2) {
-        ok = khd::mbar_wait(bar_pv_full + 8 * g, phase ^ 1u, &s_abort, status,
-                            khd::kStatusMmaWaitTimeout, 2000u + static_cast<uint32_t>(j));
+      if (g != merger) {
+        // hand the row over (once the previous item's has been read) and go on
+        if (n > 0)
+          ok = khd::mbar_wait(bar_scratch_free, static_cast<uint32_t>((n - 1) & 1), &s_abort, status,
+                              khd::kStatusEpilogueWaitTimeout, 5000u);
         if (!ok) break;
-        khd::tc_fence_after_sync();
+        s_merge_m[row_in_tile] = m;
+        s_merge_l[row_in_tile] = l;
 #pragma unroll
-        for (int h = 0; h < 4; ++h) {
-          uint32_t t[16];
-          tmem_ld_32x16(tmem_base + lane_base + col_pv + 16 * h, t);
-          khd::tmem_ld_wait();
+        for (int i = 0; i < kHeadDim; ++i) scratch_row[i ^ lane] = acc[i];
+        khd::mbar_arrive(bar_merge_ready);
+      } else {
+        ok = khd::mbar_wait(bar_merge_ready, static_cast<uint32_t>(n & 1), &s_abort, status,
+                            khd::kStatusEpilogueWaitTimeout, 5001u);
+        if (!ok) break;
+        const float m1 = s_merge_m[row_in_tile], l1 = s_merge_l[row_in_tile];
+        const float mt = fmaxf(m, m1);
+        const float w0 = fast_exp2(m - mt), w1 = fast_exp2(m1 - mt);
+        const float inv = 1.0f / (l * w0 + l1 * w1);
+        const int64_t row = static_cast<int64_t>(q0) + row_in_tile;
+        float *orow = out + (bh * seq + row) * kHeadDim;
+        if (row < seq) {
 #pragma unroll
-          for (int i = 0; i < 16; ++i)
-            acc[16 * h + i] = fmaf(__uint_as_float(t[i]), v_factor_prev, acc[16 * h + i]) * alpha;
+          for (int i = 0; i < kHeadDim / 4; ++i)
+            __stcs(reinterpret_cast<float4 *>(orow) + i,
+                   make_float4((acc[4 * i + 0] * w0 + scratch_row[(4 * i + 0) ^ lane] * w1) * inv,
+                               (acc[4 * i + 1] * w0 + scratch_row[(4 * i + 1) ^ lane] * w1) * inv,
+                               (acc[4 * i + 2] * w0 + scratch_row[(4 * i + 2) ^ lane] * w1) * inv,
+                               (acc[4 * i + 3] * w0 + scratch_row[(4 * i + 3) ^ lane] * w1) * inv));
         }
-      }
-      v_factor_prev = khd::scale_pow2(1.0f, -shift_v); // V was split as V * 2^shift
-      // P (times 2^14) -> tensor memory as fp16 hi / lo, two keys per 32-bit column
-#pragma unroll
-      for (int h = 0; h < 2; ++h) {
-        uint32_t hi[16], lo[16];
-#pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          // hi = the top 11 significant bits (exact in fp16), lo = fp16 of the rest
-          const float p0 = __uint_as_float(sv[32 * h + 2 * i]);
-          const float p1 = __uint_as_float(sv[32 * h + 2 * i + 1]);
-          const float h0 = __uint_as_float(sv[32 * h + 2 * i] & 0xFFFFE000u);
-          const float h1 = __uint_as_float(sv[32 * h + 2 * i + 1] & 0xFFFFE000u);
-          hi[i] = half2_bits(__floats2half2_rn(h0, h1));
-          lo[i] = half2_bits(__floats2half2_rn(p0 - h0, p1 - h1));
-        }
-        tmem_st_32x16(tmem_base + lane_base + col_p + 16 * h, hi);
-        tmem_st_32x16(tmem_base + lane_base + col_p + 32 + 16 * h, lo);
-      }
-      tmem_st_wait();
-      khd::tc_fence_before_sync();
-      khd::mbar_arrive(bar_p_ready + 8 * g);
-    }
-    // this group's last product
-    const int my_tiles = (num_kv - g + 1) / 2;
-    if (ok && my_tiles > 0) {
-      const int jl = g + 2 * (my_tiles - 1);
-      ok = khd::mbar_wait(bar_pv_full + 8 * g, static_cast<uint32_t>((jl >> 1) & 1), &s_abort, status,
-                          khd::kStatusMmaWaitTimeout, 3000u);
-      if (ok) {
-        khd::tc_fence_after_sync();
-#pragma unroll
-        for (int h = 0; h < 4; ++h) {
-          uint32_t t[16];
-          tmem_ld_32x16(tmem_base + lane_base + col_pv + 16 * h, t);
-          khd::tmem_ld_wait();
-#pragma unroll
-          for (int i = 0; i < 16; ++i) acc[16 * h + i] = fmaf(__uint_as_float(t[i]), v_factor_prev, acc[16 * h + i]);
-        }
-      }
-    }
-    // Merge: group 1 hands (max, sum, output row) to group 0 through the Q
-    // buffer, which is free once the very last product of the CTA has run.
-    if (ok && num_kv > 0) {
-      const int jt = num_kv - 1;
-      ok = khd::mbar_wait(bar_pv_full + 8 * (jt & 1), static_cast<uint32_t>((jt >> 1) & 1), &s_abort,
-                          status, khd::kStatusMmaWaitTimeout, 3001u);
-    }
-    float *merge = reinterpret_cast<float *>(smem_raw + (smem_q - khd::smem_u32(smem_raw))) +
-                   row_in_tile * (kHeadDim + 3);
-    if (ok && g == 1) {
-      merge[0] = m;
-      merge[1] = l;
-#pragma unroll
-      for (int i = 0; i < kHeadDim; ++i) merge[2 + i] = acc[i];
-    }
-    khd::mbar_arrive(bar_exchange);
-    ok = ok && khd::mbar_wait(bar_exchange, 0u, &s_abort, status, khd::kStatusEpilogueWaitTimeout, 5000u);
-    if (ok && g == 0 && num_kv > 0) {
-      const float m1 = merge[0], l1 = merge[1];
-      const float mt = fmaxf(m, m1);
-      const float w0 = fast_exp2(m - mt), w1 = fast_exp2(m1 - mt);
-      const float inv = 1.0f / (l * w0 + l1 * w1);
-      const int64_t row = static_cast<int64_t>(q0) + row_in_tile;
-      float *orow = out + (bh * seq + row) * kHeadDim;
-      if (row < seq) {
-#pragma unroll
-        for (int i = 0; i < kHeadDim / 4; ++i)
-          __stcs(reinterpret_cast<float4 *>(orow) + i,
-                 make_float4((acc[4 * i + 0] * w0 + merge[2 + 4 * i + 0] * w1) * inv,
-                             (acc[4 * i + 1] * w0 + merge[2 + 4 * i + 1] * w1) * inv,
-                             (acc[4 * i + 2] * w0 + merge[2 + 4 * i + 2] * w1) * inv,
-                             (acc[4 * i + 3] * w0 + merge[2 + 4 * i + 3] * w1) * inv));
-      }
-    }
-    if (kGather) {
-      // the tile is complete in this GPU's replica: make the rows visible to the whole
-      // group of softmax threads, then copy it out
-      __threadfence_block();
-      khd::mbar_arrive(bar_exchange);
-      ok = ok && khd::mbar_wait(bar_exchange, 1u, &s_abort, status, khd::kStatusEpilogueWaitTimeout, 5001u);
-      const int64_t first_row = bh * seq + q0;
-      const int64_t rows_here = (seq - q0 < kBQ) ? (seq - q0) : kBQ;
-      const float4 *src = reinterpret_cast<const float4 *>(out + first_row * kHeadDim);
-      const int t = threadIdx.x - 64; // 0..255
-      if (ok) {
-        for (int64_t i = t; i < rows_here * (kHeadDim / 4); i += kSoftmaxThreads) {
-          const float4 v = __ldcg(src + i);
-          const int64_t off = first_row * kHeadDim + i * 4;
-          if (targets->multicast != nullptr) {
-            multicast_store_float4(targets->multicast + off, v);
-          } else {
-            for (int d = 0; d < targets->count; ++d)
-              if (d != targets->self) *reinterpret_cast<float4 *>(targets->peer[d] + off) = v;
+        khd::mbar_arrive(bar_scratch_free);
+        if (kGather) {
+          // the tile is complete in this GPU's replica: make the rows visible to the
+          // whole group, then copy the tile out
+          __threadfence_block();
+          khd::mbar_arrive(bar_gather);
+          ok = khd::mbar_wait(bar_gather, static_cast<uint32_t>(n & 1), &s_abort, status,
+                              khd::kStatusEpilogueWaitTimeout, 5002u);
+          if (!ok) break;
+          const int64_t first_row = bh * seq + q0;
+          const int64_t rows_here = (seq - q0 < kBQ) ? (seq - q0) : kBQ;
+          const float4 *src = reinterpret_cast<const float4 *>(out + first_row * kHeadDim);
+          const int t = (ew & 3) * 32 + lane; // 0..127 within the group
+          for (int64_t i = t; i < rows_here * (kHeadDim / 4); i += kBQ) {
+            const float4 v = __ldcg(src + i);
+            const int64_t off = first_row * kHeadDim + i * 4;
+            if (targets->multicast != nullptr) {
+              multicast_store_float4(targets->multicast + off, v);
+            } else {
+              for (int d = 0; d < targets->count; ++d)
+                if (d != targets->self) *reinterpret_cast<float4 *>(targets->peer[d] + off) = v;
+            }
           }
         }
       }
@@ -643,7 +677,7 @@ attention(KH_MEMREF4(const float, q), KH_MEMREF4(const float, k), KH_MEMREF4(con
           const __grid_constant__ khd::TensorMap tm_q_lo, const __grid_constant__ khd::TensorMap tm_k_hi,
           const __grid_constant__ khd::TensorMap tm_k_lo, const __grid_constant__ khd::TensorMap tm_vt_hi,
           const __grid_constant__ khd::TensorMap tm_vt_lo, const int *__restrict__ shifts, uint32_t *status) {
-  (void)q_alloc; (void)q_ptr; (void)q_off; (void)q_size0; (void)q_size1; (void)q_size3; (void)q_stride0;
+  (void)q_alloc; (void)q_ptr; (void)q_off; (void)q_size3; (void)q_stride0;
   (void)q_stride1; (void)q_stride2; (void)q_stride3;
   (void)k_alloc; (void)k_ptr; (void)k_off; (void)k_size0; (void)k_size1; (void)k_size2; (void)k_size3;
   (void)k_stride0; (void)k_stride1; (void)k_stride2; (void)k_stride3;
@@ -651,7 +685,7 @@ attention(KH_MEMREF4(const float, q), KH_MEMREF4(const float, k), KH_MEMREF4(con
   (void)v_stride0; (void)v_stride1; (void)v_stride2; (void)v_stride3;
   (void)o_size0; (void)o_size1; (void)o_size2; (void)o_size3; (void)o_stride0; (void)o_stride1;
   (void)o_stride2; (void)o_stride3; (void)o_alloc;
-  attention_body<false>(q_size2, KH_DATA(o), tm_q_hi, tm_q_lo, tm_k_hi, tm_k_lo, tm_vt_hi, tm_vt_lo, shifts, status,
+  attention_body<false>(q_size0 * q_size1, q_size2, KH_DATA(o), tm_q_hi, tm_q_lo, tm_k_hi, tm_k_lo, tm_vt_hi, tm_vt_lo, shifts, status,
                         nullptr);
 }
 
@@ -667,7 +701,7 @@ attention_allgather(KH_MEMREF4(const float, q), KH_MEMREF4(const float, k), KH_M
                     const __grid_constant__ khd::TensorMap tm_k_lo, const __grid_constant__ khd::TensorMap tm_vt_hi,
                     const __grid_constant__ khd::TensorMap tm_vt_lo, const int *__restrict__ shifts,
                     uint32_t *status, const __grid_constant__ GatherOut targets) {
-  (void)q_alloc; (void)q_ptr; (void)q_off; (void)q_size0; (void)q_size1; (void)q_size3; (void)q_stride0;
+  (void)q_alloc; (void)q_ptr; (void)q_off; (void)q_size3; (void)q_stride0;
   (void)q_stride1; (void)q_stride2; (void)q_stride3;
   (void)k_alloc; (void)k_ptr; (void)k_off; (void)k_size0; (void)k_size1; (void)k_size2; (void)k_size3;
   (void)k_stride0; (void)k_stride1; (void)k_stride2; (void)k_stride3;
@@ -675,6 +709,6 @@ attention_allgather(KH_MEMREF4(const float, q), KH_MEMREF4(const float, k), KH_M
   (void)v_stride0; (void)v_stride1; (void)v_stride2; (void)v_stride3;
   (void)o_size0; (void)o_size1; (void)o_size2; (void)o_size3; (void)o_stride0; (void)o_stride1;
   (void)o_stride2; (void)o_stride3; (void)o_alloc;
-  attention_body<true>(q_size2, KH_DATA(o), tm_q_hi, tm_q_lo, tm_k_hi, tm_k_lo, tm_vt_hi, tm_vt_lo, shifts, status,
+  attention_body<true>(q_size0 * q_size1, q_size2, KH_DATA(o), tm_q_hi, tm_q_lo, tm_k_hi, tm_k_lo, tm_vt_hi, tm_vt_lo, shifts, status,
                        &targets);
 }

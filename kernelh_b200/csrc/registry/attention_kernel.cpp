@@ -11,8 +11,9 @@ namespace kh {
 namespace {
 
 constexpr int64_t kHeadDim = 64, kBQ = 128, kBKV = 64;
-// Q hi/lo (32 KiB) + four stages each of K and V^T hi/lo (16 KiB per stage) + alignment slack
-constexpr size_t kAttnSmem = 32 * 1024 + 2 * 4 * 16 * 1024 + 1024;
+// two Q tiles hi/lo (32 KiB each) + three stages each of K and V^T hi/lo (16 KiB per stage) +
+// the 32 KiB row hand-over between the softmax groups + alignment slack
+constexpr size_t kAttnSmem = 2 * 32 * 1024 + 2 * 4 * 16 * 1024 + 32 * 1024 + 1024;
 
 KernelPlan plan_attention(const ShapeMap &shape, const DeviceLimits &l) {
   for (const char *key : {"batch", "heads", "seq", "head_dim"})
@@ -48,7 +49,8 @@ KernelPlan plan_attention(const ShapeMap &shape, const DeviceLimits &l) {
   LaunchStep main;
   main.entry = "attention";
   main.block = {352, 1, 1}; // producer, two MMA issuers, eight softmax warps
-  main.grid = {static_cast<unsigned>(b * h * ((s + kBQ - 1) / kBQ)), 1, 1};
+  // persistent: a CTA per SM walks the (slice, 128-query tile) work items
+  main.grid = {static_cast<unsigned>(std::min<int64_t>(b * h * ((s + kBQ - 1) / kBQ), sms)), 1, 1};
   main.dynamic_smem = kAttnSmem;
   main.param_count = 44 + 6 + 2;
   main.tmem_columns = 512;
