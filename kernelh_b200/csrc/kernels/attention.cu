@@ -480,9 +480,11 @@ __device__ __forceinline__ void attention_body(int64_t slices, int64_t seq, floa
     const int row_in_tile = quad * 32 + lane;
     const uint32_t col_s = g ? kColS1 : kColS0, col_p = g ? kColP1 : kColP0, col_pv = g ? kColPV1 : kColPV0;
     const int merger = (num_kv - 1) & 1; // the group that owns the last tile of an item
-    // the handed-over row: element i of row r at r * 64 + (i ^ (r % 32)), conflict-free for a warp
-    float *scratch_row = reinterpret_cast<float *>(smem_raw + (smem_scratch - khd::smem_u32(smem_raw))) +
-                         row_in_tile * kHeadDim;
+    // the handed-over tile: 16-byte chunk c of row r at chunk c ^ (r % 8) of the row, conflict-free
+    // both for a thread per row and for the row-major copy to global memory
+    float4 *scratch = reinterpret_cast<float4 *>(smem_raw + (smem_scratch - khd::smem_u32(smem_raw)));
+    float4 *scratch_row = scratch + row_in_tile * (kHeadDim / 4);
+    const int group_thread = (ew & 3) * 32 + lane; // 0..127 within the group
     constexpr float kLog2eOverSqrtD = 1.4426950408889634f * 0.125f;
     uint32_t tiles_done = 0; // tiles this group has been through, over all items
     bool ok = true;
@@ -609,7 +611,8 @@ __device__ __forceinline__ void attention_body(int64_t slices, int64_t seq, floa
         s_merge_m[row_in_tile] = m;
         s_merge_l[row_in_tile] = l;
 #pragma unroll
-        for (int i = 0; i < kHeadDim; ++i) scratch_row[i ^ lane] = acc[i];
+        for (int i = 0; i < kHeadDim / 4; ++i)
+          scratch_row[i ^ (lane & 7)] = make_float4(acc[4 * i], acc[4 * i + 1], acc[4 * i + 2], acc[4 * i + 3]);
         khd::mbar_arrive(bar_merge_ready);
       } else {
         ok = khd::mbar_wait(bar_merge_ready, static_cast<uint32_t>(n & 1), &s_abort, status,
@@ -619,41 +622,39 @@ __device__ __forceinline__ void attention_body(int64_t slices, int64_t seq, floa
         const float mt = fmaxf(m, m1);
         const float w0 = fast_exp2(m - mt), w1 = fast_exp2(m1 - mt);
         const float inv = 1.0f / (l * w0 + l1 * w1);
-        const int64_t row = static_cast<int64_t>(q0) + row_in_tile;
-        float *orow = out + (bh * seq + row) * kHeadDim;
-        if (row < seq) {
+        // the finished rows replace the handed-over ones in the scratch tile ...
 #pragma unroll
-          for (int i = 0; i < kHeadDim / 4; ++i)
-            __stcs(reinterpret_cast<float4 *>(orow) + i,
-                   make_float4((acc[4 * i + 0] * w0 + scratch_row[(4 * i + 0) ^ lane] * w1) * inv,
-                               (acc[4 * i + 1] * w0 + scratch_row[(4 * i + 1) ^ lane] * w1) * inv,
-                               (acc[4 * i + 2] * w0 + scratch_row[(4 * i + 2) ^ lane] * w1) * inv,
-                               (acc[4 * i + 3] * w0 + scratch_row[(4 * i + 3) ^ lane] * w1) * inv));
+        for (int i = 0; i < kHeadDim / 4; ++i) {
+          const float4 o = scratch_row[i ^ (lane & 7)];
+          scratch_row[i ^ (lane & 7)] = make_float4((acc[4 * i + 0] * w0 + o.x * w1) * inv, (acc[4 * i + 1] * w0 + o.y * w1) * inv,
+                                                    (acc[4 * i + 2] * w0 + o.z * w1) * inv, (acc[4 * i + 3] * w0 + o.w * w1) * inv);
         }
-        khd::mbar_arrive(bar_scratch_free);
-        if (kGather) {
-          // the tile is complete in this GPU's replica: make the rows visible to the
-          // whole group, then copy the tile out
-          __threadfence_block();
-          khd::mbar_arrive(bar_gather);
-          ok = khd::mbar_wait(bar_gather, static_cast<uint32_t>(n & 1), &s_abort, status,
-                              khd::kStatusEpilogueWaitTimeout, 5002u);
-          if (!ok) break;
+        khd::mbar_arrive(bar_gather);
+        ok = khd::mbar_wait(bar_gather, static_cast<uint32_t>(n & 1), &s_abort, status,
+                            khd::kStatusEpilogueWaitTimeout, 5002u);
+        if (!ok) break;
+        // ... and the group copies the tile (contiguous in global memory) out in
+        // 512-byte warp-wide pieces, to the other replicas too when there are any
+        {
           const int64_t first_row = bh * seq + q0;
-          const int64_t rows_here = (seq - q0 < kBQ) ? (seq - q0) : kBQ;
-          const float4 *src = reinterpret_cast<const float4 *>(out + first_row * kHeadDim);
-          const int t = (ew & 3) * 32 + lane; // 0..127 within the group
-          for (int64_t i = t; i < rows_here * (kHeadDim / 4); i += kBQ) {
-            const float4 v = __ldcg(src + i);
-            const int64_t off = first_row * kHeadDim + i * 4;
-            if (targets->multicast != nullptr) {
-              multicast_store_float4(targets->multicast + off, v);
-            } else {
-              for (int d = 0; d < targets->count; ++d)
-                if (d != targets->self) *reinterpret_cast<float4 *>(targets->peer[d] + off) = v;
+          const int rows_here = (seq - q0 < kBQ) ? static_cast<int>(seq - q0) : kBQ;
+          float4 *dst = reinterpret_cast<float4 *>(out + first_row * kHeadDim);
+          for (int q = group_thread; q < rows_here * (kHeadDim / 4); q += kBQ) {
+            const int r = q >> 4, c = q & 15;
+            const float4 v = scratch[r * (kHeadDim / 4) + (c ^ (r & 7))];
+            __stcs(dst + q, v);
+            if (kGather) {
+              const int64_t off = first_row * kHeadDim + static_cast<int64_t>(q) * 4;
+              if (targets->multicast != nullptr) {
+                multicast_store_float4(targets->multicast + off, v);
+              } else {
+                for (int d = 0; d < targets->count; ++d)
+                  if (d != targets->self) *reinterpret_cast<float4 *>(targets->peer[d] + off) = v;
+              }
             }
           }
         }
+        khd::mbar_arrive(bar_scratch_free);
       }
     }
     khd::tc_fence_before_sync();
