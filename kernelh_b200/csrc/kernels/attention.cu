@@ -489,6 +489,18 @@ __device__ __forceinline__ void attention_body(int64_t slices, int64_t seq, floa
     uint32_t tiles_done = 0; // tiles this group has been through, over all items
     bool ok = true;
     int n = 0;
+    // Exponents of the 64-row tiles: shifts[(t * slices + slice) * tiles + tile], t = 0, 1, 2 for Q, K, V.
+    // Those an item starts with (its row's Q tile, the group's first K and V tile)
+    // are fetched while the item before it finishes.
+    int item_shift_q = 0, item_shift_k = 0, item_shift_v = 0;
+    const auto fetch_item_shifts = [&](int64_t w) {
+      const int64_t bh = w / q_tiles;
+      const int row_q = static_cast<int>((w - bh * q_tiles) * kBQ) + row_in_tile;
+      item_shift_q = __ldg(shifts + bh * num_kv + (row_q < seq ? row_q >> 6 : 0));
+      item_shift_k = g < num_kv ? __ldg(shifts + (slices + bh) * num_kv + g) : 0;
+      item_shift_v = g < num_kv ? __ldg(shifts + (2 * slices + bh) * num_kv + g) : 0;
+    };
+    if (blockIdx.x < items) fetch_item_shifts(blockIdx.x);
     for (int64_t w = blockIdx.x; w < items && ok; w += gridDim.x, ++n) {
       const int64_t bh = w / q_tiles;
       const int q0 = static_cast<int>((w - bh * q_tiles) * kBQ);
@@ -496,14 +508,12 @@ __device__ __forceinline__ void attention_body(int64_t slices, int64_t seq, floa
 #pragma unroll
       for (int i = 0; i < kHeadDim; ++i) acc[i] = 0.f;
       float m = -INFINITY, l = 0.f;
-      // Exponents of the 64-row tiles: shifts[(t * slices + slice) * tiles + tile], t = 0, 1, 2 for Q, K, V.
       // The running max `m` is kept in exp2 units, i.e. true score * log2(e) / sqrt(64).
       const int *k_shifts = shifts + (slices + bh) * num_kv, *v_shifts = shifts + (2 * slices + bh) * num_kv;
-      const int row_q = q0 + row_in_tile;
-      const int shift_q = __ldg(shifts + bh * num_kv + (row_q < seq ? row_q >> 6 : 0));
+      const int shift_q = item_shift_q;
       float v_factor_prev = 0.f; // 2^-(exponent of the V tile) of this group's previous product
       // the exponents of this group's next tile are fetched one tile ahead
-      int shift_k_next = g < num_kv ? __ldg(k_shifts + g) : 0, shift_v_next = g < num_kv ? __ldg(v_shifts + g) : 0;
+      int shift_k_next = item_shift_k, shift_v_next = item_shift_v;
       bool first = true; // no product of this item to fold in yet
 
       for (int j = g; j < num_kv && ok; j += 2) {
@@ -585,6 +595,7 @@ __device__ __forceinline__ void attention_body(int64_t slices, int64_t seq, floa
         ++tiles_done;
         first = false;
       }
+      if (w + gridDim.x < items) fetch_item_shifts(w + gridDim.x);
       // this group's last product of the item
       if (ok && !first) {
         ok = khd::mbar_wait(bar_pv_full + 8 * g, (tiles_done - 1) & 1u, &s_abort, status,
