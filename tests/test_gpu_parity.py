@@ -353,6 +353,21 @@ def test_attention_reference_inputs(ctx, oracle, b, h, s):
     assert cmp_.max_rel <= REL * math.sqrt(s)
 
 
+@pytest.mark.parametrize("b,h,s", [(5, 31, 192), (1, 300, 64), (2, 80, 320)])
+def test_attention_more_work_items_than_sms(ctx, oracle, b, h, s):
+    """The attention grid is persistent (a CTA per SM walks the 128-query work
+    items): more items than SMs, an odd number of key tiles (the groups end an
+    item on different sides), a single key tile (one softmax group idle), and a
+    second launch that must give the same bits."""
+    q, k, v = attention_inputs(oracle, b, h, s)
+    name = f"batch={b},heads={h},seq={s},head_dim=64"
+    o = run(ctx, "attention", name, [q, k, v], (b, h, s, 64))
+    cmp_ = oracle.compare(o, oracle.attention_ref(q, k, v), rtol=2e-3)
+    assert cmp_.non_finite == 0 and cmp_.max_violation <= 2e-3
+    assert cmp_.max_rel <= REL * math.sqrt(s)
+    assert np.array_equal(o, run(ctx, "attention", name, [q, k, v], (b, h, s, 64)))
+
+
 def test_attention_negative_control(ctx, oracle):
     q, k, v = attention_inputs(oracle, 2, 8, 256)
     o = run(ctx, "attention", "batch=2,heads=8,seq=256,head_dim=64", [q, k, v], (2, 8, 256, 64))
