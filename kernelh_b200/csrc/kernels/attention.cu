@@ -63,10 +63,13 @@ constexpr int kBQ = 128;  // query rows per CTA
 constexpr int kBKV = 64;  // keys per tile
 constexpr int kStages = 4; // K and V^T tiles in flight (rings of their own)
 constexpr int kSoftmaxThreads = 256; // two groups of one thread per query row
-constexpr int kThreads = 64 + kSoftmaxThreads + 32; // producer, issuer of the even tiles, softmax, issuer of the odd tiles
-constexpr int kOddIssuerWarp = (64 + kSoftmaxThreads) / 32;
-// registers are handed out to warps four at a time: bound the kernel as if it had twelve warps
-constexpr int kRegisterBoundThreads = 384;
+// Four warpgroups: [producer, issuer of group 0, issuer of group 1, spare], softmax
+// group 0, softmax group 1, output. A warp of the last three touches the
+// tensor-memory lanes 32 * (warp % 4) .. of its rows.
+constexpr int kThreads = 512;
+// registers per thread after the warpgroups have traded them (sum x 128 = the register file)
+constexpr int kRegsControl = 56, kRegsSoftmax = 184, kRegsOutput = 88;
+constexpr int kRegisterBoundThreads = kThreads; // 128 registers per thread at launch
 constexpr int kRowBytes = 128;                       // 64 fp16: one 128-byte swizzle row
 constexpr int kQTileBytes = kBQ * kRowBytes;         // 16 KiB: 128 rows, hi or lo
 constexpr int kKVTileBytes = kBKV * kRowBytes;       // 8 KiB: 64 rows (keys, or rows of V^T), hi or lo
@@ -75,11 +78,21 @@ constexpr int kHalfStageBytes = 2 * kKVTileBytes;    // one K (or V^T) tile: hi 
 constexpr int kPShift = 14;                          // P is split as P * 2^14
 // tensor-memory columns: two score buffers, two P buffers (32 columns of packed
 // fp16 pairs for hi, 32 for lo), two PV buffers
-constexpr uint32_t kColS0 = 0, kColS1 = 64, kColP0 = 128, kColP1 = 192, kColPV0 = 256, kColPV1 = 320;
+constexpr uint32_t kColS0 = 0, kColS1 = 64, kColP0 = 128, kColP1 = 192, kColPV0 = 256, kColPV1 = 320,
+                   kColOut0 = 384, kColOut1 = 448; // a group's finished row of an item, parked for the output warps
 constexpr uint32_t kTmemCols = 512;
 
 // 2^x by the special-function unit (2 ulp, flushes denormals): the arguments
 // here are <= 0 and the results feed a sum of at least 1.
+// Registers move between warpgroups (each executes one of these once, as a whole).
+template <int kRegs>
+__device__ __forceinline__ void registers_release() {
+  asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kRegs));
+}
+template <int kRegs>
+__device__ __forceinline__ void registers_take() {
+  asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kRegs));
+}
 __device__ __forceinline__ float fast_exp2(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -250,11 +263,11 @@ __device__ __forceinline__ void attention_body(int64_t slices, int64_t seq, floa
                                                const GatherOut *targets) {
   extern __shared__ uint8_t smem_raw[];
   // q_full[2], q_empty[2], k_full, k_empty, v_full, v_empty [kStages each], s_full[2], s_free[2],
-  // p_ready[2], pv_full[2], merge_ready, scratch_free, gather
+  // p_ready[2], pv_full[2], parked[2], out_free
   __shared__ __align__(8) uint64_t bars[4 + 4 * kStages + 8 + 3];
   __shared__ uint32_t s_tmem_base;
   __shared__ int s_abort;
-  __shared__ float s_merge_m[kBQ], s_merge_l[kBQ]; // max and sum of the group that hands its row over
+  __shared__ float s_row_m[2][kBQ], s_row_l[2][kBQ]; // max and sum that go with a group's parked row
 
   const int64_t q_tiles = (seq + kBQ - 1) / kBQ;
   const int64_t items = slices * q_tiles;
@@ -264,7 +277,7 @@ __device__ __forceinline__ void attention_body(int64_t slices, int64_t seq, floa
   const uint32_t smem_q = (khd::smem_u32(smem_raw) + 1023u) & ~1023u; // two Q tiles (hi, lo each)
   const uint32_t smem_k = smem_q + 2 * kQBytes;                       // kStages stages of K hi, lo
   const uint32_t smem_v = smem_k + kStages * kHalfStageBytes;         // kStages stages of V^T hi, lo
-  const uint32_t smem_scratch = smem_v + kStages * kHalfStageBytes;   // one output row per query row (merge)
+  const uint32_t smem_scratch = smem_v + kStages * kHalfStageBytes;   // 16 KiB: half an output row per query row
   const uint32_t bar_q_full = khd::smem_u32(&bars[0]);
   const uint32_t bar_q_empty = khd::smem_u32(&bars[2]);
   const uint32_t bar_k_full = khd::smem_u32(&bars[4]);
@@ -275,9 +288,8 @@ __device__ __forceinline__ void attention_body(int64_t slices, int64_t seq, floa
   const uint32_t bar_s_free = khd::smem_u32(&bars[6 + 4 * kStages]);
   const uint32_t bar_p_ready = khd::smem_u32(&bars[8 + 4 * kStages]);
   const uint32_t bar_pv_full = khd::smem_u32(&bars[10 + 4 * kStages]);
-  const uint32_t bar_merge_ready = khd::smem_u32(&bars[12 + 4 * kStages]);
-  const uint32_t bar_scratch_free = khd::smem_u32(&bars[13 + 4 * kStages]);
-  const uint32_t bar_gather = khd::smem_u32(&bars[14 + 4 * kStages]);
+  const uint32_t bar_parked = khd::smem_u32(&bars[12 + 4 * kStages]);   // [group]: its row of the item is parked
+  const uint32_t bar_out_free = khd::smem_u32(&bars[14 + 4 * kStages]); // the output warps have read both rows
 
   if (threadIdx.x == 0) {
     s_abort = 0;
@@ -295,9 +307,9 @@ __device__ __forceinline__ void attention_body(int64_t slices, int64_t seq, floa
       khd::mbar_init(bar_v_full + 8 * s, 1);
       khd::mbar_init(bar_v_empty + 8 * s, 1);
     }
-    khd::mbar_init(bar_merge_ready, kBQ);
-    khd::mbar_init(bar_scratch_free, kBQ);
-    khd::mbar_init(bar_gather, kBQ);
+    khd::mbar_init(bar_parked, kBQ);
+    khd::mbar_init(bar_parked + 8, kBQ);
+    khd::mbar_init(bar_out_free, kBQ);
     khd::mbar_fence_init();
     khd::tma_prefetch_descriptor(&tm_q_hi);
     khd::tma_prefetch_descriptor(&tm_q_lo);
@@ -315,6 +327,9 @@ __device__ __forceinline__ void attention_body(int64_t slices, int64_t seq, floa
   khd::tc_fence_after_sync();
   const uint32_t tmem_base = s_tmem_base;
 
+  const int wg = warp >> 2;
+  if (wg == 0) {
+  registers_release<kRegsControl>();
   if (warp == 0) {
     // ---- TMA producer: per item the Q tile (two buffers, so the next item's
     //      tile loads while this one is in use), then the item's K and V^T
@@ -368,7 +383,7 @@ __device__ __forceinline__ void attention_body(int64_t slices, int64_t seq, floa
         }
       }
     }
-  } else if (warp == 1 || warp == kOddIssuerWarp) {
+  } else if (warp == 1 || warp == 2) {
     // ---- MMA issuers, one warp per softmax group: warp 1 takes the even tiles
     //      of every item, the last warp the odd ones (a single thread cannot
     //      issue tcgen05.mma fast enough for both). Per tile j of its parity:
@@ -380,7 +395,7 @@ __device__ __forceinline__ void attention_body(int64_t slices, int64_t seq, floa
     //      uniform registers); only the tcgen05 instructions themselves sit
     //      under the elected lane. ------------------------------------------------------
     {
-      const int g = warp == 1 ? 0 : 1;
+      const int g = warp - 1;
       const bool leader = khd::elect_one();
       constexpr uint32_t idesc = khd::umma_idesc_f16(kBQ, kBKV); // M128 N64 K16 for both products
       constexpr uint64_t kKVTileStep = kKVTileBytes >> 4;
@@ -469,27 +484,23 @@ __device__ __forceinline__ void attention_body(int64_t slices, int64_t seq, floa
         }
       }
     }
-  } else {
-    // ---- softmax + output: two groups of 128 threads, one thread per query row
-    //      in each. Group g (warps 2-5 / 6-9) takes the tiles of parity g of every
-    //      item with its own running max, sum and output row; the groups work on
-    //      neighbouring tiles at the same time. At the end of an item the group
-    //      that did not have the last tile hands its (max, sum, row) over through
-    //      shared memory and goes on to the next item; the group with the last
-    //      tile combines the two and writes the rows out. A warp may only touch
-    //      tensor-memory lanes 32*(warp%4).., which both groups cover. -----------------
-    const int ew = warp - 2;
+  }
+  } else if (wg == 1 || wg == 2) {
+    registers_take<kRegsSoftmax>();
+    // ---- softmax: two groups of 128 threads (warpgroups 1 and 2), one thread per
+    //      query row in each. Group g takes the tiles of parity g of every item
+    //      with its own running max, sum and output row; the groups work on
+    //      neighbouring tiles at the same time and never wait for each other. At
+    //      the end of an item a group parks (max, sum, row) - the row in tensor
+    //      memory - for the output warps and goes on to the next item. A warp may
+    //      only touch tensor-memory lanes 32*(warp%4).., which both groups cover. ------
+    const int ew = warp - 4;
     const int quad = warp & 3;
     const int g = ew >> 2;
     const uint32_t lane_base = static_cast<uint32_t>(quad * 32) << 16;
     const int row_in_tile = quad * 32 + lane;
     const uint32_t col_s = g ? kColS1 : kColS0, col_p = g ? kColP1 : kColP0, col_pv = g ? kColPV1 : kColPV0;
-    const int merger = (num_kv - 1) & 1; // the group that owns the last tile of an item
-    // the handed-over tile: 16-byte chunk c of row r at chunk c ^ (r % 8) of the row, conflict-free
-    // both for a thread per row and for the row-major copy to global memory
-    float4 *scratch = reinterpret_cast<float4 *>(smem_raw + (smem_scratch - khd::smem_u32(smem_raw)));
-    float4 *scratch_row = scratch + row_in_tile * (kHeadDim / 4);
-    const int group_thread = (ew & 3) * 32 + lane; // 0..127 within the group
+    const uint32_t col_out = g ? kColOut1 : kColOut0;
     constexpr float kLog2eOverSqrtD = 1.4426950408889634f * 0.125f;
     uint32_t tiles_done = 0; // tiles this group has been through, over all items
     bool ok = true;
@@ -618,59 +629,97 @@ __device__ __forceinline__ void attention_body(int64_t slices, int64_t seq, floa
         }
       }
       if (!ok) break;
-      if (g != merger) {
-        // hand the row over (once the previous item's has been read) and go on
-        if (n > 0)
-          ok = khd::mbar_wait(bar_scratch_free, static_cast<uint32_t>((n - 1) & 1), &s_abort, status,
-                              khd::kStatusEpilogueWaitTimeout, 5000u);
-        if (!ok) break;
-        s_merge_m[row_in_tile] = m;
-        s_merge_l[row_in_tile] = l;
+      // park (max, sum, row) for the output warps, once they have read the previous item's
+      if (n > 0)
+        ok = khd::mbar_wait(bar_out_free, static_cast<uint32_t>((n - 1) & 1), &s_abort, status,
+                            khd::kStatusEpilogueWaitTimeout, 5000u);
+      if (!ok) break;
+      s_row_m[g][row_in_tile] = m;
+      s_row_l[g][row_in_tile] = l;
 #pragma unroll
-        for (int i = 0; i < kHeadDim / 4; ++i)
-          scratch_row[i ^ (lane & 7)] = make_float4(acc[4 * i], acc[4 * i + 1], acc[4 * i + 2], acc[4 * i + 3]);
-        khd::mbar_arrive(bar_merge_ready);
-      } else {
-        ok = khd::mbar_wait(bar_merge_ready, static_cast<uint32_t>(n & 1), &s_abort, status,
-                            khd::kStatusEpilogueWaitTimeout, 5001u);
-        if (!ok) break;
-        const float m1 = s_merge_m[row_in_tile], l1 = s_merge_l[row_in_tile];
-        const float mt = fmaxf(m, m1);
-        const float w0 = fast_exp2(m - mt), w1 = fast_exp2(m1 - mt);
-        const float inv = 1.0f / (l * w0 + l1 * w1);
-        // the finished rows replace the handed-over ones in the scratch tile ...
+      for (int h = 0; h < 4; ++h)
+        tmem_st_32x16(tmem_base + lane_base + col_out + 16 * h, *reinterpret_cast<const uint32_t(*)[16]>(&acc[16 * h]));
+      tmem_st_wait();
+      khd::tc_fence_before_sync();
+      khd::mbar_arrive(bar_parked + 8 * g);
+    }
+    khd::tc_fence_before_sync();
+  } else {
+    registers_release<kRegsOutput>();
+    // ---- output (warpgroup 3), one thread per query row: combine the two groups'
+    //      parked rows of an item, 32 columns at a time: stage the finished half
+    //      rows in shared memory (each warp its own 32 rows of 128 bytes: 16-byte
+    //      chunk c of row r at chunk c ^ (r % 8), conflict-free both for a thread
+    //      per row and for the row-major copy) and copy them out, four 128-byte
+    //      half rows per warp instruction - to the other replicas too when there
+    //      are any. ----------------------------------------------------------------------
+    const int quad = warp & 3;
+    const uint32_t lane_base = static_cast<uint32_t>(quad * 32) << 16;
+    const int row_in_tile = quad * 32 + lane;
+    constexpr int kHalfChunks = kHeadDim / 8; // 16-byte chunks in half a row
+    float4 *staged = reinterpret_cast<float4 *>(smem_raw + (smem_scratch - khd::smem_u32(smem_raw))) +
+                     quad * 32 * kHalfChunks; // this warp's 32 half rows
+    bool ok = true;
+    int n = 0;
+    for (int64_t w = blockIdx.x; w < items && ok; w += gridDim.x, ++n) {
+      const int64_t bh = w / q_tiles;
+      const int q0 = static_cast<int>((w - bh * q_tiles) * kBQ);
+      ok = khd::mbar_wait(bar_parked, static_cast<uint32_t>(n & 1), &s_abort, status,
+                          khd::kStatusEpilogueWaitTimeout, 5001u) &&
+           khd::mbar_wait(bar_parked + 8, static_cast<uint32_t>(n & 1), &s_abort, status,
+                          khd::kStatusEpilogueWaitTimeout, 5002u);
+      if (!ok) break;
+      khd::tc_fence_after_sync();
+      const float m0 = s_row_m[0][row_in_tile], l0 = s_row_l[0][row_in_tile];
+      const float m1 = s_row_m[1][row_in_tile], l1 = s_row_l[1][row_in_tile];
+      const float mt = fmaxf(m0, m1);
+      float w0 = fast_exp2(m0 - mt), w1 = fast_exp2(m1 - mt); // a group without tiles parks max = -inf: weight 0
+      const float inv = 1.0f / (l0 * w0 + l1 * w1);
+      w0 *= inv;
+      w1 *= inv;
+      const int64_t first_row = bh * seq + q0;
+      const int rows_here = (seq - q0 < kBQ) ? static_cast<int>(seq - q0) : kBQ;
+      float4 *dst = reinterpret_cast<float4 *>(out + first_row * kHeadDim);
 #pragma unroll
-        for (int i = 0; i < kHeadDim / 4; ++i) {
-          const float4 o = scratch_row[i ^ (lane & 7)];
-          scratch_row[i ^ (lane & 7)] = make_float4((acc[4 * i + 0] * w0 + o.x * w1) * inv, (acc[4 * i + 1] * w0 + o.y * w1) * inv,
-                                                    (acc[4 * i + 2] * w0 + o.z * w1) * inv, (acc[4 * i + 3] * w0 + o.w * w1) * inv);
+      for (int half = 0; half < 2; ++half) {
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          uint32_t a[16], b[16];
+          tmem_ld_32x16(tmem_base + lane_base + kColOut0 + 32 * half + 16 * h, a);
+          tmem_ld_32x16(tmem_base + lane_base + kColOut1 + 32 * half + 16 * h, b);
+          khd::tmem_ld_wait();
+#pragma unroll
+          for (int c = 0; c < 4; ++c)
+            staged[lane * kHalfChunks + ((4 * h + c) ^ (lane & 7))] =
+                make_float4(__uint_as_float(a[4 * c + 0]) * w0 + __uint_as_float(b[4 * c + 0]) * w1,
+                            __uint_as_float(a[4 * c + 1]) * w0 + __uint_as_float(b[4 * c + 1]) * w1,
+                            __uint_as_float(a[4 * c + 2]) * w0 + __uint_as_float(b[4 * c + 2]) * w1,
+                            __uint_as_float(a[4 * c + 3]) * w0 + __uint_as_float(b[4 * c + 3]) * w1);
         }
-        khd::mbar_arrive(bar_gather);
-        ok = khd::mbar_wait(bar_gather, static_cast<uint32_t>(n & 1), &s_abort, status,
-                            khd::kStatusEpilogueWaitTimeout, 5002u);
-        if (!ok) break;
-        // ... and the group copies the tile (contiguous in global memory) out in
-        // 512-byte warp-wide pieces, to the other replicas too when there are any
-        {
-          const int64_t first_row = bh * seq + q0;
-          const int rows_here = (seq - q0 < kBQ) ? static_cast<int>(seq - q0) : kBQ;
-          float4 *dst = reinterpret_cast<float4 *>(out + first_row * kHeadDim);
-          for (int q = group_thread; q < rows_here * (kHeadDim / 4); q += kBQ) {
-            const int r = q >> 4, c = q & 15;
-            const float4 v = scratch[r * (kHeadDim / 4) + (c ^ (r & 7))];
-            __stcs(dst + q, v);
-            if (kGather) {
-              const int64_t off = first_row * kHeadDim + static_cast<int64_t>(q) * 4;
-              if (targets->multicast != nullptr) {
-                multicast_store_float4(targets->multicast + off, v);
-              } else {
-                for (int d = 0; d < targets->count; ++d)
-                  if (d != targets->self) *reinterpret_cast<float4 *>(targets->peer[d] + off) = v;
-              }
+        if (half == 1) {
+          khd::tc_fence_before_sync();
+          khd::mbar_arrive(bar_out_free); // both parked rows and their (max, sum) are read
+        }
+        __syncwarp();
+#pragma unroll 4
+        for (int k = 0; k < kHalfChunks; ++k) {
+          const int q = k * 32 + lane; // this warp's half rows, row-major
+          const int r = q >> 3, c = q & 7;
+          if (quad * 32 + r >= rows_here) break;
+          const float4 v = staged[r * kHalfChunks + (c ^ (r & 7))];
+          const int64_t at = static_cast<int64_t>(quad * 32 + r) * (kHeadDim / 4) + half * kHalfChunks + c;
+          __stcs(dst + at, v);
+          if (kGather) {
+            const int64_t off = first_row * kHeadDim + at * 4;
+            if (targets->multicast != nullptr) {
+              multicast_store_float4(targets->multicast + off, v);
+            } else {
+              for (int d = 0; d < targets->count; ++d)
+                if (d != targets->self) *reinterpret_cast<float4 *>(targets->peer[d] + off) = v;
             }
           }
         }
-        khd::mbar_arrive(bar_scratch_free);
+        __syncwarp(); // the staged half rows are free again
       }
     }
     khd::tc_fence_before_sync();

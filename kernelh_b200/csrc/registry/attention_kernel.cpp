@@ -11,9 +11,9 @@ namespace kh {
 namespace {
 
 constexpr int64_t kHeadDim = 64, kBQ = 128, kBKV = 64;
-// two Q tiles hi/lo (32 KiB each) + three stages each of K and V^T hi/lo (16 KiB per stage) +
-// the 32 KiB row hand-over between the softmax groups + alignment slack
-constexpr size_t kAttnSmem = 2 * 32 * 1024 + 2 * 4 * 16 * 1024 + 32 * 1024 + 1024;
+// two Q tiles hi/lo (32 KiB each) + four stages each of K and V^T hi/lo (16 KiB per stage) +
+// 16 KiB in which the output warps stage half rows + alignment slack
+constexpr size_t kAttnSmem = 2 * 32 * 1024 + 2 * 4 * 16 * 1024 + 16 * 1024 + 1024;
 
 KernelPlan plan_attention(const ShapeMap &shape, const DeviceLimits &l) {
   for (const char *key : {"batch", "heads", "seq", "head_dim"})
@@ -48,7 +48,7 @@ KernelPlan plan_attention(const ShapeMap &shape, const DeviceLimits &l) {
   split.param_count = 33 + 7;
   LaunchStep main;
   main.entry = "attention";
-  main.block = {352, 1, 1}; // producer, two MMA issuers, eight softmax warps
+  main.block = {512, 1, 1}; // warpgroups: producer + two MMA issuers, two softmax groups, output
   // persistent: a CTA per SM walks the (slice, 128-query tile) work items
   main.grid = {static_cast<unsigned>(std::min<int64_t>(b * h * ((s + kBQ - 1) / kBQ), sms)), 1, 1};
   main.dynamic_smem = kAttnSmem;

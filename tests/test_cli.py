@@ -50,7 +50,7 @@ def test_occupancy_report_for_the_planned_launch():
     r = cli("bench", "--occupancy", "--kernel", "attention", "--shape",
             "batch=8,heads=16,seq=1024,head_dim=64", "--target", "nvptx-sm_100a")
     assert r.returncode == 0
-    assert '"threads_per_workgroup": 352' in r.stdout and '"tmem_columns": 512' in r.stdout
+    assert '"threads_per_workgroup": 512' in r.stdout and '"tmem_columns": 512' in r.stdout
     assert '"sm_resident_blocks": 1' in r.stdout
 
 
