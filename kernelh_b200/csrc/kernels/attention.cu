@@ -559,14 +559,18 @@ __device__ __forceinline__ void attention_body(int64_t slices, int64_t seq, floa
         // P is produced as P * 2^14 straight from the exponent (its split wants that
         // range); the row sum `l` and the output row are kept in the same units.
         const float offset = static_cast<float>(kPShift) - m_new;
-        float sum = 0.f;
+        // (two fp32 per instruction where the arithmetic allows)
+        const float2 f2 = make_float2(f, f), offset2 = make_float2(offset, offset);
+        float2 sum2 = make_float2(0.f, 0.f);
 #pragma unroll
-        for (int i = 0; i < kBKV; ++i) {
-          const float p = fast_exp2(fmaf(__uint_as_float(sv[i]), f, offset));
-          sv[i] = __float_as_uint(p);
-          sum += p;
+        for (int i = 0; i < kBKV; i += 2) {
+          const float2 x = __ffma2_rn(make_float2(__uint_as_float(sv[i]), __uint_as_float(sv[i + 1])), f2, offset2);
+          const float2 p = make_float2(fast_exp2(x.x), fast_exp2(x.y));
+          sv[i] = __float_as_uint(p.x);
+          sv[i + 1] = __float_as_uint(p.y);
+          sum2 = __fadd2_rn(sum2, p);
         }
-        l = l * alpha + sum;
+        l = l * alpha + (sum2.x + sum2.y);
         m = m_new;
 
         // The group's previous product PV_{j-2} read P buffer g and wrote PV buffer
