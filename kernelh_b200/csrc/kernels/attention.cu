@@ -581,14 +581,20 @@ __device__ __forceinline__ void attention_body(int64_t slices, int64_t seq, floa
                               khd::kStatusMmaWaitTimeout, 2000u + static_cast<uint32_t>(j));
           if (!ok) break;
           khd::tc_fence_after_sync();
+          const float2 vf2 = make_float2(v_factor_prev, v_factor_prev), alpha2 = make_float2(alpha, alpha);
 #pragma unroll
           for (int h = 0; h < 4; ++h) {
             uint32_t t[16];
             tmem_ld_32x16(tmem_base + lane_base + col_pv + 16 * h, t);
             khd::tmem_ld_wait();
 #pragma unroll
-            for (int i = 0; i < 16; ++i)
-              acc[16 * h + i] = fmaf(__uint_as_float(t[i]), v_factor_prev, acc[16 * h + i]) * alpha;
+            for (int i = 0; i < 16; i += 2) {
+              const float2 r = __fmul2_rn(__ffma2_rn(make_float2(__uint_as_float(t[i]), __uint_as_float(t[i + 1])), vf2,
+                                                     make_float2(acc[16 * h + i], acc[16 * h + i + 1])),
+                                          alpha2);
+              acc[16 * h + i] = r.x;
+              acc[16 * h + i + 1] = r.y;
+            }
           }
         }
         v_factor_prev = khd::scale_pow2(1.0f, -shift_v); // V was split as V * 2^shift
