@@ -139,7 +139,7 @@ __device__ __forceinline__ uint32_t half2_bits(__half2 h) { return *reinterpret_
 // tensor at a time, finds its largest magnitude, and writes the two splits scaled
 // by the exponent that gives; shifts[(t * bh + slice) * tiles + tile] receives
 // the exponent (t = 0, 1, 2 for Q, K, V).
-extern "C" __global__ void __launch_bounds__(256)
+extern "C" __global__ void __launch_bounds__(256, 5)
 attention_split(KH_MEMREF4(const float, q), KH_MEMREF4(const float, k), KH_MEMREF4(const float, v),
                 __half *__restrict__ q_hi, __half *__restrict__ q_lo, __half *__restrict__ k_hi,
                 __half *__restrict__ k_lo, __half *__restrict__ vt_hi, __half *__restrict__ vt_lo,

@@ -44,7 +44,7 @@ KernelPlan plan_attention(const ShapeMap &shape, const DeviceLimits &l) {
   LaunchStep split;
   split.entry = "attention_split";
   split.block = {256, 1, 1};
-  split.grid = {static_cast<unsigned>(std::min<int64_t>(3 * b * h * (s / kBKV), sms * 8)), 1, 1}; // a block per 64-row tile
+  split.grid = {static_cast<unsigned>(std::min<int64_t>(3 * b * h * (s / kBKV), sms * 5)), 1, 1}; // a block per 64-row tile at a time, five blocks resident per SM
   split.param_count = 33 + 7;
   LaunchStep main;
   main.entry = "attention";
