@@ -62,7 +62,6 @@ constexpr int kHeadDim = 64;
 constexpr int kBQ = 128;  // query rows per CTA
 constexpr int kBKV = 64;  // keys per tile
 constexpr int kStages = 4; // K and V^T tiles in flight (rings of their own)
-constexpr int kSoftmaxThreads = 256; // two groups of one thread per query row
 // Four warpgroups: [producer, issuer of group 0, issuer of group 1, spare], softmax
 // group 0, softmax group 1, output. A warp of the last three touches the
 // tensor-memory lanes 32 * (warp % 4) .. of its rows.
@@ -519,7 +518,6 @@ __device__ __forceinline__ void attention_body(int64_t slices, int64_t seq, floa
     if (blockIdx.x < items) fetch_item_shifts(blockIdx.x);
     for (int64_t w = blockIdx.x; w < items && ok; w += gridDim.x, ++n) {
       const int64_t bh = w / q_tiles;
-      const int q0 = static_cast<int>((w - bh * q_tiles) * kBQ);
       float acc[kHeadDim]; // running output of this group's tiles, normalised to its max
 #pragma unroll
       for (int i = 0; i < kHeadDim; ++i) acc[i] = 0.f;
