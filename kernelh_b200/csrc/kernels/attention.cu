@@ -30,20 +30,22 @@
 // Two launches:
 //  attention_split  writes Q, K and V^T as scaled fp16 hi/lo pairs into scratch
 //      and the exponent of every 64-row tile.
-//  attention  a persistent grid, one CTA per SM; a CTA takes work items (128
-//      query rows of one (batch, head) each) b, b + gridDim.x, ... and keeps
-//      its pipelines running across them. Warp 0 feeds TMA (the Q tile of an
-//      item into one of two buffers; separate 4-deep rings of K and V^T
-//      tiles); warps 1 and 10 issue the MMAs, one warp per softmax group (S of
-//      the group's next tile goes into its score buffer as soon as the group
-//      has read the current scores out, ahead of PV of the current tile, so a
-//      group never waits for scores and the tensor core works while softmax
-//      runs); warps 2-5 and 6-9 are two softmax groups (one thread per query
-//      row each) that take the even and the odd tiles with their own running
-//      max, sum and output row, so two tiles are in the softmax stage at once.
-//      At the end of an item one group hands its row over through shared
-//      memory and moves on; the other combines the two and writes the rows out.
-//      Scores, P and PV sit in tensor memory, one set per group.
+//  attention  a persistent grid, one CTA of four warpgroups per SM; a CTA takes
+//      work items (128 query rows of one (batch, head) each) b, b + gridDim.x,
+//      ... and keeps its pipelines running across them. Warpgroup 0: warp 0
+//      feeds TMA (the Q tile of an item into one of two buffers; separate
+//      4-deep rings of K and V^T tiles), warps 1 and 2 issue the MMAs, one warp
+//      per softmax group (S of the group's next tile goes into its score
+//      buffer as soon as the group has read the current scores out, ahead of PV
+//      of the current tile, so a group never waits for scores and the tensor
+//      core works while softmax runs). Warpgroups 1 and 2 are the two softmax
+//      groups (one thread per query row each) that take the even and the odd
+//      tiles with their own running max, sum and output row, so two tiles are
+//      in the softmax stage at once; at the end of an item a group parks its
+//      row in tensor memory and moves on. Warpgroup 3 combines the two parked
+//      rows and writes the finished rows out. The warpgroups trade registers
+//      at the start (setmaxnreg): most go to the softmax threads.
+//      Scores, P, PV and the parked rows sit in tensor memory, one set per group.
 //
 // Tensor-bound: 4 b h s^2 d useful flops; three products put the ceiling at one
 // third of the fp16 tensor rate.
