@@ -47,6 +47,18 @@ template <typename F> int guarded(F &&f) {
   }
 }
 
+// The tensor-core kernels and the fused all-gathers move 128-bit vectors (and
+// multimem.st.v4 / float4 peer stores) without a scalar path: an address that is
+// not 16-byte aligned is refused here, on the host, before anything is launched.
+// Returns 0 when every non-null address is aligned.
+int refuse_misaligned(const char *entry, std::initializer_list<std::pair<const char *, const void *>> buffers) {
+  if (const char *bad = kh::first_misaligned16(buffers))
+    return set_error(2, std::string(entry) + ": buffer '" + bad +
+                            "' is not 16-byte aligned; this kernel has no scalar path "
+                            "(pass an aligned allocation or copy the view)");
+  return 0;
+}
+
 int need_ctx(kh_context *ctx) {
   if (ctx == nullptr || !ctx->exec) return set_error(2, "null kernelh_b200 context");
   return 0;
@@ -227,8 +239,11 @@ int kh_gemm(kh_context *ctx, const float *a, const float *b, float *c, int64_t m
 }
 int kh_gemm_allgather(kh_context *ctx, const float *a_shard, const float *b, void *const *c_replicas,
                       int world, int rank, int64_t m_shard, int64_t n, int64_t k, void *stream) {
-  if (int rc = need_ctx(ctx)) return rc;
   if (c_replicas == nullptr || world <= 0) return set_error(2, "kh_gemm_allgather: no C replicas given");
+  if (world > 8) return set_error(2, "kh_gemm_allgather: between 1 and 8 ranks are supported");
+  for (int i = 0; i < world; ++i)
+    if (int rc = refuse_misaligned("kh_gemm_allgather", {{"C replica", c_replicas[i]}})) return rc;
+  if (int rc = need_ctx(ctx)) return rc;
   return guarded([&] {
     if (auto r = ctx->exec->backend().make_current(); !r) return set_error(r.error());
     std::vector<void *> reps(c_replicas, c_replicas + world);
@@ -239,9 +254,11 @@ int kh_gemm_allgather(kh_context *ctx, const float *a_shard, const float *b, voi
 int kh_gemm_allgather_multicast(kh_context *ctx, const float *a_shard, const float *b, float *c_local,
                                 void *c_multicast, int world, int rank, int64_t m_shard, int64_t n,
                                 int64_t k, void *stream) {
-  if (int rc = need_ctx(ctx)) return rc;
   if (c_multicast == nullptr || c_local == nullptr)
     return set_error(2, "kh_gemm_allgather_multicast: null C address");
+  if (int rc = refuse_misaligned("kh_gemm_allgather_multicast", {{"C", c_local}, {"C multicast address", c_multicast}}))
+    return rc;
+  if (int rc = need_ctx(ctx)) return rc;
   if (world < 1 || world > 8 || rank < 0 || rank >= world)
     return set_error(2, "kh_gemm_allgather_multicast: rank / world out of range");
   return guarded([&] {
@@ -254,6 +271,7 @@ int kh_gemm_allgather_multicast(kh_context *ctx, const float *a_shard, const flo
 }
 int kh_attention(kh_context *ctx, const float *q, const float *k, const float *v, float *o,
                  int64_t batch, int64_t heads, int64_t seq, int64_t head_dim, void *stream) {
+  if (int rc = refuse_misaligned("kh_attention", {{"Q", q}, {"K", k}, {"V", v}, {"O", o}})) return rc;
   return launch_named(ctx, "attention",
                       {{"batch", batch}, {"heads", heads}, {"seq", seq}, {"head_dim", head_dim}},
                       {const_cast<float *>(q), const_cast<float *>(k), const_cast<float *>(v), o},
@@ -263,9 +281,14 @@ int kh_attention(kh_context *ctx, const float *q, const float *k, const float *v
 int kh_attention_allgather(kh_context *ctx, const float *q, const float *k, const float *v,
                            void *const *o_replicas, void *o_multicast, int world, int rank, int64_t slices,
                            int64_t seq, int64_t head_dim, void *stream) {
-  if (int rc = need_ctx(ctx)) return rc;
   if (o_replicas == nullptr || world <= 0) return set_error(2, "kh_attention_allgather: no output replicas given");
+  if (world > 8) return set_error(2, "kh_attention_allgather: between 1 and 8 ranks are supported");
   if (head_dim != 64) return set_error(2, "kh_attention_allgather: the kernel is pinned to head_dim = 64");
+  if (int rc = refuse_misaligned("kh_attention_allgather", {{"Q", q}, {"K", k}, {"V", v}, {"O multicast address", o_multicast}}))
+    return rc;
+  for (int i = 0; i < world; ++i)
+    if (int rc = refuse_misaligned("kh_attention_allgather", {{"O replica", o_replicas[i]}})) return rc;
+  if (int rc = need_ctx(ctx)) return rc;
   return guarded([&] {
     if (auto r = ctx->exec->backend().make_current(); !r) return set_error(r.error());
     std::vector<void *> reps(o_replicas, o_replicas + world);

@@ -71,6 +71,9 @@ struct GatherOut {
 
 Result<void> launch_attention(Executor &ex, const KernelPlan &p, const std::vector<void *> &buf,
                               StreamHandle stream, const GatherOut *gather) {
+  if (const char *bad = first_misaligned16({{"Q", buf[0]}, {"K", buf[1]}, {"V", buf[2]}, {"O", buf[3]}}))
+    return fail(2, std::string("attention: buffer '") + bad +
+                       "' is not 16-byte aligned; the kernel reads and writes 128-bit vectors and has no scalar path");
   const std::vector<int64_t> &shape = p.tensors[0].shape;
   const int64_t bh = shape[0] * shape[1], s = shape[2];
   const int64_t elems = bh * s * kHeadDim;
@@ -160,9 +163,13 @@ Result<void> run_attention_allgather(Executor &ex, const void *q, const void *k,
   t.count = world;
   t.self = rank;
   t.multicast = multicast ? static_cast<float *>(multicast) + rank * shard_elems : nullptr;
+  if (first_misaligned16({{"O multicast address", multicast}}))
+    return fail(2, "attention_allgather: the output multicast address is not 16-byte aligned");
   for (int i = 0; i < world; ++i) {
     if (replicas[i] == nullptr && (multicast == nullptr || i == rank))
       return fail(2, "attention_allgather: null output replica pointer");
+    if (first_misaligned16({{"O replica", replicas[i]}}))
+      return fail(2, "attention_allgather: output replica " + std::to_string(i) + " is not 16-byte aligned");
     t.peer[i] = replicas[i] ? static_cast<float *>(replicas[i]) + rank * shard_elems : nullptr;
   }
   return launch_attention(ex, plan,

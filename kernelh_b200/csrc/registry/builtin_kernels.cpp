@@ -511,10 +511,15 @@ Result<void> run_gemm_allgather(Executor &ex, const void *a_shard, const void *b
   GatherTargets t{};
   t.count = world;
   t.multicast = static_cast<float *>(multicast);
+  // the epilogue's pushes are multimem.st.v4 / float4 peer stores: no scalar path for the bases
+  if (first_misaligned16({{"C multicast address", multicast}}))
+    return fail(2, "gemm_allgather: the C multicast address is not 16-byte aligned");
   for (int i = 0; i < world; ++i) {
     // with a multicast address only this rank's own replica is stored to directly
     if (replicas[i] == nullptr && (multicast == nullptr || i == rank))
       return fail(2, "gemm_allgather: null C replica pointer");
+    if (first_misaligned16({{"C replica", replicas[i]}}))
+      return fail(2, "gemm_allgather: C replica " + std::to_string(i) + " is not 16-byte aligned");
     t.base[i] = static_cast<float *>(replicas[i]);
   }
   t.self = rank;

@@ -14,6 +14,8 @@
 #include "shape_text.hpp"
 
 #include <functional>
+#include <initializer_list>
+#include <utility>
 #include <string>
 #include <vector>
 
@@ -75,6 +77,15 @@ struct KernelRecord {
                              const std::vector<void *> &dev, const HostStreams &)>
       run_host = nullptr;
 };
+
+// Name of the first non-null address in `buffers` that is not 16-byte aligned,
+// or nullptr. Pure host arithmetic (used before any launch of a kernel that has
+// no scalar path).
+inline const char *first_misaligned16(std::initializer_list<std::pair<const char *, const void *>> buffers) {
+  for (const auto &[name, ptr] : buffers)
+    if (ptr != nullptr && (reinterpret_cast<uintptr_t>(ptr) & 15u) != 0) return name;
+  return nullptr;
+}
 
 void register_kernel(KernelRecord record);
 std::vector<std::string> registered_kernels();

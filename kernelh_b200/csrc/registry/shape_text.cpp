@@ -1,7 +1,9 @@
 #include "shape_text.hpp"
 
-#include <cerrno>
-#include <cstdlib>
+#include <cctype>
+#include <charconv>
+#include <optional>
+#include <string_view>
 
 namespace kh {
 
@@ -14,22 +16,36 @@ std::string shape_to_text(const ShapeMap &shape) {
   return out;
 }
 
+namespace {
+
+// A whole decimal integer that fits int64. Leading blanks and one '+' are
+// tolerated because the C library conversion the reference's CLI relies on
+// tolerates them; anything after the digits rejects the value.
+std::optional<int64_t> whole_integer(std::string_view v) {
+  while (!v.empty() && std::isspace(static_cast<unsigned char>(v.front()))) v.remove_prefix(1);
+  if (v.size() > 1 && v.front() == '+' && v[1] != '-') v.remove_prefix(1);
+  int64_t value = 0;
+  const auto [stop, ec] = std::from_chars(v.data(), v.data() + v.size(), value, 10);
+  if (ec != std::errc() || stop != v.data() + v.size() || v.empty()) return std::nullopt;
+  return value;
+}
+
+} // namespace
+
 ShapeMap parse_shape_text(const std::string &text) {
   ShapeMap out;
-  size_t pos = 0;
-  for (;;) {
-    const size_t comma = text.find(',', pos);
-    const std::string item = text.substr(pos, comma == std::string::npos ? std::string::npos : comma - pos);
-    const size_t eq = item.find('=');
-    if (eq == std::string::npos || eq == 0 || eq + 1 >= item.size()) return {};
-    const std::string value = item.substr(eq + 1);
-    errno = 0;
-    char *end = nullptr;
-    const long long parsed = std::strtoll(value.c_str(), &end, 10);
-    if (errno != 0 || end == value.c_str() || *end != '\0') return {};
-    out[item.substr(0, eq)] = parsed;
-    if (comma == std::string::npos) break;
-    pos = comma + 1;
+  std::string_view rest(text);
+  bool more = true;
+  while (more) {
+    const size_t cut = rest.find(',');
+    const std::string_view item = rest.substr(0, cut);
+    more = cut != std::string_view::npos;
+    if (more) rest.remove_prefix(cut + 1);
+    const size_t sep = item.find('=');
+    const bool has_key = sep != std::string_view::npos && sep > 0;
+    const auto value = has_key ? whole_integer(item.substr(sep + 1)) : std::nullopt;
+    if (!value) return {}; // one bad item voids the whole text
+    out[std::string(item.substr(0, sep))] = *value; // a repeated key keeps the last value
   }
   return out;
 }

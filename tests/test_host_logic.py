@@ -227,9 +227,45 @@ def test_compute_calls_fail_loudly_without_a_device():
 def test_multi_gpu_entry_points_reject_bad_arguments_before_touching_a_device():
     """The sharded entry points validate their arguments on the host: a null
     context is a usage error (2) with a message, not a crash."""
+    import ctypes as C
+
     lib = kh.lib
+    reps = (C.c_void_p * 2)(0x1000, 0x2000)
     assert lib.kh_gemm_allgather(None, None, None, None, 2, 0, 256, 256, 64, None) == 2
+    assert b"no C replicas" in lib.kh_last_error()
+    assert lib.kh_gemm_allgather(None, None, None, reps, 2, 0, 256, 256, 64, None) == 2
     assert b"context" in lib.kh_last_error()
     assert lib.kh_gemm_allgather_multicast(None, None, None, None, None, 2, 0, 256, 256, 64, None) == 2
-    assert lib.kh_attention_allgather(None, None, None, None, None, None, 2, 0, 4, 64, 64, None) == 2
+    assert lib.kh_gemm_allgather_multicast(None, None, None, 0x1000, 0x2000, 2, 0, 256, 256, 64, None) == 2
     assert b"context" in lib.kh_last_error()
+    assert lib.kh_attention_allgather(None, None, None, None, reps, None, 2, 0, 4, 64, 64, None) == 2
+    assert b"context" in lib.kh_last_error()
+
+
+def test_kernels_without_a_scalar_path_refuse_misaligned_addresses_on_the_host():
+    """attention and the fused all-gathers move 128-bit vectors only: an address
+    that is not 16-byte aligned (a contiguous but offset view such as
+    t.flatten()[1:]) is a usage error (2) raised before any launch, and the
+    message names the buffer. No device is needed to find that out."""
+    import ctypes as C
+
+    lib = kh.lib
+    ok, off = 0x7000000, 0x7000004
+    for q, k, v, o, name in ((off, ok, ok, ok, b"'Q'"), (ok, off, ok, ok, b"'K'"), (ok, ok, off, ok, b"'V'"),
+                             (ok, ok, ok, off, b"'O'")):
+        assert lib.kh_attention(None, q, k, v, o, 1, 1, 64, 64, None) == 2
+        assert b"16-byte aligned" in lib.kh_last_error() and name in lib.kh_last_error()
+    assert lib.kh_attention(None, ok, ok, ok, ok, 1, 1, 64, 64, None) == 2
+    assert b"context" in lib.kh_last_error()  # aligned: the next check is the context
+    reps = (C.c_void_p * 2)(ok, off)
+    assert lib.kh_gemm_allgather(None, ok, ok, reps, 2, 0, 256, 256, 64, None) == 2
+    assert b"16-byte aligned" in lib.kh_last_error() and b"C replica" in lib.kh_last_error()
+    assert lib.kh_gemm_allgather_multicast(None, ok, ok, ok, off, 2, 0, 256, 256, 64, None) == 2
+    assert b"multicast" in lib.kh_last_error() and b"16-byte aligned" in lib.kh_last_error()
+    assert lib.kh_attention_allgather(None, ok, ok, ok, reps, None, 2, 0, 4, 64, 64, None) == 2
+    assert b"O replica" in lib.kh_last_error()
+    good = (C.c_void_p * 2)(ok, ok + 64)
+    assert lib.kh_attention_allgather(None, ok, off, ok, good, None, 2, 0, 4, 64, 64, None) == 2
+    assert b"'K'" in lib.kh_last_error()
+    assert lib.kh_attention_allgather(None, ok, ok, ok, good, off, 2, 0, 4, 64, 64, None) == 2
+    assert b"multicast" in lib.kh_last_error()
