@@ -282,10 +282,7 @@ def memory_bound_rows(torch, ctx, stream, hbm_peak: float) -> dict:
 
     def row(name, kernel, shape, make, bytes_per_launch, nsets, iters=200):
         sets = [make() for _ in range(nsets)]
-        # scan's look-back state carries a per-launch epoch chosen on the host, so a
-        # captured scan launch cannot be replayed: it is timed as a launch loop.
-        ms, method = time_rotating(torch, lambda s, st: ctx.launch(kernel, shape, s, st), sets, iters,
-                                   use_graph=(kernel != "scan"))
+        ms, method = time_rotating(torch, lambda s, st: ctx.launch(kernel, shape, s, st), sets, iters)
         gbs = bytes_per_launch / ms / 1e6
         out[name] = {"shape": shape, "ms": ms, "gbs": gbs, "frac_of_measured_hbm": gbs / hbm_peak,
                      "buffer_sets": nsets, "timing": method}
@@ -470,10 +467,48 @@ def gpu_arm(args) -> None:
                 "kernel_ms": kernel_ms, "split_ms": (prof["gemm_split_a"][1] + prof["gemm_colmax_b"][1] + prof["gemm_split_bt"][1]) / gemm_launches,
                 "peak_note": f"bf16_tflops_sustained of {peaks['source']} / 3 (three fp16 products per fp32-class multiply-add)"}
 
-    # ---- sampled correctness of what was timed (checker, not measured) -------------------
-    pick = torch.tensor([0, size // 3, size - 1], device="cuda")
+    # ---- parity of the timed path, asserted on every rank (checker, not measured) ----------
+    # C is overwritten with NaN on every rank, ONE more step runs, and then every rank checks
+    # its own copy of the whole C: no NaN may be left (every tile of every rank's row block
+    # arrived in this step, not in an earlier one), and rows sampled from every rank's row
+    # block must agree with an fp64 product of the same inputs.
+    parity_failures = []
+    c.fill_(float("nan"))
+    torch.cuda.synchronize()
+    barrier()
+    step()
+    torch.cuda.synchronize()
+    barrier()
+    per_block = size // world
+    sample_rows = sorted({blk * per_block + off for blk in range(world)
+                          for off in (0, per_block // 3, per_block - 1)})
+    pick = torch.tensor(sample_rows, device="cuda")
     ref = a[pick].double() @ b.double()
-    err = ((c[pick].double() - ref).abs().max() / ref.pow(2).mean().sqrt()).item()
+    got = c[pick].double()
+    rms = ref.pow(2).mean().sqrt()
+    rel_bound = 1e-5 * size ** 0.5
+    gemm_check = torch.stack([
+        torch.nan_to_num(((got - ref).abs() / torch.maximum(ref.abs(), rms)).max(), nan=float("inf")),
+        torch.nan_to_num((got - ref).norm() / ref.norm(), nan=float("inf")),
+        torch.isnan(c).sum().double(),
+        torch.nan_to_num((got - ref).abs().max() / rms, nan=float("inf"))])
+    if world > 1:
+        every = [torch.zeros_like(gemm_check) for _ in range(world)]
+        dist.all_gather(every, gemm_check)
+    else:
+        every = [gemm_check]
+    every = [e.tolist() for e in every]
+    for r, (max_rel, rel_fro, nans, _) in enumerate(every):
+        if not (max_rel <= rel_bound and rel_fro <= 1e-5 and nans == 0):
+            parity_failures.append(f"gemm: rank {r}'s C has max floored-relative error {max_rel:.3g} "
+                                   f"(bound {rel_bound:.3g}), rel. Frobenius {rel_fro:.3g} (bound 1e-5), "
+                                   f"{int(nans)} elements never written")
+    err = max(e[3] for e in every)
+    parity = {"gemm": {"checked": f"{len(sample_rows)} rows ({len(sample_rows) // world} from every rank's row "
+                                  "block) of every rank's C against fp64, after one step on a NaN-filled C",
+                       "max_rel_floored_by_rank": [e[0] for e in every], "bound": rel_bound,
+                       "rel_frobenius_by_rank": [e[1] for e in every], "frobenius_bound": 1e-5,
+                       "unwritten_elements_by_rank": [int(e[2]) for e in every]}}
 
     line = {
         "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
@@ -491,7 +526,7 @@ def gpu_arm(args) -> None:
                    "step": "gemm_split_a + gemm_colmax_b + gemm_split_bt + " + {"none": "gemm", "nccl": "gemm + nccl all_gather",
                                                                  "p2p": "gemm_allgather + barrier"}[gather]},
         "roofline": roofline, "gpu_launches": int(launches),
-        "sampled_max_err_over_rms": err,
+        "sampled_max_err_over_rms": err, "parity": parity,
     }
     if clocks is not None:
         line["clocks"] = clocks
@@ -532,7 +567,11 @@ def gpu_arm(args) -> None:
         shard = sharding.attention_shard_shape(bsz, heads, seq, dim, world, rank)
         lo, hi = shard["units"]
         even = (bsz * heads) % world == 0
-        qkv = [torch.randn(max(hi - lo, 1), seq, dim, device="cuda") for _ in range(3)]
+        # the same seeded Q, K, V on every rank (so that any rank can check any slice); a rank
+        # works on its own (batch, head) slices of them
+        gen.manual_seed(SEED + 7)
+        qkv_all = [torch.randn(bsz * heads, seq, dim, device="cuda", generator=gen) for _ in range(3)]
+        qkv = [t[lo:hi].contiguous() if hi > lo else t[:1].contiguous() for t in qkv_all]
         o_symm = None
         att_mode = "none"
         if even and gather == "p2p":
@@ -578,6 +617,48 @@ def gpu_arm(args) -> None:
         torch.cuda.synchronize()
         att = torch.tensor([a0.elapsed_time(a1) / 10], device="cuda")
         dist.all_reduce(att, op=dist.ReduceOp.MAX)
+        # parity, on every rank: NaN-fill the whole output, one more step, then the first and the
+        # last slice of every rank's share (of this rank's own share when nothing is gathered)
+        # against an fp64 evaluation; no NaN may be left anywhere a slice was due.
+        o_full.fill_(float("nan"))
+        if att_mode == "none":
+            o_shard.fill_(float("nan"))
+        torch.cuda.synchronize()
+        barrier()
+        attention_step()
+        torch.cuda.synchronize()
+        barrier()
+        per = (bsz * heads) // world if even else 0
+        owners = range(world) if att_mode != "none" else [rank]
+        worst_rel, worst_violation = 0.0, 0.0
+        for owner in owners:
+            o_lo, o_hi = (owner * per, (owner + 1) * per) if even else (lo, hi)
+            for sl in sorted({o_lo, o_hi - 1}) if o_hi > o_lo else []:
+                q64, k64, v64 = (t[sl].double() for t in qkv_all)
+                ref = torch.softmax(q64 @ k64.T / dim ** 0.5, -1) @ v64
+                got = (o_full[sl] if att_mode != "none" else o_shard[sl - lo]).double()
+                d = (got - ref).abs()
+                rel = torch.nan_to_num((d / torch.maximum(ref.abs(), ref.pow(2).mean().sqrt())).max(), nan=float("inf"))
+                vio = torch.nan_to_num((d / (2e-3 + 2e-3 * ref.abs())).max(), nan=float("inf"))
+                worst_rel, worst_violation = max(worst_rel, rel.item()), max(worst_violation, vio.item())
+        out_checked = o_full if att_mode != "none" else o_shard
+        att_check = torch.tensor([worst_rel, worst_violation, float(torch.isnan(out_checked).sum().item())],
+                                 device="cuda", dtype=torch.float64)
+        att_every = [torch.zeros_like(att_check) for _ in range(world)]
+        dist.all_gather(att_every, att_check)
+        att_every = [e.tolist() for e in att_every]
+        att_bound = 1e-5 * seq ** 0.5
+        for r, (rel, vio, nans) in enumerate(att_every):
+            if not (rel <= att_bound and vio <= 1.0 and nans == 0):
+                parity_failures.append(f"attention_sharded: rank {r}'s output has max floored-relative error "
+                                       f"{rel:.3g} (bound {att_bound:.3g}), |d| / (2e-3 + 2e-3 |ref|) = {vio:.3g} "
+                                       f"(bound 1), {int(nans)} elements never written")
+        parity["attention_sharded"] = {
+            "checked": "first and last (batch, head) slice of every rank's share in every rank's copy of the "
+                       "output against fp64, after one step on a NaN-filled output",
+            "max_rel_floored_by_rank": [e[0] for e in att_every], "bound": att_bound,
+            "reference_tolerance_ratio_by_rank": [e[1] for e in att_every],
+            "unwritten_elements_by_rank": [int(e[2]) for e in att_every]}
         line["attention_sharded"] = {"shape": f"batch={bsz},heads={heads},seq={seq},head_dim={dim}",
                                      "sharding": f"(batch, head) slices over {world} ranks" + {
                                          "fused": "; all-gather of the output fused into the kernel (" + (
@@ -601,6 +682,12 @@ def gpu_arm(args) -> None:
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
+    if parity_failures:
+        # identical on every rank (the figures were all-gathered): every rank exits non-zero
+        if rank == 0:
+            sys.stderr.write("bench.py: PARITY FAILURE, no result line printed\n" +
+                             "".join(f"  {f}\n" for f in parity_failures))
+        sys.exit(1)
     if rank == 0:
         print(json.dumps(line), flush=True)
 

@@ -169,10 +169,33 @@ int kh_attention_allgather(kh_context *ctx, const float *q, const float *k, cons
  * the call allocates and frees nothing. n may not exceed
  * kh_scan_noalloc_max_elements() (16,777,216; larger n is refused with code 2).
  * The owning device must be current; the first call on a device resolves the
- * array's address and should be made outside stream capture; calls on one
- * device share the array and must not overlap on the GPU. */
+ * array's address (under a lock: concurrent first calls are safe) and should
+ * be made outside stream capture; calls on one device share the array and
+ * must not overlap on the GPU. A look-back that runs out is not reported by
+ * this call: ask kh_scan_noalloc_status. */
 int kh_scan_noalloc(const float *x, float *y, int64_t n, void *stream);
 int64_t kh_scan_noalloc_max_elements(void);
+/* No counterpart in the reference. kh_scan_noalloc has no context that could
+ * report a look-back that ran out of its poll budget: this call waits for
+ * `stream`, reads the status word of the fixed array on the current device
+ * (an 8-byte copy, nothing is allocated) and returns 1001 when the last
+ * kh_scan_noalloc there stopped early and left y incomplete, else 0. */
+int kh_scan_noalloc_status(void *stream);
+
+/* No counterpart in the reference (whose kernels have no waits). A diagnostic
+ * that shows, on a healthy GPU and without any fault, what a device-side
+ * bounded wait that runs out looks like: the scan is launched with every tile
+ * ticket shifted by one, so tile 0 is never produced and the look-back of tile
+ * 1 gives up after `poll_limit` polls (1..1048576; a few thousand take about
+ * a millisecond). The kernel then stops and returns; the next kh_synchronize
+ * on the stream returns 1001 with the wait named in kh_last_error(), and the
+ * context stays usable. n must cover at least two 12288-element tiles; y is
+ * left incomplete. */
+int kh_scan_lookback_probe(kh_context *ctx, const float *x, float *y, int64_t n, uint32_t poll_limit,
+                           void *stream);
+/* Name of a device-side wait code as kh_synchronize reports it (1 = "scan
+ * look-back wait", 2 = "TMA (full-stage) wait", ...). */
+int kh_wait_name(uint32_t code, char *buf, int cap);
 
 /* Device memory of the context's device (Buffer::allocate / copy_from_host /
  * copy_to_host, include/kernelh/runtime/buffer.hpp). */

@@ -77,6 +77,9 @@ def _load() -> C.CDLL:
     L.kh_scan.argtypes = [vp, f32p, f32p, i64, vp]
     L.kh_scan_noalloc.argtypes = [f32p, f32p, i64, vp]
     L.kh_scan_noalloc_max_elements.restype = C.c_int64
+    L.kh_scan_noalloc_status.argtypes = [vp]
+    L.kh_scan_lookback_probe.argtypes = [vp, f32p, f32p, i64, C.c_uint32, vp]
+    L.kh_wait_name.argtypes = [C.c_uint32, C.c_char_p, C.c_int]
     L.kh_softmax.argtypes = [vp, f32p, f32p, i64, i64, vp]
     L.kh_layernorm.argtypes = [vp, f32p, f32p, f32p, f32p, i64, i64, vp]
     L.kh_gemm.argtypes = [vp, f32p, f32p, f32p, i64, i64, i64, vp]
@@ -225,6 +228,11 @@ class Context:
     def scan(self, x, y, n, stream=None):
         _check(lib.kh_scan(self._h, _ptr(x), _ptr(y), n, stream))
 
+    def scan_lookback_probe(self, x, y, n, poll_limit, stream=None):
+        """Diagnostic: a scan whose first look-back runs out of `poll_limit` polls on purpose
+        (no fault: the kernel stops and returns; `synchronize` then raises code 1001)."""
+        _check(lib.kh_scan_lookback_probe(self._h, _ptr(x), _ptr(y), n, poll_limit, stream))
+
     def softmax(self, x, y, rows, cols, stream=None):
         _check(lib.kh_softmax(self._h, _ptr(x), _ptr(y), rows, cols, stream))
 
@@ -288,6 +296,18 @@ def scan_noalloc(x, y, n: int, stream: int | None = None) -> None:
 
 def scan_noalloc_max_elements() -> int:
     return int(lib.kh_scan_noalloc_max_elements())
+
+
+def scan_noalloc_status(stream: int | None = None) -> None:
+    """Waits for `stream`; raises code 1001 when the last scan_noalloc on the current
+    device stopped on a look-back that ran out (reads 8 bytes, allocates nothing)."""
+    _check(lib.kh_scan_noalloc_status(stream))
+
+
+def wait_name(code: int) -> str:
+    buf = C.create_string_buffer(64)
+    lib.kh_wait_name(code, buf, 64)
+    return buf.value.decode()
 
 
 # --------------------------------------------------------------------------- host helpers

@@ -221,6 +221,19 @@ int kh_fused_gelu_bias(kh_context *ctx, const float *x, const float *bias, float
 int kh_scan(kh_context *ctx, const float *x, float *y, int64_t n, void *stream) {
   return launch_named(ctx, "scan", {{"n", n}}, {const_cast<float *>(x), y}, stream);
 }
+int kh_scan_lookback_probe(kh_context *ctx, const float *x, float *y, int64_t n, uint32_t poll_limit, void *stream) {
+  if (int rc = need_ctx(ctx)) return rc;
+  if (x == nullptr || y == nullptr) return set_error(2, "kh_scan_lookback_probe: null buffer");
+  return guarded([&] {
+    if (auto r = ctx->exec->backend().make_current(); !r) return set_error(r.error());
+    auto r = kh::run_scan_lookback_probe(*ctx->exec, x, y, n, poll_limit, stream);
+    return r ? 0 : set_error(r.error());
+  });
+}
+int kh_wait_name(uint32_t code, char *buf, int cap) {
+  copy_out(kh::Executor::wait_name(code), buf, cap);
+  return 0;
+}
 int kh_softmax(kh_context *ctx, const float *x, float *y, int64_t rows, int64_t cols, void *stream) {
   return launch_named(ctx, "softmax", {{"rows", rows}, {"cols", cols}}, {const_cast<float *>(x), y},
                       stream);

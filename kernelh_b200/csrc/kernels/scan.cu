@@ -1,5 +1,5 @@
-// scan: inclusive prefix sum of fp32 values, each prefix correctly rounded
-// from an fp64 running sum.
+// scan: inclusive prefix sum of fp32 values, each prefix rounded once from an
+// fp64 running sum.
 //
 // Replaces the reference's two kernels generated from
 // lib/dsl/kernels/scan.cpp:163-341 (`scan`: per-256 Blelloch scan in
@@ -7,51 +7,75 @@
 // all block totals serially per thread), whose tests require the output to
 // equal round-to-fp32 of the exact sum (test/unit/e2e_scan_test.cpp:231-241).
 // Here one launch does everything: a single-pass scan with decoupled
-// look-back. All arithmetic is fp64 (inputs widened on load, one rounding at
-// the store), so for the tested inputs (sums of < 2^20 values in [0,1) are
-// exact in fp64) any association order gives the same bits.
+// look-back. Sums that cross lanes, warps and tiles are fp64; inside a lane the
+// running sum that produces the outputs is fp64 too (one rounding per element),
+// so for the tested inputs (sums of < 2^20 values in [0,1) are exact in fp64)
+// any association order gives the same bits.
+//
+// Work split inside a block (one block per SM): twelve compute warps and one
+// look-back warp, no block-wide barrier after start-up. A tile is 12 x 1024
+// elements; compute warp w owns the w-th 1024 of them as 32 rows of 128 bytes,
+// one row (32 consecutive elements) per lane, in each of four tile buffers in
+// shared memory, and runs its own pipeline over them:
+//   load   one tensor-map copy (TMA) per warp and tile, 4 KiB, issued by one lane
+//          ahead of time; the copy engine applies the 128-byte swizzle, so a lane
+//          reads its 128 consecutive bytes without bank conflicts; rows past the
+//          end of the input arrive as zeros;
+//   A      lane sums (fp32 TwoSum pairs: the conversion unit is the narrowest pipe
+//          of the SM) -> fp64 shuffle scan -> the warp's total; the LAST warp of the
+//          block to get there sums the twelve totals and publishes the tile's
+//          aggregate at once, so aggregates never wait for a look-back;
+//   B      (two tiles later) offset from the look-back warp + lane prefix, running
+//          fp64 sum, one rounding per element, results written back over the
+//          lane's own bytes and sent out with one tensor-map copy per warp.
+// The look-back warp takes the block's tickets, and for every tile - not before
+// the block's NEXT tile has been summed, by when the neighbouring tiles'
+// aggregates are out and nothing has to be polled - runs the decoupled look-back
+// over the preceding tiles' descriptors and hands every compute warp its offset.
+// Tiles are claimed in ticket order, so a tile only ever waits for tiles that are
+// already being worked on.
 //
 // Parameters: (x, y, state) as rank-1 memref descriptors (15 eight-byte
-// parameters) followed by two scalars: `epoch` (u32) and `ticket_base` (u64).
-// `state` is scratch of 64-bit words owned by the caller:
-//   word 0            ticket counter (monotonic across launches)
+// parameters), two scalars - `spin_limit` (polls a look-back may spend on one
+// missing descriptor, 0 = default) and `tile_bias` (added to every ticket; 0 in
+// production, the bounded-wait probe passes 1 so that tile 0 is never produced and
+// the first look-back runs out) - then the tensor maps of x and y viewed as
+// [n / 32 rows][32 floats] (box 32 x 32, 128-byte swizzle) and `flags` (bit 0: the
+// x map is usable, bit 1: the y map; a side whose buffer is strided, not 16-byte
+// aligned or shorter than a row takes plain loads / stores instead).
+// `state` is scratch of 64-bit words owned by the caller, zeroed ONCE when it is
+// allocated and never again:
+//   word 0            ticket counter; back to 0 when a launch ends
 //   word 1            status word (low u32) + detail (high u32), 0 = clean
-//   words 2+2t, 3+2t  tile t: two self-validating halves of {fp64 value, tag}
-// A tag holds (epoch << 2) | s with s = 1 "the value is this tile's aggregate",
-// s = 2 "the value is the inclusive prefix up to this tile"; a tag of another
-// epoch reads as "nothing yet", so the scratch never has to be cleared between
-// launches: the host
-// passes a fresh epoch and the counter value at which this launch's tickets
-// start. Launches that share a state buffer must not overlap on the GPU.
+//   word 2            launch counter ("epoch"), advanced when a launch ends
+//   word 3            blocks of this launch that have finished
+//   words 4+2t, 5+2t  tile t: {fp64 value, tag}, read and written as ONE 128-bit word
+// A tag holds ((epoch + 1) << 2) | s with s = 1 "the value is this tile's
+// aggregate", s = 2 "the value is the inclusive prefix up to this tile"; a tag of
+// another epoch reads as "nothing yet", so descriptors are never cleared, and
+// because the counters are restored by the last block of a launch, a launch needs
+// no host-side bookkeeping (the same launch can be replayed from a CUDA graph).
+// Launches that share a state buffer must not overlap on the GPU.
 //
-// Tiles are claimed in ticket order (atomic counter), so a tile only ever
-// waits for tiles that are already running. Every wait is bounded: when the
-// look-back spin runs out, the kernel records kStatusScanLookbackTimeout in the
-// status word, stops and returns; other blocks see the word and stop too.
+// Every wait is bounded: when a look-back or a barrier wait runs out, the kernel
+// records a code in the status word, every role stops and the kernel returns.
 //
-// Data path: a block keeps a ring of three 16 KiB tile buffers in shared memory,
-// filled by bulk copies (TMA) that one thread starts two tiles ahead, so loads
-// never stop while a block waits in its look-back. The work on a tile is split
-// in two stages that are software-pipelined across tiles: stage A (as soon as
-// the tile's bytes have landed) forms the tile's total and publishes it as the
-// tile's aggregate; stage B (one tile later) does the look-back, the final
-// prefixes and the store, re-reading the tile from shared memory. Aggregates are
-// therefore visible about one tile-time before their own look-back starts, and a
-// look-back rarely has to wait for a predecessor.
-//
-// HBM-bound: 8 bytes per element; the scratch traffic is 16 bytes per
-// 4096-element tile.
+// HBM-bound: 8 bytes per element; descriptor traffic is 32 bytes per tile.
 #include "kh_tcgen05.cuh"
 
 namespace {
 
-constexpr int kThreads = 256;
-constexpr int kPerThread = 16;
-constexpr int kRows = kPerThread / 4;        // float4 per thread per tile
-constexpr int kTile = kThreads * kPerThread; // 4096 elements
-constexpr uint32_t kSpinLimit = 1u << 22;
-constexpr int kLook = 8; // tile descriptors each lane reads per look-back step
-constexpr int kSlots = 3; // tile buffers per block: one being stored, one reduced, one loading
+constexpr int kWarps = 12;                     // compute warps; warp kWarps is the look-back warp
+constexpr int kSlots = 4;                      // tile buffers per block
+constexpr int kLag = 2;                        // stage B runs two tiles behind stage A
+constexpr int kLaneElems = 32;                 // consecutive elements a lane owns in a tile
+constexpr int kUnits = kLaneElems / 4;         // 16-byte units per lane
+constexpr int kWarpElems = 32 * kLaneElems;    // a warp's part of a tile: 32 rows, one per lane
+constexpr int kPartBytes = kWarpElems * 4;
+constexpr int kTile = kWarps * kWarpElems;     // 12288 elements
+constexpr int kLook = 6;                       // descriptors each lane reads per look-back step
+constexpr uint32_t kDefaultSpinLimit = 1u << 22;
+constexpr uint32_t kFlagTmaIn = 1u, kFlagTmaOut = 2u;
 
 __device__ __forceinline__ uint32_t ld_relaxed_u32(const uint32_t *p) {
   uint32_t v;
@@ -59,219 +83,387 @@ __device__ __forceinline__ uint32_t ld_relaxed_u32(const uint32_t *p) {
   return v;
 }
 
-// A tile descriptor is two 64-bit words, each {32 bits of the fp64 value, tag},
-// tag = (epoch << 2) | status. Each word is written whole, so a reader that
-// finds the same valid tag in both words has a consistent value without any
-// fence or second dependent load: one 128-bit load per look-back step.
-__device__ __forceinline__ void publish(unsigned long long *slot, double value, uint32_t tag) {
+// A tile descriptor is one 16-byte word {value bits, tag}; 128-bit relaxed
+// accesses are single-copy atomic, so a reader sees a value together with its tag.
+__device__ __forceinline__ void publish(unsigned long long *slot, double value, unsigned long long tag) {
   const unsigned long long bits = static_cast<unsigned long long>(__double_as_longlong(value));
-  const unsigned long long w0 = (bits & 0xFFFFFFFF00000000ull) | tag;
-  const unsigned long long w1 = (bits << 32) | tag;
-  asm volatile("st.relaxed.gpu.global.v2.u64 [%0], {%1, %2};" ::"l"(slot), "l"(w0), "l"(w1) : "memory");
+  asm volatile("{\n\t.reg .b128 t;\n\tmov.b128 t, {%0, %1};\n\tst.relaxed.gpu.global.b128 [%2], t;\n\t}" ::"l"(bits),
+               "l"(tag), "l"(slot)
+               : "memory");
 }
-__device__ __forceinline__ void load_descriptor(const unsigned long long *slot, unsigned long long &w0,
-                                                unsigned long long &w1) {
-  asm volatile("ld.relaxed.gpu.global.v2.u64 {%0, %1}, [%2];" : "=l"(w0), "=l"(w1) : "l"(slot) : "memory");
+__device__ __forceinline__ void load_descriptor(const unsigned long long *slot, unsigned long long &bits,
+                                                unsigned long long &tag) {
+  asm volatile("{\n\t.reg .b128 t;\n\tld.relaxed.gpu.global.b128 t, [%2];\n\tmov.b128 {%0, %1}, t;\n\t}"
+               : "=l"(bits), "=l"(tag)
+               : "l"(slot)
+               : "memory");
 }
-// Returns the status (0 = nothing usable yet) and the value.
-__device__ __forceinline__ uint32_t decode_descriptor(unsigned long long w0, unsigned long long w1,
-                                                      uint32_t epoch, double *value) {
-  const uint32_t t0 = static_cast<uint32_t>(w0), t1 = static_cast<uint32_t>(w1);
-  if (t0 != t1 || (t0 >> 2) != epoch) return 0u;
-  *value = __longlong_as_double(static_cast<long long>((w0 & 0xFFFFFFFF00000000ull) | (w1 >> 32)));
-  return t0 & 3u;
+// 0 = nothing usable yet, 1 = aggregate, 2 = inclusive prefix.
+__device__ __forceinline__ uint32_t descriptor_status(unsigned long long tag, unsigned long long epoch_tag) {
+  return (tag >> 2) == epoch_tag ? static_cast<uint32_t>(tag & 3ull) : 0u;
+}
+
+// Byte offset, inside a warp's 4 KiB part, of 16-byte unit `u` (0..255) of the part's 1024
+// elements: row u >> 3 (128 bytes, one lane's elements), unit u & 7 of the row stored at
+// position (u & 7) ^ (row & 7). This is the 128-byte swizzle of the tensor-map copies; a
+// part starts on a 1 KiB boundary of the shared-memory window.
+__device__ __forceinline__ uint32_t unit_offset(uint32_t u) {
+  const uint32_t row = u >> 3;
+  return ((row << 3) | ((u & 7u) ^ (row & 7u))) << 4;
+}
+
+__device__ __forceinline__ void tma_store_2d(const khd::TensorMap *map, int x, int y, uint32_t smem_src) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.tile.bulk_group [%0, {%1, %2}], [%3];" ::"l"(
+                   reinterpret_cast<uint64_t>(map)),
+               "r"(x), "r"(y), "r"(smem_src)
+               : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_read_all() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+__device__ __forceinline__ void fence_proxy_async_smem() {
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
 }
 
 } // namespace
 
-extern "C" __global__ void __launch_bounds__(kThreads, 4)
-scan(KH_MEMREF1(const float, x), KH_MEMREF1(float, y), KH_MEMREF1(unsigned long long, state),
-     uint32_t epoch, unsigned long long ticket_base) {
-  extern __shared__ __align__(16) uint8_t ring_raw[]; // kSlots tile buffers
-  __shared__ __align__(8) uint64_t full_bar[kSlots];
-  __shared__ long long s_tile[kSlots]; // tile held by each buffer; >= num_tiles: none
-  __shared__ double warp_totals[kRows * (kThreads / 32)];
-  __shared__ double s_exclusive;
+extern "C" __global__ void __launch_bounds__((kWarps + 1) * 32, 1)
+scan(KH_MEMREF1(const float, x), KH_MEMREF1(float, y), KH_MEMREF1(unsigned long long, state), uint32_t spin_limit,
+     uint32_t tile_bias, const __grid_constant__ khd::TensorMap x_map, const __grid_constant__ khd::TensorMap y_map,
+     uint32_t flags) {
+  extern __shared__ __align__(1024) uint8_t ring_unaligned[]; // kSlots tile buffers + 1 KiB of slack
+  __shared__ __align__(8) uint64_t a_done[kSlots];         // 1 arrival: the tile's aggregate is published
+  __shared__ __align__(8) uint64_t lb_done[kSlots];        // 1 arrival: offsets and the next tile index are written
+  __shared__ __align__(8) uint64_t full[kSlots][kWarps];   // 1 arrival (+ bytes): a warp's part of the tile has landed
+  __shared__ double totals[kSlots][kWarps];
+  __shared__ double warp_excl[kSlots][kWarps];
+  __shared__ double offsets[kSlots][kWarps];
+  __shared__ double aggregates[kSlots];
+  __shared__ unsigned long long s_tile[kSlots]; // tile the buffer holds (or will hold next); >= num_tiles: none
+  __shared__ unsigned int arrivals[kSlots];
   __shared__ int s_abort;
 
   const float *__restrict__ x = KH_DATA(x);
   float *__restrict__ y = KH_DATA(y);
   unsigned long long *state = KH_DATA(state);
   const int64_t n = x_size0;
-  const int64_t num_tiles = (n + kTile - 1) / kTile;
+  const unsigned long long num_tiles = static_cast<unsigned long long>((n + kTile - 1) / kTile);
   uint32_t *status = reinterpret_cast<uint32_t *>(state + 1);
-  float *ring = reinterpret_cast<float *>(ring_raw);
-
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const bool bulk_ok = khd::is_aligned16(x) && x_stride0 == 1; // tiles start 16 KiB apart
-  const bool vec_out = khd::is_aligned16(y) && y_stride0 == 1;
-  const uint32_t bar0 = khd::smem_u32(&full_bar[0]);
+  // the swizzled parts must start on 1 KiB boundaries of the shared-memory window
+  uint8_t *ring_raw = ring_unaligned + ((1024u - (khd::smem_u32(ring_unaligned) & 1023u)) & 1023u);
+  const uint32_t ring = khd::smem_u32(ring_raw);
+  const uint32_t a_bar = khd::smem_u32(&a_done[0]), lb_bar = khd::smem_u32(&lb_done[0]);
+  if (spin_limit == 0) spin_limit = kDefaultSpinLimit;
 
   if (tid == 0) {
     s_abort = 0;
-    for (int s = 0; s < kSlots; ++s) khd::mbar_init(bar0 + 8 * s, 1);
+    for (int s = 0; s < kSlots; ++s) {
+      khd::mbar_init(a_bar + 8 * s, 1);
+      khd::mbar_init(lb_bar + 8 * s, 1);
+      for (int w = 0; w < kWarps; ++w) khd::mbar_init(khd::smem_u32(&full[s][w]), 1);
+      arrivals[s] = 0u;
+    }
     khd::mbar_fence_init();
   }
+  // the launch's epoch: every warp reads it (whichever warp ends a tile's stage A publishes)
+  unsigned long long epoch_tag = 0;
+  if (lane == 0) epoch_tag = state[2] + 1;
+  epoch_tag = __shfl_sync(0xffffffffu, epoch_tag, 0);
   __syncthreads();
 
-  // Thread 0 only. Takes the next ticket (tiles are claimed in ticket order, and a
-  // block works through its tiles in the order it claimed them, so a tile only ever
-  // waits for tiles that are being worked on) and starts the copy of that tile into
-  // `slot`. Once a ticket is past the end no more are taken: every block ends on
-  // exactly one surplus ticket, so a clean launch moves the counter by
-  // num_tiles + gridDim.x, which is what the host advances ticket_base by.
-  bool exhausted = false;
-  const auto fill = [&](int slot) {
-    long long tile = num_tiles;
-    if (!exhausted) {
-      tile = static_cast<long long>(atomicAdd(state, 1ull) - ticket_base);
-      exhausted = tile >= num_tiles;
-    }
-    s_tile[slot] = tile < num_tiles ? tile : num_tiles;
-    if (tile >= num_tiles || !bulk_ok) return;
-    const int64_t base = tile * kTile;
-    const int64_t count = (n - base < kTile) ? (n - base) : kTile;
-    const uint32_t bytes = static_cast<uint32_t>(count * 4) & ~15u;
-    float *dst = ring + slot * kTile;
-    for (int64_t e = bytes / 4; e < count; ++e) dst[e] = x[base + e]; // at most 3 tail elements
-    if (bytes != 0) {
-      khd::mbar_arrive_expect_tx(bar0 + 8 * slot, bytes);
-      asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
-                       khd::smem_u32(dst)),
-                   "l"(x + base), "r"(bytes), "r"(bar0 + 8 * slot)
-                   : "memory");
-    } else {
-      khd::mbar_arrive(bar0 + 8 * slot);
-    }
-  };
-
-  // Stage A of the block's seq-th tile: wait for its bytes, form the per-thread
-  // exclusive offsets inside the tile and the tile total, publish the total.
-  // Element order inside a tile: kRows rows of 1024 elements; thread t owns the
-  // four consecutive elements 4t..4t+3 of every row, so each shared-memory read
-  // and each global store of a warp covers one contiguous 512-byte run.
-  // Returns false when a wait ran out (block-uniform).
-  const auto stage_a = [&](int seq, int64_t tile, double (&thread_exclusive)[kRows], double &block_total) -> bool {
-    const int slot = seq % kSlots;
-    float *buf = ring + slot * kTile;
-    const int64_t tile_base = tile * kTile;
-    if (bulk_ok) {
-      const bool ok = khd::mbar_wait(bar0 + 8 * slot, static_cast<uint32_t>(seq / kSlots) & 1u, &s_abort, status,
-                                     khd::kStatusTmaWaitTimeout, static_cast<uint32_t>(tile));
-      if (__syncthreads_or(!ok)) return false;
-    } else {
-      // strided or misaligned input: the threads fetch the tile themselves
-      for (int e = tid; e < kTile; e += kThreads)
-        buf[e] = tile_base + e < n ? x[(tile_base + e) * x_stride0] : 0.f;
-      __syncthreads();
-    }
-    const bool full_tile = tile_base + kTile <= n;
-    double run_total[kRows], incl[kRows];
-#pragma unroll
-    for (int i = 0; i < kRows; ++i) {
-      float4 f = *reinterpret_cast<const float4 *>(buf + i * (kThreads * 4) + tid * 4);
-      if (!full_tile) {
-        const int64_t e = tile_base + i * (kThreads * 4) + tid * 4;
-        if (e >= n) f.x = 0.f;
-        if (e + 1 >= n) f.y = 0.f;
-        if (e + 2 >= n) f.z = 0.f;
-        if (e + 3 >= n) f.w = 0.f;
-      }
-      run_total[i] = ((static_cast<double>(f.x) + static_cast<double>(f.y)) + static_cast<double>(f.z)) +
-                     static_cast<double>(f.w);
-      incl[i] = run_total[i];
-    }
-#pragma unroll
-    for (int o = 1; o < 32; o <<= 1) {
-#pragma unroll
-      for (int i = 0; i < kRows; ++i) {
-        const double up = __shfl_up_sync(0xffffffffu, incl[i], o);
-        if (lane >= o) incl[i] += up;
+  // Every completion of lb_done[slot] announces the tile index in s_tile[slot]: the first
+  // one the block's tile number `slot`, each later one the tile kSlots further on (together
+  // with the offsets of the tile that was in the buffer until then).
+  if (warp == kWarps) {
+    // The block's first tickets, one after the other: drawn together they would be
+    // consecutive tiles, and every block would then hold a tile that its neighbour's first
+    // look-back needs but that is not summed before the block's own first tiles are through.
+    bool none_left = false;
+    for (int s = 0; s < kSlots; ++s) {
+      unsigned long long t = ~0ull;
+      if (!none_left && lane == 0) t = atomicAdd(state, 1ull) + tile_bias;
+      t = __shfl_sync(0xffffffffu, t, 0);
+      if (t >= num_tiles) none_left = true;
+      if (lane == 0) {
+        s_tile[s] = t;
+        khd::mbar_arrive(lb_bar + 8 * s);
       }
     }
-    if (lane == 31) {
-#pragma unroll
-      for (int i = 0; i < kRows; ++i) warp_totals[i * (kThreads / 32) + warp] = incl[i];
-    }
-    __syncthreads();
-    // (row, warp) totals in element order; everything before mine is my offset
-    double running = 0.0;
-#pragma unroll
-    for (int i = 0; i < kRows; ++i) {
-#pragma unroll
-      for (int w = 0; w < kThreads / 32; ++w) {
-        if (w == warp) thread_exclusive[i] = running + (incl[i] - run_total[i]);
-        running += warp_totals[i * (kThreads / 32) + w];
-      }
-    }
-    block_total = running;
-    // tile 0 has nothing before it: its total already is its inclusive prefix
-    if (tid == 0) publish(state + 2 + 2 * tile, block_total, (epoch << 2) | (tile == 0 ? 2u : 1u));
-    return true;
-  };
-
-  if (tid == 0) {
-    fill(0);
-    fill(1);
   }
-  __syncthreads();
-  double next_exclusive[kRows] = {};
-  double next_total = 0.0;
-  if (s_tile[0] < num_tiles && !stage_a(0, s_tile[0], next_exclusive, next_total)) return;
 
-  for (int seq = 0;; ++seq) {
-    const int64_t tile = s_tile[seq % kSlots];
-    if (tile >= num_tiles) break;
-    double thread_exclusive[kRows];
+  if (warp < kWarps) {
+    // ======================= compute warp =======================
+    const bool tma_in = (flags & kFlagTmaIn) != 0u, tma_out = (flags & kFlagTmaOut) != 0u;
+    const int64_t full_rows = n / kLaneElems;           // rows the tensor maps cover
+    const int tail = static_cast<int>(n % kLaneElems); // elements of the last, partial row
+    const uint32_t my_part = static_cast<uint32_t>(warp) * kPartBytes;
+    uint32_t own_off[kUnits];
 #pragma unroll
-    for (int i = 0; i < kRows; ++i) thread_exclusive[i] = next_exclusive[i];
-    const double block_total = next_total;
-    // the buffer of the tile before this one is free: start the tile after next
-    if (tid == 0) fill((seq + 2) % kSlots);
-    // stage A of the next tile first, so that its aggregate is out before this
-    // tile's look-back begins (stage_a's barriers also publish s_tile to the block)
-    const int64_t next_tile = s_tile[(seq + 1) % kSlots];
-    if (next_tile < num_tiles && !stage_a(seq + 1, next_tile, next_exclusive, next_total)) break;
+    for (int j = 0; j < kUnits; ++j) own_off[j] = unit_offset(static_cast<uint32_t>(lane * kUnits + j));
 
-    // ---- decoupled look-back (warp 0): kLook descriptors per lane, so one
-    //      round trip to L2 covers a window of 32 * kLook preceding tiles --------
-    if (warp == 0) {
-      unsigned long long *slot = state + 2 + 2 * tile;
+    // Starts the copy of this warp's part of `tile` into buffer `slot`. Rows past the end
+    // of the tensor arrive as zeros; a part that lies wholly past the end is not copied.
+    const auto load = [&](int slot, unsigned long long tile) {
+      if (tile >= num_tiles) return;
+      const int64_t base = static_cast<int64_t>(tile) * kTile + warp * kWarpElems;
+      if (base >= n) return;
+      const uint32_t bar = khd::smem_u32(&full[slot][warp]);
+      if (tma_in) {
+        if (lane == 0) {
+          khd::mbar_arrive_expect_tx(bar, kPartBytes);
+          khd::tma_load_2d(ring + slot * (kTile * 4) + my_part, &x_map, 0, static_cast<int>(base / kLaneElems), bar);
+        }
+      } else {
+        // strided, misaligned or very short input: plain loads, element by element
+        uint8_t *buf = ring_raw + slot * (kTile * 4) + my_part;
+        for (int u = lane; u < 32 * kUnits; u += 32) {
+          float4 v;
+          const int64_t e = base + u * 4;
+          v.x = e < n ? x[e * x_stride0] : 0.f;
+          v.y = e + 1 < n ? x[(e + 1) * x_stride0] : 0.f;
+          v.z = e + 2 < n ? x[(e + 2) * x_stride0] : 0.f;
+          v.w = e + 3 < n ? x[(e + 3) * x_stride0] : 0.f;
+          *reinterpret_cast<float4 *>(buf + unit_offset(static_cast<uint32_t>(u))) = v;
+        }
+        __syncwarp();
+        if (lane == 0) khd::mbar_arrive(bar);
+      }
+    };
+
+    bool ok = true;
+    for (int s = 0; s < kSlots && ok; ++s) {
+      ok = khd::mbar_wait(lb_bar + 8 * s, 0u, &s_abort, status, khd::kStatusEpilogueWaitTimeout, 0xffffffffu);
+      if (ok) load(s, s_tile[s]);
+    }
+
+    // Iteration i: stage A of tile i (its aggregate goes out as early as possible), the refill
+    // of the buffer that tile i - 3 left in the last iteration, then stage B of tile i - 2.
+    double excl[kLag] = {};           // lane's exclusive prefix in tiles i-1, i-2
+    unsigned long long pending[kLag]; // tiles i-1, i-2 (~0: none)
+#pragma unroll
+    for (int k = 0; k < kLag; ++k) pending[k] = ~0ull;
+    for (int seq = 0; ok; ++seq) {
+      const int slot = seq % kSlots;
+      const unsigned long long tile = s_tile[slot];
+      double lane_exclusive = 0.0;
+      if (tile < num_tiles) {
+        // ---- stage A ----
+        const int64_t base = static_cast<int64_t>(tile) * kTile + warp * kWarpElems;
+        double incl = 0.0;
+        if (base < n) { // warp-uniform
+          ok = khd::mbar_wait(khd::smem_u32(&full[slot][warp]), static_cast<uint32_t>(seq / kSlots) & 1u, &s_abort,
+                              status, khd::kStatusTmaWaitTimeout, static_cast<uint32_t>(tile));
+          if (!ok) break;
+          uint8_t *part = ring_raw + slot * (kTile * 4) + my_part;
+          if (tma_in && tail != 0 && full_rows >= base / kLaneElems && full_rows < base / kLaneElems + 32) {
+            // the tensor map stops before the partial last row: its owner fetches it
+            if (lane == static_cast<int>(full_rows - base / kLaneElems)) {
+              const int64_t e0 = full_rows * kLaneElems;
+#pragma unroll
+              for (int j = 0; j < kUnits; ++j) {
+                float4 v;
+                v.x = 4 * j < tail ? x[e0 + 4 * j] : 0.f;
+                v.y = 4 * j + 1 < tail ? x[e0 + 4 * j + 1] : 0.f;
+                v.z = 4 * j + 2 < tail ? x[e0 + 4 * j + 2] : 0.f;
+                v.w = 4 * j + 3 < tail ? x[e0 + 4 * j + 3] : 0.f;
+                *reinterpret_cast<float4 *>(part + own_off[j]) = v;
+              }
+            }
+            __syncwarp();
+          }
+          // Lane sum in fp32 pairs: TwoSum keeps the rounding error of every addition, so a
+          // pair (hi, lo) holds its sum to about 48 bits (exactly, when it needs no more) without
+          // touching the conversion unit; four independent chains, widened once at the end.
+          float hi[4] = {0.f, 0.f, 0.f, 0.f}, lo[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+          for (int j = 0; j < kUnits; ++j) {
+            const float4 f = *reinterpret_cast<const float4 *>(part + own_off[j]);
+            const float xs[4] = {f.x, f.y, f.z, f.w};
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              const float s2 = hi[q] + xs[q];
+              const float v = s2 - hi[q];
+              lo[q] += (hi[q] - (s2 - v)) + (xs[q] - v);
+              hi[q] = s2;
+            }
+          }
+          double part_sum[4];
+#pragma unroll
+          for (int q = 0; q < 4; ++q) // a non-finite input leaves NaN in lo: the sum is then hi alone
+            part_sum[q] = lo[q] == lo[q] ? static_cast<double>(hi[q]) + static_cast<double>(lo[q])
+                                         : static_cast<double>(hi[q]);
+          incl = (part_sum[0] + part_sum[1]) + (part_sum[2] + part_sum[3]);
+#pragma unroll
+          for (int o = 1; o < 32; o <<= 1) {
+            const double up = __shfl_up_sync(0xffffffffu, incl, o);
+            if (lane >= o) incl += up;
+          }
+          lane_exclusive = __shfl_up_sync(0xffffffffu, incl, 1);
+          if (lane == 0) lane_exclusive = 0.0;
+        }
+        // The warp's total. The last warp of the block to get here sums the totals and publishes
+        // the tile's aggregate at once, whatever the look-back warp is doing.
+        unsigned int before = 0;
+        if (lane == 31) {
+          totals[slot][warp] = incl;
+          __threadfence_block();
+          before = atomicAdd(&arrivals[slot], 1u);
+        }
+        before = __shfl_sync(0xffffffffu, before, 31);
+        if (before == kWarps - 1) {
+          __threadfence_block();
+          double t_incl = lane < kWarps ? totals[slot][lane] : 0.0;
+#pragma unroll
+          for (int o = 1; o < kWarps; o <<= 1) {
+            const double up = __shfl_up_sync(0xffffffffu, t_incl, o);
+            if (lane >= o) t_incl += up;
+          }
+          const double aggregate = __shfl_sync(0xffffffffu, t_incl, kWarps - 1);
+          double w_excl = __shfl_up_sync(0xffffffffu, t_incl, 1);
+          if (lane == 0) w_excl = 0.0;
+          if (lane < kWarps) warp_excl[slot][lane] = w_excl;
+          if (lane == 0) {
+            // tile 0 has nothing before it: its aggregate already is its inclusive prefix
+            publish(state + 4 + 2 * tile, aggregate, (epoch_tag << 2) | (tile == 0 ? 2ull : 1ull));
+            aggregates[slot] = aggregate;
+            arrivals[slot] = 0u;
+          }
+          __syncwarp();
+          if (lane == 0) khd::mbar_arrive(a_bar + 8 * slot);
+        }
+      }
+      if (seq >= kLag + 1) {
+        // The buffer whose stage B ended in the last iteration gets the block's next tile now:
+        // the copy out of it, started then, has had all of stage A to read it, so nothing waits
+        // here, and the new bytes have all of stage B to arrive.
+        const int rslot = (seq - kLag - 1) % kSlots;
+        const unsigned long long next = s_tile[rslot];
+        if (next < num_tiles) {
+          if (lane == 0) bulk_wait_read_all();
+          __syncwarp();
+          load(rslot, next);
+        }
+      }
+      const unsigned long long due = pending[kLag - 1];
+      if (due != ~0ull) {
+        // ---- stage B of tile seq - 2 ----
+        const int pslot = (seq + kSlots - kLag) % kSlots;
+        ok = khd::mbar_wait(lb_bar + 8 * pslot, static_cast<uint32_t>((seq - kLag) / kSlots + 1) & 1u, &s_abort, status,
+                            khd::kStatusEpilogueWaitTimeout, static_cast<uint32_t>(due));
+        if (!ok) break;
+        const int64_t base = static_cast<int64_t>(due) * kTile + warp * kWarpElems;
+        if (base < n) { // warp-uniform
+          uint8_t *part = ring_raw + pslot * (kTile * 4) + my_part;
+          double run = offsets[pslot][warp] + excl[kLag - 1];
+          const int64_t row = base / kLaneElems + lane; // this lane's row of the tensor
+          if (tma_out) {
+#pragma unroll
+            for (int j = 0; j < kUnits; ++j) {
+              float4 f = *reinterpret_cast<const float4 *>(part + own_off[j]);
+              run += static_cast<double>(f.x); f.x = static_cast<float>(run);
+              run += static_cast<double>(f.y); f.y = static_cast<float>(run);
+              run += static_cast<double>(f.z); f.z = static_cast<float>(run);
+              run += static_cast<double>(f.w); f.w = static_cast<float>(run);
+              *reinterpret_cast<float4 *>(part + own_off[j]) = f;
+              if (row == full_rows) { // the partial last row is not covered by the tensor map
+                const int64_t e = row * kLaneElems + 4 * j;
+                if (4 * j < tail) y[e] = f.x;
+                if (4 * j + 1 < tail) y[e + 1] = f.y;
+                if (4 * j + 2 < tail) y[e + 2] = f.z;
+                if (4 * j + 3 < tail) y[e + 3] = f.w;
+              }
+            }
+            fence_proxy_async_smem(); // the copy engine reads what these stores wrote
+            __syncwarp();
+            if (lane == 0 && base / kLaneElems < full_rows)
+              tma_store_2d(&y_map, 0, static_cast<int>(base / kLaneElems), ring + pslot * (kTile * 4) + my_part);
+          } else {
+            // strided, misaligned or very short output: every lane stores its own 32 results
+            const int64_t e0 = base + lane * kLaneElems;
+#pragma unroll
+            for (int j = 0; j < kUnits; ++j) {
+              const float4 f = *reinterpret_cast<const float4 *>(part + own_off[j]);
+              const int64_t e = e0 + 4 * j;
+              run += static_cast<double>(f.x); if (e < n) y[e * y_stride0] = static_cast<float>(run);
+              run += static_cast<double>(f.y); if (e + 1 < n) y[(e + 1) * y_stride0] = static_cast<float>(run);
+              run += static_cast<double>(f.z); if (e + 2 < n) y[(e + 2) * y_stride0] = static_cast<float>(run);
+              run += static_cast<double>(f.w); if (e + 3 < n) y[(e + 3) * y_stride0] = static_cast<float>(run);
+            }
+            __syncwarp();
+          }
+        }
+        if (lane == 0) bulk_commit(); // one group per stage B, with or without a copy in it
+      }
+      bool any_pending = false;
+#pragma unroll
+      for (int k = 0; k + 1 < kLag; ++k) any_pending |= pending[k] != ~0ull;
+      if (tile >= num_tiles && !any_pending) break; // nothing left in flight
+#pragma unroll
+      for (int k = kLag - 1; k > 0; --k) {
+        pending[k] = pending[k - 1];
+        excl[k] = excl[k - 1];
+      }
+      pending[0] = tile < num_tiles ? tile : ~0ull;
+      excl[0] = lane_exclusive;
+    }
+    if (lane == 0) bulk_wait_all();
+  } else {
+    // ======================= look-back warp =======================
+    bool exhausted = false;
+    for (int seq = 0;; ++seq) {
+      const int slot = seq % kSlots;
+      const uint32_t parity = static_cast<uint32_t>(seq / kSlots) & 1u;
+      const unsigned long long tile = s_tile[slot];
+      if (tile >= num_tiles) break;
+      // the block's next ticket: asked for now, needed only when this look-back is over
+      unsigned long long next_tile = ~0ull;
+      if (!exhausted && lane == 0) next_tile = atomicAdd(state, 1ull) + tile_bias;
+      bool ok = khd::mbar_wait(a_bar + 8 * slot, parity, &s_abort, status, khd::kStatusMmaWaitTimeout,
+                               static_cast<uint32_t>(tile));
+      if (!ok) break;
+      {
+        // Not before the block's next tile is summed too: the offsets are wanted two tiles later,
+        // and by then the tiles before this one, which other blocks sum at about the same
+        // time, have their aggregates out, so the look-back finds them without polling.
+        const int nslot = (seq + 1) % kSlots;
+        if (s_tile[nslot] < num_tiles) {
+          ok = khd::mbar_wait(a_bar + 8 * nslot, static_cast<uint32_t>((seq + 1) / kSlots) & 1u, &s_abort, status,
+                              khd::kStatusMmaWaitTimeout, 0xfffffffcu);
+          if (!ok) break;
+        }
+      }
       double exclusive = 0.0;
       bool aborted = false;
+      unsigned long long *desc = state + 4 + 2 * tile;
       if (tile != 0) { // tile 0 published its inclusive prefix in stage A
-        int64_t window_end = tile; // look at tiles [window_end - 32*kLook, window_end)
+        unsigned long long window_end = tile; // look at tiles [window_end - 32 * kLook, window_end)
         while (true) {
-          uint32_t st[kLook];
-          double val[kLook];
-          unsigned long long w0[kLook], w1[kLook];
+          unsigned long long bits[kLook], tag[kLook];
           // all loads of the window are issued before any result is looked at,
           // so one step costs one round trip to L2 whatever kLook is
 #pragma unroll
           for (int k = 0; k < kLook; ++k) {
-            const int64_t t = window_end - 1 - (32 * k + lane);
-            w0[k] = w1[k] = 0ull;
-            if (t >= 0) load_descriptor(state + 2 + 2 * t, w0[k], w1[k]);
+            const unsigned long long back = static_cast<unsigned long long>(32 * k + lane) + 1;
+            bits[k] = 0ull;
+            tag[k] = (epoch_tag << 2) | 2ull; // positions before tile 0 act as "inclusive prefix 0"
+            if (back <= window_end) load_descriptor(state + 4 + 2 * (window_end - back), bits[k], tag[k]);
           }
+          uint32_t st[kLook];
 #pragma unroll
           for (int k = 0; k < kLook; ++k) {
-            const int64_t t = window_end - 1 - (32 * k + lane);
-            st[k] = 2u; // positions before tile 0 act as "inclusive prefix 0"
-            val[k] = 0.0;
-            if (t >= 0) st[k] = decode_descriptor(w0[k], w1[k], epoch, &val[k]);
-          }
-#pragma unroll
-          for (int k = 0; k < kLook; ++k) {
-            const int64_t t = window_end - 1 - (32 * k + lane);
+            const unsigned long long back = static_cast<unsigned long long>(32 * k + lane) + 1;
+            st[k] = descriptor_status(tag[k], epoch_tag);
             uint32_t spins = 0;
             while (st[k] == 0u && !aborted) {
-              if (++spins > kSpinLimit || ((spins & 1023u) == 0u && ld_relaxed_u32(status) != 0u)) {
+              if (++spins > spin_limit ||
+                  ((spins & 255u) == 0u && (*static_cast<volatile int *>(&s_abort) || ld_relaxed_u32(status) != 0u))) {
                 aborted = true;
                 break;
               }
-              __nanosleep(20);
-              load_descriptor(state + 2 + 2 * t, w0[k], w1[k]);
-              st[k] = decode_descriptor(w0[k], w1[k], epoch, &val[k]);
+              __nanosleep(32);
+              load_descriptor(state + 4 + 2 * (window_end - back), bits[k], tag[k]);
+              st[k] = descriptor_status(tag[k], epoch_tag);
             }
           }
           if (__any_sync(0xffffffffu, aborted)) {
@@ -287,7 +479,7 @@ scan(KH_MEMREF1(const float, x), KH_MEMREF1(float, y), KH_MEMREF1(unsigned long 
             const uint32_t incl_mask = __ballot_sync(0xffffffffu, st[k] == 2u);
             if (!found) {
               const int first = incl_mask ? (__ffs(incl_mask) - 1) : 32;
-              if (lane <= first) contrib += val[k];
+              if (lane <= first) contrib += __longlong_as_double(static_cast<long long>(bits[k]));
               found = incl_mask != 0u;
             }
           }
@@ -295,50 +487,36 @@ scan(KH_MEMREF1(const float, x), KH_MEMREF1(float, y), KH_MEMREF1(unsigned long 
           for (int o = 16; o > 0; o >>= 1) contrib += __shfl_xor_sync(0xffffffffu, contrib, o);
           exclusive += contrib;
           if (found) break;
-          window_end -= 32 * kLook;
-        }
-        if (aborted) {
-          if (lane == 0) khd::report_status(status, khd::kStatusScanLookbackTimeout,
-                                            static_cast<uint32_t>(tile));
-        } else if (lane == 0) {
-          publish(slot, exclusive + block_total, (epoch << 2) | 2u);
+          window_end -= 32 * kLook; // nothing inclusive in the window: every position was a real tile
         }
       }
-      if (lane == 0) {
-        s_exclusive = exclusive;
-        if (aborted) s_abort = 1;
+      if (aborted) {
+        if (lane == 0) {
+          khd::report_status(status, khd::kStatusScanLookbackTimeout, static_cast<uint32_t>(tile));
+          s_abort = 1;
+        }
+        break;
       }
+      const double aggregate = aggregates[slot];
+      if (lane == 0 && tile != 0) publish(desc, exclusive + aggregate, (epoch_tag << 2) | 2ull);
+      if (lane < kWarps) offsets[slot][lane] = exclusive + warp_excl[slot][lane];
+      next_tile = __shfl_sync(0xffffffffu, next_tile, 0);
+      if (!exhausted && next_tile >= num_tiles) exhausted = true;
+      if (lane == 0) s_tile[slot] = next_tile; // ~0 once exhausted: "none"
+      __syncwarp();
+      if (lane == 0) khd::mbar_arrive(lb_bar + 8 * slot);
     }
-    __syncthreads();
-    if (s_abort) break;
-    const double tile_offset = s_exclusive;
-
-
-    // ---- store (one rounding per element), values re-read from the tile buffer --------
-    const float *buf = ring + (seq % kSlots) * kTile;
-    const int64_t tile_base = tile * kTile;
-    const bool full_tile = tile_base + kTile <= n;
-#pragma unroll
-    for (int i = 0; i < kRows; ++i) {
-      const float4 f = *reinterpret_cast<const float4 *>(buf + i * (kThreads * 4) + tid * 4);
-      double o = tile_offset + thread_exclusive[i];
-      float4 r;
-      o += static_cast<double>(f.x); r.x = static_cast<float>(o);
-      o += static_cast<double>(f.y); r.y = static_cast<float>(o);
-      o += static_cast<double>(f.z); r.z = static_cast<float>(o);
-      o += static_cast<double>(f.w); r.w = static_cast<float>(o);
-      const int64_t e = tile_base + i * (kThreads * 4) + tid * 4;
-      if (vec_out && full_tile) {
-        __stcs(reinterpret_cast<float4 *>(y + e), r);
-      } else {
-        if (e < n) y[e * y_stride0] = r.x;
-        if (e + 1 < n) y[(e + 1) * y_stride0] = r.y;
-        if (e + 2 < n) y[(e + 2) * y_stride0] = r.z;
-        if (e + 3 < n) y[(e + 3) * y_stride0] = r.w;
-      }
-    }
-    __syncthreads(); // the tile buffer and the shared words are free again
   }
-  if (s_abort) // a wait ran out: give the copies still in flight time to land before the block leaves
-    for (int i = 0; i < 64; ++i) __nanosleep(10000);
+
+  // ---- end of the block: the last block of the launch restores the counters ----
+  __syncthreads();
+  if (tid == 0) {
+    __threadfence();
+    const unsigned long long finished = atomicAdd(state + 3, 1ull);
+    if (finished + 1 == gridDim.x) {
+      state[0] = 0ull;
+      state[3] = 0ull;
+      state[2] = state[2] + 1ull;
+    }
+  }
 }

@@ -7,6 +7,7 @@
 #include "registry.hpp"
 
 #include <algorithm>
+#include <cstring>
 #include <stdexcept>
 
 namespace kh {
@@ -155,7 +156,11 @@ Result<void> run_rows(Executor &ex, const KernelPlan &p, const std::vector<void 
 }
 
 // ---------------------------------------------------------------- scan
-constexpr int64_t kScanTile = 4096;
+// One block per SM: twelve compute warps and a look-back warp over tiles of
+// 12 x 1024 elements held in four shared-memory tile buffers.
+constexpr int64_t kScanTile = 12 * 1024;
+constexpr int64_t kScanRow = 32; // floats per row of the tensor-map view
+constexpr size_t kScanSmem = 4 * static_cast<size_t>(kScanTile) * 4 + 1024;
 
 KernelPlan plan_scan(const ShapeMap &shape, const DeviceLimits &l) {
   const int64_t n = require_positive(shape, "scan", "n");
@@ -166,31 +171,65 @@ KernelPlan plan_scan(const ShapeMap &shape, const DeviceLimits &l) {
   const int64_t tiles = (n + kScanTile - 1) / kScanTile;
   LaunchStep s;
   s.entry = "scan";
-  s.block = {256, 1, 1};
-  s.grid = {static_cast<unsigned>(std::min<int64_t>(tiles, sm_count(l) * 4)), 1, 1};
-  s.dynamic_smem = 3 * kScanTile * 4; // ring of three tile buffers
-  s.param_count = 17;
+  s.block = {13 * 32, 1, 1};
+  s.grid = {static_cast<unsigned>(std::min<int64_t>(tiles, sm_count(l))), 1, 1};
+  s.dynamic_smem = kScanSmem;
+  s.param_count = 15 + 2 + 2 + 1; // three descriptors, two scalars, two tensor maps, flags
   p.steps = {s};
-  p.workspace_bytes = static_cast<size_t>(2 + 2 * tiles) * 8;
+  p.workspace_bytes = static_cast<size_t>(4 + 2 * tiles) * 8;
   p.work = 2.0 * static_cast<double>(n) * 4.0;
   return p;
 }
 
-Result<void> run_scan(Executor &ex, const KernelPlan &p, const std::vector<void *> &b,
-                      StreamHandle stream) {
+// x or y seen as [n / 32 rows][32 floats] for the kernel's tensor-map copies; nullopt-like
+// `false` when the buffer cannot be copied that way (the kernel then uses plain accesses).
+bool scan_tensor_map(Executor &ex, const void *ptr, int64_t n, TensorMapBytes *out) {
+  std::memset(out, 0, sizeof *out);
+  if (ptr == nullptr || (reinterpret_cast<uintptr_t>(ptr) & 15u) != 0 || n < kScanRow) return false;
+  TensorMapSpec t;
+  t.global_address = ptr;
+  t.rank = 2;
+  t.elem_bytes = 4;
+  t.dims[0] = static_cast<uint64_t>(kScanRow);
+  t.dims[1] = static_cast<uint64_t>(n / kScanRow);
+  t.strides_bytes[0] = static_cast<uint64_t>(kScanRow) * 4;
+  t.box[0] = static_cast<uint32_t>(kScanRow);
+  t.box[1] = 32;
+  t.swizzle_bytes = 128;
+  auto m = ex.backend().encode_tensor_map(t);
+  if (!m) return false;
+  *out = *m;
+  return true;
+}
+
+// `spin_limit` 0 = the kernel's default; `tile_bias` 0 in production (see the kernel).
+Result<void> launch_scan(Executor &ex, const KernelPlan &p, const std::vector<void *> &b, StreamHandle stream,
+                         uint32_t spin_limit, uint32_t tile_bias) {
   auto fn = ex.function("scan", "scan");
   if (!fn) return std::unexpected(fn.error());
   const int64_t n = p.tensors[0].shape[0];
   const int64_t tiles = (n + kScanTile - 1) / kScanTile;
-  auto ticket = ex.scan_ticket(tiles, p.steps[0].grid.x);
-  if (!ticket) return std::unexpected(ticket.error());
+  auto state = ex.scan_state(tiles);
+  if (!state) return std::unexpected(state.error());
+  TensorMapBytes x_map, y_map;
+  uint32_t flags = 0;
+  if (scan_tensor_map(ex, b[0], n, &x_map)) flags |= 1u;
+  if (scan_tensor_map(ex, b[1], n, &y_map)) flags |= 2u;
   LaunchArgs args;
   args.add_memref(b[0], {n});
   args.add_memref(b[1], {n});
-  args.add_memref(ticket->state, {static_cast<int64_t>(2 + 2 * tiles)});
-  args.add_scalar<uint32_t>(ticket->epoch);
-  args.add_scalar<uint64_t>(ticket->ticket_base);
+  args.add_memref(*state, {static_cast<int64_t>(4 + 2 * tiles)});
+  args.add_scalar<uint32_t>(spin_limit);
+  args.add_scalar<uint32_t>(tile_bias);
+  args.add_tensor_map(x_map);
+  args.add_tensor_map(y_map);
+  args.add_scalar<uint32_t>(flags);
   return ex.launch(*fn, p.steps[0], args, stream);
+}
+
+Result<void> run_scan(Executor &ex, const KernelPlan &p, const std::vector<void *> &b,
+                      StreamHandle stream) {
+  return launch_scan(ex, p, b, stream, 0u, 0u);
 }
 
 // ---------------------------------------------------------------- gemm
@@ -525,6 +564,26 @@ Result<void> run_gemm_allgather(Executor &ex, const void *a_shard, const void *b
   t.self = rank;
   t.row_offset = static_cast<int64_t>(rank) * m_shard;
   return launch_gemm(ex, plan, {const_cast<void *>(a_shard), const_cast<void *>(b), nullptr}, stream, &t);
+}
+
+// The scan launched so that its first look-back can never succeed: every ticket is shifted
+// by one tile, tile 0 is therefore never produced, and the look-back of tile 1 gives up
+// after `spin_limit` polls. Exists to show, on a healthy GPU and without any fault, that a
+// bounded wait that runs out is reported through the status word and leaves the context usable.
+Result<void> run_scan_lookback_probe(Executor &ex, const void *x, void *y, int64_t n, uint32_t spin_limit,
+                                     StreamHandle stream) {
+  if (n < 2 * kScanTile)
+    return fail(2, "scan look-back probe: n must cover at least two tiles (" + std::to_string(2 * kScanTile) +
+                       " elements)");
+  if (spin_limit == 0 || spin_limit > (1u << 20))
+    return fail(2, "scan look-back probe: the poll limit must be between 1 and 1048576");
+  KernelPlan plan;
+  try {
+    plan = plan_scan({{"n", n}}, ex.limits());
+  } catch (const std::exception &e) {
+    return fail(2, e.what());
+  }
+  return launch_scan(ex, plan, {const_cast<void *>(x), y}, stream, spin_limit, 1u);
 }
 
 void register_attention_kernel(); // attention_kernel.cpp

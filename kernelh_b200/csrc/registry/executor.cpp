@@ -137,12 +137,12 @@ Result<std::string> Executor::profile_report() {
   return out;
 }
 
-Result<Executor::ScanTicket> Executor::scan_ticket(int64_t tiles, unsigned grid) {
-  if (tiles > scan_capacity_tiles_ || scan_epoch_ >= (1u << 30) - 1) {
+Result<void *> Executor::scan_state(int64_t tiles) {
+  if (tiles > scan_capacity_tiles_) {
     const int64_t cap = std::max<int64_t>(tiles, 4096);
     if (auto r = backend_->device_synchronize(); !r) return std::unexpected(r.error());
     scan_state_ = Buffer();
-    const size_t words = 2 + 2 * static_cast<size_t>(cap);
+    const size_t words = 4 + 2 * static_cast<size_t>(cap);
     auto b = Buffer::allocate(backend_, words * 8);
     if (!b) return std::unexpected(b.error());
     scan_state_ = std::move(*b);
@@ -150,15 +150,14 @@ Result<Executor::ScanTicket> Executor::scan_ticket(int64_t tiles, unsigned grid)
       return std::unexpected(r.error());
     if (auto r = backend_->device_synchronize(); !r) return std::unexpected(r.error());
     scan_capacity_tiles_ = cap;
-    scan_epoch_ = 0;
-    scan_ticket_base_ = 0;
   }
-  ScanTicket t;
-  t.state = scan_state_.data();
-  t.epoch = ++scan_epoch_;
-  t.ticket_base = scan_ticket_base_;
-  scan_ticket_base_ += static_cast<uint64_t>(tiles) + grid; // each block ends on one surplus ticket
-  return t;
+  return scan_state_.data();
+}
+
+const char *Executor::wait_name(uint32_t code) {
+  static const char *names[] = {"ok", "scan look-back wait", "TMA (full-stage) wait",
+                                "MMA (accumulator) wait", "epilogue wait", "empty-stage wait"};
+  return code < 6 ? names[code] : "unknown wait";
 }
 
 Result<void> Executor::run(const std::string &kernel, const ShapeMap &shape,
@@ -194,16 +193,16 @@ Result<void> Executor::synchronize(StreamHandle stream) {
       return r;
   }
   if (host[0] == 0 && scan_host[0] == 0) return {};
-  // Clear so that the next launch starts clean; scan state is rebuilt from scratch.
+  // Clear so that the next launch starts clean. The scan kernel's last block restored the
+  // look-back state's counters and advanced its epoch even though the launch stopped early,
+  // so only the status word has to go.
   (void)backend_->memset32_async(status_.data(), 0, 2, nullptr);
-  if (scan_host[0] != 0) scan_capacity_tiles_ = 0;
+  if (scan_host[0] != 0)
+    (void)backend_->memset32_async(static_cast<char *>(scan_state_.data()) + 8, 0, 2, nullptr);
   (void)backend_->device_synchronize();
   const uint32_t code = host[0] ? host[0] : scan_host[0];
   const uint32_t detail = host[0] ? host[1] : scan_host[1];
-  static const char *names[] = {"ok", "scan look-back wait", "TMA (full-stage) wait",
-                                "MMA (accumulator) wait", "epilogue wait", "empty-stage wait"};
-  return fail(kDeviceTimeout, std::string("a device-side bounded wait ran out: ") +
-                                  (code < 6 ? names[code] : "unknown wait") + " (code " +
+  return fail(kDeviceTimeout, std::string("a device-side bounded wait ran out: ") + wait_name(code) + " (code " +
                                   std::to_string(code) + ", detail " + std::to_string(detail) +
                                   "); the kernel stopped and its output is incomplete");
 }

@@ -49,13 +49,11 @@ public:
   Result<std::string> profile_report();
   uint64_t launches_issued() const { return launches_issued_; }
 
-  struct ScanTicket {
-    void *state;
-    uint32_t epoch;
-    uint64_t ticket_base;
-  };
-  // Look-back state for a scan of `tiles` tiles launched with `grid` blocks.
-  Result<ScanTicket> scan_ticket(int64_t tiles, unsigned grid);
+  // Look-back state for scans of up to `tiles` tiles: counters and one descriptor per tile,
+  // zeroed when allocated; the kernel keeps it consistent from launch to launch by itself.
+  Result<void *> scan_state(int64_t tiles);
+  // Text of a device-side wait code (the status word's low half), e.g. "scan look-back wait".
+  static const char *wait_name(uint32_t code);
 
 private:
   Executor() = default;
@@ -73,8 +71,6 @@ private:
   Buffer status_;
   Buffer scan_state_;
   int64_t scan_capacity_tiles_ = 0;
-  uint32_t scan_epoch_ = 0;
-  uint64_t scan_ticket_base_ = 0;
   struct ProfiledLaunch {
     std::string entry;
     EventHandle start, end;
@@ -92,6 +88,9 @@ private:
 Result<void> run_gemm_allgather(Executor &ex, const void *a_shard, const void *b,
                                 const std::vector<void *> &replicas, void *multicast, int rank,
                                 int world, int64_t m_shard, int64_t n, int64_t k, StreamHandle stream);
+
+Result<void> run_scan_lookback_probe(Executor &ex, const void *x, void *y, int64_t n, uint32_t spin_limit,
+                                     StreamHandle stream);
 
 // attention_kernel.cpp
 Result<void> run_attention_allgather(Executor &ex, const void *q, const void *k, const void *v,

@@ -209,6 +209,58 @@ def test_scan_large_and_signed(ctx, oracle):
     assert oracle.bit_mismatches(y, ref) <= n // 1000  # fp64 sums of general data: last-bit ties only
 
 
+def test_scan_misaligned_strided_and_ragged_sizes(ctx, oracle):
+    """Buffers the tensor-map copies cannot take (not 16-byte aligned) go through the plain
+    load / store path of the same kernel, sizes that end inside a 32-element row use the
+    partial-row code, and sizes around the 12288-element tile and the 1024-element warp part
+    cross every boundary of the pipeline; all must give the oracle's bits."""
+    for n in (31, 32, 33, 1023, 1025, 12287, 12288, 12289, 24576 + 17, 36864, 49152 + 1, 200000, 12288 * 148 + 5):
+        x = oracle.mt19937_unit(n, 0x29C0FFEE + n)
+        ref = oracle.scan_ref(x)
+        assert oracle.bit_mismatches(run(ctx, "scan", f"n={n}", [x], (n,)), ref) == 0, n
+    n = 100003
+    x = oracle.mt19937_unit(n + 1, 0x51AC0D3E)
+    dx, out = dev(x), torch.full((n + 2,), float("nan"), device="cuda")
+    stream = torch.cuda.current_stream().cuda_stream
+    ctx.scan(dx[1:], out[1:], n, stream)  # both sides misaligned
+    ctx.synchronize(stream)
+    ref = oracle.scan_ref(x[1:].copy())
+    assert oracle.bit_mismatches(out[1:n + 1].cpu().numpy(), ref) == 0
+    assert torch.isnan(out[0]).item() and torch.isnan(out[n + 1]).item()
+    out.fill_(float("nan"))
+    ctx.scan(dx[1:], out, n, stream)      # input misaligned, output through the tensor map
+    ctx.synchronize(stream)
+    assert oracle.bit_mismatches(out[:n].cpu().numpy(), ref) == 0 and torch.isnan(out[n]).item()
+
+
+def test_scan_lookback_that_runs_out_is_reported_and_survivable(ctx, oracle):
+    """A bounded device-side wait that gives up, shown without any fault: the scan is
+    launched so that tile 0 is never produced (every ticket shifted by one), the look-back
+    of tile 1 polls its missing predecessor a few thousand times (about a millisecond),
+    records the scan look-back code in the status word, every role of the kernel stops and
+    the kernel returns. kh_synchronize then reports 1001 and names the wait, and the next
+    ordinary scan on the same context gives the oracle's bits."""
+    n = 3 * 12288 + 100
+    x = oracle.mt19937_unit(n, 0x29C0FFEE)
+    dx, dy = dev(x), torch.zeros(n, device="cuda")
+    stream = torch.cuda.current_stream().cuda_stream
+    ctx.scan_lookback_probe(dx, dy, n, 3000, stream)
+    with pytest.raises(kh.KernelhError) as e:
+        ctx.synchronize(stream)
+    assert e.value.code == kh.DEVICE_TIMEOUT == 1001
+    assert "scan look-back wait" in e.value.message and "code 1, detail 1" in e.value.message
+    assert "output is incomplete" in e.value.message
+    ctx.synchronize(stream)  # the status was cleared: a second wait is clean
+    for _ in range(2):
+        y = run(ctx, "scan", f"n={n}", [x], (n,))
+        assert oracle.bit_mismatches(y, oracle.scan_ref(x)) == 0
+    with pytest.raises(kh.KernelhError) as e:  # argument checks happen on the host
+        ctx.scan_lookback_probe(dx, dy, 1000, 3000, stream)
+    assert e.value.code == kh.USAGE_ERROR and "two tiles" in e.value.message
+    with pytest.raises(kh.KernelhError):
+        ctx.scan_lookback_probe(dx, dy, n, 0, stream)
+
+
 # --------------------------------------------------------------------------- gemm
 @pytest.mark.parametrize("size", [128, 512, 1024, 1000, 2048])
 def test_gemm_reference_pattern(ctx, oracle, size):
@@ -265,6 +317,69 @@ def test_gemm_is_insensitive_to_operand_scaling(ctx, oracle, kind):
     assert np.max(np.abs(c - ref) / np.maximum(bound, 1e-300)) <= 4e-6
     if kind == "rows_and_columns":
         assert not c[3].any() and not c[:, 5].any()
+
+
+def test_gemm_reference_pattern_4096(ctx, oracle):
+    """The largest size of the reference's pattern list (test/unit/e2e_gemm_test.cpp:277),
+    checked bit for bit on sampled rows (the fp64 routine over all of C would take minutes)."""
+    size = 4096
+    a, b = oracle.gemm_pattern(size, size, size)
+    c = run(ctx, "gemm", f"m={size},n={size},k={size}", [a, b], (size, size))
+    rows = np.sort(np.random.default_rng(2).choice(size, 96, replace=False))
+    ref = oracle.gemm_ref_pick_rows(a, b, rows)
+    assert oracle.compare(c[rows], ref).rel_frobenius <= 1e-5
+    assert oracle.bit_mismatches(np.ascontiguousarray(c[rows]), ref) == 0
+    assert np.isfinite(c).all()
+
+
+def test_gemm_propagates_inf_and_nan_like_fp32(ctx, oracle):
+    """The scaled fp16 hi/lo split must not turn one non-finite input into a
+    non-finite C anywhere an fp32 product would be finite, and must keep C
+    non-finite wherever fp32 gives Inf or NaN (Inf and NaN are not told apart:
+    the split of Inf has a NaN low part)."""
+    m, n, k = 300, 520, 264
+    a = oracle.normal((m, k), oracle.BASE_SEED + 21, 0, 1)
+    b = oracle.normal((k, n), oracle.BASE_SEED + 22, 0, 1)
+    a[7, 100] = np.inf        # row 7 of C: +-Inf everywhere (NaN where B[100, c] == 0)
+    a[130, 5] = np.nan        # row 130 of C: NaN
+    b[17, 260] = -np.inf      # column 260 of C: non-finite
+    b[200, 3] = np.nan        # column 3 of C: NaN
+    b[:, 400] = 0             # a zero column: Inf * 0 = NaN in row 7, exact zeros elsewhere
+    c = run(ctx, "gemm", f"m={m},n={n},k={k}", [a, b], (m, n))
+    with np.errstate(all="ignore"):
+        ref32 = a.astype(np.float64) @ b.astype(np.float64)
+    expect_bad = ~np.isfinite(ref32)
+    assert expect_bad[7].all() and expect_bad[130].all() and expect_bad[:, 260].all() and expect_bad[:, 3].all()
+    assert expect_bad.sum() == 2 * n + 2 * m - 4
+    assert np.array_equal(~np.isfinite(c), expect_bad)
+    assert np.isnan(c[7, 400]) and np.isnan(c[130]).all() and np.isnan(c[:, 3]).all()
+    good = ~expect_bad
+    bound = np.abs(np.nan_to_num(a, nan=0, posinf=0, neginf=0)).astype(np.float64) @ \
+        np.abs(np.nan_to_num(b, nan=0, posinf=0, neginf=0)).astype(np.float64)
+    assert np.max(np.abs(c.astype(np.float64) - ref32)[good] / np.maximum(bound[good], 1e-300)) <= 4e-6
+    assert not c[np.arange(m) != 7][:, 400][np.arange(m - 1) != 129].any()  # zero column stays exactly zero
+
+
+def test_gemm_subnormal_rows_and_columns(ctx, oracle):
+    """Rows of A (columns of B) that hold only subnormal fp32 values are scaled up
+    exactly before the split, so they keep their significant bits; the product is
+    compared with fp64 to a few fp32 roundings of |A||B| plus one subnormal step
+    (the final power-of-two un-scaling rounds once into the subnormal range)."""
+    m, n, k = 256, 384, 200
+    a = oracle.uniform((m, k), oracle.BASE_SEED + 31, -1, 1)
+    b = oracle.uniform((k, n), oracle.BASE_SEED + 32, -1, 1)
+    a[10] *= np.float32(1e-39)            # subnormal-only row
+    a[11] = a[11] * np.float32(1e-30)
+    a[11] = a[11] * np.float32(1e-9)      # 1e-39 again, reached in two steps
+    b[:, 20] *= np.float32(3e-40)         # subnormal-only column
+    assert np.all(np.abs(a[10]) < 1.1754944e-38) and np.all(np.abs(b[:, 20]) < 1.1754944e-38)
+    c = run(ctx, "gemm", f"m={m},n={n},k={k}", [a, b], (m, n)).astype(np.float64)
+    ref = a.astype(np.float64) @ b.astype(np.float64)
+    bound = np.abs(a).astype(np.float64) @ np.abs(b).astype(np.float64)
+    assert np.all(np.isfinite(c))
+    assert np.all(np.abs(c - ref) <= 4e-6 * bound + 1.5e-45)
+    assert np.count_nonzero(c[10]) > n // 2      # the subnormal row was not flushed to zero
+    assert np.count_nonzero(c[:, 20]) > m // 2
 
 
 @pytest.mark.parametrize("m,n,k", [(2500, 384, 200), (256, 256, 64), (100, 40, 33)])
@@ -366,6 +481,40 @@ def test_attention_more_work_items_than_sms(ctx, oracle, b, h, s):
     assert cmp_.non_finite == 0 and cmp_.max_violation <= 2e-3
     assert cmp_.max_rel <= REL * math.sqrt(s)
     assert np.array_equal(o, run(ctx, "attention", name, [q, k, v], (b, h, s, 64)))
+
+
+@pytest.mark.parametrize("kind", ["rows_inside_tiles", "large_scores"])
+def test_attention_wide_range_inside_tiles(ctx, oracle, kind):
+    """What the 3xFP16 arithmetic could lose against fp32: Q, K and V are scaled by
+    ONE power of two per 64-row tile before the fp16 hi/lo split, so a row far below
+    its tile's largest keeps fewer bits, and the scores carry 22 significand bits,
+    not 24. The error is measured against sum_j p_ij |v_jd| (the size of the terms
+    the output is made of). Bounds are what the kernel meets on a B200, with margin:
+    rows with e^N(0, 1.5^2) scale factors inside the tiles stay within 1e-4 (an fp32
+    evaluation of the same inputs: 2e-5 to 4e-5); Q * 6, whose scores reach several
+    hundred in exp2 units, within 5e-4 (fp32: 1e-5 to 2e-5; the missing two bits
+    of the scores are multiplied by their size)."""
+    b, h, s = (1, 300, 64) if kind == "rows_inside_tiles" else (2, 40, 320)
+    rng = np.random.default_rng(77)
+    q, k, v = (oracle.normal((b, h, s, 64), oracle.BASE_SEED + 40 + i, 0, 1) for i in range(3))
+    if kind == "rows_inside_tiles":
+        q *= np.exp(rng.normal(0, 1.0, (b, h, 1, 1))).astype(np.float32)
+        k *= np.exp(rng.normal(0, 0.5, (b, h, s, 1))).astype(np.float32)
+        v *= np.exp(rng.normal(0, 1.5, (b, h, s, 1))).astype(np.float32)
+    else:
+        q *= np.float32(6.0)
+    o = run(ctx, "attention", f"batch={b},heads={h},seq={s},head_dim=64", [q, k, v], (b, h, s, 64))
+    assert np.isfinite(o).all()
+    q64, k64, v64 = (t.astype(np.float64) for t in (q, k, v))
+    scores = q64 @ np.swapaxes(k64, -1, -2) / 8.0
+    p = np.exp(scores - scores.max(-1, keepdims=True))
+    p /= p.sum(-1, keepdims=True)
+    ref = p @ v64
+    assert np.allclose(ref, oracle.attention_ref(q, k, v), rtol=1e-9, atol=1e-12)  # the oracle agrees with this fp64 form
+    err = np.max(np.abs(o - ref) / np.maximum(p @ np.abs(v64), 1e-300))
+    assert err <= (1e-4 if kind == "rows_inside_tiles" else 5e-4), err
+    cmp_ = oracle.compare(o, ref.astype(np.float32), rtol=2e-3)
+    assert cmp_.max_violation <= 2e-3  # the reference's own tolerance still holds
 
 
 def test_attention_negative_control(ctx, oracle):

@@ -189,7 +189,12 @@ def test_plans_for_the_benchmark_configurations():
     p = kh.plan("softmax", "rows=16384,cols=4096")
     assert p.block[0] == 256 and p.grid[0] == 148 * 8
     p = kh.plan("scan", "n=1000000")
-    assert p.work == 8000000.0 and p.workspace_bytes == (2 + 2 * 245) * 8
+    # 82 tiles of 12288 elements, a block per tile (fewer tiles than SMs), 13 warps, four tile buffers
+    assert p.work == 8000000.0 and p.workspace_bytes == (4 + 2 * 82) * 8
+    assert p.grid[0] == 82 and p.block[0] == 13 * 32 and p.dynamic_smem == 4 * 12288 * 4 + 1024
+    assert p.param_count == 20
+    assert kh.verify_launch("sm_100a", p.block[0], tuple(p.grid), 2048, p.dynamic_smem) == ""
+    assert kh.plan("scan", "n=67108864").grid[0] == 148
     p = kh.plan("gemm", "m=8192,n=8192,k=8192")
     # split A, column maxima of B, split B^T, then 74 two-CTA clusters
     assert p.entry == b"gemm" and p.n_launches == 4 and p.grid[0] == 148 and p.block[0] == 320
@@ -269,3 +274,18 @@ def test_kernels_without_a_scalar_path_refuse_misaligned_addresses_on_the_host()
     assert b"'K'" in lib.kh_last_error()
     assert lib.kh_attention_allgather(None, ok, ok, ok, good, off, 2, 0, 4, 64, 64, None) == 2
     assert b"multicast" in lib.kh_last_error()
+
+
+def test_device_wait_codes_have_names():
+    """kh_synchronize reports a device-side bounded wait that ran out as code 1001
+    and names the wait; the code-to-name table is checked here without a GPU."""
+    assert kh.DEVICE_TIMEOUT == 1001
+    assert kh.wait_name(1) == "scan look-back wait"
+    assert kh.wait_name(2) == "TMA (full-stage) wait"
+    assert kh.wait_name(3) == "MMA (accumulator) wait"
+    assert kh.wait_name(4) == "epilogue wait"
+    assert kh.wait_name(5) == "empty-stage wait"
+    assert kh.wait_name(0) == "ok" and kh.wait_name(77) == "unknown wait"
+    # the probe validates its arguments on the host
+    assert kh.lib.kh_scan_lookback_probe(None, 0x1000, 0x2000, 1 << 20, 1000, None) == 2
+    assert b"context" in kh.lib.kh_last_error()

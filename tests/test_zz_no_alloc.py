@@ -54,6 +54,7 @@ def test_no_alloc_scan_matches_scan_on_consecutive_calls(ctx, oracle):
         assert torch.equal(got, want), n
         ref = oracle.scan_ref(x.cpu().numpy())
         assert oracle.bit_mismatches(got.cpu().numpy(), ref) == 0
+        kh.scan_noalloc_status(torch.cuda.current_stream().cuda_stream)  # no wait ran out
 
 
 def test_no_alloc_scan_allocates_nothing(ctx):
