@@ -531,19 +531,53 @@ def gpu_arm(args) -> None:
     if clocks is not None:
         line["clocks"] = clocks
 
-    # ---- end to end through the host-buffer entry point -------------------------------------
+    # ---- end to end through the host-buffer entry points -------------------------------------
     if not args.no_extras:
         a_h = a_shard.cpu().pin_memory()
-        b_h = b.cpu().pin_memory()
         c_h = torch.empty(rows, size).pin_memory()
         shape = f"m={rows},n={size},k={size}"
-        e2e_steps = max(3, min(args.steps, 5))
-        ctx.run_host("gemm", shape, [a_h, b_h, c_h])
+        e2e_steps = max(3, args.steps)
+        b_symm = None
+        if world > 1 and gather == "p2p" and size % world == 0:
+            # every rank uploads only ITS rows of B; the slices are exchanged over NVLink
+            try:
+                b_dev = symm_mem.empty((size, size), dtype=torch.float32, device=torch.device("cuda", local_rank))
+                b_symm = symm_mem.rendezvous(b_dev, dist.group.WORLD.group_name)
+                b_reps = [int(p) for p in b_symm.buffer_ptrs]
+                b_mc = int(getattr(b_symm, "multicast_ptr", 0) or 0) if args.gather == "p2p" else 0
+            except Exception as exc:
+                if rank == 0:
+                    sys.stderr.write(f"bench.py: symmetric memory for B unavailable ({exc!r}); every rank uploads all of B\n")
+                b_symm = None
+        if b_symm is not None:
+            k_lo, k_hi = rank * (size // world), (rank + 1) * (size // world)
+            b_h = b[k_lo:k_hi].cpu().pin_memory()
+
+            def e2e_step():
+                ctx.gemm_host_sharded_begin(a_h, b_h, b_reps if not b_mc else
+                                            [b_dev if i == rank else None for i in range(world)],
+                                            b_mc, rank, rows, size, size)
+                b_symm.barrier()           # every rank's slice of B has been sent
+                torch.cuda.synchronize()
+                ctx.gemm_host_sharded_finish(c_h)
+            e2e_note = ("kh_gemm_host_sharded_begin / _finish on pinned host buffers, per rank: H2D of this rank's 1/N of "
+                        "the rows of B, sent on to every rank's B over NVLink (" + ("multimem.st" if b_mc else "peer stores") +
+                        ") while the A shard goes up in row blocks; barrier; B is split, each A block is split and multiplied "
+                        "as it arrives and the finished rows of C go back over the other direction of the link")
+        else:
+            b_h = b.cpu().pin_memory()
+
+            def e2e_step():
+                ctx.run_host("gemm", shape, [a_h, b_h, c_h])
+            e2e_note = ("kh_run_host on pinned host buffers, per rank: H2D of B, then the A shard in about eight row "
+                        "blocks; each block is split and multiplied while the next is on the wire and the finished rows "
+                        "of C go back over the other direction of the link")
+        e2e_step()
         barrier()
         torch.cuda.synchronize()
         t0 = time.perf_counter()
         for _ in range(e2e_steps):
-            ctx.run_host("gemm", shape, [a_h, b_h, c_h])
+            e2e_step()
         torch.cuda.synchronize()
         dt = torch.tensor([(time.perf_counter() - t0) / e2e_steps], device="cuda", dtype=torch.float64)
         if world > 1:
@@ -551,12 +585,15 @@ def gpu_arm(args) -> None:
         line["e2e"] = {"value": flops / dt.item() / 1e12, "unit": "TFLOP/s",
                        "h2d_bytes_per_step": int(a_h.numel() * 4 + b_h.numel() * 4),
                        "d2h_bytes_per_step": int(c_h.numel() * 4), "steps": e2e_steps,
-                       "ms_per_step": dt.item() * 1e3,
-                       "note": "kh_run_host on pinned host buffers, per rank: H2D of B, then the A shard in "
-                               "about eight row blocks; each block is split and multiplied while the next is "
-                               "on the wire and the finished rows of C go back over the other direction of the link"}
+                       "ms_per_step": dt.item() * 1e3, "note": e2e_note}
         e2e_ok = torch.equal(c_h, c_shard.cpu())
         line["e2e"]["matches_device_path"] = bool(e2e_ok)
+        if world > 1:
+            ok_all = torch.tensor([1.0 if e2e_ok else 0.0], device="cuda")
+            dist.all_reduce(ok_all, op=dist.ReduceOp.MIN)
+            line["e2e"]["matches_device_path"] = bool(ok_all.item() == 1.0)
+        if not line["e2e"]["matches_device_path"]:
+            parity_failures.append("e2e: the rows of C that came back to the host differ from the device path's")
         del a_h, b_h, c_h
 
     if world > 1:

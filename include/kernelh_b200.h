@@ -149,6 +149,25 @@ int kh_gemm_allgather_multicast(kh_context *ctx, const float *a_shard, const flo
                                 void *c_multicast, int world, int rank, int64_t m_shard, int64_t n,
                                 int64_t k, void *stream);
 
+/* No counterpart in the reference. The M-row-sharded gemm on HOST buffers, for
+ * several GPUs of one box, without uploading the whole B once per rank: in
+ * phase `begin` a rank uploads only ITS slice of B, rows [rank*k/world,
+ * (rank+1)*k/world) given as `b_slice_host`, into its own replica of B
+ * (`b_replicas[rank]`, a full k x n device buffer) and sends it on to every
+ * other replica over NVLink (multimem.st through `b_multicast`, the replicas'
+ * multicast address, or plain peer stores when it is null; `b_replicas[i]` is
+ * rank i's replica as mapped on this device), while the upload of the A shard
+ * (m_shard x k, `a_shard_host`) starts; begin returns when the slice has left.
+ * The caller then passes a barrier across the ranks, and phase `finish`
+ * prepares B, multiplies the A blocks as they arrive and copies the rank's
+ * m_shard x n rows of C to `c_shard_host`, returning when they are there. k
+ * must be divisible by world. No other call may use the context between the
+ * two phases. Results are bit-identical with kh_gemm. */
+int kh_gemm_host_sharded_begin(kh_context *ctx, const float *a_shard_host, const float *b_slice_host,
+                               void *const *b_replicas, void *b_multicast, int world, int rank,
+                               int64_t m_shard, int64_t n, int64_t k);
+int kh_gemm_host_sharded_finish(kh_context *ctx, float *c_shard_host);
+
 /* No counterpart in the reference. Attention over (batch, head) slices sharded
  * across the GPUs of one box with the all-gather of the output fused into the
  * kernel: q, k, v are this rank's `slices` x seq x head_dim problems; every

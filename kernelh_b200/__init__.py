@@ -85,6 +85,8 @@ def _load() -> C.CDLL:
     L.kh_gemm.argtypes = [vp, f32p, f32p, f32p, i64, i64, i64, vp]
     L.kh_gemm_allgather.argtypes = [vp, f32p, f32p, C.POINTER(vp), C.c_int, C.c_int, i64, i64, i64, vp]
     L.kh_gemm_allgather_multicast.argtypes = [vp, f32p, f32p, f32p, vp, C.c_int, C.c_int, i64, i64, i64, vp]
+    L.kh_gemm_host_sharded_begin.argtypes = [vp, f32p, f32p, C.POINTER(vp), vp, C.c_int, C.c_int, i64, i64, i64]
+    L.kh_gemm_host_sharded_finish.argtypes = [vp, f32p]
     L.kh_attention.argtypes = [vp, f32p, f32p, f32p, f32p, i64, i64, i64, i64, vp]
     L.kh_attention_allgather.argtypes = [vp, f32p, f32p, f32p, C.POINTER(vp), vp, C.c_int, C.c_int, i64, i64, i64, vp]
     L.kh_malloc.argtypes = [vp, C.c_size_t, C.POINTER(vp)]
@@ -256,6 +258,19 @@ class Context:
         (`c_multicast`), reaching all ranks' full C."""
         _check(lib.kh_gemm_allgather_multicast(self._h, _ptr(a_shard), _ptr(b), _ptr(c_local),
                                                C.c_void_p(int(c_multicast)), world, rank, m_shard, n, k, stream))
+
+    def gemm_host_sharded_begin(self, a_shard_host, b_slice_host, b_replicas, b_multicast, rank, m_shard, n, k):
+        """Phase 1 of the sharded gemm on HOST buffers: upload this rank's rows of B into its
+        replica and send them to the other replicas, start the upload of the A shard. A barrier
+        across the ranks must follow before `gemm_host_sharded_finish`."""
+        arr = (C.c_void_p * len(b_replicas))(*[(None if p is None else _ptr(p)) for p in b_replicas])
+        _check(lib.kh_gemm_host_sharded_begin(self._h, _ptr(a_shard_host), _ptr(b_slice_host), arr,
+                                              C.c_void_p(int(b_multicast)) if b_multicast else None,
+                                              len(b_replicas), rank, m_shard, n, k))
+
+    def gemm_host_sharded_finish(self, c_shard_host):
+        """Phase 2: prepare B, multiply, copy this rank's rows of C to `c_shard_host`; blocking."""
+        _check(lib.kh_gemm_host_sharded_finish(self._h, _ptr(c_shard_host)))
 
     def attention(self, q, k, v, o, batch, heads, seq, head_dim, stream=None):
         _check(lib.kh_attention(self._h, _ptr(q), _ptr(k), _ptr(v), _ptr(o), batch, heads, seq,

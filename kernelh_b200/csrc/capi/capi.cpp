@@ -282,6 +282,31 @@ int kh_gemm_allgather_multicast(kh_context *ctx, const float *a_shard, const flo
     return r ? 0 : set_error(r.error());
   });
 }
+int kh_gemm_host_sharded_begin(kh_context *ctx, const float *a_shard_host, const float *b_slice_host,
+                               void *const *b_replicas, void *b_multicast, int world, int rank, int64_t m_shard,
+                               int64_t n, int64_t k) {
+  if (b_replicas == nullptr || world <= 0 || world > 8)
+    return set_error(2, "kh_gemm_host_sharded_begin: between 1 and 8 B replicas are expected");
+  if (int rc = refuse_misaligned("kh_gemm_host_sharded_begin", {{"B multicast address", b_multicast}})) return rc;
+  for (int i = 0; i < world; ++i)
+    if (int rc = refuse_misaligned("kh_gemm_host_sharded_begin", {{"B replica", b_replicas[i]}})) return rc;
+  if (int rc = need_ctx(ctx)) return rc;
+  return guarded([&] {
+    if (auto r = ctx->exec->backend().make_current(); !r) return set_error(r.error());
+    std::vector<void *> reps(b_replicas, b_replicas + world);
+    auto r = kh::run_gemm_host_sharded_begin(*ctx->exec, a_shard_host, b_slice_host, reps, b_multicast, rank, world,
+                                             m_shard, n, k);
+    return r ? 0 : set_error(r.error());
+  });
+}
+int kh_gemm_host_sharded_finish(kh_context *ctx, float *c_shard_host) {
+  if (int rc = need_ctx(ctx)) return rc;
+  return guarded([&] {
+    if (auto r = ctx->exec->backend().make_current(); !r) return set_error(r.error());
+    auto r = kh::run_gemm_host_sharded_finish(*ctx->exec, c_shard_host);
+    return r ? 0 : set_error(r.error());
+  });
+}
 int kh_attention(kh_context *ctx, const float *q, const float *k, const float *v, float *o,
                  int64_t batch, int64_t heads, int64_t seq, int64_t head_dim, void *stream) {
   if (int rc = refuse_misaligned("kh_attention", {{"Q", q}, {"K", k}, {"V", v}, {"O", o}})) return rc;

@@ -787,3 +787,34 @@ gemm_allgather(KH_MEMREF2(const float, a), KH_MEMREF2(const float, b),
   gemm_body<true>(a_size0, b_size1, nullptr, 0, 0, tm_a_hi, tm_a_lo, tm_b_hi, tm_b_lo, k_blocks, status,
                   a_shift, b_shift, &targets);
 }
+
+// Sends a run of floats of this GPU's copy of a replicated buffer to the same place in every
+// other copy: `targets.base[self] + first` .. `+ first + count` goes out with multimem.st through
+// the copies' NVLink multicast address when there is one (the switch delivers each store to
+// every GPU), else with plain peer stores. Nothing is read from a peer. Used to assemble a
+// replicated operand (B of the sharded product) from slices that each rank uploads itself.
+// `first` and `count` are multiples of 4 and the bases 16-byte aligned (checked on the host).
+extern "C" __global__ void __launch_bounds__(256)
+replicate_run(const __grid_constant__ GatherTargets targets, int64_t first, int64_t count) {
+  const float4 *__restrict__ src = reinterpret_cast<const float4 *>(targets.base[targets.self] + first);
+  const int64_t vecs = count >> 2;
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < vecs; i += 4 * stride) {
+    float4 v[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+      if (i + j * stride < vecs) v[j] = __ldcs(src + i + j * stride);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int64_t at = i + j * stride;
+      if (at >= vecs) continue;
+      if (targets.multicast != nullptr) {
+        multicast_store_float4(targets.multicast + first + 4 * at, v[j].x, v[j].y, v[j].z, v[j].w);
+      } else {
+        for (int d = 0; d < targets.count; ++d)
+          if (d != targets.self)
+            *reinterpret_cast<float4 *>(targets.base[d] + first + 4 * at) = v[j];
+      }
+    }
+  }
+}

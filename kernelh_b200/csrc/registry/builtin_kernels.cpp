@@ -586,6 +586,148 @@ Result<void> run_scan_lookback_probe(Executor &ex, const void *x, void *y, int64
   return launch_scan(ex, plan, {const_cast<void *>(x), y}, stream, spin_limit, 1u);
 }
 
+Result<void> run_gemm_host_sharded_begin(Executor &ex, const void *a_shard_host, const void *b_slice_host,
+                                         const std::vector<void *> &b_replicas, void *b_multicast, int rank,
+                                         int world, int64_t m_shard, int64_t n, int64_t k) {
+  if (world < 1 || world > 8 || rank < 0 || rank >= world || static_cast<int>(b_replicas.size()) != world)
+    return fail(2, "gemm_host_sharded: rank / replica list do not match a world of 1 to 8 ranks");
+  if (a_shard_host == nullptr || b_slice_host == nullptr || b_replicas[static_cast<size_t>(rank)] == nullptr)
+    return fail(2, "gemm_host_sharded: null buffer");
+  if (k % world != 0 || ((k / world) * n) % 4 != 0)
+    return fail(2, "gemm_host_sharded: the rows of B (k = " + std::to_string(k) + ") must split evenly over " +
+                       std::to_string(world) + " ranks into slices of a multiple of four floats");
+  if (first_misaligned16({{"B multicast address", b_multicast}}))
+    return fail(2, "gemm_host_sharded: the B multicast address is not 16-byte aligned");
+  for (int i = 0; i < world; ++i) {
+    if (b_replicas[static_cast<size_t>(i)] == nullptr && (b_multicast == nullptr || i == rank))
+      return fail(2, "gemm_host_sharded: null B replica pointer");
+    if (first_misaligned16({{"B replica", b_replicas[static_cast<size_t>(i)]}}))
+      return fail(2, "gemm_host_sharded: B replica " + std::to_string(i) + " is not 16-byte aligned");
+  }
+  KernelPlan plan;
+  try {
+    plan = plan_gemm({{"m", m_shard}, {"n", n}, {"k", k}}, ex.limits());
+  } catch (const std::exception &e) {
+    return fail(2, e.what());
+  }
+  Backend &be = ex.backend();
+  auto hs = ex.host_streams();
+  if (!hs) return std::unexpected(hs.error());
+  auto dev_a = ex.host_staging(0, static_cast<size_t>(m_shard * k) * 4);
+  if (!dev_a) return std::unexpected(dev_a.error());
+  auto dev_c = ex.host_staging(2, static_cast<size_t>(m_shard * n) * 4);
+  if (!dev_c) return std::unexpected(dev_c.error());
+  auto job = gemm_job(ex, m_shard, n, k);
+  if (!job) return std::unexpected(job.error());
+  auto push = ex.function("gemm", "replicate_run");
+  if (!push) return std::unexpected(push.error());
+
+  // this rank's rows of B: up into its own replica, then on to the others
+  const int64_t slice_rows = k / world, first = static_cast<int64_t>(rank) * slice_rows * n, count = slice_rows * n;
+  char *b_local = static_cast<char *>(b_replicas[static_cast<size_t>(rank)]);
+  if (auto r = be.memcpy_h2d_async(b_local + static_cast<size_t>(first) * 4, b_slice_host,
+                                   static_cast<size_t>(count) * 4, hs->in);
+      !r)
+    return r;
+  auto b_up = be.event_create();
+  if (!b_up) return std::unexpected(b_up.error());
+  if (auto r = be.event_record(*b_up, hs->in); !r) return r;
+  if (auto r = be.stream_wait_event(hs->compute, *b_up); !r) return r;
+  if (world > 1) {
+    GatherTargets t{};
+    t.count = world;
+    t.self = rank;
+    t.multicast = static_cast<float *>(b_multicast);
+    for (int i = 0; i < world; ++i) t.base[i] = static_cast<float *>(b_replicas[static_cast<size_t>(i)]);
+    LaunchStep step;
+    step.entry = "replicate_run";
+    step.block = {256, 1, 1};
+    step.grid = {static_cast<unsigned>(std::min<int64_t>((count / 4 + 1023) / 1024, sm_count(ex.limits()) * 4)), 1, 1};
+    step.param_count = 3;
+    LaunchArgs args;
+    args.add_struct_bytes(&t, sizeof t);
+    args.add_scalar<int64_t>(first);
+    args.add_scalar<int64_t>(count);
+    if (auto r = ex.launch(*push, step, args, hs->compute); !r) return r;
+  }
+  // the A shard: in row blocks, each with its own event (the uploads go on while the ranks meet)
+  const int64_t block_rows = std::max<int64_t>(256, ((m_shard + 7) / 8 + 255) / 256 * 256);
+  const int64_t blocks = (m_shard + block_rows - 1) / block_rows;
+  std::vector<EventHandle> a_events;
+  for (int64_t i = 0; i < blocks; ++i) {
+    const int64_t row0 = i * block_rows, rows = std::min(block_rows, m_shard - row0);
+    if (auto r = be.memcpy_h2d_async(static_cast<char *>(*dev_a) + static_cast<size_t>(row0 * k) * 4,
+                                     static_cast<const char *>(a_shard_host) + static_cast<size_t>(row0 * k) * 4,
+                                     static_cast<size_t>(rows * k) * 4, hs->in);
+        !r)
+      return r;
+    auto e = be.event_create();
+    if (!e) return std::unexpected(e.error());
+    if (auto r = be.event_record(*e, hs->in); !r) return r;
+    a_events.push_back(*e);
+  }
+  // the slice has left this GPU when the compute stream is idle
+  Result<void> pushed = be.stream_synchronize(hs->compute);
+  (void)be.event_destroy(*b_up);
+  if (!pushed) {
+    for (EventHandle e : a_events) (void)be.event_destroy(e);
+    return pushed;
+  }
+
+  const HostStreams streams = *hs;
+  void *a_dev = *dev_a, *c_dev = *dev_c;
+  const GemmJob j = *job;
+  const std::vector<LaunchStep> b_steps = plan.steps;
+  ex.pending_host_finish = [&ex, j, streams, a_dev, c_dev, b_local, b_steps, a_events, m_shard, n, k, block_rows,
+                            blocks](void *c_host) -> Result<void> {
+    Backend &be2 = ex.backend();
+    std::vector<EventHandle> events = a_events;
+    const auto body = [&]() -> Result<void> {
+      if (auto r = gemm_enqueue_b(j, b_local, b_steps, streams.compute, true); !r) return r;
+      for (int64_t i = 0; i < blocks; ++i) {
+        const int64_t row0 = i * block_rows, rows = std::min(block_rows, m_shard - row0);
+        char *a_rows = static_cast<char *>(a_dev) + static_cast<size_t>(row0 * k) * 4;
+        char *c_rows = static_cast<char *>(c_dev) + static_cast<size_t>(row0 * n) * 4;
+        if (auto r = be2.stream_wait_event(streams.compute, a_events[static_cast<size_t>(i)]); !r) return r;
+        const std::vector<LaunchStep> steps = gemm_steps(rows, n, k, ex.limits());
+        if (auto r = gemm_enqueue_a(j, a_rows, row0, rows, steps[0], streams.compute, 0); !r) return r;
+        if (auto r = gemm_enqueue_multiply(j, a_rows, b_local, c_rows, row0, rows, steps[3], streams.compute, nullptr);
+            !r)
+          return r;
+        auto c_done = be2.event_create();
+        if (!c_done) return std::unexpected(c_done.error());
+        events.push_back(*c_done);
+        if (auto r = be2.event_record(*c_done, streams.compute); !r) return r;
+        if (auto r = be2.stream_wait_event(streams.out, *c_done); !r) return r;
+        if (c_host != nullptr)
+          if (auto r = be2.memcpy_d2h_async(static_cast<char *>(c_host) + static_cast<size_t>(row0 * n) * 4, c_rows,
+                                            static_cast<size_t>(rows * n) * 4, streams.out);
+              !r)
+            return r;
+      }
+      return {};
+    };
+    Result<void> enqueued = body();
+    Result<void> s_in = be2.stream_synchronize(streams.in);
+    Result<void> s_compute = ex.synchronize(streams.compute);
+    Result<void> s_out = be2.stream_synchronize(streams.out);
+    for (EventHandle e : events) (void)be2.event_destroy(e);
+    if (!enqueued) return enqueued;
+    if (!s_compute) return s_compute;
+    if (!s_in) return s_in;
+    return s_out;
+  };
+  return {};
+}
+
+Result<void> run_gemm_host_sharded_finish(Executor &ex, void *c_shard_host) {
+  if (!ex.pending_host_finish)
+    return fail(2, "gemm_host_sharded: finish without a begin (phase 0 must come first on this context)");
+  auto finish = std::move(ex.pending_host_finish);
+  ex.pending_host_finish = nullptr;
+  return finish(c_shard_host);
+}
+
 void register_attention_kernel(); // attention_kernel.cpp
 
 void register_builtin_kernels() {

@@ -207,6 +207,28 @@ Result<void> Executor::synchronize(StreamHandle stream) {
                                   "); the kernel stopped and its output is incomplete");
 }
 
+Result<HostStreams> Executor::host_streams() {
+  for (StreamHandle *s : {&host_in_stream_, &host_stream_, &host_out_stream_}) {
+    if (*s != nullptr) continue;
+    auto created = backend_->stream_create();
+    if (!created) return std::unexpected(created.error());
+    *s = *created;
+  }
+  return HostStreams{host_in_stream_, host_stream_, host_out_stream_};
+}
+
+Result<void *> Executor::host_staging(size_t index, size_t bytes) {
+  if (host_pool_.size() <= index) host_pool_.resize(index + 1);
+  if (host_pool_[index].size() < bytes) {
+    if (auto r = backend_->device_synchronize(); !r) return std::unexpected(r.error());
+    host_pool_[index] = Buffer();
+    auto b = Buffer::allocate(backend_, bytes);
+    if (!b) return std::unexpected(b.error());
+    host_pool_[index] = std::move(*b);
+  }
+  return host_pool_[index].data();
+}
+
 Result<void> Executor::run_host(const std::string &kernel, const ShapeMap &shape,
                                 const std::vector<void *> &host) {
   if (auto r = backend_->make_current(); !r) return r;

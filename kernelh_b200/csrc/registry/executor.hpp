@@ -41,6 +41,12 @@ public:
   Result<void *> workspace(size_t bytes);
   Result<void> launch(KernelFunction fn, const LaunchStep &step, LaunchArgs &args, StreamHandle s);
   uint32_t *status_word() const { return static_cast<uint32_t *>(status_.data()); }
+  // The three streams of the host-buffer paths (uploads, compute, downloads), created on first use.
+  Result<HostStreams> host_streams();
+  // Device staging buffer number `index` of the host-buffer paths, at least `bytes` large (grow-only).
+  Result<void *> host_staging(size_t index, size_t bytes);
+  // A two-phase host-buffer call parks its second half here between the phases.
+  std::function<Result<void>(void *)> pending_host_finish;
 
   // Per-launch timing: while enabled, every launch is bracketed by two events
   // on its stream. profile_report() waits for them and returns
@@ -88,6 +94,18 @@ private:
 Result<void> run_gemm_allgather(Executor &ex, const void *a_shard, const void *b,
                                 const std::vector<void *> &replicas, void *multicast, int rank,
                                 int world, int64_t m_shard, int64_t n, int64_t k, StreamHandle stream);
+
+// The M-row-sharded product on HOST buffers, in two phases with the caller's barrier across
+// ranks in between. begin: this rank's slice of B (rows [rank * k / world, (rank + 1) * k /
+// world)) is uploaded into its own replica of B and sent on to every other replica over NVLink
+// (multimem.st through `b_multicast`, or peer stores), while the upload of the A shard starts;
+// returns when the slice has gone out. finish (after every rank's begin has returned and a
+// barrier was passed): B is split, the A blocks are split and multiplied as they arrive, and
+// the rows of C go back to `c_shard_host`; returns when they are there.
+Result<void> run_gemm_host_sharded_begin(Executor &ex, const void *a_shard_host, const void *b_slice_host,
+                                         const std::vector<void *> &b_replicas, void *b_multicast, int rank,
+                                         int world, int64_t m_shard, int64_t n, int64_t k);
+Result<void> run_gemm_host_sharded_finish(Executor &ex, void *c_shard_host);
 
 Result<void> run_scan_lookback_probe(Executor &ex, const void *x, void *y, int64_t n, uint32_t spin_limit,
                                      StreamHandle stream);

@@ -431,6 +431,38 @@ def test_gemm_allgather_two_shards_fill_every_replica(ctx, oracle):
         ctx.gemm_allgather(da, db, replicas, 2, 256, n, k, stream)
 
 
+def test_gemm_host_sharded_uploads_each_slice_of_b_once(ctx, oracle):
+    """The sharded product on host buffers: every rank uploads only its rows of B, the slices
+    are sent on to every replica of B, and after the ranks have met each one multiplies its
+    rows of A. Two ranks are played here by two contexts on one GPU (plain replica pointers,
+    no multicast address); the rows of C equal the device path bit for bit."""
+    m, n, k = 640, 384, 256
+    a = oracle.uniform((m, k), oracle.BASE_SEED + 51, -1, 1)
+    b = oracle.uniform((k, n), oracle.BASE_SEED + 52, -1, 1)
+    plain = run(ctx, "gemm", f"m={m},n={n},k={k}", [a, b], (m, n))
+    ranks = [ctx, kh.Context(0)]
+    try:
+        replicas = [torch.full((k, n), float("nan"), device="cuda") for _ in range(2)]
+        c_host = [np.full((m // 2, n), np.nan, np.float32) for _ in range(2)]
+        for r in range(2):
+            ranks[r].gemm_host_sharded_begin(np.ascontiguousarray(a[r * m // 2:(r + 1) * m // 2]),
+                                             np.ascontiguousarray(b[r * k // 2:(r + 1) * k // 2]),
+                                             replicas, 0, r, m // 2, n, k)
+        torch.cuda.synchronize()  # stands in for the barrier across ranks
+        for rep in replicas:
+            assert np.array_equal(rep.cpu().numpy(), b)  # both slices reached both replicas
+        for r in range(2):
+            ranks[r].gemm_host_sharded_finish(c_host[r])
+        assert np.array_equal(np.concatenate(c_host), plain)
+        with pytest.raises(kh.KernelhError) as e:  # finish without begin
+            ranks[0].gemm_host_sharded_finish(c_host[0])
+        assert e.value.code == kh.USAGE_ERROR and "without a begin" in e.value.message
+        with pytest.raises(kh.KernelhError):  # k does not split over three ranks
+            ranks[0].gemm_host_sharded_begin(a, b, replicas + [replicas[0]], 0, 0, m, n, k)
+    finally:
+        ranks[1].close()
+
+
 # --------------------------------------------------------------------------- attention
 def attention_inputs(oracle, b, h, s):
     return (oracle.lcg((b, h, s, 64), 0x313A171B), oracle.lcg((b, h, s, 64), 0x51AC0D3E),
