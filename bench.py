@@ -6,8 +6,8 @@
     python bench.py --impl reference --gpus N --steps K ...  # the reference's fp64 CPU routine
 
 One "step" is one pass of the path over one batch of synthetic input: the
-operand split, the tensor-core GEMM and (N > 1) the all-gather of the C row
-shards. Rank 0 prints ONE JSON line. Under torchrun every rank owns one GPU;
+operand preparation (scaled fp16 hi/lo splits of A and of B^T), the tensor-core
+GEMM and (N > 1) the all-gather of the C row shards. Rank 0 prints ONE JSON line. Under torchrun every rank owns one GPU;
 A and C are sharded by M-row blocks, B is replicated before timing (input
 placement), and the NCCL all-gather of C is inside the timed region.
 """
@@ -464,7 +464,8 @@ def gpu_arm(args) -> None:
             traffic = int(found.group(1)) / world
     roofline = {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
                 "frac": achieved / peak, "traffic": traffic, "kernel": ("gemm_allgather" if gather == "p2p" else "gemm") + " (tcgen05 3xFP16)",
-                "kernel_ms": kernel_ms, "split_ms": (prof["gemm_split_a"][1] + prof["gemm_colmax_b"][1] + prof["gemm_split_bt"][1]) / gemm_launches,
+                "kernel_ms": kernel_ms, "split_ms": sum(v[1] for k_, v in prof.items() if k_ not in ("gemm", "gemm_allgather")) / gemm_launches,
+                "split_kernels": {k_: v[1] / v[0] for k_, v in prof.items() if k_ not in ("gemm", "gemm_allgather")},
                 "peak_note": f"bf16_tflops_sustained of {peaks['source']} / 3 (three fp16 products per fp32-class multiply-add)"}
 
     # ---- parity of the timed path, asserted on every rank (checker, not measured) ----------
@@ -523,7 +524,7 @@ def gpu_arm(args) -> None:
                        ") + barrier, inside the timed step" if gather == "p2p" else
                        "NCCL all-gather of C inside the timed step")) if world > 1 else "single GPU",
                    "l2": "inputs (2 x 256 MiB) and the 512 MiB operand-split scratch are larger than the 126 MB L2",
-                   "step": "gemm_split_a + gemm_colmax_b + gemm_split_bt + " + {"none": "gemm", "nccl": "gemm + nccl all_gather",
+                   "step": "gemm_split_a + gemm_prep_b + " + {"none": "gemm", "nccl": "gemm + nccl all_gather",
                                                                  "p2p": "gemm_allgather + barrier"}[gather]},
         "roofline": roofline, "gpu_launches": int(launches),
         "sampled_max_err_over_rms": err, "parity": parity,

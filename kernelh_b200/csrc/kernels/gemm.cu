@@ -486,6 +486,168 @@ __device__ __forceinline__ void umma_commit_pair(uint32_t cluster_addr) {
                : "memory");
 }
 
+} // namespace
+
+// The same two steps (column maxima, then B^T hi / lo) in ONE pass over B, for the common case of
+// a contiguous, 16-byte aligned B whose column strips fit the shared memory of a cluster: a
+// cluster of sixteen CTAs owns a strip of 32 columns (128 bytes of every row); CTA r of the
+// cluster copies rows [r * R, (r + 1) * R) of the strip into its shared memory with tensor-map
+// copies (128-byte swizzle; rows and columns past the end arrive as zeros), takes the column
+// maxima of its rows, the CTAs exchange them through distributed shared memory, and every CTA
+// then scales and splits its rows straight out of shared memory. B is read from HBM once
+// (gemm_colmax_b + gemm_split_bt read it twice), and three CTAs fit an SM at k = 8192, so the
+// copies of one overlap the arithmetic of the others. Results leave as 64 (k) x 32 (n) boxes of
+// B^T hi and lo, which together are exactly as large as the 64 rows of the strip they come from
+// and are built IN PLACE over them (256 rows at a time: read all, barrier, write the 16-byte
+// pieces in the 128-byte swizzle, barrier, one tensor-map copy per box); nothing is reused, so
+// no copy is ever waited for before the end.
+// Parameters: B as a rank-2 descriptor, the tensor maps of B (box 32 columns x 64 rows) and
+// of B^T hi / lo (box 64 k-values x 32 rows), the exponent array, rows per CTA (a multiple of
+// 256), the status word. The cluster size is the launch's.
+constexpr int kPrepCols = 32;
+constexpr int kPrepBoxRows = 64;                                // rows of B per tensor-map copy
+constexpr int kPrepBoxBytes = kPrepBoxRows * kPrepCols * 4;     // 8 KiB = a hi box + a lo box of B^T
+constexpr int kPrepGroupRows = 256;                             // rows handled between two barriers
+constexpr int kPrepGroupBoxes = kPrepGroupRows / kPrepBoxRows;
+constexpr int kPrepMaxGroups = 6;                               // 6 x 32 KiB of rows fit an SM
+
+extern "C" __global__ void __launch_bounds__(256, 3)
+gemm_prep_b(KH_MEMREF2(const float, b), const __grid_constant__ khd::TensorMap tm_b,
+            const __grid_constant__ khd::TensorMap tm_bt_hi, const __grid_constant__ khd::TensorMap tm_bt_lo,
+            int *__restrict__ b_shift, int64_t rows_per_cta, uint32_t *status) {
+  extern __shared__ uint8_t prep_raw[];
+  __shared__ __align__(8) uint64_t landed[kPrepMaxGroups];
+  __shared__ float warp_max[8][kPrepCols];
+  __shared__ float cta_max[kPrepCols];     // read by the other CTAs of the cluster
+  __shared__ int col_shift[kPrepCols];
+  __shared__ int s_abort;
+  (void)b_alloc; (void)b_ptr; (void)b_off; (void)b_stride0; (void)b_stride1;
+
+  const int64_t k = b_size0, n = b_size1;
+  const int64_t kp = ((k + 31) / 32) * 32;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  uint32_t rank, cluster_ctas;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(rank));
+  asm volatile("mov.u32 %0, %%cluster_nctarank;" : "=r"(cluster_ctas));
+  const int64_t strip = blockIdx.x / cluster_ctas;
+  const int n0 = static_cast<int>(strip * kPrepCols);
+  const int64_t row0 = static_cast<int64_t>(rank) * rows_per_cta;
+  const int groups = static_cast<int>(rows_per_cta / kPrepGroupRows);
+  uint8_t *rows_smem = prep_raw + ((1024u - (khd::smem_u32(prep_raw) & 1023u)) & 1023u);
+  const uint32_t rows_addr = khd::smem_u32(rows_smem);
+
+  if (threadIdx.x == 0) {
+    s_abort = 0;
+    for (int g = 0; g < groups; ++g) khd::mbar_init(khd::smem_u32(&landed[g]), 1);
+    khd::mbar_fence_init();
+    for (int g = 0; g < groups; ++g) {
+      // groups that start past the last row of B hold nothing but padding: no copy is started
+      // for them (and none is waited for below; every copy that is started is also awaited)
+      if (row0 + static_cast<int64_t>(g) * kPrepGroupRows >= k) break;
+      const uint32_t bar = khd::smem_u32(&landed[g]);
+      khd::mbar_arrive_expect_tx(bar, kPrepGroupBoxes * kPrepBoxBytes);
+      for (int i = 0; i < kPrepGroupBoxes; ++i) {
+        const int box = g * kPrepGroupBoxes + i;
+        khd::tma_load_2d(rows_addr + box * kPrepBoxBytes, &tm_b, n0, static_cast<int>(row0 + box * kPrepBoxRows), bar);
+      }
+    }
+  }
+  __syncthreads();
+
+  // Element (row r, column `lane`) of this CTA's rows: the copies store 16-byte group c / 4 of a
+  // row at position (c / 4) ^ (r & 7). A warp reads one row across its lanes: no bank conflicts.
+  const uint32_t lane_bytes = static_cast<uint32_t>(lane & 3) * 4;
+  const auto element = [&](int r) -> float {
+    const uint32_t off = static_cast<uint32_t>(r) * 128u +
+                         ((static_cast<uint32_t>(lane >> 2) ^ (static_cast<uint32_t>(r) & 7u)) << 4) + lane_bytes;
+    return *reinterpret_cast<const float *>(rows_smem + off);
+  };
+
+  // ---- largest magnitude per column: this CTA's rows, then the cluster's ----
+  float mx = 0.f;
+  bool ok = true;
+  for (int g = 0; g < groups && ok; ++g) {
+    if (row0 + static_cast<int64_t>(g) * kPrepGroupRows >= k) break; // only padding from here on
+    ok = khd::mbar_wait(khd::smem_u32(&landed[g]), 0u, &s_abort, status, khd::kStatusTmaWaitTimeout, 0x50u + g);
+    if (!ok) break;
+#pragma unroll 8
+    for (int q = 0; q < kPrepGroupRows / 8; ++q) mx = fmaxf(mx, fabsf(element(g * kPrepGroupRows + q * 8 + warp)));
+  }
+  warp_max[warp][lane] = mx;
+  __syncthreads();
+  if (threadIdx.x < kPrepCols) {
+    float m = warp_max[0][threadIdx.x];
+#pragma unroll
+    for (int w = 1; w < 8; ++w) m = fmaxf(m, warp_max[w][threadIdx.x]);
+    cta_max[threadIdx.x] = m;
+  }
+  cluster_sync_all(); // every CTA's maxima are written (release / acquire across the cluster)
+  if (threadIdx.x < kPrepCols) {
+    float m = 0.f;
+    for (uint32_t r = 0; r < cluster_ctas; ++r) {
+      float v;
+      asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(map_to_cta(khd::smem_u32(&cta_max[threadIdx.x]), r)));
+      m = fmaxf(m, v);
+    }
+    const int shift = scale_shift(m);
+    col_shift[threadIdx.x] = shift;
+    if (rank == 0 && n0 + static_cast<int>(threadIdx.x) < n) b_shift[n0 + threadIdx.x] = shift;
+  }
+  cluster_sync_all(); // nobody reads a CTA's maxima after this; also publishes col_shift to the block
+  if (s_abort) return; // a copy never landed (block-uniform after the barriers): reported in the status word
+
+  // ---- scale, split, transpose, in place: 256 rows (k-values) x 32 columns at a time ----
+  // Thread (column `lane`, warp w) owns the 16-byte pieces w, w + 8, w + 16, w + 24 of its column:
+  // k-values piece * 8 .. + 7 of the group, one piece of a hi box and of a lo box each.
+  const RowScale scale = row_scale(col_shift[lane]);
+  for (int g = 0; g < groups; ++g) {
+    const int64_t k_group = row0 + static_cast<int64_t>(g) * kPrepGroupRows;
+    if (k_group >= kp) break; // past the padded k: nothing to write (block-uniform)
+    const bool real = k_group < k; // else the rows are all padding and no copy was started
+    Half8 h[4], l[4];
+#pragma unroll
+    for (int part = 0; part < 4; ++part) {
+      const int r = g * kPrepGroupRows + (warp + 8 * part) * 8;
+#pragma unroll
+      for (int q = 0; q < 4; ++q)
+        split_fp16x2(real ? element(r + 2 * q) : 0.f, real ? element(r + 2 * q + 1) : 0.f, scale, h[part].v[q],
+                     l[part].v[q]);
+    }
+    __syncthreads(); // every value of the group is in registers: its bytes may be overwritten
+#pragma unroll
+    for (int part = 0; part < 4; ++part) {
+      const int piece = warp + 8 * part; // 0..31
+      const int box = g * kPrepGroupBoxes + (piece >> 3);
+      // row `lane` of the box (one column of B), 16-byte piece (piece & 7), stored at piece ^ (row & 7)
+      const uint32_t at = static_cast<uint32_t>(box) * kPrepBoxBytes + static_cast<uint32_t>(lane) * 128u +
+                          (((static_cast<uint32_t>(piece) & 7u) ^ (static_cast<uint32_t>(lane) & 7u)) << 4);
+      *reinterpret_cast<Half8 *>(rows_smem + at) = h[part];
+      *reinterpret_cast<Half8 *>(rows_smem + at + kPrepBoxBytes / 2) = l[part];
+    }
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); // the copy engine reads these stores
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      for (int i = 0; i < kPrepGroupBoxes; ++i) {
+        const int box = g * kPrepGroupBoxes + i;
+        const int64_t kx = row0 + static_cast<int64_t>(box) * kPrepBoxRows;
+        if (kx >= kp) break;
+        asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.tile.bulk_group [%0, {%1, %2}], [%3];" ::"l"(
+                         reinterpret_cast<uint64_t>(&tm_bt_hi)),
+                     "r"(static_cast<int>(kx)), "r"(n0), "r"(rows_addr + box * kPrepBoxBytes)
+                     : "memory");
+        asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.tile.bulk_group [%0, {%1, %2}], [%3];" ::"l"(
+                         reinterpret_cast<uint64_t>(&tm_bt_lo)),
+                     "r"(static_cast<int>(kx)), "r"(n0), "r"(rows_addr + box * kPrepBoxBytes + kPrepBoxBytes / 2)
+                     : "memory");
+      }
+      asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+    }
+  }
+  if (threadIdx.x == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+}
+
+namespace {
+
 struct PendingPush {
   int m0, n0;
   int next_unit; // 0..32; 32 = done

@@ -264,8 +264,40 @@ GemmScratch gemm_scratch(int64_t m, int64_t n, int64_t kp) {
   return g;
 }
 
-// The four launches of one m x n x k product: split A, column maxima of B,
-// split B^T, multiply.
+// The cluster size gemm_prep_b is launched with (8 or 16 CTAs) and the rows of B one CTA then
+// holds (a multiple of 256); {0, 0} when the one-pass preparation does not apply: rows of B must
+// be 16-byte multiples for the tensor map, and a strip must fit the shared memory of a cluster.
+constexpr int kPrepCols = 32, kPrepBoxRows = 64, kPrepGroupRows = 256, kPrepMaxGroups = 6;
+struct PrepShape {
+  int cluster;
+  int64_t rows;
+};
+PrepShape prep_b_shape(int64_t n, int64_t k) {
+  if (n % 4 != 0) return {0, 0};
+  const int64_t kp = (k + kGemmBK - 1) / kGemmBK * kGemmBK;
+  for (int cluster : {8, 16}) { // the larger (not portable, opt-in) size only for strips eight CTAs cannot hold three to an SM
+    const int64_t rows = ((kp + cluster - 1) / cluster + kPrepGroupRows - 1) / kPrepGroupRows * kPrepGroupRows;
+    if (rows / kPrepGroupRows <= (cluster == 8 ? 2 : kPrepMaxGroups)) return {cluster, rows};
+  }
+  return {0, 0};
+}
+int64_t prep_b_rows_per_cta(int64_t n, int64_t k) { return prep_b_shape(n, k).rows; }
+LaunchStep gemm_prep_b_step(int64_t n, int64_t k) {
+  const PrepShape shape = prep_b_shape(n, k);
+  LaunchStep s;
+  s.entry = "gemm_prep_b";
+  s.block = {256, 1, 1};
+  s.cluster = static_cast<unsigned>(shape.cluster);
+  s.grid = {static_cast<unsigned>(((n + kPrepCols - 1) / kPrepCols) * shape.cluster), 1, 1};
+  // the CTA's rows of the strip (the boxes of B^T are built in place over them) and alignment slack
+  s.dynamic_smem = static_cast<size_t>(shape.rows) * kPrepCols * 4 + 1024;
+  s.param_count = 7 + 3 + 3;
+  return s;
+}
+
+// The launches of one m x n x k product: split A, prepare B (one pass: gemm_prep_b; or,
+// where that does not apply, column maxima of B and then the split of B^T), multiply.
+// The list always has the two-pass steps at [1] and [2]; `fused` tells which are used.
 std::vector<LaunchStep> gemm_steps(int64_t m, int64_t n, int64_t k, const DeviceLimits &l) {
   const int64_t kp = (k + kGemmBK - 1) / kGemmBK * kGemmBK;
   const long sms = sm_count(l);
@@ -312,6 +344,8 @@ KernelPlan plan_gemm(const ShapeMap &shape, const DeviceLimits &l) {
   const int64_t kp = (k + kGemmBK - 1) / kGemmBK * kGemmBK;
   p.workspace_bytes = gemm_scratch(m, n, kp).total;
   p.steps = gemm_steps(m, n, k, l);
+  if (prep_b_rows_per_cta(n, k) > 0) // one pass over B instead of two (taken when B is 16-byte aligned)
+    p.steps = {p.steps[0], gemm_prep_b_step(n, k), p.steps[3]};
   p.work = 2.0 * static_cast<double>(m) * static_cast<double>(n) * static_cast<double>(k);
   p.work_is_flops = true;
   return p;
@@ -332,12 +366,12 @@ struct GemmJob {
   int64_t m, n, k, kp;
   GemmScratch lay;
   char *base = nullptr; // scratch
-  KernelFunction split_a, colmax_b, split_bt, multiply, multiply_gather;
+  KernelFunction split_a, colmax_b, split_bt, prep_b, multiply, multiply_gather;
   uint64_t at(size_t off) const { return reinterpret_cast<uint64_t>(base + off); }
 };
 
 Result<GemmJob> gemm_job(Executor &ex, int64_t m, int64_t n, int64_t k) {
-  GemmJob j{ex, m, n, k, (k + kGemmBK - 1) / kGemmBK * kGemmBK, {}, nullptr, {}, {}, {}, {}, {}};
+  GemmJob j{ex, m, n, k, (k + kGemmBK - 1) / kGemmBK * kGemmBK, {}, nullptr, {}, {}, {}, {}, {}, {}};
   j.lay = gemm_scratch(m, n, j.kp);
   auto ws = ex.workspace(j.lay.total);
   if (!ws) return std::unexpected(ws.error());
@@ -345,6 +379,7 @@ Result<GemmJob> gemm_job(Executor &ex, int64_t m, int64_t n, int64_t k) {
   const std::pair<const char *, KernelFunction *> entries[] = {{"gemm_split_a", &j.split_a},
                                                                {"gemm_colmax_b", &j.colmax_b},
                                                                {"gemm_split_bt", &j.split_bt},
+                                                               {"gemm_prep_b", &j.prep_b},
                                                                {"gemm", &j.multiply},
                                                                {"gemm_allgather", &j.multiply_gather}};
   for (const auto &[name, slot] : entries) {
@@ -355,10 +390,52 @@ Result<GemmJob> gemm_job(Executor &ex, int64_t m, int64_t n, int64_t k) {
   return j;
 }
 
-// Column maxima, exponents and the fp16 splits of B^T. `clear_maxima`: zero the
-// maxima here (otherwise the gemm_split_a launched before this did).
-Result<void> gemm_enqueue_b(const GemmJob &j, const void *b_dev, const std::vector<LaunchStep> &steps,
-                            StreamHandle stream, bool clear_maxima) {
+// Exponents and the fp16 splits of B^T: in one pass over B (gemm_prep_b) when B is 16-byte
+// aligned and its strips fit, else column maxima first and the split after. `clear_maxima`:
+// zero the maxima of the two-pass form here (otherwise the gemm_split_a launched before did).
+Result<void> gemm_enqueue_b(const GemmJob &j, const void *b_dev, StreamHandle stream, bool clear_maxima) {
+  const int64_t rows_per_cta = prep_b_rows_per_cta(j.n, j.k);
+  if (rows_per_cta > 0 && first_misaligned16({{"B", b_dev}}) == nullptr) {
+    TensorMapSpec in;
+    in.global_address = b_dev;
+    in.rank = 2;
+    in.elem_bytes = 4;
+    in.dims[0] = static_cast<uint64_t>(j.n);
+    in.dims[1] = static_cast<uint64_t>(j.k);
+    in.strides_bytes[0] = static_cast<uint64_t>(j.n) * 4;
+    in.box[0] = kPrepCols;
+    in.box[1] = kPrepBoxRows;
+    in.swizzle_bytes = 128;
+    auto t_b = j.ex.backend().encode_tensor_map(in);
+    if (!t_b) return std::unexpected(t_b.error());
+    const auto out_map = [&](size_t offset) {
+      TensorMapSpec o;
+      o.global_address = j.base + offset;
+      o.rank = 2;
+      o.elem_bytes = 2;
+      o.dims[0] = static_cast<uint64_t>(j.kp);
+      o.dims[1] = static_cast<uint64_t>(j.n);
+      o.strides_bytes[0] = static_cast<uint64_t>(j.kp) * 2;
+      o.box[0] = kPrepBoxRows; // 64 k-values: one 128-byte swizzle row
+      o.box[1] = kPrepCols;
+      o.swizzle_bytes = 128;
+      return j.ex.backend().encode_tensor_map(o);
+    };
+    auto t_hi = out_map(j.lay.b_hi);
+    if (!t_hi) return std::unexpected(t_hi.error());
+    auto t_lo = out_map(j.lay.b_lo);
+    if (!t_lo) return std::unexpected(t_lo.error());
+    LaunchArgs args;
+    args.add_memref(const_cast<void *>(b_dev), {j.k, j.n});
+    args.add_tensor_map(*t_b);
+    args.add_tensor_map(*t_hi);
+    args.add_tensor_map(*t_lo);
+    args.add_scalar<uint64_t>(j.at(j.lay.b_shift));
+    args.add_scalar<int64_t>(rows_per_cta);
+    args.add_scalar<uint64_t>(reinterpret_cast<uint64_t>(j.ex.status_word()));
+    return j.ex.launch(j.prep_b, gemm_prep_b_step(j.n, j.k), args, stream);
+  }
+  const std::vector<LaunchStep> steps = gemm_steps(j.m, j.n, j.k, j.ex.limits());
   if (clear_maxima)
     if (auto r = j.ex.backend().memset32_async(j.base + j.lay.b_amax, 0, static_cast<size_t>(j.n), stream); !r)
       return r;
@@ -447,8 +524,8 @@ Result<void> launch_gemm(Executor &ex, const KernelPlan &p, const std::vector<vo
   auto job = gemm_job(ex, m, n, k);
   if (!job) return std::unexpected(job.error());
   if (auto r = gemm_enqueue_a(*job, b[0], 0, m, p.steps[0], stream, n); !r) return r;
-  if (auto r = gemm_enqueue_b(*job, b[1], p.steps, stream, false); !r) return r;
-  return gemm_enqueue_multiply(*job, b[0], b[1], gather ? nullptr : b[2], 0, m, p.steps[3], stream, gather);
+  if (auto r = gemm_enqueue_b(*job, b[1], stream, false); !r) return r;
+  return gemm_enqueue_multiply(*job, b[0], b[1], gather ? nullptr : b[2], 0, m, p.steps.back(), stream, gather);
 }
 
 Result<void> run_gemm(Executor &ex, const KernelPlan &p, const std::vector<void *> &b,
@@ -484,7 +561,7 @@ Result<void> run_gemm_host(Executor &ex, const KernelPlan &p, const std::vector<
     if (!b_up) return std::unexpected(b_up.error());
     if (auto r = be.event_record(*b_up, hs.in); !r) return r;
     if (auto r = be.stream_wait_event(hs.compute, *b_up); !r) return r;
-    if (auto r = gemm_enqueue_b(*job, dev[1], p.steps, hs.compute, true); !r) return r;
+    if (auto r = gemm_enqueue_b(*job, dev[1], hs.compute, true); !r) return r;
     for (int64_t i = 0; i < blocks; ++i) {
       const int64_t row0 = i * block_rows, rows = std::min(block_rows, m - row0);
       char *a_rows = static_cast<char *>(dev[0]) + static_cast<size_t>(row0 * k) * 4;
@@ -677,13 +754,12 @@ Result<void> run_gemm_host_sharded_begin(Executor &ex, const void *a_shard_host,
   const HostStreams streams = *hs;
   void *a_dev = *dev_a, *c_dev = *dev_c;
   const GemmJob j = *job;
-  const std::vector<LaunchStep> b_steps = plan.steps;
-  ex.pending_host_finish = [&ex, j, streams, a_dev, c_dev, b_local, b_steps, a_events, m_shard, n, k, block_rows,
+  ex.pending_host_finish = [&ex, j, streams, a_dev, c_dev, b_local, a_events, m_shard, n, k, block_rows,
                             blocks](void *c_host) -> Result<void> {
     Backend &be2 = ex.backend();
     std::vector<EventHandle> events = a_events;
     const auto body = [&]() -> Result<void> {
-      if (auto r = gemm_enqueue_b(j, b_local, b_steps, streams.compute, true); !r) return r;
+      if (auto r = gemm_enqueue_b(j, b_local, streams.compute, true); !r) return r;
       for (int64_t i = 0; i < blocks; ++i) {
         const int64_t row0 = i * block_rows, rows = std::min(block_rows, m_shard - row0);
         char *a_rows = static_cast<char *>(a_dev) + static_cast<size_t>(row0 * k) * 4;

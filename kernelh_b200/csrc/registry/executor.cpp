@@ -92,6 +92,11 @@ Result<void> Executor::launch(KernelFunction fn, const LaunchStep &step, LaunchA
                                       r.error().message);
     fi->optin_smem = step.dynamic_smem;
   }
+  if (step.cluster > 8 && fi != nullptr && !fi->large_clusters) {
+    if (auto r = backend_->function_allow_large_clusters(fn.handle); !r)
+      return fail(r.error().code, "launch of '" + step.entry + "': " + r.error().message);
+    fi->large_clusters = true;
+  }
   // Limits are checked analytically on every launch; the driver's occupancy
   // answer is asked for by KernelLaunch::launch and the occupancy report.
   LaunchVerifier verifier;

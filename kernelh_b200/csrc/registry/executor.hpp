@@ -67,6 +67,7 @@ private:
     KernelFunction fn;
     size_t static_smem = 0;
     size_t optin_smem = 0; // largest dynamic size already opted in
+    bool large_clusters = false; // opted in to cluster sizes above eight
   };
   std::shared_ptr<Backend> backend_;
   DeviceInfo info_;

@@ -92,6 +92,8 @@ public:
   virtual Result<void> module_unload(void *module) = 0;
   virtual Result<FunctionAttributes> function_attributes(void *function) = 0;
   virtual Result<void> function_set_max_dynamic_smem(void *function, size_t bytes) = 0;
+  // Cluster sizes above eight CTAs are not portable: a kernel has to opt in before such a launch.
+  virtual Result<void> function_allow_large_clusters(void *function) = 0;
   virtual Result<int> occupancy_max_blocks(void *function, int block_size, size_t dyn_smem) = 0;
   virtual Result<TensorMapBytes> encode_tensor_map(const TensorMapSpec &spec) = 0;
 

@@ -254,6 +254,13 @@ public:
       return err(r, "cuFuncSetAttribute(MAX_DYNAMIC_SHARED_SIZE_BYTES)");
     return {};
   }
+  Result<void> function_allow_large_clusters(void *function) override {
+    if (CUresult r = api_.FuncSetAttribute(static_cast<CUfunction>(function),
+                                           CU_FUNC_ATTRIBUTE_NON_PORTABLE_CLUSTER_SIZE_ALLOWED, 1);
+        r != CUDA_SUCCESS)
+      return err(r, "cuFuncSetAttribute(NON_PORTABLE_CLUSTER_SIZE_ALLOWED)");
+    return {};
+  }
   Result<int> occupancy_max_blocks(void *function, int block_size, size_t dyn_smem) override {
     int blocks = 0;
     if (CUresult r = api_.OccupancyMaxActiveBlocks(&blocks, static_cast<CUfunction>(function),

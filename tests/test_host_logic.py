@@ -196,14 +196,18 @@ def test_plans_for_the_benchmark_configurations():
     assert kh.verify_launch("sm_100a", p.block[0], tuple(p.grid), 2048, p.dynamic_smem) == ""
     assert kh.plan("scan", "n=67108864").grid[0] == 148
     p = kh.plan("gemm", "m=8192,n=8192,k=8192")
-    # split A, column maxima of B, split B^T, then 74 two-CTA clusters
-    assert p.entry == b"gemm" and p.n_launches == 4 and p.grid[0] == 148 and p.block[0] == 320
+    # split A, B prepared in one pass (sixteen-CTA clusters over 32-column strips), then 74 two-CTA clusters
+    assert p.entry == b"gemm" and p.n_launches == 3 and p.grid[0] == 148 and p.block[0] == 320
     assert p.dynamic_smem == 6 * 32768 + 1024 and p.tmem_columns == 512
     assert p.workspace_bytes == 4 * 8192 * 8192 * 2 + 3 * 8192 * 4  # fp16 hi/lo of A and B^T, exponents, maxima
     assert p.work == 1099511627776.0 and p.work_is_flops
     assert kh.verify_launch("sm_100a", p.block[0], tuple(p.grid), 48, p.dynamic_smem) == ""
     p = kh.plan("gemm", "m=1000,n=1000,k=1000")
     assert p.grid[0] == 2 * 4 * 4  # 16 tiles of 256 x 256, a cluster each
+    # rows of B that are not 16-byte multiples (or strips too tall for eight SMs) keep the two-pass form
+    assert kh.plan("gemm", "m=129,n=257,k=33").n_launches == 4
+    assert kh.plan("gemm", "m=64,n=64,k=32768").n_launches == 4
+    assert kh.plan("gemm", "m=64,n=64,k=24576").n_launches == 3
     assert p.workspace_bytes == 4 * 1000 * 1024 * 2 + 3 * 4096
     p = kh.plan("attention", "batch=8,heads=16,seq=1024,head_dim=64")
     assert p.grid[0] == 148 and p.param_count == 52 and p.work == 34359738368.0
