@@ -255,6 +255,25 @@ int kh_plan(const char *kernel, const char *shape, const char *target_token, int
  * `kernelh compile --target nvptx-sm_100a` writes as <name>.cubin). */
 int kh_kernel_image(const char *kernel, const void **image, size_t *size);
 
+/* Resource figures of a kernel's entry point, from the `ptxas -v` output of the
+ * build that made the embedded code object: the reference's resources.json
+ * (lib/compiler/resource_reporter.cpp:674-690: kernel, target, vgpr_count,
+ * sgpr_count, lds_bytes, wavefront_size, occupancy_estimate) followed by the
+ * entry symbol, barriers, stack and spill bytes. `entry` NULL or "" = the
+ * entry named like the kernel. fields6 (may be NULL): registers, static
+ * shared bytes, stack bytes, spill store bytes, spill load bytes, barriers. */
+int kh_kernel_resources(const char *kernel, const char *entry, const char *target_token, char *json, int cap,
+                        int64_t *fields6);
+/* The parser behind it, on any `ptxas -v` text (resource_reporter.cpp:614-660):
+ * the figures of `entry` (NULL or "" = the first entry in the text). */
+int kh_parse_ptxas(const char *text, const char *entry, int64_t *fields6);
+/* `kernelh bench --occupancy` (tools/kernelh/main.cpp:2082-2126): the analytic
+ * occupancy report of every launch the library makes for `shape`, fed with the
+ * registers and static shared memory of kh_kernel_resources, as occupancy.json
+ * and occupancy.md text (either buffer may be NULL). */
+int kh_occupancy_report(const char *kernel, const char *shape, const char *target_token, int sm_count, char *json,
+                        int json_cap, char *markdown, int markdown_cap);
+
 /* ---- host helpers ----------------------------------------------------------------
  * LaunchArgs::add_memref (lib/runtime/descriptor_packing.cpp:19-39): packs
  * `count` buffers; shapes are concatenated, ranks[i] dims each. Returns the

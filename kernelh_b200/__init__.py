@@ -98,6 +98,10 @@ def _load() -> C.CDLL:
     L.kh_registered_kernels.argtypes = [C.c_char_p, C.c_int]
     L.kh_plan.argtypes = [C.c_char_p, C.c_char_p, C.c_char_p, C.c_int, C.POINTER(PlanInfo)]
     L.kh_kernel_image.argtypes = [C.c_char_p, C.POINTER(vp), C.POINTER(C.c_size_t)]
+    L.kh_kernel_resources.argtypes = [C.c_char_p, C.c_char_p, C.c_char_p, C.c_char_p, C.c_int, C.POINTER(C.c_int64)]
+    L.kh_parse_ptxas.argtypes = [C.c_char_p, C.c_char_p, C.POINTER(C.c_int64)]
+    L.kh_occupancy_report.argtypes = [C.c_char_p, C.c_char_p, C.c_char_p, C.c_int, C.c_char_p, C.c_int,
+                                      C.c_char_p, C.c_int]
     L.kh_pack_memrefs.argtypes = [C.POINTER(C.c_uint64), C.POINTER(C.c_int64), C.POINTER(C.c_int),
                                   C.c_int, C.POINTER(C.c_uint64), C.c_int, C.POINTER(C.c_int)]
     L.kh_device_limits.argtypes = [C.c_char_p, C.POINTER(C.c_int64), C.c_char_p, C.c_int]
@@ -348,6 +352,30 @@ def kernel_image(kernel: str) -> bytes:
     p, n = C.c_void_p(), C.c_size_t()
     _check(lib.kh_kernel_image(kernel.encode(), C.byref(p), C.byref(n)))
     return C.string_at(p.value, n.value)
+
+
+RESOURCE_FIELDS = ("registers", "smem_bytes", "stack_bytes", "spill_store_bytes", "spill_load_bytes", "barriers")
+
+
+def kernel_resources(kernel: str, entry: str | None = None, target: str = "sm_100a") -> tuple[dict, str]:
+    """(figures, resources.json text) of an entry point, from the build's ptxas -v output."""
+    buf = C.create_string_buffer(4096)
+    f = (C.c_int64 * 6)()
+    _check(lib.kh_kernel_resources(kernel.encode(), entry.encode() if entry else None, target.encode(), buf, 4096, f))
+    return dict(zip(RESOURCE_FIELDS, [int(v) for v in f])), buf.value.decode()
+
+
+def parse_ptxas(text: str, entry: str | None = None) -> dict:
+    f = (C.c_int64 * 6)()
+    _check(lib.kh_parse_ptxas(text.encode(), entry.encode() if entry else None, f))
+    return dict(zip(RESOURCE_FIELDS, [int(v) for v in f]))
+
+
+def occupancy_report(kernel: str, shape: str, target: str = "sm_100a", sm_count: int = 148) -> tuple[str, str]:
+    """(occupancy.json text, occupancy.md text) for the launches the library makes."""
+    js, md = C.create_string_buffer(16384), C.create_string_buffer(16384)
+    _check(lib.kh_occupancy_report(kernel.encode(), shape.encode(), target.encode(), sm_count, js, 16384, md, 16384))
+    return js.value.decode(), md.value.decode()
 
 
 def pack_memrefs(ptrs, shapes) -> list[int]:

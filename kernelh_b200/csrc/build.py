@@ -74,17 +74,33 @@ def _cpp_sources() -> list[str]:
 
 
 def build_cubins(verbose: bool = False, ptxas_info: bool = False) -> list[str]:
+    """One code object per kernel source. ptxas runs verbosely every time and its per-entry
+    resource lines (registers, static shared memory, spills, barriers) are kept beside the
+    code object as ``<name>.ptxas.txt``: the library embeds that text and serves it as the
+    kernel's resources.json."""
     os.makedirs(BUILD, exist_ok=True)
     outs = []
     headers = _headers("kernels")
     for name in IMAGES:
         src = os.path.join(CSRC, "kernels", name + ".cu")
         out = os.path.join(BUILD, name + ".cubin")
+        report = os.path.join(BUILD, name + ".ptxas.txt")
         outs.append(out)
-        if _newer(out, [src] + headers) and not ptxas_info:
+        if _newer(out, [src] + headers) and _newer(report, [out]) and not ptxas_info:
             continue
-        cmd = [NVCC, "-cubin"] + NVCC_FLAGS + (["-Xptxas", "-v"] if ptxas_info else []) + ["-o", out, src]
-        _run(cmd, verbose or ptxas_info)
+        cmd = [NVCC, "-cubin"] + NVCC_FLAGS + ["-Xptxas", "-v", "-o", out, src]
+        if verbose or ptxas_info:
+            print(" ".join(cmd), flush=True)
+        res = subprocess.run(cmd, capture_output=True, text=True)
+        if res.returncode != 0:
+            sys.stderr.write(res.stdout + res.stderr)
+            raise RuntimeError(f"build step failed ({res.returncode}): {' '.join(cmd)}")
+        text = "".join(line + "\n" for line in (res.stdout + res.stderr).splitlines() if "ptxas info" in line
+                       or "bytes stack frame" in line)
+        with open(report, "w") as f:
+            f.write(text)
+        if ptxas_info:
+            print(text, flush=True)
     return outs
 
 
@@ -106,9 +122,13 @@ def _write_blob_table(cubins: list[str]) -> tuple[str, str]:
         body.append(f"extern const unsigned char kh_cubin_{name}[], kh_cubin_{name}_end[];")
     body += ["}", "namespace kh {", "const CodeObject *code_objects_begin() {",
              "  static const CodeObject objects[] = {"]
-    for name in IMAGES:
+    for name, path in zip(IMAGES, cubins):
+        with open(path[:-len(".cubin")] + ".ptxas.txt") as f:
+            report = f.read()
+        literal = "".join('\n          "' + line.replace("\\", "\\\\").replace('"', '\\"') + '\\n"'
+                          for line in report.splitlines()) or ' ""'
         body.append(f'      {{"{name}", kh_cubin_{name}, '
-                    f"static_cast<size_t>(kh_cubin_{name}_end - kh_cubin_{name})}},")
+                    f"static_cast<size_t>(kh_cubin_{name}_end - kh_cubin_{name}),{literal}}},")
     body += ["  };", "  return objects;", "}",
              f"extern const int kCodeObjectCount = {len(IMAGES)};", "} // namespace kh", ""]
     text = "\n".join(body)

@@ -9,6 +9,7 @@
 #include "../registry/registry.hpp"
 #include "../runtime/launch_verifier.hpp"
 #include "../runtime/occupancy.hpp"
+#include "../runtime/resources.hpp"
 
 #include <cstring>
 #include <string>
@@ -441,6 +442,80 @@ int kh_kernel_image(const char *kernel, const void **image, size_t *size) {
       return set_error(1, "no embedded sm_100a code object for kernel '" + rec.name + "'");
     if (image) *image = co->image;
     if (size) *size = co->size;
+    return 0;
+  });
+}
+
+int kh_parse_ptxas(const char *text, const char *entry, int64_t *fields6) {
+  if (text == nullptr || fields6 == nullptr) return set_error(2, "kh_parse_ptxas: null argument");
+  return guarded([&] {
+    for (const kh::EntryResources &e : kh::parse_ptxas_report(text)) {
+      if (entry != nullptr && *entry != '\0' && e.entry != entry) continue;
+      fields6[0] = e.registers; fields6[1] = e.smem_bytes; fields6[2] = e.stack_bytes;
+      fields6[3] = e.spill_store_bytes; fields6[4] = e.spill_load_bytes; fields6[5] = e.barriers;
+      return 0;
+    }
+    return set_error(1, std::string("unparseable ptxas output: no entry '") + (entry ? entry : "") +
+                            "' with a 'Used N registers' line");
+  });
+}
+
+int kh_kernel_resources(const char *kernel, const char *entry, const char *target_token, char *json, int cap,
+                        int64_t *fields6) {
+  return guarded([&] {
+    const std::string name(kernel ? kernel : "");
+    const kh::KernelRecord &rec = kh::find_kernel(name);
+    const kh::CodeObject *co = kh::find_code_object(rec.code_object);
+    if (co == nullptr || co->ptxas_report == nullptr)
+      return set_error(1, "no resource report embedded for kernel '" + rec.name + "'");
+    const std::string want = (entry != nullptr && *entry != '\0') ? std::string(entry) : rec.name;
+    for (const kh::EntryResources &e : kh::parse_ptxas_report(co->ptxas_report)) {
+      if (e.entry != want) continue;
+      if (json != nullptr) copy_out(kh::resources_json(e, rec.name, target_token ? target_token : "sm_100a"), json, cap);
+      if (fields6 != nullptr) {
+        fields6[0] = e.registers; fields6[1] = e.smem_bytes; fields6[2] = e.stack_bytes;
+        fields6[3] = e.spill_store_bytes; fields6[4] = e.spill_load_bytes; fields6[5] = e.barriers;
+      }
+      return 0;
+    }
+    return set_error(1, "kernel '" + rec.name + "' has no entry point '" + want + "' in its resource report");
+  });
+}
+
+int kh_occupancy_report(const char *kernel, const char *shape, const char *target_token, int sm_count, char *json,
+                        int json_cap, char *markdown, int markdown_cap) {
+  return guarded([&] {
+    const std::string token(target_token ? target_token : "sm_100a");
+    kh::DeviceLimits limits = kh::device_limits_for(token.c_str());
+    if (sm_count > 0) limits.cu_count = sm_count;
+    const std::string name(kernel ? kernel : "");
+    const kh::KernelRecord &rec = kh::find_kernel(name);
+    const kh::ShapeMap map = kh::parse_shape_text(shape ? shape : "");
+    const kh::KernelPlan plan = rec.plan(map, limits);
+    const kh::CodeObject *co = kh::find_code_object(rec.code_object);
+    const std::vector<kh::EntryResources> entries =
+        co != nullptr && co->ptxas_report != nullptr ? kh::parse_ptxas_report(co->ptxas_report)
+                                                     : std::vector<kh::EntryResources>{};
+    std::vector<kh::OccupancyReport> reports;
+    for (const kh::LaunchStep &s : plan.steps) { // one report per launch of the plan
+      kh::OccupancyInput in;
+      in.kernel = s.entry;
+      in.target = token;
+      in.config = kh::shape_to_text(map);
+      in.threads_per_workgroup = static_cast<int>(s.block.x * s.block.y * s.block.z);
+      in.dynamic_smem_bytes = static_cast<long>(s.dynamic_smem);
+      in.tmem_columns = s.tmem_columns;
+      for (const kh::EntryResources &e : entries)
+        if (e.entry == s.entry) {
+          in.vgpr_count = e.registers;
+          in.lds_bytes = e.smem_bytes;
+        }
+      kh::OccupancyReport r = kh::occupancy_report(in, limits);
+      r.measured_note = "not measured: analytic report from the build's ptxas figures";
+      reports.push_back(std::move(r));
+    }
+    if (json != nullptr) copy_out(reports.size() == 1 ? kh::occupancy_json(reports[0]) + "\n" : kh::occupancy_json_all(reports), json, json_cap);
+    if (markdown != nullptr) copy_out(kh::occupancy_markdown(reports), markdown, markdown_cap);
     return 0;
   });
 }

@@ -4,7 +4,8 @@
 // 77 when no CUDA driver or device is usable (bench/harness/run_bench.hpp:5-10).
 //
 //   kernelh compile --kernel K --shape S --target nvptx-sm_100a --out DIR
-//       writes DIR/K.cubin (the prebuilt sm_100a code object), prints
+//       writes DIR/K.cubin (the prebuilt sm_100a code object) and DIR/resources.json
+//       (registers, shared memory, occupancy estimate of the entry point), prints
 //       "wrote <file>" lines and "compile ok" like the reference's compile.
 //   kernelh run     --kernel K --shape S [--target nvptx-sm_100a] [--seed N] [--dump FILE]
 //       fills the inputs deterministically, launches once, prints a digest of
@@ -12,8 +13,10 @@
 //   kernelh bench   --kernel K --shape S [--warmup W] [--iters N] [--out DIR]
 //   kernelh bench   --suite kernelh [--out DIR]
 //       warm-up + median of event-timed launches, one results.csv row per kernel.
-//   kernelh bench   --occupancy --kernel K --shape S --target T
-//       the analytic occupancy report for the launch the library would make.
+//   kernelh bench   --occupancy --kernel K --shape S --target T [--out DIR]
+//       the analytic occupancy report of the launches the library would make, fed with
+//       the registers and static shared memory ptxas reported for each entry point;
+//       with --out also DIR/occupancy.json and DIR/occupancy.md.
 #include "kernelh_b200.h"
 
 #include <chrono>
@@ -199,7 +202,21 @@ int cmd_compile(const Flags &f) {
     std::fprintf(stderr, "kernelh: cannot write %s\n", path.c_str());
     return kExitFail;
   }
-  std::printf("wrote %s\ncompile ok\n", path.c_str());
+  std::printf("wrote %s\n", path.c_str());
+  // the resource figures of the kernel's entry point, beside the code object
+  std::vector<char> json(4096);
+  if (kh_kernel_resources(kernel.c_str(), nullptr, token.c_str(), json.data(), static_cast<int>(json.size()), nullptr) != 0) {
+    std::fprintf(stderr, "kernelh: %s\n", kh_last_error());
+    return kExitFail;
+  }
+  const std::string rpath = out + "/resources.json";
+  std::ofstream rfile(rpath, std::ios::binary);
+  rfile << json.data();
+  if (!rfile.good()) {
+    std::fprintf(stderr, "kernelh: cannot write %s\n", rpath.c_str());
+    return kExitFail;
+  }
+  std::printf("wrote %s\ncompile ok\n", rpath.c_str());
   return kExitOk;
 }
 
@@ -280,20 +297,27 @@ int cmd_bench(const Flags &f) {
   if (f.has("--occupancy")) {
     if (!f.has("--kernel") || !f.has("--shape")) return usage("bench --occupancy needs --kernel and --shape");
     if (!check_target(f, true, token)) return kExitFail;
-    kh_plan_info plan;
-    if (kh_plan(f.get("--kernel").c_str(), f.get("--shape").c_str(), token.c_str(), 148, &plan) != 0) {
+    std::vector<char> json(16384), md(16384);
+    if (kh_occupancy_report(f.get("--kernel").c_str(), f.get("--shape").c_str(), token.c_str(), 148, json.data(),
+                            static_cast<int>(json.size()), md.data(), static_cast<int>(md.size())) != 0) {
       std::fprintf(stderr, "kernelh: %s\n", kh_last_error());
       return kExitFail;
     }
-    int out5[5], sm3[3];
-    double pct = 0;
-    const int threads = static_cast<int>(plan.block[0] * plan.block[1] * plan.block[2]);
-    kh_occupancy(token.c_str(), 0, 0, threads, plan.dynamic_smem, plan.tmem_columns, out5, &pct, sm3);
-    std::printf("{\n  \"kernel\": \"%s\",\n  \"entry\": \"%s\",\n  \"threads_per_workgroup\": %d,\n"
-                "  \"grid\": %u,\n  \"dynamic_smem_bytes\": %lld,\n  \"tmem_columns\": %d,\n"
-                "  \"theoretical_pct\": %.4g,\n  \"sm_resident_blocks\": %d,\n  \"sm_occupancy_pct\": %.4g\n}\n",
-                f.get("--kernel").c_str(), plan.entry, threads, plan.grid[0],
-                static_cast<long long>(plan.dynamic_smem), plan.tmem_columns, pct, sm3[0], sm3[1] / 100.0);
+    std::fputs(json.data(), stdout);
+    if (f.has("--out")) {
+      ::mkdir(f.get("--out").c_str(), 0755);
+      for (const auto &[name, text] : {std::pair<const char *, const char *>{"occupancy.json", json.data()},
+                                       {"occupancy.md", md.data()}}) {
+        const std::string path = f.get("--out") + "/" + name;
+        std::ofstream file(path, std::ios::binary);
+        file << text;
+        if (!file.good()) {
+          std::fprintf(stderr, "kernelh: cannot write %s\n", path.c_str());
+          return kExitFail;
+        }
+        std::printf("wrote %s\n", path.c_str());
+      }
+    }
     return kExitOk;
   }
   std::vector<Row> rows;

@@ -96,6 +96,7 @@ struct CodeObject {
   const char *name;
   const unsigned char *image;
   size_t size;
+  const char *ptxas_report; // `ptxas -v` lines of the build that made the image
 };
 const CodeObject *find_code_object(const std::string &name);
 std::vector<std::string> code_object_names();

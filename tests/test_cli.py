@@ -21,10 +21,20 @@ def test_compile_writes_the_sm100a_code_object(tmp_path):
     r = cli("compile", "--kernel", "softmax", "--shape", "rows=4096,cols=1024", "--target",
             "nvptx-sm_100a", "--out", str(tmp_path))
     assert r.returncode == 0, r.stderr
-    assert r.stdout.splitlines() == [f"wrote {tmp_path}/softmax.cubin", "compile ok"]
+    assert r.stdout.splitlines() == [f"wrote {tmp_path}/softmax.cubin", f"wrote {tmp_path}/resources.json",
+                                     "compile ok"]
     blob = (tmp_path / "softmax.cubin").read_bytes()
-    assert blob[:4] == b"\x7fELF" and b"softmax" in blob
+    assert blob[:4] == b"\x7fELF" and b"softmax" in blob  # ELF magic; the entry symbol is in the symbol table
     assert blob == kh.kernel_image("softmax")
+    # resources.json beside it: the reference's seven keys first, filled from the build's ptxas -v
+    import json
+    res = json.loads((tmp_path / "resources.json").read_text())
+    assert list(res)[:7] == ["kernel", "target", "vgpr_count", "sgpr_count", "lds_bytes", "wavefront_size",
+                             "occupancy_estimate"]
+    assert res["kernel"] == "softmax" and res["target"] == "sm_100a" and res["wavefront_size"] == 32
+    assert 16 <= res["vgpr_count"] <= 255 and res["sgpr_count"] == 0
+    assert res["occupancy_estimate"] == min(64, 65536 // (res["vgpr_count"] * 32))
+    assert res["entry"] == "softmax" and res["spill_store_bytes"] == 0
     # --flag=value form
     r = cli("compile", "--kernel=vecadd", "--target=nvptx-sm_100a", f"--out={tmp_path}")
     assert r.returncode == 0 and (tmp_path / "vecadd.cubin").exists()
@@ -50,8 +60,32 @@ def test_occupancy_report_for_the_planned_launch():
     r = cli("bench", "--occupancy", "--kernel", "attention", "--shape",
             "batch=8,heads=16,seq=1024,head_dim=64", "--target", "nvptx-sm_100a")
     assert r.returncode == 0
-    assert '"threads_per_workgroup": 512' in r.stdout and '"tmem_columns": 512' in r.stdout
-    assert '"sm_resident_blocks": 1' in r.stdout
+    import json
+    reports = json.loads(r.stdout)["reports"]  # one per launch: attention_split, attention
+    assert [x["kernel"] for x in reports] == ["attention_split", "attention"]
+    main = reports[1]
+    assert main["threads_per_workgroup"] == 512 and main["sm_resident_blocks"] == 1
+    # the registers ptxas reported are fed in: the register bound is a real number, not "unknown"
+    assert main["vgpr_count"] == kh.kernel_resources("attention")[0]["registers"] > 64
+    assert main["vgpr_limited_waves"] == 65536 // (main["vgpr_count"] * 32)
+
+
+def test_occupancy_report_files(tmp_path):
+    r = cli("bench", "--occupancy", "--kernel", "gemm", "--shape", "m=8192,n=8192,k=8192", "--target",
+            "nvptx-sm_100a", "--out", str(tmp_path))
+    assert r.returncode == 0, r.stderr
+    assert f"wrote {tmp_path}/occupancy.json" in r.stdout and f"wrote {tmp_path}/occupancy.md" in r.stdout
+    import json
+    reports = json.loads((tmp_path / "occupancy.json").read_text())["reports"]
+    gemm = [x for x in reports if x["kernel"] == "gemm"][0]
+    # 320 threads of 168 registers: one cluster CTA per SM, and the registers say so
+    assert gemm["vgpr_count"] >= 128 and gemm["sm_resident_blocks"] == 1 and gemm["sm_limiter"] == "registers"
+    md = (tmp_path / "occupancy.md").read_text()
+    assert md.startswith("# Occupancy report") and "| gemm_prep_b |" in md and "| gemm |" in md
+    # a single-launch kernel gives a single report object, like the reference's occupancy.json
+    r = cli("bench", "--occupancy", "--kernel", "vecadd", "--shape", "n=16777216", "--target", "nvptx-sm_100a")
+    one = json.loads(r.stdout)
+    assert one["kernel"] == "vecadd" and one["threads_per_workgroup"] == 256 and one["vgpr_count"] > 0
 
 
 def test_run_and_bench_skip_with_77_without_a_device():

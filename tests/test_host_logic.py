@@ -293,3 +293,53 @@ def test_device_wait_codes_have_names():
     # the probe validates its arguments on the host
     assert kh.lib.kh_scan_lookback_probe(None, 0x1000, 0x2000, 1 << 20, 1000, None) == 2
     assert b"context" in kh.lib.kh_last_error()
+
+
+PTXAS_SAMPLE = """ptxas info    : 0 bytes gmem
+ptxas info    : Compiling entry function 'alpha' for 'sm_100a'
+ptxas info    : Function properties for alpha
+    16 bytes stack frame, 8 bytes spill stores, 12 bytes spill loads
+ptxas info    : Used 58 registers, used 1 barriers, 520 bytes cmem[0]
+ptxas info    : Compile time = 4.530 ms
+ptxas info    : Compiling entry function 'beta' for 'sm_100a'
+ptxas info    : Function properties for beta
+    0 bytes stack frame, 0 bytes spill stores, 0 bytes spill loads
+ptxas info    : Used 168 registers, used 3 barriers, 2048 bytes smem
+"""
+
+
+def test_ptxas_report_parser():
+    """resources.json is filled from `ptxas -v` text, as in the reference
+    (lib/compiler/resource_reporter.cpp:614-660: "Used N registers", "M bytes smem")."""
+    a = kh.parse_ptxas(PTXAS_SAMPLE, "alpha")
+    assert a == {"registers": 58, "smem_bytes": 0, "stack_bytes": 16, "spill_store_bytes": 8,
+                 "spill_load_bytes": 12, "barriers": 1}
+    b = kh.parse_ptxas(PTXAS_SAMPLE, "beta")
+    assert (b["registers"], b["smem_bytes"], b["barriers"], b["spill_store_bytes"]) == (168, 2048, 3, 0)
+    assert kh.parse_ptxas(PTXAS_SAMPLE) == a  # no name: the first entry
+    with pytest.raises(kh.KernelhError) as e:
+        kh.parse_ptxas("nothing useful here", None)
+    assert "unparseable ptxas output" in e.value.message
+    fixture = "/root/reference/test/fixtures/ptxas_gemm_v.txt"  # the reference's own sample, where its tree is present
+    if os.path.exists(fixture):
+        got = kh.parse_ptxas(open(fixture).read(), "gemm")
+        assert (got["registers"], got["barriers"], got["smem_bytes"]) == (58, 1, 0)
+
+
+def test_every_entry_point_has_resource_figures():
+    entries = {"vecadd": ["vecadd"], "fused_gelu": ["fused_gelu", "fused_gelu_bias"], "scan": ["scan"],
+               "softmax": ["softmax"], "layernorm": ["layernorm"],
+               "gemm": ["gemm", "gemm_allgather", "gemm_split_a", "gemm_prep_b", "gemm_colmax_b", "gemm_split_bt",
+                        "replicate_run"],
+               "attention": ["attention", "attention_allgather", "attention_split"]}
+    for kernel, names in entries.items():
+        for entry in names:
+            fig, text = kh.kernel_resources(kernel, entry)
+            assert 8 <= fig["registers"] <= 255, (kernel, entry, fig)
+            assert f'"entry": "{entry}"' in text and '"target": "sm_100a"' in text
+    assert kh.kernel_resources("gemm")[0]["registers"] >= 128          # the MMA kernel's epilogue holds a tile
+    assert kh.kernel_resources("vecadd")[0]["spill_store_bytes"] == 0
+    with pytest.raises(kh.KernelhError):
+        kh.kernel_resources("gemm", "no_such_entry")
+    js, md = kh.occupancy_report("scan", "n=67108864")
+    assert '"kernel": "scan"' in js and '"threads_per_workgroup": 416' in js and "| scan |" in md
