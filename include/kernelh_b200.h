@@ -234,6 +234,33 @@ int kh_bench_row(kh_context *ctx, const char *kernel, const char *shape, int war
  * registeredKernels() and the unknown-name error of emit()
  * (lib/dsl/registry.cpp:23-42, lib/dsl/program.cpp:27-37). */
 int kh_registered_kernels(char *buf, int cap); /* comma separated, sorted */
+/* registerKernel(name, fn) (include/kernelh/dsl/program.hpp:64-67,
+ * lib/dsl/registry.cpp:39-42): the plug-in point. Adds a kernel template, or
+ * REPLACES the one registered under `name`, built-ins included. Where the
+ * reference registers a function that emits IR, the registered value here is a
+ * finished kernel: an sm_100a code object (copied), the entry symbol in it,
+ * and a callback that validates a shape and lays out the launch. The entry
+ * takes its buffers as rank-1 fp32 memref descriptors (five 8-byte parameters
+ * each: allocated pointer, aligned pointer, offset, size, stride), in the order
+ * of kh_custom_plan.elements. The callback gets the shape as "k=v,k=v" text
+ * (keys sorted) and the SM count; it returns 0, or non-zero with a message in
+ * `error` that surfaces as "<name> template: <message>" (code 2).
+ * kh_unregister_kernel takes such a record away again: a built-in it had
+ * replaced comes back, any other name disappears. */
+typedef struct {
+  uint32_t grid[3], block[3];
+  size_t dynamic_smem;
+  int32_t n_buffers;      /* 1..8 */
+  int64_t elements[8];    /* fp32 elements per buffer */
+  uint8_t is_output[8];
+  double work;            /* flops or bytes for the bench rate */
+  int32_t work_is_flops;
+} kh_custom_plan;
+typedef int (*kh_plan_fn)(const char *shape_text, int sm_count, kh_custom_plan *out, char *error, int error_cap,
+                          void *user);
+int kh_register_kernel(const char *name, const void *image, size_t image_size, const char *entry, kh_plan_fn plan,
+                       void *user);
+int kh_unregister_kernel(const char *name);
 /* The launch plan for a shape on a device-limits token ("sm_100a"): counts of
  * caller buffers, scratch bytes, launches, and the main launch's geometry. */
 typedef struct {

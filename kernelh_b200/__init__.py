@@ -22,6 +22,8 @@ USAGE_ERROR = 2
 DEVICE_TIMEOUT = 1001
 
 KERNELS = ("attention", "fused_gelu", "gemm", "layernorm", "scan", "softmax", "vecadd")
+# the reference also registers the second kernel of its two-launch scan; here it launches nothing
+REGISTERED = tuple(sorted(KERNELS + ("scan_totals",)))
 
 
 class KernelhError(RuntimeError):
@@ -38,6 +40,15 @@ class DeviceInfo(C.Structure):
                 ("warp_size", C.c_int32), ("max_threads_per_block", C.c_int32),
                 ("regs_per_sm", C.c_int32), ("max_blocks_per_sm", C.c_int32),
                 ("cc_major", C.c_int32), ("cc_minor", C.c_int32), ("ordinal", C.c_int32)]
+
+
+class CustomPlan(C.Structure):
+    _fields_ = [("grid", C.c_uint32 * 3), ("block", C.c_uint32 * 3), ("dynamic_smem", C.c_size_t),
+                ("n_buffers", C.c_int32), ("elements", C.c_int64 * 8), ("is_output", C.c_uint8 * 8),
+                ("work", C.c_double), ("work_is_flops", C.c_int32)]
+
+
+PLAN_FN = C.CFUNCTYPE(C.c_int, C.c_char_p, C.c_int, C.POINTER(CustomPlan), C.POINTER(C.c_char), C.c_int, C.c_void_p)
 
 
 class PlanInfo(C.Structure):
@@ -96,6 +107,8 @@ def _load() -> C.CDLL:
     L.kh_bench_row.argtypes = [vp, C.c_char_p, C.c_char_p, C.c_int, C.c_int,
                                C.POINTER(C.c_double), C.POINTER(C.c_double), C.POINTER(C.c_int)]
     L.kh_registered_kernels.argtypes = [C.c_char_p, C.c_int]
+    L.kh_register_kernel.argtypes = [C.c_char_p, C.c_char_p, C.c_size_t, C.c_char_p, PLAN_FN, C.c_void_p]
+    L.kh_unregister_kernel.argtypes = [C.c_char_p]
     L.kh_plan.argtypes = [C.c_char_p, C.c_char_p, C.c_char_p, C.c_int, C.POINTER(PlanInfo)]
     L.kh_kernel_image.argtypes = [C.c_char_p, C.POINTER(vp), C.POINTER(C.c_size_t)]
     L.kh_kernel_resources.argtypes = [C.c_char_p, C.c_char_p, C.c_char_p, C.c_char_p, C.c_int, C.POINTER(C.c_int64)]
@@ -340,6 +353,47 @@ def registered_kernels() -> list[str]:
     buf = C.create_string_buffer(1024)
     _check(lib.kh_registered_kernels(buf, 1024))
     return buf.value.decode().split(",")
+
+
+_registered_callbacks: dict[str, object] = {}
+
+
+def register_kernel(name: str, image: bytes, entry: str, plan_fn) -> None:
+    """The plug-in point (the reference's ``registerKernel``): add a kernel template or
+    replace the one registered under `name`. `plan_fn(shape: dict, sm_count) -> dict` returns
+    ``grid``, ``block``, ``elements`` (fp32 elements per buffer), ``outputs`` (indices) and
+    optionally ``dynamic_smem``, ``work``, ``work_is_flops``; raising ValueError refuses the
+    shape with that message."""
+
+    def trampoline(shape_text, sm_count, out, error, error_cap, _user):
+        try:
+            shape = dict((k, int(v)) for k, v in (item.split("=") for item in shape_text.decode().split(",") if item))
+            d = plan_fn(shape, sm_count)
+            p = out.contents
+            for i in range(3):
+                p.grid[i] = (list(d["grid"]) + [1, 1])[i]
+                p.block[i] = (list(d["block"]) + [1, 1])[i]
+            p.dynamic_smem = int(d.get("dynamic_smem", 0))
+            p.n_buffers = len(d["elements"])
+            for i, n in enumerate(d["elements"]):
+                p.elements[i] = int(n)
+                p.is_output[i] = 1 if i in d.get("outputs", ()) else 0
+            p.work = float(d.get("work", 0.0))
+            p.work_is_flops = int(bool(d.get("work_is_flops", False)))
+            return 0
+        except Exception as exc:  # the message goes back through the C interface
+            msg = str(exc).encode()[:max(error_cap - 1, 0)]
+            C.memmove(error, msg + b"\0", len(msg) + 1)
+            return 1
+
+    cb = PLAN_FN(trampoline)
+    _check(lib.kh_register_kernel(name.encode(), image, len(image), entry.encode(), cb, None))
+    _registered_callbacks[name] = cb  # the library keeps calling it: keep it alive
+
+
+def unregister_kernel(name: str) -> None:
+    _check(lib.kh_unregister_kernel(name.encode()))
+    _registered_callbacks.pop(name, None)
 
 
 def plan(kernel: str, shape: str, target: str = "sm_100a", sm_count: int = 148) -> PlanInfo:

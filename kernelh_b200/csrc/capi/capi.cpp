@@ -11,7 +11,9 @@
 #include "../runtime/occupancy.hpp"
 #include "../runtime/resources.hpp"
 
+#include <atomic>
 #include <cstring>
+#include <stdexcept>
 #include <string>
 #include <vector>
 
@@ -396,6 +398,70 @@ int kh_bench_row(kh_context *ctx, const char *kernel, const char *shape, int war
   });
 }
 
+int kh_register_kernel(const char *name, const void *image, size_t image_size, const char *entry, kh_plan_fn plan,
+                       void *user) {
+  if (name == nullptr || *name == '\0' || image == nullptr || image_size == 0 || entry == nullptr || plan == nullptr)
+    return set_error(2, "kh_register_kernel: name, code object, entry symbol and plan callback are all required");
+  return guarded([&] {
+    static std::atomic<uint64_t> serial{0};
+    auto bytes = std::make_shared<const std::vector<unsigned char>>(static_cast<const unsigned char *>(image),
+                                                                    static_cast<const unsigned char *>(image) + image_size);
+    kh::KernelRecord rec;
+    rec.name = name;
+    // a key of its own for the executors' module caches: a later registration under the same name is a new module
+    rec.code_object = std::string("user:") + name + "#" + std::to_string(serial.fetch_add(1));
+    rec.image = bytes;
+    const std::string kernel = name, symbol = entry;
+    rec.plan = [kernel, symbol, plan, user](const kh::ShapeMap &shape, const kh::DeviceLimits &limits) {
+      kh_custom_plan out;
+      std::memset(&out, 0, sizeof out);
+      char why[512] = {0};
+      const long sms = kh::query_cu_count(limits);
+      const int rc = plan(kh::shape_to_text(shape).c_str(), static_cast<int>(sms > 0 ? sms : limits.cu_count), &out, why,
+                          static_cast<int>(sizeof why), user);
+      if (rc != 0)
+        throw std::runtime_error(kernel + " template: " + (why[0] ? why : "the plan callback refused the shape"));
+      if (out.n_buffers < 1 || out.n_buffers > 8)
+        throw std::runtime_error(kernel + " template: the plan callback must describe 1 to 8 buffers");
+      kh::KernelPlan p;
+      p.kernel = kernel;
+      p.shape = shape;
+      for (int i = 0; i < out.n_buffers; ++i)
+        p.tensors.push_back({"arg" + std::to_string(i), {out.elements[i]}, out.is_output[i] != 0});
+      kh::LaunchStep s;
+      s.entry = symbol;
+      s.grid = {out.grid[0], std::max(out.grid[1], 1u), std::max(out.grid[2], 1u)};
+      s.block = {out.block[0], std::max(out.block[1], 1u), std::max(out.block[2], 1u)};
+      s.dynamic_smem = out.dynamic_smem;
+      s.param_count = 5 * out.n_buffers;
+      p.steps = {s};
+      p.work = out.work;
+      p.work_is_flops = out.work_is_flops != 0;
+      return p;
+    };
+    const std::string key = rec.code_object;
+    rec.run = [bytes, key](kh::Executor &ex, const kh::KernelPlan &p, const std::vector<void *> &b,
+                           kh::StreamHandle stream) -> kh::Result<void> {
+      auto fn = ex.function_from_image(key, bytes->data(), bytes->size(), p.steps[0].entry);
+      if (!fn) return std::unexpected(fn.error());
+      kh::LaunchArgs args;
+      for (size_t i = 0; i < p.tensors.size(); ++i) args.add_memref(b[i], p.tensors[i].shape);
+      return ex.launch(*fn, p.steps[0], args, stream);
+    };
+    kh::register_kernel(std::move(rec));
+    return 0;
+  });
+}
+
+int kh_unregister_kernel(const char *name) {
+  return guarded([&] {
+    if (name == nullptr || !kh::unregister_kernel(name))
+      return set_error(2, std::string("kh_unregister_kernel: '") + (name ? name : "") +
+                              "' was not registered through kh_register_kernel");
+    return 0;
+  });
+}
+
 int kh_registered_kernels(char *buf, int cap) {
   return guarded([&] {
     std::string s;
@@ -420,6 +486,7 @@ int kh_plan(const char *kernel, const char *shape, const char *target_token, int
     out->n_buffers = static_cast<int32_t>(plan.tensors.size());
     out->n_launches = static_cast<int32_t>(plan.steps.size());
     out->workspace_bytes = static_cast<int64_t>(plan.workspace_bytes);
+    if (plan.steps.empty()) return 0; // a template that launches nothing (scan_totals)
     const kh::LaunchStep &s = plan.steps.back();
     copy_out(s.entry, out->entry, sizeof out->entry);
     out->grid[0] = s.grid.x; out->grid[1] = s.grid.y; out->grid[2] = s.grid.z;
@@ -437,6 +504,11 @@ int kh_kernel_image(const char *kernel, const void **image, size_t *size) {
   return guarded([&] {
     const std::string name(kernel ? kernel : "");
     const kh::KernelRecord &rec = kh::find_kernel(name);
+    if (rec.image) { // registered from outside: its own code object
+      if (image) *image = rec.image->data();
+      if (size) *size = rec.image->size();
+      return 0;
+    }
     const kh::CodeObject *co = kh::find_code_object(rec.code_object);
     if (co == nullptr || co->size == 0)
       return set_error(1, "no embedded sm_100a code object for kernel '" + rec.name + "'");

@@ -822,6 +822,30 @@ void register_builtin_kernels() {
                    [](const ShapeMap &s, const DeviceLimits &l) { return plan_rows("layernorm", s, l, true); },
                    run_rows});
   register_kernel({"scan", "scan", plan_scan, run_scan});
+  // The reference's registry also holds `scan_totals`, the second kernel of its two-launch
+  // scan (lib/dsl/kernels/scan.cpp:350-453: seven buffers, 'n' required and positive). The
+  // single-pass `scan` here leaves nothing for it to do: the name resolves, the shape rules
+  // and the buffer list are the reference's, and running it launches nothing.
+  register_kernel({"scan_totals", "scan",
+                   [](const ShapeMap &shape, const DeviceLimits &) {
+                     auto it = shape.find("n");
+                     if (it == shape.end())
+                       throw std::runtime_error("scan_totals template: shape attribute 'n' is required (pass "
+                                                "--shape n=<size>)");
+                     if (it->second <= 0)
+                       throw std::runtime_error("scan_totals template: shape attribute 'n' must be positive");
+                     const int64_t n = it->second, t = (n + 255) / 256;
+                     KernelPlan p;
+                     p.kernel = "scan_totals";
+                     p.shape = shape;
+                     p.tensors = {{"totals_hi", {t}, false}, {"totals_lo", {t}, false}, {"off_hi", {t}, true},
+                                  {"off_lo", {t}, true},     {"off_lo2", {t}, true},    {"y", {n}, true},
+                                  {"y_lo", {n}, true}};
+                     return p; // no launch steps
+                   },
+                   [](Executor &, const KernelPlan &, const std::vector<void *> &, StreamHandle) -> Result<void> {
+                     return {};
+                   }});
   register_kernel({"gemm", "gemm", plan_gemm, run_gemm, run_gemm_host});
   register_attention_kernel();
 }

@@ -43,7 +43,25 @@ Result<KernelFunction> Executor::function(const std::string &code_object, const 
     if (co == nullptr || co->size == 0)
       return fail(1, "no embedded sm_100a code object named '" + code_object +
                          "' (the library was built without its CUDA kernels)");
-    auto loaded = GpuModule::load(backend_, co->image, co->size);
+    return function_from_image(code_object, co->image, co->size, entry);
+  }
+  auto fn = mod->second.get_function(entry.c_str());
+  if (!fn) return std::unexpected(fn.error());
+  FunctionInfo fi;
+  fi.fn = *fn;
+  if (auto attrs = backend_->function_attributes(fn->handle))
+    fi.static_smem = static_cast<size_t>(attrs->static_smem_bytes);
+  functions_[key] = fi;
+  return *fn;
+}
+
+Result<KernelFunction> Executor::function_from_image(const std::string &code_object, const void *image,
+                                                     size_t size, const std::string &entry) {
+  const std::string key = code_object + ":" + entry;
+  if (auto it = functions_.find(key); it != functions_.end()) return it->second.fn;
+  auto mod = modules_.find(code_object);
+  if (mod == modules_.end()) {
+    auto loaded = GpuModule::load(backend_, image, size);
     if (!loaded) return fail(loaded.error().code, "loading code object '" + code_object + "': " +
                                                       loaded.error().message);
     mod = modules_.emplace(code_object, std::move(*loaded)).first;

@@ -38,6 +38,10 @@ public:
 
   // ---- used by the kernel records ------------------------------------------------
   Result<KernelFunction> function(const std::string &code_object, const std::string &entry);
+  // The same for a code object handed in by the caller (a kernel registered from outside);
+  // `code_object` is the cache key of the loaded module.
+  Result<KernelFunction> function_from_image(const std::string &code_object, const void *image, size_t size,
+                                             const std::string &entry);
   Result<void *> workspace(size_t bytes);
   Result<void> launch(KernelFunction fn, const LaunchStep &step, LaunchArgs &args, StreamHandle s);
   uint32_t *status_word() const { return static_cast<uint32_t *>(status_.data()); }

@@ -18,15 +18,40 @@ std::map<std::string, KernelRecord> &table() {
   static std::map<std::string, KernelRecord> t;
   return t;
 }
+// built-ins that a record registered from outside has displaced, kept for unregister_kernel
+std::map<std::string, KernelRecord> &displaced() {
+  static std::map<std::string, KernelRecord> t;
+  return t;
+}
+bool g_builtins_done = false;
 void ensure_builtins() {
   static std::once_flag once;
-  std::call_once(once, [] { register_builtin_kernels(); });
+  std::call_once(once, [] {
+    register_builtin_kernels();
+    g_builtins_done = true;
+  });
 }
 } // namespace
 
 void register_kernel(KernelRecord record) {
+  if (record.image) ensure_builtins(); // a record from outside lands on top of the built-ins, not under them
   std::lock_guard<std::mutex> lock(g_mu);
+  auto it = table().find(record.name);
+  if (record.image && it != table().end() && !it->second.image) displaced()[record.name] = it->second;
   table()[record.name] = std::move(record);
+}
+
+bool unregister_kernel(const std::string &name) {
+  ensure_builtins();
+  std::lock_guard<std::mutex> lock(g_mu);
+  auto it = table().find(name);
+  if (it == table().end() || !it->second.image) return false;
+  table().erase(it);
+  if (auto old = displaced().find(name); old != displaced().end()) {
+    table()[name] = std::move(old->second);
+    displaced().erase(old);
+  }
+  return true;
 }
 
 std::vector<std::string> registered_kernels() {

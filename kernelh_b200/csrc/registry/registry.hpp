@@ -15,6 +15,7 @@
 
 #include <functional>
 #include <initializer_list>
+#include <memory>
 #include <utility>
 #include <string>
 #include <vector>
@@ -76,6 +77,9 @@ struct KernelRecord {
   std::function<Result<void>(Executor &, const KernelPlan &, const std::vector<void *> &host,
                              const std::vector<void *> &dev, const HostStreams &)>
       run_host = nullptr;
+  // A record registered from outside carries its own code object instead of naming an
+  // embedded one (code_object is then a unique key for the executor's module cache).
+  std::shared_ptr<const std::vector<unsigned char>> image;
 };
 
 // Name of the first non-null address in `buffers` that is not 16-byte aligned,
@@ -87,7 +91,11 @@ inline const char *first_misaligned16(std::initializer_list<std::pair<const char
   return nullptr;
 }
 
+// Adds the record, or replaces the one registered under its name (built-ins included).
 void register_kernel(KernelRecord record);
+// Takes a record registered over the built-ins away again: a built-in of that name comes
+// back, any other name disappears. False when the name was not registered from outside.
+bool unregister_kernel(const std::string &name);
 std::vector<std::string> registered_kernels();
 const KernelRecord &find_kernel(const std::string &name);
 

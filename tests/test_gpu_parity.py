@@ -644,3 +644,34 @@ def test_bench_row_reports_reference_metrics(ctx):
     assert rate == pytest.approx(kh.rate(False, kh.metric("vecadd_bytes", 1 << 24), ms))
     ms, rate, is_gflops = ctx.bench_row("gemm", "m=512,n=512,k=512", 2, 5)
     assert is_gflops and rate == pytest.approx(kh.rate(True, 268435456.0, ms))
+
+
+def test_registered_kernel_runs_through_the_operator_surface(ctx, oracle):
+    """The plug-in point on the device: a code object registered under a new name is planned
+    by its callback and launched by kh_launch like a built-in (here the vecadd code object
+    under another name and with another geometry: its kernel strides over any grid), and a
+    record registered over a built-in takes its place until it is unregistered."""
+    image = kh.kernel_image("vecadd")
+    n = 123457
+    a, b = oracle.vecadd_pattern(n)
+    kh.register_kernel("user_add", image, "vecadd",
+                       lambda shape, sms: {"grid": [37], "block": [128], "elements": [shape["n"]] * 3, "outputs": [2],
+                                           "work": 12.0 * shape["n"]})
+    try:
+        c = run(ctx, "user_add", f"n={n}", [a, b], (n,))
+        assert oracle.bit_mismatches(c, oracle.vecadd_ref(a, b)) == 0
+        ms, rate, is_gflops = ctx.bench_row("user_add", f"n={n}", 1, 3)
+        assert ms > 0 and not is_gflops and rate == pytest.approx(kh.rate(False, 12.0 * n, ms))
+        # over a built-in: fused_gelu now adds, until the record is taken away again
+        x = oracle.lcg(n, 0x3A5F91)
+        want = run(ctx, "fused_gelu", f"n={n}", [x, None], (n,))
+        kh.register_kernel("fused_gelu", image, "vecadd",
+                           lambda shape, sms: {"grid": [64], "block": [256], "elements": [shape["n"]] * 3, "outputs": [2]})
+        assert oracle.bit_mismatches(run(ctx, "fused_gelu", f"n={n}", [a, b], (n,)), oracle.vecadd_ref(a, b)) == 0
+        kh.unregister_kernel("fused_gelu")
+        assert np.array_equal(run(ctx, "fused_gelu", f"n={n}", [x, None], (n,)), want)
+    finally:
+        kh.unregister_kernel("user_add")
+    with pytest.raises(kh.KernelhError) as e:
+        ctx.launch("user_add", f"n={n}", [dev(a), dev(b), dev(a)])
+    assert "unknown kernel template 'user_add'" in e.value.message

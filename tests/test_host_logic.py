@@ -138,7 +138,7 @@ def test_shape_text_matches_reference(golden):
 def test_registry_lists_sorted_names_and_rejects_unknown():
     names = kh.registered_kernels()
     assert names == sorted(names)
-    assert set(names) == set(kh.KERNELS)
+    assert names == list(kh.REGISTERED)  # the seven templates and the reference's scan_totals
     with pytest.raises(kh.KernelhError) as e:
         kh.plan("nope", "n=4")
     assert e.value.message.startswith("unknown kernel template 'nope'; registered kernels: ")
@@ -343,3 +343,73 @@ def test_every_entry_point_has_resource_figures():
         kh.kernel_resources("gemm", "no_such_entry")
     js, md = kh.occupancy_report("scan", "n=67108864")
     assert '"kernel": "scan"' in js and '"threads_per_workgroup": 416' in js and "| scan |" in md
+
+
+def test_registry_is_a_plug_in_point():
+    """registerKernel(name, fn) adds a template or replaces an existing one
+    (include/kernelh/dsl/program.hpp:64-67, lib/dsl/registry.cpp:39-42, pinned by
+    test/unit/dsl_test.cpp:153-231): a custom template is added, listed in sorted order beside
+    the built-ins, planned through the ordinary operator surface, may replace a built-in, and
+    an unknown name lists it among the registered kernels. Here the registered value is a
+    finished code object + entry + plan callback instead of an IR-emitting function."""
+    image = kh.kernel_image("vecadd")  # any sm_100a code object will do for the host-side checks
+
+    def plan_probe(shape, sm_count):
+        if "n" not in shape:
+            raise ValueError("shape attribute 'n' is required")
+        if shape["n"] <= 0:
+            raise ValueError("shape attribute 'n' must be positive")
+        n = shape["n"]
+        return {"grid": [min((n + 1023) // 1024, sm_count * 2)], "block": [256], "elements": [n, n, n], "outputs": [2],
+                "work": 12.0 * n}
+
+    kh.register_kernel("dsl_probe", image, "vecadd", plan_probe)
+    try:
+        names = kh.registered_kernels()
+        assert names == sorted(names) and "dsl_probe" in names and "vecadd" in names
+        p = kh.plan("dsl_probe", "n=4096", sm_count=148)
+        assert (p.n_buffers, p.n_launches, p.entry, p.grid[0], p.block[0]) == (3, 1, b"vecadd", 4, 256)
+        assert p.param_count == 15 and p.work == 12.0 * 4096 and not p.work_is_flops
+        assert kh.kernel_image("dsl_probe") == image
+        with pytest.raises(kh.KernelhError) as e:  # the callback's refusal comes back as a template error
+            kh.plan("dsl_probe", "m=4")
+        assert e.value.code == kh.USAGE_ERROR
+        assert e.value.message == "dsl_probe template: shape attribute 'n' is required"
+        with pytest.raises(kh.KernelhError) as e:
+            kh.plan("nope", "n=4")
+        assert "unknown kernel template 'nope'" in e.value.message and "dsl_probe" in e.value.message
+
+        # replacing a built-in: the name now plans through the new record ...
+        builtin = kh.plan("softmax", "rows=4096,cols=1024")
+        kh.register_kernel("softmax", image, "vecadd",
+                           lambda shape, sms: {"grid": [7], "block": [64], "elements": [shape["rows"] * shape["cols"]] * 3,
+                                               "outputs": [2]})
+        replaced = kh.plan("softmax", "rows=4096,cols=1024")
+        assert (replaced.grid[0], replaced.block[0], replaced.n_buffers) == (7, 64, 3)
+        assert kh.registered_kernels().count("softmax") == 1
+        # ... and registering the same name again replaces the replacement
+        kh.register_kernel("softmax", image, "vecadd",
+                           lambda shape, sms: {"grid": [9], "block": [32], "elements": [4], "outputs": [0]})
+        assert kh.plan("softmax", "rows=4,cols=1").grid[0] == 9
+        kh.unregister_kernel("softmax")  # the built-in is back
+        again = kh.plan("softmax", "rows=4096,cols=1024")
+        assert (again.grid[0], again.block[0], again.n_buffers, again.entry) == (builtin.grid[0], builtin.block[0], 2, b"softmax")
+    finally:
+        kh.unregister_kernel("dsl_probe")
+    assert "dsl_probe" not in kh.registered_kernels()
+    with pytest.raises(kh.KernelhError):
+        kh.unregister_kernel("dsl_probe")      # not registered any more
+    with pytest.raises(kh.KernelhError):
+        kh.unregister_kernel("vecadd")         # built-ins cannot be taken away
+    assert kh.lib.kh_register_kernel(b"x", None, 0, b"e", kh.PLAN_FN(lambda *a: 0), None) == 2
+
+
+def test_scan_totals_resolves_and_keeps_the_reference_shape_rules():
+    p = kh.plan("scan_totals", "n=1000000")
+    assert p.n_buffers == 7 and p.n_launches == 0  # the single-pass scan leaves nothing to launch
+    with pytest.raises(kh.KernelhError) as e:
+        kh.plan("scan_totals", "m=4")
+    assert "scan_totals template: shape attribute 'n' is required" in e.value.message
+    with pytest.raises(kh.KernelhError) as e:
+        kh.plan("scan_totals", "n=0")
+    assert "must be positive" in e.value.message
