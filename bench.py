@@ -44,6 +44,8 @@ def parse_args():
                          "(symmetric memory; one multimem.st per tile piece through the NVSwitch multicast "
                          "address when there is one, else plain peer stores) and a barrier follows; "
                          "'p2p-st' = the same, forcing plain peer stores; 'nccl' = plain gemm + NCCL all-gather")
+    ap.add_argument("--csv", default="", help="N = 1: also write the rows of this run as results CSV with the "
+                                              "appended columns (gpus, roofline_frac, max_rel_err, cpu_ms, cpu_cores)")
     ap.add_argument("--no-extras", action="store_true",
                     help="skip the memory-bound rows, the e2e leg and the CPU baseline")
     return ap.parse_args()
@@ -275,31 +277,86 @@ def time_rotating(torch, launch, sets, iters, use_graph=True):
     return e0.elapsed_time(e1) / iters, "launch loop"
 
 
+NOMINAL_HBM_GBS = 8000.0  # the "about 8 TB/s" of the B200 data sheet, beside the measured copy rate
+
+
+def cpu_row(fn, bytes_or_flops: float, is_flops: bool, kind: str, cores: int, sample: str) -> dict:
+    """Times one call of a CPU reference routine (after one untimed call)."""
+    fn()
+    t0 = time.perf_counter()
+    fn()
+    ms = (time.perf_counter() - t0) * 1e3
+    rate = bytes_or_flops / ms / 1e6
+    return {"ms": ms, ("gflops" if is_flops else "gbs"): rate, "cores": cores, "kind": kind, "sample": sample}
+
+
 def memory_bound_rows(torch, ctx, stream, hbm_peak: float) -> dict:
     """GB/s of the five HBM-bound kernels at the benchmark configurations' sizes
-    (rotating through buffer sets larger than L2) and at a large size."""
-    out = {}
+    (rotating through buffer sets larger than L2) and at a large size. The benchmark-size
+    rows also carry the largest floored-relative error against the CPU oracle on seeded
+    inputs and the time of the reference's CPU routine for the same shape."""
+    import numpy as np
 
-    def row(name, kernel, shape, make, bytes_per_launch, nsets, iters=200):
+    from oracle import oracle_py as O
+
+    out = {}
+    R = O.ref() if O.ref_available() else None
+    kind = "reference" if R is not None else "port"
+
+    def row(name, kernel, shape, make, bytes_per_launch, nsets, iters=200, check=None, cpu=None):
         sets = [make() for _ in range(nsets)]
         ms, method = time_rotating(torch, lambda s, st: ctx.launch(kernel, shape, s, st), sets, iters)
         gbs = bytes_per_launch / ms / 1e6
         out[name] = {"shape": shape, "ms": ms, "gbs": gbs, "frac_of_measured_hbm": gbs / hbm_peak,
-                     "buffer_sets": nsets, "timing": method}
+                     "frac_of_nominal_8tbs": gbs / NOMINAL_HBM_GBS, "buffer_sets": nsets, "timing": method}
+        if check is not None:
+            inputs, ref = check()
+            dev_in = [torch.from_numpy(x).cuda() if x is not None else None for x in inputs]
+            res = torch.full(ref.shape, float("nan"), device="cuda")
+            ctx.launch(kernel, shape, dev_in + [res], stream)
+            ctx.synchronize(stream)
+            c = O.compare(res.cpu().numpy(), ref)
+            out[name]["max_rel_err"] = c.max_rel
+            if ref.dtype == np.float32:  # vecadd and scan: the oracle's result is the fp32 answer itself
+                out[name]["bit_mismatches"] = int(O.bit_mismatches(res.cpu().numpy(), ref))
+        if cpu is not None:
+            out[name]["cpu"] = cpu()
 
     f = lambda *shape: torch.randn(*shape, device="cuda")
     n = 1 << 24
-    row("vecadd", "vecadd", f"n={n}", lambda: [f(n), f(n), f(n)], 3 * n * 4, 3)
+    va, vb = O.uniform(n, SEED, -1, 1), O.uniform(n, SEED + 1, -1, 1)
+    row("vecadd", "vecadd", f"n={n}", lambda: [f(n), f(n), f(n)], 3 * n * 4, 3,
+        check=lambda: ([va, vb], O.vecadd_ref(va, vb)),
+        cpu=lambda: cpu_row(lambda: O.vecadd_ref(va, vb), 3 * n * 4, False, "port", O.num_threads(), f"all {n} elements"))
     n = 1 << 22
-    row("fused_gelu_bias", "fused_gelu", f"n={n},bias=1", lambda: [f(n), f(n), f(n)], 3 * n * 4, 8)
-    row("fused_gelu", "fused_gelu", f"n={n}", lambda: [f(n), None, f(n)], 2 * n * 4, 8)
+    gx, gb = O.normal(n, SEED, 0, 1), O.normal(n, SEED + 1, 0, 1)
+    row("fused_gelu_bias", "fused_gelu", f"n={n},bias=1", lambda: [f(n), f(n), f(n)], 3 * n * 4, 8,
+        check=lambda: ([gx, gb], O.bias_gelu_ref(gx, gb)))
+    gout = np.empty(n, np.float64)
+    row("fused_gelu", "fused_gelu", f"n={n}", lambda: [f(n), None, f(n)], 2 * n * 4, 8,
+        check=lambda: ([gx, None], O.fused_gelu_ref(gx)),
+        cpu=lambda: cpu_row((lambda: R.khref_gelu_ref(gx, gout, n, 0)) if R else (lambda: O.fused_gelu_ref(gx)),
+                            2 * n * 4, False, kind, 1 if R else O.num_threads(), f"all {n} elements, fp64"))
     r, c = 4096, 1024
-    row("softmax", "softmax", f"rows={r},cols={c}", lambda: [f(r, c), f(r, c)], 2 * r * c * 4, 8)
+    sx = O.normal((r, c), SEED, 0, 2.0)
+    sout = np.empty((r, c), np.float64)
+    row("softmax", "softmax", f"rows={r},cols={c}", lambda: [f(r, c), f(r, c)], 2 * r * c * 4, 8,
+        check=lambda: ([sx], O.softmax_ref(sx)),
+        cpu=lambda: cpu_row((lambda: R.khref_softmax_ref(sx, sout, r, c)) if R else (lambda: O.softmax_ref(sx)),
+                            2 * r * c * 4, False, kind, 1 if R else O.num_threads(), f"all {r} x {c}, fp64"))
     g, b = f(c), f(c)
+    lg, lb = O.uniform(c, SEED + 1, 0.5, 1.5), O.normal(c, SEED + 2, 0, 0.1)
+    lx = O.normal((r, c), SEED, 0, 1)
     row("layernorm", "layernorm", f"rows={r},cols={c}", lambda: [f(r, c), g, b, f(r, c)],
-        2 * r * c * 4 + 2 * c * 4, 8)
+        2 * r * c * 4 + 2 * c * 4, 8, check=lambda: ([lx, lg, lb], O.layernorm_ref(lx, lg, lb)),
+        cpu=lambda: cpu_row((lambda: R.khref_layernorm_ref(lx, lg, lb, sout, r, c, 1e-5)) if R else
+                            (lambda: O.layernorm_ref(lx, lg, lb)), 2 * r * c * 4, False, kind,
+                            1 if R else O.num_threads(), f"all {r} x {c}, fp64"))
     n = 1000000
-    row("scan", "scan", f"n={n}", lambda: [torch.rand(n, device="cuda"), f(n)], 2 * n * 4, 24)
+    cx = O.uniform(n, SEED, 0, 1)
+    row("scan", "scan", f"n={n}", lambda: [torch.rand(n, device="cuda"), f(n)], 2 * n * 4, 24,
+        check=lambda: ([cx], O.scan_ref(cx)),
+        cpu=lambda: cpu_row(lambda: O.scan_ref(cx), 2 * n * 4, False, "port", 1, f"all {n} elements, fp64 running sum"))
     # large sizes: one buffer set is already far larger than L2
     n = 1 << 28
     row("vecadd_large", "vecadd", f"n={n}", lambda: [f(n), f(n), f(n)], 3 * n * 4, 1, 20)
@@ -318,16 +375,38 @@ def memory_bound_rows(torch, ctx, stream, hbm_peak: float) -> dict:
     return out
 
 
-def attention_rows(torch, ctx) -> dict:
+def attention_rows(torch, ctx, peaks: dict) -> dict:
     """TFLOP/s (4 b h s^2 d useful flops) of the fused attention at the reference's
-    benchmark shape and at a batched one; split pass included."""
+    benchmark shape and at a batched one; split pass included. Every row carries its
+    roofline record against ONE denominator pair, the same as the gemm's: the measured
+    16-bit tensor rate (burst and sustained) divided by the three fp16 products per
+    fp32-class multiply-add. The reference shape also carries the time of the reference's
+    fp64 CPU routine."""
+    import numpy as np
+
+    from oracle import oracle_py as O
+
     out = {}
     for name, (bsz, heads, seq, dim) in (("reference_shape", (1, 1, 1024, 64)), ("batched", (8, 16, 1024, 64))):
         shape = f"batch={bsz},heads={heads},seq={seq},head_dim={dim}"
         sets = [[torch.randn(bsz, heads, seq, dim, device="cuda") for _ in range(4)] for _ in range(4)]
         ms, method = time_rotating(torch, lambda s, st: ctx.launch("attention", shape, s, st), sets, 50)
-        out[name] = {"shape": shape, "ms": ms, "tflops": 4.0 * bsz * heads * seq * seq * dim / ms / 1e9,
-                     "buffer_sets": 4, "timing": method}
+        tflops = 4.0 * bsz * heads * seq * seq * dim / ms / 1e9
+        ctx.profile(True)
+        for i in range(8):
+            ctx.launch("attention", shape, sets[i % 4], torch.cuda.current_stream().cuda_stream)
+        prof = ctx.profile_report()
+        ctx.profile(False)
+        out[name] = {"shape": shape, "ms": ms, "tflops": tflops, "buffer_sets": 4, "timing": method,
+                     "kernels_ms": {k_: v[1] / v[0] for k_, v in prof.items()},
+                     "roofline": {"bound": "tensor", "achieved": tflops, "unit": "TFLOP/s",
+                                  "peak_burst": peaks["bf16_tflops"] / 3.0, "frac_of_burst": tflops / (peaks["bf16_tflops"] / 3.0),
+                                  "peak_sustained": peaks["bf16_tflops_sustained"] / 3.0,
+                                  "frac_of_sustained": tflops / (peaks["bf16_tflops_sustained"] / 3.0),
+                                  "peak_note": f"16-bit tensor rate of {peaks['source']} / 3; split pass included in the time"}}
+    q, k, v = (O.normal((1, 1, 1024, 64), SEED + i, 0, 1) for i in range(3))
+    out["reference_shape"]["cpu"] = cpu_row(lambda: O.attention_ref(q, k, v), 4.0 * 1024 * 1024 * 64, True, "port",
+                                            O.num_threads(), "batch 1, 1 head, seq 1024, fp64")
     return out
 
 
@@ -463,7 +542,8 @@ def gpu_arm(args) -> None:
         if found:
             traffic = int(found.group(1)) / world
     roofline = {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
-                "frac": achieved / peak, "traffic": traffic, "kernel": ("gemm_allgather" if gather == "p2p" else "gemm") + " (tcgen05 3xFP16)",
+                "frac": achieved / peak, "peak_burst": peaks["bf16_tflops"] / 3.0,
+                "frac_of_burst": achieved / (peaks["bf16_tflops"] / 3.0), "traffic": traffic, "kernel": ("gemm_allgather" if gather == "p2p" else "gemm") + " (tcgen05 3xFP16)",
                 "kernel_ms": kernel_ms, "split_ms": sum(v[1] for k_, v in prof.items() if k_ not in ("gemm", "gemm_allgather")) / gemm_launches,
                 "split_kernels": {k_: v[1] / v[0] for k_, v in prof.items() if k_ not in ("gemm", "gemm_allgather")},
                 "peak_note": f"bf16_tflops_sustained of {peaks['source']} / 3 (three fp16 products per fp32-class multiply-add)"}
@@ -711,8 +791,28 @@ def gpu_arm(args) -> None:
         del a, b, c
         torch.cuda.empty_cache()
         line["memory_bound"] = memory_bound_rows(torch, ctx, stream, peaks["hbm_gbs"])
-        line["attention"] = attention_rows(torch, ctx)
-        line["memory_bound_peak"] = {"hbm_gbs": peaks["hbm_gbs"], "source": peaks["source"]}
+        line["attention"] = attention_rows(torch, ctx, peaks)
+        line["memory_bound_peak"] = {"hbm_gbs": peaks["hbm_gbs"], "source": peaks["source"],
+                                     "nominal_hbm_gbs": NOMINAL_HBM_GBS}
+        if args.csv:
+            # the rows of this run in the harness's CSV, with the columns appended after the reference's seven
+            stamp = time.strftime("%Y-%m-%dT%H:%M:%SZ", time.gmtime())
+            device = torch.cuda.get_device_name(0)
+            with open(args.csv, "w") as f:
+                f.write(kh.csv_header_ext() + "\n")
+                f.write(kh.csv_line_ext("gemm", f"m={size},n={size},k={size}", "kernelh", ms_step, value * 1e3, stamp, device,
+                                        world, roofline["frac"], parity["gemm"]["max_rel_floored_by_rank"][0]) + "\n")
+                for name, r_ in line["memory_bound"].items():
+                    kernel = name.split("_large")[0].split("_16384")[0].replace("_bias", "")
+                    cpu = r_.get("cpu", {})
+                    f.write(kh.csv_line_ext(kernel, r_["shape"], "kernelh", r_["ms"], r_["gbs"], stamp, device, 1,
+                                            r_["frac_of_measured_hbm"], r_.get("max_rel_err", -1.0),
+                                            cpu.get("ms", -1.0), cpu.get("cores", 0)) + "\n")
+                for name, r_ in line["attention"].items():
+                    cpu = r_.get("cpu", {})
+                    f.write(kh.csv_line_ext("attention", r_["shape"], "kernelh", r_["ms"], r_["tflops"] * 1e3, stamp, device,
+                                            1, r_["roofline"]["frac_of_sustained"], -1.0, cpu.get("ms", -1.0),
+                                            cpu.get("cores", 0)) + "\n")
         tflops, threads, kind, sample, _ = cpu_gemm_sample(size, 2, 1)
         line["cpu_baseline"] = {"value": tflops, "unit": "TFLOP/s", "cores": threads, "kind": kind,
                                 "sample": sample}

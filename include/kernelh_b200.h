@@ -332,6 +332,13 @@ double kh_rate(int gflops, double work, double ms);
 int kh_csv_header(char *buf, int cap);
 int kh_csv_line(const char *kernel, const char *shape, const char *backend, double ms, double rate,
                 const char *timestamp, const char *device, char *buf, int cap);
+/* The same line with the columns this build appends AFTER the reference's seven (so existing
+ * consumers keep parsing those): gpus, roofline_frac, max_rel_err, cpu_ms, cpu_cores. A
+ * negative max_rel_err / cpu_ms means "not checked / not timed" and prints an empty field. */
+int kh_csv_header_ext(char *buf, int cap);
+int kh_csv_line_ext(const char *kernel, const char *shape, const char *backend, double ms, double rate,
+                    const char *timestamp, const char *device, int gpus, double roofline_frac, double max_rel_err,
+                    double cpu_ms, int cpu_cores, char *buf, int cap);
 /* parse_shape_text + shape_to_text (bench/harness/shape_text.cpp:10-44). */
 int kh_shape_roundtrip(const char *text, char *buf, int cap);
 

@@ -130,6 +130,9 @@ def _load() -> C.CDLL:
     L.kh_csv_header.argtypes = [C.c_char_p, C.c_int]
     L.kh_csv_line.argtypes = [C.c_char_p, C.c_char_p, C.c_char_p, C.c_double, C.c_double,
                               C.c_char_p, C.c_char_p, C.c_char_p, C.c_int]
+    L.kh_csv_header_ext.argtypes = [C.c_char_p, C.c_int]
+    L.kh_csv_line_ext.argtypes = [C.c_char_p, C.c_char_p, C.c_char_p, C.c_double, C.c_double, C.c_char_p, C.c_char_p,
+                                  C.c_int, C.c_double, C.c_double, C.c_double, C.c_int, C.c_char_p, C.c_int]
     L.kh_shape_roundtrip.argtypes = [C.c_char_p, C.c_char_p, C.c_int]
     return L
 
@@ -509,6 +512,20 @@ def csv_line(kernel, shape, backend, ms, rate_, timestamp, device) -> str:
     buf = C.create_string_buffer(2048)
     lib.kh_csv_line(kernel.encode(), shape.encode(), backend.encode(), ms, rate_,
                     timestamp.encode(), device.encode(), buf, 2048)
+    return buf.value.decode()
+
+
+def csv_header_ext() -> str:
+    buf = C.create_string_buffer(512)
+    lib.kh_csv_header_ext(buf, 512)
+    return buf.value.decode()
+
+
+def csv_line_ext(kernel, shape, backend, ms, rate_, timestamp, device, gpus=1, roofline_frac=0.0, max_rel_err=-1.0,
+                 cpu_ms=-1.0, cpu_cores=0) -> str:
+    buf = C.create_string_buffer(2048)
+    lib.kh_csv_line_ext(kernel.encode(), shape.encode(), backend.encode(), ms, rate_, timestamp.encode(),
+                        device.encode(), gpus, roofline_frac, max_rel_err, cpu_ms, cpu_cores, buf, 2048)
     return buf.value.decode()
 
 

@@ -722,6 +722,31 @@ int kh_csv_line(const char *kernel, const char *shape, const char *backend, doub
   return 0;
 }
 
+int kh_csv_header_ext(char *buf, int cap) {
+  copy_out(kh::bench::kCsvExtendedHeader, buf, cap);
+  return 0;
+}
+
+int kh_csv_line_ext(const char *kernel, const char *shape, const char *backend, double ms, double rate,
+                    const char *timestamp, const char *device, int gpus, double roofline_frac, double max_rel_err,
+                    double cpu_ms, int cpu_cores, char *buf, int cap) {
+  kh::bench::BenchRow r;
+  r.kernel = kernel ? kernel : "";
+  r.shape = shape ? shape : "";
+  r.backend = backend ? backend : "";
+  r.ms_median = ms;
+  r.gflops_or_gbps = rate;
+  r.timestamp = timestamp ? timestamp : "";
+  r.device = device ? device : "";
+  r.gpus = gpus;
+  r.roofline_frac = roofline_frac;
+  r.max_rel_err = max_rel_err;
+  r.cpu_ms = cpu_ms;
+  r.cpu_cores = cpu_cores;
+  copy_out(kh::bench::csv_line_extended(r), buf, cap);
+  return 0;
+}
+
 int kh_shape_roundtrip(const char *text, char *buf, int cap) {
   copy_out(kh::shape_to_text(kh::parse_shape_text(text ? text : "")), buf, cap);
   return 0;

@@ -11,8 +11,10 @@
 //       fills the inputs deterministically, launches once, prints a digest of
 //       every output (new verb; the reference has none).
 //   kernelh bench   --kernel K --shape S [--warmup W] [--iters N] [--out DIR]
-//   kernelh bench   --suite kernelh [--out DIR]
-//       warm-up + median of event-timed launches, one results.csv row per kernel.
+//   kernelh bench   --suite kernelh [--out DIR] [--peak-gbs G --peak-tflops T]
+//       warm-up + median of event-timed launches, one results.csv row per kernel; with the
+//       measured peaks also DIR/results_b200.csv, whose rows append gpus, roofline_frac,
+//       max_rel_err, cpu_ms, cpu_cores after the reference's seven columns.
 //   kernelh bench   --occupancy --kernel K --shape S --target T [--out DIR]
 //       the analytic occupancy report of the launches the library would make, fed with
 //       the registers and static shared memory ptxas reported for each entry point;
@@ -336,10 +338,17 @@ int cmd_bench(const Flags &f) {
   if (int rc = open_context(&ctx)) return rc;
   kh_device_info info;
   kh_device_info_get(ctx, &info);
-  std::string csv;
+  std::string csv, csv_ext;
   char line[2048];
   kh_csv_header(line, sizeof line);
   csv = std::string(line) + "\n";
+  // with --peak-gbs / --peak-tflops (the measured HBM and tensor peaks) a second file carries the
+  // appended columns: gpus, roofline_frac, max_rel_err, cpu_ms, cpu_cores (the last three empty here:
+  // the library holds no CPU implementation to check or time against)
+  const double peak_gbs = std::atof(f.get("--peak-gbs", "0").c_str());
+  const double peak_gflops = std::atof(f.get("--peak-tflops", "0").c_str()) * 1e3;
+  kh_csv_header_ext(line, sizeof line);
+  csv_ext = std::string(line) + "\n";
   int failures = 0;
   for (const Row &r : rows) {
     double ms = 0, rate = 0;
@@ -354,6 +363,10 @@ int cmd_bench(const Flags &f) {
     kh_csv_line(r.kernel.c_str(), r.shape.c_str(), "kernelh", ms, rate, timestamp_utc().c_str(), info.name, line,
                 sizeof line);
     csv += std::string(line) + "\n";
+    const double peak = is_gflops ? peak_gflops : peak_gbs;
+    kh_csv_line_ext(r.kernel.c_str(), r.shape.c_str(), "kernelh", ms, rate, timestamp_utc().c_str(), info.name, 1,
+                    peak > 0 ? rate / peak : 0.0, -1.0, -1.0, 0, line, sizeof line);
+    csv_ext += std::string(line) + "\n";
   }
   if (f.has("--out")) {
     ::mkdir(f.get("--out").c_str(), 0755);
@@ -361,6 +374,12 @@ int cmd_bench(const Flags &f) {
     std::ofstream file(path);
     file << csv;
     std::printf("wrote %s\n", path.c_str());
+    if (peak_gbs > 0 || peak_gflops > 0) {
+      const std::string epath = f.get("--out") + "/results_b200.csv";
+      std::ofstream efile(epath);
+      efile << csv_ext;
+      std::printf("wrote %s\n", epath.c_str());
+    }
   }
   kh_context_destroy(ctx);
   return failures ? kExitFail : kExitOk;

@@ -413,3 +413,13 @@ def test_scan_totals_resolves_and_keeps_the_reference_shape_rules():
     with pytest.raises(kh.KernelhError) as e:
         kh.plan("scan_totals", "n=0")
     assert "must be positive" in e.value.message
+
+
+def test_extended_csv_appends_columns_after_the_reference_seven(golden):
+    base = golden["host"]["csv"]["header"]
+    assert kh.csv_header_ext() == base + ",gpus,roofline_frac,max_rel_err,cpu_ms,cpu_cores"
+    row = golden["host"]["csv"]["lines"][0]
+    ext = kh.csv_line_ext(*row["row"], gpus=8, roofline_frac=0.75, max_rel_err=2.5e-6, cpu_ms=12.5, cpu_cores=16)
+    assert ext == row["line"] + ",8,0.75,2.5e-06,12.5,16"
+    # not checked / not timed: empty fields, the first seven untouched
+    assert kh.csv_line_ext(*row["row"]) == row["line"] + ",1,0,,,0"
