@@ -42,6 +42,17 @@ __device__ __forceinline__ void report_status(uint32_t *status, uint32_t code, u
   if (status != nullptr && atomicCAS(status, 0u, code) == 0u) status[1] = detail;
 }
 
+// Programmatic dependent launch. A kernel launched with the "may overlap its predecessor's
+// tail" attribute is scheduled while the previous kernel of the stream is still draining;
+// grid_dependency_wait() holds it until that kernel has completed and its writes are visible
+// (call it before the first global access), and grid_dependents_may_launch() tells the
+// scheduler that the NEXT kernel's blocks may be placed as this kernel's blocks retire.
+// Both are no-ops in a launch without the attribute.
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void grid_dependents_may_launch() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
 __device__ __forceinline__ bool is_aligned16(const void *p) {
   return (reinterpret_cast<uintptr_t>(p) & 15u) == 0;
 }
@@ -50,6 +61,18 @@ __device__ __forceinline__ float warp_max(float v) {
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
   return v;
+}
+// The warp's maximum in one instruction (sm_100a's floating-point redux); NaN if any lane holds one.
+__device__ __forceinline__ float warp_max_redux(float v) {
+  float r;
+  asm volatile("redux.sync.max.NaN.f32 %0, %1, 0xffffffff;" : "=f"(r) : "f"(v));
+  return r;
+}
+// 2^x by the special-function unit alone (about 2 ulp; denormal results flush to zero).
+__device__ __forceinline__ float exp2_approx(float x) {
+  float r;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(x));
+  return r;
 }
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll

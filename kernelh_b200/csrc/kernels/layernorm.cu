@@ -14,6 +14,10 @@
 // global read. Same row-to-thread mapping and fallbacks as softmax.
 #include "kh_device.cuh"
 
+#ifndef KH_ROW_MAX_REGS
+#define KH_ROW_MAX_REGS 72
+#endif
+
 namespace {
 
 constexpr int kMaxVec = 8;
@@ -34,7 +38,8 @@ __device__ __forceinline__ float row_sum(float v, float *smem) {
   return v;
 }
 
-template <bool kWholeBlock>
+// kFull: the row fills all kMaxVec vectors of every thread, so nothing is clamped or predicated.
+template <bool kWholeBlock, bool kFull = false>
 __device__ __forceinline__ void layernorm_row_regs(const float *__restrict__ xrow,
                                                    const float *__restrict__ gamma,
                                                    const float *__restrict__ beta,
@@ -45,20 +50,19 @@ __device__ __forceinline__ void layernorm_row_regs(const float *__restrict__ xro
   const float4 *b4 = reinterpret_cast<const float4 *>(beta);
   float4 *y4 = reinterpret_cast<float4 *>(yrow);
   float4 v[kMaxVec];
+  // Loads are unconditional (the index is clamped into the row, the value ignored later): a
+  // predicated load keeps the compiler from issuing the eight of them back to back.
 #pragma unroll
-  for (int i = 0; i < kMaxVec; ++i) {
-    const int idx = lane + i * tpr;
-    if (idx < nvec) v[i] = __ldcs(x4 + idx);
-  }
+  for (int i = 0; i < kMaxVec; ++i) v[i] = __ldcs(x4 + (kFull ? lane + i * tpr : min(lane + i * tpr, nvec - 1)));
   float s = 0.f;
 #pragma unroll
   for (int i = 0; i < kMaxVec; ++i)
-    if (lane + i * tpr < nvec) s += (v[i].x + v[i].y) + (v[i].z + v[i].w);
+    if (kFull || lane + i * tpr < nvec) s += (v[i].x + v[i].y) + (v[i].z + v[i].w);
   const float mean = row_sum<kWholeBlock>(s, smem) / static_cast<float>(cols);
   float q = 0.f;
 #pragma unroll
   for (int i = 0; i < kMaxVec; ++i)
-    if (lane + i * tpr < nvec) {
+    if (kFull || lane + i * tpr < nvec) {
       v[i].x -= mean; v[i].y -= mean; v[i].z -= mean; v[i].w -= mean;
       q += (v[i].x * v[i].x + v[i].y * v[i].y) + (v[i].z * v[i].z + v[i].w * v[i].w);
     }
@@ -67,8 +71,10 @@ __device__ __forceinline__ void layernorm_row_regs(const float *__restrict__ xro
 #pragma unroll
   for (int i = 0; i < kMaxVec; ++i) {
     const int idx = lane + i * tpr;
-    if (idx < nvec) {
-      const float4 g = __ldg(g4 + idx), b = __ldg(b4 + idx);
+    // unconditional like the loads of x; the register budget (64) keeps them in the output loop
+    const int gi = kFull ? idx : min(idx, nvec - 1);
+    const float4 g = __ldg(g4 + gi), b = __ldg(b4 + gi);
+    if (kFull || idx < nvec) {
       __stcs(y4 + idx, make_float4(fmaf(v[i].x * rstd, g.x, b.x), fmaf(v[i].y * rstd, g.y, b.y),
                                    fmaf(v[i].z * rstd, g.z, b.z), fmaf(v[i].w * rstd, g.w, b.w)));
     }
@@ -91,8 +97,7 @@ __device__ __forceinline__ void layernorm_rows_block_prefetch(const float *__res
   const auto load_row = [&](int64_t r) {
     const float4 *x4 = reinterpret_cast<const float4 *>(x + r * x_stride0);
 #pragma unroll
-    for (int i = 0; i < kVec; ++i)
-      if (tid + i * tpr < nvec) nxt[i] = __ldcs(x4 + tid + i * tpr);
+    for (int i = 0; i < kVec; ++i) nxt[i] = __ldcs(x4 + min(tid + i * tpr, nvec - 1)); // clamped, never predicated
   };
   if (blockIdx.x < rows) load_row(blockIdx.x);
   for (int64_t r = blockIdx.x; r < rows; r += gridDim.x) {
@@ -129,10 +134,13 @@ __device__ __forceinline__ void layernorm_rows_block_prefetch(const float *__res
 
 } // namespace
 
-extern "C" __global__ void __launch_bounds__(256)
+// 72 registers: the host's one-wave geometry for 1024-column rows is four resident blocks of
+// 224 threads per SM (4 x 7 warps x 72 x 32 = 64512 of the 65536 registers).
+extern "C" __global__ void __maxnreg__(KH_ROW_MAX_REGS)
 layernorm(KH_MEMREF2(const float, x), KH_MEMREF1(const float, gamma), KH_MEMREF1(const float, beta),
           KH_MEMREF2(float, y)) {
   __shared__ float smem[32];
+  khd::grid_dependency_wait(); // scheduled under the previous kernel's tail: its writes are visible from here
   const float *__restrict__ x = KH_DATA(x);
   const float *__restrict__ gamma = KH_DATA(gamma);
   const float *__restrict__ beta = KH_DATA(beta);
@@ -147,6 +155,12 @@ layernorm(KH_MEMREF2(const float, x), KH_MEMREF1(const float, gamma), KH_MEMREF1
     const int64_t warps_per_block = blockDim.x >> 5;
     const int64_t warp0 = static_cast<int64_t>(blockIdx.x) * warps_per_block + (threadIdx.x >> 5);
     const int64_t nwarps = static_cast<int64_t>(gridDim.x) * warps_per_block;
+    if (cols == 32 * 4 * kMaxVec) {
+      for (int64_t r = warp0; r < rows; r += nwarps)
+        layernorm_row_regs<false, true>(x + r * x_stride0, gamma, beta, y + r * y_stride0, 32 * kMaxVec,
+                                        32 * 4 * kMaxVec, threadIdx.x & 31, 32, smem);
+      return;
+    }
     for (int64_t r = warp0; r < rows; r += nwarps)
       layernorm_row_regs<false>(x + r * x_stride0, gamma, beta, y + r * y_stride0,
                                 static_cast<int>(cols >> 2), static_cast<int>(cols),

@@ -6,15 +6,24 @@
 // as rank-2 memref descriptors, 14 eight-byte parameters.
 //
 // One pass over HBM (8 bytes per element): a row is read once with 128-bit
-// loads into registers, each lane forms its own (max, sum of exp) pair, the
-// pairs are merged across lanes with the online rule
+// loads into registers; a warp takes the maximum m of its part in one redux
+// instruction, forms exp(v - m) as 2^(v log2e - m log2e) (one fused
+// multiply-add and one special-function instruction per element: the kernel
+// has about as many instruction-issue cycles to spare as it has DRAM cycles at
+// the small benchmark size, so the lean form is what keeps it on the memory
+// roofline) and sums by shuffles; when a row spans the block the warps' (m, s)
+// pairs are merged through shared memory with the online rule
 //   M = max(m1, m2);  s = s1 * exp(m1 - M) + s2 * exp(m2 - M)
-// by warp shuffles (plus one shared-memory exchange when a row spans the
-// block), and the row is written once. Rows up to 1024 columns take a warp
+// and the row is written once. The rounding of m log2e is common to the whole
+// row and cancels in the quotient. Rows up to 1024 columns take a warp
 // each; rows up to 8 float4 per thread take a block; anything else (long,
 // misaligned or strided rows, odd block sizes) takes a two-read generic path.
 // All row loops stride over the grid, so any launch geometry is correct.
 #include "kh_device.cuh"
+
+#ifndef KH_ROW_MIN_BLOCKS
+#define KH_ROW_MIN_BLOCKS 4 // resident blocks per SM the register budget is cut for
+#endif
 
 namespace {
 
@@ -30,13 +39,15 @@ __device__ __forceinline__ MaxSum merge(MaxSum a, MaxSum b) {
   return {M, a.s * expf(a.m - M) + b.s * expf(b.m - M)};
 }
 
-__device__ __forceinline__ MaxSum warp_merge(MaxSum v) {
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1) {
-    MaxSum other{__shfl_xor_sync(0xffffffffu, v.m, o), __shfl_xor_sync(0xffffffffu, v.s, o)};
-    v = merge(v, other);
-  }
-  return v;
+constexpr float kLog2e = 1.4426950408889634f;
+
+// exp(v - m) for a lane's vectors, given mb = m * log2e; returns the lane's sum.
+__device__ __forceinline__ float exp_in_place(float4 &v, float mb) {
+  v.x = khd::exp2_approx(fmaf(v.x, kLog2e, -mb));
+  v.y = khd::exp2_approx(fmaf(v.y, kLog2e, -mb));
+  v.z = khd::exp2_approx(fmaf(v.z, kLog2e, -mb));
+  v.w = khd::exp2_approx(fmaf(v.w, kLog2e, -mb));
+  return (v.x + v.y) + (v.z + v.w);
 }
 
 // One row held in registers by `tpr` cooperating threads (a warp, or the block).
@@ -47,26 +58,21 @@ __device__ __forceinline__ void softmax_row_regs(const float *__restrict__ xrow,
   const float4 *x4 = reinterpret_cast<const float4 *>(xrow);
   float4 *y4 = reinterpret_cast<float4 *>(yrow);
   float4 v[kMaxVec];
+  // Loads are unconditional (the index is clamped into the row, the value ignored later): a
+  // predicated load keeps the compiler from issuing the eight of them back to back.
 #pragma unroll
-  for (int i = 0; i < kMaxVec; ++i) {
-    const int idx = lane + i * tpr;
-    if (idx < nvec) v[i] = __ldcs(x4 + idx);
-  }
+  for (int i = 0; i < kMaxVec; ++i) v[i] = __ldcs(x4 + min(lane + i * tpr, nvec - 1));
   float m = -INFINITY;
 #pragma unroll
   for (int i = 0; i < kMaxVec; ++i)
     if (lane + i * tpr < nvec) m = fmaxf(m, fmaxf(fmaxf(v[i].x, v[i].y), fmaxf(v[i].z, v[i].w)));
+  m = khd::warp_max_redux(m);
+  const float mb = (m == -INFINITY) ? 0.f : m * kLog2e; // a part of -inf only: every exp is 0
   float s = 0.f;
 #pragma unroll
   for (int i = 0; i < kMaxVec; ++i)
-    if (lane + i * tpr < nvec) {
-      v[i].x = expf(v[i].x - m);
-      v[i].y = expf(v[i].y - m);
-      v[i].z = expf(v[i].z - m);
-      v[i].w = expf(v[i].w - m);
-      s += (v[i].x + v[i].y) + (v[i].z + v[i].w);
-    }
-  MaxSum t = warp_merge({m, s});
+    if (lane + i * tpr < nvec) s += exp_in_place(v[i], mb);
+  MaxSum t{m, khd::warp_sum(s)};
   if (kWholeBlock) {
     const int warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
     __syncthreads(); // smem reuse across rows
@@ -76,8 +82,8 @@ __device__ __forceinline__ void softmax_row_regs(const float *__restrict__ xrow,
     for (int w = 1; w < nwarps; ++w) acc = merge(acc, smem[w]);
     t = acc;
   }
-  // exp(v - M) / S = exp(v - m) * exp(m - M) / S
-  const float scale = (m == -INFINITY) ? 0.f : expf(m - t.m) / t.s;
+  // exp(v - M) / S = exp(v - m) * exp(m - M) / S, m the warp's maximum and M the row's
+  const float scale = (m == -INFINITY) ? 0.f : (kWholeBlock ? expf(m - t.m) : 1.0f) / t.s;
 #pragma unroll
   for (int i = 0; i < kMaxVec; ++i) {
     const int idx = lane + i * tpr;
@@ -98,8 +104,7 @@ __device__ __forceinline__ void softmax_rows_block_prefetch(const float *__restr
   const auto load_row = [&](int64_t r) {
     const float4 *x4 = reinterpret_cast<const float4 *>(x + r * x_stride0);
 #pragma unroll
-    for (int i = 0; i < kVec; ++i)
-      if (tid + i * tpr < nvec) nxt[i] = __ldcs(x4 + tid + i * tpr);
+    for (int i = 0; i < kVec; ++i) nxt[i] = __ldcs(x4 + min(tid + i * tpr, nvec - 1)); // clamped, never predicated
   };
   if (blockIdx.x < rows) load_row(blockIdx.x);
   for (int64_t r = blockIdx.x; r < rows; r += gridDim.x) {
@@ -111,17 +116,13 @@ __device__ __forceinline__ void softmax_rows_block_prefetch(const float *__restr
 #pragma unroll
     for (int i = 0; i < kVec; ++i)
       if (tid + i * tpr < nvec) m = fmaxf(m, fmaxf(fmaxf(v[i].x, v[i].y), fmaxf(v[i].z, v[i].w)));
+    m = khd::warp_max_redux(m);
+    const float mb = (m == -INFINITY) ? 0.f : m * kLog2e;
     float s = 0.f;
 #pragma unroll
     for (int i = 0; i < kVec; ++i)
-      if (tid + i * tpr < nvec) {
-        v[i].x = expf(v[i].x - m);
-        v[i].y = expf(v[i].y - m);
-        v[i].z = expf(v[i].z - m);
-        v[i].w = expf(v[i].w - m);
-        s += (v[i].x + v[i].y) + (v[i].z + v[i].w);
-      }
-    MaxSum t = warp_merge({m, s});
+      if (tid + i * tpr < nvec) s += exp_in_place(v[i], mb);
+    MaxSum t{m, khd::warp_sum(s)};
     __syncthreads(); // smem reuse across rows
     if ((tid & 31) == 0) smem[warp] = t;
     __syncthreads();
@@ -138,9 +139,11 @@ __device__ __forceinline__ void softmax_rows_block_prefetch(const float *__restr
 
 } // namespace
 
-extern "C" __global__ void __launch_bounds__(256)
+// Four blocks of up to 256 threads per SM is what the host's one-wave geometry needs: 64 registers.
+extern "C" __global__ void __launch_bounds__(256, KH_ROW_MIN_BLOCKS)
 softmax(KH_MEMREF2(const float, x), KH_MEMREF2(float, y)) {
   __shared__ MaxSum smem[32];
+  khd::grid_dependency_wait(); // scheduled under the previous kernel's tail: its writes are visible from here
   const float *__restrict__ x = KH_DATA(x);
   float *__restrict__ y = KH_DATA(y);
   const int64_t rows = x_size0, cols = x_size1;

@@ -16,6 +16,7 @@
 
 extern "C" __global__ void __launch_bounds__(256)
 vecadd(KH_MEMREF1(const float, a), KH_MEMREF1(const float, b), KH_MEMREF1(float, c)) {
+  khd::grid_dependency_wait(); // scheduled under the previous kernel's tail: its writes are visible from here
   const float *__restrict__ a = KH_DATA(a);
   const float *__restrict__ b = KH_DATA(b);
   float *__restrict__ c = KH_DATA(c);

@@ -47,6 +47,7 @@ KernelPlan plan_vecadd(const ShapeMap &shape, const DeviceLimits &l) {
   p.tensors = {{"a", {n}, false}, {"b", {n}, false}, {"c", {n}, true}};
   LaunchStep s;
   s.entry = "vecadd";
+  s.overlap_tail = true;
   s.block = {256, 1, 1};
   s.grid = {balanced_grid((n / 4 + 1023) / 1024, sm_count(l), 6), 1, 1}; // 4 float4 per thread per trip
   s.param_count = 15;
@@ -86,8 +87,19 @@ KernelPlan plan_fused_gelu(const ShapeMap &shape, const DeviceLimits &l) {
     p.tensors = {{"x", {n}, false}, {"tmp", {n}, false}, {"out", {n}, true}};
   LaunchStep s;
   s.entry = bias ? "fused_gelu_bias" : "fused_gelu";
+  s.overlap_tail = true;
   s.block = {256, 1, 1};
-  s.grid = {balanced_grid((n / 4 + 1023) / 1024, sm_count(l), 5), 1, 1};
+  // Four float4 per thread and trip, the last trip predicated. Up to two trips' worth of work
+  // runs as four blocks on every SM (measured best at the 2^22-element benchmark size: more
+  // blocks than that only add idle trips, fewer leave the memory system short of requests);
+  // beyond that, whole waves of five blocks per SM with equal trip counts.
+  {
+    const long sms = sm_count(l);
+    const int64_t needed = (n / 4 + 1023) / 1024;
+    s.grid = {needed <= 8 * sms ? static_cast<unsigned>(std::clamp<int64_t>(needed, 1, 4 * sms))
+                                : balanced_grid(needed, sms, 5),
+              1, 1};
+  }
   s.param_count = 15;
   p.steps = {s};
   // The reference counts 3*n*4 bytes for this kernel although its fused form never
@@ -101,6 +113,7 @@ LaunchStep row_kernel_step(const char *entry, int64_t rows, int64_t cols, const 
                            int params) {
   LaunchStep s;
   s.entry = entry;
+  s.overlap_tail = true;
   s.param_count = params;
   const long sms = sm_count(l);
   if (cols % 4 == 0 && cols <= 1024) {

@@ -123,14 +123,14 @@ Result<void> Executor::launch(KernelFunction fn, const LaunchStep &step, LaunchA
   ++launches_issued_;
   if (!profiling_)
     return backend_->launch_kernel(fn.handle, step.grid, step.block, step.dynamic_smem, s,
-                                   args.params(), step.cluster);
+                                   args.params(), step.cluster, step.overlap_tail);
   auto e0 = backend_->event_create();
   if (!e0) return std::unexpected(e0.error());
   auto e1 = backend_->event_create();
   if (!e1) return std::unexpected(e1.error());
   if (auto r = backend_->event_record(*e0, s); !r) return r;
   auto launched = backend_->launch_kernel(fn.handle, step.grid, step.block, step.dynamic_smem, s,
-                                          args.params(), step.cluster);
+                                          args.params(), step.cluster, step.overlap_tail);
   if (auto r = backend_->event_record(*e1, s); !r) return r;
   profiled_.push_back({step.entry, *e0, *e1});
   return launched;

@@ -40,6 +40,7 @@ struct LaunchStep {
   LaunchDims grid, block;
   size_t dynamic_smem = 0;
   unsigned cluster = 1;
+  bool overlap_tail = false; // the entry waits with griddepcontrol.wait: it may be scheduled under its predecessor's tail
   int param_count = 0;   // kernel parameters (descriptor slots + extras)
   int tmem_columns = 0;
 };

@@ -97,9 +97,12 @@ public:
   virtual Result<int> occupancy_max_blocks(void *function, int block_size, size_t dyn_smem) = 0;
   virtual Result<TensorMapBytes> encode_tensor_map(const TensorMapSpec &spec) = 0;
 
+  // `cluster_x` > 1: CTAs per cluster. `overlap_tail`: programmatic dependent launch - the
+  // kernel may be scheduled while the previous kernel of the stream is still draining; it must
+  // then wait (griddepcontrol.wait) before it touches anything that kernel may have written.
   virtual Result<void> launch_kernel(void *function, const LaunchDims &grid, const LaunchDims &block,
                                      size_t shared_bytes, StreamHandle stream, void *const *params,
-                                     unsigned cluster_x = 1) = 0;
+                                     unsigned cluster_x = 1, bool overlap_tail = false) = 0;
 
   virtual Result<StreamHandle> stream_create() = 0;
   virtual Result<void> stream_destroy(StreamHandle s) = 0;

@@ -309,9 +309,9 @@ public:
 
   Result<void> launch_kernel(void *function, const LaunchDims &grid, const LaunchDims &block,
                              size_t shared_bytes, StreamHandle stream, void *const *params,
-                             unsigned cluster_x) override {
+                             unsigned cluster_x, bool overlap_tail) override {
     CUresult r;
-    if (cluster_x <= 1) {
+    if (cluster_x <= 1 && !overlap_tail) {
       r = api_.LaunchKernel(static_cast<CUfunction>(function), grid.x, grid.y, grid.z, block.x,
                             block.y, block.z, static_cast<unsigned>(shared_bytes),
                             static_cast<CUstream>(stream), const_cast<void **>(params), nullptr);
@@ -326,14 +326,23 @@ public:
       cfg.blockDimZ = block.z;
       cfg.sharedMemBytes = static_cast<unsigned>(shared_bytes);
       cfg.hStream = static_cast<CUstream>(stream);
-      CUlaunchAttribute attr;
-      std::memset(&attr, 0, sizeof attr);
-      attr.id = CU_LAUNCH_ATTRIBUTE_CLUSTER_DIMENSION;
-      attr.value.clusterDim.x = cluster_x;
-      attr.value.clusterDim.y = 1;
-      attr.value.clusterDim.z = 1;
-      cfg.attrs = &attr;
-      cfg.numAttrs = 1;
+      CUlaunchAttribute attrs[2];
+      std::memset(attrs, 0, sizeof attrs);
+      unsigned count = 0;
+      if (cluster_x > 1) {
+        attrs[count].id = CU_LAUNCH_ATTRIBUTE_CLUSTER_DIMENSION;
+        attrs[count].value.clusterDim.x = cluster_x;
+        attrs[count].value.clusterDim.y = 1;
+        attrs[count].value.clusterDim.z = 1;
+        ++count;
+      }
+      if (overlap_tail) {
+        attrs[count].id = CU_LAUNCH_ATTRIBUTE_PROGRAMMATIC_STREAM_SERIALIZATION;
+        attrs[count].value.programmaticStreamSerializationAllowed = 1;
+        ++count;
+      }
+      cfg.attrs = attrs;
+      cfg.numAttrs = count;
       r = api_.LaunchKernelEx(&cfg, static_cast<CUfunction>(function), const_cast<void **>(params),
                               nullptr);
     }
