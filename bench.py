@@ -357,6 +357,17 @@ def memory_bound_rows(torch, ctx, stream, hbm_peak: float) -> dict:
     row("scan", "scan", f"n={n}", lambda: [torch.rand(n, device="cuda"), f(n)], 2 * n * 4, 24,
         check=lambda: ([cx], O.scan_ref(cx)),
         cpu=lambda: cpu_row(lambda: O.scan_ref(cx), 2 * n * 4, False, "port", 1, f"all {n} elements, fp64 running sum"))
+    # The floor at the small sizes: the driver's own device-to-device copy of 16 MiB (32 MiB of
+    # traffic, what softmax, layernorm and fused_gelu move at their benchmark sizes), timed the
+    # same way. A kernel at this rate is bounded by launch, ramp and drain, not by its own code.
+    n = 1 << 22
+    sets = [[f(n), f(n)] for _ in range(8)]
+    ms, method = time_rotating(torch, lambda st, _stream: st[1].copy_(st[0]), sets, 200)
+    out["d2d_copy_floor"] = {"shape": f"n={n}", "ms": ms, "gbs": 2 * n * 4 / ms / 1e6,
+                             "frac_of_measured_hbm": 2 * n * 4 / ms / 1e6 / hbm_peak,
+                             "frac_of_nominal_8tbs": 2 * n * 4 / ms / 1e6 / NOMINAL_HBM_GBS, "buffer_sets": 8,
+                             "timing": method, "note": "cudaMemcpyAsync device to device, not a kernel of this library"}
+    del sets
     # large sizes: one buffer set is already far larger than L2
     n = 1 << 28
     row("vecadd_large", "vecadd", f"n={n}", lambda: [f(n), f(n), f(n)], 3 * n * 4, 1, 20)
@@ -803,6 +814,8 @@ def gpu_arm(args) -> None:
                 f.write(kh.csv_line_ext("gemm", f"m={size},n={size},k={size}", "kernelh", ms_step, value * 1e3, stamp, device,
                                         world, roofline["frac"], parity["gemm"]["max_rel_floored_by_rank"][0]) + "\n")
                 for name, r_ in line["memory_bound"].items():
+                    if name == "d2d_copy_floor":  # the driver's copy, not a kernel of the harness's list
+                        continue
                     kernel = name.split("_large")[0].split("_16384")[0].replace("_bias", "")
                     cpu = r_.get("cpu", {})
                     f.write(kh.csv_line_ext(kernel, r_["shape"], "kernelh", r_["ms"], r_["gbs"], stamp, device, 1,

@@ -58,6 +58,7 @@ using khd::Half8;
 using khd::RowScale;
 using khd::row_scale;
 using khd::scale_shift;
+using khd::split_fp16_pairs;
 using khd::split_fp16x2;
 
 constexpr int kHeadDim = 64;
@@ -147,29 +148,37 @@ attention_split(KH_MEMREF4(const float, q), KH_MEMREF4(const float, k), KH_MEMRE
                 int *__restrict__ shifts) {
   // float4 groups of a row are stored at group ^ (row / 8 mod 8): conflict-free both ways
   __shared__ __align__(16) float tile[64][64];
-  __shared__ float warp_max[8];
+  __shared__ float warp_max[2][8]; // alternating per job, so one barrier per job orders it
   const int64_t bh = q_size0 * q_size1, seq = q_size2;
-  const int64_t tiles = seq >> 6;
-  const float *const src[3] = {KH_DATA(q), KH_DATA(k), KH_DATA(v)};
-  __half *const dst_hi[2] = {q_hi, k_hi};
-  __half *const dst_lo[2] = {q_lo, k_lo};
+  // Job arithmetic is 32-bit and free of 64-bit divisions (a software routine of about a hundred
+  // instructions each, several per tile and thread, which once made this kernel issue-bound):
+  // a tensor has bh * seq / 64 tiles (< 2^31 for anything that fits the GPU), a tile's source is
+  // 4096 contiguous floats, and only V needs (slice, tile) separately.
+  const uint32_t tiles = static_cast<uint32_t>(seq >> 6);
+  const uint32_t per_tensor = static_cast<uint32_t>(bh) * tiles;
+  const uint32_t jobs = 3u * per_tensor;
+  const float *const src_q = KH_DATA(q), *const src_k = KH_DATA(k), *const src_v = KH_DATA(v);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   // the tile of a job is 64 x 64 contiguous values = 1024 float4; a thread takes float4 tid, tid + 256, ...
-  const int64_t jobs = 3 * bh * tiles;
-  const auto tile_of = [&](int64_t job) {
-    const int64_t t = job / (bh * tiles), rest = job - t * bh * tiles; // rest = slice * tiles + tile
-    return reinterpret_cast<const float4 *>(src[t] + rest * (64 * kHeadDim)) + threadIdx.x;
+  const auto tensor_of = [&](uint32_t job) { return (job >= per_tensor ? 1u : 0u) + (job >= 2u * per_tensor ? 1u : 0u); };
+  const auto tile_of = [&](uint32_t job) {
+    const uint32_t t = tensor_of(job), rest = job - t * per_tensor; // rest = slice * tiles + tile
+    const float *base = t == 0 ? src_q : (t == 1 ? src_k : src_v); // selects, not an indexed local array
+    return reinterpret_cast<const float4 *>(base + static_cast<size_t>(rest) * (64 * kHeadDim)) + threadIdx.x;
   };
+  // The attention kernel that follows may be scheduled as soon as SMs drain: its CTAs set up
+  // their barriers and tensor memory and then wait for this whole grid before reading anything.
+  khd::grid_dependents_may_launch();
   float4 n0 = make_float4(0.f, 0.f, 0.f, 0.f), n1 = n0, n2 = n0, n3 = n0;
   if (blockIdx.x < jobs) {
     const float4 *p = tile_of(blockIdx.x);
     n0 = __ldcs(p); n1 = __ldcs(p + 256); n2 = __ldcs(p + 512); n3 = __ldcs(p + 768);
   }
-  for (int64_t job = blockIdx.x; job < jobs; job += gridDim.x) {
-    const int64_t t = job / (bh * tiles), rest = job - t * bh * tiles;
-    const int64_t slice = rest / tiles, s0 = (rest - slice * tiles) << 6;
+  int parity = 0;
+  for (uint32_t job = blockIdx.x; job < jobs; job += gridDim.x, parity ^= 1) {
+    const uint32_t t = tensor_of(job), rest = job - t * per_tensor;
     const float4 f0 = n0, f1 = n1, f2 = n2, f3 = n3;
-    if (job + gridDim.x < jobs) { // the next tile's loads fly while this one is worked on
+    if (job + gridDim.x < jobs) { // the next tile's loads fly while this one is worked on (jobs < 2^31 - grid)
       const float4 *p = tile_of(job + gridDim.x);
       n0 = __ldcs(p); n1 = __ldcs(p + 256); n2 = __ldcs(p + 512); n3 = __ldcs(p + 768);
     }
@@ -177,10 +186,10 @@ attention_split(KH_MEMREF4(const float, q), KH_MEMREF4(const float, k), KH_MEMRE
                     fmaxf(fmaxf(fabsf(f1.x), fabsf(f1.y)), fmaxf(fabsf(f1.z), fabsf(f1.w))));
     m = fmaxf(m, fmaxf(fmaxf(fmaxf(fabsf(f2.x), fabsf(f2.y)), fmaxf(fabsf(f2.z), fabsf(f2.w))),
                        fmaxf(fmaxf(fabsf(f3.x), fabsf(f3.y)), fmaxf(fabsf(f3.z), fabsf(f3.w)))));
-    m = khd::warp_max(m);
-    __syncthreads(); // the previous job is done with warp_max and the tile
-    if (lane == 0) warp_max[warp] = m;
+    m = khd::warp_max_redux_numbers(m);
+    if (lane == 0) warp_max[parity][warp] = m; // the job before last used this half: a barrier lies between
     if (t == 2) {
+      __syncthreads(); // the previous job (a V tile too, or the last K tile) is done with the tile
       // V goes through shared memory: row = key, 16 float4 groups per row; float4 tid + 256 j
       // is group tid % 16 of row tid / 16 + 16 j
       const int sl = threadIdx.x >> 4, g = threadIdx.x & 15;
@@ -190,36 +199,40 @@ attention_split(KH_MEMREF4(const float, q), KH_MEMREF4(const float, k), KH_MEMRE
       *reinterpret_cast<float4 *>(&tile[sl + 48][(g ^ (((sl + 48) >> 3) & 7)) * 4]) = f3;
     }
     __syncthreads();
-    m = warp_max[0];
+    m = warp_max[parity][0];
 #pragma unroll
-    for (int w = 1; w < 8; ++w) m = fmaxf(m, warp_max[w]);
+    for (int w = 1; w < 8; ++w) m = fmaxf(m, warp_max[parity][w]);
     const int shift = scale_shift(m);
     const RowScale sc = row_scale(shift);
     if (threadIdx.x == 0) shifts[job] = shift;
     if (t < 2) {
       // four values -> 8 bytes of hi and of lo; a warp store covers 256 contiguous bytes
-      const float4 f[4] = {f0, f1, f2, f3};
-      uint2 *out_hi = reinterpret_cast<uint2 *>(dst_hi[t] + (slice * seq + s0) * kHeadDim) + threadIdx.x;
-      uint2 *out_lo = reinterpret_cast<uint2 *>(dst_lo[t] + (slice * seq + s0) * kHeadDim) + threadIdx.x;
+      const float2 x[8] = {make_float2(f0.x, f0.y), make_float2(f0.z, f0.w), make_float2(f1.x, f1.y),
+                           make_float2(f1.z, f1.w), make_float2(f2.x, f2.y), make_float2(f2.z, f2.w),
+                           make_float2(f3.x, f3.y), make_float2(f3.z, f3.w)};
+      __half2 h[8], l[8];
+      split_fp16_pairs<8>(x, sc, h, l);
+      // (slice * seq + s0) * 64 = rest * 4096: the splits of Q and K are laid out like their sources
+      uint2 *out_hi = reinterpret_cast<uint2 *>((t == 0 ? q_hi : k_hi) + static_cast<size_t>(rest) * (64 * kHeadDim)) + threadIdx.x;
+      uint2 *out_lo = reinterpret_cast<uint2 *>((t == 0 ? q_lo : k_lo) + static_cast<size_t>(rest) * (64 * kHeadDim)) + threadIdx.x;
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
-        __half2 h01, l01, h23, l23;
-        split_fp16x2(f[j].x, f[j].y, sc, h01, l01);
-        split_fp16x2(f[j].z, f[j].w, sc, h23, l23);
-        out_hi[256 * j] = make_uint2(half2_bits(h01), half2_bits(h23));
-        out_lo[256 * j] = make_uint2(half2_bits(l01), half2_bits(l23));
+        out_hi[256 * j] = make_uint2(half2_bits(h[2 * j]), half2_bits(h[2 * j + 1]));
+        out_lo[256 * j] = make_uint2(half2_bits(l[2 * j]), half2_bits(l[2 * j + 1]));
       }
     } else {
+      const uint32_t slice = rest / tiles, s0 = (rest - slice * tiles) << 6;
       const int sub = lane >> 3, sgroup = lane & 7; // 4 rows of V^T per warp store, 8 keys per lane
 #pragma unroll
       for (int j = 0; j < 2; ++j) {
         const int dl = warp * 8 + j * 4 + sub;
         const int col = (((dl >> 2) ^ sgroup) << 2) | (dl & 3); // rows sgroup*8.. share one swizzle
         Half8 h, l;
+        float2 x[4];
 #pragma unroll
-        for (int qd = 0; qd < 4; ++qd)
-          split_fp16x2(tile[sgroup * 8 + 2 * qd][col], tile[sgroup * 8 + 2 * qd + 1][col], sc, h.v[qd], l.v[qd]);
-        const int64_t o = (slice * kHeadDim + dl) * seq + s0 + sgroup * 8;
+        for (int qd = 0; qd < 4; ++qd) x[qd] = make_float2(tile[sgroup * 8 + 2 * qd][col], tile[sgroup * 8 + 2 * qd + 1][col]);
+        split_fp16_pairs<4>(x, sc, h.v, l.v);
+        const int64_t o = (static_cast<int64_t>(slice) * kHeadDim + dl) * seq + s0 + sgroup * 8;
         *reinterpret_cast<Half8 *>(vt_hi + o) = h;
         *reinterpret_cast<Half8 *>(vt_lo + o) = l;
       }
@@ -327,6 +340,9 @@ __device__ __forceinline__ void attention_body(int64_t slices, int64_t seq, floa
   __syncthreads();
   khd::tc_fence_after_sync();
   const uint32_t tmem_base = s_tmem_base;
+  // The launch may have been scheduled under the tail of attention_split: everything above touched
+  // only this CTA's own shared and tensor memory; the splits and exponents are read from here on.
+  khd::grid_dependency_wait();
 
   const int wg = warp >> 2;
   if (wg == 0) {

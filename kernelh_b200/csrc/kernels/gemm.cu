@@ -71,6 +71,7 @@ using khd::RowScale;
 using khd::row_scale;
 using khd::scale_pow2;
 using khd::scale_shift;
+using khd::split_fp16_pairs;
 using khd::split_fp16x2;
 
 constexpr int kBM = 128;     // rows per CTA (256 per pair)
@@ -184,10 +185,9 @@ __device__ __forceinline__ void split_a_rows(const float *__restrict__ a, int64_
     if (member == 0) a_shift[r] = shift;
     const auto store8 = [&](int64_t c, const float (&in)[8]) {
       Half8 h, l;
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        split_fp16x2(in[2 * j], in[2 * j + 1], scale, h.v[j], l.v[j]);
-      }
+      const float2 x[4] = {make_float2(in[0], in[1]), make_float2(in[2], in[3]), make_float2(in[4], in[5]),
+                           make_float2(in[6], in[7])};
+      split_fp16_pairs<4>(x, scale, h.v, l.v);
       *reinterpret_cast<Half8 *>(hi + r * kp + c) = h;
       *reinterpret_cast<Half8 *>(lo + r * kp + c) = l;
     };
@@ -270,10 +270,9 @@ __device__ __forceinline__ void split_a_staged(const float *__restrict__ a, int6
         for (int q = 0; q < 8; ++q) v[q] = (c + q < k) ? row[c + q] : 0.f;
       }
       Half8 h, l;
-#pragma unroll
-      for (int q = 0; q < 4; ++q) {
-        split_fp16x2(v[2 * q], v[2 * q + 1], scale, h.v[q], l.v[q]);
-      }
+      const float2 x[4] = {make_float2(v[0], v[1]), make_float2(v[2], v[3]), make_float2(v[4], v[5]),
+                           make_float2(v[6], v[7])};
+      split_fp16_pairs<4>(x, scale, h.v, l.v);
       *reinterpret_cast<Half8 *>(hi + r * kp + c) = h;
       *reinterpret_cast<Half8 *>(lo + r * kp + c) = l;
     }
@@ -583,12 +582,18 @@ gemm_prep_b(KH_MEMREF2(const float, b), const __grid_constant__ khd::TensorMap t
   }
   cluster_sync_all(); // every CTA's maxima are written (release / acquire across the cluster)
   if (threadIdx.x < kPrepCols) {
-    float m = 0.f;
-    for (uint32_t r = 0; r < cluster_ctas; ++r) {
-      float v;
-      asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(map_to_cta(khd::smem_u32(&cta_max[threadIdx.x]), r)));
-      m = fmaxf(m, v);
+    // all the remote reads are issued before the first is used: one round trip through the
+    // cluster's shared-memory network instead of one per CTA
+    float v[16];
+#pragma unroll
+    for (uint32_t r = 0; r < 16; ++r) {
+      v[r] = 0.f;
+      if (r < cluster_ctas)
+        asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v[r]) : "r"(map_to_cta(khd::smem_u32(&cta_max[threadIdx.x]), r)));
     }
+    float m = 0.f;
+#pragma unroll
+    for (uint32_t r = 0; r < 16; ++r) m = fmaxf(m, v[r]);
     const int shift = scale_shift(m);
     col_shift[threadIdx.x] = shift;
     if (rank == 0 && n0 + static_cast<int>(threadIdx.x) < n) b_shift[n0 + threadIdx.x] = shift;
@@ -608,10 +613,10 @@ gemm_prep_b(KH_MEMREF2(const float, b), const __grid_constant__ khd::TensorMap t
 #pragma unroll
     for (int part = 0; part < 4; ++part) {
       const int r = g * kPrepGroupRows + (warp + 8 * part) * 8;
+      float2 x[4];
 #pragma unroll
-      for (int q = 0; q < 4; ++q)
-        split_fp16x2(real ? element(r + 2 * q) : 0.f, real ? element(r + 2 * q + 1) : 0.f, scale, h[part].v[q],
-                     l[part].v[q]);
+      for (int q = 0; q < 4; ++q) x[q] = real ? make_float2(element(r + 2 * q), element(r + 2 * q + 1)) : make_float2(0.f, 0.f);
+      split_fp16_pairs<4>(x, scale, h[part].v, l[part].v);
     }
     __syncthreads(); // every value of the group is in registers: its bytes may be overwritten
 #pragma unroll
@@ -643,7 +648,8 @@ gemm_prep_b(KH_MEMREF2(const float, b), const __grid_constant__ khd::TensorMap t
       asm volatile("cp.async.bulk.commit_group;" ::: "memory");
     }
   }
-  if (threadIdx.x == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+  // the copies only have to be done READING this CTA's shared memory before it goes away
+  if (threadIdx.x == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
 }
 
 namespace {

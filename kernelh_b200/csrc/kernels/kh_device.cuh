@@ -68,6 +68,12 @@ __device__ __forceinline__ float warp_max_redux(float v) {
   asm volatile("redux.sync.max.NaN.f32 %0, %1, 0xffffffff;" : "=f"(r) : "f"(v));
   return r;
 }
+// The same, NaN lanes ignored (the result is the largest number any lane holds).
+__device__ __forceinline__ float warp_max_redux_numbers(float v) {
+  float r;
+  asm volatile("redux.sync.max.f32 %0, %1, 0xffffffff;" : "=f"(r) : "f"(v));
+  return r;
+}
 // 2^x by the special-function unit alone (about 2 ulp; denormal results flush to zero).
 __device__ __forceinline__ float exp2_approx(float x) {
   float r;

@@ -59,6 +59,30 @@ __device__ __forceinline__ void split_fp16x2(float x0, float x1, const RowScale 
   lo = __floats2half2_rn(s0 - h.x, s1 - h.y);
 }
 
+// The same for a group of pairs that share one scale, with the packed two-wide fp32 instructions
+// of sm_100a (one multiply and one subtract per PAIR) and the rare three-factor scaling behind
+// ONE branch for the whole group instead of predicated multiplies on every value: the split
+// kernels are instruction-issue bound before they are HBM bound, and this halves their fp32 work.
+template <int kPairs>
+__device__ __forceinline__ void split_fp16_pairs(const float2 (&x)[kPairs], const RowScale &sc, __half2 (&hi)[kPairs],
+                                                 __half2 (&lo)[kPairs]) {
+  float2 s[kPairs];
+  const float2 f1 = make_float2(sc.f1, sc.f1);
+#pragma unroll
+  for (int j = 0; j < kPairs; ++j) s[j] = __fmul2_rn(x[j], f1);
+  if (!sc.single) {
+    const float2 f2 = make_float2(sc.f2, sc.f2), f3 = make_float2(sc.f3, sc.f3);
+#pragma unroll
+    for (int j = 0; j < kPairs; ++j) s[j] = __fmul2_rn(__fmul2_rn(s[j], f2), f3);
+  }
+  const float2 minus_one = make_float2(-1.f, -1.f);
+#pragma unroll
+  for (int j = 0; j < kPairs; ++j) {
+    hi[j] = __float22half2_rn(s[j]);
+    lo[j] = __float22half2_rn(__ffma2_rn(__half22float2(hi[j]), minus_one, s[j])); // s - hi, exact
+  }
+}
+
 struct alignas(16) Half8 {
   __half2 v[4];
 };

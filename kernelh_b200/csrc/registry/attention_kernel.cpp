@@ -48,6 +48,7 @@ KernelPlan plan_attention(const ShapeMap &shape, const DeviceLimits &l) {
   split.param_count = 33 + 7;
   LaunchStep main;
   main.entry = "attention";
+  main.overlap_tail = true; // its set-up runs under the tail of attention_split
   main.block = {512, 1, 1}; // warpgroups: producer + two MMA issuers, two softmax groups, output
   // persistent: a CTA per SM walks the (slice, 128-query tile) work items
   main.grid = {static_cast<unsigned>(std::min<int64_t>(b * h * ((s + kBQ - 1) / kBQ), sms)), 1, 1};
