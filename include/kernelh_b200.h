@@ -230,6 +230,21 @@ int kh_memcpy_d2h(kh_context *ctx, void *dst, const void *src, size_t bytes);
 int kh_bench_row(kh_context *ctx, const char *kernel, const char *shape, int warmup, int iters,
                  double *ms_median, double *rate, int *rate_is_gflops);
 
+/* The harness on several GPUs of one box, in ONE process (the reference's harness
+ * opens ordinal 0 only, bench/harness/run_bench.cpp:146-153): a context per GPU,
+ * every GPU's memory mapped into every other (kh_enable_peer_access: the driver's
+ * peer mapping; afterwards a pointer of `peer` is valid in kernels of `ctx`), the
+ * gemm sharded by M-row blocks with B on every GPU, attention by (batch, head)
+ * slices; every rank stores its finished tiles into every replica of the output
+ * with plain peer stores inside its kernel, and the host waits for all ranks, which
+ * is the barrier. ms_median is the median over `iters` steps of the slowest rank's
+ * event-timed step, rate the whole job's GFLOP/s. Only gemm (m a multiple of
+ * 256 * gpus) and attention (batch * heads a multiple of gpus) are partitioned;
+ * any other kernel name is refused with code 2. 77 when fewer GPUs are visible. */
+int kh_enable_peer_access(kh_context *ctx, kh_context *peer);
+int kh_bench_sharded(int gpus, const char *kernel, const char *shape, int warmup, int iters, double *ms_median,
+                     double *rate, int *rate_is_gflops);
+
 /* ---- registry ----------------------------------------------------------------
  * registeredKernels() and the unknown-name error of emit()
  * (lib/dsl/registry.cpp:23-42, lib/dsl/program.cpp:27-37). */

@@ -106,6 +106,9 @@ def _load() -> C.CDLL:
     L.kh_memcpy_d2h.argtypes = [vp, vp, vp, C.c_size_t]
     L.kh_bench_row.argtypes = [vp, C.c_char_p, C.c_char_p, C.c_int, C.c_int,
                                C.POINTER(C.c_double), C.POINTER(C.c_double), C.POINTER(C.c_int)]
+    L.kh_enable_peer_access.argtypes = [vp, vp]
+    L.kh_bench_sharded.argtypes = [C.c_int, C.c_char_p, C.c_char_p, C.c_int, C.c_int,
+                                   C.POINTER(C.c_double), C.POINTER(C.c_double), C.POINTER(C.c_int)]
     L.kh_registered_kernels.argtypes = [C.c_char_p, C.c_int]
     L.kh_register_kernel.argtypes = [C.c_char_p, C.c_char_p, C.c_size_t, C.c_char_p, PLAN_FN, C.c_void_p]
     L.kh_unregister_kernel.argtypes = [C.c_char_p]
@@ -237,6 +240,10 @@ class Context:
                                 C.byref(ms), C.byref(rate), C.byref(is_gflops)))
         return ms.value, rate.value, bool(is_gflops.value)
 
+    def enable_peer_access(self, peer: "Context"):
+        """Maps the memory of `peer`'s GPU into this context's GPU (both in this process)."""
+        _check(lib.kh_enable_peer_access(self._h, peer._h))
+
     # ---- typed entry points ----------------------------------------------------
     def vecadd(self, a, b, c, n, stream=None):
         _check(lib.kh_vecadd(self._h, _ptr(a), _ptr(b), _ptr(c), n, stream))
@@ -350,6 +357,15 @@ def device_count() -> int:
     n = C.c_int()
     _check(lib.kh_device_count(C.byref(n)))
     return n.value
+
+
+def bench_sharded(gpus: int, kernel: str, shape: str, warmup: int = 5, iters: int = 20):
+    """One partitioned bench row (gemm by M-row blocks, attention by (batch, head) slices) on
+    `gpus` GPUs of this box from one process: (ms of the slowest rank, median; whole-job GFLOP/s)."""
+    ms, rate, is_gflops = C.c_double(), C.c_double(), C.c_int()
+    _check(lib.kh_bench_sharded(gpus, kernel.encode(), shape.encode(), warmup, iters,
+                                C.byref(ms), C.byref(rate), C.byref(is_gflops)))
+    return ms.value, rate.value
 
 
 def registered_kernels() -> list[str]:

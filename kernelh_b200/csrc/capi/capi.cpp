@@ -62,8 +62,12 @@ int refuse_misaligned(const char *entry, std::initializer_list<std::pair<const c
   return 0;
 }
 
+// Every entry point that takes a context passes through here: besides the null check, the
+// context's device becomes the calling thread's current one, so a process that holds several
+// contexts (one per GPU) never allocates or launches on the device of the context it used last.
 int need_ctx(kh_context *ctx) {
   if (ctx == nullptr || !ctx->exec) return set_error(2, "null kernelh_b200 context");
+  if (auto r = ctx->exec->backend().make_current(); !r) return set_error(r.error());
   return 0;
 }
 
@@ -394,6 +398,141 @@ int kh_bench_row(kh_context *ctx, const char *kernel, const char *shape, int war
       *rate = plan.work_is_flops ? kh::bench::gflops_from_ms(plan.work, *ms)
                                  : kh::bench::gbps_from_ms(plan.work, *ms);
     if (rate_is_gflops) *rate_is_gflops = plan.work_is_flops ? 1 : 0;
+    return 0;
+  });
+}
+
+int kh_enable_peer_access(kh_context *ctx, kh_context *peer) {
+  if (int rc = need_ctx(ctx)) return rc;
+  if (int rc = need_ctx(peer)) return rc;
+  return guarded([&] {
+    auto r = ctx->exec->backend().enable_peer_access(peer->exec->backend());
+    return r ? 0 : set_error(r.error());
+  });
+}
+
+int kh_bench_sharded(int gpus, const char *kernel, const char *shape, int warmup, int iters, double *ms_median,
+                     double *rate, int *rate_is_gflops) {
+  if (gpus < 1 || gpus > 8) return set_error(2, "kh_bench_sharded: between 1 and 8 GPUs are supported");
+  if (kernel == nullptr || shape == nullptr) return set_error(2, "kh_bench_sharded: kernel name and shape text are required");
+  const std::string name = kernel;
+  if (name != "gemm" && name != "attention")
+    return set_error(2, "kh_bench_sharded: only gemm (M-row blocks) and attention ((batch, head) slices) are partitioned; "
+                        "the other kernels run as independent replicas");
+  if (warmup < 0 || iters < 1) return set_error(2, "kh_bench_sharded: iters must be at least 1");
+  return guarded([&] {
+    const kh::ShapeMap map = kh::parse_shape_text(shape);
+    if (map.empty()) return set_error(2, "kh_bench_sharded: malformed shape text");
+    {
+      int have = 0;
+      if (int rc = kh_device_count(&have)) return rc;
+      if (have < gpus)
+        return set_error(kh::kDriverUnavailable, "kh_bench_sharded: " + std::to_string(gpus) + " GPUs asked for, " +
+                                                     std::to_string(have) + " visible");
+    }
+    // one context per GPU, every GPU mapped into every other
+    struct Rank {
+      std::unique_ptr<kh::Executor> exec;
+      std::vector<kh::Buffer> owned;
+      std::vector<void *> in;       // this rank's inputs
+      void *out = nullptr;          // its replica of the whole output
+      kh::EventHandle start = nullptr, stop = nullptr;
+    };
+    std::vector<Rank> ranks(static_cast<size_t>(gpus));
+    for (int d = 0; d < gpus; ++d) {
+      auto backend = kh::make_cuda_backend();
+      if (!backend) return set_error(backend.error());
+      auto exec = kh::Executor::create(*backend, d);
+      if (!exec) return set_error(exec.error());
+      ranks[d].exec = std::move(*exec);
+    }
+    for (int d = 0; d < gpus; ++d)
+      for (int e = 0; e < gpus; ++e)
+        if (auto r = ranks[d].exec->backend().enable_peer_access(ranks[e].exec->backend()); !r) return set_error(r.error());
+
+    // the plan of the WHOLE problem gives the shapes and the work; each rank runs its shard of it
+    const kh::KernelPlan plan = kh::find_kernel(name).plan(map, ranks[0].exec->limits());
+    int64_t m = 0, n = 0, k = 0, slices = 0, seq = 0;
+    if (name == "gemm") {
+      m = map.at("m"), n = map.at("n"), k = map.at("k");
+      if (m % (256 * gpus) != 0)
+        return set_error(2, "kh_bench_sharded: gemm rows must split into whole 256-row tiles per GPU (m = " +
+                                std::to_string(m) + ", " + std::to_string(gpus) + " GPUs)");
+    } else {
+      slices = map.at("batch") * map.at("heads"), seq = map.at("seq");
+      if (slices % gpus != 0)
+        return set_error(2, "kh_bench_sharded: batch * heads must be a multiple of the GPU count");
+    }
+    const auto filled = [&](Rank &r, int64_t elements) -> kh::Result<void *> {
+      auto b = kh::Buffer::allocate(r.exec->backend_ptr(), static_cast<size_t>(elements) * 4);
+      if (!b) return std::unexpected(b.error());
+      // 0x3c003c00 is the fp32 value 0.0078..., finite and harmless for every kernel
+      if (auto w = r.exec->backend().memset32_async(b->data(), 0x3c003c00u, static_cast<size_t>(elements), nullptr); !w)
+        return std::unexpected(w.error());
+      void *p = b->data();
+      r.owned.push_back(std::move(*b));
+      return p;
+    };
+    for (Rank &r : ranks) {
+      if (auto c = r.exec->backend().make_current(); !c) return set_error(c.error());
+      const std::vector<int64_t> inputs = name == "gemm" ? std::vector<int64_t>{m / gpus * k, k * n}
+                                                         : std::vector<int64_t>(3, slices / gpus * seq * 64);
+      for (int64_t elements : inputs) {
+        auto p = filled(r, elements);
+        if (!p) return set_error(p.error());
+        r.in.push_back(*p);
+      }
+      auto o = filled(r, name == "gemm" ? m * n : slices * seq * 64);
+      if (!o) return set_error(o.error());
+      r.out = *o;
+      for (kh::EventHandle *e : {&r.start, &r.stop}) {
+        auto made = r.exec->backend().event_create();
+        if (!made) return set_error(made.error());
+        *e = *made;
+      }
+      if (auto done = r.exec->backend().device_synchronize(); !done) return set_error(done.error());
+    }
+    std::vector<void *> replicas;
+    for (Rank &r : ranks) replicas.push_back(r.out);
+
+    // One step: every rank's launch is enqueued (they run concurrently, each storing its tiles into
+    // every replica with plain peer stores), then the host waits for all of them: the barrier after
+    // which every replica holds the whole output. The step's time is the slowest rank's, by events.
+    std::vector<double> times;
+    for (int it = 0; it < warmup + iters; ++it) {
+      for (int d = 0; d < gpus; ++d) {
+        Rank &r = ranks[d];
+        kh::Backend &be = r.exec->backend();
+        if (auto c = be.make_current(); !c) return set_error(c.error());
+        if (auto e = be.event_record(r.start, nullptr); !e) return set_error(e.error());
+        kh::Result<void> launched =
+            name == "gemm" ? kh::run_gemm_allgather(*r.exec, r.in[0], r.in[1], replicas, nullptr, d, gpus, m / gpus, n, k, nullptr)
+                           : kh::run_attention_allgather(*r.exec, r.in[0], r.in[1], r.in[2], replicas, nullptr, d, gpus,
+                                                         slices / gpus, seq, nullptr);
+        if (!launched) return set_error(launched.error());
+        if (auto e = be.event_record(r.stop, nullptr); !e) return set_error(e.error());
+      }
+      double slowest = 0.0;
+      for (Rank &r : ranks) {
+        if (auto c = r.exec->backend().make_current(); !c) return set_error(c.error());
+        if (auto done = r.exec->synchronize(nullptr); !done) return set_error(done.error());
+        auto ms = r.exec->backend().event_elapsed_time(r.start, r.stop);
+        if (!ms) return set_error(ms.error());
+        slowest = std::max(slowest, static_cast<double>(*ms));
+      }
+      if (it >= warmup) times.push_back(slowest);
+    }
+    for (Rank &r : ranks) {
+      (void)r.exec->backend().make_current();
+      (void)r.exec->backend().event_destroy(r.start);
+      (void)r.exec->backend().event_destroy(r.stop);
+    }
+    std::sort(times.begin(), times.end());
+    const double median = times.size() % 2 ? times[times.size() / 2]
+                                           : 0.5 * (times[times.size() / 2 - 1] + times[times.size() / 2]);
+    if (ms_median) *ms_median = median;
+    if (rate) *rate = kh::bench::gflops_from_ms(plan.work, median);
+    if (rate_is_gflops) *rate_is_gflops = 1;
     return 0;
   });
 }

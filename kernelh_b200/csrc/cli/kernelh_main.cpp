@@ -10,7 +10,7 @@
 //   kernelh run     --kernel K --shape S [--target nvptx-sm_100a] [--seed N] [--dump FILE]
 //       fills the inputs deterministically, launches once, prints a digest of
 //       every output (new verb; the reference has none).
-//   kernelh bench   --kernel K --shape S [--warmup W] [--iters N] [--out DIR]
+//   kernelh bench   --kernel K --shape S [--warmup W] [--iters N] [--gpus G] [--out DIR]
 //   kernelh bench   --suite kernelh [--out DIR] [--peak-gbs G --peak-tflops T]
 //       warm-up + median of event-timed launches, one results.csv row per kernel; with the
 //       measured peaks also DIR/results_b200.csv, whose rows append gpus, roofline_frac,
@@ -78,7 +78,7 @@ int usage(const char *why) {
   std::fprintf(stderr,
                "usage: kernelh <compile|run|bench> --kernel <name> --shape k=v,k=v [--target nvptx-sm_100a]\n"
                "       compile: --out <dir>      run: [--seed N] [--dump <file>]\n"
-               "       bench:   [--warmup W] [--iters N] [--out <dir>] | --suite kernelh | --occupancy\n");
+               "       bench:   [--warmup W] [--iters N] [--gpus G] [--out <dir>] | --suite kernelh | --occupancy\n");
   return kExitUsage;
 }
 
@@ -334,6 +334,8 @@ int cmd_bench(const Flags &f) {
   if (!check_target(f, false, token)) return kExitFail;
   const int warmup = std::atoi(f.get("--warmup", "5").c_str());
   const int iters = std::atoi(f.get("--iters", "20").c_str());
+  const int gpus = std::atoi(f.get("--gpus", "1").c_str());
+  if (gpus < 1 || gpus > 8) return usage("--gpus must be between 1 and 8");
   kh_context *ctx = nullptr;
   if (int rc = open_context(&ctx)) return rc;
   kh_device_info info;
@@ -350,22 +352,51 @@ int cmd_bench(const Flags &f) {
   kh_csv_header_ext(line, sizeof line);
   csv_ext = std::string(line) + "\n";
   int failures = 0;
+  // --gpus N (2..8): gemm and attention rows are partitioned over the GPUs (kh_bench_sharded); the
+  // other kernels are not partitioned anywhere, so their rows run as N independent replicas, one
+  // per GPU, and report the sum of the rates beside the slowest replica's time.
+  std::vector<kh_context *> replicas;
+  for (int d = 1; d < gpus; ++d) {
+    kh_context *c = nullptr;
+    if (int rc = kh_context_create(d, &c)) {
+      std::fprintf(stderr, "kernelh: GPU %d of %d: %s\n", d, gpus, kh_last_error());
+      for (kh_context *r : replicas) kh_context_destroy(r);
+      kh_context_destroy(ctx);
+      return rc == 77 ? 77 : kExitFail;
+    }
+    replicas.push_back(c);
+  }
   for (const Row &r : rows) {
     double ms = 0, rate = 0;
     int is_gflops = 0;
-    if (kh_bench_row(ctx, r.kernel.c_str(), r.shape.c_str(), warmup, iters, &ms, &rate, &is_gflops) != 0) {
+    const bool partitioned = gpus > 1 && (r.kernel == "gemm" || r.kernel == "attention");
+    int rc = 0;
+    if (partitioned) {
+      rc = kh_bench_sharded(gpus, r.kernel.c_str(), r.shape.c_str(), warmup, iters, &ms, &rate, &is_gflops);
+    } else {
+      rc = kh_bench_row(ctx, r.kernel.c_str(), r.shape.c_str(), warmup, iters, &ms, &rate, &is_gflops);
+      for (kh_context *c : replicas) {
+        double ms_r = 0, rate_r = 0;
+        if (rc == 0) rc = kh_bench_row(c, r.kernel.c_str(), r.shape.c_str(), warmup, iters, &ms_r, &rate_r, &is_gflops);
+        ms = std::max(ms, ms_r);
+        rate += rate_r;
+      }
+    }
+    if (rc != 0) {
       std::fprintf(stderr, "kernelh: bench %s [%s] failed: %s\n", r.kernel.c_str(), r.shape.c_str(), kh_last_error());
       ++failures;
       continue;
     }
-    std::printf("bench: kernelh %s [%s] ms_median=%.6f rate=%.3f %s\n", r.kernel.c_str(), r.shape.c_str(), ms,
-                rate, is_gflops ? "GFLOPS" : "GB/s");
+    std::printf("bench: kernelh %s [%s] ms_median=%.6f rate=%.3f %s%s\n", r.kernel.c_str(), r.shape.c_str(), ms,
+                rate, is_gflops ? "GFLOPS" : "GB/s",
+                gpus == 1 ? "" : (partitioned ? (" gpus=" + std::to_string(gpus) + " partitioned").c_str()
+                                              : (" gpus=" + std::to_string(gpus) + " replicas").c_str()));
     kh_csv_line(r.kernel.c_str(), r.shape.c_str(), "kernelh", ms, rate, timestamp_utc().c_str(), info.name, line,
                 sizeof line);
     csv += std::string(line) + "\n";
     const double peak = is_gflops ? peak_gflops : peak_gbs;
-    kh_csv_line_ext(r.kernel.c_str(), r.shape.c_str(), "kernelh", ms, rate, timestamp_utc().c_str(), info.name, 1,
-                    peak > 0 ? rate / peak : 0.0, -1.0, -1.0, 0, line, sizeof line);
+    kh_csv_line_ext(r.kernel.c_str(), r.shape.c_str(), "kernelh", ms, rate, timestamp_utc().c_str(), info.name, gpus,
+                    peak > 0 ? rate / (peak * gpus) : 0.0, -1.0, -1.0, 0, line, sizeof line);
     csv_ext += std::string(line) + "\n";
   }
   if (f.has("--out")) {
@@ -381,6 +412,7 @@ int cmd_bench(const Flags &f) {
       std::printf("wrote %s\n", epath.c_str());
     }
   }
+  for (kh_context *c : replicas) kh_context_destroy(c);
   kh_context_destroy(ctx);
   return failures ? kExitFail : kExitOk;
 }

@@ -76,7 +76,6 @@ using khd::split_fp16x2;
 
 constexpr int kBM = 128;     // rows per CTA (256 per pair)
 constexpr int kBN = 256;     // columns per pair
-constexpr int kBNHalf = 128; // columns of B one CTA stages
 constexpr int kBK = 32;      // fp16 elements per k-block: one 64-byte swizzle row
 constexpr int kStages = 6;
 constexpr int kTileBytes = kBM * kBK * 2;   // 8 KiB: A_hi, A_lo, B_hi half, B_lo half
@@ -423,6 +422,7 @@ struct TileCoord {
   int m0, n0;
 };
 
+template <int BN>
 __device__ __forceinline__ TileCoord tile_coord(int64_t tile, int64_t tiles_m, int64_t tiles_n) {
   const int64_t per_group = kGroupM * tiles_n;
   const int64_t group = tile / per_group;
@@ -431,7 +431,7 @@ __device__ __forceinline__ TileCoord tile_coord(int64_t tile, int64_t tiles_m, i
   const int64_t in_group = tile - group * per_group;
   const int64_t tile_m = first_m + in_group % rows_in_group;
   const int64_t tile_n = in_group / rows_in_group;
-  return {static_cast<int>(tile_m * 2 * kBM), static_cast<int>(tile_n * kBN)};
+  return {static_cast<int>(tile_m * 2 * kBM), static_cast<int>(tile_n * BN)};
 }
 
 __device__ __forceinline__ uint32_t cluster_ctarank() {
@@ -656,15 +656,19 @@ namespace {
 
 struct PendingPush {
   int m0, n0;
-  int next_unit; // 0..32; 32 = done
+  int next_unit; // 0 .. units per warp; the last value = done
 };
 
+// A unit is 512 contiguous bytes (128 columns of one row) sent by one warp instruction; an epilogue
+// warp owns 16 rows of its CTA's 128 x BN part of the tile: 16 * BN / 128 units.
+template <int BN>
 __device__ __forceinline__ void push_units(const GatherTargets &t, PendingPush &p, int how_many, int ew,
                                            int lane, int64_t m, int64_t n) {
+  constexpr int kPerRow = BN / 128, kUnits = 16 * kPerRow;
   const float *local = t.base[t.self];
-  for (int i = 0; i < how_many && p.next_unit < 32; ++i, ++p.next_unit) {
-    const int64_t row = static_cast<int64_t>(p.m0) + 16 * ew + (p.next_unit >> 1);
-    const int64_t col = static_cast<int64_t>(p.n0) + (p.next_unit & 1) * 128 + lane * 4;
+  for (int i = 0; i < how_many && p.next_unit < kUnits; ++i, ++p.next_unit) {
+    const int64_t row = static_cast<int64_t>(p.m0) + 16 * ew + (p.next_unit / kPerRow);
+    const int64_t col = static_cast<int64_t>(p.n0) + (p.next_unit % kPerRow) * 128 + lane * 4;
     if (row >= m || col >= n) continue;
     const int64_t off = (t.row_offset + row) * n + col;
     if ((n & 3) == 0) {
@@ -689,7 +693,9 @@ __device__ __forceinline__ void push_units(const GatherTargets &t, PendingPush &
   }
 }
 
-template <bool kGather>
+// BN: columns of C per cluster tile, 256 or 128 (the host takes 128 where that fills the last
+// wave of tiles better; the stage layout keeps its 8 KiB slots, a B half-tile then fills half of its two).
+template <bool kGather, int BN>
 __device__ __forceinline__ void gemm_body(int64_t m, int64_t n, float *__restrict__ c, int64_t c_stride0,
                                                int64_t c_stride1, const khd::TensorMap &tm_a_hi,
                                                const khd::TensorMap &tm_a_lo, const khd::TensorMap &tm_b_hi,
@@ -713,7 +719,7 @@ __device__ __forceinline__ void gemm_body(int64_t m, int64_t n, float *__restric
   const uint32_t acc_empty0 = khd::smem_u32(&bars[2 * kStages + 2]);
   const uint32_t tile_stored = khd::smem_u32(&bars[2 * kStages + 4]);
 
-  const int64_t tiles_m = (m + 2 * kBM - 1) / (2 * kBM), tiles_n = (n + kBN - 1) / kBN;
+  const int64_t tiles_m = (m + 2 * kBM - 1) / (2 * kBM), tiles_n = (n + BN - 1) / BN;
   const int64_t num_tiles = tiles_m * tiles_n;
   const int64_t num_chunks = (k_blocks + kChunkBlocks - 1) / kChunkBlocks;
   const int64_t first_tile = blockIdx.x >> 1, tile_step = gridDim.x >> 1;
@@ -752,9 +758,9 @@ __device__ __forceinline__ void gemm_body(int64_t m, int64_t n, float *__restric
       uint32_t g_kb = 0;
       bool ok = true;
       for (int64_t tile = first_tile; tile < num_tiles && ok; tile += tile_step) {
-        const TileCoord tc = tile_coord(tile, tiles_m, tiles_n);
+        const TileCoord tc = tile_coord<BN>(tile, tiles_m, tiles_n);
         const int a_row = tc.m0 + static_cast<int>(rank) * kBM;
-        const int b_row = tc.n0 + static_cast<int>(rank) * kBNHalf;
+        const int b_row = tc.n0 + static_cast<int>(rank) * (BN / 2);
         for (int64_t kb = 0; kb < k_blocks; ++kb, ++g_kb) {
           const int s = static_cast<int>(g_kb % kStages);
           const uint32_t phase = (g_kb / kStages) & 1u;
@@ -762,7 +768,7 @@ __device__ __forceinline__ void gemm_body(int64_t m, int64_t n, float *__restric
                               khd::kStatusEmptyWaitTimeout, g_kb);
           if (!ok) break;
           const uint32_t stage = ring + s * kStageBytes;
-          if (leader_cta) khd::mbar_arrive_expect_tx(full0 + 8 * s, 2 * kStageBytes);
+          if (leader_cta) khd::mbar_arrive_expect_tx(full0 + 8 * s, 2 * (2 * kTileBytes + 2 * (BN / 2) * kBK * 2));
           const uint32_t bar = map_to_cta(full0 + 8 * s, 0);
           const int kx = static_cast<int>(kb * kBK);
           tma_load_2d_pair(stage, &tm_a_hi, kx, a_row, bar);
@@ -776,7 +782,7 @@ __device__ __forceinline__ void gemm_body(int64_t m, int64_t n, float *__restric
     // ---- MMA issuer: the leader CTA only. One instruction drives both tensor cores. ----
     if (leader_cta) {
       const bool elected = khd::elect_one();
-      constexpr uint32_t idesc = khd::umma_idesc_f16(2 * kBM, kBN);
+      constexpr uint32_t idesc = khd::umma_idesc_f16(2 * kBM, BN);
       uint32_t g_kb = 0, g_chunk = 0;
       bool ok = true;
       for (int64_t tile = first_tile; tile < num_tiles && ok; tile += tile_step) {
@@ -795,7 +801,7 @@ __device__ __forceinline__ void gemm_body(int64_t m, int64_t n, float *__restric
           ok = __all_sync(0xffffffffu, ok);
           if (!ok) break;
           khd::tc_fence_after_sync();
-          const uint32_t d = tmem_base + static_cast<uint32_t>(buf * kBN);
+          const uint32_t d = tmem_base + static_cast<uint32_t>(buf * BN);
           const uint32_t stage = ring + s * kStageBytes;
           const uint64_t a_hi = khd::umma_desc_k64(stage);
           const uint64_t a_lo = a_hi + (kTileBytes >> 4);
@@ -831,23 +837,24 @@ __device__ __forceinline__ void gemm_body(int64_t m, int64_t n, float *__restric
     const int half = ew >> 2;
     const uint32_t lane_base = static_cast<uint32_t>(quad * 32) << 16;
     uint32_t g_chunk = 0, stored_phase = 0;
-    PendingPush pending{0, 0, 32};
+    constexpr int kPushUnits = 16 * BN / 128; // per epilogue warp and tile
+    PendingPush pending{0, 0, kPushUnits};
     bool ok = true;
     for (int64_t tile = first_tile; tile < num_tiles && ok; tile += tile_step) {
-      const TileCoord tc = tile_coord(tile, tiles_m, tiles_n);
+      const TileCoord tc = tile_coord<BN>(tile, tiles_m, tiles_n);
       const int m0 = tc.m0 + static_cast<int>(rank) * kBM;
-      float acc[kBN / 2];
+      float acc[BN / 2];
 #pragma unroll
-      for (int i = 0; i < kBN / 2; ++i) acc[i] = 0.f;
+      for (int i = 0; i < BN / 2; ++i) acc[i] = 0.f;
       for (int64_t chunk = 0; chunk < num_chunks && ok; ++chunk, ++g_chunk) {
         const int buf = static_cast<int>(g_chunk & 1u);
         ok = khd::mbar_wait(acc_full0 + 8 * buf, (g_chunk >> 1) & 1u, &s_abort, status,
                             khd::kStatusMmaWaitTimeout, g_chunk);
         if (!ok) break;
         khd::tc_fence_after_sync();
-        const uint32_t src = tmem_base + lane_base + static_cast<uint32_t>(buf * kBN + half * (kBN / 2));
+        const uint32_t src = tmem_base + lane_base + static_cast<uint32_t>(buf * BN + half * (BN / 2));
 #pragma unroll
-        for (int piece = 0; piece < kBN / 2 / 32; ++piece) {
+        for (int piece = 0; piece < BN / 2 / 32; ++piece) {
           uint32_t r[32];
           khd::tmem_ld_32x32(src + piece * 32, r);
           khd::tmem_ld_wait();
@@ -857,13 +864,13 @@ __device__ __forceinline__ void gemm_body(int64_t m, int64_t n, float *__restric
         khd::tc_fence_before_sync();
         __syncwarp();
         if (lane == 0) mbar_arrive_cluster(map_to_cta(acc_empty0 + 8 * buf, 0));
-        if (kGather) push_units(*targets, pending, 1, ew, lane, m, n);
+        if (kGather) push_units<BN>(*targets, pending, 1, ew, lane, m, n);
       }
       if (!ok) break;
-      if (kGather) push_units(*targets, pending, 32, ew, lane, m, n);
+      if (kGather) push_units<BN>(*targets, pending, kPushUnits, ew, lane, m, n);
 
       const int64_t row = static_cast<int64_t>(m0) + quad * 32 + lane;
-      const int64_t col0 = static_cast<int64_t>(tc.n0) + half * (kBN / 2);
+      const int64_t col0 = static_cast<int64_t>(tc.n0) + half * (BN / 2);
       float *crow;
       int64_t cs1;
       bool vec_ok;
@@ -881,9 +888,9 @@ __device__ __forceinline__ void gemm_body(int64_t m, int64_t n, float *__restric
         // and store, four columns at a time. The loads and stores are ordered
         // (volatile asm) so that only one group of exponents is live at once.
         const int row_shift = __ldg(a_shift + row);
-        if (vec_ok && col0 + kBN / 2 <= n) {
+        if (vec_ok && col0 + BN / 2 <= n) {
 #pragma unroll
-          for (int j = 0; j < kBN / 2 / 4; ++j) {
+          for (int j = 0; j < BN / 2 / 4; ++j) {
             const int4 sh = load_shift4(b_shift + col0 + 4 * j);
             const float x = scale_pow2(acc[4 * j], -(row_shift + sh.x));
             const float y = scale_pow2(acc[4 * j + 1], -(row_shift + sh.y));
@@ -893,7 +900,7 @@ __device__ __forceinline__ void gemm_body(int64_t m, int64_t n, float *__restric
           }
         } else {
 #pragma unroll
-          for (int j = 0; j < kBN / 2; ++j)
+          for (int j = 0; j < BN / 2; ++j)
             if (col0 + j < n) {
               const float x = scale_pow2(acc[j], -(row_shift + load_shift(b_shift + col0 + j)));
               store_float(crow + (col0 + j) * cs1, x);
@@ -909,7 +916,7 @@ __device__ __forceinline__ void gemm_body(int64_t m, int64_t n, float *__restric
         pending = PendingPush{m0, tc.n0, 0};
       }
     }
-    if (kGather && ok) push_units(*targets, pending, 32, ew, lane, m, n);
+    if (kGather && ok) push_units<BN>(*targets, pending, kPushUnits, ew, lane, m, n);
   }
 
   __syncthreads();
@@ -934,8 +941,22 @@ gemm(KH_MEMREF2(const float, a), KH_MEMREF2(const float, b), KH_MEMREF2(float, c
   (void)a_alloc; (void)a_ptr; (void)a_off; (void)a_size1; (void)a_stride0; (void)a_stride1;
   (void)b_alloc; (void)b_ptr; (void)b_off; (void)b_size0; (void)b_stride0; (void)b_stride1;
   (void)c_alloc; (void)c_size0; (void)c_size1;
-  gemm_body<false>(a_size0, b_size1, KH_DATA(c), c_stride0, c_stride1, tm_a_hi, tm_a_lo, tm_b_hi, tm_b_lo,
-                   k_blocks, status, a_shift, b_shift, nullptr);
+  gemm_body<false, kBN>(a_size0, b_size1, KH_DATA(c), c_stride0, c_stride1, tm_a_hi, tm_a_lo, tm_b_hi, tm_b_lo,
+                        k_blocks, status, a_shift, b_shift, nullptr);
+}
+
+// The same with 256 x 128 tiles (the tensor maps of B then have boxes of 64 rows): taken by the
+// host when twice as many, half as wide tiles leave less of the last wave of clusters idle.
+extern "C" __global__ void __launch_bounds__(kThreads, 1)
+gemm_n128(KH_MEMREF2(const float, a), KH_MEMREF2(const float, b), KH_MEMREF2(float, c),
+          const __grid_constant__ khd::TensorMap tm_a_hi, const __grid_constant__ khd::TensorMap tm_a_lo,
+          const __grid_constant__ khd::TensorMap tm_b_hi, const __grid_constant__ khd::TensorMap tm_b_lo,
+          int64_t k_blocks, uint32_t *status, const int *a_shift, const int *b_shift) {
+  (void)a_alloc; (void)a_ptr; (void)a_off; (void)a_size1; (void)a_stride0; (void)a_stride1;
+  (void)b_alloc; (void)b_ptr; (void)b_off; (void)b_size0; (void)b_stride0; (void)b_stride1;
+  (void)c_alloc; (void)c_size0; (void)c_size1;
+  gemm_body<false, 128>(a_size0, b_size1, KH_DATA(c), c_stride0, c_stride1, tm_a_hi, tm_a_lo, tm_b_hi, tm_b_lo,
+                        k_blocks, status, a_shift, b_shift, nullptr);
 }
 
 // The M-row-sharded product with the all-gather fused into the epilogue: `a`
@@ -952,8 +973,21 @@ gemm_allgather(KH_MEMREF2(const float, a), KH_MEMREF2(const float, b),
                const __grid_constant__ GatherTargets targets) {
   (void)a_alloc; (void)a_ptr; (void)a_off; (void)a_size1; (void)a_stride0; (void)a_stride1;
   (void)b_alloc; (void)b_ptr; (void)b_off; (void)b_size0; (void)b_stride0; (void)b_stride1;
-  gemm_body<true>(a_size0, b_size1, nullptr, 0, 0, tm_a_hi, tm_a_lo, tm_b_hi, tm_b_lo, k_blocks, status,
-                  a_shift, b_shift, &targets);
+  gemm_body<true, kBN>(a_size0, b_size1, nullptr, 0, 0, tm_a_hi, tm_a_lo, tm_b_hi, tm_b_lo, k_blocks, status,
+                       a_shift, b_shift, &targets);
+}
+
+// gemm_allgather with 256 x 128 tiles (see gemm_n128).
+extern "C" __global__ void __launch_bounds__(kThreads, 1)
+gemm_allgather_n128(KH_MEMREF2(const float, a), KH_MEMREF2(const float, b),
+                    const __grid_constant__ khd::TensorMap tm_a_hi, const __grid_constant__ khd::TensorMap tm_a_lo,
+                    const __grid_constant__ khd::TensorMap tm_b_hi, const __grid_constant__ khd::TensorMap tm_b_lo,
+                    int64_t k_blocks, uint32_t *status, const int *a_shift, const int *b_shift,
+                    const __grid_constant__ GatherTargets targets) {
+  (void)a_alloc; (void)a_ptr; (void)a_off; (void)a_size1; (void)a_stride0; (void)a_stride1;
+  (void)b_alloc; (void)b_ptr; (void)b_off; (void)b_size0; (void)b_stride0; (void)b_stride1;
+  gemm_body<true, 128>(a_size0, b_size1, nullptr, 0, 0, tm_a_hi, tm_a_lo, tm_b_hi, tm_b_lo, k_blocks, status,
+                       a_shift, b_shift, &targets);
 }
 
 // Sends a run of floats of this GPU's copy of a replicated buffer to the same place in every

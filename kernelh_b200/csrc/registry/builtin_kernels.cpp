@@ -334,12 +334,26 @@ std::vector<LaunchStep> gemm_steps(int64_t m, int64_t n, int64_t k, const Device
   sb.grid = {balanced_grid(((n + 127) / 128) * ((kp + 63) / 64), sms, 6), 1, 1}; // 64 x 128 tiles
   sb.param_count = 7 + 5;
   LaunchStep g;
-  g.entry = "gemm";
   g.block = {320, 1, 1};
   g.cluster = 2;
-  const int64_t tiles = ((m + 2 * kGemmBM - 1) / (2 * kGemmBM)) * ((n + kGemmBN - 1) / kGemmBN);
-  // persistent: one cluster per pair of SMs
-  g.grid = {static_cast<unsigned>(2 * std::min<int64_t>(tiles, std::max<long>(sms / 2, 1))), 1, 1};
+  // persistent: one cluster per pair of SMs walks the 256 x BN tiles of C. BN = 256 unless the
+  // product is so small that wide tiles leave at least half of the clusters without any tile
+  // (1000^3: 16 wide tiles on 74 clusters, 32 narrow ones). A narrow tile takes 0.74 of a wide
+  // tile's time, not half (measured at 8192^3: 2.74 ms against 1.86 on constant data: the issue
+  // rate of one MMA thread and the A traffic per flop), so it never pays for filling the last wave
+  // of a large product. KERNELH_GEMM_TILE_N = 128 / 256 forces one (for measurements).
+  const int64_t clusters = std::max<long>(sms / 2, 1);
+  const int64_t tiles_m = (m + 2 * kGemmBM - 1) / (2 * kGemmBM);
+  const int64_t tiles256 = tiles_m * ((n + 255) / 256), tiles128 = tiles_m * ((n + 127) / 128);
+  const int64_t cost256 = 4 * ((tiles256 + clusters - 1) / clusters), cost128 = 3 * ((tiles128 + clusters - 1) / clusters);
+  bool narrow = cost128 < cost256;
+  if (const char *forced = std::getenv("KERNELH_GEMM_TILE_N")) {
+    if (std::strcmp(forced, "128") == 0) narrow = true;
+    if (std::strcmp(forced, "256") == 0) narrow = false;
+  }
+  g.entry = narrow ? "gemm_n128" : "gemm";
+  const int64_t tiles = narrow ? tiles128 : tiles256;
+  g.grid = {static_cast<unsigned>(2 * std::min<int64_t>(tiles, clusters)), 1, 1};
   g.dynamic_smem = kGemmStages * kGemmStageBytes + 1024;
   g.param_count = 21 + 4 + 2 + 2;
   g.tmem_columns = 512;
@@ -379,12 +393,12 @@ struct GemmJob {
   int64_t m, n, k, kp;
   GemmScratch lay;
   char *base = nullptr; // scratch
-  KernelFunction split_a, colmax_b, split_bt, prep_b, multiply, multiply_gather;
+  KernelFunction split_a, colmax_b, split_bt, prep_b, multiply, multiply_gather, multiply_n128, multiply_gather_n128;
   uint64_t at(size_t off) const { return reinterpret_cast<uint64_t>(base + off); }
 };
 
 Result<GemmJob> gemm_job(Executor &ex, int64_t m, int64_t n, int64_t k) {
-  GemmJob j{ex, m, n, k, (k + kGemmBK - 1) / kGemmBK * kGemmBK, {}, nullptr, {}, {}, {}, {}, {}, {}};
+  GemmJob j{ex, m, n, k, (k + kGemmBK - 1) / kGemmBK * kGemmBK, {}, nullptr, {}, {}, {}, {}, {}, {}, {}, {}};
   j.lay = gemm_scratch(m, n, j.kp);
   auto ws = ex.workspace(j.lay.total);
   if (!ws) return std::unexpected(ws.error());
@@ -394,7 +408,9 @@ Result<GemmJob> gemm_job(Executor &ex, int64_t m, int64_t n, int64_t k) {
                                                                {"gemm_split_bt", &j.split_bt},
                                                                {"gemm_prep_b", &j.prep_b},
                                                                {"gemm", &j.multiply},
-                                                               {"gemm_allgather", &j.multiply_gather}};
+                                                               {"gemm_allgather", &j.multiply_gather},
+                                                               {"gemm_n128", &j.multiply_n128},
+                                                               {"gemm_allgather_n128", &j.multiply_gather_n128}};
   for (const auto &[name, slot] : entries) {
     auto f = ex.function("gemm", name);
     if (!f) return std::unexpected(f.error());
@@ -489,7 +505,8 @@ Result<void> gemm_enqueue_a(const GemmJob &j, const void *a_rows, int64_t row0, 
 Result<void> gemm_enqueue_multiply(const GemmJob &j, const void *a_rows, const void *b_dev, void *c_rows,
                                    int64_t row0, int64_t rows, LaunchStep step, StreamHandle stream,
                                    const GatherTargets *gather) {
-  auto make_map = [&](size_t offset, int64_t map_rows) {
+  const bool narrow = step.entry == "gemm_n128"; // 256 x 128 tiles: a CTA stages 64 columns of B per k-block
+  auto make_map = [&](size_t offset, int64_t map_rows, uint32_t box_rows = kGemmBM) {
     TensorMapSpec s;
     s.global_address = j.base + offset;
     s.rank = 2;
@@ -498,7 +515,7 @@ Result<void> gemm_enqueue_multiply(const GemmJob &j, const void *a_rows, const v
     s.dims[1] = static_cast<uint64_t>(map_rows);
     s.strides_bytes[0] = static_cast<uint64_t>(j.kp) * 2;
     s.box[0] = kGemmBK;
-    s.box[1] = kGemmBM; // 128 rows of A, or 128 of the tile's 256 columns of B
+    s.box[1] = box_rows; // 128 rows of A, or this CTA's half of the tile's columns of B
     s.swizzle_bytes = 64;
     return j.ex.backend().encode_tensor_map(s);
   };
@@ -507,9 +524,9 @@ Result<void> gemm_enqueue_multiply(const GemmJob &j, const void *a_rows, const v
   if (!t_ah) return std::unexpected(t_ah.error());
   auto t_al = make_map(j.lay.a_lo + a_off, rows);
   if (!t_al) return std::unexpected(t_al.error());
-  auto t_bh = make_map(j.lay.b_hi, j.n);
+  auto t_bh = make_map(j.lay.b_hi, j.n, narrow ? 64u : 128u);
   if (!t_bh) return std::unexpected(t_bh.error());
-  auto t_bl = make_map(j.lay.b_lo, j.n);
+  auto t_bl = make_map(j.lay.b_lo, j.n, narrow ? 64u : 128u);
   if (!t_bl) return std::unexpected(t_bl.error());
 
   LaunchArgs args;
@@ -526,9 +543,11 @@ Result<void> gemm_enqueue_multiply(const GemmJob &j, const void *a_rows, const v
   args.add_scalar<uint64_t>(j.at(j.lay.b_shift));
   if (gather) {
     args.add_struct_bytes(gather, sizeof *gather);
-    step.entry = "gemm_allgather";
+    step.entry = narrow ? "gemm_allgather_n128" : "gemm_allgather";
   }
-  return j.ex.launch(gather ? j.multiply_gather : j.multiply, step, args, stream);
+  const KernelFunction &fn = gather ? (narrow ? j.multiply_gather_n128 : j.multiply_gather)
+                                    : (narrow ? j.multiply_n128 : j.multiply);
+  return j.ex.launch(fn, step, args, stream);
 }
 
 Result<void> launch_gemm(Executor &ex, const KernelPlan &p, const std::vector<void *> &b,

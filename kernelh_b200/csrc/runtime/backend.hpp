@@ -73,6 +73,12 @@ public:
   virtual Result<int> device_count() = 0;
   virtual Result<void> init_device(int ordinal) = 0;
   virtual Result<void> make_current() = 0;
+  // The driver's context handle (opaque here), and peer mapping between two devices of one process.
+  virtual void *native_context() { return nullptr; }
+  virtual Result<void> enable_peer_access(Backend &peer) {
+    (void)peer;
+    return fail(1, "this backend has no peer access");
+  }
   virtual Result<DeviceInfo> device_info() = 0;
   virtual Result<void> device_synchronize() = 0;
 

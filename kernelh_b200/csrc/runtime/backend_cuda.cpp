@@ -25,6 +25,8 @@ namespace {
   X(PrimaryCtxRetain, "cuDevicePrimaryCtxRetain", CUresult (*)(CUcontext *, CUdevice))             \
   X(CtxSetCurrent, "cuCtxSetCurrent", CUresult (*)(CUcontext))                                     \
   X(CtxSynchronize, "cuCtxSynchronize", CUresult (*)())                                            \
+  X(CtxEnablePeerAccess, "cuCtxEnablePeerAccess", CUresult (*)(CUcontext, unsigned))               \
+  X(DeviceCanAccessPeer, "cuDeviceCanAccessPeer", CUresult (*)(int *, CUdevice, CUdevice))         \
   X(MemAlloc, "cuMemAlloc_v2", CUresult (*)(CUdeviceptr *, size_t))                                \
   X(MemFree, "cuMemFree_v2", CUresult (*)(CUdeviceptr))                                            \
   X(MemHostAlloc, "cuMemHostAlloc", CUresult (*)(void **, size_t, unsigned))                       \
@@ -113,6 +115,30 @@ public:
   Result<void> make_current() override {
     if (ctx_ == nullptr) return fail(1, "CudaBackend: no device initialised");
     if (CUresult r = api_.CtxSetCurrent(ctx_); r != CUDA_SUCCESS) return err(r, "cuCtxSetCurrent");
+    return {};
+  }
+
+  void *native_context() override { return ctx_; }
+
+  // Maps the memory of `peer`'s device into this device's address space (unified addressing:
+  // the peer's pointers are then valid in kernels launched here). Already enabled counts as done.
+  Result<void> enable_peer_access(Backend &peer) override {
+    if (ctx_ == nullptr || peer.native_context() == nullptr)
+      return fail(1, "CudaBackend::enable_peer_access: a device is not initialised");
+    if (&peer == this) return {};
+    auto peer_info = peer.device_info();
+    if (!peer_info) return std::unexpected(peer_info.error());
+    CUdevice other;
+    if (CUresult r = api_.DeviceGet(&other, peer_info->ordinal); r != CUDA_SUCCESS) return err(r, "cuDeviceGet");
+    int can = 0;
+    if (CUresult r = api_.DeviceCanAccessPeer(&can, dev_, other); r != CUDA_SUCCESS)
+      return err(r, "cuDeviceCanAccessPeer");
+    if (!can)
+      return fail(1, "device " + std::to_string(ordinal_) + " cannot map the memory of device " +
+                         std::to_string(peer_info->ordinal) + " (no peer access between them)");
+    if (CUresult r = api_.CtxSetCurrent(ctx_); r != CUDA_SUCCESS) return err(r, "cuCtxSetCurrent");
+    const CUresult r = api_.CtxEnablePeerAccess(static_cast<CUcontext>(peer.native_context()), 0);
+    if (r != CUDA_SUCCESS && r != CUDA_ERROR_PEER_ACCESS_ALREADY_ENABLED) return err(r, "cuCtxEnablePeerAccess");
     return {};
   }
 

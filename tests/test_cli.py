@@ -121,3 +121,27 @@ def test_bench_row_and_results_csv(tmp_path):
     lines = (tmp_path / "results.csv").read_text().splitlines()
     assert lines[0] == "kernel,shape,backend,ms_median,gflops_or_gbps,timestamp,device"
     assert lines[1].startswith('softmax,"rows=4096,cols=1024",kernelh,') and "B200" in lines[1]
+
+
+def test_bench_gpus_flag_is_validated_before_any_device_is_opened():
+    r = cli("bench", "--kernel", "gemm", "--shape", "m=512,n=256,k=64", "--gpus", "9")
+    assert r.returncode == 2 and "--gpus must be between 1 and 8" in r.stderr
+    r = cli("bench", "--kernel", "gemm", "--shape", "m=512,n=256,k=64", "--gpus", "0")
+    assert r.returncode == 2
+
+
+@pytest.mark.gpu
+def test_bench_on_two_gpus_partitions_gemm_and_attention_and_replicates_the_rest():
+    import torch
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    r = cli("bench", "--kernel", "gemm", "--shape", "m=2048,n=1024,k=512", "--gpus", "2", "--warmup", "2", "--iters", "3")
+    assert r.returncode == 0, r.stderr
+    assert re.search(r"bench: kernelh gemm \[m=2048,n=1024,k=512\] ms_median=\S+ rate=\S+ GFLOPS gpus=2 partitioned", r.stdout)
+    r = cli("bench", "--kernel", "attention", "--shape", "batch=2,heads=4,seq=256,head_dim=64", "--gpus", "2",
+            "--warmup", "2", "--iters", "3")
+    assert r.returncode == 0, r.stderr
+    assert "gpus=2 partitioned" in r.stdout
+    r = cli("bench", "--kernel", "vecadd", "--shape", "n=1048576", "--gpus", "2", "--warmup", "2", "--iters", "3")
+    assert r.returncode == 0, r.stderr
+    assert "gpus=2 replicas" in r.stdout

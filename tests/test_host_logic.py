@@ -203,7 +203,12 @@ def test_plans_for_the_benchmark_configurations():
     assert p.work == 1099511627776.0 and p.work_is_flops
     assert kh.verify_launch("sm_100a", p.block[0], tuple(p.grid), 48, p.dynamic_smem) == ""
     p = kh.plan("gemm", "m=1000,n=1000,k=1000")
-    assert p.grid[0] == 2 * 4 * 4  # 16 tiles of 256 x 256, a cluster each
+    # 16 tiles of 256 x 256 would use 16 of the 74 clusters; 32 tiles of 256 x 128 take half the time
+    assert p.entry == b"gemm_n128" and p.grid[0] == 2 * 4 * 8
+    # large products keep the wide tile: a narrow one costs 0.74 of it, more than the last wave it would fill
+    assert kh.plan("gemm", "m=2048,n=8192,k=8192").entry == b"gemm"
+    assert kh.plan("gemm", "m=4096,n=8192,k=8192").entry == b"gemm"
+    assert kh.plan("gemm", "m=1024,n=8192,k=8192").entry == b"gemm"
     # rows of B that are not 16-byte multiples (or strips too tall for eight SMs) keep the two-pass form
     assert kh.plan("gemm", "m=129,n=257,k=33").n_launches == 4
     assert kh.plan("gemm", "m=64,n=64,k=32768").n_launches == 4
@@ -423,3 +428,17 @@ def test_extended_csv_appends_columns_after_the_reference_seven(golden):
     assert ext == row["line"] + ",8,0.75,2.5e-06,12.5,16"
     # not checked / not timed: empty fields, the first seven untouched
     assert kh.csv_line_ext(*row["row"]) == row["line"] + ",1,0,,,0"
+
+
+def test_sharded_bench_row_refusals():
+    """kh_bench_sharded partitions gemm and attention only (the other kernels are replicas),
+    validates the GPU count before touching a device, and answers 77 without a driver."""
+    with pytest.raises(kh.KernelhError) as e:
+        kh.bench_sharded(2, "softmax", "rows=64,cols=64")
+    assert e.value.code == 2 and "only gemm" in e.value.message and "replicas" in e.value.message
+    with pytest.raises(kh.KernelhError) as e:
+        kh.bench_sharded(9, "gemm", "m=512,n=256,k=64")
+    assert e.value.code == 2 and "between 1 and 8" in e.value.message
+    with pytest.raises(kh.KernelhError) as e:
+        kh.bench_sharded(2, "gemm", "")
+    assert e.value.code in (2, 77)
