@@ -518,6 +518,12 @@ def gpu_arm(args) -> None:
     launches = ctx.launch_count() - launches_before
     clocks = sampler.stop() if rank == 0 else None
     ctx.synchronize(stream)
+    if clocks is not None:
+        # the clock the last timed gemm launch really ran at, counted inside the kernel (block 0:
+        # SM cycles against the GPU's nanosecond timer), beside the management library's samples
+        cycles, ns = ctx.gemm_clock()
+        clocks["gemm_in_kernel_sm_mhz"] = round(cycles / ns * 1e3, 1) if ns else None
+        clocks["gemm_in_kernel"] = {"sm_cycles": cycles, "ns": ns}
     t = torch.tensor([ms_total], device="cuda", dtype=torch.float64)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)

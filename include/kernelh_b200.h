@@ -230,6 +230,12 @@ int kh_memcpy_d2h(kh_context *ctx, void *dst, const void *src, size_t bytes);
 int kh_bench_row(kh_context *ctx, const char *kernel, const char *shape, int warmup, int iters,
                  double *ms_median, double *rate, int *rate_is_gflops);
 
+/* The SM clock the last gemm launch of this context really ran at: block 0 of the
+ * kernel counts its SM's cycles against the GPU's nanosecond timer over its whole
+ * life; cycles / nanoseconds * 1000 = MHz under load (the management library's
+ * samples mostly fall into the gaps between kernels). Call after kh_synchronize. */
+int kh_gemm_clock(kh_context *ctx, uint64_t *sm_cycles, uint64_t *nanoseconds);
+
 /* The harness on several GPUs of one box, in ONE process (the reference's harness
  * opens ordinal 0 only, bench/harness/run_bench.cpp:146-153): a context per GPU,
  * every GPU's memory mapped into every other (kh_enable_peer_access: the driver's

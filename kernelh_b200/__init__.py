@@ -107,6 +107,7 @@ def _load() -> C.CDLL:
     L.kh_bench_row.argtypes = [vp, C.c_char_p, C.c_char_p, C.c_int, C.c_int,
                                C.POINTER(C.c_double), C.POINTER(C.c_double), C.POINTER(C.c_int)]
     L.kh_enable_peer_access.argtypes = [vp, vp]
+    L.kh_gemm_clock.argtypes = [vp, C.POINTER(C.c_uint64), C.POINTER(C.c_uint64)]
     L.kh_bench_sharded.argtypes = [C.c_int, C.c_char_p, C.c_char_p, C.c_int, C.c_int,
                                    C.POINTER(C.c_double), C.POINTER(C.c_double), C.POINTER(C.c_int)]
     L.kh_registered_kernels.argtypes = [C.c_char_p, C.c_int]
@@ -239,6 +240,13 @@ class Context:
         _check(lib.kh_bench_row(self._h, kernel.encode(), shape.encode(), warmup, iters,
                                 C.byref(ms), C.byref(rate), C.byref(is_gflops)))
         return ms.value, rate.value, bool(is_gflops.value)
+
+    def gemm_clock(self):
+        """(SM cycles, nanoseconds) block 0 of the last gemm launch counted over its life; call after
+        synchronize. cycles / ns * 1000 is the SM clock in MHz while the tensor cores were busy."""
+        cycles, ns = C.c_uint64(), C.c_uint64()
+        _check(lib.kh_gemm_clock(self._h, C.byref(cycles), C.byref(ns)))
+        return cycles.value, ns.value
 
     def enable_peer_access(self, peer: "Context"):
         """Maps the memory of `peer`'s GPU into this context's GPU (both in this process)."""

@@ -402,6 +402,16 @@ int kh_bench_row(kh_context *ctx, const char *kernel, const char *shape, int war
   });
 }
 
+int kh_gemm_clock(kh_context *ctx, uint64_t *sm_cycles, uint64_t *nanoseconds) {
+  if (int rc = need_ctx(ctx)) return rc;
+  uint64_t record[2] = {0, 0};
+  auto r = ctx->exec->backend().memcpy_d2h(record, reinterpret_cast<char *>(ctx->exec->status_word()) + 32, sizeof record);
+  if (!r) return set_error(r.error());
+  if (sm_cycles) *sm_cycles = record[0];
+  if (nanoseconds) *nanoseconds = record[1];
+  return 0;
+}
+
 int kh_enable_peer_access(kh_context *ctx, kh_context *peer) {
   if (int rc = need_ctx(ctx)) return rc;
   if (int rc = need_ctx(peer)) return rc;

@@ -355,7 +355,7 @@ std::vector<LaunchStep> gemm_steps(int64_t m, int64_t n, int64_t k, const Device
   const int64_t tiles = narrow ? tiles128 : tiles256;
   g.grid = {static_cast<unsigned>(2 * std::min<int64_t>(tiles, clusters)), 1, 1};
   g.dynamic_smem = kGemmStages * kGemmStageBytes + 1024;
-  g.param_count = 21 + 4 + 2 + 2;
+  g.param_count = 21 + 4 + 2 + 2 + 1;
   g.tmem_columns = 512;
   return {sa, cm, sb, g};
 }
@@ -541,6 +541,10 @@ Result<void> gemm_enqueue_multiply(const GemmJob &j, const void *a_rows, const v
   args.add_scalar<uint64_t>(reinterpret_cast<uint64_t>(j.ex.status_word()));
   args.add_scalar<uint64_t>(j.at(j.lay.a_shift + static_cast<size_t>(row0) * 4));
   args.add_scalar<uint64_t>(j.at(j.lay.b_shift));
+  // tile rows per rasterisation group; 0 = the kernel's default. KERNELH_GEMM_RASTER overrides (measurements).
+  int64_t raster = 0;
+  if (const char *forced = std::getenv("KERNELH_GEMM_RASTER")) raster = std::atoll(forced);
+  args.add_scalar<int64_t>(raster);
   if (gather) {
     args.add_struct_bytes(gather, sizeof *gather);
     step.entry = narrow ? "gemm_allgather_n128" : "gemm_allgather";
