@@ -44,6 +44,10 @@ def parse_args():
                          "(symmetric memory; one multimem.st per tile piece through the NVSwitch multicast "
                          "address when there is one, else plain peer stores) and a barrier follows; "
                          "'p2p-st' = the same, forcing plain peer stores; 'nccl' = plain gemm + NCCL all-gather")
+    ap.add_argument("--barrier", default="flags", choices=["flags", "symm"],
+                    help="N > 1 with --gather p2p: 'flags' = the gemm kernel ends with the barrier itself "
+                         "(arrival flags in symmetric memory, written after its last store and awaited by its "
+                         "last CTA); 'symm' = a symmetric-memory barrier launch after the kernel")
     ap.add_argument("--csv", default="", help="N = 1: also write the rows of this run as results CSV with the "
                                               "appended columns (gpus, roofline_frac, max_rel_err, cpu_ms, cpu_cores)")
     ap.add_argument("--no-extras", action="store_true",
@@ -459,6 +463,8 @@ def gpu_arm(args) -> None:
     symm = None
     c = None
     multicast = 0
+    flag_arrays = None
+    epoch = [0]
     if world > 1 and args.gather in ("p2p", "p2p-st"):
         # Every rank's C lives in symmetric memory, so each rank holds an address for
         # every other rank's C and the gemm epilogue can store its tiles into all of them.
@@ -471,6 +477,14 @@ def gpu_arm(args) -> None:
             multicast = int(getattr(symm, "multicast_ptr", 0) or 0) if args.gather == "p2p" else 0
             c.zero_()
             gather = "p2p"
+            if args.barrier == "flags":
+                # eight 64-bit arrival words per rank, zero before the first step
+                flag_words = symm_mem.empty((8,), dtype=torch.int64, device=torch.device("cuda", local_rank))
+                flag_symm = symm_mem.rendezvous(flag_words, dist.group.WORLD.group_name)
+                flag_words.zero_()
+                flag_arrays = [int(p) for p in flag_symm.buffer_ptrs]
+                torch.cuda.synchronize()
+                dist.barrier()
         except Exception as exc:  # no peer mapping on this box: use the collective instead
             if rank == 0:
                 sys.stderr.write(f"bench.py: symmetric memory unavailable ({exc!r}); using NCCL all-gather\n")
@@ -485,13 +499,20 @@ def gpu_arm(args) -> None:
         if world > 1:
             dist.barrier()
 
+    def fused_gather_launch():
+        if flag_arrays is not None:  # every rank counts the same launches, so the epochs agree
+            epoch[0] += 1
+            ctx.arm_arrival_flags(flag_arrays, epoch[0])
+        if multicast:
+            ctx.gemm_allgather_multicast(a_shard, b, c, multicast, world, rank, rows, size, size, stream)
+        else:
+            ctx.gemm_allgather(a_shard, b, replicas, rank, rows, size, size, stream)
+        if flag_arrays is None:
+            symm.barrier()  # all ranks' stores have landed before anyone reads C
+
     def step():
         if gather == "p2p":
-            if multicast:
-                ctx.gemm_allgather_multicast(a_shard, b, c, multicast, world, rank, rows, size, size, stream)
-            else:
-                ctx.gemm_allgather(a_shard, b, replicas, rank, rows, size, size, stream)
-            symm.barrier()  # all ranks' stores have landed before anyone reads C
+            fused_gather_launch()
         else:
             ctx.gemm(a_shard, b, c_shard, rows, size, size, stream)
             if world > 1:
@@ -533,10 +554,8 @@ def gpu_arm(args) -> None:
     # ---- the dominant kernel alone, per-launch, on this rank's stream -------------------
     ctx.profile(True)
     for _ in range(args.steps):
-        if gather == "p2p" and multicast:
-            ctx.gemm_allgather_multicast(a_shard, b, c, multicast, world, rank, rows, size, size, stream)
-        elif gather == "p2p":
-            ctx.gemm_allgather(a_shard, b, replicas, rank, rows, size, size, stream)
+        if gather == "p2p":
+            fused_gather_launch()
         else:
             ctx.gemm(a_shard, b, c_shard, rows, size, size, stream)
     prof = ctx.profile_report()
@@ -624,7 +643,8 @@ def gpu_arm(args) -> None:
                        "NCCL all-gather of C inside the timed step")) if world > 1 else "single GPU",
                    "l2": "inputs (2 x 256 MiB) and the 512 MiB operand-split scratch are larger than the 126 MB L2",
                    "step": "gemm_split_a + gemm_prep_b + " + {"none": "gemm", "nccl": "gemm + nccl all_gather",
-                                                                 "p2p": "gemm_allgather + barrier"}[gather]},
+                                                                 "p2p": "gemm_allgather ending with its own arrival-flag barrier" if flag_arrays is not None
+                                                                 else "gemm_allgather + symmetric-memory barrier"}[gather]},
         "roofline": roofline, "gpu_launches": int(launches),
         "sampled_max_err_over_rms": err, "parity": parity,
     }

@@ -127,6 +127,13 @@ int kh_gemm(kh_context *ctx, const float *a, const float *b, float *c, int64_t m
 int kh_attention(kh_context *ctx, const float *q, const float *k, const float *v, float *o,
                  int64_t batch, int64_t heads, int64_t seq, int64_t head_dim, void *stream);
 
+/* C = alpha * A.B + beta * C, the scaled store that BLAS-style callers expect (the
+ * reference's gemm epilogue is a plain store, lib/dsl/kernels/gemm.cpp:47-53; this is
+ * the first of its generalisations). alpha = 1, beta = 0 is kh_gemm bit for bit;
+ * beta = 0 never reads C, so C may hold anything, NaN included. */
+int kh_gemm_scaled(kh_context *ctx, const float *a, const float *b, float *c, int64_t m, int64_t n, int64_t k,
+                   float alpha, float beta, void *stream);
+
 /* No counterpart in the reference (which is single-GPU). The M-row-sharded gemm
  * for several GPUs of one box with the all-gather of the C shards fused into
  * the kernel's epilogue: `a_shard` is this rank's m_shard x k rows of A, `b`
@@ -229,6 +236,19 @@ int kh_memcpy_d2h(kh_context *ctx, void *dst, const void *src, size_t bytes);
  * allocated by the library and filled with a fixed pattern. */
 int kh_bench_row(kh_context *ctx, const char *kernel, const char *shape, int warmup, int iters,
                  double *ms_median, double *rate, int *rate_is_gflops);
+
+/* The barrier after a fused all-gather, done by the kernel itself. Arms the NEXT
+ * kh_gemm_allgather / kh_gemm_allgather_multicast call of this context (that one
+ * call only): flag_arrays[i] is rank i's array of eight 64-bit words, zero at the
+ * start, in peer-mapped (symmetric) memory as seen from this device. The last CTA
+ * of the launch writes `epoch` into word `rank` of every other rank's array after
+ * a system-wide fence, then waits (two seconds at most; then kh_synchronize gives
+ * 1001 naming the rank that did not arrive) until its own array holds `epoch` or
+ * more in every other word. When the kernel has completed, every rank's rows are
+ * in this rank's C: no separate barrier launch is needed. `epoch` must be positive
+ * and grow from call to call, the same on every rank. Every rank must run on a GPU
+ * of its own: kernels that wait for one another must never share a GPU. */
+int kh_arm_arrival_flags(kh_context *ctx, void *const *flag_arrays, int world, uint64_t epoch);
 
 /* The SM clock the last gemm launch of this context really ran at: block 0 of the
  * kernel counts its SM's cycles against the GPU's nanosecond timer over its whole

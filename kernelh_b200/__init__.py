@@ -107,6 +107,8 @@ def _load() -> C.CDLL:
     L.kh_bench_row.argtypes = [vp, C.c_char_p, C.c_char_p, C.c_int, C.c_int,
                                C.POINTER(C.c_double), C.POINTER(C.c_double), C.POINTER(C.c_int)]
     L.kh_enable_peer_access.argtypes = [vp, vp]
+    L.kh_gemm_scaled.argtypes = [vp, f32p, f32p, f32p, i64, i64, i64, C.c_float, C.c_float, vp]
+    L.kh_arm_arrival_flags.argtypes = [vp, C.POINTER(vp), C.c_int, C.c_uint64]
     L.kh_gemm_clock.argtypes = [vp, C.POINTER(C.c_uint64), C.POINTER(C.c_uint64)]
     L.kh_bench_sharded.argtypes = [C.c_int, C.c_char_p, C.c_char_p, C.c_int, C.c_int,
                                    C.POINTER(C.c_double), C.POINTER(C.c_double), C.POINTER(C.c_int)]
@@ -240,6 +242,17 @@ class Context:
         _check(lib.kh_bench_row(self._h, kernel.encode(), shape.encode(), warmup, iters,
                                 C.byref(ms), C.byref(rate), C.byref(is_gflops)))
         return ms.value, rate.value, bool(is_gflops.value)
+
+    def gemm_scaled(self, a, b, c, m, n, k, alpha, beta, stream=None):
+        """C = alpha * A.B + beta * C (beta = 0 never reads C)."""
+        _check(lib.kh_gemm_scaled(self._h, _ptr(a), _ptr(b), _ptr(c), m, n, k, alpha, beta, stream))
+
+    def arm_arrival_flags(self, flag_arrays, epoch: int):
+        """The next gemm_allgather / gemm_allgather_multicast call of this context ends with the
+        barrier itself: `flag_arrays` are every rank's eight-word int64 arrays (addresses as mapped
+        here, e.g. a symmetric-memory buffer's `buffer_ptrs`), `epoch` a positive, growing number."""
+        arr = (C.c_void_p * len(flag_arrays))(*[C.c_void_p(int(p)) for p in flag_arrays])
+        _check(lib.kh_arm_arrival_flags(self._h, arr, len(flag_arrays), epoch))
 
     def gemm_clock(self):
         """(SM cycles, nanoseconds) block 0 of the last gemm launch counted over its life; call after

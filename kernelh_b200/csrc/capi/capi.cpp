@@ -257,6 +257,16 @@ int kh_gemm(kh_context *ctx, const float *a, const float *b, float *c, int64_t m
   return launch_named(ctx, "gemm", {{"m", m}, {"n", n}, {"k", k}},
                       {const_cast<float *>(a), const_cast<float *>(b), c}, stream);
 }
+int kh_gemm_scaled(kh_context *ctx, const float *a, const float *b, float *c, int64_t m, int64_t n, int64_t k,
+                   float alpha, float beta, void *stream) {
+  if (int rc = need_ctx(ctx)) return rc;
+  if (a == nullptr || b == nullptr || c == nullptr) return set_error(2, "kh_gemm_scaled: null buffer");
+  if (m <= 0 || n <= 0 || k <= 0) return set_error(2, "kh_gemm_scaled: m, n and k must be positive");
+  return guarded([&] {
+    auto r = kh::run_gemm_scaled(*ctx->exec, a, b, c, m, n, k, alpha, beta, stream);
+    return r ? 0 : set_error(r.error());
+  });
+}
 int kh_gemm_allgather(kh_context *ctx, const float *a_shard, const float *b, void *const *c_replicas,
                       int world, int rank, int64_t m_shard, int64_t n, int64_t k, void *stream) {
   if (c_replicas == nullptr || world <= 0) return set_error(2, "kh_gemm_allgather: no C replicas given");
@@ -400,6 +410,15 @@ int kh_bench_row(kh_context *ctx, const char *kernel, const char *shape, int war
     if (rate_is_gflops) *rate_is_gflops = plan.work_is_flops ? 1 : 0;
     return 0;
   });
+}
+
+int kh_arm_arrival_flags(kh_context *ctx, void *const *flag_arrays, int world, uint64_t epoch) {
+  if (int rc = need_ctx(ctx)) return rc;
+  if (flag_arrays == nullptr || world < 2 || world > 8)
+    return set_error(2, "kh_arm_arrival_flags: between 2 and 8 flag arrays are expected");
+  if (epoch == 0) return set_error(2, "kh_arm_arrival_flags: the epoch must be positive (and grow from call to call)");
+  ctx->exec->arm_arrival_flags(std::vector<void *>(flag_arrays, flag_arrays + world), epoch);
+  return 0;
 }
 
 int kh_gemm_clock(kh_context *ctx, uint64_t *sm_cycles, uint64_t *nanoseconds) {

@@ -416,7 +416,43 @@ struct GatherTargets {
   int self;
   int64_t row_offset;
   float *multicast; // NVLink multicast address of the replicas (one store reaches all), or null
+  // Arrival flags (epoch != 0): the barrier that has to follow the all-gather, done by the kernel
+  // itself. flags[d] is rank d's array of eight 64-bit words as mapped on this GPU. The last CTA of
+  // this launch to finish writes `epoch` into word `self` of every other rank's array (after a
+  // system-wide fence, so that every tile this GPU sent is visible before the flag) and then waits,
+  // for at most two seconds, until its own array holds at least `epoch` in every other rank's word:
+  // when the kernel has completed, every rank's rows are in this GPU's replica. Epochs only grow.
+  unsigned long long *flags[8];
+  unsigned long long epoch;
+  unsigned int *finished; // this GPU's count of CTAs that are done; 0 between launches
 };
+
+// Runs once per CTA, by one thread, after the CTA's last store.
+__device__ __forceinline__ void signal_and_await_peers(const GatherTargets &t, uint32_t *status) {
+  __threadfence_system(); // this CTA's stores (peer stores and multimem.st included) before the count
+  if (atomicAdd(t.finished, 1u) != gridDim.x - 1) return;
+  *t.finished = 0; // the next launch on this stream starts from zero again
+  __threadfence_system(); // every CTA's stores before the flags
+  for (int d = 0; d < t.count; ++d)
+    if (d != t.self)
+      asm volatile("st.release.sys.global.u64 [%0], %1;" ::"l"(t.flags[d] + t.self), "l"(t.epoch) : "memory");
+  unsigned long long start;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(start));
+  for (int d = 0; d < t.count; ++d) {
+    if (d == t.self) continue;
+    for (;;) {
+      unsigned long long seen, now;
+      asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(seen) : "l"(t.flags[t.self] + d) : "memory");
+      if (seen >= t.epoch) break;
+      asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
+      if (now - start > 2000000000ull) { // two seconds: give up, say who was missing, return
+        khd::report_status(status, khd::kStatusPeerArrivalTimeout, static_cast<uint32_t>(d));
+        return;
+      }
+      __nanosleep(100);
+    }
+  }
+}
 
 struct TileCoord {
   int m0, n0;
@@ -705,8 +741,13 @@ __device__ __forceinline__ void gemm_body(int64_t m, int64_t n, float *__restric
                                                const khd::TensorMap &tm_a_lo, const khd::TensorMap &tm_b_hi,
                                                const khd::TensorMap &tm_b_lo, int64_t k_blocks,
                                                uint32_t *status, const int *__restrict__ a_shift,
-                                               const int *__restrict__ b_shift, int64_t raster, const GatherTargets *targets) {
+                                               const int *__restrict__ b_shift, int64_t raster, uint64_t alpha_beta,
+                                               const GatherTargets *targets) {
   extern __shared__ uint8_t smem_raw[];
+  // C = alpha * A.B + beta * C_old; alpha in the low and beta in the high 32 bits (1 and 0: a plain store)
+  const float alpha = __uint_as_float(static_cast<uint32_t>(alpha_beta));
+  const float beta = __uint_as_float(static_cast<uint32_t>(alpha_beta >> 32));
+  const bool scaled_store = !(alpha == 1.f && beta == 0.f);
   const int64_t group_m = raster > 0 ? raster : kGroupM; // tile rows per rasterisation group
   // full[kStages] (leader's are used), empty[kStages], acc_full[2], acc_empty[2] (leader's), tile_stored
   __shared__ __align__(8) uint64_t bars[2 * kStages + 5];
@@ -907,17 +948,28 @@ __device__ __forceinline__ void gemm_body(int64_t m, int64_t n, float *__restric
 #pragma unroll
           for (int j = 0; j < BN / 2 / 4; ++j) {
             const int4 sh = load_shift4(b_shift + col0 + 4 * j);
-            const float x = scale_pow2(acc[4 * j], -(row_shift + sh.x));
-            const float y = scale_pow2(acc[4 * j + 1], -(row_shift + sh.y));
-            const float z = scale_pow2(acc[4 * j + 2], -(row_shift + sh.z));
-            const float w = scale_pow2(acc[4 * j + 3], -(row_shift + sh.w));
+            float x = scale_pow2(acc[4 * j], -(row_shift + sh.x));
+            float y = scale_pow2(acc[4 * j + 1], -(row_shift + sh.y));
+            float z = scale_pow2(acc[4 * j + 2], -(row_shift + sh.z));
+            float w = scale_pow2(acc[4 * j + 3], -(row_shift + sh.w));
+            if (scaled_store) {
+              x *= alpha; y *= alpha; z *= alpha; w *= alpha;
+              if (beta != 0.f) { // beta = 0 never reads C (it may hold NaN)
+                const float4 old = *reinterpret_cast<const float4 *>(crow + col0 + 4 * j);
+                x = fmaf(beta, old.x, x); y = fmaf(beta, old.y, y); z = fmaf(beta, old.z, z); w = fmaf(beta, old.w, w);
+              }
+            }
             store_float4(crow + col0 + 4 * j, x, y, z, w);
           }
         } else {
 #pragma unroll
           for (int j = 0; j < BN / 2; ++j)
             if (col0 + j < n) {
-              const float x = scale_pow2(acc[j], -(row_shift + load_shift(b_shift + col0 + j)));
+              float x = scale_pow2(acc[j], -(row_shift + load_shift(b_shift + col0 + j)));
+              if (scaled_store) {
+                x *= alpha;
+                if (beta != 0.f) x = fmaf(beta, crow[(col0 + j) * cs1], x);
+              }
               store_float(crow + (col0 + j) * cs1, x);
             }
         }
@@ -944,6 +996,7 @@ __device__ __forceinline__ void gemm_body(int64_t m, int64_t n, float *__restric
     khd::tc_fence_after_sync();
     tmem_dealloc_pair(tmem_base, kTmemCols);
   }
+  if (kGather && threadIdx.x == 0 && targets->epoch != 0) signal_and_await_peers(*targets, status);
   if (blockIdx.x == 0 && threadIdx.x == 0) {
     unsigned long long timer_end;
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(timer_end));
@@ -959,12 +1012,12 @@ extern "C" __global__ void __launch_bounds__(kThreads, 1)
 gemm(KH_MEMREF2(const float, a), KH_MEMREF2(const float, b), KH_MEMREF2(float, c),
      const __grid_constant__ khd::TensorMap tm_a_hi, const __grid_constant__ khd::TensorMap tm_a_lo,
      const __grid_constant__ khd::TensorMap tm_b_hi, const __grid_constant__ khd::TensorMap tm_b_lo,
-     int64_t k_blocks, uint32_t *status, const int *a_shift, const int *b_shift, int64_t raster) {
+     int64_t k_blocks, uint32_t *status, const int *a_shift, const int *b_shift, int64_t raster, uint64_t alpha_beta) {
   (void)a_alloc; (void)a_ptr; (void)a_off; (void)a_size1; (void)a_stride0; (void)a_stride1;
   (void)b_alloc; (void)b_ptr; (void)b_off; (void)b_size0; (void)b_stride0; (void)b_stride1;
   (void)c_alloc; (void)c_size0; (void)c_size1;
   gemm_body<false, kBN>(a_size0, b_size1, KH_DATA(c), c_stride0, c_stride1, tm_a_hi, tm_a_lo, tm_b_hi, tm_b_lo,
-                        k_blocks, status, a_shift, b_shift, raster, nullptr);
+                        k_blocks, status, a_shift, b_shift, raster, alpha_beta, nullptr);
 }
 
 // The same with 256 x 128 tiles (the tensor maps of B then have boxes of 64 rows): taken by the
@@ -973,12 +1026,12 @@ extern "C" __global__ void __launch_bounds__(kThreads, 1)
 gemm_n128(KH_MEMREF2(const float, a), KH_MEMREF2(const float, b), KH_MEMREF2(float, c),
           const __grid_constant__ khd::TensorMap tm_a_hi, const __grid_constant__ khd::TensorMap tm_a_lo,
           const __grid_constant__ khd::TensorMap tm_b_hi, const __grid_constant__ khd::TensorMap tm_b_lo,
-          int64_t k_blocks, uint32_t *status, const int *a_shift, const int *b_shift, int64_t raster) {
+          int64_t k_blocks, uint32_t *status, const int *a_shift, const int *b_shift, int64_t raster, uint64_t alpha_beta) {
   (void)a_alloc; (void)a_ptr; (void)a_off; (void)a_size1; (void)a_stride0; (void)a_stride1;
   (void)b_alloc; (void)b_ptr; (void)b_off; (void)b_size0; (void)b_stride0; (void)b_stride1;
   (void)c_alloc; (void)c_size0; (void)c_size1;
   gemm_body<false, 128>(a_size0, b_size1, KH_DATA(c), c_stride0, c_stride1, tm_a_hi, tm_a_lo, tm_b_hi, tm_b_lo,
-                        k_blocks, status, a_shift, b_shift, raster, nullptr);
+                        k_blocks, status, a_shift, b_shift, raster, alpha_beta, nullptr);
 }
 
 // The M-row-sharded product with the all-gather fused into the epilogue: `a`
@@ -992,11 +1045,11 @@ gemm_allgather(KH_MEMREF2(const float, a), KH_MEMREF2(const float, b),
                const __grid_constant__ khd::TensorMap tm_a_hi, const __grid_constant__ khd::TensorMap tm_a_lo,
                const __grid_constant__ khd::TensorMap tm_b_hi, const __grid_constant__ khd::TensorMap tm_b_lo,
                int64_t k_blocks, uint32_t *status, const int *a_shift, const int *b_shift, int64_t raster,
-               const __grid_constant__ GatherTargets targets) {
+               uint64_t alpha_beta, const __grid_constant__ GatherTargets targets) {
   (void)a_alloc; (void)a_ptr; (void)a_off; (void)a_size1; (void)a_stride0; (void)a_stride1;
   (void)b_alloc; (void)b_ptr; (void)b_off; (void)b_size0; (void)b_stride0; (void)b_stride1;
   gemm_body<true, kBN>(a_size0, b_size1, nullptr, 0, 0, tm_a_hi, tm_a_lo, tm_b_hi, tm_b_lo, k_blocks, status,
-                       a_shift, b_shift, raster, &targets);
+                       a_shift, b_shift, raster, alpha_beta, &targets);
 }
 
 // gemm_allgather with 256 x 128 tiles (see gemm_n128).
@@ -1005,11 +1058,11 @@ gemm_allgather_n128(KH_MEMREF2(const float, a), KH_MEMREF2(const float, b),
                     const __grid_constant__ khd::TensorMap tm_a_hi, const __grid_constant__ khd::TensorMap tm_a_lo,
                     const __grid_constant__ khd::TensorMap tm_b_hi, const __grid_constant__ khd::TensorMap tm_b_lo,
                     int64_t k_blocks, uint32_t *status, const int *a_shift, const int *b_shift, int64_t raster,
-                    const __grid_constant__ GatherTargets targets) {
+                    uint64_t alpha_beta, const __grid_constant__ GatherTargets targets) {
   (void)a_alloc; (void)a_ptr; (void)a_off; (void)a_size1; (void)a_stride0; (void)a_stride1;
   (void)b_alloc; (void)b_ptr; (void)b_off; (void)b_size0; (void)b_stride0; (void)b_stride1;
   gemm_body<true, 128>(a_size0, b_size1, nullptr, 0, 0, tm_a_hi, tm_a_lo, tm_b_hi, tm_b_lo, k_blocks, status,
-                       a_shift, b_shift, raster, &targets);
+                       a_shift, b_shift, raster, alpha_beta, &targets);
 }
 
 // Sends a run of floats of this GPU's copy of a replicated buffer to the same place in every

@@ -36,6 +36,7 @@ enum : uint32_t {
   kStatusMmaWaitTimeout = 3,
   kStatusEpilogueWaitTimeout = 4,
   kStatusEmptyWaitTimeout = 5,
+  kStatusPeerArrivalTimeout = 6, // another GPU's arrival flag after a fused all-gather
 };
 
 __device__ __forceinline__ void report_status(uint32_t *status, uint32_t code, uint32_t detail) {

@@ -355,7 +355,7 @@ std::vector<LaunchStep> gemm_steps(int64_t m, int64_t n, int64_t k, const Device
   const int64_t tiles = narrow ? tiles128 : tiles256;
   g.grid = {static_cast<unsigned>(2 * std::min<int64_t>(tiles, clusters)), 1, 1};
   g.dynamic_smem = kGemmStages * kGemmStageBytes + 1024;
-  g.param_count = 21 + 4 + 2 + 2 + 1;
+  g.param_count = 21 + 4 + 2 + 2 + 1 + 1;
   g.tmem_columns = 512;
   return {sa, cm, sb, g};
 }
@@ -385,7 +385,12 @@ struct GatherTargets {
   int self;
   int64_t row_offset;
   float *multicast;
+  unsigned long long *flags[8]; // arrival flags of every rank as mapped here; used when epoch != 0
+  unsigned long long epoch;
+  unsigned int *finished;       // this GPU's finished-CTA counter (in the executor's status buffer)
 };
+static_assert(sizeof(GatherTargets) == 168 && sizeof(GatherTargets) <= LaunchArgs::kMaxStructBytes,
+              "GatherTargets is passed by value: its layout is shared with kernels/gemm.cu");
 
 // One product being enqueued: sizes, scratch and the entry points.
 struct GemmJob {
@@ -394,6 +399,7 @@ struct GemmJob {
   GemmScratch lay;
   char *base = nullptr; // scratch
   KernelFunction split_a, colmax_b, split_bt, prep_b, multiply, multiply_gather, multiply_n128, multiply_gather_n128;
+  float alpha = 1.f, beta = 0.f; // C = alpha * A.B + beta * C (1 and 0: a plain store that never reads C)
   uint64_t at(size_t off) const { return reinterpret_cast<uint64_t>(base + off); }
 };
 
@@ -545,6 +551,10 @@ Result<void> gemm_enqueue_multiply(const GemmJob &j, const void *a_rows, const v
   int64_t raster = 0;
   if (const char *forced = std::getenv("KERNELH_GEMM_RASTER")) raster = std::atoll(forced);
   args.add_scalar<int64_t>(raster);
+  uint32_t alpha_bits, beta_bits;
+  std::memcpy(&alpha_bits, &j.alpha, 4);
+  std::memcpy(&beta_bits, &j.beta, 4);
+  args.add_scalar<uint64_t>(static_cast<uint64_t>(alpha_bits) | (static_cast<uint64_t>(beta_bits) << 32));
   if (gather) {
     args.add_struct_bytes(gather, sizeof *gather);
     step.entry = narrow ? "gemm_allgather_n128" : "gemm_allgather";
@@ -568,6 +578,28 @@ Result<void> run_gemm(Executor &ex, const KernelPlan &p, const std::vector<void 
                       StreamHandle stream) {
   return launch_gemm(ex, p, b, stream, nullptr);
 }
+
+} // namespace
+
+// C = alpha * A.B + beta * C: the scaled store of the gemm epilogue (beta = 0 never reads C).
+Result<void> run_gemm_scaled(Executor &ex, const void *a, const void *b, void *c, int64_t m, int64_t n, int64_t k,
+                             float alpha, float beta, StreamHandle stream) {
+  KernelPlan p;
+  try {
+    p = plan_gemm({{"m", m}, {"n", n}, {"k", k}}, ex.limits());
+  } catch (const std::exception &e) {
+    return fail(2, e.what());
+  }
+  auto job = gemm_job(ex, m, n, k);
+  if (!job) return std::unexpected(job.error());
+  job->alpha = alpha;
+  job->beta = beta;
+  if (auto r = gemm_enqueue_a(*job, a, 0, m, p.steps[0], stream, n); !r) return r;
+  if (auto r = gemm_enqueue_b(*job, b, stream, false); !r) return r;
+  return gemm_enqueue_multiply(*job, a, b, c, 0, m, p.steps.back(), stream, nullptr);
+}
+
+namespace {
 
 // Host-buffer form of the product, pipelined over PCIe: B goes up first and is
 // split; A then goes up in row blocks, and while block i+1 is on the wire,
@@ -676,6 +708,19 @@ Result<void> run_gemm_allgather(Executor &ex, const void *a_shard, const void *b
   }
   t.self = rank;
   t.row_offset = static_cast<int64_t>(rank) * m_shard;
+  // armed by Executor::arm_arrival_flags for this one launch: the kernel then ends with the barrier itself
+  if (ArrivalFlags armed = ex.take_arrival_flags(); armed.epoch != 0) {
+    if (static_cast<int>(armed.flags.size()) != world)
+      return fail(2, "gemm_allgather: " + std::to_string(world) + " arrival-flag arrays expected, got " +
+                         std::to_string(armed.flags.size()));
+    for (int i = 0; i < world; ++i) {
+      if (armed.flags[i] == nullptr || (reinterpret_cast<uintptr_t>(armed.flags[i]) & 7u) != 0)
+        return fail(2, "gemm_allgather: arrival-flag array " + std::to_string(i) + " is null or not 8-byte aligned");
+      t.flags[i] = static_cast<unsigned long long *>(armed.flags[i]);
+    }
+    t.epoch = armed.epoch;
+    t.finished = reinterpret_cast<unsigned int *>(ex.status_word()) + 16;
+  }
   return launch_gemm(ex, plan, {const_cast<void *>(a_shard), const_cast<void *>(b), nullptr}, stream, &t);
 }
 

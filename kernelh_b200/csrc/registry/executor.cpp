@@ -179,8 +179,9 @@ Result<void *> Executor::scan_state(int64_t tiles) {
 
 const char *Executor::wait_name(uint32_t code) {
   static const char *names[] = {"ok", "scan look-back wait", "TMA (full-stage) wait",
-                                "MMA (accumulator) wait", "epilogue wait", "empty-stage wait"};
-  return code < 6 ? names[code] : "unknown wait";
+                                "MMA (accumulator) wait", "epilogue wait", "empty-stage wait",
+                                "wait for another GPU's arrival flag (detail = its rank)"};
+  return code < 7 ? names[code] : "unknown wait";
 }
 
 Result<void> Executor::run(const std::string &kernel, const ShapeMap &shape,

@@ -12,9 +12,16 @@
 #include <map>
 #include <memory>
 #include <string>
+#include <utility>
 #include <vector>
 
 namespace kh {
+
+// Arrival flags of a fused all-gather (see GatherTargets in kernels/gemm.cu).
+struct ArrivalFlags {
+  std::vector<void *> flags;
+  uint64_t epoch = 0;
+};
 
 class Executor {
 public:
@@ -45,6 +52,10 @@ public:
   Result<void *> workspace(size_t bytes);
   Result<void> launch(KernelFunction fn, const LaunchStep &step, LaunchArgs &args, StreamHandle s);
   uint32_t *status_word() const { return static_cast<uint32_t *>(status_.data()); }
+  // Arrival flags for the NEXT fused all-gather launch of this executor only (then disarmed): every
+  // rank's flag array as mapped on this device, and the epoch to write and wait for (> 0, growing).
+  void arm_arrival_flags(std::vector<void *> flags, uint64_t epoch) { arrival_ = {std::move(flags), epoch}; }
+  ArrivalFlags take_arrival_flags() { return std::exchange(arrival_, ArrivalFlags{}); }
   // The three streams of the host-buffer paths (uploads, compute, downloads), created on first use.
   Result<HostStreams> host_streams();
   // Device staging buffer number `index` of the host-buffer paths, at least `bytes` large (grow-only).
@@ -86,6 +97,7 @@ private:
     std::string entry;
     EventHandle start, end;
   };
+  ArrivalFlags arrival_;
   bool profiling_ = false;
   std::vector<ProfiledLaunch> profiled_;
   uint64_t launches_issued_ = 0;
@@ -112,6 +124,8 @@ Result<void> run_gemm_host_sharded_begin(Executor &ex, const void *a_shard_host,
                                          int world, int64_t m_shard, int64_t n, int64_t k);
 Result<void> run_gemm_host_sharded_finish(Executor &ex, void *c_shard_host);
 
+Result<void> run_gemm_scaled(Executor &ex, const void *a, const void *b, void *c, int64_t m, int64_t n, int64_t k,
+                             float alpha, float beta, StreamHandle stream);
 Result<void> run_scan_lookback_probe(Executor &ex, const void *x, void *y, int64_t n, uint32_t spin_limit,
                                      StreamHandle stream);
 

@@ -1,6 +1,8 @@
 #include "launch_args.hpp"
 
 #include <cstring>
+#include <stdexcept>
+#include <string>
 
 namespace kh {
 
@@ -26,15 +28,16 @@ void LaunchArgs::add_scalar_bytes(const void *value, size_t byte_size) {
   slots_.push_back(slot);
 }
 
-void LaunchArgs::add_tensor_map(const TensorMapBytes &map) {
-  order_.push_back({true, maps_.size()});
-  maps_.push_back(map);
-}
+void LaunchArgs::add_tensor_map(const TensorMapBytes &map) { add_struct_bytes(&map, sizeof map); }
 
 void LaunchArgs::add_struct_bytes(const void *value, size_t byte_size) {
-  TensorMapBytes blob{};
-  std::memcpy(&blob, value, byte_size > sizeof blob ? sizeof blob : byte_size);
-  add_tensor_map(blob);
+  if (byte_size > kMaxStructBytes)
+    throw std::length_error("LaunchArgs: a by-value kernel parameter of " + std::to_string(byte_size) +
+                            " bytes exceeds the " + std::to_string(kMaxStructBytes) + " bytes a parameter may have here");
+  Blob blob{};
+  std::memcpy(blob.bytes, value, byte_size);
+  order_.push_back({true, maps_.size()});
+  maps_.push_back(blob);
 }
 
 void **LaunchArgs::params() {

@@ -24,7 +24,10 @@ public:
   void add_scalar_bytes(const void *value, size_t byte_size);
   template <typename T> void add_scalar(T value) { add_scalar_bytes(&value, sizeof(T)); }
   void add_tensor_map(const TensorMapBytes &map);
-  // A by-value struct parameter of up to 128 bytes (stored 64-byte aligned).
+  // A by-value struct parameter of up to kMaxStructBytes (stored 64-byte aligned). A larger
+  // struct is refused (std::length_error), never truncated: a kernel reading past a short copy
+  // would take whatever follows it for pointers.
+  static constexpr size_t kMaxStructBytes = 256;
   void add_struct_bytes(const void *value, size_t byte_size);
 
   // Number of kernel parameters: 8-byte slots plus tensor maps.
@@ -40,11 +43,14 @@ public:
 
 private:
   struct Ref {
-    bool is_map;
+    bool is_map; // a 64-byte aligned blob (tensor map or struct) rather than an 8-byte slot
     size_t index;
   };
+  struct alignas(64) Blob {
+    unsigned char bytes[kMaxStructBytes];
+  };
   std::vector<uint64_t> slots_;
-  std::deque<TensorMapBytes> maps_; // deque: stable addresses
+  std::deque<Blob> maps_; // deque: stable addresses
   std::vector<Ref> order_;
   std::vector<void *> params_;
 };

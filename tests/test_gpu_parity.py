@@ -413,6 +413,31 @@ def test_gemm_8192_sampled_rows_and_scaling_property(ctx, oracle):
     assert np.array_equal(c2, c * 2)
 
 
+def test_gemm_scaled_store_alpha_beta(ctx, oracle):
+    """C = alpha * A.B + beta * C (the first generalisation of the reference's plain store,
+    lib/dsl/kernels/gemm.cpp:47-53): alpha = 1, beta = 0 is the plain gemm bit for bit and never
+    reads C (NaN in, numbers out); general alpha, beta meet the gemm's bound against fp64, on an
+    aligned shape, a ragged one (scalar store path) and a small one (narrow tiles)."""
+    for (m, n, k) in [(512, 768, 320), (300, 250, 100), (1000, 1000, 64)]:
+        a = oracle.uniform((m, k), oracle.BASE_SEED + 71, -1, 1)
+        b = oracle.uniform((k, n), oracle.BASE_SEED + 72, -1, 1)
+        c0 = oracle.uniform((m, n), oracle.BASE_SEED + 73, -4, 4)
+        da, db = dev(a), dev(b)
+        stream = torch.cuda.current_stream().cuda_stream
+        plain = run(ctx, "gemm", f"m={m},n={n},k={k}", [da, db], (m, n))
+        c = torch.full((m, n), float("nan"), device="cuda")
+        ctx.gemm_scaled(da, db, c, m, n, k, 1.0, 0.0, stream)
+        ctx.synchronize(stream)
+        assert np.array_equal(c.cpu().numpy(), plain)
+        for alpha, beta in [(2.5, 0.0), (1.0, 1.0), (-0.75, 0.5)]:
+            c = dev(c0)
+            ctx.gemm_scaled(da, db, c, m, n, k, alpha, beta, stream)
+            ctx.synchronize(stream)
+            ref = alpha * (a.astype(np.float64) @ b.astype(np.float64)) + beta * c0.astype(np.float64)
+            cmp_ = oracle.compare(c.cpu().numpy(), ref.astype(np.float32))
+            assert cmp_.non_finite == 0 and cmp_.max_rel <= REL * math.sqrt(k), (m, n, k, alpha, beta, cmp_.max_rel)
+
+
 def test_gemm_allgather_two_shards_fill_every_replica(ctx, oracle):
     """The fused gemm + all-gather on one GPU: the two ranks' launches run one
     after the other and each stores its row shard into both replicas of C."""
@@ -431,6 +456,50 @@ def test_gemm_allgather_two_shards_fill_every_replica(ctx, oracle):
     assert oracle.compare(plain, oracle.gemm_ref(a, b)).rel_frobenius <= 1e-5
     with pytest.raises(kh.KernelhError):
         ctx.gemm_allgather(da, db, replicas, 2, 256, n, k, stream)
+
+
+def test_gemm_allgather_arrival_flags_signal_and_bounded_wait(ctx, oracle):
+    """The barrier inside the fused gemm + all-gather. One GPU plays rank 0 of two: (1) with the
+    peer's arrival word already at the epoch (written by the host, standing in for the peer), the
+    kernel signals - word 0 of the peer's array becomes the epoch - finds the peer arrived and
+    returns cleanly, twice in a row (the finished-CTA counter went back to zero); (2) with a peer
+    word that nothing sets, the kernel's last CTA waits its two seconds, records the peer-arrival
+    code with the missing rank as detail and returns: kh_synchronize gives 1001, and the context
+    still computes the right product afterwards. A wait that gives up, not a fault."""
+    m, n, k = 512, 256, 128
+    a = oracle.uniform((m, k), oracle.BASE_SEED + 61, -1, 1)
+    b = oracle.uniform((k, n), oracle.BASE_SEED + 62, -1, 1)
+    da, db = dev(a), dev(b)
+    plain = run(ctx, "gemm", f"m={m},n={n},k={k}", [da, db], (m, n))
+    replicas = [torch.full((m, n), float("nan"), device="cuda") for _ in range(2)]
+    flags = [torch.zeros(8, dtype=torch.int64, device="cuda") for _ in range(2)]  # [mine, the peer's]
+    stream = torch.cuda.current_stream().cuda_stream
+    for epoch in (1, 2):
+        flags[0][1] = epoch  # "rank 1 has arrived"
+        ctx.arm_arrival_flags([f.data_ptr() for f in flags], epoch)
+        ctx.gemm_allgather(da[:256], db, replicas, 0, 256, n, k, stream)
+        ctx.synchronize(stream)
+        assert flags[1][0].item() == epoch and flags[1][1:].abs().sum().item() == 0
+    for r in replicas:
+        assert np.array_equal(r[:256].cpu().numpy(), plain[:256])
+    # the flags are for ONE launch: an unarmed launch neither signals nor waits
+    ctx.gemm_allgather(da[:256], db, replicas, 0, 256, n, k, stream)
+    ctx.synchronize(stream)
+    assert flags[1][0].item() == 2
+    # nobody sets epoch 3 in my array: the wait runs out after two seconds and is reported
+    ctx.arm_arrival_flags([f.data_ptr() for f in flags], 3)
+    ctx.gemm_allgather(da[:256], db, replicas, 0, 256, n, k, stream)
+    with pytest.raises(kh.KernelhError) as e:
+        ctx.synchronize(stream)
+    assert e.value.code == kh.DEVICE_TIMEOUT
+    assert "another GPU's arrival flag" in e.value.message and "code 6, detail 1" in e.value.message
+    assert flags[1][0].item() == 3  # it had signalled before it waited
+    again = run(ctx, "gemm", f"m={m},n={n},k={k}", [da, db], (m, n))
+    assert np.array_equal(again, plain)
+    with pytest.raises(kh.KernelhError):
+        ctx.arm_arrival_flags([flags[0].data_ptr()], 1)  # one array: not a world
+    with pytest.raises(kh.KernelhError):
+        ctx.arm_arrival_flags([f.data_ptr() for f in flags], 0)  # epochs are positive
 
 
 def test_gemm_host_sharded_uploads_each_slice_of_b_once(ctx, oracle):

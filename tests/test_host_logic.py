@@ -289,6 +289,7 @@ def test_device_wait_codes_have_names():
     """kh_synchronize reports a device-side bounded wait that ran out as code 1001
     and names the wait; the code-to-name table is checked here without a GPU."""
     assert kh.DEVICE_TIMEOUT == 1001
+    assert "arrival flag" in kh.wait_name(6)
     assert kh.wait_name(1) == "scan look-back wait"
     assert kh.wait_name(2) == "TMA (full-stage) wait"
     assert kh.wait_name(3) == "MMA (accumulator) wait"
