@@ -638,8 +638,15 @@ gemm_prep_b(KH_MEMREF2(const float, b), const __grid_constant__ khd::TensorMap t
     col_shift[threadIdx.x] = shift;
     if (rank == 0 && n0 + static_cast<int>(threadIdx.x) < n) b_shift[n0 + threadIdx.x] = shift;
   }
-  cluster_sync_all(); // nobody reads a CTA's maxima after this; also publishes col_shift to the block
-  if (s_abort) return; // a copy never landed (block-uniform after the barriers): reported in the status word
+  // "I have read every CTA's maxima": arrive now, wait only before leaving (a CTA's shared memory
+  // must outlive the other CTAs' reads of it), so the split does not stand behind a second
+  // cluster-wide round trip. The block barrier publishes col_shift.
+  asm volatile("barrier.cluster.arrive.release;" ::: "memory");
+  __syncthreads();
+  if (s_abort) { // a copy never landed (block-uniform after the barriers): reported in the status word
+    asm volatile("barrier.cluster.wait.acquire;" ::: "memory");
+    return;
+  }
 
   // ---- scale, split, transpose, in place: 256 rows (k-values) x 32 columns at a time ----
   // Thread (column `lane`, warp w) owns the 16-byte pieces w, w + 8, w + 16, w + 24 of its column:
@@ -690,6 +697,7 @@ gemm_prep_b(KH_MEMREF2(const float, b), const __grid_constant__ khd::TensorMap t
   }
   // the copies only have to be done READING this CTA's shared memory before it goes away
   if (threadIdx.x == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire;" ::: "memory"); // every CTA of the cluster has read this CTA's maxima
 }
 
 namespace {
