@@ -750,6 +750,7 @@ __device__ __forceinline__ void gemm_body(int64_t m, int64_t n, float *__restric
                                                const khd::TensorMap &tm_b_lo, int64_t k_blocks,
                                                uint32_t *status, const int *__restrict__ a_shift,
                                                const int *__restrict__ b_shift, int64_t raster, uint64_t alpha_beta,
+                                               float *__restrict__ partials, unsigned int *partial_flags,
                                                const GatherTargets *targets) {
   extern __shared__ uint8_t smem_raw[];
   // C = alpha * A.B + beta * C_old; alpha in the low and beta in the high 32 bits (1 and 0: a plain store)
@@ -761,6 +762,9 @@ __device__ __forceinline__ void gemm_body(int64_t m, int64_t n, float *__restric
   __shared__ __align__(8) uint64_t bars[2 * kStages + 5];
   __shared__ uint32_t s_tmem_base;
   __shared__ int s_abort;
+  __shared__ int s_split_role;
+  // named barrier 1: the eight epilogue warps of this CTA only
+  const auto epilogue_barrier = [] { asm volatile("bar.sync 1, %0;" ::"n"(kEpilogueWarps * 32) : "memory"); };
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t rank = cluster_ctarank(); // 0 = leader
@@ -775,8 +779,24 @@ __device__ __forceinline__ void gemm_body(int64_t m, int64_t n, float *__restric
 
   const int64_t tiles_m = (m + 2 * kBM - 1) / (2 * kBM), tiles_n = (n + BN - 1) / BN;
   const int64_t num_tiles = tiles_m * tiles_n;
-  const int64_t num_chunks = (k_blocks + kChunkBlocks - 1) / kChunkBlocks;
   const int64_t first_tile = blockIdx.x >> 1, tile_step = gridDim.x >> 1;
+  // Work units. Whole tiles first; when `partials` is given, the tiles of the last, partly filled
+  // wave of clusters (num_tiles mod the cluster count, at most half a wave: the host decides) are
+  // each done as TWO units, one per half of K, by two neighbouring clusters at the same time: the
+  // last wave then takes half as long. The unit that finishes first leaves its 128 x BN partial
+  // sums in `partials`; the second adds them to its own and stores the tile (epilogue below).
+  const int64_t whole_tiles = partials != nullptr ? (num_tiles / tile_step) * tile_step : num_tiles;
+  const int64_t num_units = whole_tiles + 2 * (num_tiles - whole_tiles);
+  struct Unit {
+    int64_t tile, kb0, kb1;
+    int slot; // index of the shared tile among the split ones, or -1 for a whole tile
+  };
+  const auto unit_of = [&](int64_t u) -> Unit {
+    if (u < whole_tiles) return {u, 0, k_blocks, -1};
+    const int64_t v = u - whole_tiles;
+    const int64_t half_blocks = k_blocks / 2;
+    return {whole_tiles + (v >> 1), (v & 1) ? half_blocks : 0, (v & 1) ? k_blocks : half_blocks, static_cast<int>(v >> 1)};
+  };
 
   // The SM clock this launch really ran at: block 0 counts its SM's cycles against the global
   // nanosecond timer over its whole life and leaves both in the status buffer (bytes 32..47),
@@ -821,11 +841,12 @@ __device__ __forceinline__ void gemm_body(int64_t m, int64_t n, float *__restric
     if (lane == 0) {
       uint32_t g_kb = 0;
       bool ok = true;
-      for (int64_t tile = first_tile; tile < num_tiles && ok; tile += tile_step) {
-        const TileCoord tc = tile_coord<BN>(tile, tiles_m, tiles_n, group_m);
+      for (int64_t u = first_tile; u < num_units && ok; u += tile_step) {
+        const Unit unit = unit_of(u);
+        const TileCoord tc = tile_coord<BN>(unit.tile, tiles_m, tiles_n, group_m);
         const int a_row = tc.m0 + static_cast<int>(rank) * kBM;
         const int b_row = tc.n0 + static_cast<int>(rank) * (BN / 2);
-        for (int64_t kb = 0; kb < k_blocks; ++kb, ++g_kb) {
+        for (int64_t kb = unit.kb0; kb < unit.kb1; ++kb, ++g_kb) {
           const int s = static_cast<int>(g_kb % kStages);
           const uint32_t phase = (g_kb / kStages) & 1u;
           ok = khd::mbar_wait(empty0 + 8 * s, phase ^ 1u, &s_abort, status,
@@ -849,9 +870,10 @@ __device__ __forceinline__ void gemm_body(int64_t m, int64_t n, float *__restric
       constexpr uint32_t idesc = khd::umma_idesc_f16(2 * kBM, BN);
       uint32_t g_kb = 0, g_chunk = 0;
       bool ok = true;
-      for (int64_t tile = first_tile; tile < num_tiles && ok; tile += tile_step) {
-        for (int64_t kb = 0; kb < k_blocks && ok; ++kb, ++g_kb) {
-          const int in_chunk = static_cast<int>(kb % kChunkBlocks);
+      for (int64_t u = first_tile; u < num_units && ok; u += tile_step) {
+        const Unit unit = unit_of(u);
+        for (int64_t kb = unit.kb0; kb < unit.kb1 && ok; ++kb, ++g_kb) {
+          const int in_chunk = static_cast<int>((kb - unit.kb0) % kChunkBlocks);
           const int buf = static_cast<int>(g_chunk & 1u);
           if (in_chunk == 0) {
             ok = khd::mbar_wait(acc_empty0 + 8 * buf, ((g_chunk >> 1) & 1u) ^ 1u, &s_abort, status,
@@ -871,7 +893,7 @@ __device__ __forceinline__ void gemm_body(int64_t m, int64_t n, float *__restric
           const uint64_t a_lo = a_hi + (kTileBytes >> 4);
           const uint64_t b_hi = a_hi + (2 * kTileBytes >> 4);
           const uint64_t b_lo = a_hi + (3 * kTileBytes >> 4);
-          const bool chunk_end = in_chunk == kChunkBlocks - 1 || kb == k_blocks - 1;
+          const bool chunk_end = in_chunk == kChunkBlocks - 1 || kb == unit.kb1 - 1;
           const uint32_t empty_here = map_to_cta(empty0 + 8 * s, 0), empty_peer = map_to_cta(empty0 + 8 * s, 1);
           const uint32_t accf_here = map_to_cta(acc_full0 + 8 * buf, 0), accf_peer = map_to_cta(acc_full0 + 8 * buf, 1);
           if (elected) {
@@ -904,13 +926,15 @@ __device__ __forceinline__ void gemm_body(int64_t m, int64_t n, float *__restric
     constexpr int kPushUnits = 16 * BN / 128; // per epilogue warp and tile
     PendingPush pending{0, 0, kPushUnits};
     bool ok = true;
-    for (int64_t tile = first_tile; tile < num_tiles && ok; tile += tile_step) {
-      const TileCoord tc = tile_coord<BN>(tile, tiles_m, tiles_n, group_m);
+    for (int64_t u = first_tile; u < num_units && ok; u += tile_step) {
+      const Unit unit = unit_of(u);
+      const TileCoord tc = tile_coord<BN>(unit.tile, tiles_m, tiles_n, group_m);
       const int m0 = tc.m0 + static_cast<int>(rank) * kBM;
+      const int64_t unit_chunks = (unit.kb1 - unit.kb0 + kChunkBlocks - 1) / kChunkBlocks;
       float acc[BN / 2];
 #pragma unroll
       for (int i = 0; i < BN / 2; ++i) acc[i] = 0.f;
-      for (int64_t chunk = 0; chunk < num_chunks && ok; ++chunk, ++g_chunk) {
+      for (int64_t chunk = 0; chunk < unit_chunks && ok; ++chunk, ++g_chunk) {
         const int buf = static_cast<int>(g_chunk & 1u);
         ok = khd::mbar_wait(acc_full0 + 8 * buf, (g_chunk >> 1) & 1u, &s_abort, status,
                             khd::kStatusMmaWaitTimeout, g_chunk);
@@ -932,6 +956,56 @@ __device__ __forceinline__ void gemm_body(int64_t m, int64_t n, float *__restric
       }
       if (!ok) break;
       if (kGather) push_units<BN>(*targets, pending, kPushUnits, ew, lane, m, n);
+
+      if (unit.slot >= 0) {
+        // Half of K: meet the other half. Per split tile and CTA of the pair: flags[0] counts the
+        // arrivals, flags[1] says the first arrival's partial sums are in `partials`.
+        unsigned int *flags = partial_flags + (static_cast<size_t>(unit.slot) * 2 + rank) * 2;
+        float4 *mine = reinterpret_cast<float4 *>(partials + (static_cast<size_t>(unit.slot) * 2 + rank) * (kBM * BN)) +
+                       (static_cast<size_t>(quad * 32 + lane) * BN + half * (BN / 2)) / 4;
+        epilogue_barrier();
+        if (ew == 0 && lane == 0) s_split_role = static_cast<int>(atomicAdd(flags, 1u));
+        epilogue_barrier();
+        if (s_split_role == 0) {
+          // first: leave the partial sums (a row of this thread's half of the columns: 512 contiguous bytes)
+#pragma unroll
+          for (int j = 0; j < BN / 2 / 4; ++j)
+            mine[j] = make_float4(acc[4 * j], acc[4 * j + 1], acc[4 * j + 2], acc[4 * j + 3]);
+          __threadfence();
+          epilogue_barrier();
+          if (ew == 0 && lane == 0) asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(flags + 1), "r"(1u) : "memory");
+          continue; // the other unit stores the tile
+        }
+        // second: wait (bounded) for the first one's sums, take the flags back to zero, add
+        if (ew == 0 && lane == 0) {
+          unsigned long long start, now;
+          asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(start));
+          for (;;) {
+            unsigned int ready;
+            asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(ready) : "l"(flags + 1) : "memory");
+            if (ready != 0u) break;
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
+            if (now - start > 2000000000ull) {
+              khd::report_status(status, khd::kStatusEpilogueWaitTimeout, 9100u + static_cast<uint32_t>(unit.slot));
+              s_abort = 1;
+              break;
+            }
+            __nanosleep(64);
+          }
+          flags[0] = 0u;
+          flags[1] = 0u;
+        }
+        epilogue_barrier();
+        if (s_abort) {
+          ok = false;
+          break;
+        }
+#pragma unroll
+        for (int j = 0; j < BN / 2 / 4; ++j) {
+          const float4 other = __ldcg(mine + j);
+          acc[4 * j] += other.x; acc[4 * j + 1] += other.y; acc[4 * j + 2] += other.z; acc[4 * j + 3] += other.w;
+        }
+      }
 
       const int64_t row = static_cast<int64_t>(m0) + quad * 32 + lane;
       const int64_t col0 = static_cast<int64_t>(tc.n0) + half * (BN / 2);
@@ -1020,12 +1094,13 @@ extern "C" __global__ void __launch_bounds__(kThreads, 1)
 gemm(KH_MEMREF2(const float, a), KH_MEMREF2(const float, b), KH_MEMREF2(float, c),
      const __grid_constant__ khd::TensorMap tm_a_hi, const __grid_constant__ khd::TensorMap tm_a_lo,
      const __grid_constant__ khd::TensorMap tm_b_hi, const __grid_constant__ khd::TensorMap tm_b_lo,
-     int64_t k_blocks, uint32_t *status, const int *a_shift, const int *b_shift, int64_t raster, uint64_t alpha_beta) {
+     int64_t k_blocks, uint32_t *status, const int *a_shift, const int *b_shift, int64_t raster, uint64_t alpha_beta,
+     float *partials, unsigned int *partial_flags) {
   (void)a_alloc; (void)a_ptr; (void)a_off; (void)a_size1; (void)a_stride0; (void)a_stride1;
   (void)b_alloc; (void)b_ptr; (void)b_off; (void)b_size0; (void)b_stride0; (void)b_stride1;
   (void)c_alloc; (void)c_size0; (void)c_size1;
   gemm_body<false, kBN>(a_size0, b_size1, KH_DATA(c), c_stride0, c_stride1, tm_a_hi, tm_a_lo, tm_b_hi, tm_b_lo,
-                        k_blocks, status, a_shift, b_shift, raster, alpha_beta, nullptr);
+                        k_blocks, status, a_shift, b_shift, raster, alpha_beta, partials, partial_flags, nullptr);
 }
 
 // The same with 256 x 128 tiles (the tensor maps of B then have boxes of 64 rows): taken by the
@@ -1034,12 +1109,13 @@ extern "C" __global__ void __launch_bounds__(kThreads, 1)
 gemm_n128(KH_MEMREF2(const float, a), KH_MEMREF2(const float, b), KH_MEMREF2(float, c),
           const __grid_constant__ khd::TensorMap tm_a_hi, const __grid_constant__ khd::TensorMap tm_a_lo,
           const __grid_constant__ khd::TensorMap tm_b_hi, const __grid_constant__ khd::TensorMap tm_b_lo,
-          int64_t k_blocks, uint32_t *status, const int *a_shift, const int *b_shift, int64_t raster, uint64_t alpha_beta) {
+          int64_t k_blocks, uint32_t *status, const int *a_shift, const int *b_shift, int64_t raster, uint64_t alpha_beta,
+     float *partials, unsigned int *partial_flags) {
   (void)a_alloc; (void)a_ptr; (void)a_off; (void)a_size1; (void)a_stride0; (void)a_stride1;
   (void)b_alloc; (void)b_ptr; (void)b_off; (void)b_size0; (void)b_stride0; (void)b_stride1;
   (void)c_alloc; (void)c_size0; (void)c_size1;
   gemm_body<false, 128>(a_size0, b_size1, KH_DATA(c), c_stride0, c_stride1, tm_a_hi, tm_a_lo, tm_b_hi, tm_b_lo,
-                        k_blocks, status, a_shift, b_shift, raster, alpha_beta, nullptr);
+                        k_blocks, status, a_shift, b_shift, raster, alpha_beta, partials, partial_flags, nullptr);
 }
 
 // The M-row-sharded product with the all-gather fused into the epilogue: `a`
@@ -1053,11 +1129,12 @@ gemm_allgather(KH_MEMREF2(const float, a), KH_MEMREF2(const float, b),
                const __grid_constant__ khd::TensorMap tm_a_hi, const __grid_constant__ khd::TensorMap tm_a_lo,
                const __grid_constant__ khd::TensorMap tm_b_hi, const __grid_constant__ khd::TensorMap tm_b_lo,
                int64_t k_blocks, uint32_t *status, const int *a_shift, const int *b_shift, int64_t raster,
-               uint64_t alpha_beta, const __grid_constant__ GatherTargets targets) {
+               uint64_t alpha_beta, float *partials, unsigned int *partial_flags,
+               const __grid_constant__ GatherTargets targets) {
   (void)a_alloc; (void)a_ptr; (void)a_off; (void)a_size1; (void)a_stride0; (void)a_stride1;
   (void)b_alloc; (void)b_ptr; (void)b_off; (void)b_size0; (void)b_stride0; (void)b_stride1;
   gemm_body<true, kBN>(a_size0, b_size1, nullptr, 0, 0, tm_a_hi, tm_a_lo, tm_b_hi, tm_b_lo, k_blocks, status,
-                       a_shift, b_shift, raster, alpha_beta, &targets);
+                       a_shift, b_shift, raster, alpha_beta, partials, partial_flags, &targets);
 }
 
 // gemm_allgather with 256 x 128 tiles (see gemm_n128).
@@ -1066,11 +1143,12 @@ gemm_allgather_n128(KH_MEMREF2(const float, a), KH_MEMREF2(const float, b),
                     const __grid_constant__ khd::TensorMap tm_a_hi, const __grid_constant__ khd::TensorMap tm_a_lo,
                     const __grid_constant__ khd::TensorMap tm_b_hi, const __grid_constant__ khd::TensorMap tm_b_lo,
                     int64_t k_blocks, uint32_t *status, const int *a_shift, const int *b_shift, int64_t raster,
-                    uint64_t alpha_beta, const __grid_constant__ GatherTargets targets) {
+                    uint64_t alpha_beta, float *partials, unsigned int *partial_flags,
+                    const __grid_constant__ GatherTargets targets) {
   (void)a_alloc; (void)a_ptr; (void)a_off; (void)a_size1; (void)a_stride0; (void)a_stride1;
   (void)b_alloc; (void)b_ptr; (void)b_off; (void)b_size0; (void)b_stride0; (void)b_stride1;
   gemm_body<true, 128>(a_size0, b_size1, nullptr, 0, 0, tm_a_hi, tm_a_lo, tm_b_hi, tm_b_lo, k_blocks, status,
-                       a_shift, b_shift, raster, alpha_beta, &targets);
+                       a_shift, b_shift, raster, alpha_beta, partials, partial_flags, &targets);
 }
 
 // Sends a run of floats of this GPU's copy of a replicated buffer to the same place in every

@@ -355,7 +355,7 @@ std::vector<LaunchStep> gemm_steps(int64_t m, int64_t n, int64_t k, const Device
   const int64_t tiles = narrow ? tiles128 : tiles256;
   g.grid = {static_cast<unsigned>(2 * std::min<int64_t>(tiles, clusters)), 1, 1};
   g.dynamic_smem = kGemmStages * kGemmStageBytes + 1024;
-  g.param_count = 21 + 4 + 2 + 2 + 1 + 1;
+  g.param_count = 21 + 4 + 2 + 2 + 1 + 1 + 2;
   g.tmem_columns = 512;
   return {sa, cm, sb, g};
 }
@@ -555,6 +555,29 @@ Result<void> gemm_enqueue_multiply(const GemmJob &j, const void *a_rows, const v
   std::memcpy(&alpha_bits, &j.alpha, 4);
   std::memcpy(&beta_bits, &j.beta, 4);
   args.add_scalar<uint64_t>(static_cast<uint64_t>(alpha_bits) | (static_cast<uint64_t>(beta_bits) << 32));
+  // The last, partly filled wave of clusters: when it holds at most half a wave of tiles (and there is
+  // at least one full wave before it), each of its tiles is done by two clusters, half of K each, and
+  // the wave takes half as long (2048 x 8192 x 8192, the 4-GPU shard: 3.46 waves become 3.5 half-paid
+  // instead of 4). The halves meet in a scratch of partial sums; flags zeroed before every such launch.
+  void *partials = nullptr, *partial_flags = nullptr;
+  {
+    const int64_t clusters = step.grid.x / 2;
+    const int64_t tile_cols = narrow ? 128 : 256;
+    const int64_t tiles = ((rows + 2 * kGemmBM - 1) / (2 * kGemmBM)) * ((j.n + tile_cols - 1) / tile_cols);
+    const int64_t left = tiles % clusters;
+    const int64_t k_blocks = j.kp / kGemmBK;
+    const char *off = std::getenv("KERNELH_GEMM_SPLIT_TAIL"); // "0" switches it off (measurements)
+    if (tiles > clusters && left > 0 && 2 * left <= clusters && k_blocks % 16 == 0 && !(off && off[0] == '0')) {
+      auto scratch = j.ex.gemm_partials(static_cast<size_t>(left) * 2 * kGemmBM * static_cast<size_t>(tile_cols) * 4,
+                                        static_cast<size_t>(left) * 2 * 2 * 4);
+      if (!scratch) return std::unexpected(scratch.error());
+      partials = scratch->first;
+      partial_flags = scratch->second;
+      if (auto r = j.ex.backend().memset32_async(partial_flags, 0, static_cast<size_t>(left) * 4, stream); !r) return r;
+    }
+  }
+  args.add_scalar<uint64_t>(reinterpret_cast<uint64_t>(partials));
+  args.add_scalar<uint64_t>(reinterpret_cast<uint64_t>(partial_flags));
   if (gather) {
     args.add_struct_bytes(gather, sizeof *gather);
     step.entry = narrow ? "gemm_allgather_n128" : "gemm_allgather";

@@ -231,6 +231,19 @@ Result<void> Executor::synchronize(StreamHandle stream) {
                                   "); the kernel stopped and its output is incomplete");
 }
 
+Result<std::pair<void *, void *>> Executor::gemm_partials(size_t partial_bytes, size_t flag_bytes) {
+  for (auto [buffer, bytes] : {std::pair<Buffer *, size_t>{&gemm_partials_, partial_bytes},
+                               std::pair<Buffer *, size_t>{&gemm_partial_flags_, flag_bytes}}) {
+    if (buffer->data() != nullptr && buffer->size() >= bytes) continue;
+    // a launch that still uses the old buffer may be in flight: wait before it is replaced
+    if (auto r = backend_->device_synchronize(); !r) return std::unexpected(r.error());
+    auto fresh = Buffer::allocate(backend_, bytes);
+    if (!fresh) return std::unexpected(fresh.error());
+    *buffer = std::move(*fresh);
+  }
+  return std::pair<void *, void *>{gemm_partials_.data(), gemm_partial_flags_.data()};
+}
+
 Result<HostStreams> Executor::host_streams() {
   for (StreamHandle *s : {&host_in_stream_, &host_stream_, &host_out_stream_}) {
     if (*s != nullptr) continue;

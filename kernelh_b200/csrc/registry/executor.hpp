@@ -56,6 +56,8 @@ public:
   // rank's flag array as mapped on this device, and the epoch to write and wait for (> 0, growing).
   void arm_arrival_flags(std::vector<void *> flags, uint64_t epoch) { arrival_ = {std::move(flags), epoch}; }
   ArrivalFlags take_arrival_flags() { return std::exchange(arrival_, ArrivalFlags{}); }
+  // Scratch of the gemm's split last wave: partial sums and meeting flags (grow-only).
+  Result<std::pair<void *, void *>> gemm_partials(size_t partial_bytes, size_t flag_bytes);
   // The three streams of the host-buffer paths (uploads, compute, downloads), created on first use.
   Result<HostStreams> host_streams();
   // Device staging buffer number `index` of the host-buffer paths, at least `bytes` large (grow-only).
@@ -98,6 +100,7 @@ private:
     EventHandle start, end;
   };
   ArrivalFlags arrival_;
+  Buffer gemm_partials_, gemm_partial_flags_;
   bool profiling_ = false;
   std::vector<ProfiledLaunch> profiled_;
   uint64_t launches_issued_ = 0;

@@ -413,6 +413,35 @@ def test_gemm_8192_sampled_rows_and_scaling_property(ctx, oracle):
     assert np.array_equal(c2, c * 2)
 
 
+def test_gemm_last_wave_split_over_k(ctx, oracle):
+    """80 tiles on 74 clusters: the six tiles of the last wave are each done by two clusters,
+    half of K each, which meet through a scratch of partial sums. Same bound against fp64 as any
+    gemm; the rows of the split tiles are the last ones in rasterised order, so all of C is
+    compared. Twice in a row (the meeting flags start from zero again), then through the fused
+    all-gather with two ranks played one after the other, where the split tiles are also pushed."""
+    m, n, k = 2560, 2048, 512
+    a = oracle.uniform((m, k), oracle.BASE_SEED + 81, -1, 1)
+    b = oracle.uniform((k, n), oracle.BASE_SEED + 82, -1, 1)
+    ref = (a.astype(np.float64) @ b.astype(np.float64)).astype(np.float32)
+    da, db = dev(a), dev(b)
+    for _ in range(2):
+        c = run(ctx, "gemm", f"m={m},n={n},k={k}", [da, db], (m, n))
+        cmp_ = oracle.compare(c, ref)
+        assert cmp_.non_finite == 0 and cmp_.max_rel <= REL * math.sqrt(k) and cmp_.rel_frobenius <= 1e-5
+    replicas = [torch.full((2 * m, n), float("nan"), device="cuda") for _ in range(2)]
+    stream = torch.cuda.current_stream().cuda_stream
+    a2 = np.concatenate([a, a[::-1]])
+    da2 = dev(a2)
+    for rank in range(2):
+        ctx.gemm_allgather(da2[rank * m:(rank + 1) * m], db, replicas, rank, m, n, k, stream)
+    ctx.synchronize(stream)
+    ref2 = np.concatenate([ref, ref[::-1]])
+    for r in replicas:
+        cmp_ = oracle.compare(r.cpu().numpy(), ref2)
+        assert cmp_.non_finite == 0 and cmp_.max_rel <= REL * math.sqrt(k)
+    assert torch.equal(replicas[0], replicas[1])
+
+
 def test_gemm_scaled_store_alpha_beta(ctx, oracle):
     """C = alpha * A.B + beta * C (the first generalisation of the reference's plain store,
     lib/dsl/kernels/gemm.cpp:47-53): alpha = 1, beta = 0 is the plain gemm bit for bit and never
