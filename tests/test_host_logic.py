@@ -335,8 +335,8 @@ def test_ptxas_report_parser():
 def test_every_entry_point_has_resource_figures():
     entries = {"vecadd": ["vecadd"], "fused_gelu": ["fused_gelu", "fused_gelu_bias"], "scan": ["scan"],
                "softmax": ["softmax"], "layernorm": ["layernorm"],
-               "gemm": ["gemm", "gemm_allgather", "gemm_split_a", "gemm_prep_b", "gemm_colmax_b", "gemm_split_bt",
-                        "replicate_run"],
+               "gemm": ["gemm", "gemm_n128", "gemm_allgather", "gemm_allgather_n128", "gemm_split_a", "gemm_prep_b",
+                        "gemm_colmax_b", "gemm_split_bt", "replicate_run"],
                "attention": ["attention", "attention_allgather", "attention_split"]}
     for kernel, names in entries.items():
         for entry in names:
