@@ -268,7 +268,9 @@ __device__ __forceinline__ void multicast_store_float4(float *p, float4 v) {
 // softmax groups finish the current one. kGather: after the 128 x 64 output tile
 // of an item (32 KiB, contiguous) is stored, the group that stored it reads it
 // back from L2 and sends it to the other replicas in 512-byte warp-wide pieces.
-template <bool kGather>
+// kCausal: query i sees keys 0..i (a separate instantiation: the mask costs the softmax threads
+// registers, 5 us of 105 at batch 8 x 16 heads x 1024 when it was a run-time flag).
+template <bool kGather, bool kCausal>
 __device__ __forceinline__ void attention_body(int64_t slices, int64_t seq, float *__restrict__ out,
                                                const khd::TensorMap &tm_q_hi, const khd::TensorMap &tm_q_lo,
                                                const khd::TensorMap &tm_k_hi, const khd::TensorMap &tm_k_lo,
@@ -286,6 +288,11 @@ __device__ __forceinline__ void attention_body(int64_t slices, int64_t seq, floa
   const int64_t q_tiles = (seq + kBQ - 1) / kBQ;
   const int64_t items = slices * q_tiles;
   const int num_kv = static_cast<int>(seq / kBKV);
+  // Key tiles an item (128 query rows starting at row q0 of its slice) goes through. With the causal
+  // mask (query i sees keys <= i) that is up to and including the two 64-key tiles on the item's
+  // diagonal: always an even number, so both softmax groups keep a tile parity each; the rows of the
+  // two diagonal tiles are masked in the softmax. Every role computes the same count.
+  const auto kv_tiles_of = [&](int q0) { return kCausal ? min(num_kv, 2 * (q0 / kBQ) + 2) : num_kv; };
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
   const uint32_t smem_q = (khd::smem_u32(smem_raw) + 1023u) & ~1023u; // two Q tiles (hi, lo each)
@@ -371,7 +378,8 @@ __device__ __forceinline__ void attention_body(int64_t slices, int64_t seq, floa
           khd::tma_load_2d(smem_q + qb * kQBytes, &tm_q_hi, 0, q_row, bar);
           khd::tma_load_2d(smem_q + qb * kQBytes + kQTileBytes, &tm_q_lo, 0, q_row, bar);
         }
-        for (int j = 0; j < num_kv; ++j, ++tile) {
+        const int kv_end = kv_tiles_of(q0);
+        for (int j = 0; j < kv_end; ++j, ++tile) {
           const int s = static_cast<int>(tile % kStages);
           const uint32_t phase = (tile / kStages) & 1u;
           ok = khd::mbar_wait(bar_k_empty + 8 * s, phase ^ 1u, &s_abort, status, khd::kStatusEmptyWaitTimeout,
@@ -423,7 +431,9 @@ __device__ __forceinline__ void attention_body(int64_t slices, int64_t seq, floa
       uint32_t pv_count = 0;   // PV products this warp has issued
       bool ok = true;
       int n = 0;
-      for (int64_t w = blockIdx.x; w < items && ok; w += gridDim.x, ++n, tile_base += static_cast<uint32_t>(num_kv)) {
+      int kv_end = 0;
+      for (int64_t w = blockIdx.x; w < items && ok; w += gridDim.x, ++n, tile_base += static_cast<uint32_t>(kv_end)) {
+        kv_end = kv_tiles_of(static_cast<int>((w % q_tiles) * kBQ));
         const int qb = n & 1;
         ok = khd::mbar_wait(bar_q_full + 8 * qb, static_cast<uint32_t>((n >> 1) & 1), &s_abort, status,
                             khd::kStatusTmaWaitTimeout, 1000u);
@@ -457,21 +467,21 @@ __device__ __forceinline__ void attention_body(int64_t slices, int64_t seq, floa
             }
             khd::umma_commit(bar_s_full + 8 * g);     // scores ready for the softmax threads
             khd::umma_commit(bar_k_empty + 8 * slot); // and this K slot may be refilled
-            if (t + 2 >= num_kv) khd::umma_commit(bar_q_empty + 8 * qb); // this warp's last use of the Q tile
+            if (t + 2 >= kv_end) khd::umma_commit(bar_q_empty + 8 * qb); // this warp's last use of the Q tile
           }
           __syncwarp();
           ++s_count;
           return true;
         };
-        if (g < num_kv) {
+        if (g < kv_end) {
           ok = issue_s(g);
         } else if (leader) {
           khd::mbar_arrive(bar_q_empty + 8 * qb); // no tile of this parity: nothing of Q is used here
         }
-        for (int j = g; j < num_kv && ok; j += 2) {
+        for (int j = g; j < kv_end && ok; j += 2) {
           const uint32_t tile = tile_base + static_cast<uint32_t>(j);
           const int slot = static_cast<int>(tile % kStages);
-          if (j + 2 < num_kv && !issue_s(j + 2)) {
+          if (j + 2 < kv_end && !issue_s(j + 2)) {
             ok = false;
             break;
           }
@@ -548,10 +558,13 @@ __device__ __forceinline__ void attention_body(int64_t slices, int64_t seq, floa
       int shift_k_next = item_shift_k, shift_v_next = item_shift_v;
       bool first = true; // no product of this item to fold in yet
 
-      for (int j = g; j < num_kv && ok; j += 2) {
+      const int q0_item = static_cast<int>((w - bh * q_tiles) * kBQ);
+      const int kv_end = kv_tiles_of(q0_item);
+      const int diagonal = kCausal ? q0_item / kBKV : num_kv; // first key tile that needs the mask
+      for (int j = g; j < kv_end && ok; j += 2) {
         const uint32_t phase = tiles_done & 1u;
         const int shift_k = shift_k_next, shift_v = shift_v_next;
-        if (j + 2 < num_kv) {
+        if (j + 2 < kv_end) {
           shift_k_next = __ldg(k_shifts + j + 2);
           shift_v_next = __ldg(v_shifts + j + 2);
         }
@@ -567,14 +580,26 @@ __device__ __forceinline__ void attention_body(int64_t slices, int64_t seq, floa
         khd::mbar_arrive(bar_s_free + 8 * g); // the score buffer may take S_{j+2}
         // this tile's scores carry 2^(shift_q + shift_k): one positive factor brings them to exp2 units
         const float f = khd::scale_pow2(kLog2eOverSqrtD, -(shift_q + shift_k));
+        if (kCausal && j >= diagonal) {
+          // causal mask on a diagonal tile: this thread's query sees keys 0 .. (its row - the tile's
+          // first key) of the tile; the rest count as -inf (a whole row of them on the second
+          // diagonal tile for the upper 64 queries)
+          const int last_seen = row_in_tile - (j - diagonal) * kBKV;
+#pragma unroll
+          for (int i = 0; i < kBKV; ++i)
+            if (i > last_seen) sv[i] = 0xff800000u; // -inf
+        }
         float mx = -INFINITY;
 #pragma unroll
         for (int i = 0; i < kBKV; ++i) mx = fmaxf(mx, __uint_as_float(sv[i]));
         const float m_new = fmaxf(m, mx * f);
-        const float alpha = fast_exp2(m - m_new); // m = -inf on the first tile gives 0
+        // a row that has seen nothing but masked keys so far keeps max = -inf; its exponentials are
+        // taken against 0 instead (they are all exp2(-inf) = 0), so that no inf - inf arises
+        const float m_ref = (kCausal && m_new == -INFINITY) ? 0.f : m_new;
+        const float alpha = fast_exp2(m - m_ref); // m = -inf on the first tile gives 0
         // P is produced as P * 2^14 straight from the exponent (its split wants that
         // range); the row sum `l` and the output row are kept in the same units.
-        const float offset = static_cast<float>(kPShift) - m_new;
+        const float offset = static_cast<float>(kPShift) - m_ref;
         // (two fp32 per instruction where the arithmetic allows)
         const float2 f2 = make_float2(f, f), offset2 = make_float2(offset, offset);
         float2 sum2 = make_float2(0.f, 0.f);
@@ -777,8 +802,8 @@ attention(KH_MEMREF4(const float, q), KH_MEMREF4(const float, k), KH_MEMREF4(con
   (void)v_stride0; (void)v_stride1; (void)v_stride2; (void)v_stride3;
   (void)o_size0; (void)o_size1; (void)o_size2; (void)o_size3; (void)o_stride0; (void)o_stride1;
   (void)o_stride2; (void)o_stride3; (void)o_alloc;
-  attention_body<false>(q_size0 * q_size1, q_size2, KH_DATA(o), tm_q_hi, tm_q_lo, tm_k_hi, tm_k_lo, tm_vt_hi, tm_vt_lo, shifts, status,
-                        nullptr);
+  attention_body<false, false>(q_size0 * q_size1, q_size2, KH_DATA(o), tm_q_hi, tm_q_lo, tm_k_hi, tm_k_lo, tm_vt_hi, tm_vt_lo, shifts,
+                               status, nullptr);
 }
 
 // The same for (batch, head) slices sharded over several GPUs, with the
@@ -801,6 +826,25 @@ attention_allgather(KH_MEMREF4(const float, q), KH_MEMREF4(const float, k), KH_M
   (void)v_stride0; (void)v_stride1; (void)v_stride2; (void)v_stride3;
   (void)o_size0; (void)o_size1; (void)o_size2; (void)o_size3; (void)o_stride0; (void)o_stride1;
   (void)o_stride2; (void)o_stride3; (void)o_alloc;
-  attention_body<true>(q_size0 * q_size1, q_size2, KH_DATA(o), tm_q_hi, tm_q_lo, tm_k_hi, tm_k_lo, tm_vt_hi, tm_vt_lo, shifts, status,
-                       &targets);
+  attention_body<true, false>(q_size0 * q_size1, q_size2, KH_DATA(o), tm_q_hi, tm_q_lo, tm_k_hi, tm_k_lo, tm_vt_hi, tm_vt_lo, shifts,
+                              status, &targets);
+}
+
+// `attention` with the causal mask (shape key causal=1): query i attends to keys 0..i.
+extern "C" __global__ void __launch_bounds__(kRegisterBoundThreads, 1)
+attention_causal(KH_MEMREF4(const float, q), KH_MEMREF4(const float, k), KH_MEMREF4(const float, v),
+                 KH_MEMREF4(float, o), const __grid_constant__ khd::TensorMap tm_q_hi,
+                 const __grid_constant__ khd::TensorMap tm_q_lo, const __grid_constant__ khd::TensorMap tm_k_hi,
+                 const __grid_constant__ khd::TensorMap tm_k_lo, const __grid_constant__ khd::TensorMap tm_vt_hi,
+                 const __grid_constant__ khd::TensorMap tm_vt_lo, const int *__restrict__ shifts, uint32_t *status) {
+  (void)q_alloc; (void)q_ptr; (void)q_off; (void)q_size3; (void)q_stride0;
+  (void)q_stride1; (void)q_stride2; (void)q_stride3;
+  (void)k_alloc; (void)k_ptr; (void)k_off; (void)k_size0; (void)k_size1; (void)k_size2; (void)k_size3;
+  (void)k_stride0; (void)k_stride1; (void)k_stride2; (void)k_stride3;
+  (void)v_alloc; (void)v_ptr; (void)v_off; (void)v_size0; (void)v_size1; (void)v_size2; (void)v_size3;
+  (void)v_stride0; (void)v_stride1; (void)v_stride2; (void)v_stride3;
+  (void)o_size0; (void)o_size1; (void)o_size2; (void)o_size3; (void)o_stride0; (void)o_stride1;
+  (void)o_stride2; (void)o_stride3; (void)o_alloc;
+  attention_body<false, true>(q_size0 * q_size1, q_size2, KH_DATA(o), tm_q_hi, tm_q_lo, tm_k_hi, tm_k_lo, tm_vt_hi, tm_vt_lo, shifts,
+                              status, nullptr);
 }

@@ -31,6 +31,12 @@ KernelPlan plan_attention(const ShapeMap &shape, const DeviceLimits &l) {
   if (d != kHeadDim)
     throw std::runtime_error("attention template: the kernel is pinned to head_dim = 64 (got "
                              "head_dim = " + std::to_string(d) + ")");
+  // `causal` (optional, 0 or 1): query i attends to keys 0..i only. Not a key of the reference's
+  // template (lib/dsl/kernels/attention.cpp:109-120 has no mask): the first of its generalisations.
+  const int64_t causal = shape.count("causal") ? shape.at("causal") : 0;
+  if (causal != 0 && causal != 1)
+    throw std::runtime_error("attention template: shape attribute 'causal' must be 0 or 1 (got causal = " +
+                             std::to_string(causal) + ")");
   KernelPlan p;
   p.kernel = "attention";
   p.shape = shape;
@@ -47,7 +53,7 @@ KernelPlan plan_attention(const ShapeMap &shape, const DeviceLimits &l) {
   split.grid = {static_cast<unsigned>(std::min<int64_t>(3 * b * h * (s / kBKV), sms * 5)), 1, 1}; // a block per 64-row tile at a time, five blocks resident per SM
   split.param_count = 33 + 7;
   LaunchStep main;
-  main.entry = "attention";
+  main.entry = causal ? "attention_causal" : "attention";
   main.overlap_tail = true; // its set-up runs under the tail of attention_split
   main.block = {512, 1, 1}; // warpgroups: producer + two MMA issuers, two softmax groups, output
   // persistent: a CTA per SM walks the (slice, 128-query tile) work items
@@ -58,6 +64,9 @@ KernelPlan plan_attention(const ShapeMap &shape, const DeviceLimits &l) {
   p.steps = {split, main};
   p.work = 4.0 * static_cast<double>(b) * static_cast<double>(h) * static_cast<double>(s) *
            static_cast<double>(s) * static_cast<double>(d);
+  if (causal) // the unmasked (query, key) pairs: s (s + 1) / 2 of the s^2
+    p.work = 4.0 * static_cast<double>(b) * static_cast<double>(h) * (static_cast<double>(s) * (static_cast<double>(s) + 1.0) / 2.0) *
+             static_cast<double>(d);
   p.work_is_flops = true;
   return p;
 }
@@ -88,7 +97,9 @@ Result<void> launch_attention(Executor &ex, const KernelPlan &p, const std::vect
 
   auto f_split = ex.function("attention", "attention_split");
   if (!f_split) return std::unexpected(f_split.error());
-  auto f_main = ex.function("attention", gather ? "attention_allgather" : "attention");
+  const bool causal = p.shape.count("causal") && p.shape.at("causal") != 0;
+  if (gather && causal) return fail(2, "attention: the fused all-gather has no causal form");
+  auto f_main = ex.function("attention", gather ? "attention_allgather" : p.steps[1].entry);
   if (!f_main) return std::unexpected(f_main.error());
   {
     LaunchArgs args;

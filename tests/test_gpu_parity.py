@@ -775,3 +775,29 @@ def test_registered_kernel_runs_through_the_operator_surface(ctx, oracle):
     with pytest.raises(kh.KernelhError) as e:
         ctx.launch("user_add", f"n={n}", [dev(a), dev(b), dev(a)])
     assert "unknown kernel template 'user_add'" in e.value.message
+
+
+@pytest.mark.parametrize("batch,heads,seq", [(1, 2, 128), (2, 3, 256), (1, 1, 1024), (1, 150, 320)])
+def test_attention_causal_mask(ctx, oracle, batch, heads, seq):
+    """`causal=1`: query i attends to keys 0..i. Reference: an fp64 softmax over the allowed keys
+    (the oracle's routine has no mask: the reference's template has none), on the reference test's
+    kind of inputs; same bound as the unmasked kernel. Row 0 of every slice must equal V's row 0
+    (one key), and the unmasked result must differ (negative control). seq = 128 makes one item of
+    two diagonal tiles, where the upper 64 queries of the second tile see nothing at all;
+    150 slices x 3 query tiles gives the persistent CTAs items of different lengths."""
+    q = oracle.lcg((batch, heads, seq, 64), 0xA77E17)
+    k = oracle.lcg((batch, heads, seq, 64), 0xA77E18)
+    v = oracle.lcg((batch, heads, seq, 64), 0xA77E19)
+    shape = f"batch={batch},heads={heads},seq={seq},head_dim=64"
+    o = run(ctx, "attention", shape + ",causal=1", [q, k, v], (batch, heads, seq, 64))
+    s = np.einsum("bhqd,bhkd->bhqk", q.astype(np.float64), k.astype(np.float64)) / 8.0
+    s = np.where(np.tril(np.ones((seq, seq), bool)), s, -np.inf)
+    p = np.exp(s - s.max(axis=-1, keepdims=True))
+    ref = np.einsum("bhqk,bhkd->bhqd", p / p.sum(axis=-1, keepdims=True), v.astype(np.float64))
+    cmp_ = oracle.compare(o, ref, rtol=2e-3)
+    assert cmp_.non_finite == 0 and cmp_.max_violation <= 2e-3
+    assert cmp_.max_rel <= REL * math.sqrt(seq)
+    assert np.allclose(o[:, :, 0, :], v[:, :, 0, :], rtol=0, atol=1e-6)
+    plain = run(ctx, "attention", shape, [q, k, v], (batch, heads, seq, 64))
+    assert oracle.compare(plain, ref).max_abs > 1e-3
+    assert oracle.compare(plain, oracle.attention_ref(q, k, v), rtol=2e-3).max_violation <= 2e-3  # unmasked path intact

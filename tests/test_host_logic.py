@@ -326,7 +326,8 @@ def test_ptxas_report_parser():
     with pytest.raises(kh.KernelhError) as e:
         kh.parse_ptxas("nothing useful here", None)
     assert "unparseable ptxas output" in e.value.message
-    fixture = "/root/reference/test/fixtures/ptxas_gemm_v.txt"  # the reference's own sample, where its tree is present
+    # the reference's own sample of ptxas output, where its tree is present (REF as in oracle/Makefile)
+    fixture = os.path.join(os.environ.get("REF", "/root/reference"), "test", "fixtures", "ptxas_gemm_v.txt")
     if os.path.exists(fixture):
         got = kh.parse_ptxas(open(fixture).read(), "gemm")
         assert (got["registers"], got["barriers"], got["smem_bytes"]) == (58, 1, 0)
@@ -337,7 +338,7 @@ def test_every_entry_point_has_resource_figures():
                "softmax": ["softmax"], "layernorm": ["layernorm"],
                "gemm": ["gemm", "gemm_n128", "gemm_allgather", "gemm_allgather_n128", "gemm_split_a", "gemm_prep_b",
                         "gemm_colmax_b", "gemm_split_bt", "replicate_run"],
-               "attention": ["attention", "attention_allgather", "attention_split"]}
+               "attention": ["attention", "attention_causal", "attention_allgather", "attention_split"]}
     for kernel, names in entries.items():
         for entry in names:
             fig, text = kh.kernel_resources(kernel, entry)
@@ -443,3 +444,13 @@ def test_sharded_bench_row_refusals():
     with pytest.raises(kh.KernelhError) as e:
         kh.bench_sharded(2, "gemm", "")
     assert e.value.code in (2, 77)
+
+
+def test_attention_causal_shape_key():
+    """`causal` is an optional 0/1 key of the attention template (not one of the reference's)."""
+    p = kh.plan("attention", "batch=8,heads=16,seq=1024,head_dim=64,causal=1")
+    assert p.entry == b"attention_causal" and p.work == 4.0 * 128 * (1024 * 1025 / 2) * 64
+    assert kh.plan("attention", "batch=8,heads=16,seq=1024,head_dim=64,causal=0").work == 34359738368.0
+    with pytest.raises(kh.KernelhError) as e:
+        kh.plan("attention", "batch=8,heads=16,seq=1024,head_dim=64,causal=2")
+    assert e.value.code == 2 and "'causal' must be 0 or 1" in e.value.message
