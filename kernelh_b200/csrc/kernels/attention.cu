@@ -1,5 +1,6 @@
 // attention: O = softmax(Q K^T / sqrt(d)) V, non-causal, fp32, d = 64,
-// tensors [batch, heads, seq, 64] contiguous, seq a multiple of 64.
+// tensors [batch, heads, seq, 64] contiguous (seq a multiple of 64 in the plain entries; any seq
+// and the causal mask in `attention_masked`).
 //
 // Replaces the kernel the reference generates from
 // lib/dsl/kernels/attention.cpp:86-289 (one 64-thread block per query row,
@@ -136,7 +137,7 @@ __device__ __forceinline__ uint32_t half2_bits(__half2 h) { return *reinterpret_
 } // namespace
 
 // Q, K, V [bh, seq, 64] -> q_hi, q_lo, k_hi, k_lo [bh*seq, 64] and vt_hi, vt_lo
-// [bh*64, seq] (V transposed per (batch, head)) as fp16. The unit of scaling is
+// [bh*64, seq] (V transposed per (batch, head)) as fp16 (seq rounded up to whole 64-row tiles in all six). The unit of scaling is
 // a tile of 64 rows (queries or keys) of one slice: a block takes one tile of one
 // tensor at a time, finds its largest magnitude, and writes the two splits scaled
 // by the exponent that gives; shifts[(t * bh + slice) * tiles + tile] receives
@@ -154,34 +155,48 @@ attention_split(KH_MEMREF4(const float, q), KH_MEMREF4(const float, k), KH_MEMRE
   // instructions each, several per tile and thread, which once made this kernel issue-bound):
   // a tensor has bh * seq / 64 tiles (< 2^31 for anything that fits the GPU), a tile's source is
   // 4096 contiguous floats, and only V needs (slice, tile) separately.
-  const uint32_t tiles = static_cast<uint32_t>(seq >> 6);
+  // seq need not be a multiple of 64: the last tile of a slice is then short, its missing rows count
+  // as zeros, and the splits are laid out with every slice padded to whole tiles (seq_p rows).
+  const uint32_t tiles = static_cast<uint32_t>((seq + 63) >> 6);
+  const bool ragged = (seq & 63) != 0;
+  const int64_t seq_p = static_cast<int64_t>(tiles) << 6;
   const uint32_t per_tensor = static_cast<uint32_t>(bh) * tiles;
   const uint32_t jobs = 3u * per_tensor;
   const float *const src_q = KH_DATA(q), *const src_k = KH_DATA(k), *const src_v = KH_DATA(v);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   // the tile of a job is 64 x 64 contiguous values = 1024 float4; a thread takes float4 tid, tid + 256, ...
   const auto tensor_of = [&](uint32_t job) { return (job >= per_tensor ? 1u : 0u) + (job >= 2u * per_tensor ? 1u : 0u); };
-  const auto tile_of = [&](uint32_t job) {
+  // loads a job's tile: float4 tid + 256 j of the tile is group tid % 16 of row tid / 16 + 16 j
+  const auto load_tile = [&](uint32_t job, float4 &a0, float4 &a1, float4 &a2, float4 &a3) {
     const uint32_t t = tensor_of(job), rest = job - t * per_tensor; // rest = slice * tiles + tile
     const float *base = t == 0 ? src_q : (t == 1 ? src_k : src_v); // selects, not an indexed local array
-    return reinterpret_cast<const float4 *>(base + static_cast<size_t>(rest) * (64 * kHeadDim)) + threadIdx.x;
+    if (!ragged) {
+      const float4 *p = reinterpret_cast<const float4 *>(base + static_cast<size_t>(rest) * (64 * kHeadDim)) + threadIdx.x;
+      a0 = __ldcs(p); a1 = __ldcs(p + 256); a2 = __ldcs(p + 512); a3 = __ldcs(p + 768);
+      return;
+    }
+    const uint32_t slice = rest / tiles, tile_in_slice = rest - slice * tiles;
+    const int valid = min(64, static_cast<int>(seq - static_cast<int64_t>(tile_in_slice) * 64)); // rows the tile really has
+    const float4 *p = reinterpret_cast<const float4 *>(base + (static_cast<size_t>(slice) * seq + tile_in_slice * 64) * kHeadDim) +
+                      threadIdx.x;
+    const int row = static_cast<int>(threadIdx.x >> 4);
+    const float4 zero = make_float4(0.f, 0.f, 0.f, 0.f);
+    a0 = row < valid ? __ldcs(p) : zero;
+    a1 = row + 16 < valid ? __ldcs(p + 256) : zero;
+    a2 = row + 32 < valid ? __ldcs(p + 512) : zero;
+    a3 = row + 48 < valid ? __ldcs(p + 768) : zero;
   };
   // The attention kernel that follows may be scheduled as soon as SMs drain: its CTAs set up
   // their barriers and tensor memory and then wait for this whole grid before reading anything.
   khd::grid_dependents_may_launch();
   float4 n0 = make_float4(0.f, 0.f, 0.f, 0.f), n1 = n0, n2 = n0, n3 = n0;
-  if (blockIdx.x < jobs) {
-    const float4 *p = tile_of(blockIdx.x);
-    n0 = __ldcs(p); n1 = __ldcs(p + 256); n2 = __ldcs(p + 512); n3 = __ldcs(p + 768);
-  }
+  if (blockIdx.x < jobs) load_tile(blockIdx.x, n0, n1, n2, n3);
   int parity = 0;
   for (uint32_t job = blockIdx.x; job < jobs; job += gridDim.x, parity ^= 1) {
     const uint32_t t = tensor_of(job), rest = job - t * per_tensor;
     const float4 f0 = n0, f1 = n1, f2 = n2, f3 = n3;
-    if (job + gridDim.x < jobs) { // the next tile's loads fly while this one is worked on (jobs < 2^31 - grid)
-      const float4 *p = tile_of(job + gridDim.x);
-      n0 = __ldcs(p); n1 = __ldcs(p + 256); n2 = __ldcs(p + 512); n3 = __ldcs(p + 768);
-    }
+    // the next tile's loads fly while this one is worked on (jobs < 2^31 - grid)
+    if (job + gridDim.x < jobs) load_tile(job + gridDim.x, n0, n1, n2, n3);
     float m = fmaxf(fmaxf(fmaxf(fabsf(f0.x), fabsf(f0.y)), fmaxf(fabsf(f0.z), fabsf(f0.w))),
                     fmaxf(fmaxf(fabsf(f1.x), fabsf(f1.y)), fmaxf(fabsf(f1.z), fabsf(f1.w))));
     m = fmaxf(m, fmaxf(fmaxf(fmaxf(fabsf(f2.x), fabsf(f2.y)), fmaxf(fabsf(f2.z), fabsf(f2.w))),
@@ -232,7 +247,7 @@ attention_split(KH_MEMREF4(const float, q), KH_MEMREF4(const float, k), KH_MEMRE
 #pragma unroll
         for (int qd = 0; qd < 4; ++qd) x[qd] = make_float2(tile[sgroup * 8 + 2 * qd][col], tile[sgroup * 8 + 2 * qd + 1][col]);
         split_fp16_pairs<4>(x, sc, h.v, l.v);
-        const int64_t o = (static_cast<int64_t>(slice) * kHeadDim + dl) * seq + s0 + sgroup * 8;
+        const int64_t o = (static_cast<int64_t>(slice) * kHeadDim + dl) * seq_p + s0 + sgroup * 8;
         *reinterpret_cast<Half8 *>(vt_hi + o) = h;
         *reinterpret_cast<Half8 *>(vt_lo + o) = l;
       }
@@ -268,14 +283,15 @@ __device__ __forceinline__ void multicast_store_float4(float *p, float4 v) {
 // softmax groups finish the current one. kGather: after the 128 x 64 output tile
 // of an item (32 KiB, contiguous) is stored, the group that stored it reads it
 // back from L2 and sends it to the other replicas in 512-byte warp-wide pieces.
-// kCausal: query i sees keys 0..i (a separate instantiation: the mask costs the softmax threads
-// registers, 5 us of 105 at batch 8 x 16 heads x 1024 when it was a run-time flag).
-template <bool kGather, bool kCausal>
+// kMask: the instantiation that can mask scores - `causal` (query i sees keys 0..i) and / or a seq
+// that is not a multiple of 64 (the last key tile's missing keys). Separate from the plain one: the
+// mask costs the softmax threads registers, 5 us of 105 at batch 8 x 16 heads x 1024 as a run-time flag.
+template <bool kGather, bool kMask>
 __device__ __forceinline__ void attention_body(int64_t slices, int64_t seq, float *__restrict__ out,
                                                const khd::TensorMap &tm_q_hi, const khd::TensorMap &tm_q_lo,
                                                const khd::TensorMap &tm_k_hi, const khd::TensorMap &tm_k_lo,
                                                const khd::TensorMap &tm_vt_hi, const khd::TensorMap &tm_vt_lo,
-                                               const int *__restrict__ shifts, uint32_t *status,
+                                               const int *__restrict__ shifts, uint32_t *status, int causal_flag,
                                                const GatherOut *targets) {
   extern __shared__ uint8_t smem_raw[];
   // q_full[2], q_empty[2], k_full, k_empty, v_full, v_empty [kStages each], s_full[2], s_free[2],
@@ -285,14 +301,16 @@ __device__ __forceinline__ void attention_body(int64_t slices, int64_t seq, floa
   __shared__ int s_abort;
   __shared__ float s_row_m[2][kBQ], s_row_l[2][kBQ]; // max and sum that go with a group's parked row
 
+  const bool causal = kMask && causal_flag != 0;
+  const int64_t seq_p = (seq + kBKV - 1) / kBKV * kBKV; // rows a slice has in the splits (whole 64-row tiles)
   const int64_t q_tiles = (seq + kBQ - 1) / kBQ;
   const int64_t items = slices * q_tiles;
-  const int num_kv = static_cast<int>(seq / kBKV);
+  const int num_kv = static_cast<int>(seq_p / kBKV);
   // Key tiles an item (128 query rows starting at row q0 of its slice) goes through. With the causal
   // mask (query i sees keys <= i) that is up to and including the two 64-key tiles on the item's
   // diagonal: always an even number, so both softmax groups keep a tile parity each; the rows of the
   // two diagonal tiles are masked in the softmax. Every role computes the same count.
-  const auto kv_tiles_of = [&](int q0) { return kCausal ? min(num_kv, 2 * (q0 / kBQ) + 2) : num_kv; };
+  const auto kv_tiles_of = [&](int q0) { return causal ? min(num_kv, 2 * (q0 / kBQ) + 2) : num_kv; };
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
   const uint32_t smem_q = (khd::smem_u32(smem_raw) + 1023u) & ~1023u; // two Q tiles (hi, lo each)
@@ -373,7 +391,7 @@ __device__ __forceinline__ void attention_body(int64_t slices, int64_t seq, floa
         if (!ok) break;
         {
           const uint32_t bar = bar_q_full + 8 * qb;
-          const int q_row = static_cast<int>(bh * seq) + q0;
+          const int q_row = static_cast<int>(bh * seq_p) + q0;
           khd::mbar_arrive_expect_tx(bar, kQBytes);
           khd::tma_load_2d(smem_q + qb * kQBytes, &tm_q_hi, 0, q_row, bar);
           khd::tma_load_2d(smem_q + qb * kQBytes + kQTileBytes, &tm_q_lo, 0, q_row, bar);
@@ -389,7 +407,7 @@ __device__ __forceinline__ void attention_body(int64_t slices, int64_t seq, floa
             const uint32_t st = smem_k + s * kHalfStageBytes;
             const uint32_t bar = bar_k_full + 8 * s;
             khd::mbar_arrive_expect_tx(bar, kHalfStageBytes);
-            const int k_row = static_cast<int>(bh * seq) + j * kBKV;
+            const int k_row = static_cast<int>(bh * seq_p) + j * kBKV;
             khd::tma_load_2d(st, &tm_k_hi, 0, k_row, bar);
             khd::tma_load_2d(st + kKVTileBytes, &tm_k_lo, 0, k_row, bar);
           }
@@ -560,7 +578,8 @@ __device__ __forceinline__ void attention_body(int64_t slices, int64_t seq, floa
 
       const int q0_item = static_cast<int>((w - bh * q_tiles) * kBQ);
       const int kv_end = kv_tiles_of(q0_item);
-      const int diagonal = kCausal ? q0_item / kBKV : num_kv; // first key tile that needs the mask
+      const int diagonal = causal ? q0_item / kBKV : num_kv; // first key tile that needs the causal mask
+      const int keys_in_last = static_cast<int>(seq - static_cast<int64_t>(num_kv - 1) * kBKV); // 64 unless seq is ragged
       for (int j = g; j < kv_end && ok; j += 2) {
         const uint32_t phase = tiles_done & 1u;
         const int shift_k = shift_k_next, shift_v = shift_v_next;
@@ -580,11 +599,14 @@ __device__ __forceinline__ void attention_body(int64_t slices, int64_t seq, floa
         khd::mbar_arrive(bar_s_free + 8 * g); // the score buffer may take S_{j+2}
         // this tile's scores carry 2^(shift_q + shift_k): one positive factor brings them to exp2 units
         const float f = khd::scale_pow2(kLog2eOverSqrtD, -(shift_q + shift_k));
-        if (kCausal && j >= diagonal) {
-          // causal mask on a diagonal tile: this thread's query sees keys 0 .. (its row - the tile's
-          // first key) of the tile; the rest count as -inf (a whole row of them on the second
-          // diagonal tile for the upper 64 queries)
-          const int last_seen = row_in_tile - (j - diagonal) * kBKV;
+        if (kMask && (j >= diagonal || j == num_kv - 1)) {
+          // Keys of this tile the thread's query sees: all 64; on a diagonal tile of the causal mask
+          // only 0 .. (its row - the tile's first key) (none at all on the second diagonal tile for the
+          // upper 64 queries); in the last tile of a ragged seq only the keys that exist. The rest
+          // count as -inf.
+          int last_seen = kBKV - 1;
+          if (j >= diagonal) last_seen = row_in_tile - (j - diagonal) * kBKV;
+          if (j == num_kv - 1) last_seen = min(last_seen, keys_in_last - 1);
 #pragma unroll
           for (int i = 0; i < kBKV; ++i)
             if (i > last_seen) sv[i] = 0xff800000u; // -inf
@@ -595,7 +617,7 @@ __device__ __forceinline__ void attention_body(int64_t slices, int64_t seq, floa
         const float m_new = fmaxf(m, mx * f);
         // a row that has seen nothing but masked keys so far keeps max = -inf; its exponentials are
         // taken against 0 instead (they are all exp2(-inf) = 0), so that no inf - inf arises
-        const float m_ref = (kCausal && m_new == -INFINITY) ? 0.f : m_new;
+        const float m_ref = (kMask && m_new == -INFINITY) ? 0.f : m_new;
         const float alpha = fast_exp2(m - m_ref); // m = -inf on the first tile gives 0
         // P is produced as P * 2^14 straight from the exponent (its split wants that
         // range); the row sum `l` and the output row are kept in the same units.
@@ -803,7 +825,7 @@ attention(KH_MEMREF4(const float, q), KH_MEMREF4(const float, k), KH_MEMREF4(con
   (void)o_size0; (void)o_size1; (void)o_size2; (void)o_size3; (void)o_stride0; (void)o_stride1;
   (void)o_stride2; (void)o_stride3; (void)o_alloc;
   attention_body<false, false>(q_size0 * q_size1, q_size2, KH_DATA(o), tm_q_hi, tm_q_lo, tm_k_hi, tm_k_lo, tm_vt_hi, tm_vt_lo, shifts,
-                               status, nullptr);
+                               status, 0, nullptr);
 }
 
 // The same for (batch, head) slices sharded over several GPUs, with the
@@ -827,16 +849,18 @@ attention_allgather(KH_MEMREF4(const float, q), KH_MEMREF4(const float, k), KH_M
   (void)o_size0; (void)o_size1; (void)o_size2; (void)o_size3; (void)o_stride0; (void)o_stride1;
   (void)o_stride2; (void)o_stride3; (void)o_alloc;
   attention_body<true, false>(q_size0 * q_size1, q_size2, KH_DATA(o), tm_q_hi, tm_q_lo, tm_k_hi, tm_k_lo, tm_vt_hi, tm_vt_lo, shifts,
-                              status, &targets);
+                              status, 0, &targets);
 }
 
-// `attention` with the causal mask (shape key causal=1): query i attends to keys 0..i.
+// `attention` for the shapes that need scores masked: the causal mask (shape key causal=1: query i
+// attends to keys 0..i) and / or a seq that is not a multiple of 64. One more parameter: `causal`.
 extern "C" __global__ void __launch_bounds__(kRegisterBoundThreads, 1)
-attention_causal(KH_MEMREF4(const float, q), KH_MEMREF4(const float, k), KH_MEMREF4(const float, v),
+attention_masked(KH_MEMREF4(const float, q), KH_MEMREF4(const float, k), KH_MEMREF4(const float, v),
                  KH_MEMREF4(float, o), const __grid_constant__ khd::TensorMap tm_q_hi,
                  const __grid_constant__ khd::TensorMap tm_q_lo, const __grid_constant__ khd::TensorMap tm_k_hi,
                  const __grid_constant__ khd::TensorMap tm_k_lo, const __grid_constant__ khd::TensorMap tm_vt_hi,
-                 const __grid_constant__ khd::TensorMap tm_vt_lo, const int *__restrict__ shifts, uint32_t *status) {
+                 const __grid_constant__ khd::TensorMap tm_vt_lo, const int *__restrict__ shifts, uint32_t *status,
+                 int causal) {
   (void)q_alloc; (void)q_ptr; (void)q_off; (void)q_size3; (void)q_stride0;
   (void)q_stride1; (void)q_stride2; (void)q_stride3;
   (void)k_alloc; (void)k_ptr; (void)k_off; (void)k_size0; (void)k_size1; (void)k_size2; (void)k_size3;
@@ -846,5 +870,5 @@ attention_causal(KH_MEMREF4(const float, q), KH_MEMREF4(const float, k), KH_MEMR
   (void)o_size0; (void)o_size1; (void)o_size2; (void)o_size3; (void)o_stride0; (void)o_stride1;
   (void)o_stride2; (void)o_stride3; (void)o_alloc;
   attention_body<false, true>(q_size0 * q_size1, q_size2, KH_DATA(o), tm_q_hi, tm_q_lo, tm_k_hi, tm_k_lo, tm_vt_hi, tm_vt_lo, shifts,
-                              status, nullptr);
+                              status, causal, nullptr);
 }

@@ -25,9 +25,6 @@ KernelPlan plan_attention(const ShapeMap &shape, const DeviceLimits &l) {
   if (b <= 0 || h <= 0 || s <= 0 || d <= 0)
     throw std::runtime_error("attention template: shape attributes 'batch', 'heads', 'seq' and "
                              "'head_dim' must be positive");
-  if (s % kBKV != 0)
-    throw std::runtime_error("attention template: shape attribute 'seq' must be divisible by the "
-                             "K/V tile extent 64 (got seq = " + std::to_string(s) + ")");
   if (d != kHeadDim)
     throw std::runtime_error("attention template: the kernel is pinned to head_dim = 64 (got "
                              "head_dim = " + std::to_string(d) + ")");
@@ -42,24 +39,28 @@ KernelPlan plan_attention(const ShapeMap &shape, const DeviceLimits &l) {
   p.shape = shape;
   for (const char *name : {"Q", "K", "V"}) p.tensors.push_back({name, {b, h, s, d}, false});
   p.tensors.push_back({"O", {b, h, s, d}, true});
-  const int64_t elems = b * h * s * d;
+  // The reference pins seq to a multiple of its 64-key tile (lib/dsl/kernels/attention.cpp:109-120);
+  // here any seq runs: the splits pad every slice to whole tiles and the last tile's missing keys are masked.
+  const int64_t tiles = (s + kBKV - 1) / kBKV, s_padded = tiles * kBKV;
+  const int64_t elems = b * h * s_padded * d;
   // six fp16 arrays, then one exponent per 64-row tile of Q, K and V
-  p.workspace_bytes = static_cast<size_t>(elems) * 2 * 6 + static_cast<size_t>(b * h * (s / kBKV)) * 3 * 4;
+  p.workspace_bytes = static_cast<size_t>(elems) * 2 * 6 + static_cast<size_t>(b * h * tiles) * 3 * 4;
   long sms = query_cu_count(l);
   if (sms <= 0) sms = 148;
   LaunchStep split;
   split.entry = "attention_split";
   split.block = {256, 1, 1};
-  split.grid = {static_cast<unsigned>(std::min<int64_t>(3 * b * h * (s / kBKV), sms * 5)), 1, 1}; // a block per 64-row tile at a time, five blocks resident per SM
+  split.grid = {static_cast<unsigned>(std::min<int64_t>(3 * b * h * tiles, sms * 5)), 1, 1}; // a block per 64-row tile at a time, five blocks resident per SM
   split.param_count = 33 + 7;
   LaunchStep main;
-  main.entry = causal ? "attention_causal" : "attention";
+  const bool masked = causal != 0 || s % kBKV != 0;
+  main.entry = masked ? "attention_masked" : "attention";
   main.overlap_tail = true; // its set-up runs under the tail of attention_split
   main.block = {512, 1, 1}; // warpgroups: producer + two MMA issuers, two softmax groups, output
   // persistent: a CTA per SM walks the (slice, 128-query tile) work items
   main.grid = {static_cast<unsigned>(std::min<int64_t>(b * h * ((s + kBQ - 1) / kBQ), sms)), 1, 1};
   main.dynamic_smem = kAttnSmem;
-  main.param_count = 44 + 6 + 2;
+  main.param_count = 44 + 6 + 2 + (masked ? 1 : 0);
   main.tmem_columns = 512;
   p.steps = {split, main};
   p.work = 4.0 * static_cast<double>(b) * static_cast<double>(h) * static_cast<double>(s) *
@@ -85,7 +86,8 @@ Result<void> launch_attention(Executor &ex, const KernelPlan &p, const std::vect
     return fail(2, std::string("attention: buffer '") + bad +
                        "' is not 16-byte aligned; the kernel reads and writes 128-bit vectors and has no scalar path");
   const std::vector<int64_t> &shape = p.tensors[0].shape;
-  const int64_t bh = shape[0] * shape[1], s = shape[2];
+  const int64_t bh = shape[0] * shape[1], seq = shape[2];
+  const int64_t s = (seq + kBKV - 1) / kBKV * kBKV; // rows of a slice in the splits: whole 64-row tiles
   const int64_t elems = bh * s * kHeadDim;
   auto ws = ex.workspace(p.workspace_bytes);
   if (!ws) return std::unexpected(ws.error());
@@ -98,7 +100,10 @@ Result<void> launch_attention(Executor &ex, const KernelPlan &p, const std::vect
   auto f_split = ex.function("attention", "attention_split");
   if (!f_split) return std::unexpected(f_split.error());
   const bool causal = p.shape.count("causal") && p.shape.at("causal") != 0;
-  if (gather && causal) return fail(2, "attention: the fused all-gather has no causal form");
+  const bool masked = causal || seq % kBKV != 0;
+  if (gather && masked)
+    return fail(2, "attention: the fused all-gather takes whole 64-key tiles and no causal mask (seq = " +
+                       std::to_string(seq) + (causal ? ", causal" : "") + ")");
   auto f_main = ex.function("attention", gather ? "attention_allgather" : p.steps[1].entry);
   if (!f_main) return std::unexpected(f_main.error());
   {
@@ -108,7 +113,7 @@ Result<void> launch_attention(Executor &ex, const KernelPlan &p, const std::vect
       args.add_scalar<uint64_t>(reinterpret_cast<uint64_t>(ptr));
     if (auto r = ex.launch(*f_split, p.steps[0], args, stream); !r) return r;
   }
-  // Q, K: [bh*seq rows, 64 fp16]; V^T: [bh*64 rows, seq fp16]. 64-column boxes = one 128-byte swizzle row.
+  // Q, K: [bh*s rows, 64 fp16]; V^T: [bh*64 rows, s fp16] (s = seq padded to whole tiles). 64-column boxes = one 128-byte swizzle row.
   auto make_map = [&](const char *ptr, int64_t cols, int64_t rows, uint32_t box_rows) {
     TensorMapSpec t;
     t.global_address = ptr;
@@ -138,6 +143,7 @@ Result<void> launch_attention(Executor &ex, const KernelPlan &p, const std::vect
   }
   args.add_scalar<uint64_t>(reinterpret_cast<uint64_t>(shifts));
   args.add_scalar<uint64_t>(reinterpret_cast<uint64_t>(ex.status_word()));
+  if (masked) args.add_scalar<int64_t>(causal ? 1 : 0);
   LaunchStep step = p.steps[1];
   if (gather) {
     args.add_struct_bytes(gather, sizeof *gather);

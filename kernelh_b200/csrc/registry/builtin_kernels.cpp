@@ -629,16 +629,32 @@ namespace {
 // block i is split and multiplied and the finished rows of C of block i-1 go
 // back down (the two directions of the link run at once). `dev` are device
 // staging buffers for A, B and C.
+// Row blocks of the host-buffer product: about eight blocks of whole 256-row cluster tiles
+// (sixteen measured slower: more launches and tensor maps per step than the shorter tail saves),
+// except that the LAST block is cut again into a half and two quarters: what follows the last
+// upload - that block's split, product and the trip of its rows of C back - is the part of the
+// step nothing overlaps, and it shrinks with the block.
+std::vector<std::pair<int64_t, int64_t>> host_row_blocks(int64_t m) {
+  const int64_t block_rows = std::max<int64_t>(256, ((m + 7) / 8 + 255) / 256 * 256);
+  std::vector<std::pair<int64_t, int64_t>> blocks;
+  for (int64_t row0 = 0; row0 < m; row0 += block_rows) blocks.push_back({row0, std::min(block_rows, m - row0)});
+  const auto [last0, last_rows] = blocks.back();
+  if (blocks.size() > 1 && last_rows >= 1024 && last_rows % 1024 == 0) {
+    blocks.pop_back();
+    blocks.push_back({last0, last_rows / 2});
+    blocks.push_back({last0 + last_rows / 2, last_rows / 4});
+    blocks.push_back({last0 + 3 * last_rows / 4, last_rows / 4});
+  }
+  return blocks;
+}
+
 Result<void> run_gemm_host(Executor &ex, const KernelPlan &p, const std::vector<void *> &host,
                            const std::vector<void *> &dev, const HostStreams &hs) {
   const int64_t m = p.tensors[0].shape[0], k = p.tensors[0].shape[1], n = p.tensors[1].shape[1];
   Backend &be = ex.backend();
   auto job = gemm_job(ex, m, n, k);
   if (!job) return std::unexpected(job.error());
-  // row blocks: about eight, whole 256-row cluster tiles (sixteen measured slower: more
-  // launches and tensor maps per step than the shorter tail after the last upload saves)
-  const int64_t block_rows = std::max<int64_t>(256, ((m + 7) / 8 + 255) / 256 * 256);
-  const int64_t blocks = (m + block_rows - 1) / block_rows;
+  const std::vector<std::pair<int64_t, int64_t>> blocks = host_row_blocks(m);
   std::vector<EventHandle> events;
   const auto fresh_event = [&]() -> Result<EventHandle> {
     auto e = be.event_create();
@@ -653,8 +669,7 @@ Result<void> run_gemm_host(Executor &ex, const KernelPlan &p, const std::vector<
     if (auto r = be.event_record(*b_up, hs.in); !r) return r;
     if (auto r = be.stream_wait_event(hs.compute, *b_up); !r) return r;
     if (auto r = gemm_enqueue_b(*job, dev[1], hs.compute, true); !r) return r;
-    for (int64_t i = 0; i < blocks; ++i) {
-      const int64_t row0 = i * block_rows, rows = std::min(block_rows, m - row0);
+    for (const auto &[row0, rows] : blocks) {
       char *a_rows = static_cast<char *>(dev[0]) + static_cast<size_t>(row0 * k) * 4;
       char *c_rows = static_cast<char *>(dev[2]) + static_cast<size_t>(row0 * n) * 4;
       if (host[0] != nullptr)
@@ -832,11 +847,9 @@ Result<void> run_gemm_host_sharded_begin(Executor &ex, const void *a_shard_host,
     if (auto r = ex.launch(*push, step, args, hs->compute); !r) return r;
   }
   // the A shard: in row blocks, each with its own event (the uploads go on while the ranks meet)
-  const int64_t block_rows = std::max<int64_t>(256, ((m_shard + 7) / 8 + 255) / 256 * 256);
-  const int64_t blocks = (m_shard + block_rows - 1) / block_rows;
+  const std::vector<std::pair<int64_t, int64_t>> blocks = host_row_blocks(m_shard);
   std::vector<EventHandle> a_events;
-  for (int64_t i = 0; i < blocks; ++i) {
-    const int64_t row0 = i * block_rows, rows = std::min(block_rows, m_shard - row0);
+  for (const auto &[row0, rows] : blocks) {
     if (auto r = be.memcpy_h2d_async(static_cast<char *>(*dev_a) + static_cast<size_t>(row0 * k) * 4,
                                      static_cast<const char *>(a_shard_host) + static_cast<size_t>(row0 * k) * 4,
                                      static_cast<size_t>(rows * k) * 4, hs->in);
@@ -858,17 +871,16 @@ Result<void> run_gemm_host_sharded_begin(Executor &ex, const void *a_shard_host,
   const HostStreams streams = *hs;
   void *a_dev = *dev_a, *c_dev = *dev_c;
   const GemmJob j = *job;
-  ex.pending_host_finish = [&ex, j, streams, a_dev, c_dev, b_local, a_events, m_shard, n, k, block_rows,
-                            blocks](void *c_host) -> Result<void> {
+  ex.pending_host_finish = [&ex, j, streams, a_dev, c_dev, b_local, a_events, n, k, blocks](void *c_host) -> Result<void> {
     Backend &be2 = ex.backend();
     std::vector<EventHandle> events = a_events;
     const auto body = [&]() -> Result<void> {
       if (auto r = gemm_enqueue_b(j, b_local, streams.compute, true); !r) return r;
-      for (int64_t i = 0; i < blocks; ++i) {
-        const int64_t row0 = i * block_rows, rows = std::min(block_rows, m_shard - row0);
+      for (size_t i = 0; i < blocks.size(); ++i) {
+        const auto [row0, rows] = blocks[i];
         char *a_rows = static_cast<char *>(a_dev) + static_cast<size_t>(row0 * k) * 4;
         char *c_rows = static_cast<char *>(c_dev) + static_cast<size_t>(row0 * n) * 4;
-        if (auto r = be2.stream_wait_event(streams.compute, a_events[static_cast<size_t>(i)]); !r) return r;
+        if (auto r = be2.stream_wait_event(streams.compute, a_events[i]); !r) return r;
         const std::vector<LaunchStep> steps = gemm_steps(rows, n, k, ex.limits());
         if (auto r = gemm_enqueue_a(j, a_rows, row0, rows, steps[0], streams.compute, 0); !r) return r;
         if (auto r = gemm_enqueue_multiply(j, a_rows, b_local, c_rows, row0, rows, steps[3], streams.compute, nullptr);

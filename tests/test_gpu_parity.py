@@ -801,3 +801,31 @@ def test_attention_causal_mask(ctx, oracle, batch, heads, seq):
     plain = run(ctx, "attention", shape, [q, k, v], (batch, heads, seq, 64))
     assert oracle.compare(plain, ref).max_abs > 1e-3
     assert oracle.compare(plain, oracle.attention_ref(q, k, v), rtol=2e-3).max_violation <= 2e-3  # unmasked path intact
+
+
+@pytest.mark.parametrize("batch,heads,seq,causal", [(1, 2, 100, 0), (2, 2, 333, 0), (1, 1, 1000, 0), (1, 3, 65, 0),
+                                                     (1, 1, 40, 0), (2, 2, 200, 1), (1, 2, 1000, 1)])
+def test_attention_ragged_seq(ctx, oracle, batch, heads, seq, causal):
+    """seq that is not a multiple of the 64-key tile (the reference refuses it): the last tile's
+    missing keys are masked and its missing queries are not stored. Against an fp64 softmax on the
+    reference test's kind of inputs, with and without the causal mask; the rows after the output
+    (a canary slice) stay untouched."""
+    q = oracle.lcg((batch, heads, seq, 64), 0xA77E27)
+    k = oracle.lcg((batch, heads, seq, 64), 0xA77E28)
+    v = oracle.lcg((batch, heads, seq, 64), 0xA77E29)
+    shape = f"batch={batch},heads={heads},seq={seq},head_dim=64" + (",causal=1" if causal else "")
+    out = torch.full((batch * heads * seq * 64 + 4096,), float("nan"), device="cuda")
+    bufs = [dev(q), dev(k), dev(v), out]
+    ctx.launch("attention", shape, bufs, torch.cuda.current_stream().cuda_stream)
+    ctx.synchronize(torch.cuda.current_stream().cuda_stream)
+    got = out.cpu().numpy()
+    assert np.isnan(got[batch * heads * seq * 64:]).all()  # nothing written past the last real query
+    o = got[:batch * heads * seq * 64].reshape(batch, heads, seq, 64)
+    s = np.einsum("bhqd,bhkd->bhqk", q.astype(np.float64), k.astype(np.float64)) / 8.0
+    if causal:
+        s = np.where(np.tril(np.ones((seq, seq), bool)), s, -np.inf)
+    p = np.exp(s - s.max(axis=-1, keepdims=True))
+    ref = np.einsum("bhqk,bhkd->bhqd", p / p.sum(axis=-1, keepdims=True), v.astype(np.float64))
+    cmp_ = oracle.compare(o, ref, rtol=2e-3)
+    assert cmp_.non_finite == 0 and cmp_.max_violation <= 2e-3
+    assert cmp_.max_rel <= REL * math.sqrt(seq)

@@ -164,9 +164,11 @@ def test_shape_value_rules():
         with pytest.raises(kh.KernelhError) as e:
             kh.plan(kernel, shape)
         assert "must be positive" in e.value.message
-    with pytest.raises(kh.KernelhError) as e:
-        kh.plan("attention", "batch=1,heads=1,seq=100,head_dim=64")
-    assert "divisible by the K/V tile extent 64 (got seq = 100)" in e.value.message
+    # seq need not be a multiple of the 64-key tile (the reference's template refuses that,
+    # lib/dsl/kernels/attention.cpp:109-120): such shapes take the entry that masks the missing keys
+    p = kh.plan("attention", "batch=1,heads=1,seq=100,head_dim=64")
+    assert p.entry == b"attention_masked" and p.param_count == 53
+    assert p.workspace_bytes == 128 * 64 * 2 * 6 + 2 * 3 * 4  # the splits hold whole tiles: 128 rows
     with pytest.raises(kh.KernelhError) as e:
         kh.plan("attention", "batch=1,heads=1,seq=128,head_dim=32")
     assert "pinned to head_dim = 64" in e.value.message
@@ -338,7 +340,7 @@ def test_every_entry_point_has_resource_figures():
                "softmax": ["softmax"], "layernorm": ["layernorm"],
                "gemm": ["gemm", "gemm_n128", "gemm_allgather", "gemm_allgather_n128", "gemm_split_a", "gemm_prep_b",
                         "gemm_colmax_b", "gemm_split_bt", "replicate_run"],
-               "attention": ["attention", "attention_causal", "attention_allgather", "attention_split"]}
+               "attention": ["attention", "attention_masked", "attention_allgather", "attention_split"]}
     for kernel, names in entries.items():
         for entry in names:
             fig, text = kh.kernel_resources(kernel, entry)
@@ -449,7 +451,7 @@ def test_sharded_bench_row_refusals():
 def test_attention_causal_shape_key():
     """`causal` is an optional 0/1 key of the attention template (not one of the reference's)."""
     p = kh.plan("attention", "batch=8,heads=16,seq=1024,head_dim=64,causal=1")
-    assert p.entry == b"attention_causal" and p.work == 4.0 * 128 * (1024 * 1025 / 2) * 64
+    assert p.entry == b"attention_masked" and p.work == 4.0 * 128 * (1024 * 1025 / 2) * 64
     assert kh.plan("attention", "batch=8,heads=16,seq=1024,head_dim=64,causal=0").work == 34359738368.0
     with pytest.raises(kh.KernelhError) as e:
         kh.plan("attention", "batch=8,heads=16,seq=1024,head_dim=64,causal=2")
