@@ -750,7 +750,7 @@ __device__ __forceinline__ void gemm_body(int64_t m, int64_t n, float *__restric
                                                const khd::TensorMap &tm_b_lo, int64_t k_blocks,
                                                uint32_t *status, const int *__restrict__ a_shift,
                                                const int *__restrict__ b_shift, int64_t raster, uint64_t alpha_beta,
-                                               float *__restrict__ partials, unsigned int *partial_flags,
+                                               float *__restrict__ partials, unsigned int *partial_flags, int64_t split_plan,
                                                const GatherTargets *targets) {
   extern __shared__ uint8_t smem_raw[];
   // C = alpha * A.B + beta * C_old; alpha in the low and beta in the high 32 bits (1 and 0: a plain store)
@@ -780,24 +780,30 @@ __device__ __forceinline__ void gemm_body(int64_t m, int64_t n, float *__restric
   const int64_t tiles_m = (m + 2 * kBM - 1) / (2 * kBM), tiles_n = (n + BN - 1) / BN;
   const int64_t num_tiles = tiles_m * tiles_n;
   const int64_t first_tile = blockIdx.x >> 1, tile_step = gridDim.x >> 1;
-  // Work units. Whole tiles first; when `partials` is given, the tiles of the last, partly filled
-  // wave of clusters (num_tiles mod the cluster count, at most half a wave: the host decides) are
-  // each done as TWO units, one per half of K, by two neighbouring clusters at the same time: the
-  // last wave then takes half as long. The unit that finishes first leaves its 128 x BN partial
-  // sums in `partials`; the second adds them to its own and stores the tile (epilogue below).
-  const int64_t whole_tiles = partials != nullptr ? (num_tiles / tile_step) * tile_step : num_tiles;
-  const int64_t num_units = whole_tiles + 2 * (num_tiles - whole_tiles);
+  // Work units. A tile is normally one unit. Where the host asks for it (`split_plan`: tiles at the
+  // head of the list in its low half, at the tail in its high half), a tile is done as TWO units, one
+  // per half of K, by two neighbouring clusters at the same time; the unit that finishes first leaves
+  // its 128 x BN partial sums in `partials`, the second adds them to its own and stores the tile
+  // (epilogue below). At the tail that is the last, partly filled wave of clusters, which then takes
+  // half as long; at the head (fused all-gather of a short shard only) it makes the first tiles, and
+  // with them the traffic over NVLink that bounds such a launch, start after half a tile's time.
+  const int64_t head_tiles = partials != nullptr ? (split_plan & 0xffffffff) : 0;
+  const int64_t tail_tiles = partials != nullptr ? (split_plan >> 32) : 0;
+  const int64_t whole_tiles = num_tiles - head_tiles - tail_tiles;
+  const int64_t num_units = 2 * head_tiles + whole_tiles + 2 * tail_tiles;
   struct Unit {
     int64_t tile, kb0, kb1;
     int slot; // index of the shared tile among the split ones, or -1 for a whole tile
   };
   const auto unit_of = [&](int64_t u) -> Unit {
-    if (u < whole_tiles) return {u, 0, k_blocks, -1};
-    const int64_t v = u - whole_tiles;
     const int64_t half_blocks = k_blocks / 2;
-    return {whole_tiles + (v >> 1), (v & 1) ? half_blocks : 0, (v & 1) ? k_blocks : half_blocks, static_cast<int>(v >> 1)};
+    if (u < 2 * head_tiles)
+      return {u >> 1, (u & 1) ? half_blocks : 0, (u & 1) ? k_blocks : half_blocks, static_cast<int>(u >> 1)};
+    if (u < 2 * head_tiles + whole_tiles) return {head_tiles + (u - 2 * head_tiles), 0, k_blocks, -1};
+    const int64_t v = u - 2 * head_tiles - whole_tiles;
+    return {head_tiles + whole_tiles + (v >> 1), (v & 1) ? half_blocks : 0, (v & 1) ? k_blocks : half_blocks,
+            static_cast<int>(head_tiles + (v >> 1))};
   };
-
   // The SM clock this launch really ran at: block 0 counts its SM's cycles against the global
   // nanosecond timer over its whole life and leaves both in the status buffer (bytes 32..47),
   // where the host reads them beside the management library's figure.
@@ -1095,12 +1101,12 @@ gemm(KH_MEMREF2(const float, a), KH_MEMREF2(const float, b), KH_MEMREF2(float, c
      const __grid_constant__ khd::TensorMap tm_a_hi, const __grid_constant__ khd::TensorMap tm_a_lo,
      const __grid_constant__ khd::TensorMap tm_b_hi, const __grid_constant__ khd::TensorMap tm_b_lo,
      int64_t k_blocks, uint32_t *status, const int *a_shift, const int *b_shift, int64_t raster, uint64_t alpha_beta,
-     float *partials, unsigned int *partial_flags) {
+     float *partials, unsigned int *partial_flags, int64_t split_plan) {
   (void)a_alloc; (void)a_ptr; (void)a_off; (void)a_size1; (void)a_stride0; (void)a_stride1;
   (void)b_alloc; (void)b_ptr; (void)b_off; (void)b_size0; (void)b_stride0; (void)b_stride1;
   (void)c_alloc; (void)c_size0; (void)c_size1;
   gemm_body<false, kBN>(a_size0, b_size1, KH_DATA(c), c_stride0, c_stride1, tm_a_hi, tm_a_lo, tm_b_hi, tm_b_lo,
-                        k_blocks, status, a_shift, b_shift, raster, alpha_beta, partials, partial_flags, nullptr);
+                        k_blocks, status, a_shift, b_shift, raster, alpha_beta, partials, partial_flags, split_plan, nullptr);
 }
 
 // The same with 256 x 128 tiles (the tensor maps of B then have boxes of 64 rows): taken by the
@@ -1110,12 +1116,12 @@ gemm_n128(KH_MEMREF2(const float, a), KH_MEMREF2(const float, b), KH_MEMREF2(flo
           const __grid_constant__ khd::TensorMap tm_a_hi, const __grid_constant__ khd::TensorMap tm_a_lo,
           const __grid_constant__ khd::TensorMap tm_b_hi, const __grid_constant__ khd::TensorMap tm_b_lo,
           int64_t k_blocks, uint32_t *status, const int *a_shift, const int *b_shift, int64_t raster, uint64_t alpha_beta,
-     float *partials, unsigned int *partial_flags) {
+     float *partials, unsigned int *partial_flags, int64_t split_plan) {
   (void)a_alloc; (void)a_ptr; (void)a_off; (void)a_size1; (void)a_stride0; (void)a_stride1;
   (void)b_alloc; (void)b_ptr; (void)b_off; (void)b_size0; (void)b_stride0; (void)b_stride1;
   (void)c_alloc; (void)c_size0; (void)c_size1;
   gemm_body<false, 128>(a_size0, b_size1, KH_DATA(c), c_stride0, c_stride1, tm_a_hi, tm_a_lo, tm_b_hi, tm_b_lo,
-                        k_blocks, status, a_shift, b_shift, raster, alpha_beta, partials, partial_flags, nullptr);
+                        k_blocks, status, a_shift, b_shift, raster, alpha_beta, partials, partial_flags, split_plan, nullptr);
 }
 
 // The M-row-sharded product with the all-gather fused into the epilogue: `a`
@@ -1129,12 +1135,12 @@ gemm_allgather(KH_MEMREF2(const float, a), KH_MEMREF2(const float, b),
                const __grid_constant__ khd::TensorMap tm_a_hi, const __grid_constant__ khd::TensorMap tm_a_lo,
                const __grid_constant__ khd::TensorMap tm_b_hi, const __grid_constant__ khd::TensorMap tm_b_lo,
                int64_t k_blocks, uint32_t *status, const int *a_shift, const int *b_shift, int64_t raster,
-               uint64_t alpha_beta, float *partials, unsigned int *partial_flags,
+               uint64_t alpha_beta, float *partials, unsigned int *partial_flags, int64_t split_plan,
                const __grid_constant__ GatherTargets targets) {
   (void)a_alloc; (void)a_ptr; (void)a_off; (void)a_size1; (void)a_stride0; (void)a_stride1;
   (void)b_alloc; (void)b_ptr; (void)b_off; (void)b_size0; (void)b_stride0; (void)b_stride1;
   gemm_body<true, kBN>(a_size0, b_size1, nullptr, 0, 0, tm_a_hi, tm_a_lo, tm_b_hi, tm_b_lo, k_blocks, status,
-                       a_shift, b_shift, raster, alpha_beta, partials, partial_flags, &targets);
+                       a_shift, b_shift, raster, alpha_beta, partials, partial_flags, split_plan, &targets);
 }
 
 // gemm_allgather with 256 x 128 tiles (see gemm_n128).
@@ -1143,12 +1149,12 @@ gemm_allgather_n128(KH_MEMREF2(const float, a), KH_MEMREF2(const float, b),
                     const __grid_constant__ khd::TensorMap tm_a_hi, const __grid_constant__ khd::TensorMap tm_a_lo,
                     const __grid_constant__ khd::TensorMap tm_b_hi, const __grid_constant__ khd::TensorMap tm_b_lo,
                     int64_t k_blocks, uint32_t *status, const int *a_shift, const int *b_shift, int64_t raster,
-                    uint64_t alpha_beta, float *partials, unsigned int *partial_flags,
+                    uint64_t alpha_beta, float *partials, unsigned int *partial_flags, int64_t split_plan,
                     const __grid_constant__ GatherTargets targets) {
   (void)a_alloc; (void)a_ptr; (void)a_off; (void)a_size1; (void)a_stride0; (void)a_stride1;
   (void)b_alloc; (void)b_ptr; (void)b_off; (void)b_size0; (void)b_stride0; (void)b_stride1;
   gemm_body<true, 128>(a_size0, b_size1, nullptr, 0, 0, tm_a_hi, tm_a_lo, tm_b_hi, tm_b_lo, k_blocks, status,
-                       a_shift, b_shift, raster, alpha_beta, partials, partial_flags, &targets);
+                       a_shift, b_shift, raster, alpha_beta, partials, partial_flags, split_plan, &targets);
 }
 
 // Sends a run of floats of this GPU's copy of a replicated buffer to the same place in every

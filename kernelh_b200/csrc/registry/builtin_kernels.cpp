@@ -355,7 +355,7 @@ std::vector<LaunchStep> gemm_steps(int64_t m, int64_t n, int64_t k, const Device
   const int64_t tiles = narrow ? tiles128 : tiles256;
   g.grid = {static_cast<unsigned>(2 * std::min<int64_t>(tiles, clusters)), 1, 1};
   g.dynamic_smem = kGemmStages * kGemmStageBytes + 1024;
-  g.param_count = 21 + 4 + 2 + 2 + 1 + 1 + 2;
+  g.param_count = 21 + 4 + 2 + 2 + 1 + 1 + 3;
   g.tmem_columns = 512;
   return {sa, cm, sb, g};
 }
@@ -555,29 +555,63 @@ Result<void> gemm_enqueue_multiply(const GemmJob &j, const void *a_rows, const v
   std::memcpy(&alpha_bits, &j.alpha, 4);
   std::memcpy(&beta_bits, &j.beta, 4);
   args.add_scalar<uint64_t>(static_cast<uint64_t>(alpha_bits) | (static_cast<uint64_t>(beta_bits) << 32));
-  // The last, partly filled wave of clusters: when it holds at most half a wave of tiles (and there is
-  // at least one full wave before it), each of its tiles is done by two clusters, half of K each, and
-  // the wave takes half as long (2048 x 8192 x 8192, the 4-GPU shard: 3.46 waves become 3.5 half-paid
-  // instead of 4). The halves meet in a scratch of partial sums; flags zeroed before every such launch.
+  // Tiles done as two units, half of K each, by two clusters at once (partial sums meet in scratch):
+  //  - at the TAIL: the last, partly filled wave of clusters, when it holds at most half a wave of tiles
+  //    and there is a full wave before it; it then takes half as long (2048 x 8192 x 8192, the 4-GPU
+  //    shard: 3.46 waves are paid as 3.5 instead of 4);
+  //  - at the HEAD, only with the fused all-gather of a short shard (fewer than 2.5 waves of tiles) whose
+  //    traffic into every GPU, started after the first wave, would outlast the tensor work: half a wave of
+  //    tiles, so that the first tiles are finished, and NVLink starts, after half a tile's time; taken
+  //    only when it costs no wave (1024 x 8192 x 8192, the 8-GPU shard: 0.5 + 1 + 0.5 waves instead of
+  //    1 + 1, with the first push at 0.5 instead of 1).
+  // The meeting flags are zeroed before every such launch. KERNELH_GEMM_SPLIT_TAIL=0 switches both off.
   void *partials = nullptr, *partial_flags = nullptr;
+  int64_t split_plan = 0;
   {
     const int64_t clusters = step.grid.x / 2;
     const int64_t tile_cols = narrow ? 128 : 256;
     const int64_t tiles = ((rows + 2 * kGemmBM - 1) / (2 * kGemmBM)) * ((j.n + tile_cols - 1) / tile_cols);
-    const int64_t left = tiles % clusters;
     const int64_t k_blocks = j.kp / kGemmBK;
-    const char *off = std::getenv("KERNELH_GEMM_SPLIT_TAIL"); // "0" switches it off (measurements)
-    if (tiles > clusters && left > 0 && 2 * left <= clusters && k_blocks % 16 == 0 && !(off && off[0] == '0')) {
-      auto scratch = j.ex.gemm_partials(static_cast<size_t>(left) * 2 * kGemmBM * static_cast<size_t>(tile_cols) * 4,
-                                        static_cast<size_t>(left) * 2 * 2 * 4);
+    const char *off = std::getenv("KERNELH_GEMM_SPLIT_TAIL");
+    const bool allowed = k_blocks % 16 == 0 && !(off && off[0] == '0');
+    const auto tail_of = [&](int64_t t) { // tiles of the last wave worth splitting, else 0
+      const int64_t left = t % clusters;
+      return (t > clusters && left > 0 && 2 * left <= clusters) ? left : int64_t{0};
+    };
+    const auto half_waves = [&](int64_t t) { // cost of t tiles in half waves, with the tail rule
+      const int64_t left = t % clusters;
+      return 2 * (t / clusters) + (left == 0 ? 0 : (tail_of(t) > 0 ? 1 : 2));
+    };
+    int64_t head = 0;
+    if (allowed && gather != nullptr && tiles > clusters && 2 * tiles < 5 * clusters) {
+      const int64_t candidate = clusters / 2;
+      const char *force = std::getenv("KERNELH_GEMM_SPLIT_HEAD"); // "0" / "1": measurements
+      // Is the launch bound by what flows INTO this GPU? Every other rank sends a shard like this one;
+      // nothing can leave before the first tiles are done. Measured on this hardware: 770 GB/s into a
+      // GPU over NVLink, 0.153 ms for a wave of 256 x 256 x 8192 tiles (where the all-gather hides
+      // under the tensor work, splitting the head only costs: 0.491 against 0.475 ms on 4 GPUs).
+      const double wave_ms = 0.153 * static_cast<double>(k_blocks) / 256.0 * (narrow ? 0.74 : 1.0);
+      const double ingress_ms = static_cast<double>(gather->count - 1) * static_cast<double>(rows) *
+                                static_cast<double>(j.n) * 4.0 / 770e6;
+      const bool ingress_bound = wave_ms + ingress_ms > 0.5 * static_cast<double>(half_waves(tiles)) * wave_ms;
+      if ((ingress_bound && 1 + half_waves(tiles - candidate) <= half_waves(tiles) && !(force && force[0] == '0')) ||
+          (force && force[0] == '1'))
+        head = candidate;
+    }
+    const int64_t tail = allowed ? tail_of(tiles - head) : 0;
+    if (head + tail > 0) {
+      auto scratch = j.ex.gemm_partials(static_cast<size_t>(head + tail) * 2 * kGemmBM * static_cast<size_t>(tile_cols) * 4,
+                                        static_cast<size_t>(head + tail) * 2 * 2 * 4);
       if (!scratch) return std::unexpected(scratch.error());
       partials = scratch->first;
       partial_flags = scratch->second;
-      if (auto r = j.ex.backend().memset32_async(partial_flags, 0, static_cast<size_t>(left) * 4, stream); !r) return r;
+      split_plan = head | (tail << 32);
+      if (auto r = j.ex.backend().memset32_async(partial_flags, 0, static_cast<size_t>(head + tail) * 4, stream); !r) return r;
     }
   }
   args.add_scalar<uint64_t>(reinterpret_cast<uint64_t>(partials));
   args.add_scalar<uint64_t>(reinterpret_cast<uint64_t>(partial_flags));
+  args.add_scalar<int64_t>(split_plan);
   if (gather) {
     args.add_struct_bytes(gather, sizeof *gather);
     step.entry = narrow ? "gemm_allgather_n128" : "gemm_allgather";

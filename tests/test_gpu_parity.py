@@ -442,6 +442,31 @@ def test_gemm_last_wave_split_over_k(ctx, oracle):
     assert torch.equal(replicas[0], replicas[1])
 
 
+def test_gemm_allgather_short_shard_splits_its_first_tiles_too(ctx, oracle, monkeypatch):
+    """A shard of 128 tiles (1024 x 8192, what a rank has at 8 GPUs) in the fused all-gather: the
+    first 37 tiles AND the 17 of the last wave are each done by two clusters over half of K, so
+    that the first pushes leave after half a tile's time. Two ranks played one after the other;
+    every element of both replicas against fp64."""
+    m, n, k = 1024, 8192, 512
+    monkeypatch.setenv("KERNELH_GEMM_SPLIT_HEAD", "1")  # two ranks would not be bound by NVLink ingress: ask for it
+    a = oracle.uniform((2 * m, k), oracle.BASE_SEED + 91, -1, 1)
+    b = oracle.uniform((k, n), oracle.BASE_SEED + 92, -1, 1)
+    ref = (a.astype(np.float64) @ b.astype(np.float64)).astype(np.float32)
+    da, db = dev(a), dev(b)
+    replicas = [torch.full((2 * m, n), float("nan"), device="cuda") for _ in range(2)]
+    stream = torch.cuda.current_stream().cuda_stream
+    for _ in range(2):
+        for rank in range(2):
+            ctx.gemm_allgather(da[rank * m:(rank + 1) * m], db, replicas, rank, m, n, k, stream)
+        ctx.synchronize(stream)
+        for r in replicas:
+            cmp_ = oracle.compare(r.cpu().numpy(), ref)
+            assert cmp_.non_finite == 0 and cmp_.max_rel <= REL * math.sqrt(k) and cmp_.rel_frobenius <= 1e-5
+        assert torch.equal(replicas[0], replicas[1])
+        for r in replicas:
+            r.fill_(float("nan"))
+
+
 def test_gemm_scaled_store_alpha_beta(ctx, oracle):
     """C = alpha * A.B + beta * C (the first generalisation of the reference's plain store,
     lib/dsl/kernels/gemm.cpp:47-53): alpha = 1, beta = 0 is the plain gemm bit for bit and never
