@@ -583,7 +583,7 @@ Result<void> gemm_enqueue_multiply(const GemmJob &j, const void *a_rows, const v
       return 2 * (t / clusters) + (left == 0 ? 0 : (tail_of(t) > 0 ? 1 : 2));
     };
     int64_t head = 0;
-    if (allowed && gather != nullptr && tiles > clusters && 2 * tiles < 5 * clusters) {
+    if (allowed && gather != nullptr && tiles > clusters) {
       const int64_t candidate = clusters / 2;
       const char *force = std::getenv("KERNELH_GEMM_SPLIT_HEAD"); // "0" / "1": measurements
       // Is the launch bound by what flows INTO this GPU? Every other rank sends a shard like this one;
@@ -594,9 +594,8 @@ Result<void> gemm_enqueue_multiply(const GemmJob &j, const void *a_rows, const v
       const double ingress_ms = static_cast<double>(gather->count - 1) * static_cast<double>(rows) *
                                 static_cast<double>(j.n) * 4.0 / 770e6;
       const bool ingress_bound = wave_ms + ingress_ms > 0.5 * static_cast<double>(half_waves(tiles)) * wave_ms;
-      if ((ingress_bound && 1 + half_waves(tiles - candidate) <= half_waves(tiles) && !(force && force[0] == '0')) ||
-          (force && force[0] == '1'))
-        head = candidate;
+      const bool pays = 2 * tiles < 5 * clusters && ingress_bound && 1 + half_waves(tiles - candidate) <= half_waves(tiles);
+      if ((pays && !(force && force[0] == '0')) || (force && force[0] == '1')) head = candidate;
     }
     const int64_t tail = allowed ? tail_of(tiles - head) : 0;
     if (head + tail > 0) {
