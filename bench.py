@@ -44,10 +44,11 @@ def parse_args():
                          "(symmetric memory; one multimem.st per tile piece through the NVSwitch multicast "
                          "address when there is one, else plain peer stores) and a barrier follows; "
                          "'p2p-st' = the same, forcing plain peer stores; 'nccl' = plain gemm + NCCL all-gather")
-    ap.add_argument("--barrier", default="flags", choices=["flags", "symm"],
-                    help="N > 1 with --gather p2p: 'flags' = the gemm kernel ends with the barrier itself "
-                         "(arrival flags in symmetric memory, written after its last store and awaited by its "
-                         "last CTA); 'symm' = a symmetric-memory barrier launch after the kernel")
+    ap.add_argument("--barrier", default="overlap", choices=["overlap", "flags", "symm"],
+                    help="N > 1 with --gather p2p: 'overlap' = the gemm kernel signals its arrival (flags in "
+                         "symmetric memory, written after its last store) and the wait for the peers runs on a "
+                         "second stream beside the next step's operand preparation; 'flags' = the kernel's last CTA "
+                         "waits itself; 'symm' = a symmetric-memory barrier launch after the kernel")
     ap.add_argument("--csv", default="", help="N = 1: also write the rows of this run as results CSV with the "
                                               "appended columns (gpus, roofline_frac, max_rel_err, cpu_ms, cpu_cores)")
     ap.add_argument("--no-extras", action="store_true",
@@ -477,7 +478,7 @@ def gpu_arm(args) -> None:
             multicast = int(getattr(symm, "multicast_ptr", 0) or 0) if args.gather == "p2p" else 0
             c.zero_()
             gather = "p2p"
-            if args.barrier == "flags":
+            if args.barrier in ("flags", "overlap"):
                 # eight 64-bit arrival words per rank, zero before the first step
                 flag_words = symm_mem.empty((8,), dtype=torch.int64, device=torch.device("cuda", local_rank))
                 flag_symm = symm_mem.rendezvous(flag_words, dist.group.WORLD.group_name)
@@ -502,7 +503,7 @@ def gpu_arm(args) -> None:
     def fused_gather_launch():
         if flag_arrays is not None:  # every rank counts the same launches, so the epochs agree
             epoch[0] += 1
-            ctx.arm_arrival_flags(flag_arrays, epoch[0])
+            ctx.arm_arrival_flags(flag_arrays, epoch[0], overlapped=args.barrier == "overlap")
         if multicast:
             ctx.gemm_allgather_multicast(a_shard, b, c, multicast, world, rank, rows, size, size, stream)
         else:
@@ -532,6 +533,7 @@ def gpu_arm(args) -> None:
     e0.record()
     for _ in range(args.steps):
         step()
+    ctx.join_arrivals(stream)  # the last step's wait for the peers belongs to the timed region
     e1.record()
     torch.cuda.synchronize()
     barrier()
@@ -643,7 +645,9 @@ def gpu_arm(args) -> None:
                        "NCCL all-gather of C inside the timed step")) if world > 1 else "single GPU",
                    "l2": "inputs (2 x 256 MiB) and the 512 MiB operand-split scratch are larger than the 126 MB L2",
                    "step": "gemm_split_a + gemm_prep_b + " + {"none": "gemm", "nccl": "gemm + nccl all_gather",
-                                                                 "p2p": "gemm_allgather ending with its own arrival-flag barrier" if flag_arrays is not None
+                                                                 "p2p": ("gemm_allgather signalling its arrival, the wait for the peers on a second stream beside the "
+                                                                         "next step's preparation" if args.barrier == "overlap" else
+                                                                         "gemm_allgather ending with its own arrival-flag barrier") if flag_arrays is not None
                                                                  else "gemm_allgather + symmetric-memory barrier"}[gather]},
         "roofline": roofline, "gpu_launches": int(launches),
         "sampled_max_err_over_rms": err, "parity": parity,

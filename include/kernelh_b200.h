@@ -249,6 +249,15 @@ int kh_bench_row(kh_context *ctx, const char *kernel, const char *shape, int war
  * and grow from call to call, the same on every rank. Every rank must run on a GPU
  * of its own: kernels that wait for one another must never share a GPU. */
 int kh_arm_arrival_flags(kh_context *ctx, void *const *flag_arrays, int world, uint64_t epoch);
+/* The same barrier with its wait taken out of the kernel: the armed launch only signals, and the
+ * wait for the peers runs as a one-thread launch on a second stream of the context, behind the
+ * kernel and beside whatever the caller enqueues next - typically the next step's operand
+ * preparation, which needs nothing from the peers. The next kh_gemm_allgather* call of the context
+ * orders its gemm (not its preparation) behind that wait; kh_join_arrivals(ctx, stream) orders
+ * `stream` behind it (call it before reading C or recording an event that should include it), and
+ * kh_synchronize waits for it and reports a wait that ran out (1001) like any other. */
+int kh_arm_arrival_flags_overlapped(kh_context *ctx, void *const *flag_arrays, int world, uint64_t epoch);
+int kh_join_arrivals(kh_context *ctx, void *stream);
 
 /* The SM clock the last gemm launch of this context really ran at: block 0 of the
  * kernel counts its SM's cycles against the GPU's nanosecond timer over its whole

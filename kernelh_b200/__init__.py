@@ -109,6 +109,8 @@ def _load() -> C.CDLL:
     L.kh_enable_peer_access.argtypes = [vp, vp]
     L.kh_gemm_scaled.argtypes = [vp, f32p, f32p, f32p, i64, i64, i64, C.c_float, C.c_float, vp]
     L.kh_arm_arrival_flags.argtypes = [vp, C.POINTER(vp), C.c_int, C.c_uint64]
+    L.kh_arm_arrival_flags_overlapped.argtypes = [vp, C.POINTER(vp), C.c_int, C.c_uint64]
+    L.kh_join_arrivals.argtypes = [vp, vp]
     L.kh_gemm_clock.argtypes = [vp, C.POINTER(C.c_uint64), C.POINTER(C.c_uint64)]
     L.kh_bench_sharded.argtypes = [C.c_int, C.c_char_p, C.c_char_p, C.c_int, C.c_int,
                                    C.POINTER(C.c_double), C.POINTER(C.c_double), C.POINTER(C.c_int)]
@@ -247,12 +249,19 @@ class Context:
         """C = alpha * A.B + beta * C (beta = 0 never reads C)."""
         _check(lib.kh_gemm_scaled(self._h, _ptr(a), _ptr(b), _ptr(c), m, n, k, alpha, beta, stream))
 
-    def arm_arrival_flags(self, flag_arrays, epoch: int):
+    def arm_arrival_flags(self, flag_arrays, epoch: int, overlapped: bool = False):
         """The next gemm_allgather / gemm_allgather_multicast call of this context ends with the
         barrier itself: `flag_arrays` are every rank's eight-word int64 arrays (addresses as mapped
-        here, e.g. a symmetric-memory buffer's `buffer_ptrs`), `epoch` a positive, growing number."""
+        here, e.g. a symmetric-memory buffer's `buffer_ptrs`), `epoch` a positive, growing number.
+        `overlapped`: the kernel only signals; the wait runs on a second stream beside what is enqueued
+        next (see join_arrivals)."""
         arr = (C.c_void_p * len(flag_arrays))(*[C.c_void_p(int(p)) for p in flag_arrays])
-        _check(lib.kh_arm_arrival_flags(self._h, arr, len(flag_arrays), epoch))
+        fn = lib.kh_arm_arrival_flags_overlapped if overlapped else lib.kh_arm_arrival_flags
+        _check(fn(self._h, arr, len(flag_arrays), epoch))
+
+    def join_arrivals(self, stream=None):
+        """Orders `stream` behind the wait of the last overlapped arrival barrier, if one is running."""
+        _check(lib.kh_join_arrivals(self._h, stream))
 
     def gemm_clock(self):
         """(SM cycles, nanoseconds) block 0 of the last gemm launch counted over its life; call after

@@ -421,6 +421,18 @@ int kh_arm_arrival_flags(kh_context *ctx, void *const *flag_arrays, int world, u
   return 0;
 }
 
+int kh_arm_arrival_flags_overlapped(kh_context *ctx, void *const *flag_arrays, int world, uint64_t epoch) {
+  if (int rc = kh_arm_arrival_flags(ctx, flag_arrays, world, epoch)) return rc;
+  ctx->exec->arm_arrival_flags(std::vector<void *>(flag_arrays, flag_arrays + world), epoch, /*overlap=*/true);
+  return 0;
+}
+
+int kh_join_arrivals(kh_context *ctx, void *stream) {
+  if (int rc = need_ctx(ctx)) return rc;
+  auto r = ctx->exec->join_arrival_wait(stream);
+  return r ? 0 : set_error(r.error());
+}
+
 int kh_gemm_clock(kh_context *ctx, uint64_t *sm_cycles, uint64_t *nanoseconds) {
   if (int rc = need_ctx(ctx)) return rc;
   uint64_t record[2] = {0, 0};

@@ -425,17 +425,12 @@ struct GatherTargets {
   unsigned long long *flags[8];
   unsigned long long epoch;
   unsigned int *finished; // this GPU's count of CTAs that are done; 0 between launches
+  int wait_later;         // the kernel only signals; `await_arrivals` does the waiting
 };
 
-// Runs once per CTA, by one thread, after the CTA's last store.
-__device__ __forceinline__ void signal_and_await_peers(const GatherTargets &t, uint32_t *status) {
-  __threadfence_system(); // this CTA's stores (peer stores and multimem.st included) before the count
-  if (atomicAdd(t.finished, 1u) != gridDim.x - 1) return;
-  *t.finished = 0; // the next launch on this stream starts from zero again
-  __threadfence_system(); // every CTA's stores before the flags
-  for (int d = 0; d < t.count; ++d)
-    if (d != t.self)
-      asm volatile("st.release.sys.global.u64 [%0], %1;" ::"l"(t.flags[d] + t.self), "l"(t.epoch) : "memory");
+// The wait half of the arrival barrier: until this GPU's flag array holds at least `epoch` in every
+// other rank's word, for at most two seconds (then: status code, the missing rank as detail, return).
+__device__ __forceinline__ void await_peers(const GatherTargets &t, uint32_t *status) {
   unsigned long long start;
   asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(start));
   for (int d = 0; d < t.count; ++d) {
@@ -452,6 +447,20 @@ __device__ __forceinline__ void signal_and_await_peers(const GatherTargets &t, u
       __nanosleep(100);
     }
   }
+}
+
+// Runs once per CTA, by one thread, after the CTA's last store. The last CTA of the launch signals
+// every peer and, unless the wait was handed to a later `await_arrivals` launch (`wait_later`: the
+// host runs that one beside the next step's operand preparation), waits for the peers itself.
+__device__ __forceinline__ void signal_and_await_peers(const GatherTargets &t, uint32_t *status) {
+  __threadfence_system(); // this CTA's stores (peer stores and multimem.st included) before the count
+  if (atomicAdd(t.finished, 1u) != gridDim.x - 1) return;
+  *t.finished = 0; // the next launch on this stream starts from zero again
+  __threadfence_system(); // every CTA's stores before the flags
+  for (int d = 0; d < t.count; ++d)
+    if (d != t.self)
+      asm volatile("st.release.sys.global.u64 [%0], %1;" ::"l"(t.flags[d] + t.self), "l"(t.epoch) : "memory");
+  if (!t.wait_later) await_peers(t, status);
 }
 
 struct TileCoord {
@@ -1155,6 +1164,15 @@ gemm_allgather_n128(KH_MEMREF2(const float, a), KH_MEMREF2(const float, b),
   (void)b_alloc; (void)b_ptr; (void)b_off; (void)b_size0; (void)b_stride0; (void)b_stride1;
   gemm_body<true, 128>(a_size0, b_size1, nullptr, 0, 0, tm_a_hi, tm_a_lo, tm_b_hi, tm_b_lo, k_blocks, status,
                        a_shift, b_shift, raster, alpha_beta, partials, partial_flags, split_plan, &targets);
+}
+
+// The wait half of the arrival barrier as a launch of its own (one thread): the host puts it on a
+// second stream behind a `gemm_allgather` that only signalled, so that the wait for the other GPUs'
+// tiles runs beside the next step's operand preparation; the next `gemm_allgather` is ordered behind it.
+// It waits for kernels of OTHER GPUs only. Bounded like every wait here.
+extern "C" __global__ void __launch_bounds__(32)
+await_arrivals(const __grid_constant__ GatherTargets targets, uint32_t *status) {
+  if (blockIdx.x == 0 && threadIdx.x == 0) await_peers(targets, status);
 }
 
 // Sends a run of floats of this GPU's copy of a replicated buffer to the same place in every

@@ -388,8 +388,9 @@ struct GatherTargets {
   unsigned long long *flags[8]; // arrival flags of every rank as mapped here; used when epoch != 0
   unsigned long long epoch;
   unsigned int *finished;       // this GPU's finished-CTA counter (in the executor's status buffer)
+  int wait_later;               // signal only; await_arrivals waits (on the executor's second stream)
 };
-static_assert(sizeof(GatherTargets) == 168 && sizeof(GatherTargets) <= LaunchArgs::kMaxStructBytes,
+static_assert(sizeof(GatherTargets) == 176 && sizeof(GatherTargets) <= LaunchArgs::kMaxStructBytes,
               "GatherTargets is passed by value: its layout is shared with kernels/gemm.cu");
 
 // One product being enqueued: sizes, scratch and the entry points.
@@ -614,6 +615,9 @@ Result<void> gemm_enqueue_multiply(const GemmJob &j, const void *a_rows, const v
   if (gather) {
     args.add_struct_bytes(gather, sizeof *gather);
     step.entry = narrow ? "gemm_allgather_n128" : "gemm_allgather";
+    // a wait for the previous launch's peers that is still running beside this step's preparation:
+    // the tiles of this launch go out only after it (the peers have then taken the previous ones in)
+    if (auto r = j.ex.join_arrival_wait(stream); !r) return r;
   }
   const KernelFunction &fn = gather ? (narrow ? j.multiply_gather_n128 : j.multiply_gather)
                                     : (narrow ? j.multiply_n128 : j.multiply);
@@ -791,8 +795,18 @@ Result<void> run_gemm_allgather(Executor &ex, const void *a_shard, const void *b
     }
     t.epoch = armed.epoch;
     t.finished = reinterpret_cast<unsigned int *>(ex.status_word()) + 16;
+    t.wait_later = armed.overlap ? 1 : 0;
   }
-  return launch_gemm(ex, plan, {const_cast<void *>(a_shard), const_cast<void *>(b), nullptr}, stream, &t);
+  if (auto r = launch_gemm(ex, plan, {const_cast<void *>(a_shard), const_cast<void *>(b), nullptr}, stream, &t); !r)
+    return r;
+  if (t.wait_later) {
+    // the wait for the peers, on the executor's second stream, ordered behind this launch; the NEXT
+    // fused launch (or kh_join_arrivals / kh_synchronize) is ordered behind it
+    auto fn = ex.function("gemm", "await_arrivals");
+    if (!fn) return std::unexpected(fn.error());
+    return ex.enqueue_arrival_wait(*fn, &t, sizeof t, stream);
+  }
+  return {};
 }
 
 // The scan launched so that its first look-back can never succeed: every ticket is shifted

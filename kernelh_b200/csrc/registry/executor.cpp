@@ -30,8 +30,10 @@ Result<std::unique_ptr<Executor>> Executor::create(std::shared_ptr<Backend> back
 }
 
 Executor::~Executor() {
-  for (StreamHandle s : {host_stream_, host_in_stream_, host_out_stream_})
+  for (StreamHandle s : {host_stream_, host_in_stream_, host_out_stream_, arrival_stream_})
     if (backend_ && s) (void)backend_->stream_destroy(s);
+  for (EventHandle e : {arrival_launched_, arrival_seen_})
+    if (backend_ && e) (void)backend_->event_destroy(e);
 }
 
 Result<KernelFunction> Executor::function(const std::string &code_object, const std::string &entry) {
@@ -207,6 +209,10 @@ Result<void> Executor::run(const std::string &kernel, const ShapeMap &shape,
 Result<void> Executor::synchronize(StreamHandle stream) {
   if (auto r = backend_->make_current(); !r) return r;
   if (auto r = backend_->stream_synchronize(stream); !r) return r;
+  if (arrival_pending_) { // a wait for the peers that runs on the second stream: it belongs to this work
+    arrival_pending_ = false;
+    if (auto r = backend_->stream_synchronize(arrival_stream_); !r) return r;
+  }
   uint32_t host[2] = {0, 0};
   if (auto r = backend_->memcpy_d2h(host, status_.data(), sizeof host); !r) return r;
   uint32_t scan_host[2] = {0, 0};
@@ -229,6 +235,40 @@ Result<void> Executor::synchronize(StreamHandle stream) {
   return fail(kDeviceTimeout, std::string("a device-side bounded wait ran out: ") + wait_name(code) + " (code " +
                                   std::to_string(code) + ", detail " + std::to_string(detail) +
                                   "); the kernel stopped and its output is incomplete");
+}
+
+Result<void> Executor::enqueue_arrival_wait(const KernelFunction &await, const void *targets, size_t bytes,
+                                            StreamHandle stream) {
+  if (arrival_stream_ == nullptr) {
+    auto s = backend_->stream_create();
+    if (!s) return std::unexpected(s.error());
+    arrival_stream_ = *s;
+    for (EventHandle *e : {&arrival_launched_, &arrival_seen_}) {
+      auto made = backend_->event_create();
+      if (!made) return std::unexpected(made.error());
+      *e = *made;
+    }
+  }
+  if (auto r = backend_->event_record(arrival_launched_, stream); !r) return r;
+  if (auto r = backend_->stream_wait_event(arrival_stream_, arrival_launched_); !r) return r;
+  LaunchStep step;
+  step.entry = "await_arrivals";
+  step.block = {32, 1, 1};
+  step.grid = {1, 1, 1};
+  step.param_count = 2;
+  LaunchArgs args;
+  args.add_struct_bytes(targets, bytes);
+  args.add_scalar<uint64_t>(reinterpret_cast<uint64_t>(status_word()));
+  if (auto r = launch(await, step, args, arrival_stream_); !r) return r;
+  if (auto r = backend_->event_record(arrival_seen_, arrival_stream_); !r) return r;
+  arrival_pending_ = true;
+  return {};
+}
+
+Result<void> Executor::join_arrival_wait(StreamHandle stream) {
+  if (!arrival_pending_) return {};
+  arrival_pending_ = false;
+  return backend_->stream_wait_event(stream, arrival_seen_);
 }
 
 Result<std::pair<void *, void *>> Executor::gemm_partials(size_t partial_bytes, size_t flag_bytes) {

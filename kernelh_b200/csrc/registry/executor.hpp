@@ -21,6 +21,7 @@ namespace kh {
 struct ArrivalFlags {
   std::vector<void *> flags;
   uint64_t epoch = 0;
+  bool overlap = false; // the kernel only signals; the wait runs as a launch of its own on a second stream
 };
 
 class Executor {
@@ -54,7 +55,13 @@ public:
   uint32_t *status_word() const { return static_cast<uint32_t *>(status_.data()); }
   // Arrival flags for the NEXT fused all-gather launch of this executor only (then disarmed): every
   // rank's flag array as mapped on this device, and the epoch to write and wait for (> 0, growing).
-  void arm_arrival_flags(std::vector<void *> flags, uint64_t epoch) { arrival_ = {std::move(flags), epoch}; }
+  void arm_arrival_flags(std::vector<void *> flags, uint64_t epoch, bool overlap = false) {
+    arrival_ = {std::move(flags), epoch, overlap};
+  }
+  // The overlapped wait: `await` (the gemm code object's await_arrivals) goes on a second stream behind
+  // what `stream` holds now; join_arrival_wait orders `stream` behind the last such wait, if any.
+  Result<void> enqueue_arrival_wait(const KernelFunction &await, const void *targets, size_t bytes, StreamHandle stream);
+  Result<void> join_arrival_wait(StreamHandle stream);
   ArrivalFlags take_arrival_flags() { return std::exchange(arrival_, ArrivalFlags{}); }
   // Scratch of the gemm's split last wave: partial sums and meeting flags (grow-only).
   Result<std::pair<void *, void *>> gemm_partials(size_t partial_bytes, size_t flag_bytes);
@@ -100,6 +107,9 @@ private:
     EventHandle start, end;
   };
   ArrivalFlags arrival_;
+  StreamHandle arrival_stream_ = nullptr;
+  EventHandle arrival_launched_ = nullptr, arrival_seen_ = nullptr;
+  bool arrival_pending_ = false;
   Buffer gemm_partials_, gemm_partial_flags_;
   bool profiling_ = false;
   std::vector<ProfiledLaunch> profiled_;

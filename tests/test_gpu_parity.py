@@ -550,6 +550,23 @@ def test_gemm_allgather_arrival_flags_signal_and_bounded_wait(ctx, oracle):
     assert flags[1][0].item() == 3  # it had signalled before it waited
     again = run(ctx, "gemm", f"m={m},n={n},k={k}", [da, db], (m, n))
     assert np.array_equal(again, plain)
+    # the overlapped form: the kernel only signals, a one-thread launch on the context's second stream
+    # waits; the next fused launch, join_arrivals and synchronize are ordered behind it
+    for epoch in (4, 5):
+        flags[0][1] = epoch
+        torch.cuda.current_stream().synchronize()
+        ctx.arm_arrival_flags([f.data_ptr() for f in flags], epoch, overlapped=True)
+        ctx.gemm_allgather(da[:256], db, replicas, 0, 256, n, k, stream)
+    ctx.join_arrivals(stream)
+    ctx.synchronize(stream)
+    assert flags[1][0].item() == 5
+    ctx.arm_arrival_flags([f.data_ptr() for f in flags], 6, overlapped=True)  # nobody sets 6 in my array
+    ctx.gemm_allgather(da[:256], db, replicas, 0, 256, n, k, stream)
+    with pytest.raises(kh.KernelhError) as e:
+        ctx.synchronize(stream)  # waits for the second stream too: its wait gave up after two seconds
+    assert e.value.code == kh.DEVICE_TIMEOUT and "code 6, detail 1" in e.value.message
+    assert flags[1][0].item() == 6
+    assert np.array_equal(run(ctx, "gemm", f"m={m},n={n},k={k}", [da, db], (m, n)), plain)
     with pytest.raises(kh.KernelhError):
         ctx.arm_arrival_flags([flags[0].data_ptr()], 1)  # one array: not a world
     with pytest.raises(kh.KernelhError):
