@@ -44,11 +44,12 @@ def parse_args():
                          "(symmetric memory; one multimem.st per tile piece through the NVSwitch multicast "
                          "address when there is one, else plain peer stores) and a barrier follows; "
                          "'p2p-st' = the same, forcing plain peer stores; 'nccl' = plain gemm + NCCL all-gather")
-    ap.add_argument("--barrier", default="overlap", choices=["overlap", "flags", "symm"],
-                    help="N > 1 with --gather p2p: 'overlap' = the gemm kernel signals its arrival (flags in "
-                         "symmetric memory, written after its last store) and the wait for the peers runs on a "
-                         "second stream beside the next step's operand preparation; 'flags' = the kernel's last CTA "
-                         "waits itself; 'symm' = a symmetric-memory barrier launch after the kernel")
+    ap.add_argument("--barrier", default="flags", choices=["flags", "overlap", "symm"],
+                    help="N > 1 with --gather p2p: 'flags' = the gemm kernel ends with the barrier itself (arrival "
+                         "flags in symmetric memory, written after its last store and awaited by its last CTA); "
+                         "'overlap' = the kernel only signals and the wait for the peers runs on a second stream "
+                         "beside the next step's operand preparation (measured: no faster, the kernel itself is as "
+                         "long as the traffic into the GPU); 'symm' = a symmetric-memory barrier launch after the kernel")
     ap.add_argument("--csv", default="", help="N = 1: also write the rows of this run as results CSV with the "
                                               "appended columns (gpus, roofline_frac, max_rel_err, cpu_ms, cpu_cores)")
     ap.add_argument("--no-extras", action="store_true",
