@@ -84,7 +84,6 @@ constexpr int kTmemCols = 512;              // two 256-column accumulators, used
 constexpr int kChunkBlocks = 8;             // k-blocks accumulated in tensor memory before a drain (K = 256)
 constexpr int kEpilogueWarps = 8;
 constexpr int kThreads = 64 + 32 * kEpilogueWarps; // TMA warp + MMA warp + epilogue warps
-constexpr int kMaxSplitParts = 4;            // a split tile's K goes to 2 or 4 units; one buffer of partial sums per part
 constexpr int kGroupM = 8;                  // default: pair tiles (256 rows) per rasterisation group (L2 reuse of B)
 
 // Ordered accesses for the epilogue (see the store loop of gemm_body).
@@ -791,33 +790,28 @@ __device__ __forceinline__ void gemm_body(int64_t m, int64_t n, float *__restric
   const int64_t num_tiles = tiles_m * tiles_n;
   const int64_t first_tile = blockIdx.x >> 1, tile_step = gridDim.x >> 1;
   // Work units. A tile is normally one unit. Where the host asks for it (`split_plan`: tiles at the
-  // head of the list in its low half, at the tail in its high half, each as a count in 24 bits and
-  // log2 of the number of parts above it), a tile is done as 2 or 4 units, one per part of K, by
-  // neighbouring clusters at the same time; the units that finish first leave their 128 x BN partial
-  // sums in `partials`, the last one adds all parts in the order of K and stores the tile (epilogue
-  // below). At the tail that is the last, partly filled wave of clusters, which then takes a half or
-  // a quarter as long; at the head (fused all-gather of a short shard only) it makes the first tiles,
-  // and with them the traffic over NVLink that bounds such a launch, start after a quarter of a
-  // tile's time.
-  const int64_t head_tiles = partials != nullptr ? (split_plan & 0xffffff) : 0;
-  const int64_t tail_tiles = partials != nullptr ? ((split_plan >> 32) & 0xffffff) : 0;
-  const int head_log2 = static_cast<int>((split_plan >> 24) & 0xff), tail_log2 = static_cast<int>((split_plan >> 56) & 0xff);
+  // head of the list in its low half, at the tail in its high half), a tile is done as TWO units, one
+  // per half of K, by two neighbouring clusters at the same time; the unit that finishes first leaves
+  // its 128 x BN partial sums in `partials`, the second adds them to its own and stores the tile
+  // (epilogue below). At the tail that is the last, partly filled wave of clusters, which then takes
+  // half as long; at the head (fused all-gather of a short shard only) it makes the first tiles, and
+  // with them the traffic over NVLink that bounds such a launch, start after half a tile's time.
+  const int64_t head_tiles = partials != nullptr ? (split_plan & 0xffffffff) : 0;
+  const int64_t tail_tiles = partials != nullptr ? (split_plan >> 32) : 0;
   const int64_t whole_tiles = num_tiles - head_tiles - tail_tiles;
-  const int64_t head_units = head_tiles << head_log2;
-  const int64_t num_units = head_units + whole_tiles + (tail_tiles << tail_log2);
+  const int64_t num_units = 2 * head_tiles + whole_tiles + 2 * tail_tiles;
   struct Unit {
     int64_t tile, kb0, kb1;
-    int slot;        // index of the shared tile among the split ones, or -1 for a whole tile
-    int part, parts; // which part of K, of how many
+    int slot; // index of the shared tile among the split ones, or -1 for a whole tile
   };
   const auto unit_of = [&](int64_t u) -> Unit {
-    if (u >= head_units && u < head_units + whole_tiles) return {head_tiles + (u - head_units), 0, k_blocks, -1, 0, 1};
-    const bool at_head = u < head_units;
-    const int log2 = at_head ? head_log2 : tail_log2;
-    const int64_t v = at_head ? u : u - head_units - whole_tiles;
-    const int64_t among = v >> log2, part = v & ((int64_t{1} << log2) - 1);
-    return {at_head ? among : head_tiles + whole_tiles + among, (part * k_blocks) >> log2, ((part + 1) * k_blocks) >> log2,
-            static_cast<int>(at_head ? among : head_tiles + among), static_cast<int>(part), 1 << log2};
+    const int64_t half_blocks = k_blocks / 2;
+    if (u < 2 * head_tiles)
+      return {u >> 1, (u & 1) ? half_blocks : 0, (u & 1) ? k_blocks : half_blocks, static_cast<int>(u >> 1)};
+    if (u < 2 * head_tiles + whole_tiles) return {head_tiles + (u - 2 * head_tiles), 0, k_blocks, -1};
+    const int64_t v = u - 2 * head_tiles - whole_tiles;
+    return {head_tiles + whole_tiles + (v >> 1), (v & 1) ? half_blocks : 0, (v & 1) ? k_blocks : half_blocks,
+            static_cast<int>(head_tiles + (v >> 1))};
   };
   // The SM clock this launch really ran at: block 0 counts its SM's cycles against the global
   // nanosecond timer over its whole life and leaves both in the status buffer (bytes 32..47),
@@ -979,38 +973,34 @@ __device__ __forceinline__ void gemm_body(int64_t m, int64_t n, float *__restric
       if (kGather) push_units<BN>(*targets, pending, kPushUnits, ew, lane, m, n);
 
       if (unit.slot >= 0) {
-        // A part of K: meet the other parts. Per split tile and CTA of the pair: flags[0] counts the
-        // arrivals, flags[1] the parts whose sums are in `partials` (one buffer per part).
+        // Half of K: meet the other half. Per split tile and CTA of the pair: flags[0] counts the
+        // arrivals, flags[1] says the first arrival's partial sums are in `partials`.
         unsigned int *flags = partial_flags + (static_cast<size_t>(unit.slot) * 2 + rank) * 2;
-        constexpr size_t kPartFloat4s = static_cast<size_t>(kBM) * BN / 4;
-        float4 *slot_sums = reinterpret_cast<float4 *>(partials) + (static_cast<size_t>(unit.slot) * 2 + rank) * kMaxSplitParts * kPartFloat4s +
-                            (static_cast<size_t>(quad * 32 + lane) * BN + half * (BN / 2)) / 4;
+        // A thread's j-th four sums sit at [warp][j][lane]: the thread at the same place of the other
+        // unit reads what this one wrote, so the layout is free, and this one makes a warp's accesses contiguous.
+        float4 *mine = reinterpret_cast<float4 *>(partials + (static_cast<size_t>(unit.slot) * 2 + rank) * (kBM * BN)) +
+                       static_cast<size_t>(ew) * (BN / 2 / 4) * 32 + lane;
         epilogue_barrier();
         if (ew == 0 && lane == 0) s_split_role = static_cast<int>(atomicAdd(flags, 1u));
         epilogue_barrier();
-        const bool last_unit = s_split_role == unit.parts - 1;
-        if (!last_unit || unit.parts > 2) {
-          // leave the partial sums (a row of this thread's half of the columns: 512 contiguous bytes). The
-          // last of four leaves its own too and reads them back, so that the sums below run in one order.
-          float4 *mine = slot_sums + unit.part * kPartFloat4s;
+        if (s_split_role == 0) {
+          // first: leave the partial sums
 #pragma unroll
           for (int j = 0; j < BN / 2 / 4; ++j)
-            mine[j] = make_float4(acc[4 * j], acc[4 * j + 1], acc[4 * j + 2], acc[4 * j + 3]);
-        }
-        if (!last_unit) {
+            mine[j * 32] = make_float4(acc[4 * j], acc[4 * j + 1], acc[4 * j + 2], acc[4 * j + 3]);
           __threadfence();
           epilogue_barrier();
-          if (ew == 0 && lane == 0) asm volatile("red.release.gpu.global.add.u32 [%0], %1;" ::"l"(flags + 1), "r"(1u) : "memory");
-          continue; // the last unit stores the tile
+          if (ew == 0 && lane == 0) asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(flags + 1), "r"(1u) : "memory");
+          continue; // the other unit stores the tile
         }
-        // last: wait (bounded) for the others' sums, take the flags back to zero, add in the order of K
+        // second: wait (bounded) for the first one's sums, take the flags back to zero, add
         if (ew == 0 && lane == 0) {
           unsigned long long start, now;
           asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(start));
           for (;;) {
             unsigned int ready;
             asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(ready) : "l"(flags + 1) : "memory");
-            if (ready + 1u >= static_cast<unsigned int>(unit.parts)) break;
+            if (ready != 0u) break;
             asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
             if (now - start > 2000000000ull) {
               khd::report_status(status, khd::kStatusEpilogueWaitTimeout, 9100u + static_cast<uint32_t>(unit.slot));
@@ -1027,30 +1017,10 @@ __device__ __forceinline__ void gemm_body(int64_t m, int64_t n, float *__restric
           ok = false;
           break;
         }
-        // The same additions in the same order whichever unit came last (a + b = b + a for two parts;
-        // for four, all parts are read back in the order of K): results do not depend on timing.
-        if (unit.parts == 2) {
-          const float4 *other = slot_sums + (unit.part ^ 1) * kPartFloat4s;
 #pragma unroll
-          for (int j = 0; j < BN / 2 / 4; ++j) {
-            const float4 term = __ldcg(other + j);
-            acc[4 * j] += term.x; acc[4 * j + 1] += term.y; acc[4 * j + 2] += term.z; acc[4 * j + 3] += term.w;
-          }
-        } else {
-#pragma unroll
-          for (int j = 0; j < BN / 2 / 4; ++j) {
-            const float4 term = __ldcg(slot_sums + j);
-            acc[4 * j] = term.x; acc[4 * j + 1] = term.y; acc[4 * j + 2] = term.z; acc[4 * j + 3] = term.w;
-          }
-#pragma unroll 1
-          for (int p = 1; p < unit.parts; ++p) {
-            const float4 *other = slot_sums + p * kPartFloat4s;
-#pragma unroll
-            for (int j = 0; j < BN / 2 / 4; ++j) {
-              const float4 term = __ldcg(other + j);
-              acc[4 * j] += term.x; acc[4 * j + 1] += term.y; acc[4 * j + 2] += term.z; acc[4 * j + 3] += term.w;
-            }
-          }
+        for (int j = 0; j < BN / 2 / 4; ++j) {
+          const float4 other = __ldcg(mine + j * 32);
+          acc[4 * j] += other.x; acc[4 * j + 1] += other.y; acc[4 * j + 2] += other.z; acc[4 * j + 3] += other.w;
         }
       }
 

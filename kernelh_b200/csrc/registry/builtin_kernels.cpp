@@ -556,20 +556,16 @@ Result<void> gemm_enqueue_multiply(const GemmJob &j, const void *a_rows, const v
   std::memcpy(&alpha_bits, &j.alpha, 4);
   std::memcpy(&beta_bits, &j.beta, 4);
   args.add_scalar<uint64_t>(static_cast<uint64_t>(alpha_bits) | (static_cast<uint64_t>(beta_bits) << 32));
-  // Tiles done as 2 or 4 units, a part of K each, by neighbouring clusters at once (partial sums meet in
-  // scratch; the unit that finishes last adds them in the order of K and stores the tile):
-  //  - at the TAIL: the last, partly filled wave of clusters, when there is a full wave before it and the
-  //    parts fill fewer quarter waves than the whole tiles' one wave (2048 x 8192 x 8192, the 4-GPU shard:
-  //    3.46 waves are paid as 3.5 instead of 4). Of 2 and 4 parts the cheaper; when they cost the same, 2,
-  //    or 4 with the fused all-gather (half of the split tiles are then finished, and sent, a quarter wave
-  //    before the end instead of all of them at the end);
+  // Tiles done as two units, half of K each, by two clusters at once (partial sums meet in scratch):
+  //  - at the TAIL: the last, partly filled wave of clusters, when it holds at most half a wave of tiles
+  //    and there is a full wave before it; it then takes half as long (2048 x 8192 x 8192, the 4-GPU
+  //    shard: 3.46 waves are paid as 3.5 instead of 4);
   //  - at the HEAD, only with the fused all-gather of a short shard (fewer than 2.5 waves of tiles) whose
   //    traffic into every GPU, started after the first wave, would outlast the tensor work: half a wave of
-  //    tiles in 4 parts, so that the first tiles are finished, and NVLink starts, after a quarter of a
-  //    tile's time; taken only when it costs no quarter wave (1024 x 8192 x 8192, the 8-GPU shard: 0.5 + 1 +
-  //    0.25 waves instead of 1 + 0.75, with the first push at 0.25 instead of 1).
-  // The meeting flags are zeroed before every such launch. KERNELH_GEMM_SPLIT_TAIL=0 switches both off,
-  // KERNELH_GEMM_SPLIT_PARTS=2 keeps to two parts (measurements).
+  //    tiles, so that the first tiles are finished, and NVLink starts, after half a tile's time; taken
+  //    only when it costs no wave (1024 x 8192 x 8192, the 8-GPU shard: 0.5 + 1 + 0.5 waves instead of
+  //    1 + 1, with the first push at 0.5 instead of 1).
+  // The meeting flags are zeroed before every such launch. KERNELH_GEMM_SPLIT_TAIL=0 switches both off.
   void *partials = nullptr, *partial_flags = nullptr;
   int64_t split_plan = 0;
   {
@@ -578,26 +574,16 @@ Result<void> gemm_enqueue_multiply(const GemmJob &j, const void *a_rows, const v
     const int64_t tiles = ((rows + 2 * kGemmBM - 1) / (2 * kGemmBM)) * ((j.n + tile_cols - 1) / tile_cols);
     const int64_t k_blocks = j.kp / kGemmBK;
     const char *off = std::getenv("KERNELH_GEMM_SPLIT_TAIL");
-    const char *parts_cap = std::getenv("KERNELH_GEMM_SPLIT_PARTS");
-    const bool allowed = k_blocks % 16 == 0 && !(off && off[0] == '0');        // halves are whole 256-deep chunks
-    const bool four = allowed && k_blocks % 32 == 0 && !(parts_cap && parts_cap[0] == '2'); // quarters too
-    struct Tail {
-      int64_t tiles, parts, quarter_waves;
-    };
-    const auto tail_of = [&](int64_t t) -> Tail { // the last wave of t tiles: how it is split and what it costs
+    const bool allowed = k_blocks % 16 == 0 && !(off && off[0] == '0');
+    const auto tail_of = [&](int64_t t) { // tiles of the last wave worth splitting, else 0
       const int64_t left = t % clusters;
-      if (left == 0) return {0, 1, 0};
-      Tail best{0, 1, 4};
-      if (!allowed || t <= clusters) return best;
-      const int64_t cost2 = 2 * ((2 * left + clusters - 1) / clusters), cost4 = (4 * left + clusters - 1) / clusters;
-      if (cost2 < best.quarter_waves) best = {left, 2, cost2};
-      if (four && (cost4 < best.quarter_waves || (cost4 == best.quarter_waves && best.parts == 2 && gather != nullptr)))
-        best = {left, 4, cost4};
-      return best;
+      return (t > clusters && left > 0 && 2 * left <= clusters) ? left : int64_t{0};
     };
-    const auto quarter_waves = [&](int64_t t) { return 4 * (t / clusters) + tail_of(t).quarter_waves; };
+    const auto half_waves = [&](int64_t t) { // cost of t tiles in half waves, with the tail rule
+      const int64_t left = t % clusters;
+      return 2 * (t / clusters) + (left == 0 ? 0 : (tail_of(t) > 0 ? 1 : 2));
+    };
     int64_t head = 0;
-    const int64_t head_parts = four ? 4 : 2;
     if (allowed && gather != nullptr && tiles > clusters) {
       const int64_t candidate = clusters / 2;
       const char *force = std::getenv("KERNELH_GEMM_SPLIT_HEAD"); // "0" / "1": measurements
@@ -608,21 +594,19 @@ Result<void> gemm_enqueue_multiply(const GemmJob &j, const void *a_rows, const v
       const double wave_ms = 0.153 * static_cast<double>(k_blocks) / 256.0 * (narrow ? 0.74 : 1.0);
       const double ingress_ms = static_cast<double>(gather->count - 1) * static_cast<double>(rows) *
                                 static_cast<double>(j.n) * 4.0 / 770e6;
-      const bool ingress_bound = wave_ms + ingress_ms > 0.25 * static_cast<double>(quarter_waves(tiles)) * wave_ms;
-      const bool pays = 2 * tiles < 5 * clusters && ingress_bound && 2 + quarter_waves(tiles - candidate) <= quarter_waves(tiles);
+      const bool ingress_bound = wave_ms + ingress_ms > 0.5 * static_cast<double>(half_waves(tiles)) * wave_ms;
+      const bool pays = 2 * tiles < 5 * clusters && ingress_bound && 1 + half_waves(tiles - candidate) <= half_waves(tiles);
       if ((pays && !(force && force[0] == '0')) || (force && force[0] == '1')) head = candidate;
     }
-    const Tail tail = tail_of(tiles - head);
-    if (head + tail.tiles > 0) {
-      const size_t slots = static_cast<size_t>(head + tail.tiles);
-      // per split tile and CTA of the pair: kMaxSplitParts (4) buffers of 128 x tile_cols sums, two flag words
-      auto scratch = j.ex.gemm_partials(slots * 2 * 4 * kGemmBM * static_cast<size_t>(tile_cols) * 4, slots * 2 * 2 * 4);
+    const int64_t tail = allowed ? tail_of(tiles - head) : 0;
+    if (head + tail > 0) {
+      auto scratch = j.ex.gemm_partials(static_cast<size_t>(head + tail) * 2 * kGemmBM * static_cast<size_t>(tile_cols) * 4,
+                                        static_cast<size_t>(head + tail) * 2 * 2 * 4);
       if (!scratch) return std::unexpected(scratch.error());
       partials = scratch->first;
       partial_flags = scratch->second;
-      const auto log2_of = [](int64_t parts) { return parts == 4 ? int64_t{2} : int64_t{1}; };
-      split_plan = head | (log2_of(head_parts) << 24) | (tail.tiles << 32) | (log2_of(tail.parts) << 56);
-      if (auto r = j.ex.backend().memset32_async(partial_flags, 0, slots * 4, stream); !r) return r;
+      split_plan = head | (tail << 32);
+      if (auto r = j.ex.backend().memset32_async(partial_flags, 0, static_cast<size_t>(head + tail) * 4, stream); !r) return r;
     }
   }
   args.add_scalar<uint64_t>(reinterpret_cast<uint64_t>(partials));

@@ -413,16 +413,13 @@ def test_gemm_8192_sampled_rows_and_scaling_property(ctx, oracle):
     assert np.array_equal(c2, c * 2)
 
 
-@pytest.mark.parametrize("k", [512, 1024])
-def test_gemm_last_wave_split_over_k(ctx, oracle, k):
-    """80 tiles on 74 clusters: the six tiles of the last wave are each done by two clusters (k = 512:
-    a half of K must be whole 256-deep chunks) or four (k = 1024), a part of K each, which meet
-    through a scratch of partial sums. Same bound against fp64 as any gemm; the rows of the split
-    tiles are the last ones in rasterised order, so all of C is compared. Twice in a row (the meeting
-    flags start from zero again, and the sums are added in one order whichever unit comes last: the
-    same bits), then through the fused all-gather with two ranks played one after the other, where
-    the split tiles are also pushed."""
-    m, n = 2560, 2048
+def test_gemm_last_wave_split_over_k(ctx, oracle):
+    """80 tiles on 74 clusters: the six tiles of the last wave are each done by two clusters,
+    half of K each, which meet through a scratch of partial sums. Same bound against fp64 as any
+    gemm; the rows of the split tiles are the last ones in rasterised order, so all of C is
+    compared. Three times in a row (the meeting flags start from zero again), then through the fused
+    all-gather with two ranks played one after the other, where the split tiles are also pushed."""
+    m, n, k = 2560, 2048, 512
     a = oracle.uniform((m, k), oracle.BASE_SEED + 81, -1, 1)
     b = oracle.uniform((k, n), oracle.BASE_SEED + 82, -1, 1)
     ref = (a.astype(np.float64) @ b.astype(np.float64)).astype(np.float32)
@@ -433,6 +430,7 @@ def test_gemm_last_wave_split_over_k(ctx, oracle, k):
         cmp_ = oracle.compare(c, ref)
         assert cmp_.non_finite == 0 and cmp_.max_rel <= REL * math.sqrt(k) and cmp_.rel_frobenius <= 1e-5
         runs.append(c)
+    # whichever unit comes last adds the same two numbers: the bits do not depend on timing
     assert np.array_equal(runs[0], runs[1]) and np.array_equal(runs[0], runs[2])
     replicas = [torch.full((2 * m, n), float("nan"), device="cuda") for _ in range(2)]
     stream = torch.cuda.current_stream().cuda_stream
@@ -448,18 +446,13 @@ def test_gemm_last_wave_split_over_k(ctx, oracle, k):
     assert torch.equal(replicas[0], replicas[1])
 
 
-@pytest.mark.parametrize("k,parts_cap", [(512, None), (1024, None), (1024, "2")])
-def test_gemm_allgather_short_shard_splits_its_first_tiles_too(ctx, oracle, monkeypatch, k, parts_cap):
+def test_gemm_allgather_short_shard_splits_its_first_tiles_too(ctx, oracle, monkeypatch):
     """A shard of 128 tiles (1024 x 8192, what a rank has at 8 GPUs) in the fused all-gather: the
-    first 37 tiles AND the 17 of the last wave are each done by four clusters over a quarter of K
-    (two over a half where a quarter is not whole 256-deep chunks, k = 512, or where the
-    environment keeps to two), so that the first pushes leave after a quarter of a tile's time.
-    Two ranks played one after the other; every element of both replicas against fp64. Without the
-    all-gather the same shape splits the 54 tiles of its last wave in four (three quarter waves)."""
-    m, n = 1024, 8192
+    first 37 tiles AND the 17 of the last wave are each done by two clusters over half of K, so
+    that the first pushes leave after half a tile's time. Two ranks played one after the other;
+    every element of both replicas against fp64."""
+    m, n, k = 1024, 8192, 512
     monkeypatch.setenv("KERNELH_GEMM_SPLIT_HEAD", "1")  # two ranks would not be bound by NVLink ingress: ask for it
-    if parts_cap:
-        monkeypatch.setenv("KERNELH_GEMM_SPLIT_PARTS", parts_cap)
     a = oracle.uniform((2 * m, k), oracle.BASE_SEED + 91, -1, 1)
     b = oracle.uniform((k, n), oracle.BASE_SEED + 92, -1, 1)
     ref = (a.astype(np.float64) @ b.astype(np.float64)).astype(np.float32)
@@ -476,9 +469,6 @@ def test_gemm_allgather_short_shard_splits_its_first_tiles_too(ctx, oracle, monk
         assert torch.equal(replicas[0], replicas[1])
         for r in replicas:
             r.fill_(float("nan"))
-    plain = run(ctx, "gemm", f"m={m},n={n},k={k}", [da[:m], db], (m, n))
-    cmp_ = oracle.compare(plain, ref[:m])
-    assert cmp_.non_finite == 0 and cmp_.max_rel <= REL * math.sqrt(k) and cmp_.rel_frobenius <= 1e-5
 
 
 def test_gemm_scaled_store_alpha_beta(ctx, oracle):
