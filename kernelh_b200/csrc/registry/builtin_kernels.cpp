@@ -667,10 +667,12 @@ namespace {
 // back down (the two directions of the link run at once). `dev` are device
 // staging buffers for A, B and C.
 // Row blocks of the host-buffer product: about eight blocks of whole 256-row cluster tiles
-// (sixteen measured slower: more launches and tensor maps per step than the shorter tail saves),
-// except that the LAST block is cut again into a half and two quarters: what follows the last
-// upload - that block's split, product and the trip of its rows of C back - is the part of the
-// step nothing overlaps, and it shrinks with the block.
+// (sixteen equal ones measured slower: more launches and tensor maps per step than the shorter tail
+// saves), except at the two ends. The LAST block is cut again into a half and two quarters: what
+// follows the last upload - that block's split, product and the trip of its rows of C back - is the
+// part of the step nothing overlaps, and it shrinks with the block. The FIRST block is cut the same
+// way, smallest first: the downloads of C take as long as the uploads of A, and they cannot start
+// before the first block's rows are up and multiplied.
 std::vector<std::pair<int64_t, int64_t>> host_row_blocks(int64_t m) {
   const int64_t block_rows = std::max<int64_t>(256, ((m + 7) / 8 + 255) / 256 * 256);
   std::vector<std::pair<int64_t, int64_t>> blocks;
@@ -681,6 +683,11 @@ std::vector<std::pair<int64_t, int64_t>> host_row_blocks(int64_t m) {
     blocks.push_back({last0, last_rows / 2});
     blocks.push_back({last0 + last_rows / 2, last_rows / 4});
     blocks.push_back({last0 + 3 * last_rows / 4, last_rows / 4});
+  }
+  const char *head = std::getenv("KERNELH_HOST_BLOCKS_HEAD"); // "0": the first block stays whole (measurements)
+  if (blocks.size() > 4 && block_rows >= 1024 && block_rows % 1024 == 0 && !(head && head[0] == '0')) {
+    blocks.erase(blocks.begin());
+    blocks.insert(blocks.begin(), {{0, block_rows / 4}, {block_rows / 4, block_rows / 4}, {block_rows / 2, block_rows / 2}});
   }
   return blocks;
 }
