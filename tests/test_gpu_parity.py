@@ -384,10 +384,11 @@ def test_gemm_subnormal_rows_and_columns(ctx, oracle):
     assert np.count_nonzero(c[:, 20]) > m // 2
 
 
-@pytest.mark.parametrize("m,n,k", [(2500, 384, 200), (256, 256, 64), (100, 40, 33)])
+@pytest.mark.parametrize("m,n,k", [(2500, 384, 200), (256, 256, 64), (100, 40, 33), (8192, 256, 64)])
 def test_gemm_host_path_is_pipelined_and_identical(ctx, oracle, m, n, k):
     """kh_run_host for gemm uploads A in row blocks and multiplies them while the
-    next block is on the wire; the result equals the device path bit for bit."""
+    next block is on the wire; the result equals the device path bit for bit. m = 8192 has the
+    benchmark's block list: 1024-row blocks with the first and the last cut into 256, 256 and 512 rows."""
     a = oracle.uniform((m, k), oracle.BASE_SEED + 11, -1, 1)
     b = oracle.uniform((k, n), oracle.BASE_SEED + 12, -1, 1)
     c_dev = run(ctx, "gemm", f"m={m},n={n},k={k}", [a, b], (m, n))
